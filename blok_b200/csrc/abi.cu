@@ -1,0 +1,39 @@
+// Error plumbing and small ABI-level helpers.
+#include <cstdarg>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace blok {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char *what) {
+  set_error("%s: %s", what, cudaGetErrorString(e));
+  return BLOK_ERR_CUDA;
+}
+
+int sm_count() {
+  static thread_local int cached_dev = -1, cached = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (dev != cached_dev) {
+    cudaDeviceProp p;
+    if (cudaGetDeviceProperties(&p, dev) != cudaSuccess) return 148;
+    cached = p.multiProcessorCount;
+    cached_dev = dev;
+  }
+  return cached;
+}
+
+}  // namespace blok
+
+extern "C" const char *blok_last_error(void) { return blok::g_error; }
+extern "C" int blok_abi_version(void) { return BLOK_ABI_VERSION; }

@@ -1,0 +1,269 @@
+// bf16 mat-vec for up to 8 tokens on mma.sync tensor cores, the dense SwiGLU MLP,
+// RMSNorm and the rounded residual add.
+// Reference arithmetic: src/kimi_exec.cu:272-298 (matvec_bf16_k, matvec_bf16_f32_k),
+// :674-686 (bf16_mlp), :258-270 (rmsnorm_k), :248-251 (add_k).
+//
+// Mapping of the mat-vec: a warp owns 16 weight rows (lane group g = lane/4 owns
+// rows g and g+8); a k-step is 32 columns, lane t = lane%4 loads the 8 consecutive
+// bf16 (one uint4) at column 8t of each of its two rows.  The B operand's column n
+// is token n, so lane (g, t) reads the same 8 columns of token g's activation row
+// from shared memory.  D[row][token] accumulates in fp32.
+#include "common.cuh"
+
+namespace blok {
+
+constexpr int kBfMaxWarps = 16;
+constexpr int kBfBatch = 4;  // k-steps (uint4 pairs) in flight per lane
+
+__host__ __device__ constexpr size_t bf16_x_row_bytes(int cols) { return (size_t)cols * 2 + 64; }
+
+// Stage T (<= 8) activation rows into shared memory with a 64-byte skew per row.
+__device__ __forceinline__ void stage_x_bf16(const uint16_t *x, unsigned char *smem, int cols, int T, int tid,
+                                             int nthreads) {
+  const int per_row = cols / 8;
+  for (int u = tid; u < per_row * T; u += nthreads) {
+    int tok = u / per_row, c = u - tok * per_row;
+    uint4 v = reinterpret_cast<const uint4 *>(x + (size_t)tok * cols)[c];
+    reinterpret_cast<uint4 *>(smem + tok * bf16_x_row_bytes(cols))[c] = v;
+  }
+}
+
+// Accumulate k-steps [ks0, ks0 + nsteps) for this warp's 16 rows.
+__device__ __forceinline__ void bf16_rows16_accumulate(const uint4 *__restrict__ w_lo, const uint4 *__restrict__ w_hi,
+                                                       const uint4 *xrow /*token g row, +t applied*/, int ks0,
+                                                       int nsteps, int t, float (&d)[4]) {
+  int s = 0;
+  for (; s + kBfBatch <= nsteps; s += kBfBatch) {
+    uint4 wl[kBfBatch], wh[kBfBatch];
+#pragma unroll
+    for (int k = 0; k < kBfBatch; ++k) {
+      wl[k] = ldg_stream(w_lo + (ks0 + s + k) * 4 + t);
+      wh[k] = ldg_stream(w_hi + (ks0 + s + k) * 4 + t);
+    }
+#pragma unroll
+    for (int k = 0; k < kBfBatch; ++k) {
+      uint4 xb = xrow[(ks0 + s + k) * 4];
+      mma_bf16_16816(d, wl[k].x, wh[k].x, wl[k].y, wh[k].y, xb.x, xb.y);
+      mma_bf16_16816(d, wl[k].z, wh[k].z, wl[k].w, wh[k].w, xb.z, xb.w);
+    }
+  }
+  for (; s < nsteps; ++s) {
+    uint4 wl = ldg_stream(w_lo + (ks0 + s) * 4 + t);
+    uint4 wh = ldg_stream(w_hi + (ks0 + s) * 4 + t);
+    uint4 xb = xrow[(ks0 + s) * 4];
+    mma_bf16_16816(d, wl.x, wh.x, wl.y, wh.y, xb.x, xb.y);
+    mma_bf16_16816(d, wl.z, wh.z, wl.w, wh.w, xb.z, xb.w);
+  }
+}
+
+// mode 0: y[t, row] plain mat-vec (rows from w_a only; CTA = 16 rows).
+// mode 1: SwiGLU front half (CTA = 8 gate rows from w_a + the same 8 up rows
+//         from w_b); writes mid = bf16(bf16(silu(bf16 g)) * bf16 u) to y_bf16 [T, rows].
+template <int MODE>
+__global__ void __launch_bounds__(kBfMaxWarps * 32)
+    bf16_gemv16_kernel(const uint16_t *__restrict__ w_a, const uint16_t *__restrict__ w_b,
+                       const uint16_t *__restrict__ x, uint16_t *__restrict__ y_bf16, float *__restrict__ y_f32,
+                       int rows, int cols, int T) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  __shared__ float partial[kBfMaxWarps][16][8];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  stage_x_bf16(x, smem, cols, T, tid, blockDim.x);
+  __syncthreads();
+  const size_t wrow = cols / 8;  // uint4 per row
+  const uint4 *w_lo, *w_hi;
+  if (MODE == 0) {
+    const int row0 = blockIdx.x * 16;
+    w_lo = reinterpret_cast<const uint4 *>(w_a) + (size_t)(row0 + g) * wrow;
+    w_hi = w_lo + 8 * wrow;
+  } else {
+    const int row0 = blockIdx.x * 8;
+    w_lo = reinterpret_cast<const uint4 *>(w_a) + (size_t)(row0 + g) * wrow;
+    w_hi = reinterpret_cast<const uint4 *>(w_b) + (size_t)(row0 + g) * wrow;
+  }
+  const int tok = g < T ? g : T - 1;
+  const uint4 *xrow = reinterpret_cast<const uint4 *>(smem + tok * bf16_x_row_bytes(cols)) + t;
+  // k-steps split as evenly as possible over the warps
+  const int ksteps = cols / 32;
+  const int base = ksteps / nwarps, rem = ksteps % nwarps;
+  const int ks0 = warp * base + (warp < rem ? warp : rem);
+  const int nsteps = base + (warp < rem ? 1 : 0);
+  float d[4] = {0.f, 0.f, 0.f, 0.f};
+  bf16_rows16_accumulate(w_lo, w_hi, xrow, ks0, nsteps, t, d);
+  partial[warp][g][2 * t] = d[0];
+  partial[warp][g][2 * t + 1] = d[1];
+  partial[warp][g + 8][2 * t] = d[2];
+  partial[warp][g + 8][2 * t + 1] = d[3];
+  __syncthreads();
+  if (MODE == 0) {
+    if (tid < 16 * 8) {
+      int r = tid >> 3, tk = tid & 7;
+      if (tk < T) {
+        float v = 0.f;
+        for (int wi = 0; wi < nwarps; ++wi) v += partial[wi][r][tk];
+        size_t o = (size_t)tk * rows + blockIdx.x * 16 + r;
+        if (y_f32) y_f32[o] = v;
+        else y_bf16[o] = f32_to_bf16_bits(v);
+      }
+    }
+  } else {
+    if (tid < 8 * 8) {
+      int r = tid >> 3, tk = tid & 7;
+      if (tk < T) {
+        float gv = 0.f, uv = 0.f;
+        for (int wi = 0; wi < nwarps; ++wi) {
+          gv += partial[wi][r][tk];
+          uv += partial[wi][r + 8][tk];
+        }
+        gv = round_bf16(gv);
+        uv = round_bf16(uv);
+        float m = round_bf16(round_bf16(gv / (1.0f + expf(-gv))) * uv);
+        y_bf16[(size_t)tk * rows + blockIdx.x * 8 + r] = f32_to_bf16_bits(m);
+      }
+    }
+  }
+}
+
+// Scalar fallback: one warp per (row, token); cols % 8 == 0, any rows.
+__global__ void bf16_gemv_scalar_kernel(const uint16_t *__restrict__ w, const uint16_t *__restrict__ x,
+                                        uint16_t *__restrict__ y_bf16, float *__restrict__ y_f32, int rows, int cols,
+                                        int T) {
+  int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= rows) return;
+  const uint4 *wr = reinterpret_cast<const uint4 *>(w + (size_t)warp * cols);
+  for (int tk = 0; tk < T; ++tk) {
+    const uint4 *xr = reinterpret_cast<const uint4 *>(x + (size_t)tk * cols);
+    float acc = 0.f;
+    for (int c = lane; c < cols / 8; c += 32) {
+      uint4 a = ldg_stream(wr + c), b = xr[c];
+      acc = fmaf(bf16lo(a.x), bf16lo(b.x), acc);
+      acc = fmaf(bf16hi(a.x), bf16hi(b.x), acc);
+      acc = fmaf(bf16lo(a.y), bf16lo(b.y), acc);
+      acc = fmaf(bf16hi(a.y), bf16hi(b.y), acc);
+      acc = fmaf(bf16lo(a.z), bf16lo(b.z), acc);
+      acc = fmaf(bf16hi(a.z), bf16hi(b.z), acc);
+      acc = fmaf(bf16lo(a.w), bf16lo(b.w), acc);
+      acc = fmaf(bf16hi(a.w), bf16hi(b.w), acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      if (y_f32) y_f32[(size_t)tk * rows + warp] = acc;
+      else y_bf16[(size_t)tk * rows + warp] = f32_to_bf16_bits(acc);
+    }
+  }
+}
+
+// One CTA per token.
+__global__ void rmsnorm_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__ w,
+                               uint16_t *__restrict__ y, int n, float eps) {
+  __shared__ float red[32];
+  const uint16_t *xr = x + (size_t)blockIdx.x * n;
+  uint16_t *yr = y + (size_t)blockIdx.x * n;
+  float v = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float a = bf16_bits_to_f32(xr[i]);
+    v = fmaf(a, a, v);
+  }
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float s = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    s = warp_sum(s);
+    if (threadIdx.x == 0) red[0] = s;
+  }
+  __syncthreads();
+  float scale = rsqrtf(red[0] / n + eps);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float a = bf16_bits_to_f32(xr[i]);
+    yr[i] = f32_to_bf16_bits(round_bf16(a * scale) * bf16_bits_to_f32(w[i]));
+  }
+}
+
+__global__ void add_bf16_kernel(uint16_t *__restrict__ a, const uint16_t *__restrict__ b, long n) {
+  long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) a[i] = f32_to_bf16_bits(bf16_bits_to_f32(a[i]) + bf16_bits_to_f32(b[i]));
+}
+
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+int launch_bf16_gemv(const uint16_t *w, const uint16_t *x, uint16_t *y_bf16, float *y_f32, int rows, int cols, int T,
+                     cudaStream_t stream) {
+  size_t smem = bf16_x_row_bytes(cols) * T;
+  bool tc = rows % 16 == 0 && cols % 32 == 0 && aligned16(w) && aligned16(x) && smem <= 200 * 1024;
+  if (tc) {
+    if (smem > 48 * 1024)
+      BLOK_CUDA(cudaFuncSetAttribute(bf16_gemv16_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int nwarps = cols >= 4096 ? 16 : (cols >= 1024 ? 8 : 4);
+    bf16_gemv16_kernel<0><<<rows / 16, nwarps * 32, smem, stream>>>(w, nullptr, x, y_bf16, y_f32, rows, cols, T);
+    return launch_status("bf16_gemv16_kernel");
+  }
+  bf16_gemv_scalar_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(w, x, y_bf16, y_f32, rows, cols, T);
+  return launch_status("bf16_gemv_scalar_kernel");
+}
+
+// mid[T, ffn] = SwiGLU front half.
+int launch_bf16_gateup(const uint16_t *gate, const uint16_t *up, const uint16_t *x, uint16_t *mid, int ffn, int cols,
+                       int T, cudaStream_t stream) {
+  size_t smem = bf16_x_row_bytes(cols) * T;
+  if (smem > 48 * 1024)
+    BLOK_CUDA(cudaFuncSetAttribute(bf16_gemv16_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int nwarps = cols >= 4096 ? 16 : (cols >= 1024 ? 8 : 4);
+  bf16_gemv16_kernel<1><<<ffn / 8, nwarps * 32, smem, stream>>>(gate, up, x, mid, nullptr, ffn, cols, T);
+  return launch_status("bf16_gemv16_kernel<swiglu>");
+}
+
+}  // namespace blok
+
+using namespace blok;
+
+extern "C" int blok_bf16_gemv(const blok_bf16_t *w, const blok_bf16_t *x, blok_bf16_t *y_bf16, float *y_f32, int rows,
+                              int cols, int T, blok_stream_t stream) {
+  BLOK_REQUIRE(w && x && ((y_bf16 != nullptr) != (y_f32 != nullptr)), BLOK_ERR_ARG,
+               "blok_bf16_gemv: need w, x and exactly one of y_bf16 / y_f32");
+  BLOK_REQUIRE(rows >= 0 && cols > 0 && cols % 8 == 0 && T >= 1 && T <= 8, BLOK_ERR_SHAPE,
+               "blok_bf16_gemv: cols %d must be a positive multiple of 8 and 1 <= T=%d <= 8", cols, T);
+  BLOK_REQUIRE(aligned16(w) && aligned16(x), BLOK_ERR_ARG, "blok_bf16_gemv: w and x must be 16-byte aligned");
+  if (rows == 0) return BLOK_OK;
+  return launch_bf16_gemv(w, x, y_bf16, y_f32, rows, cols, T, (cudaStream_t)stream);
+}
+
+extern "C" size_t blok_bf16_mlp_workspace_bytes(int hidden, int ffn, int T) {
+  (void)hidden;
+  return (ffn > 0 && T > 0) ? (size_t)ffn * T * sizeof(uint16_t) : 0;
+}
+
+extern "C" int blok_bf16_mlp(const blok_bf16_t *gate, const blok_bf16_t *up, const blok_bf16_t *down,
+                             const blok_bf16_t *x, blok_bf16_t *y, int hidden, int ffn, int T, void *workspace,
+                             size_t workspace_bytes, blok_stream_t stream) {
+  BLOK_REQUIRE(gate && up && down && x && y && workspace, BLOK_ERR_ARG, "blok_bf16_mlp: null pointer");
+  BLOK_REQUIRE(hidden > 0 && ffn > 0 && hidden % 32 == 0 && ffn % 32 == 0 && hidden % 16 == 0 && T >= 1 && T <= 8,
+               BLOK_ERR_SHAPE, "blok_bf16_mlp: hidden %d, ffn %d must be multiples of 32 and 1 <= T=%d <= 8", hidden, ffn, T);
+  BLOK_REQUIRE(bf16_x_row_bytes(hidden > ffn ? hidden : ffn) * T <= 200 * 1024, BLOK_ERR_SHAPE,
+               "blok_bf16_mlp: T * max(hidden, ffn) does not fit in shared memory");
+  BLOK_REQUIRE(workspace_bytes >= blok_bf16_mlp_workspace_bytes(hidden, ffn, T), BLOK_ERR_WORKSPACE,
+               "blok_bf16_mlp: workspace too small");
+  BLOK_REQUIRE(aligned16(gate) && aligned16(up) && aligned16(down) && aligned16(x) && aligned16(workspace), BLOK_ERR_ARG,
+               "blok_bf16_mlp: pointers must be 16-byte aligned");
+  uint16_t *mid = static_cast<uint16_t *>(workspace);
+  int rc = launch_bf16_gateup(gate, up, x, mid, ffn, hidden, T, (cudaStream_t)stream);
+  if (rc) return rc;
+  return launch_bf16_gemv(down, mid, y, nullptr, hidden, ffn, T, (cudaStream_t)stream);
+}
+
+extern "C" int blok_rmsnorm(const blok_bf16_t *x, const blok_bf16_t *w, blok_bf16_t *y, int T, int n, float eps,
+                            blok_stream_t stream) {
+  BLOK_REQUIRE(x && w && y, BLOK_ERR_ARG, "blok_rmsnorm: null pointer");
+  BLOK_REQUIRE(T >= 0 && n > 0, BLOK_ERR_SHAPE, "blok_rmsnorm: bad shape T=%d n=%d", T, n);
+  if (T == 0) return BLOK_OK;
+  rmsnorm_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(x, w, y, n, eps);
+  return launch_status("rmsnorm_kernel");
+}
+
+extern "C" int blok_add_bf16(blok_bf16_t *a, const blok_bf16_t *b, long n, blok_stream_t stream) {
+  BLOK_REQUIRE(a && b, BLOK_ERR_ARG, "blok_add_bf16: null pointer");
+  BLOK_REQUIRE(n >= 0, BLOK_ERR_SHAPE, "blok_add_bf16: negative n");
+  if (n == 0) return BLOK_OK;
+  add_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(a, b, n);
+  return launch_status("add_bf16_kernel");
+}

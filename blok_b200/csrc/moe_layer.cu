@@ -1,0 +1,129 @@
+// Routed-MoE layer handle and the batch-1 decode path.
+// Reference: the MoE branch of the layer body, src/kimi_exec.cu:836-875.
+#include <cstdlib>
+#include <new>
+
+#include "common.cuh"
+#include "moe_layer.h"
+
+namespace blok {
+
+int launch_bf16_gemv(const uint16_t *w, const uint16_t *x, uint16_t *y_bf16, float *y_f32, int rows, int cols, int T,
+                     cudaStream_t stream);
+int launch_bf16_gateup(const uint16_t *gate, const uint16_t *up, const uint16_t *x, uint16_t *mid, int ffn, int cols,
+                       int T, cudaStream_t stream);
+int launch_router_topk(const float *logits, const float *bias, int T, int experts, int topk, float routed_scale,
+                       uint16_t *ids, float *wts, int *local_ids, int expert_base, cudaStream_t stream);
+int launch_i4_gateup(const uint32_t *gate_w, const uint16_t *gate_s, const uint32_t *up_w, const uint16_t *up_s,
+                     const uint16_t *x, const int *slot_expert, uint16_t *mid, int hidden, int inter, int slots,
+                     cudaStream_t stream);
+int launch_i4_down(const uint32_t *down_w, const uint16_t *down_s, const uint16_t *mid, const int *slot_expert,
+                   const float *wts, const uint16_t *addend, uint16_t *out, int hidden, int inter, int slots,
+                   cudaStream_t stream);
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace blok
+
+using namespace blok;
+
+extern "C" int blok_moe_layer_create(const blok_moe_weights *w, int max_tokens, blok_moe_layer_t **out) {
+  BLOK_REQUIRE(w && out, BLOK_ERR_ARG, "blok_moe_layer_create: null pointer");
+  BLOK_REQUIRE(max_tokens >= 1, BLOK_ERR_ARG, "blok_moe_layer_create: max_tokens must be >= 1");
+  BLOK_REQUIRE(w->hidden > 0 && w->hidden % 256 == 0 && w->inter > 0 && w->inter % 256 == 0 && w->hidden <= 32768 &&
+                   w->inter <= 32768,
+               BLOK_ERR_SHAPE, "blok_moe_layer_create: hidden %d / inter %d must be multiples of 256 (<= 32768)",
+               w->hidden, w->inter);
+  BLOK_REQUIRE(w->experts > 0 && w->experts <= 1024 && w->topk >= 1 && w->topk <= 16 && w->topk <= w->experts,
+               BLOK_ERR_SHAPE, "blok_moe_layer_create: experts %d / topk %d unsupported", w->experts, w->topk);
+  BLOK_REQUIRE(w->experts_local >= 0 && w->expert_base >= 0 && w->expert_base + w->experts_local <= w->experts,
+               BLOK_ERR_SHAPE, "blok_moe_layer_create: local expert range [%d, %d) outside [0, %d)", w->expert_base,
+               w->expert_base + w->experts_local, w->experts);
+  BLOK_REQUIRE(w->shared_inter >= 0 && w->shared_inter % 32 == 0, BLOK_ERR_SHAPE,
+               "blok_moe_layer_create: shared_inter %d must be a multiple of 32", w->shared_inter);
+  BLOK_REQUIRE(w->router_w && w->router_bias, BLOK_ERR_ARG, "blok_moe_layer_create: router weights missing");
+  if (w->experts_local > 0)
+    BLOK_REQUIRE(w->gate_w && w->gate_s && w->up_w && w->up_s && w->down_w && w->down_s, BLOK_ERR_ARG,
+                 "blok_moe_layer_create: routed expert weights missing");
+  if (w->shared_inter > 0)
+    BLOK_REQUIRE(w->shared_gate && w->shared_up && w->shared_down, BLOK_ERR_ARG,
+                 "blok_moe_layer_create: shared expert weights missing");
+  blok_moe_layer *L = new (std::nothrow) blok_moe_layer();
+  BLOK_REQUIRE(L, BLOK_ERR_ARG, "blok_moe_layer_create: out of host memory");
+  L->w = *w;
+  L->max_tokens = max_tokens;
+  // decode workspace carve-up
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    size_t at = off;
+    off = align_up(off + bytes, 256);
+    return at;
+  };
+  size_t o_logits = take((size_t)max_tokens * w->experts * sizeof(float));
+  size_t o_ids = take((size_t)max_tokens * w->topk * sizeof(uint16_t));
+  size_t o_local = take((size_t)max_tokens * w->topk * sizeof(int));
+  size_t o_wts = take((size_t)max_tokens * w->topk * sizeof(float));
+  size_t o_mid = take((size_t)w->topk * w->inter * sizeof(uint16_t));
+  size_t o_smid = take((size_t)(w->shared_inter ? w->shared_inter : 1) * 8 * sizeof(uint16_t));
+  size_t o_sout = take((size_t)w->hidden * 8 * sizeof(uint16_t));
+  L->ws_bytes = off;
+  cudaError_t e = cudaMalloc(&L->ws, L->ws_bytes);
+  if (e != cudaSuccess) {
+    delete L;
+    return cuda_fail(e, "cudaMalloc(moe layer workspace)");
+  }
+  e = cudaMemset(L->ws, 0, L->ws_bytes);
+  if (e != cudaSuccess) {
+    cudaFree(L->ws);
+    delete L;
+    return cuda_fail(e, "cudaMemset(moe layer workspace)");
+  }
+  unsigned char *b = static_cast<unsigned char *>(L->ws);
+  L->logits = reinterpret_cast<float *>(b + o_logits);
+  L->ids = reinterpret_cast<uint16_t *>(b + o_ids);
+  L->local_ids = reinterpret_cast<int *>(b + o_local);
+  L->wts = reinterpret_cast<float *>(b + o_wts);
+  L->mid = reinterpret_cast<uint16_t *>(b + o_mid);
+  L->shared_mid = reinterpret_cast<uint16_t *>(b + o_smid);
+  L->shared_out = reinterpret_cast<uint16_t *>(b + o_sout);
+  *out = L;
+  return BLOK_OK;
+}
+
+extern "C" int blok_moe_layer_destroy(blok_moe_layer_t *L) {
+  if (!L) return BLOK_OK;
+  cudaError_t e = L->ws ? cudaFree(L->ws) : cudaSuccess;
+  delete L;
+  return e == cudaSuccess ? BLOK_OK : cuda_fail(e, "cudaFree(moe layer workspace)");
+}
+
+extern "C" int blok_moe_decode(blok_moe_layer_t *L, const blok_bf16_t *x, blok_bf16_t *y, uint16_t *ids_out,
+                               float *wts_out, blok_stream_t stream_) {
+  BLOK_REQUIRE(L && x && y, BLOK_ERR_ARG, "blok_moe_decode: null pointer");
+  const blok_moe_weights &w = L->w;
+  BLOK_REQUIRE(w.experts_local == w.experts && w.expert_base == 0, BLOK_ERR_ROUTE,
+               "blok_moe_decode: needs every expert local (have [%d, %d) of %d)", w.expert_base,
+               w.expert_base + w.experts_local, w.experts);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int rc = launch_bf16_gemv(w.router_w, x, nullptr, L->logits, w.experts, w.hidden, 1, stream);
+  if (rc) return rc;
+  rc = launch_router_topk(L->logits, w.router_bias, 1, w.experts, w.topk, w.routed_scale, L->ids, L->wts, L->local_ids,
+                          w.expert_base, stream);
+  if (rc) return rc;
+  const uint16_t *addend = nullptr;
+  if (w.shared_inter > 0) {
+    rc = launch_bf16_gateup(w.shared_gate, w.shared_up, x, L->shared_mid, w.shared_inter, w.hidden, 1, stream);
+    if (rc) return rc;
+    rc = launch_bf16_gemv(w.shared_down, L->shared_mid, L->shared_out, nullptr, w.hidden, w.shared_inter, 1, stream);
+    if (rc) return rc;
+    addend = L->shared_out;
+  }
+  rc = launch_i4_gateup(w.gate_w, w.gate_s, w.up_w, w.up_s, x, L->local_ids, L->mid, w.hidden, w.inter, w.topk, stream);
+  if (rc) return rc;
+  rc = launch_i4_down(w.down_w, w.down_s, L->mid, L->local_ids, L->wts, addend, y, w.hidden, w.inter, w.topk, stream);
+  if (rc) return rc;
+  if (ids_out)
+    BLOK_CUDA(cudaMemcpyAsync(ids_out, L->ids, w.topk * sizeof(uint16_t), cudaMemcpyDeviceToDevice, stream));
+  if (wts_out) BLOK_CUDA(cudaMemcpyAsync(wts_out, L->wts, w.topk * sizeof(float), cudaMemcpyDeviceToDevice, stream));
+  return BLOK_OK;
+}

@@ -1,0 +1,101 @@
+// Router: fp32 logits, sigmoid, bias, top-k by repeated argmax, normalise, scale.
+// Reference arithmetic: src/kimi_exec.cu:836-842 with matvec_bf16_f32_k :286-298,
+// sigmoid_k :377-380, add_bf16_k :372-375, router_topk_k :382-397.
+#include <cmath>
+
+#include "common.cuh"
+
+namespace blok {
+
+int launch_bf16_gemv(const uint16_t *w, const uint16_t *x, uint16_t *y_bf16, float *y_f32, int rows, int cols, int T,
+                     cudaStream_t stream);
+
+constexpr int kTopkWarps = 4;
+
+// One warp per token.  logits [T, experts] fp32.  The selection reproduces the
+// reference's rule exactly: k rounds of argmax over sel = sigmoid(logit) + bias
+// with strict '>' scanning ascending indices, i.e. the lowest index wins a tie,
+// and the outputs are in descending sel order.
+__global__ void router_topk_kernel(const float *__restrict__ logits, const float *__restrict__ bias, int T,
+                                   int experts, int topk, float routed_scale, uint16_t *__restrict__ ids,
+                                   float *__restrict__ wts, int *__restrict__ local_ids, int expert_base) {
+  extern __shared__ float sm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tok = blockIdx.x * kTopkWarps + warp;
+  if (tok >= T) return;
+  float *score = sm + (size_t)warp * 2 * experts;
+  float *sel = score + experts;
+  for (int i = lane; i < experts; i += 32) {
+    float s = 1.0f / (1.0f + expf(-logits[(size_t)tok * experts + i]));
+    score[i] = s;
+    sel[i] = s + bias[i];
+  }
+  __syncwarp();
+  float sum = 0.f;
+  float my_w = 0.f;  // lane k keeps the k-th selected score
+  int my_id = 0;
+  for (int k = 0; k < topk; ++k) {
+    float best = -INFINITY;
+    int id = 0x7fffffff;
+    for (int i = lane; i < experts; i += 32) {
+      float v = sel[i];
+      if (v > best) best = v, id = i;
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      int oi = __shfl_xor_sync(0xffffffffu, id, o);
+      if (ob > best || (ob == best && oi < id)) best = ob, id = oi;
+    }
+    if (id == 0x7fffffff) id = 0;  // every candidate was -inf or NaN: the reference keeps id 0
+    float s = score[id];
+    sum += s;
+    if (lane == k) my_w = s, my_id = id;
+    __syncwarp();
+    if (lane == 0) sel[id] = -INFINITY;
+    __syncwarp();
+  }
+  if (lane < topk) {
+    if (ids) ids[(size_t)tok * topk + lane] = (uint16_t)my_id;
+    if (local_ids) local_ids[(size_t)tok * topk + lane] = my_id - expert_base;
+    wts[(size_t)tok * topk + lane] = my_w / (sum + 1.0e-20f) * routed_scale;
+  }
+}
+
+int launch_router_topk(const float *logits, const float *bias, int T, int experts, int topk, float routed_scale,
+                       uint16_t *ids, float *wts, int *local_ids, int expert_base, cudaStream_t stream) {
+  size_t smem = (size_t)kTopkWarps * 2 * experts * sizeof(float);
+  router_topk_kernel<<<(T + kTopkWarps - 1) / kTopkWarps, kTopkWarps * 32, smem, stream>>>(logits, bias, T, experts,
+                                                                                            topk, routed_scale, ids,
+                                                                                            wts, local_ids,
+                                                                                            expert_base);
+  return launch_status("router_topk_kernel");
+}
+
+}  // namespace blok
+
+using namespace blok;
+
+extern "C" size_t blok_router_workspace_bytes(int T, int experts) {
+  return (T > 0 && experts > 0) ? (size_t)T * experts * sizeof(float) : 0;
+}
+
+extern "C" int blok_router(const blok_bf16_t *router_w, const float *bias, const blok_bf16_t *x, int T, int experts,
+                           int hidden, int topk, float routed_scale, uint16_t *ids, float *wts, void *workspace,
+                           size_t workspace_bytes, blok_stream_t stream) {
+  BLOK_REQUIRE(router_w && bias && x && ids && wts && workspace, BLOK_ERR_ARG, "blok_router: null pointer");
+  BLOK_REQUIRE(T >= 0 && experts > 0 && experts <= 1024 && topk >= 1 && topk <= 32 && topk <= experts && hidden > 0 &&
+                   hidden % 8 == 0,
+               BLOK_ERR_SHAPE, "blok_router: unsupported shape T=%d experts=%d topk=%d hidden=%d", T, experts, topk, hidden);
+  BLOK_REQUIRE(workspace_bytes >= blok_router_workspace_bytes(T, experts), BLOK_ERR_WORKSPACE,
+               "blok_router: workspace too small");
+  if (T == 0) return BLOK_OK;
+  float *logits = static_cast<float *>(workspace);
+  for (int t0 = 0; t0 < T; t0 += 8) {
+    int n = T - t0 < 8 ? T - t0 : 8;
+    int rc = launch_bf16_gemv(router_w, x + (size_t)t0 * hidden, nullptr, logits + (size_t)t0 * experts, experts, hidden,
+                              n, (cudaStream_t)stream);
+    if (rc) return rc;
+  }
+  return launch_router_topk(logits, bias, T, experts, topk, routed_scale, ids, wts, nullptr, 0, (cudaStream_t)stream);
+}

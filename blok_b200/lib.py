@@ -1,0 +1,230 @@
+"""ctypes front end of libblok_b200.so.
+
+Each wrapper mirrors one host op of the reference executor (src/kimi_exec.cu) and
+takes torch CUDA tensors; the tensor's data pointer and the current CUDA stream
+are what crosses the C ABI.  A missing or stale library is an error, never a
+fallback.
+"""
+import ctypes as C
+import os
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libblok_b200.so")
+
+OK = 0
+
+
+class BlokError(RuntimeError):
+    def __init__(self, code, message):
+        super().__init__("blok_b200 error %d: %s" % (code, message))
+        self.code = code
+
+
+class MoeWeights(C.Structure):
+    _fields_ = [
+        ("hidden", C.c_int), ("inter", C.c_int), ("experts", C.c_int), ("topk", C.c_int), ("shared_inter", C.c_int),
+        ("routed_scale", C.c_float),
+        ("router_w", C.c_void_p), ("router_bias", C.c_void_p),
+        ("expert_base", C.c_int), ("experts_local", C.c_int),
+        ("gate_w", C.c_void_p), ("gate_s", C.c_void_p), ("up_w", C.c_void_p), ("up_s", C.c_void_p),
+        ("down_w", C.c_void_p), ("down_s", C.c_void_p),
+        ("shared_gate", C.c_void_p), ("shared_up", C.c_void_p), ("shared_down", C.c_void_p),
+    ]
+
+
+_lib = None
+
+
+def load():
+    """Load the CUDA library; raises if it has not been built (python -m blok_b200.build)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise BlokError(-100, "%s is missing: run `python -m blok_b200.build` (there is no CPU fallback)" % LIB_PATH)
+    lib = C.CDLL(LIB_PATH)
+    lib.blok_last_error.restype = C.c_char_p
+    for name in ("blok_expert_ffn_workspace_bytes", "blok_bf16_mlp_workspace_bytes", "blok_router_workspace_bytes"):
+        getattr(lib, name).restype = C.c_size_t
+    _lib = lib
+    return lib
+
+
+def _check(rc):
+    if rc != OK:
+        raise BlokError(rc, load().blok_last_error().decode())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t, dtype=None, name="tensor"):
+    if t is None:
+        return C.c_void_p(0)
+    if not t.is_cuda:
+        raise BlokError(-1, "%s must be a CUDA tensor" % name)
+    if not t.is_contiguous():
+        raise BlokError(-1, "%s must be contiguous" % name)
+    if dtype is not None and t.dtype != dtype:
+        raise BlokError(-1, "%s must have dtype %s, got %s" % (name, dtype, t.dtype))
+    return C.c_void_p(t.data_ptr())
+
+
+def i4_dequant(w_packed, scale):
+    """bf16 [rows, cols] = bf16_rn(q * scale); the bit-exactness probe (src/kimi_exec.cu:311-312)."""
+    rows, cols = w_packed.shape[0], w_packed.shape[1] * 8
+    out = torch.empty((rows, cols), dtype=torch.bfloat16, device=w_packed.device)
+    _check(load().blok_i4_dequant(_ptr(w_packed, torch.int32, "weight_packed"), _ptr(scale, torch.bfloat16, "weight_scale"),
+                                  _ptr(out), C.c_int(rows), C.c_int(cols), _stream()))
+    return out
+
+
+def i4_gemv(w_packed, scale, x):
+    """matvec_i4_slice (src/kimi_exec.cu:688): y[rows] from x[cols]; bf16 in/out, or the fp32 shim if x is fp32."""
+    rows, cols = w_packed.shape[0], w_packed.shape[1] * 8
+    if x.numel() != cols:
+        raise BlokError(-2, "x has %d elements, expected %d" % (x.numel(), cols))
+    y = torch.empty(rows, dtype=x.dtype, device=x.device)
+    if x.dtype == torch.float32:
+        _check(load().blok_i4_gemv_f32(_ptr(w_packed, torch.int32), _ptr(scale, torch.bfloat16), _ptr(x), _ptr(y),
+                                       C.c_int(rows), C.c_int(cols), _stream()))
+    else:
+        _check(load().blok_i4_gemv(_ptr(w_packed, torch.int32), _ptr(scale, torch.bfloat16), _ptr(x, torch.bfloat16), _ptr(y),
+                                   C.c_int(rows), C.c_int(cols), _stream()))
+    return y
+
+
+def expert_ffn(gate_w, gate_s, up_w, up_s, down_w, down_s, x, workspace=None):
+    """One routed expert, y = down(SiLU(gate x) * up x) (src/kimi_exec.cu:853-869)."""
+    inter, hidden = gate_w.shape[0], gate_w.shape[1] * 8
+    lib = load()
+    need = lib.blok_expert_ffn_workspace_bytes(C.c_int(hidden), C.c_int(inter))
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    y = torch.empty(hidden, dtype=torch.bfloat16, device=x.device)
+    _check(lib.blok_expert_ffn(_ptr(gate_w, torch.int32), _ptr(gate_s, torch.bfloat16), _ptr(up_w, torch.int32),
+                               _ptr(up_s, torch.bfloat16), _ptr(down_w, torch.int32), _ptr(down_s, torch.bfloat16),
+                               _ptr(x, torch.bfloat16), _ptr(y), C.c_int(hidden), C.c_int(inter), _ptr(workspace),
+                               C.c_size_t(workspace.numel() * workspace.element_size()), _stream()))
+    return y
+
+
+def bf16_gemv(w, x, out_f32=False):
+    """matvec_bf16_k / matvec_bf16_f32_k (src/kimi_exec.cu:272-298) for x [T<=8, cols] or [cols]."""
+    rows, cols = w.shape
+    x2 = x.reshape(-1, cols)
+    T = x2.shape[0]
+    y = torch.empty((T, rows), dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+    _check(load().blok_bf16_gemv(_ptr(w, torch.bfloat16), _ptr(x2, torch.bfloat16), _ptr(None if out_f32 else y),
+                                 _ptr(y if out_f32 else None), C.c_int(rows), C.c_int(cols), C.c_int(T), _stream()))
+    return y.reshape(*x.shape[:-1], rows)
+
+
+def bf16_mlp(gate, up, down, x):
+    """bf16_mlp (src/kimi_exec.cu:674-686) without the running-sum side effect."""
+    ffn, hidden = gate.shape
+    x2 = x.reshape(-1, hidden)
+    T = x2.shape[0]
+    lib = load()
+    need = lib.blok_bf16_mlp_workspace_bytes(C.c_int(hidden), C.c_int(ffn), C.c_int(T))
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=x.device)
+    y = torch.empty((T, hidden), dtype=torch.bfloat16, device=x.device)
+    _check(lib.blok_bf16_mlp(_ptr(gate, torch.bfloat16), _ptr(up, torch.bfloat16), _ptr(down, torch.bfloat16),
+                             _ptr(x2, torch.bfloat16), _ptr(y), C.c_int(hidden), C.c_int(ffn), C.c_int(T), _ptr(ws),
+                             C.c_size_t(ws.numel()), _stream()))
+    return y.reshape(x.shape)
+
+
+def rmsnorm(x, w, eps=1e-5, out=None):
+    """rmsnorm_k (src/kimi_exec.cu:258-270); x [T, n] or [n]."""
+    n = x.shape[-1]
+    T = x.numel() // n if n else 0
+    y = torch.empty_like(x) if out is None else out
+    _check(load().blok_rmsnorm(_ptr(x, torch.bfloat16), _ptr(w, torch.bfloat16), _ptr(y, torch.bfloat16), C.c_int(T),
+                               C.c_int(n), C.c_float(eps), _stream()))
+    return y
+
+
+def add_(a, b):
+    """a = bf16(a + b), add_k (src/kimi_exec.cu:248-251)."""
+    _check(load().blok_add_bf16(_ptr(a, torch.bfloat16), _ptr(b, torch.bfloat16), C.c_long(a.numel()), _stream()))
+    return a
+
+
+def router(router_w, bias, x, topk=8, routed_scale=2.827):
+    """Router (src/kimi_exec.cu:836-842): returns ids uint16 [T, topk] (as int16 storage) and weights fp32 [T, topk]."""
+    experts, hidden = router_w.shape
+    x2 = x.reshape(-1, hidden)
+    T = x2.shape[0]
+    lib = load()
+    need = lib.blok_router_workspace_bytes(C.c_int(T), C.c_int(experts))
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=x.device)
+    ids = torch.empty((T, topk), dtype=torch.int16, device=x.device)
+    wts = torch.empty((T, topk), dtype=torch.float32, device=x.device)
+    _check(lib.blok_router(_ptr(router_w, torch.bfloat16), _ptr(bias, torch.float32), _ptr(x2, torch.bfloat16), C.c_int(T),
+                           C.c_int(experts), C.c_int(hidden), C.c_int(topk), C.c_float(routed_scale), _ptr(ids), _ptr(wts),
+                           _ptr(ws), C.c_size_t(ws.numel()), _stream()))
+    return ids, wts
+
+
+class MoeLayer:
+    """Handle of one routed-MoE layer (the MoE branch of src/kimi_exec.cu:836-875).
+
+    `weights` is a dict of CUDA tensors:
+      router_w bf16 [E, H], router_bias f32 [E],
+      gate_w/up_w int32 [n, I, H/8], gate_s/up_s bf16 [n, I, H/32],
+      down_w int32 [n, H, I/8], down_s bf16 [n, H, I/32],
+      optional shared_gate/shared_up bf16 [S, H], shared_down bf16 [H, S].
+    The tensors are borrowed: this object keeps references so they outlive the handle.
+    """
+
+    def __init__(self, weights, topk=8, routed_scale=2.827, expert_base=0, max_tokens=1):
+        self.weights = dict(weights)
+        w = self.weights
+        E, H = w["router_w"].shape
+        n, I = w["gate_w"].shape[0], w["gate_w"].shape[1]
+        S = w["shared_gate"].shape[0] if w.get("shared_gate") is not None else 0
+        self.hidden, self.inter, self.experts, self.topk, self.shared_inter = H, I, E, topk, S
+        self.experts_local, self.expert_base = n, expert_base
+        mw = MoeWeights(
+            hidden=H, inter=I, experts=E, topk=topk, shared_inter=S, routed_scale=routed_scale,
+            router_w=_ptr(w["router_w"], torch.bfloat16, "router_w").value,
+            router_bias=_ptr(w["router_bias"], torch.float32, "router_bias").value,
+            expert_base=expert_base, experts_local=n,
+            gate_w=_ptr(w["gate_w"], torch.int32, "gate_w").value, gate_s=_ptr(w["gate_s"], torch.bfloat16, "gate_s").value,
+            up_w=_ptr(w["up_w"], torch.int32, "up_w").value, up_s=_ptr(w["up_s"], torch.bfloat16, "up_s").value,
+            down_w=_ptr(w["down_w"], torch.int32, "down_w").value, down_s=_ptr(w["down_s"], torch.bfloat16, "down_s").value,
+            shared_gate=_ptr(w.get("shared_gate"), torch.bfloat16).value,
+            shared_up=_ptr(w.get("shared_up"), torch.bfloat16).value,
+            shared_down=_ptr(w.get("shared_down"), torch.bfloat16).value,
+        )
+        self._handle = C.c_void_p()
+        self.device = w["router_w"].device
+        with torch.cuda.device(self.device):
+            _check(load().blok_moe_layer_create(C.byref(mw), C.c_int(max_tokens), C.byref(self._handle)))
+        self.max_tokens = max_tokens
+
+    def close(self):
+        if getattr(self, "_handle", None) is not None and self._handle.value:
+            load().blok_moe_layer_destroy(self._handle)
+            self._handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def decode(self, x, out=None, return_routing=False):
+        """Batch-1 decode layer: x bf16 [hidden] -> y bf16 [hidden]."""
+        y = torch.empty(self.hidden, dtype=torch.bfloat16, device=x.device) if out is None else out
+        ids = wts = None
+        if return_routing:
+            ids = torch.empty(self.topk, dtype=torch.int16, device=x.device)
+            wts = torch.empty(self.topk, dtype=torch.float32, device=x.device)
+        _check(load().blok_moe_decode(self._handle, _ptr(x, torch.bfloat16, "x"), _ptr(y, torch.bfloat16, "y"), _ptr(ids),
+                                      _ptr(wts), _stream()))
+        return (y, ids, wts) if return_routing else y

@@ -1,0 +1,177 @@
+/*
+ * blok_b200 — C ABI of the B200 (sm_100a) implementation of Blok's decode hot path:
+ * the W4A16 routed-expert MoE layer over compressed-tensors pack_quantized INT4
+ * weights and the MLA decode attention that feeds it.
+ *
+ * Conventions
+ *  - Every function returns an int status: BLOK_OK (0) or a negative BLOK_ERR_*.
+ *    Nothing here calls exit(); blok_last_error() gives the message of the last
+ *    failure on the calling thread.  (The reference's die(), src/kimi_exec.cu:495,
+ *    terminates the process instead.)
+ *  - Every data pointer is a DEVICE pointer owned by the caller unless the
+ *    parameter comment says "host".  Work is enqueued on `stream`; no call
+ *    synchronises unless stated.
+ *  - Only *_create functions allocate.  Stateless entry points that need scratch
+ *    take a caller-provided workspace and report its size through *_workspace_bytes.
+ *  - bf16 values cross the ABI as uint16_t bit patterns (blok_bf16_t).
+ *  - INT4 layout (compressed-tensors pack_quantized, the reference's contract at
+ *    src/kimi_exec.cu:599-606, decode rule at :311): weight_packed is int32
+ *    [rows, cols/8], nibble = q + 8, nibble k of a word (bits 4k..4k+3) is column
+ *    8*word + k; weight_scale is bf16 [rows, cols/32]; dequantised weight =
+ *    bf16_rn(float(q) * float(scale)).
+ */
+#ifndef BLOK_B200_H
+#define BLOK_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st *blok_stream_t; /* cudaStream_t */
+typedef uint16_t blok_bf16_t;
+
+enum {
+  BLOK_OK = 0,
+  BLOK_ERR_ARG = -1,         /* null pointer, bad size, misaligned pointer */
+  BLOK_ERR_SHAPE = -2,       /* shape not supported by the kernels */
+  BLOK_ERR_CUDA = -3,        /* a CUDA runtime call failed */
+  BLOK_ERR_STATE = -4,       /* handle misuse */
+  BLOK_ERR_TIMEOUT = -5,     /* a bounded device-side wait gave up */
+  BLOK_ERR_WORKSPACE = -6,   /* workspace too small */
+  BLOK_ERR_ROUTE = -7        /* routed expert id not held by this rank / capacity exceeded */
+};
+
+#define BLOK_ABI_VERSION 1
+
+/* Message of the last failure on this thread ("" if none). */
+const char *blok_last_error(void);
+int blok_abi_version(void);
+
+/* ------------------------------------------------------------------------- */
+/* A1  INT4 weights                                                           */
+/* ------------------------------------------------------------------------- */
+
+/* Bit-exactness probe: out[r,c] = bf16_rn(float(q[r,c]) * float(scale[r,c/32])),
+ * out is bf16 [rows, cols].  Replaces the dequant expression at
+ * src/kimi_exec.cu:311-312.  cols % 32 == 0. */
+int blok_i4_dequant(const uint32_t *w_packed, const blok_bf16_t *scale, blok_bf16_t *out, int rows, int cols,
+                    blok_stream_t stream);
+
+/* y[r] = bf16(sum_c x[c] * dequant(w[r,c])), fp32 accumulation.  Replaces
+ * matvec_i4_slice / matvec_i4_bf16_scale_k (src/kimi_exec.cu:688-690, :300-323).
+ * x bf16 [cols], y bf16 [rows].  cols % 128 == 0, rows % 16 == 0 use the
+ * tensor-core path; other shapes with cols % 32 == 0 use the scalar path. */
+int blok_i4_gemv(const uint32_t *w_packed, const blok_bf16_t *scale, const blok_bf16_t *x, blok_bf16_t *y, int rows,
+                 int cols, blok_stream_t stream);
+
+/* Same with the reference's own signature: x and y are fp32 buffers holding
+ * bf16-valued numbers (src/kimi_exec.cu:688: const float *x, float *y). */
+int blok_i4_gemv_f32(const uint32_t *w_packed, const blok_bf16_t *scale, const float *x, float *y, int rows, int cols,
+                     blok_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* A2-A4  one routed expert (config 0): y = down(SiLU(gate x) * up x)         */
+/* ------------------------------------------------------------------------- */
+
+size_t blok_expert_ffn_workspace_bytes(int hidden, int inter);
+
+/* Replaces the per-slot body of the routed-expert loop, src/kimi_exec.cu:853-869
+ * (gate and up GEMV, silu_mul_k :253, down GEMV).  x bf16 [hidden], y bf16 [hidden].
+ * gate/up packed [inter, hidden/8] + scale [inter, hidden/32]; down packed
+ * [hidden, inter/8] + scale [hidden, inter/32].  hidden % 128 == 0, inter % 128 == 0. */
+int blok_expert_ffn(const uint32_t *gate_w, const blok_bf16_t *gate_s, const uint32_t *up_w, const blok_bf16_t *up_s,
+                    const uint32_t *down_w, const blok_bf16_t *down_s, const blok_bf16_t *x, blok_bf16_t *y,
+                    int hidden, int inter, void *workspace, size_t workspace_bytes, blok_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* A6/A7/A10  bf16 GEMV, dense SwiGLU MLP, RMSNorm, residual add               */
+/* ------------------------------------------------------------------------- */
+
+/* y[t,r] = sum_c w[r,c] * x[t,c] for T <= 8 tokens; y is bf16 [T, rows] (y_f32 == NULL)
+ * or unrounded fp32 [T, rows] (y_bf16 == NULL).  Replaces matvec_bf16_k /
+ * matvec_bf16_f32_k (src/kimi_exec.cu:272-298).  cols % 8 == 0. */
+int blok_bf16_gemv(const blok_bf16_t *w, const blok_bf16_t *x, blok_bf16_t *y_bf16, float *y_f32, int rows, int cols,
+                   int T, blok_stream_t stream);
+
+size_t blok_bf16_mlp_workspace_bytes(int hidden, int ffn, int T);
+
+/* y[t] = W_d (SiLU(W_g x[t]) * W_u x[t]); replaces bf16_mlp (src/kimi_exec.cu:674-686)
+ * without its running-sum side effect (the caller adds).  T <= 8. */
+int blok_bf16_mlp(const blok_bf16_t *gate, const blok_bf16_t *up, const blok_bf16_t *down, const blok_bf16_t *x,
+                  blok_bf16_t *y, int hidden, int ffn, int T, void *workspace, size_t workspace_bytes,
+                  blok_stream_t stream);
+
+/* y[t,i] = bf16(bf16(x[t,i] * rsqrt(mean(x[t]^2) + eps)) * w[i]); in place allowed.
+ * Replaces rmsnorm_k (src/kimi_exec.cu:258-270).  x, y bf16 [T, n]. */
+int blok_rmsnorm(const blok_bf16_t *x, const blok_bf16_t *w, blok_bf16_t *y, int T, int n, float eps,
+                 blok_stream_t stream);
+
+/* a[i] = bf16(a[i] + b[i]).  Replaces add_k (src/kimi_exec.cu:248-251). */
+int blok_add_bf16(blok_bf16_t *a, const blok_bf16_t *b, long n, blok_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* A5  router                                                                 */
+/* ------------------------------------------------------------------------- */
+
+size_t blok_router_workspace_bytes(int T, int experts);
+
+/* logits = W_r x (fp32, unrounded), s = sigmoid(logits), sel = s + bias, top-k of
+ * sel by repeated argmax (ties to the lowest index, output in descending sel
+ * order), w_k = s[id_k] / (sum_k s[id_k] + 1e-20) * routed_scale.  Replaces
+ * src/kimi_exec.cu:836-842 (matvec_bf16_f32_k :286, sigmoid_k :377, add_bf16_k
+ * :372, router_topk_k :382).  x bf16 [T, hidden]; bias fp32 [experts]; ids uint16
+ * [T, topk]; wts fp32 [T, topk].  experts <= 1024, topk <= 32. */
+int blok_router(const blok_bf16_t *router_w, const float *bias, const blok_bf16_t *x, int T, int experts, int hidden,
+                int topk, float routed_scale, uint16_t *ids, float *wts, void *workspace, size_t workspace_bytes,
+                blok_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* A4-A6  routed-MoE layer (configs 1 and 2)                                  */
+/* ------------------------------------------------------------------------- */
+
+typedef struct blok_moe_weights {
+  int hidden;        /* 7168 */
+  int inter;         /* 2048, routed expert intermediate size */
+  int experts;       /* 384, global expert count (router width) */
+  int topk;          /* 8 */
+  int shared_inter;  /* 2048; 0 = no shared expert */
+  float routed_scale; /* 2.827 */
+  const blok_bf16_t *router_w; /* [experts, hidden] */
+  const float *router_bias;    /* [experts] fp32 (bf16 checkpoints widen exactly) */
+  /* Expert-major arrays of the experts this rank holds, ids [expert_base,
+   * expert_base + experts_local): packed [n, out, in/8], scale [n, out, in/32]. */
+  int expert_base;
+  int experts_local;
+  const uint32_t *gate_w;
+  const blok_bf16_t *gate_s;
+  const uint32_t *up_w;
+  const blok_bf16_t *up_s;
+  const uint32_t *down_w;
+  const blok_bf16_t *down_s;
+  const blok_bf16_t *shared_gate; /* [shared_inter, hidden] */
+  const blok_bf16_t *shared_up;   /* [shared_inter, hidden] */
+  const blok_bf16_t *shared_down; /* [hidden, shared_inter] */
+} blok_moe_weights;
+
+typedef struct blok_moe_layer blok_moe_layer_t;
+
+/* Allocates the layer's workspace (for up to max_tokens tokens) on the current
+ * device.  The weight pointers are borrowed and must outlive the handle. */
+int blok_moe_layer_create(const blok_moe_weights *weights, int max_tokens, blok_moe_layer_t **out);
+int blok_moe_layer_destroy(blok_moe_layer_t *layer);
+
+/* Batch-1 decode layer: y = bf16(bf16(sum_k w_k * expert_k(x)) + shared(x)).
+ * Replaces the MoE branch of the layer body, src/kimi_exec.cu:836-875, with the
+ * expert ids kept on the device (no host copy as at :844).  x, y bf16 [hidden];
+ * ids_out (uint16 [topk]) and wts_out (fp32 [topk]) may be NULL.  All experts
+ * must be local (experts_local == experts). */
+int blok_moe_decode(blok_moe_layer_t *layer, const blok_bf16_t *x, blok_bf16_t *y, uint16_t *ids_out, float *wts_out,
+                    blok_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BLOK_B200_H */
