@@ -308,8 +308,9 @@ using namespace blok;
 
 extern "C" int blok_i4_dequant(const uint32_t *w, const blok_bf16_t *scale, blok_bf16_t *out, int rows, int cols,
                                blok_stream_t stream) {
-  BLOK_REQUIRE(w && scale && out, BLOK_ERR_ARG, "blok_i4_dequant: null pointer");
   BLOK_REQUIRE(rows >= 0 && cols >= 0 && cols % 32 == 0, BLOK_ERR_SHAPE, "blok_i4_dequant: cols %d must be a multiple of 32", cols);
+  if (rows == 0 || cols == 0) return BLOK_OK;  // empty tensors may carry null pointers
+  BLOK_REQUIRE(w && scale && out, BLOK_ERR_ARG, "blok_i4_dequant: null pointer");
   BLOK_REQUIRE(aligned16(out), BLOK_ERR_ARG, "blok_i4_dequant: out must be 16-byte aligned");
   long words = (long)rows * (cols / 8);
   if (words == 0) return BLOK_OK;
@@ -320,10 +321,10 @@ extern "C" int blok_i4_dequant(const uint32_t *w, const blok_bf16_t *scale, blok
 
 static int i4_gemv_common(const uint32_t *w, const blok_bf16_t *scale, const blok_bf16_t *x_bf16, const float *x_f32,
                           blok_bf16_t *y_bf16, float *y_f32, int rows, int cols, cudaStream_t stream) {
-  BLOK_REQUIRE(w && scale && (x_bf16 || x_f32) && (y_bf16 || y_f32), BLOK_ERR_ARG, "blok_i4_gemv: null pointer");
   BLOK_REQUIRE(rows >= 0 && cols > 0 && cols % 32 == 0, BLOK_ERR_SHAPE, "blok_i4_gemv: cols %d must be a positive multiple of 32", cols);
+  if (rows == 0) return BLOK_OK;  // empty tensors may carry null pointers
+  BLOK_REQUIRE(w && scale && (x_bf16 || x_f32) && (y_bf16 || y_f32), BLOK_ERR_ARG, "blok_i4_gemv: null pointer");
   BLOK_REQUIRE(aligned16(w), BLOK_ERR_ARG, "blok_i4_gemv: weight_packed must be 16-byte aligned");
-  if (rows == 0) return BLOK_OK;
   bool tc = x_bf16 && rows % 16 == 0 && cols % 256 == 0 && aligned16(x_bf16) && cols <= 32768;
   if (tc) return launch_i4_gemv16(w, scale, x_bf16, y_bf16, y_f32, rows, cols, stream);
   unsigned blocks = (unsigned)((rows + 7) / 8);

@@ -1,0 +1,75 @@
+"""GPU parity of the batch-1 routed-MoE decode layer (config 1) against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+import util
+
+pytestmark = pytest.mark.gpu
+
+
+def _host_layer(w, chosen):
+    """Copy router, shared expert and the chosen experts to the host for the oracle."""
+    experts = w["router_w"].shape[0]
+    slot_of = np.full(experts, -1, np.int32)
+    chosen = sorted(set(int(e) for e in chosen))
+    for i, e in enumerate(chosen):
+        slot_of[e] = i
+    idx = torch.tensor(chosen, device=w["gate_w"].device)
+    packs = {k: util.t2np_u32(w[k].index_select(0, idx)) for k in ("gate_w", "up_w", "down_w")}
+    scs = {k: util.t2np_bf16(w[k].index_select(0, idx)) for k in ("gate_s", "up_s", "down_s")}
+    shared = [util.t2np_bf16(w[k]) if w.get(k) is not None else None for k in ("shared_gate", "shared_up", "shared_down")]
+    return slot_of, packs, scs, shared
+
+
+def _check(cuda, oracle, hidden, inter, experts, shared_inter, seed, topk=8):
+    from blok_b200 import lib, synth
+    w = synth.moe_layer_weights(cuda, seed=seed, hidden=hidden, inter=inter, experts=experts, shared_inter=shared_inter)
+    if hidden < 7168:  # keep small layers in a comparable numeric range
+        for k in ("gate_s", "up_s", "down_s"):
+            w[k] = (w[k].float() * 8).bfloat16()
+    layer = lib.MoeLayer(w, topk=topk, routed_scale=2.827)
+    x = synth.activations(1, hidden, cuda, seed)[0].contiguous()
+    y, ids, wts = layer.decode(x, return_routing=True)
+    torch.cuda.synchronize()
+    ids_h = util.ids_np(ids)
+    xh = util.t2np_f32(x)
+    oid, owt, margin, _ = oracle.router(util.t2np_bf16(w["router_w"]), util.t2np_f32(w["router_bias"]), xh[None], topk=topk,
+                                        mode=0)
+    if margin[0] > 2e-6:
+        assert ids_h.tolist() == oid[0].tolist(), "top-k ids must be bit-exact"
+    slot_of, packs, scs, shared = _host_layer(w, list(ids_h) + list(oid[0]))
+    out, _, _ = oracle.moe_layer(util.t2np_bf16(w["router_w"]), util.t2np_f32(w["router_bias"]), slot_of, packs["gate_w"],
+                                 scs["gate_s"], packs["up_w"], scs["up_s"], packs["down_w"], scs["down_s"], shared[0],
+                                 shared[1], shared[2], xh[None], topk=topk, mode=0)
+    r, c = util.assert_close(util.t2np_f32(y), out[0], "moe_decode")
+    out1, _, _ = oracle.moe_layer(util.t2np_bf16(w["router_w"]), util.t2np_f32(w["router_bias"]), slot_of, packs["gate_w"],
+                                  scs["gate_s"], packs["up_w"], scs["up_s"], packs["down_w"], scs["down_s"], shared[0],
+                                  shared[1], shared[2], xh[None], topk=topk, mode=1)
+    util.assert_close(util.t2np_f32(y), out1[0], "moe_decode vs ref_exact")
+    np.testing.assert_allclose(util.t2np_f32(wts), owt[0], rtol=2e-5)
+    y2 = layer.decode(x)
+    assert torch.equal(y, y2), "decode must be deterministic"
+    layer.close()
+    return r, c
+
+
+@pytest.mark.parametrize("hidden,inter,experts,shared_inter,seed", [(512, 256, 16, 256, 11), (1024, 512, 32, 0, 12),
+                                                                    (7168, 2048, 24, 2048, 13)])
+def test_moe_decode_small(cuda, oracle, hidden, inter, experts, shared_inter, seed):
+    _check(cuda, oracle, hidden, inter, experts, shared_inter, seed)
+
+
+def test_moe_decode_config1_full_size(cuda, oracle):
+    """Config 1: 384 experts (9.5 GB packed), hidden 7168, shared expert, seed 1."""
+    r, c = _check(cuda, oracle, 7168, 2048, 384, 2048, seed=1)
+    print("config 1: max-abs-rel %.2e cosine %.7f" % (r, c))
+
+
+def test_moe_decode_rejects_partial_expert_set(cuda):
+    from blok_b200 import lib, synth
+    w = synth.moe_layer_weights(cuda, seed=3, hidden=256, inter=256, experts=16, shared_inter=0, experts_local=8)
+    layer = lib.MoeLayer(w)
+    with pytest.raises(lib.BlokError) as e:
+        layer.decode(torch.zeros(256, dtype=torch.bfloat16, device=cuda))
+    assert e.value.code == -7
