@@ -1,0 +1,297 @@
+"""Benchmark of the hot path: one routed-MoE decode layer, batch 1 (config 1).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one pass of the layer over one token: router (384 experts, top-8), the 8
+selected INT4 experts, the bf16 shared expert, weighted combine.  Weights are
+synthetic (seeded) with the shapes and distributions of the configuration; no
+dataset or checkpoint is involved.  Prints ONE JSON line on rank 0.
+
+  value      layer-tokens/s with inputs resident in HBM (device-timed, CUDA events)
+  e2e        the same through the host-buffer C-ABI call (pinned host x in, y out,
+             both copies and the synchronisation inside the timed region)
+  roofline   algorithmic bytes per layer pass / device time, against the measured
+             HBM copy bandwidth of this pool (MEASURED_PEAKS.json)
+  cpu_baseline  the CPU oracle (a port of the reference arithmetic) on the host cores
+
+--impl reference times the reference arithmetic on the host cores (the reference's
+GPU executor cannot run without its storage stack; its math is restated in oracle/).
+
+Between steps the layer is rotated over several distinct synthetic layers and the
+token over a pool of inputs, so that the weights read by a step (292 MB) were last
+touched several hundred MB ago: nothing is served from L2 across steps.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "decode tok/s, INT4 MoE layer (batch 1)"
+WORKLOAD = "config 1: routed-MoE decode layer, batch 1, 384 INT4 experts top-8 + bf16 shared expert, hidden 7168"
+HBM_FALLBACK_GBS = 6650.0
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return HBM_FALLBACK_GBS, "fallback"
+
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 6:
+                    continue
+                try:
+                    sm.append(float(parts[0]))
+                    mx = max(mx, float(parts[1]))
+                except ValueError:
+                    continue
+                for n, v in zip(names, parts[2:6]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if not sm:
+            return None
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def host_layer_for_oracle(w, token_ids):
+    """Host copies of what the oracle needs for the given routed experts."""
+    import numpy as np
+    import torch
+    chosen = sorted(set(int(e) for e in token_ids))
+    experts = w["router_w"].shape[0]
+    slot_of = np.full(experts, -1, np.int32)
+    for i, e in enumerate(chosen):
+        slot_of[e] = i
+    idx = torch.tensor(chosen, device=w["gate_w"].device)
+
+    def bits(t):
+        return t.detach().contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+    def words(t):
+        return t.detach().contiguous().cpu().numpy().view(np.uint32)
+
+    h = dict(slot_of=slot_of, router_w=bits(w["router_w"]), router_bias=w["router_bias"].float().cpu().numpy())
+    for k in ("gate_w", "up_w", "down_w"):
+        h[k] = words(w[k].index_select(0, idx))
+    for k in ("gate_s", "up_s", "down_s"):
+        h[k] = bits(w[k].index_select(0, idx))
+    for k in ("shared_gate", "shared_up", "shared_down"):
+        h[k] = bits(w[k])
+    return h
+
+
+def oracle_layer_token(orc, h, x_f32):
+    out, _, _ = orc.moe_layer(h["router_w"], h["router_bias"], h["slot_of"], h["gate_w"], h["gate_s"], h["up_w"], h["up_s"],
+                              h["down_w"], h["down_s"], h["shared_gate"], h["shared_up"], h["shared_down"], x_f32,
+                              mode=orc.REF_EXACT)
+    return out
+
+
+def cpu_arm(steps, warmup, device):
+    """Times the reference arithmetic (oracle port, all host threads) on `steps` layer-tokens of config 1."""
+    import numpy as np
+    import torch
+    from blok_b200 import synth
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle as orc
+    # Weights are drawn with the same generator as the GPU arm; only the experts the sampled tokens route to are
+    # brought to the host (the full layer is 9.5 GB).
+    w = synth.moe_layer_weights(device, seed=1)
+    xs = synth.activations(max(steps + warmup, 1), 7168, device, 1).float().cpu().numpy()
+    ids, _, _, _ = orc.router(w["router_w"].view(torch.int16).cpu().numpy().view(np.uint16),
+                              w["router_bias"].float().cpu().numpy(), xs, mode=orc.REF_EXACT)
+    h = host_layer_for_oracle(w, ids.ravel())
+    del w
+    for i in range(warmup):
+        oracle_layer_token(orc, h, xs[i:i + 1])
+    t0 = time.perf_counter()
+    for i in range(warmup, warmup + steps):
+        oracle_layer_token(orc, h, xs[i:i + 1])
+    dt = time.perf_counter() - t0
+    return steps / dt, dt, orc.num_threads()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=3, help="distinct synthetic layers rotated between steps")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    a = ap.parse_args()
+
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if a.impl == "reference":
+        if rank != 0:
+            return 0
+        steps = a.steps if a.steps is not None else 12
+        warmup = a.warmup if a.warmup is not None else 3
+        steps_run = min(steps, 64)  # bounded sample: each step is one full layer-token on the host cores
+        device = torch.device("cuda:0") if torch.cuda.is_available() else torch.device("cpu")
+        rate, dt, threads = cpu_arm(steps_run, min(warmup, 3), device)
+        line = {"impl": "reference", "metric": METRIC, "value": rate, "unit": "tok/s", "n_gpus": a.gpus, "steps": steps,
+                "warmup": warmup, "ms_per_step": 1e3 / rate, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": WORKLOAD, "note": "reference arithmetic on host cores (oracle port); the reference's "
+                           "GPU executor needs its NVMe/uGDS storage stack and cannot run"},
+                "cpu_baseline": {"value": rate, "unit": "tok/s", "cores": threads, "kind": "port",
+                                 "sample": "%d layer-tokens of config 1 (%.1f s)" % (steps_run, dt)},
+                "e2e": {"value": rate, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return 0
+
+    steps = a.steps if a.steps is not None else 600
+    warmup = a.warmup if a.warmup is not None else 30
+    import torch.distributed as dist
+    from blok_b200 import lib, synth
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    lib.load()
+
+    # distinct layers (each 9.5 GB of packed experts + its own router and shared expert)
+    layers = [lib.MoeLayer(synth.moe_layer_weights(device, seed=1 + 17 * i + 1000 * rank)) for i in range(a.layers)]
+    pool = 64
+    xs = synth.activations(pool, 7168, device, 1 + rank)
+    y = torch.empty(7168, dtype=torch.bfloat16, device=device)
+
+    def step(i):
+        layers[i % len(layers)].decode(xs[i % pool], out=y)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for i in range(max(warmup, 3)):
+        step(i)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    l0 = lib.kernel_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        step(warmup + i)
+    e1.record()
+    barrier()
+    launches = lib.kernel_launch_count() - l0
+    ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms.item())
+    clocks = sampler.stop() if rank == 0 else None
+
+    # end to end through the host-buffer C-ABI call
+    xh = xs.cpu().pin_memory()
+    yh = torch.empty(7168, dtype=torch.bfloat16).pin_memory()
+    e2e_steps = max(steps // 2, 1)
+    for i in range(5):
+        layers[i % len(layers)].decode_host(xh[i % pool], yh)
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for i in range(e2e_steps):
+        layers[i % len(layers)].decode_host(xh[i % pool], yh)
+    f1.record()
+    barrier()
+    e2e_ms = torch.tensor([f0.elapsed_time(f1)], device=device)
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_ms = float(e2e_ms.item())
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+
+    ms_per_step = ms / steps
+    value = world * steps / (ms / 1e3)
+    peak, peak_kind = measured_peak()
+    alg_bytes = synth.moe_layer_bytes()
+    achieved = alg_bytes / (ms_per_step * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "parallelism": "1 GPU" if world == 1 else "replicas x%d" % world,
+                   "l2": "rotating %d distinct layers and %d tokens; a step's 292 MB were last read > L2 capacity ago"
+                         % (len(layers), pool),
+                   "algorithmic_bytes_per_step": alg_bytes},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_kind": peak_kind, "frac_of_nominal_8TBs": achieved / 8000.0,
+                     "kernel": "moe decode layer (%d launches per step)" % round(launches / steps),
+                     "traffic": None},
+        "e2e": {"value": world * e2e_steps / (e2e_ms / 1e3), "unit": "tok/s", "h2d_bytes_per_step": 7168 * 2,
+                "d2h_bytes_per_step": 7168 * 2, "ms_per_step": e2e_ms / e2e_steps},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+    if world == 1 and not a.no_cpu_baseline:
+        for L in layers:
+            L.close()
+        del layers
+        torch.cuda.empty_cache()
+        rate, dt, threads = cpu_arm(48, 1, device)
+        line["cpu_baseline"] = {"value": rate, "unit": "tok/s", "cores": threads, "kind": "port",
+                                "sample": "48 layer-tokens of config 1 (%.1f s)" % dt}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

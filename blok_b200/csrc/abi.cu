@@ -1,4 +1,5 @@
 // Error plumbing and small ABI-level helpers.
+#include <atomic>
 #include <cstdarg>
 #include <cstring>
 
@@ -20,6 +21,10 @@ int cuda_fail(cudaError_t e, const char *what) {
   return BLOK_ERR_CUDA;
 }
 
+static std::atomic<long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+long long launches() { return g_launches.load(std::memory_order_relaxed); }
+
 int sm_count() {
   static thread_local int cached_dev = -1, cached = 0;
   int dev = 0;
@@ -37,3 +42,4 @@ int sm_count() {
 
 extern "C" const char *blok_last_error(void) { return blok::g_error; }
 extern "C" int blok_abi_version(void) { return BLOK_ABI_VERSION; }
+extern "C" long long blok_kernel_launch_count(void) { return blok::launches(); }

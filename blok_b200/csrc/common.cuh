@@ -27,7 +27,10 @@ int cuda_fail(cudaError_t e, const char *what);
     }                                 \
   } while (0)
 
+void count_launch();
+
 inline int launch_status(const char *what) {
+  count_launch();
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? BLOK_OK : cuda_fail(e, what);
 }

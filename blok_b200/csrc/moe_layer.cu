@@ -66,6 +66,8 @@ extern "C" int blok_moe_layer_create(const blok_moe_weights *w, int max_tokens, 
   size_t o_mid = take((size_t)w->topk * w->inter * sizeof(uint16_t));
   size_t o_smid = take((size_t)(w->shared_inter ? w->shared_inter : 1) * 8 * sizeof(uint16_t));
   size_t o_sout = take((size_t)w->hidden * 8 * sizeof(uint16_t));
+  size_t o_iox = take((size_t)w->hidden * sizeof(uint16_t));
+  size_t o_ioy = take((size_t)w->hidden * sizeof(uint16_t));
   L->ws_bytes = off;
   cudaError_t e = cudaMalloc(&L->ws, L->ws_bytes);
   if (e != cudaSuccess) {
@@ -86,6 +88,8 @@ extern "C" int blok_moe_layer_create(const blok_moe_weights *w, int max_tokens, 
   L->mid = reinterpret_cast<uint16_t *>(b + o_mid);
   L->shared_mid = reinterpret_cast<uint16_t *>(b + o_smid);
   L->shared_out = reinterpret_cast<uint16_t *>(b + o_sout);
+  L->io_x = reinterpret_cast<uint16_t *>(b + o_iox);
+  L->io_y = reinterpret_cast<uint16_t *>(b + o_ioy);
   *out = L;
   return BLOK_OK;
 }
@@ -125,5 +129,18 @@ extern "C" int blok_moe_decode(blok_moe_layer_t *L, const blok_bf16_t *x, blok_b
   if (ids_out)
     BLOK_CUDA(cudaMemcpyAsync(ids_out, L->ids, w.topk * sizeof(uint16_t), cudaMemcpyDeviceToDevice, stream));
   if (wts_out) BLOK_CUDA(cudaMemcpyAsync(wts_out, L->wts, w.topk * sizeof(float), cudaMemcpyDeviceToDevice, stream));
+  return BLOK_OK;
+}
+
+extern "C" int blok_moe_decode_host(blok_moe_layer_t *L, const blok_bf16_t *x_host, blok_bf16_t *y_host,
+                                    blok_stream_t stream_) {
+  BLOK_REQUIRE(L && x_host && y_host, BLOK_ERR_ARG, "blok_moe_decode_host: null pointer");
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const size_t bytes = (size_t)L->w.hidden * sizeof(uint16_t);
+  BLOK_CUDA(cudaMemcpyAsync(L->io_x, x_host, bytes, cudaMemcpyHostToDevice, stream));
+  int rc = blok_moe_decode(L, L->io_x, L->io_y, nullptr, nullptr, stream_);
+  if (rc) return rc;
+  BLOK_CUDA(cudaMemcpyAsync(y_host, L->io_y, bytes, cudaMemcpyDeviceToHost, stream));
+  BLOK_CUDA(cudaStreamSynchronize(stream));
   return BLOK_OK;
 }

@@ -18,4 +18,6 @@ struct blok_moe_layer {
   uint16_t *mid = nullptr;       // [topk, inter] bf16
   uint16_t *shared_mid = nullptr;  // [8, shared_inter]
   uint16_t *shared_out = nullptr;  // [8, hidden]
+  uint16_t *io_x = nullptr;        // [hidden] staging for the host-buffer entry point
+  uint16_t *io_y = nullptr;        // [hidden]
 };

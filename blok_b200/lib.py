@@ -46,6 +46,7 @@ def load():
         raise BlokError(-100, "%s is missing: run `python -m blok_b200.build` (there is no CPU fallback)" % LIB_PATH)
     lib = C.CDLL(LIB_PATH)
     lib.blok_last_error.restype = C.c_char_p
+    lib.blok_kernel_launch_count.restype = C.c_longlong
     for name in ("blok_expert_ffn_workspace_bytes", "blok_bf16_mlp_workspace_bytes", "blok_router_workspace_bytes"):
         getattr(lib, name).restype = C.c_size_t
     _lib = lib
@@ -71,6 +72,11 @@ def _ptr(t, dtype=None, name="tensor"):
     if dtype is not None and t.dtype != dtype:
         raise BlokError(-1, "%s must have dtype %s, got %s" % (name, dtype, t.dtype))
     return C.c_void_p(t.data_ptr())
+
+
+def kernel_launch_count():
+    """Kernels launched by the library so far in this process."""
+    return int(load().blok_kernel_launch_count())
 
 
 def i4_dequant(w_packed, scale):
@@ -228,3 +234,16 @@ class MoeLayer:
         _check(load().blok_moe_decode(self._handle, _ptr(x, torch.bfloat16, "x"), _ptr(y, torch.bfloat16, "y"), _ptr(ids),
                                       _ptr(wts), _stream()))
         return (y, ids, wts) if return_routing else y
+
+    def decode_host(self, x_host, y_host):
+        """Host-buffer call: x_host / y_host are (ideally pinned) CPU bf16 tensors of [hidden]; returns after the
+        result has landed in y_host."""
+        if x_host.is_cuda or y_host.is_cuda:
+            raise BlokError(-1, "decode_host takes CPU tensors")
+        if x_host.dtype != torch.bfloat16 or y_host.dtype != torch.bfloat16 or x_host.numel() != self.hidden or \
+                y_host.numel() != self.hidden or not x_host.is_contiguous() or not y_host.is_contiguous():
+            raise BlokError(-1, "decode_host needs contiguous bf16 [hidden] tensors")
+        with torch.cuda.device(self.device):
+            _check(load().blok_moe_decode_host(self._handle, C.c_void_p(x_host.data_ptr()), C.c_void_p(y_host.data_ptr()),
+                                               _stream()))
+        return y_host

@@ -49,6 +49,9 @@ enum {
 /* Message of the last failure on this thread ("" if none). */
 const char *blok_last_error(void);
 int blok_abi_version(void);
+/* Number of kernels this library has launched in this process (all threads).  No
+ * counterpart in the reference; the bench reports it. */
+long long blok_kernel_launch_count(void);
 
 /* ------------------------------------------------------------------------- */
 /* A1  INT4 weights                                                           */
@@ -170,6 +173,15 @@ int blok_moe_layer_destroy(blok_moe_layer_t *layer);
  * must be local (experts_local == experts). */
 int blok_moe_decode(blok_moe_layer_t *layer, const blok_bf16_t *x, blok_bf16_t *y, uint16_t *ids_out, float *wts_out,
                     blok_stream_t stream);
+
+/* The same layer with HOST buffers: copies x_host (bf16 [hidden]) to the device,
+ * runs blok_moe_decode, copies the result to y_host and synchronises `stream`
+ * before returning.  This is the call shape of the reference's own boundary,
+ * where activations enter and leave through host memory per token
+ * (src/kimi_exec.cu:651-655 embed, :728-730 sampled id); pinned host memory
+ * makes the two copies asynchronous with respect to the host. */
+int blok_moe_decode_host(blok_moe_layer_t *layer, const blok_bf16_t *x_host, blok_bf16_t *y_host,
+                         blok_stream_t stream);
 
 #ifdef __cplusplus
 }
