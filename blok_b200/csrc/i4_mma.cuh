@@ -36,12 +36,22 @@ constexpr uint32_t kNibMask = 0x000f000fu;
 constexpr uint32_t kNibMagic = 0x43004300u;  // bf16 128.0 in both halves
 constexpr float kNibOffset = 136.0f;         // 128 (magic) + 8 (nibble bias)
 
-__device__ __forceinline__ uint32_t nib_pair(uint32_t shifted) { return (shifted & kNibMask) | kNibMagic; }
+// (shifted & mask) | magic as ONE three-input logic op.  Written as lop3 because the
+// plain C expression was compiled into two logic instructions per pair, which doubled
+// the load on the integer pipe, the busiest one in these kernels.
+__device__ __forceinline__ uint32_t nib_pair(uint32_t shifted) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xea;" : "=r"(r) : "r"(shifted), "r"(kNibMask), "r"(kNibMagic));
+  return r;
+}
 
-// Per-lane read-only state for the x fragments.
+// Per-lane read-only state for the x fragments.  Supplying lanes walk the
+// fragment array (16 uint4 per k-block); the other lanes stay inside the zero
+// region, which is as large as one batch of k-blocks, so every lane issues the
+// same LDS with the same immediate offsets and no predicate.
 struct XFragLane {
   const uint4 *ptr;  // supplying lanes: xfrag + t; others: zero region + t
-  int batch_stride;  // in uint4: BATCH*16 for supplying lanes, 0 for the others
+  int kb_stride;     // in uint4 per k-block: 16 for supplying lanes, 0 for the others
 };
 
 // Bytes of shared memory needed to stage `cols` columns for a given BATCH.
@@ -65,10 +75,13 @@ __device__ __forceinline__ I4Stage i4_stage_carve(unsigned char *smem, int cols,
 
 // Stage x (bf16, global, cols % 256 == 0) into fragment order, with group sums.
 // Called by all threads of the CTA (nthreads % 32 == 0); caller syncs afterwards.
+// CG = true reads through L2 (ld.global.cg): needed when x was written earlier in
+// the same kernel by another CTA.
+template <bool CG = false>
 __device__ __forceinline__ void stage_x_i4(const uint4 *x, const I4Stage &st, int cols, int batch, int tid,
                                            int nthreads) {
   for (int u = tid; u < cols / 8; u += nthreads) {
-    uint4 v = x[u];
+    uint4 v = CG ? __ldcg(x + u) : x[u];
     int kb = u >> 4, t = (u >> 2) & 3, i = u & 3;
     uint4 o;
     o.x = __byte_perm(v.x, v.z, 0x5410);
@@ -89,8 +102,9 @@ __device__ __forceinline__ XFragLane xfrag_lane(const I4Stage &st, int lane, int
   int g = lane >> 2, t = lane & 3;
   bool supply = (t == (g & 3));
   XFragLane x;
+  (void)batch;
   x.ptr = (supply ? st.xfrag : st.zero) + t;
-  x.batch_stride = supply ? batch * 16 : 0;
+  x.kb_stride = supply ? 16 : 0;
   return x;
 }
 
@@ -132,7 +146,7 @@ __device__ __forceinline__ float i4_rows16_accumulate(const uint4 *__restrict__ 
     }
 #pragma unroll
     for (int k = 0; k < BATCH; ++k) sc[k] = __ldg(reinterpret_cast<const uint32_t *>(s_sel + (kbb + k) * 4));
-    const uint4 *xp = xl.ptr + (size_t)(kbb / BATCH) * xl.batch_stride;
+    const uint4 *xp = xl.ptr + kbb * xl.kb_stride;
 #pragma unroll
     for (int k = 0; k < BATCH; ++k) {
       float d[4] = {0.f, 0.f, 0.f, 0.f};
@@ -144,6 +158,61 @@ __device__ __forceinline__ float i4_rows16_accumulate(const uint4 *__restrict__ 
       acc = fmaf(bf16hi(sc[k]), fmaf(-kNibOffset, xs.y, db), acc);
     }
   }
+  return acc;
+}
+
+// Loads and arithmetic of one batch of k-blocks as separate steps, so that a caller
+// can put the weight loads in flight, wait for something else (another CTA's
+// results, say) and only then touch the activations.
+template <int BATCH>
+struct I4Batch {
+  uint4 wl[BATCH], wh[BATCH];
+  uint32_t sc[BATCH];
+};
+
+template <int BATCH>
+__device__ __forceinline__ void i4_batch_load(I4Batch<BATCH> &b, const uint4 *__restrict__ w_lo,
+                                              const uint4 *__restrict__ w_hi, const uint16_t *__restrict__ s_sel,
+                                              int kb0, int t) {
+#pragma unroll
+  for (int k = 0; k < BATCH; ++k) {
+    b.wl[k] = ldg_stream(w_lo + (kb0 + k) * 4 + t);
+    b.wh[k] = ldg_stream(w_hi + (kb0 + k) * 4 + t);
+  }
+#pragma unroll
+  for (int k = 0; k < BATCH; ++k) b.sc[k] = __ldg(reinterpret_cast<const uint32_t *>(s_sel + (kb0 + k) * 4));
+}
+
+// kbx is the k-block index of the batch inside the staged activation segment.
+template <int BATCH>
+__device__ __forceinline__ float i4_batch_compute(const I4Batch<BATCH> &b, const XFragLane &xl, const float *xsum,
+                                                  int kbx, int lane, float acc) {
+  const int t = lane & 3;
+  const bool hi_row = (t >> 1) != 0;
+  const int j0 = 2 * (t & 1);
+  const uint4 *xp = xl.ptr + kbx * xl.kb_stride;
+#pragma unroll
+  for (int k = 0; k < BATCH; ++k) {
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+    i4_kblock_mma(b.wl[k], b.wh[k], xp + k * 16, d);
+    float2 xs = *reinterpret_cast<const float2 *>(xsum + (kbx + k) * 4 + j0);
+    float da = hi_row ? d[2] : d[0];
+    float db = hi_row ? d[3] : d[1];
+    acc = fmaf(bf16lo(b.sc[k]), fmaf(-kNibOffset, xs.x, da), acc);
+    acc = fmaf(bf16hi(b.sc[k]), fmaf(-kNibOffset, xs.y, db), acc);
+  }
+  return acc;
+}
+
+// The same over an arbitrary k-block range [kb0, kb0 + nkb): full batches, then singles.
+template <int BATCH>
+__device__ __forceinline__ float i4_rows16_range(const uint4 *__restrict__ w_lo, const uint4 *__restrict__ w_hi,
+                                                 const uint16_t *__restrict__ s_sel, const XFragLane &xl,
+                                                 const float *xsum, int kb0, int nkb, int lane) {
+  const int nfull = nkb / BATCH;
+  float acc = i4_rows16_accumulate<BATCH>(w_lo, w_hi, s_sel, xl, xsum, kb0, nfull, lane);
+  const int done = nfull * BATCH;
+  if (done < nkb) acc += i4_rows16_accumulate<1>(w_lo, w_hi, s_sel, xl, xsum, kb0 + done, nkb - done, lane);
   return acc;
 }
 

@@ -1,7 +1,9 @@
 // Routed-MoE layer handle and the batch-1 decode path.
 // Reference: the MoE branch of the layer body, src/kimi_exec.cu:836-875.
+#include <algorithm>
 #include <cstdlib>
 #include <new>
+#include <string>
 
 #include "common.cuh"
 #include "moe_layer.h"
@@ -20,6 +22,10 @@ int launch_i4_gateup(const uint32_t *gate_w, const uint16_t *gate_s, const uint3
 int launch_i4_down(const uint32_t *down_w, const uint16_t *down_s, const uint16_t *mid, const int *slot_expert,
                    const float *wts, const uint16_t *addend, uint16_t *out, int hidden, int inter, int slots,
                    cudaStream_t stream);
+
+int fused_plan(const blok_moe_weights &w, FusedPlan *plan);
+int launch_moe_decode_fused(blok_moe_layer *L, const uint16_t *x, uint16_t *y, uint16_t *ids_out, float *wts_out,
+                            cudaStream_t stream);
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -52,6 +58,15 @@ extern "C" int blok_moe_layer_create(const blok_moe_weights *w, int max_tokens, 
   BLOK_REQUIRE(L, BLOK_ERR_ARG, "blok_moe_layer_create: out of host memory");
   L->w = *w;
   L->max_tokens = max_tokens;
+  {
+    int rc = fused_plan(*w, &L->plan);
+    if (rc) {
+      delete L;
+      return rc;
+    }
+    const char *impl = std::getenv("BLOK_MOE_DECODE_IMPL");  // "multi" forces the multi-kernel path (for comparison)
+    L->use_fused = L->plan.enabled && !(impl && std::string(impl) == "multi");
+  }
   // decode workspace carve-up
   size_t off = 0;
   auto take = [&](size_t bytes) {
@@ -68,6 +83,23 @@ extern "C" int blok_moe_layer_create(const blok_moe_weights *w, int max_tokens, 
   size_t o_sout = take((size_t)w->hidden * 8 * sizeof(uint16_t));
   size_t o_iox = take((size_t)w->hidden * sizeof(uint16_t));
   size_t o_ioy = take((size_t)w->hidden * sizeof(uint16_t));
+  const blok::FusedPlan &pl = L->plan;
+  size_t o_fmid = 0, o_fys = 0, o_pR = 0, o_route = 0, o_pA = 0, o_pB = 0, o_pC2 = 0, o_cnt = 0, n_cnt = 0;
+  if (pl.enabled) {
+    L->f_mid_stride = (int)align_up((size_t)std::max(w->inter, w->shared_inter), 64);
+    o_fmid = take((size_t)(w->topk + 1) * L->f_mid_stride * sizeof(uint16_t));
+    o_fys = take((size_t)(w->topk + 1) * w->hidden * sizeof(float));
+    o_route = take(32 * sizeof(float));
+    o_pR = take((size_t)pl.nrbR * pl.cprR * 16 * sizeof(float));
+    o_pA = take((size_t)std::max(pl.nrbA, 1) * pl.cprA * 16 * sizeof(float));
+    o_pB = take((size_t)pl.nrbB * pl.cprB * 16 * sizeof(float));
+    o_pC2 = take((size_t)std::max(pl.nrbC2, 1) * pl.cprC2 * 16 * sizeof(float));
+    n_cnt = (size_t)pl.nrbR + pl.nrbA + pl.nrbB + pl.nrbC2 + w->hidden / 16 + 8;
+    o_cnt = take(n_cnt * sizeof(unsigned));
+  }
+  const char *trace_env = std::getenv("BLOK_MOE_TRACE");
+  const bool want_trace = pl.enabled && trace_env && trace_env[0] == '1';
+  size_t o_trace = want_trace ? take(((size_t)pl.grid + 1) * 16 * sizeof(long long)) : 0;
   L->ws_bytes = off;
   cudaError_t e = cudaMalloc(&L->ws, L->ws_bytes);
   if (e != cudaSuccess) {
@@ -90,6 +122,27 @@ extern "C" int blok_moe_layer_create(const blok_moe_weights *w, int max_tokens, 
   L->shared_out = reinterpret_cast<uint16_t *>(b + o_sout);
   L->io_x = reinterpret_cast<uint16_t *>(b + o_iox);
   L->io_y = reinterpret_cast<uint16_t *>(b + o_ioy);
+  if (pl.enabled) {
+    L->f_mid = reinterpret_cast<uint16_t *>(b + o_fmid);
+    L->f_ys = reinterpret_cast<float *>(b + o_fys);
+    L->f_route_ids = reinterpret_cast<int *>(b + o_route);
+    L->f_route_wts = reinterpret_cast<float *>(b + o_route) + 16;
+    L->f_partR = reinterpret_cast<float *>(b + o_pR);
+    L->f_partA = reinterpret_cast<float *>(b + o_pA);
+    L->f_partB = reinterpret_cast<float *>(b + o_pB);
+    L->f_partC2 = reinterpret_cast<float *>(b + o_pC2);
+    unsigned *c = reinterpret_cast<unsigned *>(b + o_cnt);
+    L->f_counters = c;
+    L->f_counters_bytes = n_cnt * sizeof(unsigned);
+    L->f_ctrl = c;
+    c += 8;
+    L->f_cntR = c; c += pl.nrbR;
+    L->f_cntA = c; c += pl.nrbA;
+    L->f_cntB = c; c += pl.nrbB;
+    L->f_cntC2 = c; c += pl.nrbC2;
+    L->f_cntOut = c;
+    if (want_trace) L->f_trace = reinterpret_cast<long long *>(b + o_trace);
+  }
   *out = L;
   return BLOK_OK;
 }
@@ -109,6 +162,7 @@ extern "C" int blok_moe_decode(blok_moe_layer_t *L, const blok_bf16_t *x, blok_b
                "blok_moe_decode: needs every expert local (have [%d, %d) of %d)", w.expert_base,
                w.expert_base + w.experts_local, w.experts);
   cudaStream_t stream = (cudaStream_t)stream_;
+  if (L->use_fused) return launch_moe_decode_fused(L, x, y, ids_out, wts_out, stream);
   int rc = launch_bf16_gemv(w.router_w, x, nullptr, L->logits, w.experts, w.hidden, 1, stream);
   if (rc) return rc;
   rc = launch_router_topk(L->logits, w.router_bias, 1, w.experts, w.topk, w.routed_scale, L->ids, L->wts, L->local_ids,
@@ -132,6 +186,20 @@ extern "C" int blok_moe_decode(blok_moe_layer_t *L, const blok_bf16_t *x, blok_b
   return BLOK_OK;
 }
 
+extern "C" int blok_moe_layer_check(blok_moe_layer_t *L, blok_stream_t stream_) {
+  BLOK_REQUIRE(L, BLOK_ERR_ARG, "blok_moe_layer_check: null pointer");
+  cudaStream_t stream = (cudaStream_t)stream_;
+  BLOK_CUDA(cudaStreamSynchronize(stream));
+  if (!L->f_ctrl) return BLOK_OK;
+  unsigned err = 0;
+  BLOK_CUDA(cudaMemcpy(&err, L->f_ctrl + 5, sizeof(err), cudaMemcpyDeviceToHost));
+  if (err == 0) return BLOK_OK;
+  // a bounded wait inside the fused kernel gave up: clear every counter so that the handle stays usable
+  BLOK_CUDA(cudaMemset(L->f_counters, 0, L->f_counters_bytes));
+  set_error("blok_moe_decode: device-side wait %u timed out (1 = routing, 2 = mid values)", err);
+  return BLOK_ERR_TIMEOUT;
+}
+
 extern "C" int blok_moe_decode_host(blok_moe_layer_t *L, const blok_bf16_t *x_host, blok_bf16_t *y_host,
                                     blok_stream_t stream_) {
   BLOK_REQUIRE(L && x_host && y_host, BLOK_ERR_ARG, "blok_moe_decode_host: null pointer");
@@ -141,6 +209,15 @@ extern "C" int blok_moe_decode_host(blok_moe_layer_t *L, const blok_bf16_t *x_ho
   int rc = blok_moe_decode(L, L->io_x, L->io_y, nullptr, nullptr, stream_);
   if (rc) return rc;
   BLOK_CUDA(cudaMemcpyAsync(y_host, L->io_y, bytes, cudaMemcpyDeviceToHost, stream));
-  BLOK_CUDA(cudaStreamSynchronize(stream));
-  return BLOK_OK;
+  return blok_moe_layer_check(L, stream_);
+}
+
+extern "C" int blok_moe_layer_trace(blok_moe_layer_t *L, long long *host_out, int max_entries) {
+  BLOK_REQUIRE(L && host_out, BLOK_ERR_ARG, "blok_moe_layer_trace: null pointer");
+  if (!L->f_trace) return 0;
+  int n = (L->plan.grid + 1) * 16;
+  if (n > max_entries) n = max_entries;
+  BLOK_CUDA(cudaDeviceSynchronize());
+  BLOK_CUDA(cudaMemcpy(host_out, L->f_trace, (size_t)n * sizeof(long long), cudaMemcpyDeviceToHost));
+  return n;
 }

@@ -5,6 +5,23 @@
 
 #include "../../include/blok_b200.h"
 
+namespace blok {
+// Launch geometry and scratch sizing of the fused decode kernel (moe_fused.cu).
+struct FusedPlan {
+  bool enabled = false;
+  int grid = 0;
+  size_t smem = 0;
+  int total_warps = 0;
+  // row-blocks per phase; steps per row-block, steps per chunk, chunks per row-block
+  int nrbR = 0, nrbA = 0, nrbB = 0, nrbC1 = 0, nrbC2 = 0;
+  int sprR = 0, spcR = 0, cprR = 1;
+  int sprA = 0, spcA = 0, cprA = 1;
+  int sprB = 0, spcB = 0, cprB = 1;
+  int sprC1 = 0;
+  int sprC2 = 0, spcC2 = 0, cprC2 = 1;
+};
+}  // namespace blok
+
 struct blok_moe_layer {
   blok_moe_weights w;
   int max_tokens = 0;
@@ -20,4 +37,18 @@ struct blok_moe_layer {
   uint16_t *shared_out = nullptr;  // [8, hidden]
   uint16_t *io_x = nullptr;        // [hidden] staging for the host-buffer entry point
   uint16_t *io_y = nullptr;        // [hidden]
+  // fused decode kernel scratch
+  blok::FusedPlan plan;
+  bool use_fused = false;
+  uint16_t *f_mid = nullptr;  // [topk + 1][f_mid_stride]
+  int f_mid_stride = 0;
+  float *f_ys = nullptr;      // [topk + 1][hidden]
+  float *f_partR = nullptr, *f_partA = nullptr, *f_partB = nullptr, *f_partC2 = nullptr;
+  unsigned *f_cntR = nullptr, *f_cntA = nullptr, *f_cntB = nullptr, *f_cntC2 = nullptr, *f_cntOut = nullptr;
+  unsigned *f_ctrl = nullptr;  // [8] queue head, router row-blocks, routed, mid row-blocks, exits, error
+  int *f_route_ids = nullptr;   // [16]
+  float *f_route_wts = nullptr; // [16]
+  long long *f_trace = nullptr;  // [1 + grid][16] time stamps, only with BLOK_MOE_TRACE=1
+  void *f_counters = nullptr;  // start of the counter block (zeroed on reset)
+  size_t f_counters_bytes = 0;
 };

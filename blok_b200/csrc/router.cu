@@ -1,9 +1,7 @@
 // Router: fp32 logits, sigmoid, bias, top-k by repeated argmax, normalise, scale.
 // Reference arithmetic: src/kimi_exec.cu:836-842 with matvec_bf16_f32_k :286-298,
 // sigmoid_k :377-380, add_bf16_k :372-375, router_topk_k :382-397.
-#include <cmath>
-
-#include "common.cuh"
+#include "router_topk.cuh"
 
 namespace blok {
 
@@ -31,34 +29,13 @@ __global__ void router_topk_kernel(const float *__restrict__ logits, const float
     sel[i] = s + bias[i];
   }
   __syncwarp();
-  float sum = 0.f;
-  float my_w = 0.f;  // lane k keeps the k-th selected score
-  int my_id = 0;
-  for (int k = 0; k < topk; ++k) {
-    float best = -INFINITY;
-    int id = 0x7fffffff;
-    for (int i = lane; i < experts; i += 32) {
-      float v = sel[i];
-      if (v > best) best = v, id = i;
-    }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) {
-      float ob = __shfl_xor_sync(0xffffffffu, best, o);
-      int oi = __shfl_xor_sync(0xffffffffu, id, o);
-      if (ob > best || (ob == best && oi < id)) best = ob, id = oi;
-    }
-    if (id == 0x7fffffff) id = 0;  // every candidate was -inf or NaN: the reference keeps id 0
-    float s = score[id];
-    sum += s;
-    if (lane == k) my_w = s, my_id = id;
-    __syncwarp();
-    if (lane == 0) sel[id] = -INFINITY;
-    __syncwarp();
-  }
+  int my_id;
+  float my_w;
+  warp_topk(score, sel, experts, topk, routed_scale, lane, my_id, my_w);
   if (lane < topk) {
     if (ids) ids[(size_t)tok * topk + lane] = (uint16_t)my_id;
     if (local_ids) local_ids[(size_t)tok * topk + lane] = my_id - expert_base;
-    wts[(size_t)tok * topk + lane] = my_w / (sum + 1.0e-20f) * routed_scale;
+    wts[(size_t)tok * topk + lane] = my_w;
   }
 }
 

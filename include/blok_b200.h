@@ -174,6 +174,18 @@ int blok_moe_layer_destroy(blok_moe_layer_t *layer);
 int blok_moe_decode(blok_moe_layer_t *layer, const blok_bf16_t *x, blok_bf16_t *y, uint16_t *ids_out, float *wts_out,
                     blok_stream_t stream);
 
+/* Synchronises `stream` and reports whether a device-side wait of an earlier
+ * blok_moe_decode on this handle gave up (BLOK_ERR_TIMEOUT; the handle is reset
+ * and stays usable).  The reference has no such state: its kernels never wait
+ * on one another (src/kimi_exec.cu launches are all on the default stream). */
+int blok_moe_layer_check(blok_moe_layer_t *layer, blok_stream_t stream);
+
+/* Diagnostics (no counterpart in the reference): when the handle was created with
+ * the environment variable BLOK_MOE_TRACE=1, the fused decode kernel records
+ * nanosecond time stamps: 16 launch-wide slots, then 16 slots per CTA.  Copies up to max_entries of
+ * them to host_out after a device synchronise; returns the count (0 = tracing off). */
+int blok_moe_layer_trace(blok_moe_layer_t *layer, long long *host_out, int max_entries);
+
 /* The same layer with HOST buffers: copies x_host (bf16 [hidden]) to the device,
  * runs blok_moe_decode, copies the result to y_host and synchronises `stream`
  * before returning.  This is the call shape of the reference's own boundary,

@@ -54,10 +54,27 @@ def _check(cuda, oracle, hidden, inter, experts, shared_inter, seed, topk=8):
     return r, c
 
 
+@pytest.mark.parametrize("impl", ["fused", "multi"])
 @pytest.mark.parametrize("hidden,inter,experts,shared_inter,seed", [(512, 256, 16, 256, 11), (1024, 512, 32, 0, 12),
-                                                                    (7168, 2048, 24, 2048, 13)])
-def test_moe_decode_small(cuda, oracle, hidden, inter, experts, shared_inter, seed):
+                                                                    (7168, 2048, 24, 2048, 13), (256, 256, 48, 32, 14)])
+def test_moe_decode_small(cuda, oracle, monkeypatch, impl, hidden, inter, experts, shared_inter, seed):
+    """Both implementations of the layer: the single persistent kernel and the multi-kernel path."""
+    monkeypatch.setenv("BLOK_MOE_DECODE_IMPL", impl)
     _check(cuda, oracle, hidden, inter, experts, shared_inter, seed)
+
+
+def test_moe_decode_many_tokens_fused(cuda, oracle):
+    """Back-to-back launches on one handle: the kernel's self-cleaning counters must leave no state behind."""
+    from blok_b200 import lib, synth
+    w = synth.moe_layer_weights(cuda, seed=21, hidden=1024, inter=512, experts=32, shared_inter=512)
+    layer = lib.MoeLayer(w)
+    xs = synth.activations(24, 1024, cuda, 21)
+    first = [layer.decode(xs[i]).clone() for i in range(24)]
+    again = [layer.decode(xs[i]).clone() for i in range(24)]
+    for a, b in zip(first, again):
+        assert torch.equal(a, b)
+    assert lib.load().blok_moe_layer_check(layer._handle, None) == 0
+    layer.close()
 
 
 def test_moe_decode_config1_full_size(cuda, oracle):
