@@ -1,6 +1,8 @@
 // INT4 (W4A16) kernels: dequant probe, mat-vec, and the single-expert SwiGLU FFN.
 // Reference arithmetic: src/kimi_exec.cu:300-323 (matvec_i4_bf16_scale_k),
 // :253-256 (silu_mul_k), :853-869 (per-slot body of the routed-expert loop).
+#include <mutex>
+
 #include "i4_mma.cuh"
 
 namespace blok {
@@ -364,6 +366,74 @@ extern "C" int blok_expert_ffn(const uint32_t *gate_w, const blok_bf16_t *gate_s
                BLOK_ERR_ARG, "blok_expert_ffn: pointers must be 16-byte aligned");
   uint16_t *mid = static_cast<uint16_t *>(workspace);
   int rc = launch_i4_gateup(gate_w, gate_s, up_w, up_s, x, nullptr, mid, hidden, inter, 1, (cudaStream_t)stream);
+  if (rc) return rc;
+  return launch_i4_down(down_w, down_s, mid, nullptr, nullptr, nullptr, y, hidden, inter, 1, (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------
+// blok_expert_ffn_static: the single-expert FFN for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc at the point where they run an
+// expert: a serving loop that has handed all device memory to its own pool, code
+// running inside a region where the allocator is locked, or a plugin boundary that
+// forbids allocation after start-up.  blok_expert_ffn makes such a caller bring a
+// workspace for the intermediate vector (mid = SiLU(gate x) * up x); this variant
+// keeps that vector in a fixed array that is part of the library image instead.
+//
+// The array below lives in every CUDA context that loads the library, for as long
+// as the context lives (BLOK_STATIC_MAX_INTER * 2 bytes = 16 KB per GPU).  In host
+// code the name g_static_mid is only a handle for the symbol, not a device address:
+// the address that kernels may use comes from cudaGetSymbolAddress, asked once per
+// device with that device current, and cached.
+// ---------------------------------------------------------------------------
+static __device__ __align__(256) uint16_t g_static_mid[BLOK_STATIC_MAX_INTER];
+
+namespace blok {
+constexpr int kMaxDevices = 64;
+static std::mutex g_static_mutex;
+static uint16_t *g_static_mid_addr[kMaxDevices] = {};
+
+// Device address of g_static_mid on the current device (looked up on first use).
+static int static_mid_address(uint16_t **out) {
+  int dev = 0;
+  BLOK_CUDA(cudaGetDevice(&dev));
+  BLOK_REQUIRE(dev >= 0 && dev < kMaxDevices, BLOK_ERR_STATE, "blok_expert_ffn_static: device ordinal %d not supported", dev);
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (!g_static_mid_addr[dev]) {
+    void *p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_mid);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_static_mid)");
+    BLOK_REQUIRE(p != nullptr, BLOK_ERR_CUDA, "blok_expert_ffn_static: symbol address is null");
+    g_static_mid_addr[dev] = static_cast<uint16_t *>(p);
+  }
+  *out = g_static_mid_addr[dev];
+  return BLOK_OK;
+}
+}  // namespace blok
+
+extern "C" int blok_expert_ffn_static_max_inter(void) { return BLOK_STATIC_MAX_INTER; }
+
+extern "C" int blok_expert_ffn_static(const uint32_t *gate_w, const blok_bf16_t *gate_s, const uint32_t *up_w,
+                                      const blok_bf16_t *up_s, const uint32_t *down_w, const blok_bf16_t *down_s,
+                                      const blok_bf16_t *x, blok_bf16_t *y, int hidden, int inter,
+                                      blok_stream_t stream) {
+  BLOK_REQUIRE(gate_w && gate_s && up_w && up_s && down_w && down_s && x && y, BLOK_ERR_ARG,
+               "blok_expert_ffn_static: null pointer");
+  BLOK_REQUIRE(hidden > 0 && inter > 0 && hidden % 256 == 0 && inter % 256 == 0 && hidden <= 32768, BLOK_ERR_SHAPE,
+               "blok_expert_ffn_static: hidden %d and inter %d must be positive multiples of 256 (hidden <= 32768)",
+               hidden, inter);
+  BLOK_REQUIRE(inter <= BLOK_STATIC_MAX_INTER, BLOK_ERR_WORKSPACE,
+               "blok_expert_ffn_static: inter %d exceeds the built-in scratch of %d values; use blok_expert_ffn with a "
+               "caller workspace",
+               inter, BLOK_STATIC_MAX_INTER);
+  BLOK_REQUIRE(aligned16(gate_w) && aligned16(up_w) && aligned16(down_w) && aligned16(x), BLOK_ERR_ARG,
+               "blok_expert_ffn_static: pointers must be 16-byte aligned");
+  uint16_t *mid = nullptr;
+  int rc = static_mid_address(&mid);
+  if (rc) return rc;
+  // every element of mid[0, inter) is rewritten by the gate/up kernel before the down kernel reads it,
+  // so nothing left over from an earlier call can leak into this one
+  rc = launch_i4_gateup(gate_w, gate_s, up_w, up_s, x, nullptr, mid, hidden, inter, 1, (cudaStream_t)stream);
   if (rc) return rc;
   return launch_i4_down(down_w, down_s, mid, nullptr, nullptr, nullptr, y, hidden, inter, 1, (cudaStream_t)stream);
 }

@@ -118,6 +118,19 @@ def expert_ffn(gate_w, gate_s, up_w, up_s, down_w, down_s, x, workspace=None):
     return y
 
 
+def expert_ffn_static(gate_w, gate_s, up_w, up_s, down_w, down_s, x, out=None):
+    """One routed expert without a workspace argument: the intermediate vector lives in a fixed array inside the
+    library, so the call allocates nothing on the device when `out` is given.  For callers that may not allocate;
+    inter is limited to blok_expert_ffn_static_max_inter(); calls that can overlap on the GPU race on that array."""
+    inter, hidden = gate_w.shape[0], gate_w.shape[1] * 8
+    y = torch.empty(hidden, dtype=torch.bfloat16, device=x.device) if out is None else out
+    _check(load().blok_expert_ffn_static(_ptr(gate_w, torch.int32), _ptr(gate_s, torch.bfloat16), _ptr(up_w, torch.int32),
+                                         _ptr(up_s, torch.bfloat16), _ptr(down_w, torch.int32),
+                                         _ptr(down_s, torch.bfloat16), _ptr(x, torch.bfloat16), _ptr(y, torch.bfloat16),
+                                         C.c_int(hidden), C.c_int(inter), _stream()))
+    return y
+
+
 def bf16_gemv(w, x, out_f32=False):
     """matvec_bf16_k / matvec_bf16_f32_k (src/kimi_exec.cu:272-298) for x [T<=8, cols] or [cols]."""
     rows, cols = w.shape

@@ -89,6 +89,26 @@ int blok_expert_ffn(const uint32_t *gate_w, const blok_bf16_t *gate_s, const uin
                     const uint32_t *down_w, const blok_bf16_t *down_s, const blok_bf16_t *x, blok_bf16_t *y,
                     int hidden, int inter, void *workspace, size_t workspace_bytes, blok_stream_t stream);
 
+/* The same expert for callers that cannot allocate device memory when they call
+ * (an engine that owns all of HBM through its own pool, a code path that runs with
+ * the allocator locked, a host that forbids allocation after start-up).  It has no
+ * counterpart in the reference, whose executor allocates freely (src/kimi_exec.cu
+ * cudaMalloc per tile).  The intermediate vector lives in a fixed array inside the
+ * library (BLOK_STATIC_MAX_INTER bf16 values, 16 KB, held by every GPU that loads
+ * the library until the process exits), so there is no workspace argument and no
+ * cudaMalloc / cudaFree anywhere on this path.
+ *  - inter > BLOK_STATIC_MAX_INTER is rejected with BLOK_ERR_WORKSPACE.
+ *  - The first call on each device looks up the array's device address; make that
+ *    first call before any stream capture on that device.
+ *  - All calls on a device share the one array: two calls whose kernels can overlap
+ *    on the GPU (different streams, no dependency between them) race on it.  Calls
+ *    on one stream are safe; nothing needs clearing between calls. */
+#define BLOK_STATIC_MAX_INTER 8192
+int blok_expert_ffn_static_max_inter(void);
+int blok_expert_ffn_static(const uint32_t *gate_w, const blok_bf16_t *gate_s, const uint32_t *up_w,
+                           const blok_bf16_t *up_s, const uint32_t *down_w, const blok_bf16_t *down_s,
+                           const blok_bf16_t *x, blok_bf16_t *y, int hidden, int inter, blok_stream_t stream);
+
 /* ------------------------------------------------------------------------- */
 /* A6/A7/A10  bf16 GEMV, dense SwiGLU MLP, RMSNorm, residual add               */
 /* ------------------------------------------------------------------------- */
