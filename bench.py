@@ -35,6 +35,7 @@ sys.path.insert(0, ROOT)
 METRIC = "decode tok/s, INT4 MoE layer (batch 1)"
 WORKLOAD = "config 1: routed-MoE decode layer, batch 1, 384 INT4 experts top-8 + bf16 shared expert, hidden 7168"
 HBM_FALLBACK_GBS = 6650.0
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 297.5e6
 
 
 def measured_peak():
@@ -60,7 +61,7 @@ class ClockSampler:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
@@ -189,8 +190,8 @@ def main():
         print(json.dumps(line))
         return 0
 
-    steps = a.steps if a.steps is not None else 600
-    warmup = a.warmup if a.warmup is not None else 30
+    steps = a.steps if a.steps is not None else 4000
+    warmup = a.warmup if a.warmup is not None else 50
     import torch.distributed as dist
     from blok_b200 import lib, synth
     torch.cuda.set_device(local_rank)
@@ -237,7 +238,7 @@ def main():
     # end to end through the host-buffer C-ABI call
     xh = xs.cpu().pin_memory()
     yh = torch.empty(7168, dtype=torch.bfloat16).pin_memory()
-    e2e_steps = max(steps // 2, 1)
+    e2e_steps = max(min(steps // 2, 1000), 1)
     for i in range(5):
         layers[i % len(layers)].decode_host(xh[i % pool], yh)
     barrier()
@@ -273,7 +274,9 @@ def main():
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": peak_kind, "frac_of_nominal_8TBs": achieved / 8000.0,
                      "kernel": "moe decode layer (%d launches per step)" % round(launches / steps),
-                     "traffic": None},
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised
+                     # in profiles/moe_decode_fused_config1.md (a launch reads 8 experts whatever the expert count)
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
         "e2e": {"value": world * e2e_steps / (e2e_ms / 1e3), "unit": "tok/s", "h2d_bytes_per_step": 7168 * 2,
                 "d2h_bytes_per_step": 7168 * 2, "ms_per_step": e2e_ms / e2e_steps},
         "gpu_launches": int(launches),
