@@ -1,0 +1,375 @@
+// MLA decode attention in the absorbed form over a bf16 latent cache.
+// Reference: src/kimi_exec.cu:813-826 (projections, RMSNorm, RoPE, KV store, o_proj)
+// and :692-716 / :414-475 (three-pass softmax attention over materialised K/V).
+//
+// The reference stores, per token and layer, the full K [64 x 192] and V [64 x 128]
+// in fp32 (81,920 B) and re-reads K three times.  Both are functions of the bf16
+// latent row (normed c_kv [512], roped k_pe [64]) that the reference computes at
+// :817-823, so the cache here is that row, 1,152 B per token, and the attention is
+// evaluated in the latent space:
+//   q_abs_h = W_UK_h^T q_nope_h        W_UK_h = kv_b rows [h*256, h*256+128)   (:366-369)
+//   s_t     = (q_abs_h . c_t + q_rope_h . kpe_t) * scale
+//   o_lat_h = sum_t softmax(s)_t c_t
+//   out_h   = W_UV_h o_lat_h           W_UV_h = kv_b rows [h*256+128, h*256+256)
+// One pass over the cache with an online softmax; the sequence is split over CTAs
+// (flash-decoding) and the partial results are merged by a second kernel.
+#include <cmath>
+#include <new>
+
+#include "bf16_mma.cuh"
+
+namespace blok {
+
+int launch_bf16_gemv(const uint16_t *w, const uint16_t *x, uint16_t *y_bf16, float *y_f32, int rows, int cols, int T,
+                     cudaStream_t stream);
+
+// ---------------------------------------------------------------------------
+// Per-head mat-vec for up to 8 tokens: y[tok, head, r] = sum_c W[head][r][c] * x[tok, head, c].
+// grid = (rows/16, heads), 4 warps split K.  Strides are in elements.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+    bf16_head_gemv_kernel(const uint16_t *__restrict__ w, long w_head_stride, const uint16_t *__restrict__ x,
+                          long x_tok_stride, long x_head_stride, uint16_t *__restrict__ y, long y_tok_stride,
+                          long y_head_stride, int cols, int T) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  __shared__ float partial[4][16][8];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int head = blockIdx.y;
+  const int per_row = cols / 8;
+  for (int u = tid; u < per_row * T; u += blockDim.x) {
+    int tok = u / per_row, c = u - tok * per_row;
+    uint4 v = reinterpret_cast<const uint4 *>(x + (size_t)tok * x_tok_stride + (size_t)head * x_head_stride)[c];
+    reinterpret_cast<uint4 *>(smem + tok * bf16_x_row_bytes(cols))[c] = v;
+  }
+  __syncthreads();
+  const size_t wrow = cols / 8;
+  const int row0 = blockIdx.x * 16;
+  const uint4 *w_lo = reinterpret_cast<const uint4 *>(w + (size_t)head * w_head_stride) + (size_t)(row0 + g) * wrow;
+  const uint4 *w_hi = w_lo + 8 * wrow;
+  const int tok = g < T ? g : T - 1;
+  const uint4 *xrow = reinterpret_cast<const uint4 *>(smem + tok * bf16_x_row_bytes(cols)) + t;
+  const int ksteps = cols / 32;
+  const int base = ksteps / 4, rem = ksteps % 4;
+  const int ks0 = warp * base + (warp < rem ? warp : rem);
+  const int nsteps = base + (warp < rem ? 1 : 0);
+  float d[4] = {0.f, 0.f, 0.f, 0.f};
+  bf16_rows16_accumulate(w_lo, w_hi, xrow, ks0, nsteps, t, d);
+  partial[warp][g][2 * t] = d[0];
+  partial[warp][g][2 * t + 1] = d[1];
+  partial[warp][g + 8][2 * t] = d[2];
+  partial[warp][g + 8][2 * t + 1] = d[3];
+  __syncthreads();
+  if (tid < 128) {
+    int r = tid >> 3, tk = tid & 7;
+    if (tk < T) {
+      float v = partial[0][r][tk] + partial[1][r][tk] + partial[2][r][tk] + partial[3][r][tk];
+      y[(size_t)tk * y_tok_stride + (size_t)head * y_head_stride + row0 + r] = f32_to_bf16_bits(v);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Per sequence: RMSNorm of c_kv, RoPE of k_pe, append to the cache; RoPE of the
+// query's rope part into q_full.  src/kimi_exec.cu:817 (norm), :346-357 (rope).
+//   kva    bf16 [B, kv_rank + rope]   output of kv_a_proj_with_mqa
+//   q      bf16 [B, heads, nope + rope]
+//   q_full bf16 [B, heads, kv_rank + rope]; this kernel writes columns [kv_rank, kv_rank+rope)
+// ---------------------------------------------------------------------------
+__global__ void mla_prep_kernel(const uint16_t *__restrict__ kva, const uint16_t *__restrict__ kva_ln,
+                                const uint16_t *__restrict__ q, const float *__restrict__ inv_freq,
+                                const int *__restrict__ ctx_len, uint16_t *__restrict__ cache, long ctx_stride,
+                                uint16_t *__restrict__ q_full, int heads, int nope, int rope, int kv_rank, float eps) {
+  __shared__ float red[32];
+  __shared__ float cs[256];  // cos then sin, rope/2 each
+  const int b = blockIdx.x, tid = threadIdx.x;
+  const int pos = ctx_len[b];
+  const int half = rope / 2, lat_w = kv_rank + rope;
+  const uint16_t *kr = kva + (size_t)b * lat_w;
+  uint16_t *row = cache + ((size_t)b * ctx_stride + pos) * lat_w;
+  for (int p = tid; p < half; p += blockDim.x) {
+    float ang = pos * inv_freq[p];
+    cs[p] = round_bf16(cosf(ang));
+    cs[half + p] = round_bf16(sinf(ang));
+  }
+  float v = 0.f;
+  for (int i = tid; i < kv_rank; i += blockDim.x) {
+    float a = bf16_bits_to_f32(kr[i]);
+    v = fmaf(a, a, v);
+  }
+  v = warp_sum(v);
+  if ((tid & 31) == 0) red[tid >> 5] = v;
+  __syncthreads();
+  if (tid < 32) {
+    float s = tid < (blockDim.x >> 5) ? red[tid] : 0.f;
+    s = warp_sum(s);
+    if (tid == 0) red[0] = s;
+  }
+  __syncthreads();
+  const float scale = rsqrtf(red[0] / kv_rank + eps);
+  for (int i = tid; i < kv_rank; i += blockDim.x)
+    row[i] = f32_to_bf16_bits(round_bf16(bf16_bits_to_f32(kr[i]) * scale) * bf16_bits_to_f32(kva_ln[i]));
+  // k_pe: interleaved pair (2p, 2p+1) -> de-interleaved (p, half+p); every product rounded (:353-356)
+  for (int p = tid; p < half; p += blockDim.x) {
+    float c = cs[p], s = cs[half + p];
+    float x0 = bf16_bits_to_f32(kr[kv_rank + 2 * p]), x1 = bf16_bits_to_f32(kr[kv_rank + 2 * p + 1]);
+    row[kv_rank + p] = f32_to_bf16_bits(round_bf16(x0 * c) - round_bf16(x1 * s));
+    row[kv_rank + half + p] = f32_to_bf16_bits(round_bf16(x1 * c) + round_bf16(x0 * s));
+  }
+  const int qk_head = nope + rope;
+  for (int i = tid; i < heads * half; i += blockDim.x) {
+    int h = i / half, p = i - h * half;
+    const uint16_t *qr = q + ((size_t)b * heads + h) * qk_head + nope;
+    uint16_t *qo = q_full + ((size_t)b * heads + h) * lat_w + kv_rank;
+    float c = cs[p], s = cs[half + p];
+    float x0 = bf16_bits_to_f32(qr[2 * p]), x1 = bf16_bits_to_f32(qr[2 * p + 1]);
+    qo[p] = f32_to_bf16_bits(round_bf16(x0 * c) - round_bf16(x1 * s));
+    qo[half + p] = f32_to_bf16_bits(round_bf16(x1 * c) + round_bf16(x0 * s));
+  }
+}
+
+__global__ void add_one_kernel(const int *__restrict__ a, int *__restrict__ b, int n) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) b[i] = a[i] + 1;
+}
+
+// W_UK^T: out[h][j][d] = kv_b[h*(nope+v) + d][j]  (a pure re-arrangement, no arithmetic)
+__global__ void transpose_wuk_kernel(const uint16_t *__restrict__ kv_b, uint16_t *__restrict__ out, int heads, int nope,
+                                     int v_head, int kv_rank) {
+  long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  long total = (long)heads * kv_rank * nope;
+  if (i >= total) return;
+  int d = (int)(i % nope);
+  long r = i / nope;
+  int j = (int)(r % kv_rank);
+  int h = (int)(r / kv_rank);
+  out[i] = kv_b[((size_t)h * (nope + v_head) + d) * kv_rank + j];
+}
+
+// ---------------------------------------------------------------------------
+// Merge of the split-KV partial results.  grid = (heads, B), 128 threads.
+//   part_o fp32 [B, splits, heads, kv_rank] unnormalised, part_ml fp32 [B, splits, heads, 2] = (max, sum)
+// ---------------------------------------------------------------------------
+__global__ void mla_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml, int splits,
+                                 int heads, int kv_rank, uint16_t *__restrict__ o_lat) {
+  const int h = blockIdx.x, b = blockIdx.y;
+  float M = -INFINITY;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(((size_t)b * splits + s) * heads + h) * 2]);
+  float L = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float *ml = part_ml + (((size_t)b * splits + s) * heads + h) * 2;
+    if (ml[0] != -INFINITY) L += expf(ml[0] - M) * ml[1];
+  }
+  const float inv = L > 0.f ? 1.0f / L : 0.f;
+  for (int j = threadIdx.x; j < kv_rank; j += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float m = part_ml[(((size_t)b * splits + s) * heads + h) * 2];
+      if (m != -INFINITY) acc += expf(m - M) * part_o[(((size_t)b * splits + s) * heads + h) * kv_rank + j];
+    }
+    o_lat[((size_t)b * heads + h) * kv_rank + j] = f32_to_bf16_bits(acc * inv);
+  }
+}
+
+size_t mla_attend_smem_bytes();
+int launch_mla_attend(const uint16_t *q, const uint16_t *cache, long ctx_stride, const int *seq_len, int B, int splits,
+                      float scale, float *part_o, float *part_ml, cudaStream_t stream);
+
+static int launch_head_gemv(const uint16_t *w, long w_head_stride, const uint16_t *x, long x_tok_stride,
+                            long x_head_stride, uint16_t *y, long y_tok_stride, long y_head_stride, int rows, int cols,
+                            int heads, int T, cudaStream_t stream) {
+  size_t smem = bf16_x_row_bytes(cols) * T;
+  bf16_head_gemv_kernel<<<dim3(rows / 16, heads), 128, smem, stream>>>(w, w_head_stride, x, x_tok_stride, x_head_stride,
+                                                                      y, y_tok_stride, y_head_stride, cols, T);
+  return launch_status("bf16_head_gemv_kernel");
+}
+
+static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+}  // namespace blok
+
+struct blok_mla_layer {
+  blok_mla_weights w;
+  int max_batch = 0;
+  int max_splits = 0;
+  float scale = 0.f;
+  void *ws = nullptr;
+  uint16_t *wuk_t = nullptr;   // [heads, kv_rank, qk_nope]
+  float *inv_freq = nullptr;   // [qk_rope / 2]
+  uint16_t *qa = nullptr;      // [B, q_rank]
+  uint16_t *q = nullptr;       // [B, heads, nope + rope]
+  uint16_t *kva = nullptr;     // [B, kv_rank + rope]
+  uint16_t *q_full = nullptr;  // [B, heads, kv_rank + rope]
+  uint16_t *o_lat = nullptr;   // [B, heads, kv_rank]
+  uint16_t *av = nullptr;      // [B, heads * v_head]
+  int *seq = nullptr;          // [B]
+  float *part_o = nullptr;     // [max_splits * max_batch..]
+  float *part_ml = nullptr;
+};
+
+using namespace blok;
+
+// YaRN inverse frequencies, src/kimi_exec.cu:325-344 with the factor as a parameter.
+static void yarn_inv_freq_host(const blok_mla_weights &w, float *out) {
+  const float dim = (float)w.qk_rope;
+  auto corr = [&](float rotations) {
+    return dim * logf(w.yarn_original_ctx / (rotations * 2.0f * 3.141592654f)) / (2.0f * logf(w.rope_theta));
+  };
+  float low = fmaxf(floorf(corr(w.yarn_beta_fast)), 0.0f);
+  float high = fminf(ceilf(corr(w.yarn_beta_slow)), dim - 1.0f);
+  if (low == high) high += 0.001f;
+  for (int p = 0; p < w.qk_rope / 2; ++p) {
+    float extra = powf(w.rope_theta, -2.0f * (float)p / dim);
+    float inter = extra / w.yarn_factor;
+    float ramp = fminf(1.0f, fmaxf(0.0f, ((float)p - low) / (high - low)));
+    float mask = 1.0f - ramp;
+    out[p] = inter * (1.0f - mask) + extra * mask;
+  }
+}
+
+extern "C" float blok_mla_softmax_scale(const blok_mla_weights *w) {
+  if (!w) return 0.f;
+  float mscale = 0.1f * w->yarn_mscale_all_dim * logf(w->yarn_factor) + 1.0f;
+  return (1.0f / sqrtf((float)(w->qk_nope + w->qk_rope))) * mscale * mscale;
+}
+
+extern "C" int blok_mla_layer_create(const blok_mla_weights *w, int max_batch, int max_ctx, blok_mla_layer_t **out) {
+  BLOK_REQUIRE(w && out, BLOK_ERR_ARG, "blok_mla_layer_create: null pointer");
+  BLOK_REQUIRE(max_batch >= 1 && max_batch <= 8 && max_ctx >= 1, BLOK_ERR_ARG,
+               "blok_mla_layer_create: need 1 <= max_batch <= 8 and max_ctx >= 1");
+  BLOK_REQUIRE(w->heads == 64 && w->kv_rank == 512 && w->qk_rope == 64 && w->qk_nope % 32 == 0 && w->v_head % 16 == 0 &&
+                   w->hidden % 32 == 0 && w->q_rank % 32 == 0,
+               BLOK_ERR_SHAPE,
+               "blok_mla_layer_create: the attention kernel is built for 64 heads, kv_rank 512, qk_rope 64 (got %d, %d, %d)",
+               w->heads, w->kv_rank, w->qk_rope);
+  BLOK_REQUIRE(w->q_a && w->q_a_ln && w->q_b && w->kv_a && w->kv_a_ln && w->kv_b && w->o, BLOK_ERR_ARG,
+               "blok_mla_layer_create: weight pointer missing");
+  BLOK_REQUIRE(w->yarn_factor > 0.f && w->rope_theta > 1.f, BLOK_ERR_ARG, "blok_mla_layer_create: bad rope parameters");
+  blok_mla_layer *L = new (std::nothrow) blok_mla_layer();
+  BLOK_REQUIRE(L, BLOK_ERR_ARG, "blok_mla_layer_create: out of host memory");
+  L->w = *w;
+  L->max_batch = max_batch;
+  L->max_splits = sm_count();
+  L->scale = blok_mla_softmax_scale(w);
+  const int lat_w = w->kv_rank + w->qk_rope, qk_head = w->qk_nope + w->qk_rope;
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    size_t at = off;
+    off = align256(off + bytes);
+    return at;
+  };
+  size_t o_wuk = take((size_t)w->heads * w->kv_rank * w->qk_nope * 2);
+  size_t o_freq = take((size_t)(w->qk_rope / 2) * 4);
+  size_t o_qa = take((size_t)max_batch * w->q_rank * 2);
+  size_t o_q = take((size_t)max_batch * w->heads * qk_head * 2);
+  size_t o_kva = take((size_t)max_batch * lat_w * 2);
+  size_t o_qf = take((size_t)max_batch * w->heads * lat_w * 2);
+  size_t o_ol = take((size_t)max_batch * w->heads * w->kv_rank * 2);
+  size_t o_av = take((size_t)max_batch * w->heads * w->v_head * 2);
+  size_t o_seq = take((size_t)max_batch * 4);
+  size_t o_po = take((size_t)(L->max_splits + max_batch) * w->heads * w->kv_rank * 4);
+  size_t o_pml = take((size_t)(L->max_splits + max_batch) * w->heads * 2 * 4);
+  cudaError_t e = cudaMalloc(&L->ws, off);
+  if (e != cudaSuccess) {
+    delete L;
+    return cuda_fail(e, "cudaMalloc(mla layer workspace)");
+  }
+  unsigned char *b = static_cast<unsigned char *>(L->ws);
+  L->wuk_t = reinterpret_cast<uint16_t *>(b + o_wuk);
+  L->inv_freq = reinterpret_cast<float *>(b + o_freq);
+  L->qa = reinterpret_cast<uint16_t *>(b + o_qa);
+  L->q = reinterpret_cast<uint16_t *>(b + o_q);
+  L->kva = reinterpret_cast<uint16_t *>(b + o_kva);
+  L->q_full = reinterpret_cast<uint16_t *>(b + o_qf);
+  L->o_lat = reinterpret_cast<uint16_t *>(b + o_ol);
+  L->av = reinterpret_cast<uint16_t *>(b + o_av);
+  L->seq = reinterpret_cast<int *>(b + o_seq);
+  L->part_o = reinterpret_cast<float *>(b + o_po);
+  L->part_ml = reinterpret_cast<float *>(b + o_pml);
+  float freq[128];
+  yarn_inv_freq_host(*w, freq);
+  e = cudaMemcpy(L->inv_freq, freq, (size_t)(w->qk_rope / 2) * 4, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) {
+    long total = (long)w->heads * w->kv_rank * w->qk_nope;
+    transpose_wuk_kernel<<<(unsigned)((total + 255) / 256), 256>>>(w->kv_b, L->wuk_t, w->heads, w->qk_nope, w->v_head,
+                                                                   w->kv_rank);
+    count_launch();
+    e = cudaDeviceSynchronize();
+  }
+  if (e != cudaSuccess) {
+    cudaFree(L->ws);
+    delete L;
+    return cuda_fail(e, "blok_mla_layer_create: set-up");
+  }
+  (void)max_ctx;
+  *out = L;
+  return BLOK_OK;
+}
+
+extern "C" int blok_mla_layer_destroy(blok_mla_layer_t *L) {
+  if (!L) return BLOK_OK;
+  cudaError_t e = L->ws ? cudaFree(L->ws) : cudaSuccess;
+  delete L;
+  return e == cudaSuccess ? BLOK_OK : cuda_fail(e, "cudaFree(mla layer workspace)");
+}
+
+static int splits_for(const blok_mla_layer *L, int B) {
+  int s = L->max_splits / B;
+  return s < 1 ? 1 : s;
+}
+
+static int attend_and_merge(blok_mla_layer *L, const uint16_t *q, const uint16_t *cache, long ctx_stride,
+                            const int *seq_len, int B, float scale, uint16_t *o_lat, cudaStream_t stream) {
+  const int splits = splits_for(L, B);
+  int rc = launch_mla_attend(q, cache, ctx_stride, seq_len, B, splits, scale, L->part_o, L->part_ml, stream);
+  if (rc) return rc;
+  mla_merge_kernel<<<dim3(L->w.heads, B), 128, 0, stream>>>(L->part_o, L->part_ml, splits, L->w.heads, L->w.kv_rank,
+                                                           o_lat);
+  return launch_status("mla_merge_kernel");
+}
+
+extern "C" int blok_mla_attend(blok_mla_layer_t *L, const blok_bf16_t *q, const blok_bf16_t *cache, long ctx_stride,
+                               const int *seq_len, int B, float softmax_scale, blok_bf16_t *o_lat,
+                               blok_stream_t stream) {
+  BLOK_REQUIRE(L && q && cache && seq_len && o_lat, BLOK_ERR_ARG, "blok_mla_attend: null pointer");
+  BLOK_REQUIRE(B >= 1 && B <= L->max_batch && ctx_stride >= 1, BLOK_ERR_SHAPE, "blok_mla_attend: B=%d outside [1, %d]", B,
+               L->max_batch);
+  BLOK_REQUIRE((reinterpret_cast<uintptr_t>(q) & 15) == 0 && (reinterpret_cast<uintptr_t>(cache) & 15) == 0, BLOK_ERR_ARG,
+               "blok_mla_attend: q and cache must be 16-byte aligned");
+  return attend_and_merge(L, q, cache, ctx_stride, seq_len, B, softmax_scale, o_lat, (cudaStream_t)stream);
+}
+
+extern "C" int blok_mla_decode(blok_mla_layer_t *L, const blok_bf16_t *n, blok_bf16_t *cache, long ctx_stride,
+                               const int *ctx_len, int B, blok_bf16_t *out, blok_stream_t stream_) {
+  BLOK_REQUIRE(L && n && cache && ctx_len && out, BLOK_ERR_ARG, "blok_mla_decode: null pointer");
+  BLOK_REQUIRE(B >= 1 && B <= L->max_batch && ctx_stride >= 1, BLOK_ERR_SHAPE, "blok_mla_decode: B=%d outside [1, %d]", B,
+               L->max_batch);
+  BLOK_REQUIRE((reinterpret_cast<uintptr_t>(n) & 15) == 0 && (reinterpret_cast<uintptr_t>(cache) & 15) == 0, BLOK_ERR_ARG,
+               "blok_mla_decode: n and cache must be 16-byte aligned");
+  const blok_mla_weights &w = L->w;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const int lat_w = w.kv_rank + w.qk_rope, qk_head = w.qk_nope + w.qk_rope;
+  int rc;
+  // q_a -> RMSNorm -> q_b   (:813-815)
+  if ((rc = launch_bf16_gemv(w.q_a, n, L->qa, nullptr, w.q_rank, w.hidden, B, stream))) return rc;
+  if ((rc = blok_rmsnorm(L->qa, w.q_a_ln, L->qa, B, w.q_rank, w.rms_eps, stream_))) return rc;
+  if ((rc = launch_bf16_gemv(w.q_b, L->qa, L->q, nullptr, w.heads * qk_head, w.q_rank, B, stream))) return rc;
+  // kv_a; norm of c_kv, RoPE of k_pe and of q's rope part, cache append   (:816-824)
+  if ((rc = launch_bf16_gemv(w.kv_a, n, L->kva, nullptr, lat_w, w.hidden, B, stream))) return rc;
+  mla_prep_kernel<<<B, 256, 0, stream>>>(L->kva, w.kv_a_ln, L->q, L->inv_freq, ctx_len, cache, ctx_stride, L->q_full,
+                                         w.heads, w.qk_nope, w.qk_rope, w.kv_rank, w.rms_eps);
+  if ((rc = launch_status("mla_prep_kernel"))) return rc;
+  // q_abs = W_UK^T q_nope
+  if ((rc = launch_head_gemv(L->wuk_t, (long)w.kv_rank * w.qk_nope, L->q, (long)w.heads * qk_head, qk_head, L->q_full,
+                             (long)w.heads * lat_w, lat_w, w.kv_rank, w.qk_nope, w.heads, B, stream)))
+    return rc;
+  add_one_kernel<<<1, 32, 0, stream>>>(ctx_len, L->seq, B);
+  if ((rc = launch_status("add_one_kernel"))) return rc;
+  if ((rc = attend_and_merge(L, L->q_full, cache, ctx_stride, L->seq, B, L->scale, L->o_lat, stream))) return rc;
+  // out_h = W_UV o_lat_h, then o_proj   (:826)
+  if ((rc = launch_head_gemv(w.kv_b + (size_t)w.qk_nope * w.kv_rank, (long)(w.qk_nope + w.v_head) * w.kv_rank, L->o_lat,
+                             (long)w.heads * w.kv_rank, w.kv_rank, L->av, (long)w.heads * w.v_head, w.v_head, w.v_head,
+                             w.kv_rank, w.heads, B, stream)))
+    return rc;
+  return launch_bf16_gemv(w.o, L->av, out, nullptr, w.hidden, w.heads * w.v_head, B, stream);
+}

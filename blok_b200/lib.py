@@ -260,3 +260,67 @@ class MoeLayer:
             _check(load().blok_moe_decode_host(self._handle, C.c_void_p(x_host.data_ptr()), C.c_void_p(y_host.data_ptr()),
                                                _stream()))
         return y_host
+
+
+class MlaWeights(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("hidden", "heads", "qk_nope", "qk_rope", "v_head", "q_rank", "kv_rank")] + \
+               [(n, C.c_float) for n in ("rms_eps", "rope_theta", "yarn_factor", "yarn_beta_fast", "yarn_beta_slow",
+                                         "yarn_original_ctx", "yarn_mscale_all_dim")] + \
+               [(n, C.c_void_p) for n in ("q_a", "q_a_ln", "q_b", "kv_a", "kv_a_ln", "kv_b", "o")]
+
+
+class MlaLayer:
+    """Handle of one MLA attention block (src/kimi_exec.cu:813-826 + :692-716) in the absorbed form over a bf16
+    latent cache.  `weights`: dict of CUDA bf16 tensors q_a [1536,7168], q_a_ln [1536], q_b [12288,1536],
+    kv_a [576,7168], kv_a_ln [512], kv_b [16384,512], o [7168,8192].  The tensors are borrowed."""
+
+    def __init__(self, weights, yarn_factor=32.0, rope_theta=50000.0, rms_eps=1e-5, max_batch=8, max_ctx=32768,
+                 heads=64, qk_nope=128, qk_rope=64, v_head=128):
+        self.weights = dict(weights)
+        w = self.weights
+        q_rank, hidden = w["q_a"].shape
+        kv_rank = w["kv_a_ln"].shape[0]
+        self.hidden, self.heads, self.kv_rank, self.qk_rope = hidden, heads, kv_rank, qk_rope
+        self.lat_w = kv_rank + qk_rope
+        self._w = MlaWeights(hidden=hidden, heads=heads, qk_nope=qk_nope, qk_rope=qk_rope, v_head=v_head, q_rank=q_rank,
+                             kv_rank=kv_rank, rms_eps=rms_eps, rope_theta=rope_theta, yarn_factor=yarn_factor,
+                             yarn_beta_fast=32.0, yarn_beta_slow=1.0, yarn_original_ctx=4096.0, yarn_mscale_all_dim=1.0,
+                             **{k: _ptr(w[k], torch.bfloat16, k).value for k in ("q_a", "q_a_ln", "q_b", "kv_a", "kv_a_ln",
+                                                                                 "kv_b", "o")})
+        lib = load()
+        lib.blok_mla_softmax_scale.restype = C.c_float
+        self.scale = float(lib.blok_mla_softmax_scale(C.byref(self._w)))
+        self._handle = C.c_void_p()
+        self.device = w["q_a"].device
+        with torch.cuda.device(self.device):
+            _check(lib.blok_mla_layer_create(C.byref(self._w), C.c_int(max_batch), C.c_int(max_ctx), C.byref(self._handle)))
+
+    def close(self):
+        if getattr(self, "_handle", None) is not None and self._handle.value:
+            load().blok_mla_layer_destroy(self._handle)
+            self._handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def decode(self, n, cache, ctx_len, out=None):
+        """n bf16 [B, hidden]; cache bf16 [B, ctx_stride, 576] (row ctx_len[b] is written); ctx_len int32 [B] (device)."""
+        B = n.shape[0]
+        y = torch.empty((B, self.hidden), dtype=torch.bfloat16, device=n.device) if out is None else out
+        _check(load().blok_mla_decode(self._handle, _ptr(n, torch.bfloat16, "n"), _ptr(cache, torch.bfloat16, "cache"),
+                                      C.c_long(cache.shape[1]), _ptr(ctx_len, torch.int32, "ctx_len"), C.c_int(B),
+                                      _ptr(y, torch.bfloat16, "out"), _stream()))
+        return y
+
+    def attend(self, q, cache, seq_len, scale=None, out=None):
+        """The attention core: q bf16 [B, heads, 576], seq_len int32 [B] (device) -> o_lat bf16 [B, heads, 512]."""
+        B = q.shape[0]
+        o = torch.empty((B, self.heads, self.kv_rank), dtype=torch.bfloat16, device=q.device) if out is None else out
+        _check(load().blok_mla_attend(self._handle, _ptr(q, torch.bfloat16, "q"), _ptr(cache, torch.bfloat16, "cache"),
+                                      C.c_long(cache.shape[1]), _ptr(seq_len, torch.int32, "seq_len"), C.c_int(B),
+                                      C.c_float(self.scale if scale is None else scale), _ptr(o, torch.bfloat16, "o_lat"),
+                                      _stream()))
+        return o

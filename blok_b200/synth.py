@@ -71,3 +71,20 @@ def moe_layer_bytes(hidden=7168, inter=2048, experts=384, topk=8, shared_inter=2
     per_expert = 3 * (inter * hidden // 2 + inter * hidden // 32 * 2)
     k = topk if distinct_experts is None else distinct_experts
     return k * per_expert + experts * hidden * 2 + experts * 4 + 3 * shared_inter * hidden * 2
+
+
+def mla_weights(device, seed=3, hidden=7168, heads=64, qk_nope=128, qk_rope=64, v_head=128, q_rank=1536, kv_rank=512,
+                std=0.006):
+    """Config-3 attention block: every projection bf16 N(0, std), RMSNorm weights 1."""
+    g = _gen(device, seed)
+    one = lambda n: torch.ones(n, dtype=torch.bfloat16, device=device)
+    return dict(q_a=normal_bf16((q_rank, hidden), g, device, std), q_a_ln=one(q_rank),
+                q_b=normal_bf16((heads * (qk_nope + qk_rope), q_rank), g, device, std),
+                kv_a=normal_bf16((kv_rank + qk_rope, hidden), g, device, std), kv_a_ln=one(kv_rank),
+                kv_b=normal_bf16((heads * (qk_nope + v_head), kv_rank), g, device, std),
+                o=normal_bf16((hidden, heads * v_head), g, device, std))
+
+
+def latent_cache(B, ctx, device, seed=3, width=576):
+    """bf16 [B, ctx, 576] ~ N(0, 1)."""
+    return normal_bf16((B, ctx, width), _gen(device, seed + 104729), device, 1.0)

@@ -215,6 +215,66 @@ int blok_moe_layer_trace(blok_moe_layer_t *layer, long long *host_out, int max_e
 int blok_moe_decode_host(blok_moe_layer_t *layer, const blok_bf16_t *x_host, blok_bf16_t *y_host,
                          blok_stream_t stream);
 
+/* ------------------------------------------------------------------------- */
+/* A8-A10  MLA decode attention (config 3)                                    */
+/* ------------------------------------------------------------------------- */
+
+typedef struct blok_mla_weights {
+  int hidden;   /* 7168 */
+  int heads;    /* 64 */
+  int qk_nope;  /* 128 */
+  int qk_rope;  /* 64 */
+  int v_head;   /* 128 */
+  int q_rank;   /* 1536 */
+  int kv_rank;  /* 512 */
+  float rms_eps;          /* 1e-5 (src/kimi_exec.cu:183) */
+  float rope_theta;       /* 50000 */
+  float yarn_factor;      /* 64 in the reference (:184), 32 in the benchmark configuration */
+  float yarn_beta_fast;   /* 32 */
+  float yarn_beta_slow;   /* 1 */
+  float yarn_original_ctx; /* 4096 */
+  float yarn_mscale_all_dim; /* 1 */
+  const blok_bf16_t *q_a;      /* [q_rank, hidden] */
+  const blok_bf16_t *q_a_ln;   /* [q_rank] */
+  const blok_bf16_t *q_b;      /* [heads*(qk_nope+qk_rope), q_rank] */
+  const blok_bf16_t *kv_a;     /* [kv_rank+qk_rope, hidden] (kv_a_proj_with_mqa) */
+  const blok_bf16_t *kv_a_ln;  /* [kv_rank] */
+  const blok_bf16_t *kv_b;     /* [heads*(qk_nope+v_head), kv_rank] */
+  const blok_bf16_t *o;        /* [hidden, heads*v_head] */
+} blok_mla_weights;
+
+typedef struct blok_mla_layer blok_mla_layer_t;
+
+/* Allocates the layer's workspace for up to max_batch (<= 8) sequences and up to
+ * max_ctx cached tokens each, and a transposed copy of the W_UK half of kv_b. */
+int blok_mla_layer_create(const blok_mla_weights *weights, int max_batch, int max_ctx, blok_mla_layer_t **out);
+int blok_mla_layer_destroy(blok_mla_layer_t *layer);
+
+/* One decode step of the attention block for B sequences, one new token each.
+ * Replaces src/kimi_exec.cu:813-826 (q_a -> norm -> q_b, kv_a -> norm, RoPE,
+ * KV store, tiled_attention :692-716, o_proj) in the absorbed form over a bf16
+ * latent cache: row [b, t] of `cache` is (normed c_kv [kv_rank], roped k_pe
+ * [qk_rope]), the state the reference itself holds in bf16-valued form.
+ *   n        bf16 [B, hidden]  the normed hidden state (output of the input RMSNorm, :812)
+ *   cache    bf16 [B, ctx_stride, kv_rank+qk_rope]; this call WRITES row ctx_len[b]
+ *   ctx_len  int32 [B] on the device: tokens already cached; also the new token's position
+ *   out      bf16 [B, hidden]  o_proj output (the caller adds the residual, :827)
+ * Attention covers positions 0..ctx_len[b] inclusive.  ctx_len[b] < ctx_stride. */
+int blok_mla_decode(blok_mla_layer_t *layer, const blok_bf16_t *n, blok_bf16_t *cache, long ctx_stride,
+                    const int *ctx_len, int B, blok_bf16_t *out, blok_stream_t stream);
+
+/* The attention core alone, for measurement and parity: q bf16 [B, heads,
+ * kv_rank+qk_rope] (absorbed nope part, then roped part), seq_len int32 [B] on the
+ * device (tokens to attend to), o_lat bf16 [B, heads, kv_rank] =
+ * softmax(q . cache^T * scale) . cache[:, :kv_rank].  Replaces the score / max /
+ * sum / accumulate kernels at src/kimi_exec.cu:414-475. */
+int blok_mla_attend(blok_mla_layer_t *layer, const blok_bf16_t *q, const blok_bf16_t *cache, long ctx_stride,
+                    const int *seq_len, int B, float softmax_scale, blok_bf16_t *o_lat, blok_stream_t stream);
+
+/* The softmax scale the layer uses: (qk_nope+qk_rope)^-1/2 * mscale^2, mscale =
+ * 0.1 * mscale_all_dim * ln(yarn_factor) + 1 (src/kimi_exec.cu:428-429). */
+float blok_mla_softmax_scale(const blok_mla_weights *weights);
+
 #ifdef __cplusplus
 }
 #endif
