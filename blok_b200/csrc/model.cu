@@ -1,0 +1,341 @@
+// Whole-model decode step and greedy generation.  Reference: generate() and its
+// `run` lambda, src/kimi_exec.cu:780-893 (per-layer body :803-878, sampler :880-881,
+// prompt replay and decode loop :885-890).  Weights are resident in HBM; the
+// reference re-reads every tile from storage on every use (:608-649).
+#include <cstring>
+#include <map>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+namespace blok {
+
+// ---- seeded synthetic weights: a counter-based generator, one value per element --------------
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {
+  z += 0x9e3779b97f4a7c15ull;
+  z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+  z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+  return z ^ (z >> 31);
+}
+__device__ __forceinline__ float unit_normal(uint64_t key, uint64_t i) {
+  uint64_t r = mix64(key ^ mix64(i));
+  float u1 = ((uint32_t)(r >> 40) + 1.0f) * (1.0f / 16777217.0f);  // (0, 1)
+  float u2 = (uint32_t)(r & 0xffffff) * (1.0f / 16777216.0f);
+  return sqrtf(-2.0f * logf(u1)) * cosf(6.28318530718f * u2);
+}
+
+__global__ void fill_words_kernel(uint32_t *p, size_t n, uint64_t key) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) p[i] = (uint32_t)mix64(key ^ mix64(i));
+}
+// mode 0: N(0, std); mode 1: |N(0, std)|; mode 2: constant std
+__global__ void fill_bf16_kernel(uint16_t *p, size_t n, uint64_t key, float std, int mode) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float v = mode == 2 ? std : unit_normal(key, i) * std;
+  if (mode == 1) v = fabsf(v);
+  p[i] = f32_to_bf16_bits(v);
+}
+__global__ void fill_f32_kernel(float *p, size_t n, uint64_t key, float std) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) p[i] = unit_normal(key, i) * std;
+}
+__global__ void advance_kernel(int *pos, int n) {
+  int i = threadIdx.x;
+  if (i < n) pos[i] += 1;
+}
+
+struct Tensor {
+  void *ptr = nullptr;
+  size_t bytes = 0;
+};
+
+struct LayerWeights {
+  std::map<std::string, Tensor> t;
+  blok_mla_layer_t *mla = nullptr;
+  blok_moe_layer_t *moe = nullptr;
+  uint16_t *cache = nullptr;  // [max_batch, max_ctx, kv_rank + qk_rope]
+};
+
+}  // namespace blok
+
+struct blok_model {
+  blok_model_config cfg;
+  std::vector<blok::LayerWeights> layers;
+  std::map<std::string, blok::Tensor> top;
+  std::vector<void *> allocations;
+  // step buffers
+  uint16_t *x = nullptr, *n = nullptr, *tmp = nullptr;  // [max_batch, hidden]
+  int *pos = nullptr;                                   // [max_batch]
+  uint32_t *ids = nullptr, *next = nullptr;             // [max_batch]
+  void *mlp_ws = nullptr;
+  size_t mlp_ws_bytes = 0;
+  void *head_ws = nullptr;
+  size_t head_ws_bytes = 0;
+  uint64_t seed = 0, counter = 0;
+};
+
+using namespace blok;
+
+namespace {
+
+int dev_alloc(blok_model *m, size_t bytes, void **out) {
+  void *p = nullptr;
+  BLOK_CUDA(cudaMalloc(&p, bytes ? bytes : 16));
+  m->allocations.push_back(p);
+  *out = p;
+  return BLOK_OK;
+}
+
+enum Fill { F_NORMAL, F_ABS, F_ONE, F_WORDS, F_F32 };
+
+int make_tensor(blok_model *m, std::map<std::string, Tensor> &into, const char *name, size_t elems, Fill fill, float std) {
+  size_t esz = (fill == F_WORDS || fill == F_F32) ? 4 : 2;
+  Tensor t;
+  t.bytes = elems * esz;
+  int rc = dev_alloc(m, t.bytes, &t.ptr);
+  if (rc) return rc;
+  const uint64_t key = m->seed * 0x100000001b3ull + (++m->counter) * 0x9e3779b97f4a7c15ull;
+  const unsigned blocks = (unsigned)((elems + 255) / 256);
+  if (elems) {
+    if (fill == F_WORDS) fill_words_kernel<<<blocks, 256>>>(static_cast<uint32_t *>(t.ptr), elems, key);
+    else if (fill == F_F32) fill_f32_kernel<<<blocks, 256>>>(static_cast<float *>(t.ptr), elems, key, std);
+    else fill_bf16_kernel<<<blocks, 256>>>(static_cast<uint16_t *>(t.ptr), elems, key, fill == F_ONE ? 1.0f : std,
+                                           fill == F_ONE ? 2 : (fill == F_ABS ? 1 : 0));
+    rc = launch_status("synthetic fill");
+    if (rc) return rc;
+  }
+  into[name] = t;
+  return BLOK_OK;
+}
+
+template <typename T>
+T *tp(const std::map<std::string, Tensor> &m, const char *name) {
+  auto it = m.find(name);
+  return it == m.end() ? nullptr : static_cast<T *>(it->second.ptr);
+}
+
+int build(blok_model *m) {
+  const blok_model_config &c = m->cfg;
+  const size_t H = c.hidden;
+  const float wstd = 0.006f;
+  int rc;
+#define MK(map, name, elems, fill, std) \
+  if ((rc = make_tensor(m, map, name, (size_t)(elems), fill, std))) return rc;
+  MK(m->top, "embed_tokens", (size_t)c.vocab * H, F_NORMAL, wstd);
+  MK(m->top, "norm", H, F_ONE, 1.f);
+  MK(m->top, "lm_head", (size_t)c.vocab * H, F_NORMAL, wstd);
+  m->layers.resize(c.layers);
+  const int qk_head = c.qk_nope + c.qk_rope, lat_w = c.kv_rank + c.qk_rope;
+  for (int l = 0; l < c.layers; ++l) {
+    auto &t = m->layers[l].t;
+    MK(t, "input_layernorm", H, F_ONE, 1.f);
+    MK(t, "post_attention_layernorm", H, F_ONE, 1.f);
+    MK(t, "q_a_proj", (size_t)c.q_rank * H, F_NORMAL, wstd);
+    MK(t, "q_a_layernorm", c.q_rank, F_ONE, 1.f);
+    MK(t, "q_b_proj", (size_t)c.heads * qk_head * c.q_rank, F_NORMAL, wstd);
+    MK(t, "kv_a_proj_with_mqa", (size_t)lat_w * H, F_NORMAL, wstd);
+    MK(t, "kv_a_layernorm", c.kv_rank, F_ONE, 1.f);
+    MK(t, "kv_b_proj", (size_t)c.heads * (c.qk_nope + c.v_head) * c.kv_rank, F_NORMAL, wstd);
+    MK(t, "o_proj", H * (size_t)c.heads * c.v_head, F_NORMAL, wstd);
+    if (l < c.first_dense) {
+      MK(t, "gate_proj", (size_t)c.dense_inter * H, F_NORMAL, wstd);
+      MK(t, "up_proj", (size_t)c.dense_inter * H, F_NORMAL, wstd);
+      MK(t, "down_proj", H * (size_t)c.dense_inter, F_NORMAL, wstd);
+    } else {
+      const size_t E = c.experts, I = c.inter;
+      MK(t, "router", E * H, F_NORMAL, wstd);
+      MK(t, "router_bias", E, F_F32, 0.01f);
+      MK(t, "gate_w", E * I * (H / 8), F_WORDS, 0.f);
+      MK(t, "gate_s", E * I * (H / 32), F_ABS, 0.003f);
+      MK(t, "up_w", E * I * (H / 8), F_WORDS, 0.f);
+      MK(t, "up_s", E * I * (H / 32), F_ABS, 0.003f);
+      MK(t, "down_w", E * H * (I / 8), F_WORDS, 0.f);
+      MK(t, "down_s", E * H * (I / 32), F_ABS, 0.003f);
+      if (c.shared_inter) {
+        MK(t, "shared_gate", (size_t)c.shared_inter * H, F_NORMAL, wstd);
+        MK(t, "shared_up", (size_t)c.shared_inter * H, F_NORMAL, wstd);
+        MK(t, "shared_down", H * (size_t)c.shared_inter, F_NORMAL, wstd);
+      }
+    }
+    void *cache = nullptr;
+    if ((rc = dev_alloc(m, (size_t)c.max_batch * c.max_ctx * lat_w * 2, &cache))) return rc;
+    m->layers[l].cache = static_cast<uint16_t *>(cache);
+  }
+#undef MK
+  BLOK_CUDA(cudaDeviceSynchronize());
+  for (int l = 0; l < c.layers; ++l) {
+    auto &L = m->layers[l];
+    blok_mla_weights mw;
+    memset(&mw, 0, sizeof(mw));
+    mw.hidden = c.hidden; mw.heads = c.heads; mw.qk_nope = c.qk_nope; mw.qk_rope = c.qk_rope; mw.v_head = c.v_head;
+    mw.q_rank = c.q_rank; mw.kv_rank = c.kv_rank; mw.rms_eps = c.rms_eps; mw.rope_theta = c.rope_theta;
+    mw.yarn_factor = c.yarn_factor; mw.yarn_beta_fast = c.yarn_beta_fast; mw.yarn_beta_slow = c.yarn_beta_slow;
+    mw.yarn_original_ctx = c.yarn_original_ctx; mw.yarn_mscale_all_dim = c.yarn_mscale_all_dim;
+    mw.q_a = tp<uint16_t>(L.t, "q_a_proj"); mw.q_a_ln = tp<uint16_t>(L.t, "q_a_layernorm");
+    mw.q_b = tp<uint16_t>(L.t, "q_b_proj"); mw.kv_a = tp<uint16_t>(L.t, "kv_a_proj_with_mqa");
+    mw.kv_a_ln = tp<uint16_t>(L.t, "kv_a_layernorm"); mw.kv_b = tp<uint16_t>(L.t, "kv_b_proj");
+    mw.o = tp<uint16_t>(L.t, "o_proj");
+    if ((rc = blok_mla_layer_create(&mw, c.max_batch, c.max_ctx, &L.mla))) return rc;
+    if (l >= c.first_dense) {
+      blok_moe_weights ew;
+      memset(&ew, 0, sizeof(ew));
+      ew.hidden = c.hidden; ew.inter = c.inter; ew.experts = c.experts; ew.topk = c.topk; ew.shared_inter = c.shared_inter;
+      ew.routed_scale = c.routed_scale; ew.router_w = tp<uint16_t>(L.t, "router");
+      ew.router_bias = tp<float>(L.t, "router_bias"); ew.expert_base = 0; ew.experts_local = c.experts;
+      ew.gate_w = tp<uint32_t>(L.t, "gate_w"); ew.gate_s = tp<uint16_t>(L.t, "gate_s");
+      ew.up_w = tp<uint32_t>(L.t, "up_w"); ew.up_s = tp<uint16_t>(L.t, "up_s");
+      ew.down_w = tp<uint32_t>(L.t, "down_w"); ew.down_s = tp<uint16_t>(L.t, "down_s");
+      ew.shared_gate = tp<uint16_t>(L.t, "shared_gate"); ew.shared_up = tp<uint16_t>(L.t, "shared_up");
+      ew.shared_down = tp<uint16_t>(L.t, "shared_down");
+      if ((rc = blok_moe_layer_create(&ew, 1, &L.moe))) return rc;
+    }
+  }
+  void *p;
+  const size_t act = (size_t)c.max_batch * c.hidden * 2;
+  if ((rc = dev_alloc(m, act, &p))) return rc; m->x = static_cast<uint16_t *>(p);
+  if ((rc = dev_alloc(m, act, &p))) return rc; m->n = static_cast<uint16_t *>(p);
+  if ((rc = dev_alloc(m, act, &p))) return rc; m->tmp = static_cast<uint16_t *>(p);
+  if ((rc = dev_alloc(m, c.max_batch * 4, &p))) return rc; m->pos = static_cast<int *>(p);
+  if ((rc = dev_alloc(m, c.max_batch * 4, &p))) return rc; m->ids = static_cast<uint32_t *>(p);
+  if ((rc = dev_alloc(m, c.max_batch * 4, &p))) return rc; m->next = static_cast<uint32_t *>(p);
+  m->mlp_ws_bytes = blok_bf16_mlp_workspace_bytes(c.hidden, c.dense_inter > 0 ? c.dense_inter : 32, 1);
+  if ((rc = dev_alloc(m, m->mlp_ws_bytes, &m->mlp_ws))) return rc;
+  m->head_ws_bytes = blok_lm_head_workspace_bytes(c.vocab, c.max_batch);
+  if ((rc = dev_alloc(m, m->head_ws_bytes, &m->head_ws))) return rc;
+  BLOK_CUDA(cudaMemset(m->pos, 0, c.max_batch * 4));
+  return BLOK_OK;
+}
+
+}  // namespace
+
+extern "C" void blok_model_default_config(blok_model_config *c) {
+  if (!c) return;
+  memset(c, 0, sizeof(*c));
+  c->layers = 61; c->first_dense = 1; c->hidden = 7168; c->vocab = 163840; c->dense_inter = 18432;
+  c->inter = 2048; c->experts = 384; c->topk = 8; c->shared_inter = 2048; c->routed_scale = 2.827f;
+  c->heads = 64; c->qk_nope = 128; c->qk_rope = 64; c->v_head = 128; c->q_rank = 1536; c->kv_rank = 512;
+  c->rms_eps = 1.0e-5f; c->final_rms_eps = 1.0e-5f;
+  c->rope_theta = 50000.0f; c->yarn_factor = 64.0f; c->yarn_beta_fast = 32.0f; c->yarn_beta_slow = 1.0f;
+  c->yarn_original_ctx = 4096.0f; c->yarn_mscale_all_dim = 1.0f;
+  c->max_batch = 1; c->max_ctx = 1024; c->eos_id = 163586u;
+}
+
+extern "C" int blok_model_destroy(blok_model_t *m) {
+  if (!m) return BLOK_OK;
+  for (auto &L : m->layers) {
+    if (L.mla) blok_mla_layer_destroy(L.mla);
+    if (L.moe) blok_moe_layer_destroy(L.moe);
+  }
+  cudaError_t first = cudaSuccess;
+  for (void *p : m->allocations) {
+    cudaError_t e = cudaFree(p);
+    if (first == cudaSuccess) first = e;
+  }
+  delete m;
+  return first == cudaSuccess ? BLOK_OK : cuda_fail(first, "cudaFree(model)");
+}
+
+extern "C" int blok_model_create_synthetic(const blok_model_config *cfg, uint64_t seed, blok_model_t **out) {
+  BLOK_REQUIRE(cfg && out, BLOK_ERR_ARG, "blok_model_create_synthetic: null pointer");
+  BLOK_REQUIRE(cfg->layers >= 1 && cfg->first_dense >= 0 && cfg->first_dense <= cfg->layers && cfg->vocab > 0 &&
+                   cfg->hidden % 256 == 0 && cfg->max_batch >= 1 && cfg->max_batch <= 8 && cfg->max_ctx >= 1,
+               BLOK_ERR_SHAPE, "blok_model_create_synthetic: unsupported configuration");
+  BLOK_REQUIRE(cfg->first_dense == 0 || (cfg->dense_inter > 0 && cfg->dense_inter % 32 == 0), BLOK_ERR_SHAPE,
+               "blok_model_create_synthetic: dense_inter %d must be a positive multiple of 32", cfg->dense_inter);
+  blok_model *m = new (std::nothrow) blok_model();
+  BLOK_REQUIRE(m, BLOK_ERR_ARG, "blok_model_create_synthetic: out of host memory");
+  m->cfg = *cfg;
+  m->seed = seed;
+  int rc = build(m);
+  if (rc) {
+    blok_model_destroy(m);
+    return rc;
+  }
+  *out = m;
+  return BLOK_OK;
+}
+
+extern "C" int blok_model_tensor(blok_model_t *m, int layer, const char *name, void **ptr, size_t *bytes) {
+  BLOK_REQUIRE(m && name && ptr && bytes, BLOK_ERR_ARG, "blok_model_tensor: null pointer");
+  const std::map<std::string, Tensor> *map = nullptr;
+  if (layer == -1) map = &m->top;
+  else if (layer >= 0 && layer < (int)m->layers.size()) map = &m->layers[layer].t;
+  BLOK_REQUIRE(map, BLOK_ERR_ARG, "blok_model_tensor: layer %d out of range", layer);
+  auto it = map->find(name);
+  BLOK_REQUIRE(it != map->end(), BLOK_ERR_ARG, "blok_model_tensor: layer %d has no tensor '%s'", layer, name);
+  *ptr = it->second.ptr;
+  *bytes = it->second.bytes;
+  return BLOK_OK;
+}
+
+extern "C" int blok_model_reset(blok_model_t *m) {
+  BLOK_REQUIRE(m, BLOK_ERR_ARG, "blok_model_reset: null pointer");
+  BLOK_CUDA(cudaMemset(m->pos, 0, m->cfg.max_batch * 4));
+  return BLOK_OK;
+}
+
+extern "C" int blok_model_step(blok_model_t *m, const uint32_t *ids, int B, uint32_t *next_ids, blok_stream_t stream_) {
+  BLOK_REQUIRE(m && ids && next_ids, BLOK_ERR_ARG, "blok_model_step: null pointer");
+  BLOK_REQUIRE(B >= 1 && B <= m->cfg.max_batch, BLOK_ERR_SHAPE, "blok_model_step: B=%d outside [1, %d]", B, m->cfg.max_batch);
+  const blok_model_config &c = m->cfg;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const size_t H = c.hidden;
+  int rc;
+  if ((rc = blok_embed(tp<uint16_t>(m->top, "embed_tokens"), ids, c.vocab, c.hidden, B, m->x, stream_))) return rc;  // :802
+  for (int l = 0; l < c.layers; ++l) {
+    auto &L = m->layers[l];
+    // attention block, :812-827
+    if ((rc = blok_rmsnorm(m->x, tp<uint16_t>(L.t, "input_layernorm"), m->n, B, c.hidden, c.rms_eps, stream_))) return rc;
+    if ((rc = blok_mla_decode(L.mla, m->n, L.cache, c.max_ctx, m->pos, B, m->tmp, stream_))) return rc;
+    if ((rc = blok_add_bf16(m->x, m->tmp, (long)B * H, stream_))) return rc;
+    // feed-forward block, :829-877
+    if ((rc = blok_rmsnorm(m->x, tp<uint16_t>(L.t, "post_attention_layernorm"), m->n, B, c.hidden, c.rms_eps, stream_)))
+      return rc;
+    for (int b = 0; b < B; ++b) {
+      if (l < c.first_dense)
+        rc = blok_bf16_mlp(tp<uint16_t>(L.t, "gate_proj"), tp<uint16_t>(L.t, "up_proj"), tp<uint16_t>(L.t, "down_proj"),
+                           m->n + b * H, m->tmp + b * H, c.hidden, c.dense_inter, 1, m->mlp_ws, m->mlp_ws_bytes, stream_);
+      else
+        rc = blok_moe_decode(L.moe, m->n + b * H, m->tmp + b * H, nullptr, nullptr, stream_);
+      if (rc) return rc;
+    }
+    if ((rc = blok_add_bf16(m->x, m->tmp, (long)B * H, stream_))) return rc;
+  }
+  if ((rc = blok_rmsnorm(m->x, tp<uint16_t>(m->top, "norm"), m->n, B, c.hidden, c.final_rms_eps, stream_))) return rc;  // :880
+  if ((rc = blok_lm_head_argmax(tp<uint16_t>(m->top, "lm_head"), m->n, c.vocab, c.hidden, B, next_ids, m->head_ws,
+                                m->head_ws_bytes, stream_)))
+    return rc;
+  advance_kernel<<<1, 32, 0, stream>>>(m->pos, B);
+  return launch_status("advance_kernel");
+}
+
+extern "C" int blok_model_generate(blok_model_t *m, const uint32_t *prompt, int n_prompt, int max_new, uint32_t *out,
+                                   int *n_out) {
+  BLOK_REQUIRE(m && prompt && out && n_out, BLOK_ERR_ARG, "blok_model_generate: null pointer");
+  BLOK_REQUIRE(n_prompt >= 1 && max_new >= 1, BLOK_ERR_ARG, "blok_model_generate: empty prompt or max_new < 1");
+  BLOK_REQUIRE((long)n_prompt + max_new <= m->cfg.max_ctx, BLOK_ERR_SHAPE,
+               "blok_model_generate: requested sequence exceeds the model's context (%d)", m->cfg.max_ctx);  // :784
+  for (int i = 0; i < n_prompt; ++i)
+    BLOK_REQUIRE(prompt[i] < (uint32_t)m->cfg.vocab, BLOK_ERR_ARG, "blok_model_generate: prompt token outside vocabulary");
+  int rc = blok_model_reset(m);
+  if (rc) return rc;
+  *n_out = 0;
+  uint32_t next = prompt[0];
+  // prompt replay, token by token; only the last step's sample is used (:886)
+  for (int i = 0; i < n_prompt; ++i) {
+    BLOK_CUDA(cudaMemcpyAsync(m->ids, prompt + i, 4, cudaMemcpyHostToDevice, nullptr));
+    if ((rc = blok_model_step(m, m->ids, 1, m->next, nullptr))) return rc;
+  }
+  BLOK_CUDA(cudaMemcpy(&next, m->next, 4, cudaMemcpyDeviceToHost));
+  for (int i = 0; i < max_new && next != m->cfg.eos_id; ++i) {  // :887-890
+    out[(*n_out)++] = next;
+    if (i + 1 < max_new) {
+      if ((rc = blok_model_step(m, m->next, 1, m->next, nullptr))) return rc;
+      BLOK_CUDA(cudaMemcpy(&next, m->next, 4, cudaMemcpyDeviceToHost));
+    }
+  }
+  return BLOK_OK;
+}

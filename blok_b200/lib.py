@@ -262,6 +262,30 @@ class MoeLayer:
         return y_host
 
 
+def lm_head_argmax(w, n):
+    """Greedy sampler (src/kimi_exec.cu:718-734): n bf16 [T<=8, hidden] -> token ids int32 [T] on the device."""
+    vocab, hidden = w.shape
+    n2 = n.reshape(-1, hidden)
+    T = n2.shape[0]
+    lib = load()
+    lib.blok_lm_head_workspace_bytes.restype = C.c_size_t
+    need = lib.blok_lm_head_workspace_bytes(C.c_int(vocab), C.c_int(T))
+    ws = torch.empty(need, dtype=torch.uint8, device=n.device)
+    ids = torch.empty(T, dtype=torch.int32, device=n.device)
+    _check(lib.blok_lm_head_argmax(_ptr(w, torch.bfloat16), _ptr(n2, torch.bfloat16), C.c_int(vocab), C.c_int(hidden),
+                                   C.c_int(T), _ptr(ids), _ptr(ws), C.c_size_t(need), _stream()))
+    return ids
+
+
+def embed(table, ids):
+    """embed_token (src/kimi_exec.cu:651-655): ids int32 [T] on the device -> bf16 [T, hidden]."""
+    vocab, hidden = table.shape
+    x = torch.zeros((ids.numel(), hidden), dtype=torch.bfloat16, device=table.device)
+    _check(load().blok_embed(_ptr(table, torch.bfloat16), _ptr(ids, torch.int32), C.c_int(vocab), C.c_int(hidden),
+                             C.c_int(ids.numel()), _ptr(x), _stream()))
+    return x
+
+
 class MlaWeights(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("hidden", "heads", "qk_nope", "qk_rope", "v_head", "q_rank", "kv_rank")] + \
                [(n, C.c_float) for n in ("rms_eps", "rope_theta", "yarn_factor", "yarn_beta_fast", "yarn_beta_slow",
@@ -324,3 +348,97 @@ class MlaLayer:
                                       C.c_float(self.scale if scale is None else scale), _ptr(o, torch.bfloat16, "o_lat"),
                                       _stream()))
         return o
+
+
+class ModelConfig(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("layers", "first_dense", "hidden", "vocab", "dense_inter", "inter", "experts", "topk",
+                                       "shared_inter")] + [("routed_scale", C.c_float)] + \
+               [(n, C.c_int) for n in ("heads", "qk_nope", "qk_rope", "v_head", "q_rank", "kv_rank")] + \
+               [(n, C.c_float) for n in ("rms_eps", "final_rms_eps", "rope_theta", "yarn_factor", "yarn_beta_fast",
+                                         "yarn_beta_slow", "yarn_original_ctx", "yarn_mscale_all_dim")] + \
+               [("max_batch", C.c_int), ("max_ctx", C.c_int), ("eos_id", C.c_uint32)]
+
+
+_cudart = None
+
+
+def _rt():
+    global _cudart
+    if _cudart is None:
+        for name in ("libcudart.so.12", "libcudart.so"):
+            try:
+                _cudart = C.CDLL(name)
+                break
+            except OSError:
+                continue
+        if _cudart is None:
+            raise BlokError(-100, "libcudart not found")
+    return _cudart
+
+
+class Model:
+    """The whole decode model with seeded synthetic weights (generate(), src/kimi_exec.cu:780-893)."""
+
+    def __init__(self, seed=4, **overrides):
+        lib = load()
+        self.cfg = ModelConfig()
+        lib.blok_model_default_config(C.byref(self.cfg))
+        for k, v in overrides.items():
+            if not hasattr(self.cfg, k):
+                raise BlokError(-1, "unknown model config field %r" % k)
+            setattr(self.cfg, k, v)
+        self._handle = C.c_void_p()
+        _check(lib.blok_model_create_synthetic(C.byref(self.cfg), C.c_uint64(seed), C.byref(self._handle)))
+
+    def close(self):
+        if getattr(self, "_handle", None) is not None and self._handle.value:
+            load().blok_model_destroy(self._handle)
+            self._handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def tensor(self, layer, name, dtype, shape=None):
+        """Host copy (numpy) of a weight tensor."""
+        import numpy as np
+        ptr, nbytes = C.c_void_p(), C.c_size_t()
+        _check(load().blok_model_tensor(self._handle, C.c_int(layer), name.encode(), C.byref(ptr), C.byref(nbytes)))
+        torch.cuda.synchronize()
+        out = np.empty(nbytes.value // np.dtype(dtype).itemsize, dtype)
+        rc = _rt().cudaMemcpy(out.ctypes.data_as(C.c_void_p), ptr, C.c_size_t(nbytes.value), C.c_int(2))
+        if rc != 0:
+            raise BlokError(-3, "cudaMemcpy D2H failed: %d" % rc)
+        return out.reshape(shape) if shape is not None else out
+
+    def write_tensor(self, layer, name, array):
+        """Overwrite a weight tensor from a numpy array of the same byte size."""
+        ptr, nbytes = C.c_void_p(), C.c_size_t()
+        _check(load().blok_model_tensor(self._handle, C.c_int(layer), name.encode(), C.byref(ptr), C.byref(nbytes)))
+        if array.nbytes != nbytes.value:
+            raise BlokError(-2, "size mismatch for %s" % name)
+        torch.cuda.synchronize()
+        rc = _rt().cudaMemcpy(ptr, array.ctypes.data_as(C.c_void_p), C.c_size_t(nbytes.value), C.c_int(1))
+        if rc != 0:
+            raise BlokError(-3, "cudaMemcpy H2D failed: %d" % rc)
+
+    def reset(self):
+        _check(load().blok_model_reset(self._handle))
+
+    def step(self, ids):
+        """ids int32 [B] on the device -> next ids int32 [B] on the device."""
+        nxt = torch.empty_like(ids)
+        _check(load().blok_model_step(self._handle, _ptr(ids, torch.int32, "ids"), C.c_int(ids.numel()), _ptr(nxt), _stream()))
+        return nxt
+
+    def generate(self, prompt, max_new):
+        """Greedy generation with host token lists, like the reference executor's command line."""
+        import numpy as np
+        p = np.ascontiguousarray(prompt, np.uint32)
+        out = np.zeros(max_new, np.uint32)
+        n = C.c_int(0)
+        _check(load().blok_model_generate(self._handle, p.ctypes.data_as(C.c_void_p), C.c_int(p.size), C.c_int(max_new),
+                                          out.ctypes.data_as(C.c_void_p), C.byref(n)))
+        return out[:n.value].tolist()

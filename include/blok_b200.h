@@ -275,6 +275,82 @@ int blok_mla_attend(blok_mla_layer_t *layer, const blok_bf16_t *q, const blok_bf
  * 0.1 * mscale_all_dim * ln(yarn_factor) + 1 (src/kimi_exec.cu:428-429). */
 float blok_mla_softmax_scale(const blok_mla_weights *weights);
 
+/* ------------------------------------------------------------------------- */
+/* A11  embedding fetch and greedy sampler                                    */
+/* ------------------------------------------------------------------------- */
+
+/* x[t, :] = table[ids[t], :].  Replaces embed_token (src/kimi_exec.cu:651-655); ids
+ * are uint32 on the device and must be < vocab (rows of out-of-range ids are left
+ * untouched; the host checks prompt ids as the reference does at :552). */
+int blok_embed(const blok_bf16_t *table, const uint32_t *ids, int vocab, int hidden, int T, blok_bf16_t *x,
+               blok_stream_t stream);
+
+size_t blok_lm_head_workspace_bytes(int vocab, int T);
+
+/* ids[t] = argmax_v bf16(sum_c W[v,c] n[t,c]), the lowest id winning ties.  Replaces
+ * sample_lm_head / argmax_k (src/kimi_exec.cu:718-734, :477-493).  ids stay on the
+ * device.  T <= 8. */
+int blok_lm_head_argmax(const blok_bf16_t *w, const blok_bf16_t *n, int vocab, int hidden, int T, uint32_t *ids,
+                        void *workspace, size_t workspace_bytes, blok_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* A11/A12  whole model: decode step and greedy generation (config 4)          */
+/* ------------------------------------------------------------------------- */
+
+typedef struct blok_model_config {
+  int layers;        /* 61 */
+  int first_dense;   /* 1: layers [0, first_dense) use the dense FFN (src/kimi_exec.cu:176, :831) */
+  int hidden;        /* 7168 */
+  int vocab;         /* 163840 */
+  int dense_inter;   /* 18432 */
+  int inter;         /* 2048 */
+  int experts;       /* 384 */
+  int topk;          /* 8 */
+  int shared_inter;  /* 2048 */
+  float routed_scale; /* 2.827 */
+  int heads, qk_nope, qk_rope, v_head, q_rank, kv_rank; /* 64, 128, 64, 128, 1536, 512 */
+  float rms_eps;       /* 1e-5, every per-layer norm */
+  float final_rms_eps; /* 1e-5 in the reference (:880 uses RMS_EPS); 1e-6 in the benchmark configuration */
+  float rope_theta, yarn_factor, yarn_beta_fast, yarn_beta_slow, yarn_original_ctx, yarn_mscale_all_dim;
+  int max_batch;     /* <= 8 */
+  int max_ctx;       /* tokens of latent cache per sequence and layer */
+  uint32_t eos_id;   /* 163586 (:186) */
+} blok_model_config;
+
+typedef struct blok_model blok_model_t;
+
+/* Fills cfg with the reference's constants (src/kimi_exec.cu:176-186). */
+void blok_model_default_config(blok_model_config *cfg);
+
+/* Builds a model with seeded synthetic weights on the current device (INT4 words
+ * uniform, scales |N(0,0.003)|, bf16 weights N(0,0.006), router bias N(0,0.01), norm
+ * weights 1).  Stands in for the checkpoint loader of the reference (:736-778). */
+int blok_model_create_synthetic(const blok_model_config *cfg, uint64_t seed, blok_model_t **out);
+int blok_model_destroy(blok_model_t *model);
+
+/* Device pointer and byte size of a weight tensor, for tests and loaders.  layer = -1
+ * for "embed_tokens", "norm", "lm_head"; per layer: "input_layernorm",
+ * "post_attention_layernorm", "q_a_proj", "q_a_layernorm", "q_b_proj", "kv_a_proj_with_mqa",
+ * "kv_a_layernorm", "kv_b_proj", "o_proj", dense "gate_proj"/"up_proj"/"down_proj", MoE
+ * "router", "router_bias", "gate_w", "gate_s", "up_w", "up_s", "down_w", "down_s",
+ * "shared_gate", "shared_up", "shared_down" (the slot names of the reference's index). */
+int blok_model_tensor(blok_model_t *model, int layer, const char *name, void **ptr, size_t *bytes);
+
+/* Forgets all cached tokens (positions restart at 0). */
+int blok_model_reset(blok_model_t *model);
+
+/* One decode step for B sequences: ids uint32 [B] on the device are embedded, run
+ * through every layer at each sequence's current position (appending to the latent
+ * caches), and next_ids [B] receives the greedy choice.  Replaces the `run` lambda,
+ * src/kimi_exec.cu:801-884.  Positions advance by one. */
+int blok_model_step(blok_model_t *model, const uint32_t *ids, int B, uint32_t *next_ids, blok_stream_t stream);
+
+/* Greedy generation for one sequence with HOST token arrays, as generate()
+ * (src/kimi_exec.cu:885-890): the prompt is replayed token by token, then up to
+ * max_new tokens are produced, stopping before eos_id.  Returns the count in *n_out. */
+int blok_model_generate(blok_model_t *model, const uint32_t *prompt, int n_prompt, int max_new, uint32_t *out,
+                        int *n_out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -105,3 +105,23 @@ def test_router_tie_rule_on_device(cuda):
     for t in range(2):
         assert util.ids_np(ids)[t].tolist() == [5, 17, 200, 300, 0, 1, 2, 3]
     np.testing.assert_allclose(util.t2np_f32(wts), 2.827 / 8, rtol=1e-6)
+
+
+@pytest.mark.parametrize("vocab,hidden,T", [(163840, 7168, 1), (4096, 512, 3)])
+def test_lm_head_argmax_and_embed(cuda, oracle, vocab, hidden, T):
+    from blok_b200 import lib
+    g = torch.Generator(device=cuda).manual_seed(vocab)
+    w = (torch.randn((vocab, hidden), generator=g, device=cuda) * 0.006).bfloat16()
+    ids_in = torch.randint(0, vocab, (T,), generator=g, device=cuda, dtype=torch.int32)
+    x = lib.embed(w, ids_in)
+    assert torch.equal(x, w[ids_in.long()])
+    # a query aligned with its own row must select that row; identical rows resolve to the lowest id
+    w[vocab - 5] = w[17]
+    n = (w[torch.tensor([17] + [int(i) for i in ids_in[1:]], device=cuda)].float() * 50).bfloat16()
+    got = lib.lm_head_argmax(w, n).cpu().numpy()
+    assert got[0] == 17
+    if vocab <= 4096:
+        wh, nh = util.t2np_bf16(w), util.t2np_f32(n)
+        for t in range(T):
+            tok, _ = oracle.lm_head_argmax(wh, nh[t], mode=0)
+            assert got[t] == tok
