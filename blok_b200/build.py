@@ -17,6 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libblok_b200.so")
 OBJ = os.path.join(HERE, "build")
+CLI = os.path.join(HERE, "blok-kimi-exec")
 
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
@@ -55,6 +56,11 @@ def build(force=False, verbose_ptxas=False):
     if force or not os.path.exists(OUT) or any(os.path.getmtime(o) > os.path.getmtime(OUT) for o in objs):
         cmd = ["nvcc", "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", OUT] + objs + ["-lcudart"]
         subprocess.check_call(cmd)
+    cli_src = os.path.join(HERE, "cli", "blok_kimi_exec.cpp")
+    if os.path.exists(cli_src) and (force or not os.path.exists(CLI) or os.path.getmtime(cli_src) > os.path.getmtime(CLI)
+                                    or os.path.getmtime(OUT) > os.path.getmtime(CLI)):
+        subprocess.check_call(["g++", "-std=c++17", "-O2", "-I", os.path.join(HERE, "..", "include"), cli_src, "-o", CLI,
+                               "-L", HERE, "-lblok_b200", "-Wl,-rpath,$ORIGIN"])
     return OUT, log
 
 
