@@ -24,6 +24,7 @@ int launch_i4_down(const uint32_t *down_w, const uint16_t *down_s, const uint16_
                    cudaStream_t stream);
 
 int fused_plan(const blok_moe_weights &w, FusedPlan *plan);
+int batched_alloc(blok_moe_layer *L);
 int launch_moe_decode_fused(blok_moe_layer *L, const uint16_t *x, uint16_t *y, uint16_t *ids_out, float *wts_out,
                             cudaStream_t stream);
 
@@ -143,6 +144,14 @@ extern "C" int blok_moe_layer_create(const blok_moe_weights *w, int max_tokens, 
     L->f_cntOut = c;
     if (want_trace) L->f_trace = reinterpret_cast<long long *>(b + o_trace);
   }
+  if (max_tokens > 1) {
+    int rc = batched_alloc(L);
+    if (rc) {
+      cudaFree(L->ws);
+      delete L;
+      return rc;
+    }
+  }
   *out = L;
   return BLOK_OK;
 }
@@ -150,6 +159,10 @@ extern "C" int blok_moe_layer_create(const blok_moe_weights *w, int max_tokens, 
 extern "C" int blok_moe_layer_destroy(blok_moe_layer_t *L) {
   if (!L) return BLOK_OK;
   cudaError_t e = L->ws ? cudaFree(L->ws) : cudaSuccess;
+  if (L->bws) {
+    cudaError_t e2 = cudaFree(L->bws);
+    if (e == cudaSuccess) e = e2;
+  }
   delete L;
   return e == cudaSuccess ? BLOK_OK : cuda_fail(e, "cudaFree(moe layer workspace)");
 }

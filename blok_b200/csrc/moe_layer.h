@@ -37,6 +37,21 @@ struct blok_moe_layer {
   uint16_t *shared_out = nullptr;  // [8, hidden]
   uint16_t *io_x = nullptr;        // [hidden] staging for the host-buffer entry point
   uint16_t *io_y = nullptr;        // [hidden]
+  // batched path (moe_batched.cu); allocated when max_tokens > 1
+  void *bws = nullptr;
+  int b_max_assign = 0;          // max_tokens * topk
+  int b_max_tiles = 0, b_max_ttiles = 0;
+  int *b_counts = nullptr;       // [experts_local + 1]
+  int *b_offsets = nullptr;      // [experts_local + 1]
+  int *b_sorted_assign = nullptr;  // [N] assignment id at sorted position p
+  int *b_sorted_row = nullptr;     // [N] x row at sorted position p
+  int *b_tile_expert = nullptr, *b_tile_start = nullptr, *b_tile_count = nullptr, *b_num_tiles = nullptr;
+  int *b_ttile_expert = nullptr, *b_ttile_start = nullptr, *b_ttile_count = nullptr, *b_num_ttiles = nullptr;
+  int *b_assign_row = nullptr;   // [N] token row of assignment a (a / topk)
+  uint16_t *b_mid = nullptr;     // [N, inter] sorted order
+  uint16_t *b_y = nullptr;       // [N, hidden] assignment order
+  uint16_t *b_smid = nullptr;    // [T, shared_inter]
+  uint16_t *b_sout = nullptr;    // [T, hidden]
   // fused decode kernel scratch
   blok::FusedPlan plan;
   bool use_fused = false;

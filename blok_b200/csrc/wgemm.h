@@ -1,0 +1,33 @@
+// Interface of the weight-streaming GEMM (wgemm.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <cstddef>
+#include <cstdint>
+
+namespace blok {
+
+enum { WG_BF16_PLAIN = 0, WG_BF16_SWIGLU = 1, WG_I4_SWIGLU = 2, WG_I4_PLAIN = 3 };
+constexpr int kWgTileTokens = 64;
+
+struct WgArgs {
+  const void *w_a;
+  const void *w_b;
+  const uint16_t *s_a;
+  const uint16_t *s_b;
+  long expert_stride_rows;
+  const uint16_t *x;
+  const int *x_index;
+  int K;
+  int R;
+  uint16_t *out_bf16;
+  float *out_f32;
+  const int *tile_expert;
+  const int *tile_start;
+  const int *tile_count;
+  const int *num_tiles;
+  const int *out_index;
+};
+
+int launch_wgemm(int mode, const WgArgs &args, int max_tiles, cudaStream_t stream);
+
+}  // namespace blok

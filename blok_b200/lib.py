@@ -189,6 +189,16 @@ def router(router_w, bias, x, topk=8, routed_scale=2.827):
     return ids, wts
 
 
+def moe_combine(y_assign, wts, shared=None):
+    """out[t] = bf16(bf16(sum_k w[t,k] * y[t*topk+k]) + shared[t]) (src/kimi_exec.cu:399-407, :248)."""
+    T, topk = wts.shape
+    hidden = y_assign.shape[-1]
+    out = torch.empty((T, hidden), dtype=torch.bfloat16, device=y_assign.device)
+    _check(load().blok_moe_combine(_ptr(y_assign, torch.bfloat16), _ptr(wts, torch.float32), _ptr(shared, torch.bfloat16),
+                                   C.c_int(T), C.c_int(topk), C.c_int(hidden), _ptr(out), _stream()))
+    return out
+
+
 class MoeLayer:
     """Handle of one routed-MoE layer (the MoE branch of src/kimi_exec.cu:836-875).
 
@@ -247,6 +257,34 @@ class MoeLayer:
         _check(load().blok_moe_decode(self._handle, _ptr(x, torch.bfloat16, "x"), _ptr(y, torch.bfloat16, "y"), _ptr(ids),
                                       _ptr(wts), _stream()))
         return (y, ids, wts) if return_routing else y
+
+    def batched(self, x, return_routing=False):
+        """Batched layer (config 2): x bf16 [T, hidden] -> y bf16 [T, hidden]; T <= max_tokens of the handle."""
+        T = x.shape[0]
+        y = torch.empty((T, self.hidden), dtype=torch.bfloat16, device=x.device)
+        ids = wts = None
+        if return_routing:
+            ids = torch.empty((T, self.topk), dtype=torch.int16, device=x.device)
+            wts = torch.empty((T, self.topk), dtype=torch.float32, device=x.device)
+        _check(load().blok_moe_batched(self._handle, _ptr(x, torch.bfloat16, "x"), C.c_int(T), _ptr(y), _ptr(ids), _ptr(wts),
+                                       _stream()))
+        return (y, ids, wts) if return_routing else y
+
+    def experts_grouped(self, x, expert_local, x_index=None):
+        """y[a] = bf16(expert_{expert_local[a]}(x[x_index[a]])) for N assignments (the expert-parallel building block)."""
+        N = expert_local.numel()
+        y = torch.empty((N, self.hidden), dtype=torch.bfloat16, device=x.device)
+        _check(load().blok_moe_experts_grouped(self._handle, _ptr(x, torch.bfloat16, "x"), _ptr(x_index, torch.int32),
+                                               _ptr(expert_local, torch.int32, "expert_local"), C.c_int(N), _ptr(y),
+                                               _stream()))
+        return y
+
+    def shared(self, x):
+        """The shared expert for T tokens (bf16_mlp, src/kimi_exec.cu:872-875)."""
+        T = x.shape[0]
+        out = torch.empty((T, self.hidden), dtype=torch.bfloat16, device=x.device)
+        _check(load().blok_moe_shared(self._handle, _ptr(x, torch.bfloat16, "x"), C.c_int(T), _ptr(out), _stream()))
+        return out
 
     def decode_host(self, x_host, y_host):
         """Host-buffer call: x_host / y_host are (ideally pinned) CPU bf16 tensors of [hidden]; returns after the

@@ -194,6 +194,32 @@ int blok_moe_layer_destroy(blok_moe_layer_t *layer);
 int blok_moe_decode(blok_moe_layer_t *layer, const blok_bf16_t *x, blok_bf16_t *y, uint16_t *ids_out, float *wts_out,
                     blok_stream_t stream);
 
+/* Batched layer (config 2): x, y bf16 [T, hidden], T <= max_tokens of the handle.
+ * Tokens are permuted by expert, every touched expert's INT4 weights are streamed
+ * once through a grouped W4A16 GEMM, outputs are combined per token with the
+ * routing weights and the shared expert is added: the arithmetic of
+ * src/kimi_exec.cu:836-877 for each token.  ids_out uint16 [T, topk] and wts_out
+ * fp32 [T, topk] may be NULL.  All experts must be local. */
+int blok_moe_batched(blok_moe_layer_t *layer, const blok_bf16_t *x, int T, blok_bf16_t *y, uint16_t *ids_out,
+                     float *wts_out, blok_stream_t stream);
+
+/* The expert half of the batched layer on its own, the building block of expert
+ * parallelism: N assignments, assignment a = (row x_index[a] of x, local expert
+ * expert_local[a] in [0, experts_local)); y[a, :] = bf16(expert(x_row)) (unweighted;
+ * the owner of the token applies the routing weight, as expert_accum_k :399 does).
+ * x_index NULL means row a.  N <= max_tokens * topk of the handle. */
+int blok_moe_experts_grouped(blok_moe_layer_t *layer, const blok_bf16_t *x, const int *x_index, const int *expert_local,
+                             int N, blok_bf16_t *y, blok_stream_t stream);
+
+/* The shared expert for T tokens: out[t] = bf16(W_d(SiLU(W_g x[t]) * W_u x[t])), bf16_mlp
+ * (src/kimi_exec.cu:674-686, call site :872-875) without its running-sum side effect. */
+int blok_moe_shared(blok_moe_layer_t *layer, const blok_bf16_t *x, int T, blok_bf16_t *out, blok_stream_t stream);
+
+/* out[t] = bf16(bf16(sum_k wts[t,k] * y_assign[t*topk + k]) + shared[t]) in slot order
+ * (expert_accum_k :399, round_bf16_k :404, add_k :248); shared may be NULL. */
+int blok_moe_combine(const blok_bf16_t *y_assign, const float *wts, const blok_bf16_t *shared, int T, int topk, int hidden,
+                     blok_bf16_t *out, blok_stream_t stream);
+
 /* Synchronises `stream` and reports whether a device-side wait of an earlier
  * blok_moe_decode on this handle gave up (BLOK_ERR_TIMEOUT; the handle is reset
  * and stays usable).  The reference has no such state: its kernels never wait

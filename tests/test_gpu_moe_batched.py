@@ -1,0 +1,89 @@
+"""GPU parity of the batched routed-MoE layer (config 2) against the oracle and against the batch-1 path."""
+import numpy as np
+import pytest
+import torch
+
+import util
+from test_gpu_moe_decode import _host_layer
+
+pytestmark = pytest.mark.gpu
+MARGIN = 2e-6
+
+
+def _oracle_layer(oracle, w, x, ids_needed, topk=8):
+    slot_of, packs, scs, shared = _host_layer(w, ids_needed)
+    return oracle.moe_layer(util.t2np_bf16(w["router_w"]), util.t2np_f32(w["router_bias"]), slot_of, packs["gate_w"],
+                            scs["gate_s"], packs["up_w"], scs["up_s"], packs["down_w"], scs["down_s"], shared[0], shared[1],
+                            shared[2], util.t2np_f32(x), topk=topk, mode=0)
+
+
+@pytest.mark.parametrize("T,hidden,inter,experts,shared,seed", [(40, 1024, 512, 128, 512, 31), (1, 1024, 512, 128, 512, 32),
+                                                                (64, 7168, 2048, 384, 2048, 2), (130, 512, 512, 128, 0, 33)])
+def test_moe_batched_vs_oracle(cuda, oracle, T, hidden, inter, experts, shared, seed):
+    from blok_b200 import lib, synth
+    w = synth.moe_layer_weights(cuda, seed=seed, hidden=hidden, inter=inter, experts=experts, shared_inter=shared)
+    if hidden < 7168:
+        for k in ("gate_s", "up_s", "down_s"):
+            w[k] = (w[k].float() * 8).bfloat16()
+        w["router_w"] = (w["router_w"].float() * 20).bfloat16()
+    layer = lib.MoeLayer(w, max_tokens=max(T, 2))
+    x = synth.activations(T, hidden, cuda, seed)
+    y, ids, wts = layer.batched(x, return_routing=True)
+    torch.cuda.synchronize()
+    ids_h = util.ids_np(ids)
+    oid, owt, margin, _ = oracle.router(util.t2np_bf16(w["router_w"]), util.t2np_f32(w["router_bias"]), util.t2np_f32(x), mode=0)
+    clear = margin > MARGIN
+    assert clear.mean() > 0.95
+    for t in np.nonzero(clear)[0]:
+        assert set(ids_h[t].tolist()) == set(oid[t].tolist()), "token %d" % t
+    out, _, _ = _oracle_layer(oracle, w, x, list(ids_h.ravel()) + list(oid.ravel()))
+    yh = util.t2np_f32(y)
+    same = np.all(ids_h == oid, axis=1)
+    for t in np.nonzero(same)[0]:
+        util.assert_close(yh[t], out[t], "batched token %d" % t)
+    assert same.mean() > 0.9
+    assert torch.equal(y, layer.batched(x)), "deterministic"
+    layer.close()
+
+
+def test_moe_batched_agrees_with_decode_path_at_2048_tokens(cuda):
+    """T = 2048 (config 2's large case): every token of the batch must match the batch-1 kernel on the same token."""
+    from blok_b200 import lib, synth
+    w = synth.moe_layer_weights(cuda, seed=2)
+    layer = lib.MoeLayer(w, max_tokens=2048)
+    x = synth.activations(2048, 7168, cuda, 2)
+    y, ids, wts = layer.batched(x, return_routing=True)
+    counts = torch.bincount(ids.view(torch.int16).long().ravel() & 0xFFFF, minlength=384)
+    assert int(counts.sum()) == 2048 * 8 and int((counts > 0).sum()) > 350
+    for t in (0, 1, 777, 2047):
+        y1, i1, w1 = layer.decode(x[t].contiguous(), return_routing=True)
+        if torch.equal(i1, ids[t]):
+            assert util.max_abs_rel(util.t2np_f32(y[t]), util.t2np_f32(y1)) < 1e-2
+            assert util.cosine(util.t2np_f32(y[t]), util.t2np_f32(y1)) > 0.9999
+    np.testing.assert_allclose(util.t2np_f32(wts).sum(axis=1), 2.827, rtol=1e-5)
+    layer.close()
+
+
+def test_experts_grouped_handles_empty_and_ragged_groups(cuda, oracle):
+    """Assignments concentrated on few experts (others get zero tokens), more than one 64-token tile for one expert."""
+    from blok_b200 import lib, synth
+    hidden, inter, experts = 512, 512, 128
+    w = synth.moe_layer_weights(cuda, seed=41, hidden=hidden, inter=inter, experts=experts, shared_inter=0)
+    for k in ("gate_s", "up_s", "down_s"):
+        w[k] = (w[k].float() * 8).bfloat16()
+    layer = lib.MoeLayer(w, max_tokens=64)
+    x = synth.activations(30, hidden, cuda, 41)
+    e = torch.tensor([5] * 70 + [127] * 3 + [0] + [64] * 9, dtype=torch.int32, device=cuda)
+    rows = torch.arange(e.numel(), dtype=torch.int32, device=cuda) % 30
+    y = util.t2np_f32(layer.experts_grouped(x, e, rows))
+    xh = util.t2np_f32(x)
+    for a in (0, 69, 70, 72, 73, 82):
+        ex = int(e[a])
+        ref = oracle.expert_ffn(util.t2np_u32(w["gate_w"][ex]), util.t2np_bf16(w["gate_s"][ex]), util.t2np_u32(w["up_w"][ex]),
+                                util.t2np_bf16(w["up_s"][ex]), util.t2np_u32(w["down_w"][ex]), util.t2np_bf16(w["down_s"][ex]),
+                                xh[int(rows[a])], mode=0, round_out=True)
+        util.assert_close(y[a], ref, "assignment %d" % a)
+    assert layer.experts_grouped(x, e[:0].contiguous(), rows[:0].contiguous()).shape == (0, hidden)
+    with pytest.raises(lib.BlokError):
+        layer.experts_grouped(x, torch.zeros(64 * 8 + 1, dtype=torch.int32, device=cuda))
+    layer.close()
