@@ -169,7 +169,9 @@ using namespace blok;
 
 extern "C" int blok_moe_experts_grouped(blok_moe_layer_t *L, const blok_bf16_t *x, const int *x_index,
                                         const int *expert_local, int N, blok_bf16_t *y, blok_stream_t stream) {
-  BLOK_REQUIRE(L && x && expert_local && y, BLOK_ERR_ARG, "blok_moe_experts_grouped: null pointer");
+  BLOK_REQUIRE(L, BLOK_ERR_ARG, "blok_moe_experts_grouped: null layer");
+  if (N == 0) return BLOK_OK;  // empty inputs may carry null pointers
+  BLOK_REQUIRE(x && expert_local && y, BLOK_ERR_ARG, "blok_moe_experts_grouped: null pointer");
   BLOK_REQUIRE(L->bws, BLOK_ERR_STATE, "blok_moe_experts_grouped: the layer was created with max_tokens = 1");
   BLOK_REQUIRE(N >= 0 && N <= L->b_max_assign, BLOK_ERR_SHAPE, "blok_moe_experts_grouped: N=%d exceeds capacity %d", N,
                L->b_max_assign);
