@@ -9,26 +9,32 @@
 // with an atomic counter, so the load balances itself and nothing waits at a
 // phase boundary except where the data really is not there yet:
 //
-//   R   router logits, bf16               16 rows x 8 k-steps per chunk
-//   A   shared-expert gate/up, bf16       (8 gate + 8 up rows) x 16 k-steps
-//   B   the selected experts' INT4 gate/up (8 + 8 rows) x 8 k-blocks; needs the routing
-//   C1  INT4 down, one (slot, 16 output rows) block per chunk; needs every mid value
-//   C2  shared-expert down, bf16          16 rows x 16 k-steps; needs the shared mid
+//   R   router logits, bf16               16 rows x 28 k-steps per chunk
+//   A   shared-expert gate/up, bf16       (8 gate + 8 up rows) x 28 k-steps
+//   B   the selected experts' INT4 gate/up (8 + 8 rows) x 14 k-blocks; needs the routing
+//   C1  INT4 down, one (slot, 16 output rows) block per chunk; needs that slot's mid values
+//   C2  shared-expert down, bf16          16 rows x 32 k-steps; needs the shared mid
 //
 // A chunk covers a row-block only partly.  Its 16 partial dot products go to a
-// scratch slot indexed by the chunk's position in the row-block, and the warp that
-// hands in the last chunk of a row-block (an arrival counter tells) sums the slots
-// in index order and runs the row-block's epilogue: logits (and, for the last
-// router row-block, the top-k for the whole grid), SiLU*up -> mid, or the
-// per-slot down output whose 9th arrival triggers the weighted combine
+// scratch slot indexed by the chunk's position in the row-block.  The warp that holds
+// the LAST chunk of a row-block in queue order is its finisher: it sums the slots in
+// index order and runs the row-block's epilogue: logits; SiLU*up -> mid; or, for the
+// shared-expert down rows, the weighted combine of all nine contributions
 //   y = bf16(bf16(sum_k w_k * bf16(y_k)) + bf16(shared)).
 // Which warp computes a chunk varies from run to run; what is summed in which
 // order does not, so results are deterministic.
 //
-// A warp that pulls a C chunk puts its weight loads in flight BEFORE it waits for
-// the mid values, so the one real dependency of the layer costs little.  Every
-// wait on another warp is a bounded spin that records an error word and goes on:
-// the kernel always terminates.  The launch is cooperative (all CTAs resident).
+// Everything one warp hands to another (partial sums, logits, mid values, per-slot
+// outputs) travels as an 8-byte (value, tag) pair written with one store; the tag is
+// the launch's epoch.  A reader polls a slot until the tag matches, so there is no
+// fence, no arrival counter and no grid barrier: a down-projection chunk only waits
+// if the very mid values it needs are not written yet, and its weight loads are in
+// flight before it looks.  The routing is computed once per CTA from the tagged
+// logits.  Every poll is bounded and records an error word read by
+// blok_moe_layer_check; the launch is cooperative (all CTAs resident), so the warps
+// being waited for are always running.  Weights stream through a warp-private
+// cp.async ring in shared memory (each lane copies and later reads back its own
+// words, so the ring needs no barrier).
 #include <algorithm>
 #include <vector>
 
@@ -49,7 +55,7 @@ constexpr int kFusedWarps = BLOK_FUSED_WARPS;
 constexpr int kFusedThreads = kFusedWarps * 32;
 constexpr unsigned kSpinLimit = 1u << 22;  // polls before a wait gives up with an error word
 
-enum { CTRL_QUEUE = 0, CTRL_ROUTER = 1, CTRL_ROUTED = 2, CTRL_MID = 3, CTRL_EXIT = 4, CTRL_ERROR = 5 };
+enum { CTRL_QUEUE = 0, CTRL_ROUTER = 1, CTRL_ROUTED = 2, CTRL_MID = 3, CTRL_EXIT = 4, CTRL_ERROR = 5, CTRL_EPOCH = 6 };
 constexpr int kTraceSlots = 16;
 
 struct FusedParams {
@@ -64,14 +70,13 @@ struct FusedParams {
   uint16_t *y;
   uint16_t *ids_out;
   float *wts_out;
-  float *logits;   // [experts]
+  uint2 *logits;   // [experts] (router logit, launch tag)
   int *route_ids;  // [topk] selected experts, published by the warp that runs the top-k
   float *route_wts;
-  uint16_t *mid;   // [topk + 1][mid_stride] bf16; row topk is the shared expert's
+  uint2 *mid;      // [topk + 1][mid_stride / 2] (two bf16 mid values, launch tag); row topk is the shared expert's
   int mid_stride;
-  float *ys;       // [topk + 1][hidden] bf16-valued per-slot down outputs
-  float *partR, *partA, *partB, *partC2;
-  unsigned *cntR, *cntA, *cntB, *cntC2, *cntOut;
+  uint2 *ys;       // [topk + 1][hidden] (bf16-valued per-slot down output, launch tag)
+  uint2 *partR, *partA, *partB, *partC2;  // [row-block][chunk][16] (partial dot product, launch tag)
   // chunking: steps per row-block, steps per chunk, chunks per row-block
   int sprR, spcR, cprR;
   int sprA, spcA, cprA;
@@ -133,36 +138,66 @@ __device__ __forceinline__ unsigned warp_arrive(unsigned *counter, int lane) {
   return old;
 }
 
-// A warp hands in chunk `kc` of row-block `rb` (npieces chunks per row-block).  `v`
-// is the chunk's partial dot product for A row g + 8*(t>>1) (lanes with even t).
-// Returns true in the warp that completes the row-block, with the 16 row totals in
-// lanes 0..15 (chunks summed in index order).
-__device__ __forceinline__ bool hand_in_piece(float v, float *part, unsigned *cnt, int rb, int kc, int npieces,
-                                              int lane, float &total) {
-  const int g = lane >> 2, t = lane & 3;
-  if (npieces == 1) {
-    total = __shfl_sync(0xffffffffu, v, ((lane & 7) << 2) + ((lane >> 3) & 1) * 2);
-    return true;
-  }
-  if ((t & 1) == 0) __stcg(part + ((size_t)rb * npieces + kc) * 16 + g + 8 * (t >> 1), v);
-  const unsigned old = warp_arrive(cnt + rb, lane);
-  if (old != (unsigned)(npieces - 1)) return false;
-  float s = 0.f;
-  if (lane < 16) {
-    const float *src = part + (size_t)rb * npieces * 16 + lane;
-    int i = 0;
-    for (; i + 8 <= npieces; i += 8) {  // eight loads in flight, summed in index order
-      float a[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) a[j] = __ldcg(src + (i + j) * 16);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) s += a[j];
+// Results that one warp hands to another travel as (value, tag) pairs written with one
+// 8-byte store; the tag is the launch's epoch, so a reader that polls a slot until the
+// tag matches knows the value is this launch's, without any fence or counter.
+__device__ __forceinline__ void st_tagged(uint2 *p, float v, unsigned tag) {
+  asm volatile("st.global.cg.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+}
+__device__ __forceinline__ float ld_tagged(const uint2 *p, unsigned tag, unsigned *err) {
+  unsigned v, tg, it = 0;
+  for (;;) {
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v), "=r"(tg) : "l"(p) : "memory");
+    if (tg == tag) break;
+    if (++it > kSpinLimit) {
+      atomicExch(err, 3u);
+      break;
     }
-    for (; i < npieces; ++i) s += __ldcg(src + i * 16);
+    __nanosleep(20);
   }
-  total = s;
-  if (lane == 0) cnt[rb] = 0;  // leave the counter clean for the next launch
-  return true;
+  return __uint_as_float(v);
+}
+// N tagged values at p[0], p[stride], ...: all loads are issued before any tag is looked at,
+// so the wait is one memory round trip, not N; the batch is re-read only while a tag is missing.
+template <int N>
+__device__ __noinline__ void ld_tagged_n(const uint2 *p, int stride, int n, unsigned tag, unsigned *err,
+                                            float (&out)[N]) {
+  unsigned v[N], tg[N];
+  for (unsigned it = 0;; ++it) {
+#pragma unroll
+    for (int i = 0; i < N; ++i)
+      if (i < n) asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v[i]), "=r"(tg[i]) : "l"(p + (size_t)i * stride) : "memory");
+    bool ok = true;
+#pragma unroll
+    for (int i = 0; i < N; ++i)
+      if (i < n && tg[i] != tag) ok = false;
+    if (ok) break;
+    if (it > kSpinLimit) {
+      atomicExch(err, 3u);
+      break;
+    }
+    __nanosleep(20);
+  }
+#pragma unroll
+  for (int i = 0; i < N; ++i) out[i] = i < n ? __uint_as_float(v[i]) : 0.f;
+}
+
+// Two consecutive tagged pairs with one 16-byte load: {v0, tag0, v1, tag1}.
+__device__ __forceinline__ uint2 ld_tagged2(const uint2 *p, unsigned tag, unsigned *err) {
+  unsigned v0, t0, v1, t1, it = 0;
+  for (;;) {
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v0), "=r"(t0), "=r"(v1), "=r"(t1) : "l"(p) : "memory");
+    if (t0 == tag && t1 == tag) break;
+    if (++it > kSpinLimit) {
+      atomicExch(err, 4u);
+      break;
+    }
+    __nanosleep(20);
+  }
+  return make_uint2(v0, v1);
+}
+__device__ __forceinline__ void red_release_add(unsigned *p, unsigned v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 __device__ __forceinline__ float swiglu_ref_rounding(float g, float u) {
@@ -266,23 +301,62 @@ __device__ __forceinline__ float ring_consume(const Chunk &ch, uint32_t ring, co
   return (t & 2) ? d[2] : d[0];
 }
 
-// One warp stages `cols` activation values (bf16, written earlier in this kernel by
-// other CTAs, hence read through L2) into INT4 fragment order with group sums.
-__device__ __forceinline__ void warp_stage_i4(const uint4 *src, uint4 *xfrag, float *xsum, int cols, int lane) {
-  for (int u = lane; u < cols / 8; u += 32) {
-    uint4 v = __ldcg(src + u);
-    int kb = u >> 4, t = (u >> 2) & 3, i = u & 3;
-    uint4 o;
-    o.x = __byte_perm(v.x, v.z, 0x5410);
-    o.y = __byte_perm(v.x, v.z, 0x7632);
-    o.z = __byte_perm(v.y, v.w, 0x5410);
-    o.w = __byte_perm(v.y, v.w, 0x7632);
-    xfrag[kb * 16 + i * 4 + t] = o;
-    float s = ((bf16lo(v.x) + bf16hi(v.x)) + (bf16lo(v.y) + bf16hi(v.y))) +
-              ((bf16lo(v.z) + bf16hi(v.z)) + (bf16lo(v.w) + bf16hi(v.w)));
-    s += __shfl_xor_sync(0xffffffffu, s, 1);
-    s += __shfl_xor_sync(0xffffffffu, s, 2);
-    if ((u & 3) == 0) xsum[u >> 2] = s;
+// Up to NU tagged 32-byte units (8 mid values each) at p, p + stride, ...: loads first, tags after.
+template <int NU>
+__device__ __forceinline__ void ld_tagged_units(const uint2 *p, int stride, int n, unsigned tag, unsigned *err,
+                                                uint4 (&out)[NU]) {
+  unsigned r[NU][8];
+  for (unsigned it = 0;; ++it) {
+#pragma unroll
+    for (int i = 0; i < NU; ++i)
+      if (i < n) {
+        const uint2 *q = p + (size_t)i * stride;
+        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(r[i][0]), "=r"(r[i][1]), "=r"(r[i][2]), "=r"(r[i][3]) : "l"(q) : "memory");
+        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(r[i][4]), "=r"(r[i][5]), "=r"(r[i][6]), "=r"(r[i][7]) : "l"(q + 2) : "memory");
+      }
+    bool ok = true;
+#pragma unroll
+    for (int i = 0; i < NU; ++i)
+      if (i < n && (r[i][1] != tag || r[i][3] != tag || r[i][5] != tag || r[i][7] != tag)) ok = false;
+    if (ok) break;
+    if (it > kSpinLimit) {
+      atomicExch(err, 4u);
+      break;
+    }
+    __nanosleep(20);
+  }
+#pragma unroll
+  for (int i = 0; i < NU; ++i) out[i] = make_uint4(r[i][0], r[i][2], r[i][4], r[i][6]);
+}
+
+// One warp stages `cols` mid values (tagged pairs written earlier in this launch by other
+// warps; values that are not there yet are polled) into INT4 fragment order with group sums.
+__device__ __noinline__ void warp_stage_i4(const uint2 *src, uint4 *xfrag, float *xsum, int cols, int lane,
+                                              unsigned epoch, unsigned *err) {
+  const int units = cols / 8;  // 32-byte tagged units; lane handles units lane, lane + 32, ...
+  for (int u0 = lane; u0 < units; u0 += 64) {
+    uint4 vv[2];
+    const int n = min(2, (units - u0 + 31) / 32);
+    ld_tagged_units<2>(src + (size_t)u0 * 4, 32 * 4, n, epoch, err, vv);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int u = u0 + 32 * j;
+      if (u < units) {  // units is a multiple of 32, so this is warp-uniform
+        const uint4 v = vv[j];
+        int kb = u >> 4, t = (u >> 2) & 3, i = u & 3;
+        uint4 o;
+        o.x = __byte_perm(v.x, v.z, 0x5410);
+        o.y = __byte_perm(v.x, v.z, 0x7632);
+        o.z = __byte_perm(v.y, v.w, 0x5410);
+        o.w = __byte_perm(v.y, v.w, 0x7632);
+        xfrag[kb * 16 + i * 4 + t] = o;
+        float s = ((bf16lo(v.x) + bf16hi(v.x)) + (bf16lo(v.y) + bf16hi(v.y))) +
+                  ((bf16lo(v.z) + bf16hi(v.z)) + (bf16lo(v.w) + bf16hi(v.w)));
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        if ((u & 3) == 0) xsum[u >> 2] = s;
+      }
+    }
   }
   __syncwarp();
 }
@@ -307,10 +381,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
   const size_t wstage_bytes = (size_t)p.inter * 2 + (size_t)(p.inter / 32) * 4;
   unsigned char *wstage = sp + (size_t)warp * wstage_bytes;  // this warp's private segment of mid
   sp += (size_t)kFusedWarps * wstage_bytes;
-  int *w_ids = reinterpret_cast<int *>(sp) + warp * 16;  // this warp's copy of the routing
+  int *w_ids = reinterpret_cast<int *>(sp);  // the CTA's copy of the routing
   sp += (size_t)kFusedWarps * 16 * 4;
-  float *w_wts = reinterpret_cast<float *>(sp) + warp * 16;
+  float *w_wts = reinterpret_cast<float *>(sp);
   sp += (size_t)kFusedWarps * 16 * 4;
+  __shared__ int s_route_state;  // 0 nobody has it, 1 one warp is computing it, 2 ready
+  if (tid == 0) s_route_state = 0;
   float *s_score = reinterpret_cast<float *>(sp);  // top-k scratch (one warp of the grid uses it)
   float *s_sel = s_score + p.experts;
   const uint32_t ring = (uint32_t)__cvta_generic_to_shared(ring_ptr);
@@ -336,8 +412,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
   xl_m.kb_stride = supply ? 16 : 0;
   float *msum = reinterpret_cast<float *>(wstage + (size_t)p.inter * 2);
 
+  const unsigned epoch = p.ctrl[CTRL_EPOCH] + 1u;  // stable during the launch; the last CTA to leave bumps it
+  unsigned *const err = p.ctrl + CTRL_ERROR;
   bool have_routing = false;
-  bool mid_ready = false;
   const int nrb_router = p.experts / 16;
   const unsigned ncontrib = (unsigned)p.topk + (p.shared_inter ? 1u : 0u);
 
@@ -412,100 +489,186 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
     return ch;
   };
 
+  // The routing is computed once per CTA, by the first warp that needs it, from the tagged
+  // logits (polled until the router's finishers have written them); same inputs, same rule,
+  // so every CTA selects the same experts.  The other warps wait on a shared-memory flag.
   auto fetch_routing = [&]() {
-    warp_wait(p.ctrl + CTRL_ROUTED, 1u, p.ctrl + CTRL_ERROR, 1u, lane);
-    if (lane < p.topk) {
-      w_ids[lane] = __ldcg(p.route_ids + lane);
-      w_wts[lane] = __ldcg(p.route_wts + lane);
-    }
-    __syncwarp();
-    have_routing = true;
-  };
-
-  // Hand the finished chunk in and run whatever epilogue its completion triggers.
-  auto finish = [&](const Chunk &ch, float v) {
-    float total;
-    if (ch.kind == KIND_R) {
-      if (!hand_in_piece(v, p.partR, p.cntR, ch.rb, ch.kc, p.cprR, lane, total)) return;
-      if (lane < 16) __stcg(p.logits + ch.rb * 16 + lane, total);
-      if (warp_arrive(p.ctrl + CTRL_ROUTER, lane) != (unsigned)nrb_router - 1) return;
-      // every logit is in place: this warp selects the experts for the whole grid
-      for (int i = lane; i < p.experts; i += 32) {
-        float sc = 1.0f / (1.0f + expf(-__ldcg(p.logits + i)));
-        s_score[i] = sc;
-        s_sel[i] = sc + p.router_bias[i];
+    int st = 0;
+    if (lane == 0) st = atomicCAS(&s_route_state, 0, 1);
+    st = __shfl_sync(0xffffffffu, st, 0);
+    if (st == 0) {
+      for (int i0 = lane; i0 < p.experts; i0 += 32 * 4) {
+        float lg[4];
+        const int n = min(4, (p.experts - i0 + 31) / 32);
+        ld_tagged_n<4>(p.logits + i0, 32, n, epoch, err, lg);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int i = i0 + 32 * j;
+          if (j < n) {
+            const float sc = 1.0f / (1.0f + expf(-lg[j]));
+            s_score[i] = sc;
+            s_sel[i] = sc + p.router_bias[i];
+          }
+        }
       }
       __syncwarp();
       int my_id;
       float my_w;
       warp_topk(s_score, s_sel, p.experts, p.topk, p.routed_scale, lane, my_id, my_w);
       if (lane < p.topk) {
-        __stcg(p.route_ids + lane, my_id);
-        __stcg(p.route_wts + lane, my_w);
-        if (p.ids_out) p.ids_out[lane] = (uint16_t)my_id;
-        if (p.wts_out) p.wts_out[lane] = my_w;
+        w_ids[lane] = my_id;
+        w_wts[lane] = my_w;
+        if (blockIdx.x == 0) {
+          if (p.ids_out) p.ids_out[lane] = (uint16_t)my_id;
+          if (p.wts_out) p.wts_out[lane] = my_w;
+        }
       }
-      warp_arrive(p.ctrl + CTRL_ROUTED, lane);
-      if (lane == 0) trace_launch(p, 1);
+      __threadfence_block();
+      __syncwarp();
+      if (lane == 0) {
+        atomicExch(&s_route_state, 2);
+        if (blockIdx.x == 0) trace_launch(p, 1);
+      }
+    } else if (st == 1) {
+      if (lane == 0) {
+        unsigned it = 0;
+        while (atomicAdd(&s_route_state, 0) != 2) {
+          if (++it > kSpinLimit) {
+            atomicExch(err, 1u);
+            break;
+          }
+          __nanosleep(100);
+        }
+      }
+      __syncwarp();
+    }
+    __threadfence_block();
+    have_routing = true;
+  };
+
+  // Handing a finished chunk in: arrive() publishes the chunk's partial result as tagged
+  // values and returns at once (no fence, no atomic).  The warp that holds the LAST chunk of
+  // a row-block in queue order is its finisher: complete() makes it collect the other
+  // chunks' values (polling a slot only if its writer is still at work), sum them in index
+  // order and run the row-block's epilogue.  Chunks are handed out in order, so the chunks a
+  // finisher waits for are already being worked on by warps that never wait for it.
+  auto piece_part = [&](const Chunk &ch) { return ch.kind == KIND_R ? p.partR : ch.kind == KIND_A ? p.partA : ch.kind == KIND_B ? p.partB : p.partC2; };
+  auto piece_n = [&](const Chunk &ch) { return ch.kind == KIND_R ? p.cprR : ch.kind == KIND_A ? p.cprA : ch.kind == KIND_B ? p.cprB : p.cprC2; };
+
+  auto arrive = [&](const Chunk &ch, float v) {
+    if (ch.kind == KIND_C1) {
+      const float total = __shfl_sync(0xffffffffu, v, ((lane & 7) << 2) + ((lane >> 3) & 1) * 2);
+      if (lane < 16) st_tagged(p.ys + (size_t)ch.slot * p.hidden + ch.rb * 16 + lane, round_bf16(total), epoch);
+      return;
+    }
+    const int np = piece_n(ch);
+    if (np > 1 && ch.kc != np - 1 && (t & 1) == 0)
+      st_tagged(piece_part(ch) + ((size_t)ch.rb * np + ch.kc) * 16 + g + 8 * (t >> 1), v, epoch);
+  };
+
+  // out rows [ob*16, +16): every slot's contribution (tagged) weighted in slot order, plus the shared expert's
+  auto combine_rows = [&](int ob, float own, int own_slot) {
+    if (lane < 16) {
+      float o = 0.f;
+      for (int k0 = 0; k0 < p.topk; k0 += 4) {
+        float yk[4];
+        const int n = min(4, p.topk - k0);
+        if (own_slot >= k0 && own_slot < k0 + n) {  // the own slot's value is not in memory: read the others one by one
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            yk[j] = (j >= n || k0 + j == own_slot) ? own : ld_tagged(p.ys + (size_t)(k0 + j) * p.hidden + ob * 16 + lane, epoch, err);
+        } else {
+          ld_tagged_n<4>(p.ys + (size_t)k0 * p.hidden + ob * 16 + lane, p.hidden, n, epoch, err, yk);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (j < n) o = fmaf(yk[j], w_wts[k0 + j], o);
+      }
+      o = round_bf16(o);
+      if (p.shared_inter) o = round_bf16(o + own);
+      p.y[ob * 16 + lane] = f32_to_bf16_bits(o);
+    }
+  };
+
+  auto complete = [&](const Chunk &ch, float v) {
+    if (ch.kind == KIND_C1) {
+      // without a shared expert the last routed slot finishes the output rows
+      if (p.shared_inter == 0 && ch.slot == p.topk - 1) {
+        const float total = round_bf16(__shfl_sync(0xffffffffu, v, ((lane & 7) << 2) + ((lane >> 3) & 1) * 2));
+        combine_rows(ch.rb, total, ch.slot);
+      }
+      return;
+    }
+    const int np = piece_n(ch);
+    if (ch.kc != np - 1) return;
+    float total = __shfl_sync(0xffffffffu, v, ((lane & 7) << 2) + ((lane >> 3) & 1) * 2);  // this chunk's rows in lanes 0..15
+    if (np > 1 && lane < 16) {
+      const uint2 *src = piece_part(ch) + (size_t)ch.rb * np * 16 + lane;
+      float s = 0.f;
+      for (int i0 = 0; i0 < np - 1; i0 += 4) {  // index order, then the own (last) chunk
+        float part[4];
+        const int n = min(4, np - 1 - i0);
+        ld_tagged_n<4>(src + (size_t)i0 * 16, 16, n, epoch, err, part);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (j < n) s += part[j];
+      }
+      total = s + total;
+    }
+    if (ch.kind == KIND_R) {
+      if (lane < 16) st_tagged(p.logits + ch.rb * 16 + lane, total, epoch);
+      if (lane == 0) trace_launch(p, 5);
       return;
     }
     if (ch.kind == KIND_A || ch.kind == KIND_B) {
-      const bool a = ch.kind == KIND_A;
-      if (!hand_in_piece(v, a ? p.partA : p.partB, a ? p.cntA : p.cntB, ch.rb, ch.kc, a ? p.cprA : p.cprB, lane, total))
-        return;
       const float up = __shfl_down_sync(0xffffffffu, total, 8);
-      const int row0 = a ? ch.rb * 8 : (ch.rb - ch.slot * (p.inter / 8)) * 8;
-      if (lane < 8) p.mid[(size_t)ch.slot * p.mid_stride + row0 + lane] = f32_to_bf16_bits(swiglu_ref_rounding(total, up));
-      if (warp_arrive(p.ctrl + CTRL_MID, lane) == p.mid_target - 1 && lane == 0) trace_launch(p, 2);
+      const int row0 = ch.kind == KIND_A ? ch.rb * 8 : (ch.rb - ch.slot * (p.inter / 8)) * 8;
+      const uint32_t m = f32_to_bf16_bits(swiglu_ref_rounding(total, up));
+      const uint32_t hi = __shfl_down_sync(0xffffffffu, m, 1);
+      if (lane < 8 && (lane & 1) == 0)
+        st_tagged(p.mid + ((size_t)ch.slot * p.mid_stride + row0 + lane) / 2, __uint_as_float(m | (hi << 16)), epoch);
       return;
     }
-    if (ch.kind == KIND_C1) {
-      total = __shfl_sync(0xffffffffu, v, ((lane & 7) << 2) + ((lane >> 3) & 1) * 2);
-    } else {
-      if (!hand_in_piece(v, p.partC2, p.cntC2, ch.rb, ch.kc, p.cprC2, lane, total)) return;
-    }
-    // this slot's contribution to output rows [rb*16, rb*16+16) is complete
-    const int ob = ch.rb;
-    if (lane < 16) __stcg(p.ys + (size_t)ch.slot * p.hidden + ob * 16 + lane, round_bf16(total));
-    if (warp_arrive(p.cntOut + ob, lane) != ncontrib - 1) return;
-    if (lane < 16) {
-      float o = 0.f;
-      for (int k = 0; k < p.topk; ++k) o = fmaf(__ldcg(p.ys + (size_t)k * p.hidden + ob * 16 + lane), w_wts[k], o);
-      o = round_bf16(o);
-      if (p.shared_inter) o = round_bf16(o + __ldcg(p.ys + (size_t)p.topk * p.hidden + ob * 16 + lane));
-      p.y[ob * 16 + lane] = f32_to_bf16_bits(o);
-    }
-    if (lane == 0) p.cntOut[ob] = 0;
+    // KIND_C2: the shared expert's rows are complete, and with them the output rows
+    combine_rows(ch.rb, round_bf16(total), -1);
   };
 
+  // The first chunk of every warp is its own index (no herd of atomics at the start); later
+  // chunks come from the queue counter, fetched one chunk ahead.
+  const unsigned W = gridDim.x * kFusedWarps;
   unsigned next = 0;
-  if (lane == 0) next = atomicAdd(p.ctrl + CTRL_QUEUE, 1u);
-  unsigned c = __shfl_sync(0xffffffffu, next, 0);
+  unsigned c = blockIdx.x * kFusedWarps + warp;
   Chunk cur;
   cur.kind = KIND_NONE;
   if (c < p.total) {
-    if (lane == 0) next = atomicAdd(p.ctrl + CTRL_QUEUE, 1u);
+    if (lane == 0) next = W + atomicAdd(p.ctrl + CTRL_QUEUE, 1u);
     if (c >= p.cB0 && c < p.cC20) fetch_routing();
     cur = decode(c);
     ring_prologue(cur, ring, lane);
   }
+  int traced = 0;
   while (cur.kind != KIND_NONE) {
     // ---- the chunk's weights are in flight; now the activations -------------------------------
     float v;
+    const bool tr = p.trace && warp == 1 && lane == 0 && traced < 2;
+    if (tr) p.trace[16 + (size_t)blockIdx.x * kTraceSlots + 8 + traced * 4 + 0] = global_ns();
     if (cur.kind == KIND_C1 || cur.kind == KIND_C2) {
       if (!have_routing) fetch_routing();  // the combine needs the routing weights
-      if (!mid_ready) {
-        warp_wait(p.ctrl + CTRL_MID, p.mid_target, p.ctrl + CTRL_ERROR, 2u, lane);
-        mid_ready = true;
-      }
       if (cur.kind == KIND_C1) {
-        warp_stage_i4(reinterpret_cast<const uint4 *>(p.mid + (size_t)cur.slot * p.mid_stride),
-                      reinterpret_cast<uint4 *>(wstage), msum, p.inter, lane);
+        warp_stage_i4(p.mid + (size_t)cur.slot * p.mid_stride / 2, reinterpret_cast<uint4 *>(wstage), msum, p.inter, lane,
+                      epoch, err);
         v = ring_consume(cur, ring, ring_ptr, xl_m, msum, nullptr, 0, lane);
       } else {
         uint4 *seg = reinterpret_cast<uint4 *>(wstage);
-        const uint4 *src = reinterpret_cast<const uint4 *>(p.mid + (size_t)p.topk * p.mid_stride) + cur.k0 * 4;
-        for (int u = lane; u < cur.n * 4; u += 32) seg[u] = __ldcg(src + u);
+        const uint2 *src = p.mid + (size_t)p.topk * p.mid_stride / 2 + (size_t)cur.k0 * 16;
+        for (int u0 = lane; u0 < cur.n * 4; u0 += 64) {
+          uint4 vv[2];
+          const int n = min(2, (cur.n * 4 - u0 + 31) / 32);
+          ld_tagged_units<2>(src + (size_t)u0 * 4, 32 * 4, n, epoch, err, vv);
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+            if (u0 + 32 * j < cur.n * 4) seg[u0 + 32 * j] = vv[j];
+        }
         __syncwarp();
         v = ring_consume(cur, ring, ring_ptr, xl_m, msum, seg + t, cur.k0, lane);
       }
@@ -515,32 +678,38 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
     } else {
       v = ring_consume(cur, ring, ring_ptr, xl_x, xsum, xnat + t, 0, lane);
     }
-    // ---- next chunk: put its weights in flight before handing this one in -----------------------
+    // ---- hand in (without waiting), put the next chunk's weights in flight, then look at the count ----
+    if (tr) p.trace[16 + (size_t)blockIdx.x * kTraceSlots + 8 + traced * 4 + 1] = global_ns();
+    arrive(cur, v);
     c = __shfl_sync(0xffffffffu, next, 0);
     Chunk nx;
     nx.kind = KIND_NONE;
-    bool finished = false;
+    bool completed = false;
     if (c < p.total) {
-      if (lane == 0) next = atomicAdd(p.ctrl + CTRL_QUEUE, 1u);
+      if (lane == 0) next = W + atomicAdd(p.ctrl + CTRL_QUEUE, 1u);
       if (c >= p.cB0 && c < p.cC20 && !have_routing) {
-        // the routing may depend on the chunk in hand: hand it in before waiting
-        finish(cur, v);
-        finished = true;
+        // the routing may depend on the chunk in hand: finish it before waiting
+        complete(cur, v);
+        completed = true;
         fetch_routing();
       }
       nx = decode(c);
       ring_prologue(nx, ring, lane);
     }
-    if (!finished) finish(cur, v);
+    if (tr) p.trace[16 + (size_t)blockIdx.x * kTraceSlots + 8 + traced * 4 + 2] = global_ns();
+    if (!completed) complete(cur, v);
+    if (tr) p.trace[16 + (size_t)blockIdx.x * kTraceSlots + 8 + traced * 4 + 3] = global_ns(), ++traced;
     cur = nx;
   }
 
+  if (blockIdx.x == 0 && warp == 0 && !have_routing) fetch_routing();  // CTA 0 reports the routing to the caller
   // ---- the last CTA to leave resets the launch-wide counters ------------------------------------
   cp_async_wait<0>();
   if (warp == 0 && lane == 0) trace_cta(p, 6);
   __syncthreads();
   if (tid == 0) {
     trace_cta(p, 7);
+    const unsigned epoch_now = p.ctrl[CTRL_EPOCH] + 1u;
     __threadfence();
     unsigned old = atomicAdd(p.ctrl + CTRL_EXIT, 1u);
     if (old == gridDim.x - 1) {
@@ -549,6 +718,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
       p.ctrl[CTRL_ROUTED] = 0;
       p.ctrl[CTRL_MID] = 0;
       p.ctrl[CTRL_EXIT] = 0;
+      p.ctrl[CTRL_EPOCH] = epoch_now;
       __threadfence();
       trace_launch(p, 3);
     }
@@ -632,12 +802,12 @@ int launch_moe_decode_fused(blok_moe_layer *L, const uint16_t *x, uint16_t *y, u
   p.x = x; p.y = y;
   p.ids_out = ids_out ? ids_out : L->ids;
   p.wts_out = wts_out ? wts_out : L->wts;
-  p.logits = L->logits;
+  p.logits = reinterpret_cast<uint2 *>(L->f_logits_t);
   p.route_ids = L->f_route_ids; p.route_wts = L->f_route_wts;
-  p.mid = L->f_mid; p.mid_stride = L->f_mid_stride;
-  p.ys = L->f_ys;
-  p.partR = L->f_partR; p.partA = L->f_partA; p.partB = L->f_partB; p.partC2 = L->f_partC2;
-  p.cntR = L->f_cntR; p.cntA = L->f_cntA; p.cntB = L->f_cntB; p.cntC2 = L->f_cntC2; p.cntOut = L->f_cntOut;
+  p.mid = reinterpret_cast<uint2 *>(L->f_mid); p.mid_stride = L->f_mid_stride;
+  p.ys = reinterpret_cast<uint2 *>(L->f_ys);
+  p.partR = reinterpret_cast<uint2 *>(L->f_partR); p.partA = reinterpret_cast<uint2 *>(L->f_partA);
+  p.partB = reinterpret_cast<uint2 *>(L->f_partB); p.partC2 = reinterpret_cast<uint2 *>(L->f_partC2);
   p.sprR = pl.sprR; p.spcR = pl.spcR; p.cprR = pl.cprR;
   p.sprA = pl.sprA; p.spcA = pl.spcA; p.cprA = pl.cprA;
   p.sprB = pl.sprB; p.spcB = pl.spcB; p.cprB = pl.cprB;

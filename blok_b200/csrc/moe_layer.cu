@@ -85,16 +85,17 @@ extern "C" int blok_moe_layer_create(const blok_moe_weights *w, int max_tokens, 
   size_t o_iox = take((size_t)w->hidden * sizeof(uint16_t));
   size_t o_ioy = take((size_t)w->hidden * sizeof(uint16_t));
   const blok::FusedPlan &pl = L->plan;
-  size_t o_fmid = 0, o_fys = 0, o_pR = 0, o_route = 0, o_pA = 0, o_pB = 0, o_pC2 = 0, o_cnt = 0, n_cnt = 0;
+  size_t o_flog = 0, o_fmid = 0, o_fys = 0, o_pR = 0, o_route = 0, o_pA = 0, o_pB = 0, o_pC2 = 0, o_cnt = 0, n_cnt = 0;
   if (pl.enabled) {
     L->f_mid_stride = (int)align_up((size_t)std::max(w->inter, w->shared_inter), 64);
-    o_fmid = take((size_t)(w->topk + 1) * L->f_mid_stride * sizeof(uint16_t));
-    o_fys = take((size_t)(w->topk + 1) * w->hidden * sizeof(float));
+    o_fmid = take((size_t)(w->topk + 1) * L->f_mid_stride * 4);
+    o_flog = take((size_t)w->experts * 8);
+    o_fys = take((size_t)(w->topk + 1) * w->hidden * 2 * sizeof(float));
     o_route = take(32 * sizeof(float));
-    o_pR = take((size_t)pl.nrbR * pl.cprR * 16 * sizeof(float));
-    o_pA = take((size_t)std::max(pl.nrbA, 1) * pl.cprA * 16 * sizeof(float));
-    o_pB = take((size_t)pl.nrbB * pl.cprB * 16 * sizeof(float));
-    o_pC2 = take((size_t)std::max(pl.nrbC2, 1) * pl.cprC2 * 16 * sizeof(float));
+    o_pR = take((size_t)pl.nrbR * pl.cprR * 16 * 2 * sizeof(float));
+    o_pA = take((size_t)std::max(pl.nrbA, 1) * pl.cprA * 16 * 2 * sizeof(float));
+    o_pB = take((size_t)pl.nrbB * pl.cprB * 16 * 2 * sizeof(float));
+    o_pC2 = take((size_t)std::max(pl.nrbC2, 1) * pl.cprC2 * 16 * 2 * sizeof(float));
     n_cnt = (size_t)pl.nrbR + pl.nrbA + pl.nrbB + pl.nrbC2 + w->hidden / 16 + 8;
     o_cnt = take(n_cnt * sizeof(unsigned));
   }
@@ -125,6 +126,7 @@ extern "C" int blok_moe_layer_create(const blok_moe_weights *w, int max_tokens, 
   L->io_y = reinterpret_cast<uint16_t *>(b + o_ioy);
   if (pl.enabled) {
     L->f_mid = reinterpret_cast<uint16_t *>(b + o_fmid);
+    L->f_logits_t = reinterpret_cast<float *>(b + o_flog);
     L->f_ys = reinterpret_cast<float *>(b + o_fys);
     L->f_route_ids = reinterpret_cast<int *>(b + o_route);
     L->f_route_wts = reinterpret_cast<float *>(b + o_route) + 16;
@@ -208,7 +210,7 @@ extern "C" int blok_moe_layer_check(blok_moe_layer_t *L, blok_stream_t stream_) 
   BLOK_CUDA(cudaMemcpy(&err, L->f_ctrl + 5, sizeof(err), cudaMemcpyDeviceToHost));
   if (err == 0) return BLOK_OK;
   // a bounded wait inside the fused kernel gave up: clear every counter so that the handle stays usable
-  BLOK_CUDA(cudaMemset(L->f_counters, 0, L->f_counters_bytes));
+  BLOK_CUDA(cudaMemset(L->ws, 0, L->ws_bytes));  // counters, launch tags and the epoch all restart together
   set_error("blok_moe_decode: device-side wait %u timed out (1 = routing, 2 = mid values)", err);
   return BLOK_ERR_TIMEOUT;
 }

@@ -55,7 +55,8 @@ struct blok_moe_layer {
   // fused decode kernel scratch
   blok::FusedPlan plan;
   bool use_fused = false;
-  uint16_t *f_mid = nullptr;  // [topk + 1][f_mid_stride]
+  uint16_t *f_mid = nullptr;  // [topk + 1][f_mid_stride / 2] tagged pairs (8 bytes each)
+  float *f_logits_t = nullptr;  // [experts] tagged logits (8 bytes each)
   int f_mid_stride = 0;
   float *f_ys = nullptr;      // [topk + 1][hidden]
   float *f_partR = nullptr, *f_partA = nullptr, *f_partB = nullptr, *f_partC2 = nullptr;
