@@ -1,0 +1,72 @@
+"""Expert parallelism on real GPUs: 2 ranks over NCCL, each holding half of the experts; the sharded layer must
+reproduce the single-GPU batched layer on every rank's own tokens.  Skipped with fewer than 2 GPUs."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        import torch.distributed as dist
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        from blok_b200 import ep, lib, synth
+        hidden, inter, experts, shared, topk = 1024, 512, 128, 512, 8
+        w = synth.moe_layer_weights(dev, seed=77, hidden=hidden, inter=inter, experts=experts, shared_inter=shared)
+        for k in ("gate_s", "up_s", "down_s"):
+            w[k] = (w[k].float() * 8).bfloat16()
+        w["router_w"] = (w["router_w"].float() * 20).bfloat16()
+        per = experts // world
+        shard = dict(w)
+        for k in ("gate_w", "gate_s", "up_w", "up_s", "down_w", "down_s"):
+            shard[k] = w[k][rank * per:(rank + 1) * per].contiguous()
+        layer = ep.gpu_layer(shard, experts, topk=topk, max_tokens=64)
+        T = 20 + 13 * rank                                   # ragged across ranks
+        x = synth.activations(T, hidden, dev, 500 + rank)
+        y = layer.forward(x)
+        full = lib.MoeLayer(w, topk=topk, max_tokens=64)
+        ref, ref_ids, _ = full.batched(x, return_routing=True)
+        ids, _ = lib.router(w["router_w"], w["router_bias"], x, topk=topk)
+        same = (ids == ref_ids).all(dim=1)
+        err = (y.float() - ref.float()).abs().amax(dim=1) / ref.float().abs().amax()
+        ok = bool(same.float().mean() > 0.9) and bool((err[same] < 1e-2).all())
+        dist.barrier()
+        q.put((rank, "ok" if ok else "mismatch %.3e" % float(err[same].max()), layer.last_stats))
+        dist.destroy_process_group()
+    except Exception as e:  # report instead of hanging the parent
+        q.put((rank, "error: %r" % (e,), {}))
+
+
+def test_two_rank_expert_parallel_layer_matches_single_gpu():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = {}
+    for _ in range(2):
+        r, status, stats = q.get(timeout=300)
+        res[r] = (status, stats)
+    for p in procs:
+        p.join(timeout=60)
+        if p.is_alive():
+            p.terminate()
+    assert all(v[0] == "ok" for v in res.values()), res
+    assert any(v[1]["remote"] > 0 for v in res.values())
