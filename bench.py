@@ -156,6 +156,92 @@ def cpu_arm(steps, warmup, device):
     return steps / dt, dt, orc.num_threads()
 
 
+def other_workload(a, rank, world, device, steps, warmup):
+    """Configs 2 and 3 through the same timing rules (CUDA events, barrier both sides, max over ranks)."""
+    import torch
+    import torch.distributed as dist
+    from blok_b200 import ep, lib, synth
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    peak, peak_kind = measured_peak()
+    if a.workload.startswith("batched"):
+        T = int(a.workload[len("batched"):])
+        Tl = T // world
+        per = 384 // world
+        # every rank draws the same layer and keeps its shard; two layers are rotated (2 x 9.5 GB / world per GPU)
+        nl = 2
+        shards, reps = [], []
+        for i in range(nl):
+            w = synth.moe_layer_weights(device, seed=2 + 31 * i)
+            if world > 1:
+                for k in ("gate_w", "gate_s", "up_w", "up_s", "down_w", "down_s"):
+                    w[k] = w[k][rank * per:(rank + 1) * per].contiguous()
+                torch.cuda.empty_cache()
+                reps.append(ep.gpu_layer(w, 384, max_tokens=max(Tl, 2)))
+            else:
+                reps.append(lib.MoeLayer(w, max_tokens=max(T, 2)))
+        xs = [synth.activations(Tl, 7168, device, 2 + 7 * i + rank) for i in range(4)]
+        run = (lambda i: reps[i % nl].forward(xs[i % 4])) if world > 1 else (lambda i: reps[i % nl].batched(xs[i % 4]))
+        ids = lib.router(reps[0].layer.weights["router_w"] if world > 1 else reps[0].weights["router_w"],
+                         reps[0].layer.weights["router_bias"] if world > 1 else reps[0].weights["router_bias"], xs[0])[0]
+        mine = (ids.view(torch.int16).long() & 0xFFFF).unique()
+        distinct = int(mine.numel())
+        alg = distinct * 24772608 / world + 5505024 + 88080384 + 4 * Tl * 7168  # per-GPU estimate, own tokens' routing
+        unit_tokens = T
+        workload = "config 2: batched routed-MoE layer, T=%d tokens, %s" % (T, "1 GPU" if world == 1 else "expert parallel x%d, NCCL all-to-all" % world)
+        scaling = "strong"
+        metric = "tok/s, INT4 MoE layer (T=%d)" % T
+    else:
+        ctx = int(a.workload[len("mla"):])
+        layer = lib.MlaLayer(synth.mla_weights(device, seed=3), yarn_factor=32.0, max_batch=8, max_ctx=ctx + 8)
+        ncache = 6 if ctx <= 4096 else 3
+        caches = [synth.latent_cache(8, ctx + 8, device, seed=10 + i + rank) for i in range(ncache)]
+        n = synth.activations(8, 7168, device, 3)
+        ctx_len = torch.full((8,), ctx, dtype=torch.int32, device=device)
+        out = torch.empty((8, 7168), dtype=torch.bfloat16, device=device)
+        run = lambda i: layer.decode(n, caches[i % ncache], ctx_len, out=out)
+        alg = 8 * ctx * 1152 + 202244096
+        unit_tokens = 8 * world
+        workload = "config 3: MLA absorbed decode block, batch 8, ctx %d, bf16 latent cache%s" % (ctx, "" if world == 1 else ", replicas x%d" % world)
+        scaling = "weak"
+        metric = "tok/s, MLA decode block (batch 8, ctx %d)" % ctx
+    for i in range(max(warmup, 3)):
+        run(i)
+    barrier()
+    l0 = lib.kernel_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        run(warmup + i)
+    e1.record()
+    barrier()
+    launches = lib.kernel_launch_count() - l0
+    ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms.item())
+    if rank == 0:
+        per_step = ms / steps
+        achieved = alg / (per_step * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": metric, "value": unit_tokens * steps / (ms / 1e3), "unit": "tok/s", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": per_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": workload, "algorithmic_bytes_per_step_per_gpu": alg,
+                       "l2": "weights and caches rotated over several copies larger than L2"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": peak_kind, "traffic": None},
+            "gpu_launches": int(launches)}))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -164,6 +250,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=3, help="distinct synthetic layers rotated between steps")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="decode", choices=["decode", "batched64", "batched2048", "mla4096", "mla32768"],
+                    help="decode = config 1 (the default, the headline metric); batched* = config 2 (expert parallel "
+                         "when --gpus > 1); mla* = config 3 (attention block, batch 8)")
     a = ap.parse_args()
 
     import torch
@@ -199,6 +288,8 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     lib.load()
+    if a.workload != "decode":
+        return other_workload(a, rank, world, device, steps if a.steps is not None else 20, warmup if a.warmup is not None else 5)
 
     # distinct layers (each 9.5 GB of packed experts + its own router and shared expert)
     layers = [lib.MoeLayer(synth.moe_layer_weights(device, seed=1 + 17 * i + 1000 * rank)) for i in range(a.layers)]

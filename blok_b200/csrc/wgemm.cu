@@ -74,9 +74,24 @@ __global__ void __launch_bounds__(kWgThreads) wgemm_kernel(const WgArgs a) {
   for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
   for (int c0 = 0; c0 < a.K; c0 += kWgChunk) {
+    // INT4: the chunk's weights (4 k-blocks of the lane's two rows) and scales go in flight first; they do not
+    // depend on the activations being staged below
+    uint4 pwl[kWgChunk / 128], pwh[kWgChunk / 128];
+    uint32_t psl[kWgChunk / 128], psh[kWgChunk / 128];
+    if (kI4) {
+#pragma unroll
+      for (int kb = 0; kb < kWgChunk / 128; ++kb) {
+        const int kblock = c0 / 128 + kb;
+        pwl[kb] = ldg_stream(w_lo + (size_t)kblock * 4 + t);
+        pwh[kb] = ldg_stream(w_hi + (size_t)kblock * 4 + t);
+        psl[kb] = s_lo[kblock * 4 + t];
+        psh[kb] = s_hi[kblock * 4 + t];
+      }
+    }
     // ---- stage the tile's activations for columns [c0, c0 + 512): 64 sixteen-byte units per token ----
     for (int u = tid; u < kWgTokens * 64; u += kWgThreads) {
       const int tok = u >> 6, unit = u & 63;
+      if (tok >= 8 * ntiles) break;  // token rows beyond the tile's last 8-token group are never read
       uint4 v = make_uint4(0, 0, 0, 0);
       if (tok < cnt) {
         const int p = p0 + tok;
@@ -101,23 +116,20 @@ __global__ void __launch_bounds__(kWgThreads) wgemm_kernel(const WgArgs a) {
       *reinterpret_cast<uint4 *>(smem + (size_t)tok * kWgTokPitch + dst * 16) = v;
     }
     __syncthreads();
-#pragma unroll 1
+#pragma unroll
     for (int kb = 0; kb < kWgChunk / 128; ++kb) {
       const int kblock = c0 / 128 + kb;
       uint32_t alo[4][4], ahi[4][4];  // [word i][pair j] A-fragment registers of the two rows
       if (kI4) {
-        const uint4 wl = ldg_stream(w_lo + (size_t)kblock * 4 + t);
-        const uint4 wh = ldg_stream(w_hi + (size_t)kblock * 4 + t);
-        const uint32_t sl = s_lo[kblock * 4 + t], sh = s_hi[kblock * 4 + t];
-        const uint32_t sl2 = sl | (sl << 16), sh2 = sh | (sh << 16);
-        dequant_word(wl.x, sl2, alo[0]);
-        dequant_word(wl.y, sl2, alo[1]);
-        dequant_word(wl.z, sl2, alo[2]);
-        dequant_word(wl.w, sl2, alo[3]);
-        dequant_word(wh.x, sh2, ahi[0]);
-        dequant_word(wh.y, sh2, ahi[1]);
-        dequant_word(wh.z, sh2, ahi[2]);
-        dequant_word(wh.w, sh2, ahi[3]);
+        const uint32_t sl2 = psl[kb] | (psl[kb] << 16), sh2 = psh[kb] | (psh[kb] << 16);
+        dequant_word(pwl[kb].x, sl2, alo[0]);
+        dequant_word(pwl[kb].y, sl2, alo[1]);
+        dequant_word(pwl[kb].z, sl2, alo[2]);
+        dequant_word(pwl[kb].w, sl2, alo[3]);
+        dequant_word(pwh[kb].x, sh2, ahi[0]);
+        dequant_word(pwh[kb].y, sh2, ahi[1]);
+        dequant_word(pwh[kb].z, sh2, ahi[2]);
+        dequant_word(pwh[kb].w, sh2, ahi[3]);
       } else {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
