@@ -139,6 +139,8 @@ def cpu_arm(steps, warmup, device):
     from blok_b200 import synth
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import oracle as orc
+    # torchrun exports OMP_NUM_THREADS=1 to its ranks; the CPU arm is meant to use every core this process may run on
+    orc.set_num_threads(len(os.sched_getaffinity(0)))
     # Weights are drawn with the same generator as the GPU arm; only the experts the sampled tokens route to are
     # brought to the host (the full layer is 9.5 GB).
     w = synth.moe_layer_weights(device, seed=1)
@@ -172,17 +174,17 @@ def other_workload(a, rank, world, device, steps, warmup):
     if a.workload.startswith("batched"):
         T = int(a.workload[len("batched"):])
         Tl = T // world
-        per = 384 // world
+        per = a.experts // world
         # every rank draws the same layer and keeps its shard; two layers are rotated (2 x 9.5 GB / world per GPU)
         nl = 2
         shards, reps = [], []
         for i in range(nl):
-            w = synth.moe_layer_weights(device, seed=2 + 31 * i)
+            w = synth.moe_layer_weights(device, seed=2 + 31 * i, experts=a.experts)
             if world > 1:
                 for k in ("gate_w", "gate_s", "up_w", "up_s", "down_w", "down_s"):
                     w[k] = w[k][rank * per:(rank + 1) * per].contiguous()
                 torch.cuda.empty_cache()
-                reps.append(ep.gpu_layer(w, 384, max_tokens=max(Tl, 2)))
+                reps.append(ep.gpu_layer(w, a.experts, max_tokens=max(Tl, 2)))
             else:
                 reps.append(lib.MoeLayer(w, max_tokens=max(T, 2)))
         xs = [synth.activations(Tl, 7168, device, 2 + 7 * i + rank) for i in range(4)]
@@ -194,6 +196,8 @@ def other_workload(a, rank, world, device, steps, warmup):
         alg = distinct * 24772608 / world + 5505024 + 88080384 + 4 * Tl * 7168  # per-GPU estimate, own tokens' routing
         unit_tokens = T
         workload = "config 2: batched routed-MoE layer, T=%d tokens, %s" % (T, "1 GPU" if world == 1 else "expert parallel x%d, NCCL all-to-all" % world)
+        if a.experts != 384:
+            workload = "REDUCED CASE (%d experts, profiler capture size) of " % a.experts + workload
         scaling = "strong"
         metric = "tok/s, INT4 MoE layer (T=%d)" % T
     else:
@@ -250,6 +254,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=3, help="distinct synthetic layers rotated between steps")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--experts", type=int, default=384,
+                    help="routed experts per layer; below 384 the run is a reduced case for profiler captures, "
+                         "not the benchmark configuration, and the line says so")
     ap.add_argument("--workload", default="decode", choices=["decode", "batched64", "batched2048", "mla4096", "mla32768"],
                     help="decode = config 1 (the default, the headline metric); batched* = config 2 (expert parallel "
                          "when --gpus > 1); mla* = config 3 (attention block, batch 8)")
@@ -292,7 +299,8 @@ def main():
         return other_workload(a, rank, world, device, steps if a.steps is not None else 20, warmup if a.warmup is not None else 5)
 
     # distinct layers (each 9.5 GB of packed experts + its own router and shared expert)
-    layers = [lib.MoeLayer(synth.moe_layer_weights(device, seed=1 + 17 * i + 1000 * rank)) for i in range(a.layers)]
+    layers = [lib.MoeLayer(synth.moe_layer_weights(device, seed=1 + 17 * i + 1000 * rank, experts=a.experts))
+              for i in range(a.layers)]
     pool = 64
     xs = synth.activations(pool, 7168, device, 1 + rank)
     y = torch.empty(7168, dtype=torch.bfloat16, device=device)
@@ -358,7 +366,9 @@ def main():
         "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD, "parallelism": "1 GPU" if world == 1 else "replicas x%d" % world,
+        "config": {"workload": WORKLOAD if a.experts == 384 else
+                   "REDUCED CASE (%d experts, profiler capture size) of " % a.experts + WORKLOAD,
+                   "parallelism": "1 GPU" if world == 1 else "replicas x%d" % world,
                    "l2": "rotating %d distinct layers and %d tokens; a step's 292 MB were last read > L2 capacity ago"
                          % (len(layers), pool),
                    "algorithmic_bytes_per_step": alg_bytes},

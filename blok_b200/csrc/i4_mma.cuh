@@ -56,12 +56,12 @@ struct XFragLane {
 
 // Bytes of shared memory needed to stage `cols` columns for a given BATCH.
 __host__ __device__ constexpr size_t i4_stage_bytes(int cols, int batch) {
-  return (size_t)cols * 2 /*xfrag*/ + (size_t)batch * 256 /*zero region*/ + (size_t)(cols / 32) * 4 /*xsum*/;
+  return (size_t)cols * 2 /*xfrag*/ + (size_t)batch * 256 + 64 /*zero region*/ + (size_t)(cols / 32) * 4 /*xsum*/;
 }
 
 struct I4Stage {
   uint4 *xfrag;  // cols/8 uint4
-  uint4 *zero;   // batch*16 uint4
+  uint4 *zero;   // batch*16 + 4 uint4
   float *xsum;   // cols/32 floats
 };
 
@@ -69,7 +69,7 @@ __device__ __forceinline__ I4Stage i4_stage_carve(unsigned char *smem, int cols,
   I4Stage s;
   s.xfrag = reinterpret_cast<uint4 *>(smem);
   s.zero = s.xfrag + cols / 8;
-  s.xsum = reinterpret_cast<float *>(s.zero + batch * 16);
+  s.xsum = reinterpret_cast<float *>(s.zero + batch * 16 + 4);
   return s;
 }
 
@@ -95,7 +95,7 @@ __device__ __forceinline__ void stage_x_i4(const uint4 *x, const I4Stage &st, in
     s += __shfl_xor_sync(0xffffffffu, s, 2);
     if ((u & 3) == 0) st.xsum[u >> 2] = s;
   }
-  for (int u = tid; u < batch * 16; u += nthreads) st.zero[u] = make_uint4(0, 0, 0, 0);
+  for (int u = tid; u < batch * 16 + 4; u += nthreads) st.zero[u] = make_uint4(0, 0, 0, 0);
 }
 
 __device__ __forceinline__ XFragLane xfrag_lane(const I4Stage &st, int lane, int batch) {
@@ -103,7 +103,9 @@ __device__ __forceinline__ XFragLane xfrag_lane(const I4Stage &st, int lane, int
   bool supply = (t == (g & 3));
   XFragLane x;
   (void)batch;
-  x.ptr = (supply ? st.xfrag : st.zero) + t;
+  // The zero lanes read 64 bytes further into their region than the supplying lanes do into a k-block: the fragment
+  // array is a multiple of 128 bytes long, so without the shift both would hit the same banks in every 8-lane phase.
+  x.ptr = supply ? st.xfrag + t : st.zero + 4 + t;
   x.kb_stride = supply ? 16 : 0;
   return x;
 }

@@ -372,8 +372,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
   sp += (size_t)p.hidden * 2;
   uint4 *xfrag = reinterpret_cast<uint4 *>(sp);  // x, INT4 fragment order
   sp += (size_t)p.hidden * 2;
-  uint4 *zero = reinterpret_cast<uint4 *>(sp);  // what the non-supplying lanes of an INT4 mma read
-  sp += 256;
+  // what the non-supplying lanes of an INT4 mma read: 256 bytes, entered 64 bytes in so that they fall on the other
+  // half of the banks than the fragment words the supplying lanes read in the same 8-lane phase
+  uint4 *zero = reinterpret_cast<uint4 *>(sp);
+  sp += 384;
   float *xsum = reinterpret_cast<float *>(sp);
   sp += (size_t)(p.hidden / 32) * 4;
   unsigned char *ring_ptr = sp + (size_t)warp * kRingDepth * kRingStepBytes;  // this warp's weight ring
@@ -405,10 +407,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
 
   const bool supply = (t == (g & 3));
   XFragLane xl_x;  // fragments of x
-  xl_x.ptr = (supply ? xfrag : zero) + t;
+  xl_x.ptr = supply ? xfrag + t : zero + 4 + t;
   xl_x.kb_stride = supply ? 16 : 0;
   XFragLane xl_m;  // fragments of this warp's staged mid
-  xl_m.ptr = (supply ? reinterpret_cast<const uint4 *>(wstage) : zero) + t;
+  xl_m.ptr = supply ? reinterpret_cast<const uint4 *>(wstage) + t : zero + 4 + t;
   xl_m.kb_stride = supply ? 16 : 0;
   float *msum = reinterpret_cast<float *>(wstage + (size_t)p.inter * 2);
 
@@ -731,7 +733,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
 static int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 size_t fused_smem_bytes(const blok_moe_weights &w) {
-  return (size_t)w.hidden * 4 + 256 + (size_t)(w.hidden / 32) * 4 + (size_t)kFusedWarps * kRingDepth * kRingStepBytes +
+  return (size_t)w.hidden * 4 + 384 + (size_t)(w.hidden / 32) * 4 + (size_t)kFusedWarps * kRingDepth * kRingStepBytes +
          (size_t)kFusedWarps * ((size_t)w.inter * 2 + (size_t)(w.inter / 32) * 4) + (size_t)kFusedWarps * 16 * 8 +
          (size_t)w.experts * 2 * sizeof(float);
 }
