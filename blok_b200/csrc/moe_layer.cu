@@ -7,6 +7,7 @@
 
 #include "common.cuh"
 #include "moe_layer.h"
+#include "wgemm.h"
 
 namespace blok {
 
@@ -205,6 +206,12 @@ extern "C" int blok_moe_layer_check(blok_moe_layer_t *L, blok_stream_t stream_) 
   BLOK_REQUIRE(L, BLOK_ERR_ARG, "blok_moe_layer_check: null pointer");
   cudaStream_t stream = (cudaStream_t)stream_;
   BLOK_CUDA(cudaStreamSynchronize(stream));
+  unsigned tc_err = 0;
+  if (int rc = wgemm_tc_take_error(&tc_err)) return rc;
+  if (tc_err) {
+    set_error("blok_moe_batched: a tensor-core GEMM tile gave up waiting for its MMAs");
+    return BLOK_ERR_TIMEOUT;
+  }
   if (!L->f_ctrl) return BLOK_OK;
   unsigned err = 0;
   BLOK_CUDA(cudaMemcpy(&err, L->f_ctrl + 5, sizeof(err), cudaMemcpyDeviceToHost));

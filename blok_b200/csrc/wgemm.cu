@@ -14,6 +14,8 @@
 // multiply on packed bf16 pairs) and reused across the tile's token columns.
 #include "common.cuh"
 #include "wgemm.h"
+#include <cstdlib>
+#include <cstring>
 
 namespace blok {
 
@@ -181,7 +183,16 @@ __global__ void __launch_bounds__(kWgThreads) wgemm_kernel(const WgArgs a) {
 
 size_t wgemm_smem_bytes() { return (size_t)kWgTokens * kWgTokPitch; }
 
+static bool wgemm_force_mma() {
+  static const bool v = [] {
+    const char *e = getenv("BLOK_WGEMM_IMPL");
+    return e && strcmp(e, "mma") == 0;
+  }();
+  return v;
+}
+
 int launch_wgemm(int mode, const WgArgs &args, int max_tiles, cudaStream_t stream) {
+  if (!wgemm_force_mma() && wgemm_tc_supports(mode, args)) return launch_wgemm_tc(mode, args, max_tiles, stream);
   const size_t smem = wgemm_smem_bytes();
   const bool swiglu = mode == WG_BF16_SWIGLU || mode == WG_I4_SWIGLU;
   const int rows_per_cta = swiglu ? 8 * kWgWarps : 16 * kWgWarps;

@@ -28,6 +28,13 @@ struct WgArgs {
   const int *out_index;
 };
 
+// Dispatches to the tcgen05 kernel (wgemm_tc.cu) when it covers the mode and shape, else to the mma.sync kernel;
+// BLOK_WGEMM_IMPL=mma in the environment forces the latter.
 int launch_wgemm(int mode, const WgArgs &args, int max_tiles, cudaStream_t stream);
+
+bool wgemm_tc_supports(int mode, const WgArgs &args);
+int launch_wgemm_tc(int mode, const WgArgs &args, int max_tiles, cudaStream_t stream);
+// *out becomes non-zero if a tcgen05 GEMM CTA has given up on a barrier since the last call (the flag is cleared).
+int wgemm_tc_take_error(unsigned *out);
 
 }  // namespace blok

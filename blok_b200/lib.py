@@ -270,6 +270,10 @@ class MoeLayer:
                                        _stream()))
         return (y, ids, wts) if return_routing else y
 
+    def check(self):
+        """Synchronises the stream and raises if a device-side bounded wait gave up (blok_moe_layer_check)."""
+        _check(load().blok_moe_layer_check(self._handle, _stream()))
+
     def experts_grouped(self, x, expert_local, x_index=None):
         """y[a] = bf16(expert_{expert_local[a]}(x[x_index[a]])) for N assignments (the expert-parallel building block)."""
         N = expert_local.numel()

@@ -29,7 +29,7 @@ def test_moe_batched_vs_oracle(cuda, oracle, T, hidden, inter, experts, shared, 
     layer = lib.MoeLayer(w, max_tokens=max(T, 2))
     x = synth.activations(T, hidden, cuda, seed)
     y, ids, wts = layer.batched(x, return_routing=True)
-    torch.cuda.synchronize()
+    layer.check()  # no tensor-core tile gave up on a barrier
     ids_h = util.ids_np(ids)
     oid, owt, margin, _ = oracle.router(util.t2np_bf16(w["router_w"]), util.t2np_f32(w["router_bias"]), util.t2np_f32(x), mode=0)
     clear = margin > MARGIN
