@@ -8,7 +8,7 @@
 // and up rows of the same indices, or rows r and r + 128 of the down projection).  The
 // weight rows are the M = 128 dimension of tcgen05.mma, the tokens the N dimension, so
 // a weight byte is read from HBM and dequantised once per tile whatever the token
-// count.  Per 64-column step the 128 threads (one weight row each) unpack their packed
+// count.  Per 64-column step the 256 threads (one weight row each) unpack their packed
 // words into shared memory in the K-major core-matrix layout the instruction reads
 // (no swizzle: 8 rows x 16 bytes per core matrix), permute the tile's activations the
 // same way, and one thread issues the MMAs; tcgen05.commit on an mbarrier frees the
@@ -20,17 +20,18 @@
 
 namespace blok {
 
-constexpr int kTcThreads = 128;
+constexpr int kTcThreads = 256;
 constexpr int kTcN = kWgTileTokens;  // token columns of a tile
 constexpr int kTcKC = 64;            // weight columns per pipeline step
 constexpr int kTcStages = 2;
-constexpr int kTcALbo = 2048;        // bytes between core matrices adjacent in K (16 row groups x 128 B)
-constexpr int kTcSbo = 128;          // bytes between 8-row groups
-constexpr int kTcABytes = (kTcKC / 8) * kTcALbo;
+constexpr int kTcSbo = 128;          // bytes between 8-token groups of the activation tile
 constexpr int kTcBLbo = 1040;        // 8 token groups x 128 B, plus 16 B so that the 8 K-slices of a token hit 8 banks
 constexpr int kTcBBytes = (kTcKC / 8) * kTcBLbo;
-constexpr int kTcStageBytes = 2 * kTcABytes + ((kTcBBytes + 127) / 128) * 128;
-constexpr int kTcTmemCols = 2 * kTcN;
+constexpr int kTcStageBytes = ((kTcBBytes + 127) / 128) * 128;  // shared memory per stage: the activation tile only
+constexpr int kTcRing = 6;                       // steps of packed words in flight per CTA (cp.async)
+constexpr int kTcRawBytes = 2 * 256 * 16 + 256 * 4;  // one step: 256 rows x 2 halves x 16 B, and the rows' scale pairs
+constexpr int kTcACols = kTcKC / 2;                       // tensor-memory columns of one 128-row block of one step (2 bf16 per column)
+constexpr int kTcTmemCols = 256;                          // 2 accumulators x 64 columns + 2 stages x 2 blocks x 32 columns of weights
 constexpr unsigned kTcSpinLimit = 1u << 22;
 
 __device__ unsigned g_wgemm_tc_error = 0;
@@ -76,6 +77,28 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t adesc, uint
       : "memory");
 }
 
+// The same with the A operand (128 rows x 16 columns of bf16) taken from tensor memory.
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}\n" ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, "
+      "%19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+      "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+      "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
+      "r"(r[31])
+      : "memory");
+}
+
 __device__ __forceinline__ void tc_commit(uint32_t mbar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
 }
@@ -107,59 +130,69 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "memory");
 }
 
-struct TcPrefetch {
-  uint4 q[2][2];    // [matrix][32-column half] packed words of this thread's row
-  uint32_t sc[2];   // [matrix] the two halves' scales (bf16 pair)
-  uint4 x[4];       // this thread's four 16-byte pieces of the activation tile
-};
+__device__ __forceinline__ void tc_cp_async16(uint32_t dst, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void tc_cp_async4(uint32_t dst, const void *src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
 
 template <bool SWIGLU>
-__global__ void __launch_bounds__(kTcThreads) wgemm_tc_kernel(const WgArgs a) {
+__global__ void __launch_bounds__(kTcThreads, 2) wgemm_tc_kernel(const WgArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) unsigned long long s_mbar[kTcStages];
   __shared__ uint32_t s_tmem_base;
   const int tile = blockIdx.y;
   if (tile >= *a.num_tiles) return;
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int e = a.tile_expert[tile], p0 = a.tile_start[tile], cnt = a.tile_count[tile];
   const int N = max(16, (cnt + 15) & ~15);  // token columns the MMAs cover
 
-  // ---- this thread's weight row in both 128-row blocks ----
+  // ---- this thread's weight row: threads 0..127 unpack block 0 (gate rows / rows r), 128..255 block 1 (up / r + 128) ----
+  const int blk = tid >> 7, r = tid & 127;
   const int rows_per_cta = SWIGLU ? 128 : 256;
   const int row0 = blockIdx.x * rows_per_cta;
-  const size_t r_a = (size_t)e * a.expert_stride_rows + row0 + tid;
-  const size_t r_b = SWIGLU ? r_a : r_a + 128;
   const size_t wrow16 = (size_t)a.K / 32;  // uint4 (= scale groups) per packed row
-  const uint4 *wa = reinterpret_cast<const uint4 *>(a.w_a) + r_a * wrow16;
-  const uint4 *wb = reinterpret_cast<const uint4 *>(SWIGLU ? a.w_b : a.w_a) + r_b * wrow16;
-  const uint32_t *sa = reinterpret_cast<const uint32_t *>(a.s_a + r_a * wrow16);
-  const uint32_t *sb = reinterpret_cast<const uint32_t *>((SWIGLU ? a.s_b : a.s_a) + r_b * wrow16);
-  // ---- this thread's four pieces of the activation tile: token (tid / 8) + 16 i, K-slice tid % 8 ----
+  const size_t grow = (size_t)e * a.expert_stride_rows + row0 + r + ((!SWIGLU && blk) ? 128 : 0);
+  const uint4 *wsrc = reinterpret_cast<const uint4 *>((SWIGLU && blk) ? a.w_b : a.w_a) + grow * wrow16;
+  const uint32_t *ssrc = reinterpret_cast<const uint32_t *>(((SWIGLU && blk) ? a.s_b : a.s_a) + grow * wrow16);
+  // ---- this thread's two pieces of the activation tile: token (tid / 8) + 32 i, K-slice tid % 8 ----
   const int ki = tid & 7;
-  const uint4 *xp[4];
+  const uint4 *xp[2];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int tok = (tid >> 3) + 16 * i;
+  for (int i = 0; i < 2; ++i) {
+    const int tok = (tid >> 3) + 32 * i;
     xp[i] = nullptr;
     if (tok < cnt) {
       const size_t xr = a.x_index ? (size_t)a.x_index[p0 + tok] : (size_t)(p0 + tok);
       xp[i] = reinterpret_cast<const uint4 *>(a.x + xr * a.K) + ki;
     }
   }
-  auto prefetch = [&](int c, TcPrefetch &pf) {
-    pf.q[0][0] = ldg_stream(wa + 2 * c);
-    pf.q[0][1] = ldg_stream(wa + 2 * c + 1);
-    pf.q[1][0] = ldg_stream(wb + 2 * c);
-    pf.q[1][1] = ldg_stream(wb + 2 * c + 1);
-    pf.sc[0] = __ldg(sa + c);
-    pf.sc[1] = __ldg(sb + c);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) pf.x[i] = xp[i] ? __ldg(xp[i] + (size_t)c * (kTcKC / 8)) : make_uint4(0, 0, 0, 0);
+  // Packed words and scales travel through a cp.async ring of kTcRing steps: every thread copies its own row's 32
+  // bytes per step and reads the same bytes back, so the ring needs no barrier.  The activations (L2 resident,
+  // shared by all row blocks of the expert) are fetched one step ahead into registers.
+  const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(smem);
+  const uint32_t raw0 = sbase + kTcStages * kTcStageBytes;
+  const unsigned char *rawp = smem + kTcStages * kTcStageBytes;
+  const int nchunks = a.K / kTcKC;
+  auto issue = [&](int c) {
+    if (c < nchunks) {
+      const uint32_t slot = raw0 + (uint32_t)(c % kTcRing) * kTcRawBytes;
+      tc_cp_async16(slot + (0 * kTcThreads + tid) * 16, wsrc + 2 * c);
+      tc_cp_async16(slot + (1 * kTcThreads + tid) * 16, wsrc + 2 * c + 1);
+      tc_cp_async4(slot + 2 * kTcThreads * 16 + tid * 4, ssrc + c);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
   };
+  auto fetch_x = [&](int c, uint4 (&xv)[2]) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) xv[i] = xp[i] ? __ldg(xp[i] + (size_t)c * (kTcKC / 8)) : make_uint4(0, 0, 0, 0);
+  };
+#pragma unroll
+  for (int c = 0; c < kTcRing - 1; ++c) issue(c);
 
   // ---- barriers and tensor memory ----
   const uint32_t mbar0 = (uint32_t)__cvta_generic_to_shared(&s_mbar[0]);
-  const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(smem);
   if (tid == 0) {
 #pragma unroll
     for (int s = 0; s < kTcStages; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(mbar0 + 8 * s) : "memory");
@@ -171,74 +204,86 @@ __global__ void __launch_bounds__(kTcThreads) wgemm_tc_kernel(const WgArgs a) {
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  TcPrefetch pf;
-  prefetch(0, pf);
+  uint4 xnext[2];
+  fetch_x(0, xnext);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = s_tmem_base;
   const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((128u >> 4) << 24);
 
-  const int nchunks = a.K / kTcKC;
   bool failed = false;
   for (int c = 0; c < nchunks; ++c) {
-    const TcPrefetch cur = pf;
-    if (c + 1 < nchunks) prefetch(c + 1, pf);
+    issue(c + kTcRing - 1);
+    uint4 xcur[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) xcur[i] = xnext[i];
+    if (c + 1 < nchunks) fetch_x(c + 1, xnext);
     const int s = c % kTcStages;
-    // the MMAs that read this stage two steps ago must be done with it
+    // the MMAs that read this stage kTcStages steps ago must be done with it
     bool ok = true;
     if (c >= kTcStages) ok = tc_mbar_wait(mbar0 + 8 * s, (uint32_t)((c / kTcStages - 1) & 1));
     if (__syncthreads_or(!ok)) {
       failed = true;
       break;
     }
-    unsigned char *A0 = smem + (size_t)s * kTcStageBytes;
-    unsigned char *A1 = A0 + kTcABytes;
-    unsigned char *B = A1 + kTcABytes;
-    const int rowoff = (tid >> 3) * kTcSbo + (tid & 7) * 16;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    unsigned char *B = smem + (size_t)s * kTcStageBytes;
+    asm volatile("cp.async.wait_group %0;" ::"n"(kTcRing - 1) : "memory");  // this step's own words have landed
+    const unsigned char *raw = rawp + (size_t)(c % kTcRing) * kTcRawBytes;
+    const uint32_t scm = *reinterpret_cast<const uint32_t *>(raw + 2 * kTcThreads * 16 + tid * 4);
+    // The row's 64 dequantised weights of this step go to tensor memory as the MMA's A operand: lane = row, two
+    // bf16 per 32-bit column, 8 columns per K = 16 step (column pairs in the order 0 4 1 5 2 6 3 7 of each word).
+    uint32_t av[32];
 #pragma unroll
-    for (int m = 0; m < 2; ++m) {
-      unsigned char *A = m ? A1 : A0;
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t s2 = __byte_perm(scm, scm, h ? 0x3232 : 0x1010);
+      const uint4 q = *reinterpret_cast<const uint4 *>(raw + (h * kTcThreads + tid) * 16);
+      const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const uint32_t s2 = __byte_perm(cur.sc[m], cur.sc[m], h ? 0x3232 : 0x1010);
-        const uint4 q = cur.q[m][h];
-        *reinterpret_cast<uint4 *>(A + (h * 4 + 0) * kTcALbo + rowoff) = tc_dequant_word(q.x, s2);
-        *reinterpret_cast<uint4 *>(A + (h * 4 + 1) * kTcALbo + rowoff) = tc_dequant_word(q.y, s2);
-        *reinterpret_cast<uint4 *>(A + (h * 4 + 2) * kTcALbo + rowoff) = tc_dequant_word(q.z, s2);
-        *reinterpret_cast<uint4 *>(A + (h * 4 + 3) * kTcALbo + rowoff) = tc_dequant_word(q.w, s2);
+      for (int w = 0; w < 4; ++w) {
+        const uint4 d = tc_dequant_word(qw[w], s2);
+        av[(h * 4 + w) * 4 + 0] = d.x;
+        av[(h * 4 + w) * 4 + 1] = d.y;
+        av[(h * 4 + w) * 4 + 2] = d.z;
+        av[(h * 4 + w) * 4 + 3] = d.w;
       }
     }
+    tc_st32(tmem + ((uint32_t)(32 * (warp & 3)) << 16) + 2 * kTcN + (uint32_t)(s * 2 + blk) * kTcACols, av);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      if (16 * i < N) {
-        const uint4 v = cur.x[i];
+    for (int i = 0; i < 2; ++i) {
+      if (32 * i < N) {
+        const uint4 v = xcur[i];
         uint4 o;  // columns 0 4 1 5 2 6 3 7, as the weights
         o.x = __byte_perm(v.x, v.z, 0x5410);
         o.y = __byte_perm(v.x, v.z, 0x7632);
         o.z = __byte_perm(v.y, v.w, 0x5410);
         o.w = __byte_perm(v.y, v.w, 0x7632);
-        const int tok = (tid >> 3) + 16 * i;
+        const int tok = (tid >> 3) + 32 * i;
         *reinterpret_cast<uint4 *>(B + ki * kTcBLbo + (tok >> 3) * kTcSbo + (tok & 7) * 16) = o;
       }
     }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the stores above are read by the tensor core's proxy
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the activation tile is read by the tensor core's proxy
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (tid == 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t a0 = sbase + (uint32_t)s * kTcStageBytes, a1 = a0 + kTcABytes, b = a1 + kTcABytes;
+      const uint32_t b = sbase + (uint32_t)s * kTcStageBytes;
+      const uint32_t ta = tmem + 2 * kTcN + (uint32_t)(s * 2) * kTcACols;
 #pragma unroll
       for (int j = 0; j < kTcKC / 16; ++j) {
         const uint32_t acc = (c > 0 || j > 0) ? 1u : 0u;
         const uint64_t bd = tc_smem_desc(b + j * 2 * kTcBLbo, kTcBLbo, kTcSbo);
-        tc_mma_f16(tmem, tc_smem_desc(a0 + j * 2 * kTcALbo, kTcALbo, kTcSbo), bd, idesc, acc);
-        tc_mma_f16(tmem + kTcN, tc_smem_desc(a1 + j * 2 * kTcALbo, kTcALbo, kTcSbo), bd, idesc, acc);
+        tc_mma_f16_ts(tmem, ta + 8 * j, bd, idesc, acc);
+        tc_mma_f16_ts(tmem + kTcN, ta + kTcACols + 8 * j, bd, idesc, acc);
       }
       tc_commit(mbar0 + 8 * s);
     }
   }
 
-  // ---- epilogue: thread tid holds accumulator row tid of both blocks (tensor-memory lane tid) ----
+  // ---- epilogue: lane l of warp w holds accumulator row 32 (w % 4) + l of both blocks (tensor-memory lane);
+  //      warps 0..3 take the even 16-token column blocks, warps 4..7 the odd ones ----
   if (!failed) {
     const int last = nchunks - 1;
     const bool ok = tc_mbar_wait(mbar0 + 8 * (last % kTcStages), (uint32_t)((last / kTcStages) & 1));
@@ -246,8 +291,9 @@ __global__ void __launch_bounds__(kTcThreads) wgemm_tc_kernel(const WgArgs a) {
   }
   if (!failed) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
-    for (int n0 = 0; n0 < N; n0 += 16) {
+    const int lg = warp & 3, row = 32 * lg + lane;
+    const uint32_t trow = tmem + ((uint32_t)(32 * lg) << 16);
+    for (int n0 = 16 * (warp >> 2); n0 < N; n0 += 32) {
       uint32_t ra[16], rb[16];
       tc_ld16(trow + n0, ra);
       tc_ld16(trow + kTcN + n0, rb);
@@ -261,13 +307,13 @@ __global__ void __launch_bounds__(kTcThreads) wgemm_tc_kernel(const WgArgs a) {
           if (SWIGLU) {
             const float gv = round_bf16(va), uv = round_bf16(vb);
             const float m = round_bf16(round_bf16(gv / (1.0f + expf(-gv))) * uv);
-            a.out_bf16[p * a.R + row0 + tid] = f32_to_bf16_bits(m);
+            a.out_bf16[p * a.R + row0 + row] = f32_to_bf16_bits(m);
           } else if (a.out_f32) {
-            a.out_f32[p * a.R + row0 + tid] = va;
-            a.out_f32[p * a.R + row0 + 128 + tid] = vb;
+            a.out_f32[p * a.R + row0 + row] = va;
+            a.out_f32[p * a.R + row0 + 128 + row] = vb;
           } else {
-            a.out_bf16[p * a.R + row0 + tid] = f32_to_bf16_bits(va);
-            a.out_bf16[p * a.R + row0 + 128 + tid] = f32_to_bf16_bits(vb);
+            a.out_bf16[p * a.R + row0 + row] = f32_to_bf16_bits(va);
+            a.out_bf16[p * a.R + row0 + 128 + row] = f32_to_bf16_bits(vb);
           }
         }
       }
@@ -281,7 +327,7 @@ __global__ void __launch_bounds__(kTcThreads) wgemm_tc_kernel(const WgArgs a) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)kTcTmemCols) : "memory");
 }
 
-size_t wgemm_tc_smem_bytes() { return (size_t)kTcStages * kTcStageBytes; }
+size_t wgemm_tc_smem_bytes() { return (size_t)kTcStages * kTcStageBytes + (size_t)kTcRing * kTcRawBytes; }
 
 // True when the tcgen05 kernel covers this mode and shape.
 bool wgemm_tc_supports(int mode, const WgArgs &args) {
