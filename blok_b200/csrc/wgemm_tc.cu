@@ -20,7 +20,8 @@
 
 namespace blok {
 
-constexpr int kTcThreads = 256;
+constexpr int kTcProducers = 256;    // threads that unpack weights: one weight row each
+constexpr int kTcThreads = kTcProducers + 32;  // plus one warp whose first lane issues the MMAs
 constexpr int kTcN = kWgTileTokens;  // token columns of a tile
 constexpr int kTcKC = 64;            // weight columns per pipeline step
 constexpr int kTcStages = 2;
@@ -29,7 +30,7 @@ constexpr int kTcBLbo = 1040;        // 8 token groups x 128 B, plus 16 B so tha
 constexpr int kTcBBytes = (kTcKC / 8) * kTcBLbo;
 constexpr int kTcStageBytes = ((kTcBBytes + 127) / 128) * 128;  // shared memory per stage: the activation tile only
 constexpr int kTcRing = 6;                       // steps of packed words in flight per CTA (cp.async)
-constexpr int kTcRawBytes = 2 * 256 * 16 + 256 * 4;  // one step: 256 rows x 2 halves x 16 B, and the rows' scale pairs
+constexpr int kTcRawBytes = 2 * kTcProducers * 16 + kTcProducers * 4;  // one step: 256 rows x 2 halves x 16 B, and the rows' scale pairs
 constexpr int kTcACols = kTcKC / 2;                       // tensor-memory columns of one 128-row block of one step (2 bf16 per column)
 constexpr int kTcTmemCols = 256;                          // 2 accumulators x 64 columns + 2 stages x 2 blocks x 32 columns of weights
 constexpr unsigned kTcSpinLimit = 1u << 22;
@@ -140,7 +141,7 @@ __device__ __forceinline__ void tc_cp_async4(uint32_t dst, const void *src) {
 template <bool SWIGLU>
 __global__ void __launch_bounds__(kTcThreads, 2) wgemm_tc_kernel(const WgArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ __align__(8) unsigned long long s_mbar[kTcStages];
+  __shared__ __align__(8) unsigned long long s_mbar[2 * kTcStages];
   __shared__ uint32_t s_tmem_base;
   const int tile = blockIdx.y;
   if (tile >= *a.num_tiles) return;
@@ -175,12 +176,13 @@ __global__ void __launch_bounds__(kTcThreads, 2) wgemm_tc_kernel(const WgArgs a)
   const uint32_t raw0 = sbase + kTcStages * kTcStageBytes;
   const unsigned char *rawp = smem + kTcStages * kTcStageBytes;
   const int nchunks = a.K / kTcKC;
+  const bool producer = tid < kTcProducers;
   auto issue = [&](int c) {
     if (c < nchunks) {
       const uint32_t slot = raw0 + (uint32_t)(c % kTcRing) * kTcRawBytes;
-      tc_cp_async16(slot + (0 * kTcThreads + tid) * 16, wsrc + 2 * c);
-      tc_cp_async16(slot + (1 * kTcThreads + tid) * 16, wsrc + 2 * c + 1);
-      tc_cp_async4(slot + 2 * kTcThreads * 16 + tid * 4, ssrc + c);
+      tc_cp_async16(slot + (0 * kTcProducers + tid) * 16, wsrc + 2 * c);
+      tc_cp_async16(slot + (1 * kTcProducers + tid) * 16, wsrc + 2 * c + 1);
+      tc_cp_async4(slot + 2 * kTcProducers * 16 + tid * 4, ssrc + c);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -188,14 +190,20 @@ __global__ void __launch_bounds__(kTcThreads, 2) wgemm_tc_kernel(const WgArgs a)
 #pragma unroll
     for (int i = 0; i < 2; ++i) xv[i] = xp[i] ? __ldg(xp[i] + (size_t)c * (kTcKC / 8)) : make_uint4(0, 0, 0, 0);
   };
+  if (producer) {
 #pragma unroll
-  for (int c = 0; c < kTcRing - 1; ++c) issue(c);
+    for (int c = 0; c < kTcRing - 1; ++c) issue(c);
+  }
 
-  // ---- barriers and tensor memory ----
-  const uint32_t mbar0 = (uint32_t)__cvta_generic_to_shared(&s_mbar[0]);
+  // ---- barriers and tensor memory: full[s] counts the 8 producer warps, empty[s] the MMAs' commit ----
+  const uint32_t mbar_full = (uint32_t)__cvta_generic_to_shared(&s_mbar[0]);
+  const uint32_t mbar_empty = mbar_full + 8 * kTcStages;
   if (tid == 0) {
 #pragma unroll
-    for (int s = 0; s < kTcStages; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(mbar0 + 8 * s) : "memory");
+    for (int s = 0; s < kTcStages; ++s) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar_full + 8 * s), "r"(kTcProducers / 32) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(mbar_empty + 8 * s) : "memory");
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
@@ -205,7 +213,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) wgemm_tc_kernel(const WgArgs a)
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   uint4 xnext[2];
-  fetch_x(0, xnext);
+  if (producer) fetch_x(0, xnext);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -213,61 +221,74 @@ __global__ void __launch_bounds__(kTcThreads, 2) wgemm_tc_kernel(const WgArgs a)
   const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((128u >> 4) << 24);
 
   bool failed = false;
-  for (int c = 0; c < nchunks; ++c) {
-    issue(c + kTcRing - 1);
-    uint4 xcur[2];
+  if (producer) {
+    // ---- producers: unpack step c into stage c % 2 as soon as the MMAs of step c - 2 have released it ----
+    for (int c = 0; c < nchunks; ++c) {
+      issue(c + kTcRing - 1);
+      uint4 xcur[2];
 #pragma unroll
-    for (int i = 0; i < 2; ++i) xcur[i] = xnext[i];
-    if (c + 1 < nchunks) fetch_x(c + 1, xnext);
-    const int s = c % kTcStages;
-    // the MMAs that read this stage kTcStages steps ago must be done with it
-    bool ok = true;
-    if (c >= kTcStages) ok = tc_mbar_wait(mbar0 + 8 * s, (uint32_t)((c / kTcStages - 1) & 1));
-    if (__syncthreads_or(!ok)) {
-      failed = true;
-      break;
-    }
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    unsigned char *B = smem + (size_t)s * kTcStageBytes;
-    asm volatile("cp.async.wait_group %0;" ::"n"(kTcRing - 1) : "memory");  // this step's own words have landed
-    const unsigned char *raw = rawp + (size_t)(c % kTcRing) * kTcRawBytes;
-    const uint32_t scm = *reinterpret_cast<const uint32_t *>(raw + 2 * kTcThreads * 16 + tid * 4);
-    // The row's 64 dequantised weights of this step go to tensor memory as the MMA's A operand: lane = row, two
-    // bf16 per 32-bit column, 8 columns per K = 16 step (column pairs in the order 0 4 1 5 2 6 3 7 of each word).
-    uint32_t av[32];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const uint32_t s2 = __byte_perm(scm, scm, h ? 0x3232 : 0x1010);
-      const uint4 q = *reinterpret_cast<const uint4 *>(raw + (h * kTcThreads + tid) * 16);
-      const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const uint4 d = tc_dequant_word(qw[w], s2);
-        av[(h * 4 + w) * 4 + 0] = d.x;
-        av[(h * 4 + w) * 4 + 1] = d.y;
-        av[(h * 4 + w) * 4 + 2] = d.z;
-        av[(h * 4 + w) * 4 + 3] = d.w;
+      for (int i = 0; i < 2; ++i) xcur[i] = xnext[i];
+      if (c + 1 < nchunks) fetch_x(c + 1, xnext);
+      const int s = c % kTcStages;
+      if (c >= kTcStages && !tc_mbar_wait(mbar_empty + 8 * s, (uint32_t)((c / kTcStages - 1) & 1))) {
+        failed = true;
+        break;
       }
-    }
-    tc_st32(tmem + ((uint32_t)(32 * (warp & 3)) << 16) + 2 * kTcN + (uint32_t)(s * 2 + blk) * kTcACols, av);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      unsigned char *B = smem + (size_t)s * kTcStageBytes;
+      asm volatile("cp.async.wait_group %0;" ::"n"(kTcRing - 1) : "memory");  // this step's own words have landed
+      const unsigned char *raw = rawp + (size_t)(c % kTcRing) * kTcRawBytes;
+      const uint32_t scm = *reinterpret_cast<const uint32_t *>(raw + 2 * kTcProducers * 16 + tid * 4);
+      // The row's 64 dequantised weights of this step go to tensor memory as the MMA's A operand: lane = row, two
+      // bf16 per 32-bit column, 8 columns per K = 16 step (column pairs in the order 0 4 1 5 2 6 3 7 of each word).
+      uint32_t av[32];
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      if (32 * i < N) {
-        const uint4 v = xcur[i];
-        uint4 o;  // columns 0 4 1 5 2 6 3 7, as the weights
-        o.x = __byte_perm(v.x, v.z, 0x5410);
-        o.y = __byte_perm(v.x, v.z, 0x7632);
-        o.z = __byte_perm(v.y, v.w, 0x5410);
-        o.w = __byte_perm(v.y, v.w, 0x7632);
-        const int tok = (tid >> 3) + 32 * i;
-        *reinterpret_cast<uint4 *>(B + ki * kTcBLbo + (tok >> 3) * kTcSbo + (tok & 7) * 16) = o;
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t s2 = __byte_perm(scm, scm, h ? 0x3232 : 0x1010);
+        const uint4 q = *reinterpret_cast<const uint4 *>(raw + (h * kTcProducers + tid) * 16);
+        const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const uint4 d = tc_dequant_word(qw[w], s2);
+          av[(h * 4 + w) * 4 + 0] = d.x;
+          av[(h * 4 + w) * 4 + 1] = d.y;
+          av[(h * 4 + w) * 4 + 2] = d.z;
+          av[(h * 4 + w) * 4 + 3] = d.w;
+        }
       }
+      tc_st32(tmem + ((uint32_t)(32 * (warp & 3)) << 16) + 2 * kTcN + (uint32_t)(s * 2 + blk) * kTcACols, av);
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        if (32 * i < N) {
+          const uint4 v = xcur[i];
+          uint4 o;  // columns 0 4 1 5 2 6 3 7, as the weights
+          o.x = __byte_perm(v.x, v.z, 0x5410);
+          o.y = __byte_perm(v.x, v.z, 0x7632);
+          o.z = __byte_perm(v.y, v.w, 0x5410);
+          o.w = __byte_perm(v.y, v.w, 0x7632);
+          const int tok = (tid >> 3) + 32 * i;
+          *reinterpret_cast<uint4 *>(B + ki * kTcBLbo + (tok >> 3) * kTcSbo + (tok & 7) * 16) = o;
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the activation tile is read by the tensor core's proxy
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mbar_full + 8 * s) : "memory");
     }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the activation tile is read by the tensor core's proxy
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (tid == 0) {
+    // all MMAs have completed once the last step's commit has arrived
+    if (!failed) {
+      const int last = nchunks - 1;
+      failed = !tc_mbar_wait(mbar_empty + 8 * (last % kTcStages), (uint32_t)((last / kTcStages) & 1));
+    }
+  } else if (lane == 0) {
+    // ---- the MMA thread: 4 K = 16 steps x 2 row blocks per stage, then the commit that releases the stage ----
+    for (int c = 0; c < nchunks; ++c) {
+      const int s = c % kTcStages;
+      if (!tc_mbar_wait(mbar_full + 8 * s, (uint32_t)((c / kTcStages) & 1))) {
+        failed = true;
+        break;
+      }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t b = sbase + (uint32_t)s * kTcStageBytes;
       const uint32_t ta = tmem + 2 * kTcN + (uint32_t)(s * 2) * kTcACols;
@@ -278,18 +299,15 @@ __global__ void __launch_bounds__(kTcThreads, 2) wgemm_tc_kernel(const WgArgs a)
         tc_mma_f16_ts(tmem, ta + 8 * j, bd, idesc, acc);
         tc_mma_f16_ts(tmem + kTcN, ta + kTcACols + 8 * j, bd, idesc, acc);
       }
-      tc_commit(mbar0 + 8 * s);
+      tc_commit(mbar_empty + 8 * s);
     }
   }
+  failed = __any_sync(0xffffffffu, failed);  // warp-uniform: the tensor-memory loads below are warp-wide
+  if (failed && lane == 0) atomicExch(&g_wgemm_tc_error, 1u);
 
-  // ---- epilogue: lane l of warp w holds accumulator row 32 (w % 4) + l of both blocks (tensor-memory lane);
+  // ---- epilogue: lane l of producer warp w holds accumulator row 32 (w % 4) + l of both blocks (tensor-memory lane);
   //      warps 0..3 take the even 16-token column blocks, warps 4..7 the odd ones ----
-  if (!failed) {
-    const int last = nchunks - 1;
-    const bool ok = tc_mbar_wait(mbar0 + 8 * (last % kTcStages), (uint32_t)((last / kTcStages) & 1));
-    if (__syncthreads_or(!ok)) failed = true;
-  }
-  if (!failed) {
+  if (producer && !failed) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int lg = warp & 3, row = 32 * lg + lane;
     const uint32_t trow = tmem + ((uint32_t)(32 * lg) << 16);
@@ -318,8 +336,6 @@ __global__ void __launch_bounds__(kTcThreads, 2) wgemm_tc_kernel(const WgArgs a)
         }
       }
     }
-  } else if (tid == 0) {
-    atomicExch(&g_wgemm_tc_error, 1u);
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
