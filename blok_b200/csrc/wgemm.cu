@@ -183,16 +183,19 @@ __global__ void __launch_bounds__(kWgThreads) wgemm_kernel(const WgArgs a) {
 
 size_t wgemm_smem_bytes() { return (size_t)kWgTokens * kWgTokPitch; }
 
-static bool wgemm_force_mma() {
-  static const bool v = [] {
-    const char *e = getenv("BLOK_WGEMM_IMPL");
-    return e && strcmp(e, "mma") == 0;
-  }();
-  return v;
+// 0 = pick by size, 1 = mma.sync kernel always, 2 = tcgen05 kernels wherever they apply
+static int wgemm_forced_impl() {  // read at every launch, so that a test can switch it inside one process
+  const char *e = getenv("BLOK_WGEMM_IMPL");
+  if (e && strcmp(e, "mma") == 0) return 1;
+  if (e && strcmp(e, "tc") == 0) return 2;
+  return 0;
 }
 
 int launch_wgemm(int mode, const WgArgs &args, int max_tiles, cudaStream_t stream) {
-  if (!wgemm_force_mma() && wgemm_tc_supports(mode, args)) return launch_wgemm_tc(mode, args, max_tiles, stream);
+  const int forced = wgemm_forced_impl();
+  const bool i4 = mode == WG_I4_SWIGLU || mode == WG_I4_PLAIN;
+  const bool enough = args.n_rows >= (i4 ? 2048 : 512);
+  if (forced != 1 && (forced == 2 || enough) && wgemm_tc_supports(mode, args)) return launch_wgemm_tc(mode, args, max_tiles, stream);
   const size_t smem = wgemm_smem_bytes();
   const bool swiglu = mode == WG_BF16_SWIGLU || mode == WG_I4_SWIGLU;
   const int rows_per_cta = swiglu ? 8 * kWgWarps : 16 * kWgWarps;

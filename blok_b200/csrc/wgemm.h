@@ -26,10 +26,12 @@ struct WgArgs {
   const int *tile_count;
   const int *num_tiles;
   const int *out_index;
+  int n_rows = 0;  // rows of x the launch covers (tokens, or token-expert assignments): picks the kernel
 };
 
-// Dispatches to the tcgen05 kernel (wgemm_tc.cu) when it covers the mode and shape, else to the mma.sync kernel;
-// BLOK_WGEMM_IMPL=mma in the environment forces the latter.
+// Dispatches to the tcgen05 kernels (wgemm_tc.cu) when they cover the mode and shape and the launch has enough rows
+// of x for the tensor cores to matter (INT4: 2048 assignments, bf16: 512 tokens), else to the mma.sync kernel,
+// which streams the weights better at small counts.  BLOK_WGEMM_IMPL=mma / =tc in the environment forces one.
 int launch_wgemm(int mode, const WgArgs &args, int max_tiles, cudaStream_t stream);
 
 bool wgemm_tc_supports(int mode, const WgArgs &args);

@@ -138,6 +138,40 @@ __device__ __forceinline__ void tc_cp_async4(uint32_t dst, const void *src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
 
+// Epilogue of a tile: lane l of warp w (8 warps) holds accumulator row 32 (w % 4) + l of both row blocks (its
+// tensor-memory lane); warps 0..3 take the even 16-token column blocks, warps 4..7 the odd ones.
+template <bool SWIGLU>
+__device__ __forceinline__ void tc_epilogue(const WgArgs &a, uint32_t tmem, int warp, int lane, int N, int cnt, int p0, int row0) {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const int lg = warp & 3, row = 32 * lg + lane;
+  const uint32_t trow = tmem + ((uint32_t)(32 * lg) << 16);
+  for (int n0 = 16 * (warp >> 2); n0 < N; n0 += 32) {
+    uint32_t ra[16], rb[16];
+    tc_ld16(trow + n0, ra);
+    tc_ld16(trow + kTcN + n0, rb);
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int tok = n0 + j;
+      if (tok < cnt) {
+        const size_t p = a.out_index ? (size_t)a.out_index[p0 + tok] : (size_t)(p0 + tok);
+        const float va = __uint_as_float(ra[j]), vb = __uint_as_float(rb[j]);
+        if (SWIGLU) {
+          const float gv = round_bf16(va), uv = round_bf16(vb);
+          const float m = round_bf16(round_bf16(gv / (1.0f + expf(-gv))) * uv);
+          a.out_bf16[p * a.R + row0 + row] = f32_to_bf16_bits(m);
+        } else if (a.out_f32) {
+          a.out_f32[p * a.R + row0 + row] = va;
+          a.out_f32[p * a.R + row0 + 128 + row] = vb;
+        } else {
+          a.out_bf16[p * a.R + row0 + row] = f32_to_bf16_bits(va);
+          a.out_bf16[p * a.R + row0 + 128 + row] = f32_to_bf16_bits(vb);
+        }
+      }
+    }
+  }
+}
+
 template <bool SWIGLU>
 __global__ void __launch_bounds__(kTcThreads, 2) wgemm_tc_kernel(const WgArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
@@ -305,57 +339,180 @@ __global__ void __launch_bounds__(kTcThreads, 2) wgemm_tc_kernel(const WgArgs a)
   failed = __any_sync(0xffffffffu, failed);  // warp-uniform: the tensor-memory loads below are warp-wide
   if (failed && lane == 0) atomicExch(&g_wgemm_tc_error, 1u);
 
-  // ---- epilogue: lane l of producer warp w holds accumulator row 32 (w % 4) + l of both blocks (tensor-memory lane);
-  //      warps 0..3 take the even 16-token column blocks, warps 4..7 the odd ones ----
-  if (producer && !failed) {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const int lg = warp & 3, row = 32 * lg + lane;
-    const uint32_t trow = tmem + ((uint32_t)(32 * lg) << 16);
-    for (int n0 = 16 * (warp >> 2); n0 < N; n0 += 32) {
-      uint32_t ra[16], rb[16];
-      tc_ld16(trow + n0, ra);
-      tc_ld16(trow + kTcN + n0, rb);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const int tok = n0 + j;
-        if (tok < cnt) {
-          const size_t p = a.out_index ? (size_t)a.out_index[p0 + tok] : (size_t)(p0 + tok);
-          const float va = __uint_as_float(ra[j]), vb = __uint_as_float(rb[j]);
-          if (SWIGLU) {
-            const float gv = round_bf16(va), uv = round_bf16(vb);
-            const float m = round_bf16(round_bf16(gv / (1.0f + expf(-gv))) * uv);
-            a.out_bf16[p * a.R + row0 + row] = f32_to_bf16_bits(m);
-          } else if (a.out_f32) {
-            a.out_f32[p * a.R + row0 + row] = va;
-            a.out_f32[p * a.R + row0 + 128 + row] = vb;
-          } else {
-            a.out_bf16[p * a.R + row0 + row] = f32_to_bf16_bits(va);
-            a.out_bf16[p * a.R + row0 + 128 + row] = f32_to_bf16_bits(vb);
-          }
-        }
-      }
-    }
-  }
+  if (producer && !failed) tc_epilogue<SWIGLU>(a, tmem, warp, lane, N, cnt, p0, row0);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 0)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)kTcTmemCols) : "memory");
 }
 
+// ---- bf16 weights (shared expert): both operands come straight from global memory into the core-matrix layout
+// with 16-byte cp.async copies, one per (row, 8-column slice); no registers, no permutation.  kBfStages steps of
+// 2 x 128 weight rows + the token tile are in flight per CTA. ----
+constexpr int kBfStages = 4;
+constexpr int kBfALbo = 2048 + 16;   // + 16 B: the 8 K-slices of a row, copied by 8 neighbouring lanes, hit 8 banks
+constexpr int kBfABytes = (kTcKC / 8) * kBfALbo;
+constexpr int kBfStageBytes = ((2 * kBfABytes + kTcBBytes + 127) / 128) * 128;
+constexpr int kBfTmemCols = 2 * kTcN;
+
+__device__ __forceinline__ void tc_cp_async16_zfill(uint32_t dst, const void *src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+
+template <bool SWIGLU>
+__global__ void __launch_bounds__(kTcThreads, 1) wgemm_tc_bf16_kernel(const WgArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) unsigned long long s_mbar[2 * kBfStages];
+  __shared__ uint32_t s_tmem_base;
+  const int tile = blockIdx.y;
+  if (tile >= *a.num_tiles) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int e = a.tile_expert[tile], p0 = a.tile_start[tile], cnt = a.tile_count[tile];
+  const int N = max(16, (cnt + 15) & ~15);
+  const int rows_per_cta = SWIGLU ? 128 : 256;
+  const int row0 = blockIdx.x * rows_per_cta;
+  const bool producer = tid < kTcProducers;
+  const int nchunks = a.K / kTcKC;
+  const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(smem);
+
+  // this thread's pieces: weight rows (tid / 8) + 32 i of both blocks (i < 4), tokens (tid / 8) + 32 i (i < 2), K-slice tid % 8
+  const int ki = tid & 7, r0 = tid >> 3;
+  const size_t rowbytes = (size_t)a.K * 2;
+  const unsigned char *wa = reinterpret_cast<const unsigned char *>(a.w_a) + ((size_t)e * a.expert_stride_rows + row0 + r0) * rowbytes + ki * 16;
+  const unsigned char *wb = SWIGLU ? reinterpret_cast<const unsigned char *>(a.w_b) + ((size_t)e * a.expert_stride_rows + row0 + r0) * rowbytes + ki * 16
+                                   : wa + 128 * rowbytes;
+  const unsigned char *xs[2];
+  uint32_t xbytes[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int tok = r0 + 32 * i;
+    xs[i] = reinterpret_cast<const unsigned char *>(a.x);
+    xbytes[i] = 0;  // rows beyond the tile's tokens are filled with zeros
+    if (tok < cnt) {
+      const size_t xr = a.x_index ? (size_t)a.x_index[p0 + tok] : (size_t)(p0 + tok);
+      xs[i] = reinterpret_cast<const unsigned char *>(a.x) + xr * rowbytes + ki * 16;
+      xbytes[i] = 16;
+    }
+  }
+  auto issue = [&](int c) {
+    if (c < nchunks) {
+      const uint32_t st = sbase + (uint32_t)(c % kBfStages) * kBfStageBytes;
+      const size_t koff = (size_t)c * (kTcKC * 2);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int row = r0 + 32 * i;
+        const uint32_t d = (uint32_t)(ki * kBfALbo + (row >> 3) * kTcSbo + (row & 7) * 16);
+        tc_cp_async16(st + d, wa + (size_t)(32 * i) * rowbytes + koff);
+        tc_cp_async16(st + kBfABytes + d, wb + (size_t)(32 * i) * rowbytes + koff);
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int tok = r0 + 32 * i;
+        if (32 * i < N)
+          tc_cp_async16_zfill(st + 2 * kBfABytes + (uint32_t)(ki * kTcBLbo + (tok >> 3) * kTcSbo + (tok & 7) * 16),
+                              xs[i] + (xbytes[i] ? koff : 0), xbytes[i]);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (producer) {
+#pragma unroll
+    for (int c = 0; c < kBfStages - 1; ++c) issue(c);
+  }
+
+  const uint32_t mbar_full = (uint32_t)__cvta_generic_to_shared(&s_mbar[0]);
+  const uint32_t mbar_empty = mbar_full + 8 * kBfStages;
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < kBfStages; ++s) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar_full + 8 * s), "r"(kTcProducers / 32) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(mbar_empty + 8 * s) : "memory");
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(&s_tmem_base)),
+                 "r"((uint32_t)kBfTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = s_tmem_base;
+  const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((128u >> 4) << 24);
+
+  bool failed = false;
+  if (producer) {
+    for (int c = 0; c < nchunks; ++c) {
+      // the stage that step c + kBfStages - 1 goes to was read by the MMAs of step c - 1
+      if (c >= 1 && c + kBfStages - 1 < nchunks &&
+          !tc_mbar_wait(mbar_empty + 8 * ((c - 1) % kBfStages), (uint32_t)(((c - 1) / kBfStages) & 1))) {
+        failed = true;
+        break;
+      }
+      issue(c + kBfStages - 1);
+      asm volatile("cp.async.wait_group %0;" ::"n"(kBfStages - 1) : "memory");  // this thread's pieces of step c have landed
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mbar_full + 8 * (c % kBfStages)) : "memory");
+    }
+    if (!failed) {
+      const int last = nchunks - 1;
+      failed = !tc_mbar_wait(mbar_empty + 8 * (last % kBfStages), (uint32_t)((last / kBfStages) & 1));
+    }
+  } else if (lane == 0) {
+    for (int c = 0; c < nchunks; ++c) {
+      const int s = c % kBfStages;
+      if (!tc_mbar_wait(mbar_full + 8 * s, (uint32_t)((c / kBfStages) & 1))) {
+        failed = true;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t a0 = sbase + (uint32_t)s * kBfStageBytes, a1 = a0 + kBfABytes, b = a1 + kBfABytes;
+#pragma unroll
+      for (int j = 0; j < kTcKC / 16; ++j) {
+        const uint32_t acc = (c > 0 || j > 0) ? 1u : 0u;
+        const uint64_t bd = tc_smem_desc(b + j * 2 * kTcBLbo, kTcBLbo, kTcSbo);
+        tc_mma_f16(tmem, tc_smem_desc(a0 + j * 2 * kBfALbo, kBfALbo, kTcSbo), bd, idesc, acc);
+        tc_mma_f16(tmem + kTcN, tc_smem_desc(a1 + j * 2 * kBfALbo, kBfALbo, kTcSbo), bd, idesc, acc);
+      }
+      tc_commit(mbar_empty + 8 * s);
+    }
+  }
+  failed = __any_sync(0xffffffffu, failed);
+  if (failed && lane == 0) atomicExch(&g_wgemm_tc_error, 1u);
+  if (producer && !failed) tc_epilogue<SWIGLU>(a, tmem, warp, lane, N, cnt, p0, row0);
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)kBfTmemCols) : "memory");
+}
+
 size_t wgemm_tc_smem_bytes() { return (size_t)kTcStages * kTcStageBytes + (size_t)kTcRing * kTcRawBytes; }
 
 // True when the tcgen05 kernel covers this mode and shape.
 bool wgemm_tc_supports(int mode, const WgArgs &args) {
-  if (mode != WG_I4_SWIGLU && mode != WG_I4_PLAIN) return false;
-  const int rows_per_cta = mode == WG_I4_SWIGLU ? 128 : 256;
-  return args.R % rows_per_cta == 0 && args.K % kTcKC == 0;
+  const bool swiglu = mode == WG_I4_SWIGLU || mode == WG_BF16_SWIGLU;
+  const int rows_per_cta = swiglu ? 128 : 256;
+  return args.R % rows_per_cta == 0 && args.K % kTcKC == 0 && args.K / kTcKC >= kBfStages;
 }
 
 int launch_wgemm_tc(int mode, const WgArgs &args, int max_tiles, cudaStream_t stream) {
-  const size_t smem = wgemm_tc_smem_bytes();
-  const bool swiglu = mode == WG_I4_SWIGLU;
+  const bool swiglu = mode == WG_I4_SWIGLU || mode == WG_BF16_SWIGLU;
   dim3 grid(args.R / (swiglu ? 128 : 256), max_tiles);
+  if (mode == WG_BF16_SWIGLU || mode == WG_BF16_PLAIN) {
+    const size_t bsmem = (size_t)kBfStages * kBfStageBytes;
+    if (swiglu) {
+      BLOK_CUDA(cudaFuncSetAttribute(wgemm_tc_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bsmem));
+      wgemm_tc_bf16_kernel<true><<<grid, kTcThreads, bsmem, stream>>>(args);
+    } else {
+      BLOK_CUDA(cudaFuncSetAttribute(wgemm_tc_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bsmem));
+      wgemm_tc_bf16_kernel<false><<<grid, kTcThreads, bsmem, stream>>>(args);
+    }
+    return launch_status("wgemm_tc_bf16_kernel");
+  }
+  const size_t smem = wgemm_tc_smem_bytes();
   if (swiglu) {
     BLOK_CUDA(cudaFuncSetAttribute(wgemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     wgemm_tc_kernel<true><<<grid, kTcThreads, smem, stream>>>(args);

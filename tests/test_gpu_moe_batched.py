@@ -17,10 +17,12 @@ def _oracle_layer(oracle, w, x, ids_needed, topk=8):
                             shared[2], util.t2np_f32(x), topk=topk, mode=0)
 
 
+@pytest.mark.parametrize("impl", ["mma", "tc"])  # the mma.sync kernel and the tcgen05 kernels, whatever the size
 @pytest.mark.parametrize("T,hidden,inter,experts,shared,seed", [(40, 1024, 512, 128, 512, 31), (1, 1024, 512, 128, 512, 32),
                                                                 (64, 7168, 2048, 384, 2048, 2), (130, 512, 512, 128, 0, 33)])
-def test_moe_batched_vs_oracle(cuda, oracle, T, hidden, inter, experts, shared, seed):
+def test_moe_batched_vs_oracle(cuda, oracle, monkeypatch, impl, T, hidden, inter, experts, shared, seed):
     from blok_b200 import lib, synth
+    monkeypatch.setenv("BLOK_WGEMM_IMPL", impl)
     w = synth.moe_layer_weights(cuda, seed=seed, hidden=hidden, inter=inter, experts=experts, shared_inter=shared)
     if hidden < 7168:
         for k in ("gate_s", "up_s", "down_s"):
@@ -64,9 +66,11 @@ def test_moe_batched_agrees_with_decode_path_at_2048_tokens(cuda):
     layer.close()
 
 
-def test_experts_grouped_handles_empty_and_ragged_groups(cuda, oracle):
+@pytest.mark.parametrize("impl", ["mma", "tc"])
+def test_experts_grouped_handles_empty_and_ragged_groups(cuda, oracle, monkeypatch, impl):
     """Assignments concentrated on few experts (others get zero tokens), more than one 64-token tile for one expert."""
     from blok_b200 import lib, synth
+    monkeypatch.setenv("BLOK_WGEMM_IMPL", impl)
     hidden, inter, experts = 512, 512, 128
     w = synth.moe_layer_weights(cuda, seed=41, hidden=hidden, inter=inter, experts=experts, shared_inter=0)
     for k in ("gate_s", "up_s", "down_s"):
@@ -83,6 +87,7 @@ def test_experts_grouped_handles_empty_and_ragged_groups(cuda, oracle):
                                 util.t2np_bf16(w["up_s"][ex]), util.t2np_u32(w["down_w"][ex]), util.t2np_bf16(w["down_s"][ex]),
                                 xh[int(rows[a])], mode=0, round_out=True)
         util.assert_close(y[a], ref, "assignment %d" % a)
+    layer.check()
     assert layer.experts_grouped(x, e[:0].contiguous(), rows[:0].contiguous()).shape == (0, hidden)
     with pytest.raises(lib.BlokError):
         layer.experts_grouped(x, torch.zeros(64 * 8 + 1, dtype=torch.int32, device=cuda))
