@@ -176,7 +176,7 @@ def other_workload(a, rank, world, device, steps, warmup):
         Tl = T // world
         per = a.experts // world
         # every rank draws the same layer and keeps its shard; two layers are rotated (2 x 9.5 GB / world per GPU)
-        nl = 2
+        nl = 2 if a.experts == 384 else 1  # a reduced case (profiler capture) holds one layer
         shards, reps = [], []
         for i in range(nl):
             w = synth.moe_layer_weights(device, seed=2 + 31 * i, experts=a.experts)

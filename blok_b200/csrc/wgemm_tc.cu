@@ -29,8 +29,9 @@ constexpr int kTcSbo = 128;          // bytes between 8-token groups of the acti
 constexpr int kTcBLbo = 1040;        // 8 token groups x 128 B, plus 16 B so that the 8 K-slices of a token hit 8 banks
 constexpr int kTcBBytes = (kTcKC / 8) * kTcBLbo;
 constexpr int kTcStageBytes = ((kTcBBytes + 127) / 128) * 128;  // shared memory per stage: the activation tile only
-constexpr int kTcRing = 6;                       // steps of packed words in flight per CTA (cp.async)
-constexpr int kTcRawBytes = 2 * kTcProducers * 16 + kTcProducers * 4;  // one step: 256 rows x 2 halves x 16 B, and the rows' scale pairs
+constexpr int kTcSuper = 256;        // weight columns per copy step: 128 packed bytes and 8 scales of each row
+constexpr int kTcRing = 2;           // copy steps resident per CTA: one being unpacked, one in flight
+constexpr int kTcRawBytes = kTcProducers * 128 + kTcProducers * 16;  // 256 rows x (128 B of words + 16 B of scales)
 constexpr int kTcACols = kTcKC / 2;                       // tensor-memory columns of one 128-row block of one step (2 bf16 per column)
 constexpr int kTcTmemCols = 256;                          // 2 accumulators x 64 columns + 2 stages x 2 blocks x 32 columns of weights
 constexpr unsigned kTcSpinLimit = 1u << 22;
@@ -118,6 +119,7 @@ __device__ __forceinline__ bool tc_mbar_wait(uint32_t mbar, uint32_t parity) {
         : "r"(mbar), "r"(parity)
         : "memory");
     if (ok) return true;
+    __nanosleep(64);  // a failed try already waited out the hardware's own time slice; do not burn issue slots
   }
   return false;
 }
@@ -183,14 +185,17 @@ __global__ void __launch_bounds__(kTcThreads, 2) wgemm_tc_kernel(const WgArgs a)
   const int e = a.tile_expert[tile], p0 = a.tile_start[tile], cnt = a.tile_count[tile];
   const int N = max(16, (cnt + 15) & ~15);  // token columns the MMAs cover
 
-  // ---- this thread's weight row: threads 0..127 unpack block 0 (gate rows / rows r), 128..255 block 1 (up / r + 128) ----
+  // ---- this thread unpacks weight row r of block blk: threads 0..127 block 0 (gate rows / rows r), 128..255 block 1 ----
   const int blk = tid >> 7, r = tid & 127;
   const int rows_per_cta = SWIGLU ? 128 : 256;
   const int row0 = blockIdx.x * rows_per_cta;
-  const size_t wrow16 = (size_t)a.K / 32;  // uint4 (= scale groups) per packed row
-  const size_t grow = (size_t)e * a.expert_stride_rows + row0 + r + ((!SWIGLU && blk) ? 128 : 0);
-  const uint4 *wsrc = reinterpret_cast<const uint4 *>((SWIGLU && blk) ? a.w_b : a.w_a) + grow * wrow16;
-  const uint32_t *ssrc = reinterpret_cast<const uint32_t *>(((SWIGLU && blk) ? a.s_b : a.s_a) + grow * wrow16);
+  const size_t rowbytes = (size_t)a.K / 2;  // packed bytes per weight row
+  const size_t srowbytes = (size_t)a.K / 16;  // scale bytes per weight row
+  const size_t grow0 = (size_t)e * a.expert_stride_rows + row0;
+  const unsigned char *wbase0 = reinterpret_cast<const unsigned char *>(a.w_a) + grow0 * rowbytes;
+  const unsigned char *wbase1 = SWIGLU ? reinterpret_cast<const unsigned char *>(a.w_b) + grow0 * rowbytes : wbase0 + 128 * rowbytes;
+  const unsigned char *sbase0 = reinterpret_cast<const unsigned char *>(a.s_a) + grow0 * srowbytes;
+  const unsigned char *sbase1 = SWIGLU ? reinterpret_cast<const unsigned char *>(a.s_b) + grow0 * srowbytes : sbase0 + 128 * srowbytes;
   // ---- this thread's two pieces of the activation tile: token (tid / 8) + 32 i, K-slice tid % 8 ----
   const int ki = tid & 7;
   const uint4 *xp[2];
@@ -203,20 +208,27 @@ __global__ void __launch_bounds__(kTcThreads, 2) wgemm_tc_kernel(const WgArgs a)
       xp[i] = reinterpret_cast<const uint4 *>(a.x + xr * a.K) + ki;
     }
   }
-  // Packed words and scales travel through a cp.async ring of kTcRing steps: every thread copies its own row's 32
-  // bytes per step and reads the same bytes back, so the ring needs no barrier.  The activations (L2 resident,
-  // shared by all row blocks of the expert) are fetched one step ahead into registers.
+  // Packed words and scales reach shared memory in copy steps of 256 columns: 8 neighbouring lanes copy the 128
+  // contiguous bytes of one row (16 bytes each), so a warp's cp.async touches 4 cache lines, not 32.  Piece p of row
+  // q lands at q * 128 + ((p ^ (q & 7)) * 16): both the copy and the later per-row reads are free of bank conflicts.
+  // The activations (L2 resident, shared by all row blocks of the expert) are fetched one step ahead into registers.
   const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(smem);
   const uint32_t raw0 = sbase + kTcStages * kTcStageBytes;
   const unsigned char *rawp = smem + kTcStages * kTcStageBytes;
   const int nchunks = a.K / kTcKC;
+  const int nsuper = a.K / kTcSuper;
   const bool producer = tid < kTcProducers;
-  auto issue = [&](int c) {
-    if (c < nchunks) {
-      const uint32_t slot = raw0 + (uint32_t)(c % kTcRing) * kTcRawBytes;
-      tc_cp_async16(slot + (0 * kTcProducers + tid) * 16, wsrc + 2 * c);
-      tc_cp_async16(slot + (1 * kTcProducers + tid) * 16, wsrc + 2 * c + 1);
-      tc_cp_async4(slot + 2 * kTcProducers * 16 + tid * 4, ssrc + c);
+  auto issue = [&](int sc) {
+    if (sc < nsuper) {
+      const uint32_t slot = raw0 + (uint32_t)(sc % kTcRing) * kTcRawBytes;
+      const int q0 = tid >> 3, pc = tid & 7;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int q = q0 + 32 * i;  // 0..255: block q / 128, row q % 128
+        const unsigned char *src = (i < 4 ? wbase0 : wbase1) + (size_t)(q & 127) * rowbytes + (size_t)sc * 128 + pc * 16;
+        tc_cp_async16(slot + q * 128 + ((pc ^ (q & 7)) * 16), src);
+      }
+      tc_cp_async16(slot + kTcProducers * 128 + tid * 16, (blk ? sbase1 : sbase0) + (size_t)r * srowbytes + (size_t)sc * 16);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -224,10 +236,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) wgemm_tc_kernel(const WgArgs a)
 #pragma unroll
     for (int i = 0; i < 2; ++i) xv[i] = xp[i] ? __ldg(xp[i] + (size_t)c * (kTcKC / 8)) : make_uint4(0, 0, 0, 0);
   };
-  if (producer) {
-#pragma unroll
-    for (int c = 0; c < kTcRing - 1; ++c) issue(c);
-  }
+  if (producer) issue(0);
 
   // ---- barriers and tensor memory: full[s] counts the 8 producer warps, empty[s] the MMAs' commit ----
   const uint32_t mbar_full = (uint32_t)__cvta_generic_to_shared(&s_mbar[0]);
@@ -257,58 +266,80 @@ __global__ void __launch_bounds__(kTcThreads, 2) wgemm_tc_kernel(const WgArgs a)
   bool failed = false;
   if (producer) {
     // ---- producers: unpack step c into stage c % 2 as soon as the MMAs of step c - 2 have released it ----
-    for (int c = 0; c < nchunks; ++c) {
-      issue(c + kTcRing - 1);
-      uint4 xcur[2];
-#pragma unroll
-      for (int i = 0; i < 2; ++i) xcur[i] = xnext[i];
-      if (c + 1 < nchunks) fetch_x(c + 1, xnext);
-      const int s = c % kTcStages;
-      if (c >= kTcStages && !tc_mbar_wait(mbar_empty + 8 * s, (uint32_t)((c / kTcStages - 1) & 1))) {
+    for (int sc = 0; sc < nsuper; ++sc) {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");  // this thread's copies of the step have landed
+      // producers' barrier: everybody's copies have landed and the other slot is no longer read.  It also ORs the
+      // threads' failure flags, so that after a timeout all of them leave together and nobody waits here alone.
+      uint32_t anyfail;
+      asm volatile(
+          "{\n\t"
+          ".reg .pred p, q;\n\t"
+          "setp.ne.u32 q, %1, 0;\n\t"
+          "bar.red.or.pred p, 1, %2, q;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t"
+          "}\n"
+          : "=r"(anyfail)
+          : "r"((uint32_t)failed), "n"(kTcProducers)
+          : "memory");
+      if (anyfail) {
         failed = true;
         break;
       }
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      unsigned char *B = smem + (size_t)s * kTcStageBytes;
-      asm volatile("cp.async.wait_group %0;" ::"n"(kTcRing - 1) : "memory");  // this step's own words have landed
-      const unsigned char *raw = rawp + (size_t)(c % kTcRing) * kTcRawBytes;
-      const uint32_t scm = *reinterpret_cast<const uint32_t *>(raw + 2 * kTcProducers * 16 + tid * 4);
-      // The row's 64 dequantised weights of this step go to tensor memory as the MMA's A operand: lane = row, two
-      // bf16 per 32-bit column, 8 columns per K = 16 step (column pairs in the order 0 4 1 5 2 6 3 7 of each word).
-      uint32_t av[32];
+      issue(sc + 1);
+      const unsigned char *raw = rawp + (size_t)(sc % kTcRing) * kTcRawBytes;
+      const uint4 scq = *reinterpret_cast<const uint4 *>(raw + kTcProducers * 128 + tid * 16);  // the row's 8 scales
+      const uint32_t scw[4] = {scq.x, scq.y, scq.z, scq.w};
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const uint32_t s2 = __byte_perm(scm, scm, h ? 0x3232 : 0x1010);
-        const uint4 q = *reinterpret_cast<const uint4 *>(raw + (h * kTcProducers + tid) * 16);
-        const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+      for (int j = 0; j < kTcSuper / kTcKC; ++j) {
+        const int c = sc * (kTcSuper / kTcKC) + j;
+        uint4 xcur[2];
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          const uint4 d = tc_dequant_word(qw[w], s2);
-          av[(h * 4 + w) * 4 + 0] = d.x;
-          av[(h * 4 + w) * 4 + 1] = d.y;
-          av[(h * 4 + w) * 4 + 2] = d.z;
-          av[(h * 4 + w) * 4 + 3] = d.w;
+        for (int i = 0; i < 2; ++i) xcur[i] = xnext[i];
+        if (c + 1 < nchunks) fetch_x(c + 1, xnext);
+        const int s = c % kTcStages;
+        if (c >= kTcStages && !tc_mbar_wait(mbar_empty + 8 * s, (uint32_t)((c / kTcStages - 1) & 1))) {
+          failed = true;
+          break;
         }
-      }
-      tc_st32(tmem + ((uint32_t)(32 * (warp & 3)) << 16) + 2 * kTcN + (uint32_t)(s * 2 + blk) * kTcACols, av);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        unsigned char *B = smem + (size_t)s * kTcStageBytes;
+        // The row's 64 dequantised weights of this step go to tensor memory as the MMA's A operand: lane = row, two
+        // bf16 per 32-bit column, 8 columns per K = 16 step (column pairs in the order 0 4 1 5 2 6 3 7 of each word).
+        uint32_t av[32];
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        if (32 * i < N) {
-          const uint4 v = xcur[i];
-          uint4 o;  // columns 0 4 1 5 2 6 3 7, as the weights
-          o.x = __byte_perm(v.x, v.z, 0x5410);
-          o.y = __byte_perm(v.x, v.z, 0x7632);
-          o.z = __byte_perm(v.y, v.w, 0x5410);
-          o.w = __byte_perm(v.y, v.w, 0x7632);
-          const int tok = (tid >> 3) + 32 * i;
-          *reinterpret_cast<uint4 *>(B + ki * kTcBLbo + (tok >> 3) * kTcSbo + (tok & 7) * 16) = o;
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t s2 = __byte_perm(scw[j], scw[j], h ? 0x3232 : 0x1010);
+          const uint4 q = *reinterpret_cast<const uint4 *>(raw + tid * 128 + (((2 * j + h) ^ (tid & 7)) * 16));
+          const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            const uint4 d = tc_dequant_word(qw[w], s2);
+            av[(h * 4 + w) * 4 + 0] = d.x;
+            av[(h * 4 + w) * 4 + 1] = d.y;
+            av[(h * 4 + w) * 4 + 2] = d.z;
+            av[(h * 4 + w) * 4 + 3] = d.w;
+          }
         }
+        tc_st32(tmem + ((uint32_t)(32 * (warp & 3)) << 16) + 2 * kTcN + (uint32_t)(s * 2 + blk) * kTcACols, av);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          if (32 * i < N) {
+            const uint4 v = xcur[i];
+            uint4 o;  // columns 0 4 1 5 2 6 3 7, as the weights
+            o.x = __byte_perm(v.x, v.z, 0x5410);
+            o.y = __byte_perm(v.x, v.z, 0x7632);
+            o.z = __byte_perm(v.y, v.w, 0x5410);
+            o.w = __byte_perm(v.y, v.w, 0x7632);
+            const int tok = (tid >> 3) + 32 * i;
+            *reinterpret_cast<uint4 *>(B + ki * kTcBLbo + (tok >> 3) * kTcSbo + (tok & 7) * 16) = o;
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the activation tile is read by the tensor core's proxy
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mbar_full + 8 * s) : "memory");
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the activation tile is read by the tensor core's proxy
-      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mbar_full + 8 * s) : "memory");
     }
     // all MMAs have completed once the last step's commit has arrived
     if (!failed) {
@@ -495,7 +526,7 @@ size_t wgemm_tc_smem_bytes() { return (size_t)kTcStages * kTcStageBytes + (size_
 bool wgemm_tc_supports(int mode, const WgArgs &args) {
   const bool swiglu = mode == WG_I4_SWIGLU || mode == WG_BF16_SWIGLU;
   const int rows_per_cta = swiglu ? 128 : 256;
-  return args.R % rows_per_cta == 0 && args.K % kTcKC == 0 && args.K / kTcKC >= kBfStages;
+  return args.R % rows_per_cta == 0 && args.K % kTcSuper == 0 && args.K / kTcKC >= kBfStages;
 }
 
 int launch_wgemm_tc(int mode, const WgArgs &args, int max_tiles, cudaStream_t stream) {
