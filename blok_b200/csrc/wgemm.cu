@@ -194,7 +194,7 @@ static int wgemm_forced_impl() {  // read at every launch, so that a test can sw
 int launch_wgemm(int mode, const WgArgs &args, int max_tiles, cudaStream_t stream) {
   const int forced = wgemm_forced_impl();
   const bool i4 = mode == WG_I4_SWIGLU || mode == WG_I4_PLAIN;
-  const bool enough = args.n_rows >= (i4 ? 2048 : 512);
+  const bool enough = args.n_rows >= (i4 ? 256 : 512);
   if (forced != 1 && (forced == 2 || enough) && wgemm_tc_supports(mode, args)) return launch_wgemm_tc(mode, args, max_tiles, stream);
   const size_t smem = wgemm_smem_bytes();
   const bool swiglu = mode == WG_BF16_SWIGLU || mode == WG_I4_SWIGLU;
