@@ -204,7 +204,7 @@ extern "C" int blok_moe_batched(blok_moe_layer_t *L, const blok_bf16_t *x, int T
   r.w_a = w.router_w; r.w_b = nullptr; r.s_a = r.s_b = nullptr; r.expert_stride_rows = 0; r.x = x; r.x_index = nullptr;
   r.K = w.hidden; r.R = w.experts; r.out_bf16 = nullptr; r.out_f32 = L->logits;
   r.tile_expert = L->b_ttile_expert; r.tile_start = L->b_ttile_start; r.tile_count = L->b_ttile_count;
-  r.num_tiles = L->b_num_ttiles; r.out_index = nullptr; r.n_rows = T;
+  r.num_tiles = L->b_num_ttiles; r.out_index = nullptr; r.n_rows = T; r.identity_tiles = 1;
   if ((rc = launch_wgemm(WG_BF16_PLAIN, r, tt, stream))) return rc;
   if ((rc = launch_router_topk(L->logits, w.router_bias, T, w.experts, w.topk, w.routed_scale, L->ids, L->wts, L->local_ids,
                                w.expert_base, stream)))
@@ -247,7 +247,7 @@ extern "C" int blok_moe_shared(blok_moe_layer_t *L, const blok_bf16_t *x, int T,
   s.w_a = w.shared_gate; s.w_b = w.shared_up; s.s_a = s.s_b = nullptr; s.expert_stride_rows = 0; s.x = x; s.x_index = nullptr;
   s.K = w.hidden; s.R = w.shared_inter; s.out_bf16 = L->b_smid; s.out_f32 = nullptr;
   s.tile_expert = L->b_ttile_expert; s.tile_start = L->b_ttile_start; s.tile_count = L->b_ttile_count;
-  s.num_tiles = L->b_num_ttiles; s.out_index = nullptr; s.n_rows = T;
+  s.num_tiles = L->b_num_ttiles; s.out_index = nullptr; s.n_rows = T; s.identity_tiles = 1;
   if ((rc = launch_wgemm(WG_BF16_SWIGLU, s, tt, stream))) return rc;
   WgArgs d = s;
   d.w_a = w.shared_down; d.w_b = nullptr; d.x = L->b_smid; d.K = w.shared_inter; d.R = w.hidden; d.out_bf16 = out;

@@ -26,6 +26,7 @@ struct WgArgs {
   const int *tile_count;
   const int *num_tiles;
   const int *out_index;
+  int identity_tiles = 0;  // the tiles are consecutive 64-row blocks of x (one group: a dense layer over n_rows tokens)
   int n_rows = 0;  // rows of x the launch covers (tokens, or token-expert assignments): picks the kernel
 };
 

@@ -143,14 +143,15 @@ __device__ __forceinline__ void tc_cp_async4(uint32_t dst, const void *src) {
 // Epilogue of a tile: lane l of warp w (8 warps) holds accumulator row 32 (w % 4) + l of both row blocks (its
 // tensor-memory lane); warps 0..3 take the even 16-token column blocks, warps 4..7 the odd ones.
 template <bool SWIGLU>
-__device__ __forceinline__ void tc_epilogue(const WgArgs &a, uint32_t tmem, int warp, int lane, int N, int cnt, int p0, int row0) {
+__device__ __forceinline__ void tc_epilogue(const WgArgs &a, uint32_t tmem, int acc1_col, int warp, int lane, int N, int cnt, int p0,
+                                            int row0) {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const int lg = warp & 3, row = 32 * lg + lane;
   const uint32_t trow = tmem + ((uint32_t)(32 * lg) << 16);
   for (int n0 = 16 * (warp >> 2); n0 < N; n0 += 32) {
     uint32_t ra[16], rb[16];
     tc_ld16(trow + n0, ra);
-    tc_ld16(trow + kTcN + n0, rb);
+    tc_ld16(trow + acc1_col + n0, rb);
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
@@ -370,7 +371,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) wgemm_tc_kernel(const WgArgs a)
   failed = __any_sync(0xffffffffu, failed);  // warp-uniform: the tensor-memory loads below are warp-wide
   if (failed && lane == 0) atomicExch(&g_wgemm_tc_error, 1u);
 
-  if (producer && !failed) tc_epilogue<SWIGLU>(a, tmem, warp, lane, N, cnt, p0, row0);
+  if (producer && !failed) tc_epilogue<SWIGLU>(a, tmem, kTcN, warp, lane, N, cnt, p0, row0);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 0)
@@ -380,25 +381,46 @@ __global__ void __launch_bounds__(kTcThreads, 2) wgemm_tc_kernel(const WgArgs a)
 // ---- bf16 weights (shared expert): both operands come straight from global memory into the core-matrix layout
 // with 16-byte cp.async copies, one per (row, 8-column slice); no registers, no permutation.  kBfStages steps of
 // 2 x 128 weight rows + the token tile are in flight per CTA. ----
-constexpr int kBfStages = 4;
+constexpr int kBfMinSteps = 4;       // fewest 64-column steps the pipelines below are written for
 constexpr int kBfALbo = 2048 + 16;   // + 16 B: the 8 K-slices of a row, copied by 8 neighbouring lanes, hit 8 banks
 constexpr int kBfABytes = (kTcKC / 8) * kBfALbo;
-constexpr int kBfStageBytes = ((2 * kBfABytes + kTcBBytes + 127) / 128) * 128;
-constexpr int kBfTmemCols = 2 * kTcN;
+// NT = token columns per tile: 64 for tiles of an expert group, 256 for a dense layer (every token, same weights),
+// where the larger tile halves the bytes fetched from L2 per flop.  STAGES steps are resident per CTA.
+template <int NT>
+struct BfCfg {
+  static constexpr int kBLbo = (NT / 8) * 128 + 16;
+  static constexpr int kBBytes = (kTcKC / 8) * kBLbo;
+  static constexpr int kStageBytes = ((2 * kBfABytes + kBBytes + 127) / 128) * 128;
+  static constexpr int kStages = NT == 64 ? 4 : 3;
+  static constexpr int kTmemCols = 2 * NT;
+};
 
 __device__ __forceinline__ void tc_cp_async16_zfill(uint32_t dst, const void *src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
 
-template <bool SWIGLU>
+template <bool SWIGLU, int NT>
 __global__ void __launch_bounds__(kTcThreads, 1) wgemm_tc_bf16_kernel(const WgArgs a) {
+  using Cfg = BfCfg<NT>;
+  constexpr int kBfStages = Cfg::kStages;
+  constexpr int kBfStageBytes = Cfg::kStageBytes;
+  constexpr int kBfTmemCols = Cfg::kTmemCols;
+  constexpr int kBLbo = Cfg::kBLbo;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) unsigned long long s_mbar[2 * kBfStages];
   __shared__ uint32_t s_tmem_base;
   const int tile = blockIdx.y;
-  if (tile >= *a.num_tiles) return;
+  int e, p0, cnt;
+  if (a.identity_tiles) {  // dense: tile t covers rows [NT t, NT t + NT) of x
+    e = 0;
+    p0 = NT * tile;
+    cnt = min(NT, a.n_rows - p0);
+    if (cnt <= 0) return;
+  } else {
+    if (tile >= *a.num_tiles) return;
+    e = a.tile_expert[tile], p0 = a.tile_start[tile], cnt = a.tile_count[tile];
+  }
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int e = a.tile_expert[tile], p0 = a.tile_start[tile], cnt = a.tile_count[tile];
   const int N = max(16, (cnt + 15) & ~15);
   const int rows_per_cta = SWIGLU ? 128 : 256;
   const int row0 = blockIdx.x * rows_per_cta;
@@ -412,10 +434,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) wgemm_tc_bf16_kernel(const WgAr
   const unsigned char *wa = reinterpret_cast<const unsigned char *>(a.w_a) + ((size_t)e * a.expert_stride_rows + row0 + r0) * rowbytes + ki * 16;
   const unsigned char *wb = SWIGLU ? reinterpret_cast<const unsigned char *>(a.w_b) + ((size_t)e * a.expert_stride_rows + row0 + r0) * rowbytes + ki * 16
                                    : wa + 128 * rowbytes;
-  const unsigned char *xs[2];
-  uint32_t xbytes[2];
+  constexpr int kXPieces = NT / 32;  // activation pieces per thread and step
+  const unsigned char *xs[kXPieces];
+  uint32_t xbytes[kXPieces];
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
+  for (int i = 0; i < kXPieces; ++i) {
     const int tok = r0 + 32 * i;
     xs[i] = reinterpret_cast<const unsigned char *>(a.x);
     xbytes[i] = 0;  // rows beyond the tile's tokens are filled with zeros
@@ -437,10 +460,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) wgemm_tc_bf16_kernel(const WgAr
         tc_cp_async16(st + kBfABytes + d, wb + (size_t)(32 * i) * rowbytes + koff);
       }
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
+      for (int i = 0; i < kXPieces; ++i) {
         const int tok = r0 + 32 * i;
         if (32 * i < N)
-          tc_cp_async16_zfill(st + 2 * kBfABytes + (uint32_t)(ki * kTcBLbo + (tok >> 3) * kTcSbo + (tok & 7) * 16),
+          tc_cp_async16_zfill(st + 2 * kBfABytes + (uint32_t)(ki * kBLbo + (tok >> 3) * kTcSbo + (tok & 7) * 16),
                               xs[i] + (xbytes[i] ? koff : 0), xbytes[i]);
       }
     }
@@ -476,17 +499,18 @@ __global__ void __launch_bounds__(kTcThreads, 1) wgemm_tc_bf16_kernel(const WgAr
   bool failed = false;
   if (producer) {
     for (int c = 0; c < nchunks; ++c) {
-      // the stage that step c + kBfStages - 1 goes to was read by the MMAs of step c - 1
+      // hand step c to the MMA thread as soon as this thread's pieces of it have landed ...
+      asm volatile("cp.async.wait_group %0;" ::"n"(kBfStages - 2) : "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mbar_full + 8 * (c % kBfStages)) : "memory");
+      // ... and only then wait for the stage that step c + kBfStages - 1 goes to: the MMAs of step c - 1 read it
       if (c >= 1 && c + kBfStages - 1 < nchunks &&
           !tc_mbar_wait(mbar_empty + 8 * ((c - 1) % kBfStages), (uint32_t)(((c - 1) / kBfStages) & 1))) {
         failed = true;
         break;
       }
       issue(c + kBfStages - 1);
-      asm volatile("cp.async.wait_group %0;" ::"n"(kBfStages - 1) : "memory");  // this thread's pieces of step c have landed
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mbar_full + 8 * (c % kBfStages)) : "memory");
     }
     if (!failed) {
       const int last = nchunks - 1;
@@ -504,16 +528,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) wgemm_tc_bf16_kernel(const WgAr
 #pragma unroll
       for (int j = 0; j < kTcKC / 16; ++j) {
         const uint32_t acc = (c > 0 || j > 0) ? 1u : 0u;
-        const uint64_t bd = tc_smem_desc(b + j * 2 * kTcBLbo, kTcBLbo, kTcSbo);
+        const uint64_t bd = tc_smem_desc(b + j * 2 * kBLbo, kBLbo, kTcSbo);
         tc_mma_f16(tmem, tc_smem_desc(a0 + j * 2 * kBfALbo, kBfALbo, kTcSbo), bd, idesc, acc);
-        tc_mma_f16(tmem + kTcN, tc_smem_desc(a1 + j * 2 * kBfALbo, kBfALbo, kTcSbo), bd, idesc, acc);
+        tc_mma_f16(tmem + NT, tc_smem_desc(a1 + j * 2 * kBfALbo, kBfALbo, kTcSbo), bd, idesc, acc);
       }
       tc_commit(mbar_empty + 8 * s);
     }
   }
   failed = __any_sync(0xffffffffu, failed);
   if (failed && lane == 0) atomicExch(&g_wgemm_tc_error, 1u);
-  if (producer && !failed) tc_epilogue<SWIGLU>(a, tmem, warp, lane, N, cnt, p0, row0);
+  if (producer && !failed) tc_epilogue<SWIGLU>(a, tmem, NT, warp, lane, N, cnt, p0, row0);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 0)
@@ -526,21 +550,26 @@ size_t wgemm_tc_smem_bytes() { return (size_t)kTcStages * kTcStageBytes + (size_
 bool wgemm_tc_supports(int mode, const WgArgs &args) {
   const bool swiglu = mode == WG_I4_SWIGLU || mode == WG_BF16_SWIGLU;
   const int rows_per_cta = swiglu ? 128 : 256;
-  return args.R % rows_per_cta == 0 && args.K % kTcSuper == 0 && args.K / kTcKC >= kBfStages;
+  return args.R % rows_per_cta == 0 && args.K % kTcSuper == 0 && args.K / kTcKC >= kBfMinSteps;
 }
 
 int launch_wgemm_tc(int mode, const WgArgs &args, int max_tiles, cudaStream_t stream) {
   const bool swiglu = mode == WG_I4_SWIGLU || mode == WG_BF16_SWIGLU;
   dim3 grid(args.R / (swiglu ? 128 : 256), max_tiles);
   if (mode == WG_BF16_SWIGLU || mode == WG_BF16_PLAIN) {
-    const size_t bsmem = (size_t)kBfStages * kBfStageBytes;
-    if (swiglu) {
-      BLOK_CUDA(cudaFuncSetAttribute(wgemm_tc_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bsmem));
-      wgemm_tc_bf16_kernel<true><<<grid, kTcThreads, bsmem, stream>>>(args);
+#define BLOK_BF_LAUNCH(SW, NT)                                                                                                 \
+  {                                                                                                                            \
+    const size_t bsmem = (size_t)BfCfg<NT>::kStages * BfCfg<NT>::kStageBytes;                                                  \
+    BLOK_CUDA(cudaFuncSetAttribute(wgemm_tc_bf16_kernel<SW, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bsmem));    \
+    wgemm_tc_bf16_kernel<SW, NT><<<grid, kTcThreads, bsmem, stream>>>(args);                                                   \
+  }
+    if (args.identity_tiles) {
+      grid.y = (args.n_rows + 255) / 256;
+      if (swiglu) BLOK_BF_LAUNCH(true, 256) else BLOK_BF_LAUNCH(false, 256)
     } else {
-      BLOK_CUDA(cudaFuncSetAttribute(wgemm_tc_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bsmem));
-      wgemm_tc_bf16_kernel<false><<<grid, kTcThreads, bsmem, stream>>>(args);
+      if (swiglu) BLOK_BF_LAUNCH(true, 64) else BLOK_BF_LAUNCH(false, 64)
     }
+#undef BLOK_BF_LAUNCH
     return launch_status("wgemm_tc_bf16_kernel");
   }
   const size_t smem = wgemm_tc_smem_bytes();
