@@ -171,7 +171,28 @@ def other_workload(a, rank, world, device, steps, warmup):
             torch.cuda.synchronize()
 
     peak, peak_kind = measured_peak()
-    if a.workload.startswith("batched"):
+    if a.workload == "model":
+        # config 4 on what ONE GPU holds: layer 0 dense + (model_layers - 1) MoE layers of the full shapes, full
+        # vocabulary, batch 1, greedy decode after a 32-token prompt replay.  A step is one new token through every
+        # layer (embedding, MLA, dense / MoE, final norm, lm_head, argmax); a step reads > 6 GB, far beyond L2.
+        L = a.model_layers
+        model = lib.Model(seed=4 + rank, layers=L, max_batch=1, max_ctx=max(256, 64 + steps + warmup + 8))
+        ids = torch.randint(0, 163840, (1,), device=device, dtype=torch.int32)
+        for _ in range(32):
+            ids = model.step(ids)
+        state = {"ids": ids}
+
+        def run(i):
+            state["ids"] = model.step(state["ids"])
+        moe_bytes = 291767808 + 202244096          # routed-MoE decode layer + MLA projections, per MoE layer
+        dense_bytes = 3 * 18432 * 7168 * 2 + 202244096
+        alg = (L - 1) * moe_bytes + dense_bytes + 163840 * 7168 * 2   # + lm_head; the cache (<= 300 tokens) is negligible
+        unit_tokens = world
+        workload = ("config 4 on one GPU: %d of the 61 layers (1 dense + %d MoE, full shapes), vocab 163840, batch 1, "
+                    "greedy decode%s" % (L, L - 1, "" if world == 1 else ", replicas x%d" % world))
+        scaling = "weak"
+        metric = "decode tok/s, %d-layer model (batch 1)" % L
+    elif a.workload.startswith("batched"):
         T = int(a.workload[len("batched"):])
         Tl = T // world
         per = a.experts // world
@@ -254,10 +275,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=3, help="distinct synthetic layers rotated between steps")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--model-layers", type=int, default=12, help="layers of the `model` workload (one GPU holds about 15)")
     ap.add_argument("--experts", type=int, default=384,
                     help="routed experts per layer; below 384 the run is a reduced case for profiler captures, "
                          "not the benchmark configuration, and the line says so")
-    ap.add_argument("--workload", default="decode", choices=["decode", "batched64", "batched2048", "mla4096", "mla32768"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "batched64", "batched2048", "mla4096", "mla32768", "model"],
                     help="decode = config 1 (the default, the headline metric); batched* = config 2 (expert parallel "
                          "when --gpus > 1); mla* = config 3 (attention block, batch 8)")
     a = ap.parse_args()

@@ -3,13 +3,15 @@
 //
 //   blok-kimi-exec --index <runtime-index.blok> --prompt-tokens <id,id,...> --tokens <n>
 //                  [--synthetic-seed <s>] [--layers <n>] [--experts <n>] [--vocab <n>] [--max-ctx <n>]
+//                  [--hidden --inter --dense-inter --shared-inter --heads --q-rank --kv-rank <n>]
 //
 // Success: exit 0 and exactly one stdout line {"status":"ok","token_ids":[...]}.
 // Failure: a message on stderr and exit 1, which blok/runtime.py:86-94 turns into
 // BlokRuntimeError.  Flags come in pairs and an unknown flag is an error, as in the
-// reference.  Loading a real checkpoint through the runtime index is not built yet:
-// without --synthetic-seed the program says so and exits 1; with it, a model with
-// seeded synthetic weights of the requested size is built on the current GPU.
+// reference.  Every tensor of the forward contract is read ONCE from the files the index
+// names into the model's resident tensors on the current GPU (the model must fit that
+// GPU: the size flags exist for reduced checkpoints and tests).  With --synthetic-seed
+// the index is not read and the weights are seeded synthetic tensors of the requested size.
 #include <cerrno>
 #include <cstdint>
 #include <cstdio>
@@ -51,6 +53,13 @@ int main(int argc, char **argv) {
     else if (f == "--experts") cfg.experts = (int)u64(argv[i + 1], "experts");
     else if (f == "--vocab") cfg.vocab = (int)u64(argv[i + 1], "vocab");
     else if (f == "--max-ctx") cfg.max_ctx = (int)u64(argv[i + 1], "max-ctx");
+    else if (f == "--hidden") cfg.hidden = (int)u64(argv[i + 1], "hidden");
+    else if (f == "--inter") cfg.inter = (int)u64(argv[i + 1], "inter");
+    else if (f == "--dense-inter") cfg.dense_inter = (int)u64(argv[i + 1], "dense-inter");
+    else if (f == "--shared-inter") cfg.shared_inter = (int)u64(argv[i + 1], "shared-inter");
+    else if (f == "--heads") cfg.heads = (int)u64(argv[i + 1], "heads");
+    else if (f == "--q-rank") cfg.q_rank = (int)u64(argv[i + 1], "q-rank");
+    else if (f == "--kv-rank") cfg.kv_rank = (int)u64(argv[i + 1], "kv-rank");
     else die("unknown flag: " + f);
   }
   if ((index.empty() && !synthetic) || prompt.empty() || tokens == 0) die("bad args");
@@ -65,10 +74,14 @@ int main(int argc, char **argv) {
     }
   }
   if (ids.empty()) die("prompt token list is empty");
-  if (!synthetic) die("loading weights from a runtime index is not built; pass --synthetic-seed <n> for seeded synthetic weights");
   if ((uint64_t)cfg.max_ctx < ids.size() + tokens) cfg.max_ctx = (int)(ids.size() + tokens);
+  // --synthetic-seed stands in for the checkpoint: the index is then not read.  Otherwise the index is parsed and
+  // checked against the forward contract before any device memory is taken.
+  if (!synthetic && blok_index_validate(index.c_str(), &cfg, nullptr, nullptr) != BLOK_OK) die(std::string("index: ") + blok_last_error());
   blok_model_t *model = nullptr;
   if (blok_model_create_synthetic(&cfg, seed, &model) != BLOK_OK) die(std::string("model: ") + blok_last_error());
+  // every tensor of the forward contract is read once into the model's resident tensors
+  if (!synthetic && blok_model_load_index(model, index.c_str()) != BLOK_OK) die(std::string("index: ") + blok_last_error());
   std::vector<uint32_t> out(tokens);
   int n = 0;
   if (blok_model_generate(model, ids.data(), (int)ids.size(), (int)tokens, out.data(), &n) != BLOK_OK)

@@ -306,6 +306,16 @@ extern "C" int blok_mla_layer_create(const blok_mla_weights *w, int max_batch, i
   return BLOK_OK;
 }
 
+extern "C" int blok_mla_layer_refresh(blok_mla_layer_t *L) {
+  BLOK_REQUIRE(L, BLOK_ERR_ARG, "blok_mla_layer_refresh: null pointer");
+  const blok_mla_weights &w = L->w;
+  const long total = (long)w.heads * w.kv_rank * w.qk_nope;
+  transpose_wuk_kernel<<<(unsigned)((total + 255) / 256), 256>>>(w.kv_b, L->wuk_t, w.heads, w.qk_nope, w.v_head, w.kv_rank);
+  count_launch();
+  BLOK_CUDA(cudaDeviceSynchronize());
+  return launch_status("transpose_wuk_kernel");
+}
+
 extern "C" int blok_mla_layer_destroy(blok_mla_layer_t *L) {
   if (!L) return BLOK_OK;
   cudaError_t e = L->ws ? cudaFree(L->ws) : cudaSuccess;

@@ -271,6 +271,20 @@ extern "C" int blok_model_tensor(blok_model_t *m, int layer, const char *name, v
   return BLOK_OK;
 }
 
+extern "C" int blok_model_get_config(blok_model_t *m, blok_model_config *cfg) {
+  BLOK_REQUIRE(m && cfg, BLOK_ERR_ARG, "blok_model_get_config: null pointer");
+  *cfg = m->cfg;
+  return BLOK_OK;
+}
+
+extern "C" int blok_model_refresh_derived(blok_model_t *m) {
+  BLOK_REQUIRE(m, BLOK_ERR_ARG, "blok_model_refresh_derived: null pointer");
+  for (auto &L : m->layers)
+    if (L.mla)
+      if (int rc = blok_mla_layer_refresh(L.mla)) return rc;
+  return BLOK_OK;
+}
+
 extern "C" int blok_model_reset(blok_model_t *m) {
   BLOK_REQUIRE(m, BLOK_ERR_ARG, "blok_model_reset: null pointer");
   BLOK_CUDA(cudaMemset(m->pos, 0, m->cfg.max_batch * 4));

@@ -401,6 +401,23 @@ class ModelConfig(C.Structure):
                [("max_batch", C.c_int), ("max_ctx", C.c_int), ("eos_id", C.c_uint32)]
 
 
+def index_validate(path, cfg):
+    """Parses a runtime index and checks the forward contract for cfg (no GPU needed): (tensors, bytes) to load."""
+    n, b = C.c_long(0), C.c_ulonglong(0)
+    _check(load().blok_index_validate(str(path).encode(), C.byref(cfg), C.byref(n), C.byref(b)))
+    return n.value, b.value
+
+
+def default_model_config(**overrides):
+    cfg = ModelConfig()
+    load().blok_model_default_config(C.byref(cfg))
+    for k, v in overrides.items():
+        if not hasattr(cfg, k):
+            raise BlokError(-1, "unknown model config field %r" % k)
+        setattr(cfg, k, v)
+    return cfg
+
+
 _cudart = None
 
 
@@ -465,6 +482,10 @@ class Model:
         rc = _rt().cudaMemcpy(ptr, array.ctypes.data_as(C.c_void_p), C.c_size_t(nbytes.value), C.c_int(1))
         if rc != 0:
             raise BlokError(-3, "cudaMemcpy H2D failed: %d" % rc)
+
+    def load_index(self, path):
+        """Replace the weights by the checkpoint a runtime index describes (blok_model_load_index)."""
+        _check(load().blok_model_load_index(self._handle, str(path).encode()))
 
     def reset(self):
         _check(load().blok_model_reset(self._handle))

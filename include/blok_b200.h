@@ -275,6 +275,9 @@ typedef struct blok_mla_layer blok_mla_layer_t;
  * max_ctx cached tokens each, and a transposed copy of the W_UK half of kv_b. */
 int blok_mla_layer_create(const blok_mla_weights *weights, int max_batch, int max_ctx, blok_mla_layer_t **out);
 int blok_mla_layer_destroy(blok_mla_layer_t *layer);
+/* Rebuilds what create derived from the weights (the transposed W_UK copy) after the caller has overwritten kv_b in
+ * place.  Synchronises the device. */
+int blok_mla_layer_refresh(blok_mla_layer_t *layer);
 
 /* One decode step of the attention block for B sequences, one new token each.
  * Replaces src/kimi_exec.cu:813-826 (q_a -> norm -> q_b, kv_a -> norm, RoPE,
@@ -361,6 +364,27 @@ int blok_model_destroy(blok_model_t *model);
  * "router", "router_bias", "gate_w", "gate_s", "up_w", "up_s", "down_w", "down_s",
  * "shared_gate", "shared_up", "shared_down" (the slot names of the reference's index). */
 int blok_model_tensor(blok_model_t *model, int layer, const char *name, void **ptr, size_t *bytes);
+
+/* The configuration the model was created with. */
+int blok_model_get_config(blok_model_t *model, blok_model_config *cfg);
+
+/* After weights were overwritten in place through blok_model_tensor: rebuilds the copies derived from them at
+ * creation (each layer's transposed W_UK). */
+int blok_model_refresh_derived(blok_model_t *model);
+
+/* Loads a materialised checkpoint into the model's resident tensors.  `index_path` is the text index
+ * "blok-runtime-index-v1" written by the reference's scripts/model_fetch.py:113-127 (one line of 14 fields per
+ * tensor: name role layer expert slot dtype shape off bytes align data data_bytes file).  Replaces runtime_index
+ * (src/kimi_exec.cu:559-581) and validate_forward_contract (:736-778) with the shapes taken from the model's
+ * configuration, and the reference's per-token tile reads with ONE read of every tensor: pread of the byte range
+ * [data, data + data_bytes) of `file`, staged through pinned memory into HBM (routed experts into their slice of the
+ * expert-major arrays, the router's bf16 correction bias widened to fp32).  Any missing tensor, wrong type, shape,
+ * byte count or extent is an error and names the tensor. */
+int blok_model_load_index(blok_model_t *model, const char *index_path);
+
+/* The same checks without a model or a GPU: parses the index and verifies the forward contract for cfg.  Returns the
+ * number of tensors the model would load and their total bytes. */
+int blok_index_validate(const char *index_path, const blok_model_config *cfg, long *n_tensors, unsigned long long *n_bytes);
 
 /* Forgets all cached tokens (positions restart at 0). */
 int blok_model_reset(blok_model_t *model);

@@ -128,3 +128,31 @@ def test_generate_replays_prompt_and_stops(cuda, oracle):
     assert m2.generate(prompt, 6) == []
     m2.close()
     model.close()
+
+
+def test_load_index_replaces_every_weight(cuda, tmp_path):
+    """Model B (other seed) loads the checkpoint dumped from model A: every tensor equals A's, and B generates A's tokens."""
+    from blok_b200 import lib
+    a = lib.Model(seed=31, **CFG)
+    b = lib.Model(seed=32, **CFG)
+    prompt = [3, 1, 4, 1, 5]
+    want = a.generate(prompt, 8)
+    assert b.generate(prompt, 8) != want
+    tensors = util.checkpoint_tensors(a.cfg, lambda l, n, dt, sh: a.tensor(l, n, dt, sh))
+    path = util.write_checkpoint(str(tmp_path), tensors, shards=3)
+    b.load_index(path)
+    for l, name, dt in ((-1, "lm_head", np.uint16), (0, "down_proj", np.uint16), (1, "router_bias", np.float32),
+                        (2, "gate_w", np.uint32), (2, "down_s", np.uint16), (1, "kv_b_proj", np.uint16)):
+        ta, tb = a.tensor(l, name, dt), b.tensor(l, name, dt)
+        if name == "router_bias":  # stored as bf16 in a checkpoint
+            ta = util.bf16_np_to_f32(util.f32_to_bf16_np(ta))
+        assert np.array_equal(ta, tb), (l, name)
+    b.reset()
+    got = b.generate(prompt, 8)
+    # the router bias lost its low mantissa bits on the way through the checkpoint; A with the same bias must agree
+    a.write_tensor(1, "router_bias", util.bf16_np_to_f32(util.f32_to_bf16_np(a.tensor(1, "router_bias", np.float32))))
+    a.write_tensor(2, "router_bias", util.bf16_np_to_f32(util.f32_to_bf16_np(a.tensor(2, "router_bias", np.float32))))
+    a.reset()
+    assert got == a.generate(prompt, 8)
+    a.close()
+    b.close()

@@ -82,3 +82,84 @@ def np_bf16_to_torch(h, device):
 
 def np_u32_to_torch(w, device):
     return torch.from_numpy(np.ascontiguousarray(w, np.uint32).view(np.int32)).to(device)
+
+
+# ---- a materialised checkpoint in miniature: shard files plus the text index of scripts/model_fetch.py:113-127 ----
+
+def checkpoint_tensors(cfg, get):
+    """The tensors of the forward contract (src/kimi_exec.cu:736-778) for a model configuration, as
+    (name, role, layer, expert, slot, dtype, shape, array) with the checkpoint's naming.  get(layer, model_name,
+    dtype, shape) returns the numpy array of a model tensor; the router bias comes back fp32 and is stored as bf16."""
+    H, c = cfg.hidden, cfg
+    qk, kvo, lat = c.qk_nope + c.qk_rope, c.qk_nope + c.v_head, c.kv_rank + c.qk_rope
+    out = []
+
+    def bf(layer, role, slot, model_name, rows, cols=0):
+        shape = (rows, cols) if cols else (rows,)
+        prefix = "language_model.model.layers.%d." % layer if layer >= 0 else "language_model."
+        out.append((prefix + slot + ".weight", role, layer, -1, slot, "bf16", shape, get(layer, model_name, np.uint16, shape)))
+
+    for l in range(c.layers):
+        bf(l, "attention_resident", "q_a_proj", "q_a_proj", c.q_rank, H)
+        bf(l, "attention_resident", "q_a_layernorm", "q_a_layernorm", c.q_rank)
+        bf(l, "attention_resident", "q_b_proj", "q_b_proj", c.heads * qk, c.q_rank)
+        bf(l, "attention_resident", "kv_a_proj_with_mqa", "kv_a_proj_with_mqa", lat, H)
+        bf(l, "attention_resident", "kv_a_layernorm", "kv_a_layernorm", c.kv_rank)
+        bf(l, "attention_resident", "kv_b_proj", "kv_b_proj", c.heads * kvo, c.kv_rank)
+        bf(l, "attention_resident", "o_proj", "o_proj", H, c.heads * c.v_head)
+        bf(l, "resident", "input_layernorm", "input_layernorm", H)
+        bf(l, "resident", "post_attention_layernorm", "post_attention_layernorm", H)
+        if l < c.first_dense:
+            bf(l, "dense_ffn_rowcol", "gate_proj", "gate_proj", c.dense_inter, H)
+            bf(l, "dense_ffn_rowcol", "up_proj", "up_proj", c.dense_inter, H)
+            bf(l, "dense_ffn_rowcol", "down_proj", "down_proj", H, c.dense_inter)
+            continue
+        bf(l, "router", "gate", "router", c.experts, H)
+        bias = f32_to_bf16_np(get(l, "router_bias", np.float32, (c.experts,)))
+        out.append(("language_model.model.layers.%d.mlp.gate.e_score_correction_bias" % l, "router", l, -1,
+                    "e_score_correction_bias", "bf16", (c.experts,), bias))
+        if c.shared_inter:
+            bf(l, "shared_expert_resident", "gate_proj", "shared_gate", c.shared_inter, H)
+            bf(l, "shared_expert_resident", "up_proj", "shared_up", c.shared_inter, H)
+            bf(l, "shared_expert_resident", "down_proj", "shared_down", H, c.shared_inter)
+        for proj, wn, sn, rows, cols in (("gate_proj", "gate_w", "gate_s", c.inter, H), ("up_proj", "up_w", "up_s", c.inter, H),
+                                         ("down_proj", "down_w", "down_s", H, c.inter)):
+            w = get(l, wn, np.uint32, (c.experts, rows, cols // 8))
+            s = get(l, sn, np.uint16, (c.experts, rows, cols // 32))
+            for e in range(c.experts):
+                base = "language_model.model.layers.%d.mlp.experts.%d.%s." % (l, e, proj)
+                out.append((base + "weight_packed", "routed_expert", l, e, proj + ".weight_packed", "i32", (rows, cols // 8), w[e]))
+                out.append((base + "weight_scale", "routed_expert", l, e, proj + ".weight_scale", "bf16", (rows, cols // 32), s[e]))
+    bf(-1, "resident", "embed_tokens", "embed_tokens", c.vocab, H)
+    bf(-1, "resident", "norm", "norm", H)
+    bf(-1, "resident", "lm_head", "lm_head", c.vocab, H)
+    return out
+
+
+def write_checkpoint(directory, tensors, shards=2, lead=8 + 1234):
+    """Writes the tensors into `shards` files at unaligned offsets (a safetensors file starts with an 8-byte length and
+    a JSON header) and returns the path of the runtime index describing them; 4 KiB-aligned read extents as the
+    reference's materialize step computes them."""
+    import os
+    files = [open(os.path.join(directory, "model-%05d.safetensors" % i), "wb") for i in range(shards)]
+    for f in files:
+        f.write(b"\0" * lead)
+    lines = ["blok-runtime-index-v1"]
+    for i, (name, role, layer, expert, slot, dtype, shape, arr) in enumerate(tensors):
+        f = files[i % shards]
+        raw = np.ascontiguousarray(arr).tobytes()
+        start = f.tell()
+        f.write(raw)
+        f.write(b"\0" * (3 + i % 5))  # neighbours are not aligned to anything
+        off = start // 4096 * 4096
+        end = (start + len(raw) + 4095) // 4096 * 4096
+        lines.append("tensor %s %s %d %d %s %s %s %d %d 4096 %d %d %s" % (name, role, layer, expert, slot, dtype,
+                                                                            "x".join(str(d) for d in shape), off, end - off, start,
+                                                                            len(raw), f.name))
+    for f in files:
+        f.write(b"\0" * 4096)
+        f.close()
+    path = os.path.join(directory, "runtime-index.blok")
+    with open(path, "w") as fh:
+        fh.write("\n".join(lines) + "\n")
+    return path
