@@ -235,16 +235,20 @@ def other_workload(a, rank, world, device, steps, warmup):
         workload = "config 3: MLA absorbed decode block, batch 8, ctx %d, bf16 latent cache%s" % (ctx, "" if world == 1 else ", replicas x%d" % world)
         scaling = "weak"
         metric = "tok/s, MLA decode block (batch 8, ctx %d)" % ctx
-    for i in range(max(warmup, 3)):
-        run(i)
-    barrier()
-    l0 = lib.kernel_launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(steps):
-        run(warmup + i)
-    e1.record()
-    barrier()
+    # a side stream: the whole-model step replays a CUDA graph, which the legacy default stream cannot capture
+    side = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        for i in range(max(warmup, 3)):
+            run(i)
+        barrier()
+        l0 = lib.kernel_launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            run(warmup + i)
+        e1.record()
+        barrier()
     launches = lib.kernel_launch_count() - l0
     ms = torch.tensor([e0.elapsed_time(e1)], device=device)
     if world > 1:

@@ -109,16 +109,40 @@ __global__ void bf16_gemv_scalar_kernel(const uint16_t *__restrict__ w, const ui
   }
 }
 
-// One CTA per token.
-__global__ void rmsnorm_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__ w,
-                               uint16_t *__restrict__ y, int n, float eps) {
+// One CTA per token.  The row is read once with 16-byte loads, all of them in flight before the first use (a row of
+// up to 256 x 4 x 8 = 8192 values stays in registers between the sum and the scaling); longer or unaligned rows take
+// the element loop.
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__ w,
+                                                      uint16_t *__restrict__ y, int n, float eps) {
   __shared__ float red[32];
   const uint16_t *xr = x + (size_t)blockIdx.x * n;
   uint16_t *yr = y + (size_t)blockIdx.x * n;
+  const bool vec = (n % 8 == 0) && n <= 8192 && ((reinterpret_cast<uintptr_t>(xr) | reinterpret_cast<uintptr_t>(yr) |
+                                                  reinterpret_cast<uintptr_t>(w)) & 15) == 0;
   float v = 0.f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    float a = bf16_bits_to_f32(xr[i]);
-    v = fmaf(a, a, v);
+  uint4 xv[4];
+  const int nu = n / 8;
+  if (vec) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int u = threadIdx.x + k * 256;
+      xv[k] = u < nu ? reinterpret_cast<const uint4 *>(xr)[u] : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t q[4] = {xv[k].x, xv[k].y, xv[k].z, xv[k].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lo = bf16lo(q[j]), hi = bf16hi(q[j]);
+        v = fmaf(lo, lo, v);
+        v = fmaf(hi, hi, v);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      float a = bf16_bits_to_f32(xr[i]);
+      v = fmaf(a, a, v);
+    }
   }
   v = warp_sum(v);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
@@ -129,13 +153,31 @@ __global__ void rmsnorm_kernel(const uint16_t *__restrict__ x, const uint16_t *_
     if (threadIdx.x == 0) red[0] = s;
   }
   __syncthreads();
-  float scale = rsqrtf(red[0] / n + eps);
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    float a = bf16_bits_to_f32(xr[i]);
-    yr[i] = f32_to_bf16_bits(round_bf16(a * scale) * bf16_bits_to_f32(w[i]));
+  const float scale = rsqrtf(red[0] / n + eps);
+  if (vec) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int u = threadIdx.x + k * 256;
+      if (u < nu) {
+        const uint4 wv = reinterpret_cast<const uint4 *>(w)[u];
+        const uint32_t q[4] = {xv[k].x, xv[k].y, xv[k].z, xv[k].w}, ww[4] = {wv.x, wv.y, wv.z, wv.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t lo = f32_to_bf16_bits(round_bf16(bf16lo(q[j]) * scale) * bf16lo(ww[j]));
+          const uint32_t hi = f32_to_bf16_bits(round_bf16(bf16hi(q[j]) * scale) * bf16hi(ww[j]));
+          o[j] = lo | (hi << 16);
+        }
+        reinterpret_cast<uint4 *>(yr)[u] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      float a = bf16_bits_to_f32(xr[i]);
+      yr[i] = f32_to_bf16_bits(round_bf16(a * scale) * bf16_bits_to_f32(w[i]));
+    }
   }
 }
-
 __global__ void add_bf16_kernel(uint16_t *__restrict__ a, const uint16_t *__restrict__ b, long n) {
   long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) a[i] = f32_to_bf16_bits(bf16_bits_to_f32(a[i]) + bf16_bits_to_f32(b[i]));

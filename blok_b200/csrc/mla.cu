@@ -152,21 +152,33 @@ __global__ void transpose_wuk_kernel(const uint16_t *__restrict__ kv_b, uint16_t
 // ---------------------------------------------------------------------------
 __global__ void mla_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml, int splits,
                                  int heads, int kv_rank, uint16_t *__restrict__ o_lat) {
-  const int h = blockIdx.x, b = blockIdx.y;
+  extern __shared__ float s_wt[];  // [splits] weight of every split: exp(m_s - M), 0 for an empty split
+  __shared__ float s_red[2][4];
+  const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+  const float *ml = part_ml + ((size_t)b * splits * heads + h) * 2;  // split s at + s * heads * 2
   float M = -INFINITY;
-  for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(((size_t)b * splits + s) * heads + h) * 2]);
+  for (int s = tid; s < splits; s += blockDim.x) M = fmaxf(M, ml[(size_t)s * heads * 2]);
+  M = warp_max(M);
+  if ((tid & 31) == 0) s_red[0][tid >> 5] = M;
+  __syncthreads();
+  M = fmaxf(fmaxf(s_red[0][0], s_red[0][1]), fmaxf(s_red[0][2], s_red[0][3]));
   float L = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float *ml = part_ml + (((size_t)b * splits + s) * heads + h) * 2;
-    if (ml[0] != -INFINITY) L += expf(ml[0] - M) * ml[1];
+  for (int s = tid; s < splits; s += blockDim.x) {
+    const float m = ml[(size_t)s * heads * 2];
+    const float wt = m != -INFINITY ? expf(m - M) : 0.f;
+    s_wt[s] = wt;
+    L += wt * ml[(size_t)s * heads * 2 + 1];
   }
+  L = warp_sum(L);
+  if ((tid & 31) == 0) s_red[1][tid >> 5] = L;
+  __syncthreads();
+  L = (s_red[1][0] + s_red[1][1]) + (s_red[1][2] + s_red[1][3]);
   const float inv = L > 0.f ? 1.0f / L : 0.f;
-  for (int j = threadIdx.x; j < kv_rank; j += blockDim.x) {
+  const float *po = part_o + ((size_t)b * splits * heads + h) * kv_rank;  // split s at + s * heads * kv_rank
+  for (int j = tid; j < kv_rank; j += blockDim.x) {
     float acc = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float m = part_ml[(((size_t)b * splits + s) * heads + h) * 2];
-      if (m != -INFINITY) acc += expf(m - M) * part_o[(((size_t)b * splits + s) * heads + h) * kv_rank + j];
-    }
+#pragma unroll 4
+    for (int s = 0; s < splits; ++s) acc = fmaf(s_wt[s], po[(size_t)s * heads * kv_rank + j], acc);
     o_lat[((size_t)b * heads + h) * kv_rank + j] = f32_to_bf16_bits(acc * inv);
   }
 }
@@ -323,17 +335,22 @@ extern "C" int blok_mla_layer_destroy(blok_mla_layer_t *L) {
   return e == cudaSuccess ? BLOK_OK : cuda_fail(e, "cudaFree(mla layer workspace)");
 }
 
-static int splits_for(const blok_mla_layer *L, int B) {
-  int s = L->max_splits / B;
-  return s < 1 ? 1 : s;
+// Context splits per sequence: enough CTAs to fill the GPU, but never more than one per 64 rows of the cache
+// allocation (the sequence lengths live on the device; ctx_stride bounds them), so that a short cache is not cut
+// into slivers whose merge costs more than the attention.
+static int splits_for(const blok_mla_layer *L, int B, long ctx_stride) {
+  long s = L->max_splits / B;
+  const long cap = (ctx_stride + 63) / 64;
+  if (s > cap) s = cap;
+  return s < 1 ? 1 : (int)s;
 }
 
 static int attend_and_merge(blok_mla_layer *L, const uint16_t *q, const uint16_t *cache, long ctx_stride,
                             const int *seq_len, int B, float scale, uint16_t *o_lat, cudaStream_t stream) {
-  const int splits = splits_for(L, B);
+  const int splits = splits_for(L, B, ctx_stride);
   int rc = launch_mla_attend(q, cache, ctx_stride, seq_len, B, splits, scale, L->part_o, L->part_ml, stream);
   if (rc) return rc;
-  mla_merge_kernel<<<dim3(L->w.heads, B), 128, 0, stream>>>(L->part_o, L->part_ml, splits, L->w.heads, L->w.kv_rank,
+  mla_merge_kernel<<<dim3(L->w.heads, B), 128, (size_t)splits * sizeof(float), stream>>>(L->part_o, L->part_ml, splits, L->w.heads, L->w.kv_rank,
                                                            o_lat);
   return launch_status("mla_merge_kernel");
 }

@@ -75,6 +75,11 @@ struct blok_model {
   void *head_ws = nullptr;
   size_t head_ws_bytes = 0;
   uint64_t seed = 0, counter = 0;
+  // One CUDA graph of the whole step per batch size: a step is ~16 small launches per layer and the host cannot issue
+  // them as fast as the GPU runs them.  steps_seen counts eager steps (the first one also sets kernel attributes).
+  cudaGraphExec_t step_graph[9] = {};
+  int steps_seen[9] = {};
+  bool graphs_enabled = true;
 };
 
 using namespace blok;
@@ -224,6 +229,9 @@ extern "C" void blok_model_default_config(blok_model_config *c) {
 }
 
 extern "C" int blok_model_destroy(blok_model_t *m) {
+  if (m)
+    for (auto &g : m->step_graph)
+      if (g) cudaGraphExecDestroy(g);
   if (!m) return BLOK_OK;
   for (auto &L : m->layers) {
     if (L.mla) blok_mla_layer_destroy(L.mla);
@@ -249,6 +257,7 @@ extern "C" int blok_model_create_synthetic(const blok_model_config *cfg, uint64_
   BLOK_REQUIRE(m, BLOK_ERR_ARG, "blok_model_create_synthetic: out of host memory");
   m->cfg = *cfg;
   m->seed = seed;
+  if (const char *g = getenv("BLOK_MODEL_GRAPH")) m->graphs_enabled = strcmp(g, "0") != 0;  // BLOK_MODEL_GRAPH=0: eager launches
   int rc = build(m);
   if (rc) {
     blok_model_destroy(m);
@@ -291,14 +300,14 @@ extern "C" int blok_model_reset(blok_model_t *m) {
   return BLOK_OK;
 }
 
-extern "C" int blok_model_step(blok_model_t *m, const uint32_t *ids, int B, uint32_t *next_ids, blok_stream_t stream_) {
-  BLOK_REQUIRE(m && ids && next_ids, BLOK_ERR_ARG, "blok_model_step: null pointer");
-  BLOK_REQUIRE(B >= 1 && B <= m->cfg.max_batch, BLOK_ERR_SHAPE, "blok_model_step: B=%d outside [1, %d]", B, m->cfg.max_batch);
+// The launches of one decode step on `stream`, reading m->ids and writing m->next; every position and length is device
+// resident, so the same sequence of launches serves every step and can be replayed from a graph.
+static int step_body(blok_model_t *m, int B, blok_stream_t stream_) {
   const blok_model_config &c = m->cfg;
   cudaStream_t stream = (cudaStream_t)stream_;
   const size_t H = c.hidden;
   int rc;
-  if ((rc = blok_embed(tp<uint16_t>(m->top, "embed_tokens"), ids, c.vocab, c.hidden, B, m->x, stream_))) return rc;  // :802
+  if ((rc = blok_embed(tp<uint16_t>(m->top, "embed_tokens"), m->ids, c.vocab, c.hidden, B, m->x, stream_))) return rc;  // :802
   for (int l = 0; l < c.layers; ++l) {
     auto &L = m->layers[l];
     // attention block, :812-827
@@ -319,11 +328,51 @@ extern "C" int blok_model_step(blok_model_t *m, const uint32_t *ids, int B, uint
     if ((rc = blok_add_bf16(m->x, m->tmp, (long)B * H, stream_))) return rc;
   }
   if ((rc = blok_rmsnorm(m->x, tp<uint16_t>(m->top, "norm"), m->n, B, c.hidden, c.final_rms_eps, stream_))) return rc;  // :880
-  if ((rc = blok_lm_head_argmax(tp<uint16_t>(m->top, "lm_head"), m->n, c.vocab, c.hidden, B, next_ids, m->head_ws,
+  if ((rc = blok_lm_head_argmax(tp<uint16_t>(m->top, "lm_head"), m->n, c.vocab, c.hidden, B, m->next, m->head_ws,
                                 m->head_ws_bytes, stream_)))
     return rc;
   advance_kernel<<<1, 32, 0, stream>>>(m->pos, B);
   return launch_status("advance_kernel");
+}
+
+extern "C" int blok_model_step(blok_model_t *m, const uint32_t *ids, int B, uint32_t *next_ids, blok_stream_t stream_) {
+  BLOK_REQUIRE(m && ids && next_ids, BLOK_ERR_ARG, "blok_model_step: null pointer");
+  BLOK_REQUIRE(B >= 1 && B <= m->cfg.max_batch && B <= 8, BLOK_ERR_SHAPE, "blok_model_step: B=%d outside [1, %d]", B,
+               m->cfg.max_batch);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (ids != m->ids) BLOK_CUDA(cudaMemcpyAsync(m->ids, ids, (size_t)B * 4, cudaMemcpyDeviceToDevice, stream));
+  int rc = BLOK_OK;
+  // The first step of a batch size runs eagerly, the second is captured (nothing executes during capture) and
+  // replayed at once, later steps replay the graph.  The legacy default stream cannot be captured.
+  const bool can_graph = m->graphs_enabled && stream != nullptr && stream != cudaStreamLegacy;
+  if (can_graph && m->step_graph[B]) {
+    BLOK_CUDA(cudaGraphLaunch(m->step_graph[B], stream));
+  } else if (can_graph && m->steps_seen[B] >= 1) {
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal);
+    if (e == cudaSuccess) {
+      rc = step_body(m, B, stream_);
+      cudaError_t e2 = cudaStreamEndCapture(stream, &graph);
+      if (rc == BLOK_OK && e2 == cudaSuccess && graph) e = cudaGraphInstantiate(&m->step_graph[B], graph, 0);
+      else e = e2 == cudaSuccess ? cudaErrorUnknown : e2;
+      if (graph) cudaGraphDestroy(graph);
+    }
+    if (e != cudaSuccess || !m->step_graph[B]) {  // capture is not possible here: stay with eager launches
+      cudaGetLastError();
+      m->step_graph[B] = nullptr;
+      m->graphs_enabled = false;
+      rc = step_body(m, B, stream_);
+    } else {
+      BLOK_CUDA(cudaGraphLaunch(m->step_graph[B], stream));
+      rc = BLOK_OK;
+    }
+  } else {
+    rc = step_body(m, B, stream_);
+    ++m->steps_seen[B];
+  }
+  if (rc) return rc;
+  if (next_ids != m->next) BLOK_CUDA(cudaMemcpyAsync(next_ids, m->next, (size_t)B * 4, cudaMemcpyDeviceToDevice, stream));
+  return BLOK_OK;
 }
 
 extern "C" int blok_model_generate(blok_model_t *m, const uint32_t *prompt, int n_prompt, int max_new, uint32_t *out,
