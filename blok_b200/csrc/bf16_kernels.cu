@@ -8,6 +8,8 @@
 // bf16 (one uint4) at column 8t of each of its two rows.  The B operand's column n
 // is token n, so lane (g, t) reads the same 8 columns of token g's activation row
 // from shared memory.  D[row][token] accumulates in fp32.
+#include <algorithm>
+
 #include "bf16_mma.cuh"
 
 namespace blok {
@@ -109,6 +111,67 @@ __global__ void bf16_gemv_scalar_kernel(const uint16_t *__restrict__ w, const ui
   }
 }
 
+// Split-K form of the plain mat-vec for matrices with few rows (q_a 1536, kv_a 576 rows): grid = (rows / 16, ksplit),
+// so that every SM streams weights whatever the row count, and a CTA stages only its own K-range of the
+// activations.  Partial sums go to `part` ([ksplit][rows / 16][16][8] fp32); the CTA that draws the last ticket of a
+// row block adds them in split order (deterministic) and writes the rounded result, then re-arms the ticket.
+__global__ void __launch_bounds__(128) bf16_gemv16_splitk_kernel(const uint16_t *__restrict__ w, const uint16_t *__restrict__ x,
+                                                                 uint16_t *__restrict__ y_bf16, float *__restrict__ y_f32,
+                                                                 int rows, int cols, int T, int ksteps_per_split,
+                                                                 float *__restrict__ part, unsigned *__restrict__ tickets) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  __shared__ float partial[4][16][8];
+  __shared__ unsigned s_ticket;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int ksteps = cols / 32;
+  const int kbeg = blockIdx.y * ksteps_per_split;
+  const int kn = min(ksteps_per_split, ksteps - kbeg);  // k-steps of this CTA
+  // stage x[:, 32 kbeg .. 32 (kbeg + kn)) with the row skew of stage_x_bf16
+  const int per_row = kn * 4;  // uint4 per token row
+  const size_t row_bytes = bf16_x_row_bytes(kn * 32);
+  for (int u = tid; u < per_row * T; u += blockDim.x) {
+    const int tok = u / per_row, c = u - tok * per_row;
+    reinterpret_cast<uint4 *>(smem + tok * row_bytes)[c] = reinterpret_cast<const uint4 *>(x + (size_t)tok * cols)[kbeg * 4 + c];
+  }
+  __syncthreads();
+  const size_t wrow = cols / 8;
+  const uint4 *w_lo = reinterpret_cast<const uint4 *>(w) + (size_t)(blockIdx.x * 16 + g) * wrow + (size_t)kbeg * 4;
+  const uint4 *w_hi = w_lo + 8 * wrow;
+  const int tok = g < T ? g : T - 1;
+  const uint4 *xrow = reinterpret_cast<const uint4 *>(smem + tok * row_bytes) + t;
+  const int base = kn / 4, rem = kn % 4;
+  const int ks0 = warp * base + (warp < rem ? warp : rem);
+  const int nsteps = base + (warp < rem ? 1 : 0);
+  float d[4] = {0.f, 0.f, 0.f, 0.f};
+  bf16_rows16_accumulate(w_lo, w_hi, xrow, ks0, nsteps, t, d);
+  partial[warp][g][2 * t] = d[0];
+  partial[warp][g][2 * t + 1] = d[1];
+  partial[warp][g + 8][2 * t] = d[2];
+  partial[warp][g + 8][2 * t + 1] = d[3];
+  __syncthreads();
+  const int r = tid >> 3, tk = tid & 7;  // 128 threads = 16 rows x 8 tokens
+  float v = (partial[0][r][tk] + partial[1][r][tk]) + (partial[2][r][tk] + partial[3][r][tk]);
+  const int nsplit = gridDim.y;
+  if (nsplit > 1) {
+    part[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 128 + tid] = v;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_ticket = atomicAdd(tickets + blockIdx.x, 1u);
+    __syncthreads();
+    if (s_ticket != (unsigned)nsplit - 1) return;
+    __threadfence();
+    v = 0.f;
+    for (int sidx = 0; sidx < nsplit; ++sidx) v += __ldcg(part + ((size_t)sidx * gridDim.x + blockIdx.x) * 128 + tid);
+    if (tid == 0) tickets[blockIdx.x] = 0;
+  }
+  if (tk < T) {
+    const size_t o = (size_t)tk * rows + blockIdx.x * 16 + r;
+    if (y_f32) y_f32[o] = v;
+    else y_bf16[o] = f32_to_bf16_bits(v);
+  }
+}
+
 // One CTA per token.  The row is read once with 16-byte loads, all of them in flight before the first use (a row of
 // up to 256 x 4 x 8 = 8192 values stays in registers between the sum and the scaling); longer or unaligned rows take
 // the element loop.
@@ -199,6 +262,35 @@ int launch_bf16_gemv(const uint16_t *w, const uint16_t *x, uint16_t *y_bf16, flo
   bf16_gemv_scalar_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(w, x, y_bf16, y_f32, rows, cols, T);
   return launch_status("bf16_gemv_scalar_kernel");
 }
+
+// Bytes of workspace launch_bf16_gemv_splitk may need for a matrix of `rows` rows: 512 bytes of partial sums per CTA
+// (splits x row blocks < 4 SMs' worth + row blocks), then one ticket per row block.
+static size_t splitk_part_bytes(int rows) { return ((size_t)4 * sm_count() + rows / 16) * 128 * 4; }
+size_t bf16_gemv_splitk_workspace_bytes(int rows) { return splitk_part_bytes(rows) + (size_t)(rows / 16) * 4 + 256; }
+
+// The mat-vec with as many K-splits as it takes to put about four CTAs on every SM; falls back to the one-CTA-per-
+// row-block kernel when the matrix has enough rows or the shape does not fit.  `ws` must be zero before the first call
+// (the tickets re-arm themselves) and is used by one launch at a time.
+int launch_bf16_gemv_splitk(const uint16_t *w, const uint16_t *x, uint16_t *y_bf16, float *y_f32, int rows, int cols, int T,
+                            void *ws, size_t ws_bytes, cudaStream_t stream) {
+  const int rb = rows / 16, ksteps = cols / 32;
+  int ksplit = rb > 0 ? (4 * sm_count() + rb - 1) / rb : 1;
+  ksplit = std::min(ksplit, std::min(32, ksteps / 8));
+  const bool ok = rows % 16 == 0 && cols % 32 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 &&
+                  (reinterpret_cast<uintptr_t>(x) & 15) == 0 && T >= 1 && T <= 8 && ws &&
+                  ws_bytes >= bf16_gemv_splitk_workspace_bytes(rows);
+  if (!ok || ksplit < 2) return launch_bf16_gemv(w, x, y_bf16, y_f32, rows, cols, T, stream);
+  const int per = (ksteps + ksplit - 1) / ksplit;
+  ksplit = (ksteps + per - 1) / per;
+  float *part = static_cast<float *>(ws);
+  unsigned *tickets = reinterpret_cast<unsigned *>(static_cast<unsigned char *>(ws) + splitk_part_bytes(rows));
+  const size_t smem = bf16_x_row_bytes(per * 32) * T;
+  if (smem > 48 * 1024)
+    BLOK_CUDA(cudaFuncSetAttribute(bf16_gemv16_splitk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  bf16_gemv16_splitk_kernel<<<dim3(rb, ksplit), 128, smem, stream>>>(w, x, y_bf16, y_f32, rows, cols, T, per, part, tickets);
+  return launch_status("bf16_gemv16_splitk_kernel");
+}
+
 
 // mid[T, ffn] = SwiGLU front half.
 int launch_bf16_gateup(const uint16_t *gate, const uint16_t *up, const uint16_t *x, uint16_t *mid, int ffn, int cols,

@@ -22,6 +22,9 @@ namespace blok {
 
 int launch_bf16_gemv(const uint16_t *w, const uint16_t *x, uint16_t *y_bf16, float *y_f32, int rows, int cols, int T,
                      cudaStream_t stream);
+size_t bf16_gemv_splitk_workspace_bytes(int rows);
+int launch_bf16_gemv_splitk(const uint16_t *w, const uint16_t *x, uint16_t *y_bf16, float *y_f32, int rows, int cols, int T,
+                            void *ws, size_t ws_bytes, cudaStream_t stream);
 
 // ---------------------------------------------------------------------------
 // Per-head mat-vec for up to 8 tokens: y[tok, head, r] = sum_c W[head][r][c] * x[tok, head, c].
@@ -215,6 +218,8 @@ struct blok_mla_layer {
   uint16_t *o_lat = nullptr;   // [B, heads, kv_rank]
   uint16_t *av = nullptr;      // [B, heads * v_head]
   int *seq = nullptr;          // [B]
+  void *sk_ws = nullptr;       // split-K partial sums and tickets of the projections (zeroed at create)
+  size_t sk_bytes = 0;
   float *part_o = nullptr;     // [max_splits * max_batch..]
   float *part_ml = nullptr;
 };
@@ -281,10 +286,18 @@ extern "C" int blok_mla_layer_create(const blok_mla_weights *w, int max_batch, i
   size_t o_seq = take((size_t)max_batch * 4);
   size_t o_po = take((size_t)(L->max_splits + max_batch) * w->heads * w->kv_rank * 4);
   size_t o_pml = take((size_t)(L->max_splits + max_batch) * w->heads * 2 * 4);
+  L->sk_bytes = bf16_gemv_splitk_workspace_bytes(std::max(std::max(w->q_rank, lat_w), std::max(w->heads * qk_head, w->hidden)));
+  size_t o_sk = take(L->sk_bytes);
   cudaError_t e = cudaMalloc(&L->ws, off);
   if (e != cudaSuccess) {
     delete L;
     return cuda_fail(e, "cudaMalloc(mla layer workspace)");
+  }
+  e = cudaMemset(L->ws, 0, off);  // the split-K tickets start at zero
+  if (e != cudaSuccess) {
+    cudaFree(L->ws);
+    delete L;
+    return cuda_fail(e, "cudaMemset(mla layer workspace)");
   }
   unsigned char *b = static_cast<unsigned char *>(L->ws);
   L->wuk_t = reinterpret_cast<uint16_t *>(b + o_wuk);
@@ -298,6 +311,7 @@ extern "C" int blok_mla_layer_create(const blok_mla_weights *w, int max_batch, i
   L->seq = reinterpret_cast<int *>(b + o_seq);
   L->part_o = reinterpret_cast<float *>(b + o_po);
   L->part_ml = reinterpret_cast<float *>(b + o_pml);
+  L->sk_ws = b + o_sk;
   float freq[128];
   yarn_inv_freq_host(*w, freq);
   e = cudaMemcpy(L->inv_freq, freq, (size_t)(w->qk_rope / 2) * 4, cudaMemcpyHostToDevice);
@@ -378,11 +392,11 @@ extern "C" int blok_mla_decode(blok_mla_layer_t *L, const blok_bf16_t *n, blok_b
   const int lat_w = w.kv_rank + w.qk_rope, qk_head = w.qk_nope + w.qk_rope;
   int rc;
   // q_a -> RMSNorm -> q_b   (:813-815)
-  if ((rc = launch_bf16_gemv(w.q_a, n, L->qa, nullptr, w.q_rank, w.hidden, B, stream))) return rc;
+  if ((rc = launch_bf16_gemv_splitk(w.q_a, n, L->qa, nullptr, w.q_rank, w.hidden, B, L->sk_ws, L->sk_bytes, stream))) return rc;
   if ((rc = blok_rmsnorm(L->qa, w.q_a_ln, L->qa, B, w.q_rank, w.rms_eps, stream_))) return rc;
-  if ((rc = launch_bf16_gemv(w.q_b, L->qa, L->q, nullptr, w.heads * qk_head, w.q_rank, B, stream))) return rc;
+  if ((rc = launch_bf16_gemv_splitk(w.q_b, L->qa, L->q, nullptr, w.heads * qk_head, w.q_rank, B, L->sk_ws, L->sk_bytes, stream))) return rc;
   // kv_a; norm of c_kv, RoPE of k_pe and of q's rope part, cache append   (:816-824)
-  if ((rc = launch_bf16_gemv(w.kv_a, n, L->kva, nullptr, lat_w, w.hidden, B, stream))) return rc;
+  if ((rc = launch_bf16_gemv_splitk(w.kv_a, n, L->kva, nullptr, lat_w, w.hidden, B, L->sk_ws, L->sk_bytes, stream))) return rc;
   mla_prep_kernel<<<B, 256, 0, stream>>>(L->kva, w.kv_a_ln, L->q, L->inv_freq, ctx_len, cache, ctx_stride, L->q_full,
                                          w.heads, w.qk_nope, w.qk_rope, w.kv_rank, w.rms_eps);
   if ((rc = launch_status("mla_prep_kernel"))) return rc;
@@ -398,5 +412,5 @@ extern "C" int blok_mla_decode(blok_mla_layer_t *L, const blok_bf16_t *n, blok_b
                              (long)w.heads * w.kv_rank, w.kv_rank, L->av, (long)w.heads * w.v_head, w.v_head, w.v_head,
                              w.kv_rank, w.heads, B, stream)))
     return rc;
-  return launch_bf16_gemv(w.o, L->av, out, nullptr, w.hidden, w.heads * w.v_head, B, stream);
+  return launch_bf16_gemv_splitk(w.o, L->av, out, nullptr, w.hidden, w.heads * w.v_head, B, L->sk_ws, L->sk_bytes, stream);
 }

@@ -55,7 +55,7 @@ constexpr int kFusedWarps = BLOK_FUSED_WARPS;
 constexpr int kFusedThreads = kFusedWarps * 32;
 constexpr unsigned kSpinLimit = 1u << 22;  // polls before a wait gives up with an error word
 
-enum { CTRL_QUEUE = 0, CTRL_ROUTER = 1, CTRL_ROUTED = 2, CTRL_MID = 3, CTRL_EXIT = 4, CTRL_ERROR = 5, CTRL_EPOCH = 6 };
+enum { CTRL_QUEUE = 0, CTRL_EXIT = 4, CTRL_ERROR = 5, CTRL_EPOCH = 6 };  // word indices in the control block
 constexpr int kTraceSlots = 16;
 
 struct FusedParams {
@@ -71,8 +71,6 @@ struct FusedParams {
   uint16_t *ids_out;
   float *wts_out;
   uint2 *logits;   // [experts] (router logit, launch tag)
-  int *route_ids;  // [topk] selected experts, published by the warp that runs the top-k
-  float *route_wts;
   uint2 *mid;      // [topk + 1][mid_stride / 2] (two bf16 mid values, launch tag); row topk is the shared expert's
   int mid_stride;
   uint2 *ys;       // [topk + 1][hidden] (bf16-valued per-slot down output, launch tag)
@@ -84,7 +82,6 @@ struct FusedParams {
   int sprC1;
   int sprC2, spcC2, cprC2;
   unsigned cA0, cB0, cC10, cC20, total;  // first queue index of each phase; queue length
-  unsigned mid_target;                    // row-blocks of A and B together
   unsigned *ctrl;
   long long *trace;  // optional: [0..15] launch-wide stamps, then [grid][kTraceSlots] per-CTA stamps (ns)
 };
@@ -99,43 +96,6 @@ __device__ __forceinline__ void trace_cta(const FusedParams &p, int slot) {
 }
 __device__ __forceinline__ void trace_launch(const FusedParams &p, int slot) {
   if (p.trace) p.trace[slot] = global_ns();
-}
-
-__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned *p) {
-  unsigned v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ unsigned atom_add_acq_rel(unsigned *p, unsigned v) {
-  unsigned old;
-  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
-  return old;
-}
-
-// Lane 0 polls until *p >= target (bounded); the warp leaves together.
-__device__ __forceinline__ void warp_wait(const unsigned *p, unsigned target, unsigned *err, unsigned code, int lane) {
-  if (lane == 0) {
-    unsigned it = 0;
-    while (ld_acquire_u32(p) < target) {
-      if (++it > kSpinLimit) {
-        atomicExch(err, code);
-        break;
-      }
-      __nanosleep(40);
-    }
-  }
-  __syncwarp();
-}
-
-// The warp's earlier global writes become visible before lane 0's increment; the
-// increment also acquires, so a warp that sees the final count may read what the
-// other arrivals wrote.  Returns the old count in every lane.
-__device__ __forceinline__ unsigned warp_arrive(unsigned *counter, int lane) {
-  __syncwarp();
-  unsigned old = 0;
-  if (lane == 0) old = atom_add_acq_rel(counter, 1u);
-  old = __shfl_sync(0xffffffffu, old, 0);
-  return old;
 }
 
 // Results that one warp hands to another travel as (value, tag) pairs written with one
@@ -180,24 +140,6 @@ __device__ __noinline__ void ld_tagged_n(const uint2 *p, int stride, int n, unsi
   }
 #pragma unroll
   for (int i = 0; i < N; ++i) out[i] = i < n ? __uint_as_float(v[i]) : 0.f;
-}
-
-// Two consecutive tagged pairs with one 16-byte load: {v0, tag0, v1, tag1}.
-__device__ __forceinline__ uint2 ld_tagged2(const uint2 *p, unsigned tag, unsigned *err) {
-  unsigned v0, t0, v1, t1, it = 0;
-  for (;;) {
-    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v0), "=r"(t0), "=r"(v1), "=r"(t1) : "l"(p) : "memory");
-    if (t0 == tag && t1 == tag) break;
-    if (++it > kSpinLimit) {
-      atomicExch(err, 4u);
-      break;
-    }
-    __nanosleep(20);
-  }
-  return make_uint2(v0, v1);
-}
-__device__ __forceinline__ void red_release_add(unsigned *p, unsigned v) {
-  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 __device__ __forceinline__ float swiglu_ref_rounding(float g, float u) {
@@ -417,8 +359,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
   const unsigned epoch = p.ctrl[CTRL_EPOCH] + 1u;  // stable during the launch; the last CTA to leave bumps it
   unsigned *const err = p.ctrl + CTRL_ERROR;
   bool have_routing = false;
-  const int nrb_router = p.experts / 16;
-  const unsigned ncontrib = (unsigned)p.topk + (p.shared_inter ? 1u : 0u);
 
   // Queue index -> chunk.  B and C1 chunks need the routing (w_ids) to be in hand.
   auto decode = [&](unsigned c) {
@@ -716,9 +656,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
     unsigned old = atomicAdd(p.ctrl + CTRL_EXIT, 1u);
     if (old == gridDim.x - 1) {
       p.ctrl[CTRL_QUEUE] = 0;
-      p.ctrl[CTRL_ROUTER] = 0;
-      p.ctrl[CTRL_ROUTED] = 0;
-      p.ctrl[CTRL_MID] = 0;
       p.ctrl[CTRL_EXIT] = 0;
       p.ctrl[CTRL_EPOCH] = epoch_now;
       __threadfence();
@@ -805,7 +742,6 @@ int launch_moe_decode_fused(blok_moe_layer *L, const uint16_t *x, uint16_t *y, u
   p.ids_out = ids_out ? ids_out : L->ids;
   p.wts_out = wts_out ? wts_out : L->wts;
   p.logits = reinterpret_cast<uint2 *>(L->f_logits_t);
-  p.route_ids = L->f_route_ids; p.route_wts = L->f_route_wts;
   p.mid = reinterpret_cast<uint2 *>(L->f_mid); p.mid_stride = L->f_mid_stride;
   p.ys = reinterpret_cast<uint2 *>(L->f_ys);
   p.partR = reinterpret_cast<uint2 *>(L->f_partR); p.partA = reinterpret_cast<uint2 *>(L->f_partA);
@@ -820,7 +756,6 @@ int launch_moe_decode_fused(blok_moe_layer *L, const uint16_t *x, uint16_t *y, u
   p.cC10 = p.cB0 + (unsigned)pl.nrbB * pl.cprB;
   p.cC20 = p.cC10 + (unsigned)pl.nrbC1;
   p.total = p.cC20 + (unsigned)pl.nrbC2 * pl.cprC2;
-  p.mid_target = (unsigned)pl.nrbA + (unsigned)pl.nrbB;
   p.ctrl = L->f_ctrl;
   p.trace = L->f_trace;
   void *args[] = {&p};
