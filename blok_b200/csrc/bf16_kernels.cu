@@ -263,10 +263,13 @@ int launch_bf16_gemv(const uint16_t *w, const uint16_t *x, uint16_t *y_bf16, flo
   return launch_status("bf16_gemv_scalar_kernel");
 }
 
-// Bytes of workspace launch_bf16_gemv_splitk may need for a matrix of `rows` rows: 512 bytes of partial sums per CTA
-// (splits x row blocks < 4 SMs' worth + row blocks), then one ticket per row block.
-static size_t splitk_part_bytes(int rows) { return ((size_t)4 * sm_count() + rows / 16) * 128 * 4; }
-size_t bf16_gemv_splitk_workspace_bytes(int rows) { return splitk_part_bytes(rows) + (size_t)(rows / 16) * 4 + 256; }
+// Bytes of workspace launch_bf16_gemv_splitk may need for a matrix of `rows` rows: one ticket per row block at the
+// start (the same words serve every matrix that uses the workspace; they re-arm themselves), then 512 bytes of
+// partial sums per CTA (splits x row blocks < 4 SMs' worth + row blocks).
+static size_t splitk_ticket_bytes(int rows) { return ((size_t)(rows / 16) * 4 + 255) / 256 * 256; }
+size_t bf16_gemv_splitk_workspace_bytes(int rows) {
+  return splitk_ticket_bytes(rows) + ((size_t)4 * sm_count() + rows / 16) * 128 * 4;
+}
 
 // The mat-vec with as many K-splits as it takes to put about four CTAs on every SM; falls back to the one-CTA-per-
 // row-block kernel when the matrix has enough rows or the shape does not fit.  `ws` must be zero before the first call
@@ -279,11 +282,13 @@ int launch_bf16_gemv_splitk(const uint16_t *w, const uint16_t *x, uint16_t *y_bf
   const bool ok = rows % 16 == 0 && cols % 32 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 &&
                   (reinterpret_cast<uintptr_t>(x) & 15) == 0 && T >= 1 && T <= 8 && ws &&
                   ws_bytes >= bf16_gemv_splitk_workspace_bytes(rows);
-  if (!ok || ksplit < 2) return launch_bf16_gemv(w, x, y_bf16, y_f32, rows, cols, T, stream);
+  // with more than two tokens the staged activation slice is no longer small against a CTA's 16 weight rows
+  if (!ok || ksplit < 2 || T > 2) return launch_bf16_gemv(w, x, y_bf16, y_f32, rows, cols, T, stream);
   const int per = (ksteps + ksplit - 1) / ksplit;
   ksplit = (ksteps + per - 1) / per;
-  float *part = static_cast<float *>(ws);
-  unsigned *tickets = reinterpret_cast<unsigned *>(static_cast<unsigned char *>(ws) + splitk_part_bytes(rows));
+  // the ticket block is sized for the largest matrix the workspace was made for; this matrix uses its first rb words
+  unsigned *tickets = static_cast<unsigned *>(ws);
+  float *part = reinterpret_cast<float *>(static_cast<unsigned char *>(ws) + (ws_bytes - ((size_t)4 * sm_count() + rb) * 128 * 4) / 256 * 256);
   const size_t smem = bf16_x_row_bytes(per * 32) * T;
   if (smem > 48 * 1024)
     BLOK_CUDA(cudaFuncSetAttribute(bf16_gemv16_splitk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
