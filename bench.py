@@ -35,7 +35,7 @@ sys.path.insert(0, ROOT)
 METRIC = "decode tok/s, INT4 MoE layer (batch 1)"
 WORKLOAD = "config 1: routed-MoE decode layer, batch 1, 384 INT4 experts top-8 + bf16 shared expert, hidden 7168"
 HBM_FALLBACK_GBS = 6650.0
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 297.5e6
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 292.6e6  # 287.5 MB read + 5.1 MB written (profiles/moe_decode_fused_config1.md)
 
 
 def measured_peak():

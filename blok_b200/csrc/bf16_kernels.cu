@@ -175,13 +175,16 @@ __global__ void __launch_bounds__(128) bf16_gemv16_splitk_kernel(const uint16_t 
 // One CTA per token.  The row is read once with 16-byte loads, all of them in flight before the first use (a row of
 // up to 256 x 4 x 8 = 8192 values stays in registers between the sum and the scaling); longer or unaligned rows take
 // the element loop.
-__global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__ w,
-                                                      uint16_t *__restrict__ y, int n, float eps) {
+// ADD: first x <- bf16(x + t) (the rounded residual add, src/kimi_exec.cu:248-251), written back, then the norm of it.
+template <bool ADD>
+__global__ void __launch_bounds__(256) rmsnorm_kernel(uint16_t *__restrict__ x, const uint16_t *__restrict__ tadd,
+                                                      const uint16_t *__restrict__ w, uint16_t *__restrict__ y, int n, float eps) {
   __shared__ float red[32];
-  const uint16_t *xr = x + (size_t)blockIdx.x * n;
+  uint16_t *xr = x + (size_t)blockIdx.x * n;
+  const uint16_t *tr = ADD ? tadd + (size_t)blockIdx.x * n : nullptr;
   uint16_t *yr = y + (size_t)blockIdx.x * n;
   const bool vec = (n % 8 == 0) && n <= 8192 && ((reinterpret_cast<uintptr_t>(xr) | reinterpret_cast<uintptr_t>(yr) |
-                                                  reinterpret_cast<uintptr_t>(w)) & 15) == 0;
+                                                  reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(tr)) & 15) == 0;
   float v = 0.f;
   uint4 xv[4];
   const int nu = n / 8;
@@ -190,6 +193,16 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t *__restrict
     for (int k = 0; k < 4; ++k) {
       const int u = threadIdx.x + k * 256;
       xv[k] = u < nu ? reinterpret_cast<const uint4 *>(xr)[u] : make_uint4(0, 0, 0, 0);
+      if (ADD && u < nu) {
+        const uint4 tv = reinterpret_cast<const uint4 *>(tr)[u];
+        const uint32_t a[4] = {xv[k].x, xv[k].y, xv[k].z, xv[k].w}, c[4] = {tv.x, tv.y, tv.z, tv.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          o[j] = f32_to_bf16_bits(bf16lo(a[j]) + bf16lo(c[j])) | ((uint32_t)f32_to_bf16_bits(bf16hi(a[j]) + bf16hi(c[j])) << 16);
+        xv[k] = make_uint4(o[0], o[1], o[2], o[3]);
+        reinterpret_cast<uint4 *>(xr)[u] = xv[k];
+      }
     }
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -203,6 +216,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t *__restrict
     }
   } else {
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      if (ADD) xr[i] = f32_to_bf16_bits(bf16_bits_to_f32(xr[i]) + bf16_bits_to_f32(tr[i]));
       float a = bf16_bits_to_f32(xr[i]);
       v = fmaf(a, a, v);
     }
@@ -351,8 +365,17 @@ extern "C" int blok_rmsnorm(const blok_bf16_t *x, const blok_bf16_t *w, blok_bf1
   BLOK_REQUIRE(x && w && y, BLOK_ERR_ARG, "blok_rmsnorm: null pointer");
   BLOK_REQUIRE(T >= 0 && n > 0, BLOK_ERR_SHAPE, "blok_rmsnorm: bad shape T=%d n=%d", T, n);
   if (T == 0) return BLOK_OK;
-  rmsnorm_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(x, w, y, n, eps);
+  rmsnorm_kernel<false><<<T, 256, 0, (cudaStream_t)stream>>>(const_cast<uint16_t *>(x), nullptr, w, y, n, eps);
   return launch_status("rmsnorm_kernel");
+}
+
+extern "C" int blok_add_rmsnorm(blok_bf16_t *x, const blok_bf16_t *t, const blok_bf16_t *w, blok_bf16_t *y, int T, int n,
+                                float eps, blok_stream_t stream) {
+  BLOK_REQUIRE(x && t && w && y, BLOK_ERR_ARG, "blok_add_rmsnorm: null pointer");
+  BLOK_REQUIRE(T >= 0 && n > 0, BLOK_ERR_SHAPE, "blok_add_rmsnorm: bad shape T=%d n=%d", T, n);
+  if (T == 0) return BLOK_OK;
+  rmsnorm_kernel<true><<<T, 256, 0, (cudaStream_t)stream>>>(x, t, w, y, n, eps);
+  return launch_status("rmsnorm_kernel<add>");
 }
 
 extern "C" int blok_add_bf16(blok_bf16_t *a, const blok_bf16_t *b, long n, blok_stream_t stream) {

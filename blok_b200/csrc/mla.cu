@@ -79,22 +79,36 @@ __global__ void __launch_bounds__(128)
 //   q      bf16 [B, heads, nope + rope]
 //   q_full bf16 [B, heads, kv_rank + rope]; this kernel writes columns [kv_rank, kv_rank+rope)
 // ---------------------------------------------------------------------------
-__global__ void mla_prep_kernel(const uint16_t *__restrict__ kva, const uint16_t *__restrict__ kva_ln,
-                                const uint16_t *__restrict__ q, const float *__restrict__ inv_freq,
-                                const int *__restrict__ ctx_len, uint16_t *__restrict__ cache, long ctx_stride,
-                                uint16_t *__restrict__ q_full, int heads, int nope, int rope, int kv_rank, float eps) {
+// grid = (1 + heads / 8, B), 256 threads: block 0 of a sequence normalises c_kv, rotates k_pe, appends the cache row
+// and publishes seq = ctx_len + 1 (the tokens the attention covers); blocks 1.. rotate the rope part of 8 heads each.
+__global__ void __launch_bounds__(256) mla_prep_kernel(const uint16_t *__restrict__ kva, const uint16_t *__restrict__ kva_ln,
+                                                       const uint16_t *__restrict__ q, const float *__restrict__ inv_freq,
+                                                       const int *__restrict__ ctx_len, uint16_t *__restrict__ cache,
+                                                       long ctx_stride, uint16_t *__restrict__ q_full, int *__restrict__ seq,
+                                                       int heads, int nope, int rope, int kv_rank, float eps) {
   __shared__ float red[32];
-  __shared__ float cs[256];  // cos then sin, rope/2 each
-  const int b = blockIdx.x, tid = threadIdx.x;
+  const int b = blockIdx.y, tid = threadIdx.x;
   const int pos = ctx_len[b];
   const int half = rope / 2, lat_w = kv_rank + rope;
+  if (blockIdx.x > 0) {
+    // thread = (head, pair): interleaved pair (2p, 2p+1) -> de-interleaved (p, half+p); every product rounded (:353-356)
+    const int i = (blockIdx.x - 1) * 256 + tid;
+    if (i < heads * half) {
+      const int h = i / half, p = i - h * half;
+      const float ang = pos * inv_freq[p];
+      const float c = round_bf16(cosf(ang)), s = round_bf16(sinf(ang));
+      const uint16_t *qr = q + ((size_t)b * heads + h) * (nope + rope) + nope;
+      uint16_t *qo = q_full + ((size_t)b * heads + h) * lat_w + kv_rank;
+      const uint32_t pair = *reinterpret_cast<const uint32_t *>(qr + 2 * p);
+      const float x0 = bf16lo(pair), x1 = bf16hi(pair);
+      qo[p] = f32_to_bf16_bits(round_bf16(x0 * c) - round_bf16(x1 * s));
+      qo[half + p] = f32_to_bf16_bits(round_bf16(x1 * c) + round_bf16(x0 * s));
+    }
+    return;
+  }
+  if (tid == 0) seq[b] = pos + 1;
   const uint16_t *kr = kva + (size_t)b * lat_w;
   uint16_t *row = cache + ((size_t)b * ctx_stride + pos) * lat_w;
-  for (int p = tid; p < half; p += blockDim.x) {
-    float ang = pos * inv_freq[p];
-    cs[p] = round_bf16(cosf(ang));
-    cs[half + p] = round_bf16(sinf(ang));
-  }
   float v = 0.f;
   for (int i = tid; i < kv_rank; i += blockDim.x) {
     float a = bf16_bits_to_f32(kr[i]);
@@ -112,29 +126,16 @@ __global__ void mla_prep_kernel(const uint16_t *__restrict__ kva, const uint16_t
   const float scale = rsqrtf(red[0] / kv_rank + eps);
   for (int i = tid; i < kv_rank; i += blockDim.x)
     row[i] = f32_to_bf16_bits(round_bf16(bf16_bits_to_f32(kr[i]) * scale) * bf16_bits_to_f32(kva_ln[i]));
-  // k_pe: interleaved pair (2p, 2p+1) -> de-interleaved (p, half+p); every product rounded (:353-356)
-  for (int p = tid; p < half; p += blockDim.x) {
-    float c = cs[p], s = cs[half + p];
-    float x0 = bf16_bits_to_f32(kr[kv_rank + 2 * p]), x1 = bf16_bits_to_f32(kr[kv_rank + 2 * p + 1]);
+  if (tid < half) {
+    const int p = tid;
+    const float ang = pos * inv_freq[p];
+    const float c = round_bf16(cosf(ang)), s = round_bf16(sinf(ang));
+    const float x0 = bf16_bits_to_f32(kr[kv_rank + 2 * p]), x1 = bf16_bits_to_f32(kr[kv_rank + 2 * p + 1]);
     row[kv_rank + p] = f32_to_bf16_bits(round_bf16(x0 * c) - round_bf16(x1 * s));
     row[kv_rank + half + p] = f32_to_bf16_bits(round_bf16(x1 * c) + round_bf16(x0 * s));
   }
-  const int qk_head = nope + rope;
-  for (int i = tid; i < heads * half; i += blockDim.x) {
-    int h = i / half, p = i - h * half;
-    const uint16_t *qr = q + ((size_t)b * heads + h) * qk_head + nope;
-    uint16_t *qo = q_full + ((size_t)b * heads + h) * lat_w + kv_rank;
-    float c = cs[p], s = cs[half + p];
-    float x0 = bf16_bits_to_f32(qr[2 * p]), x1 = bf16_bits_to_f32(qr[2 * p + 1]);
-    qo[p] = f32_to_bf16_bits(round_bf16(x0 * c) - round_bf16(x1 * s));
-    qo[half + p] = f32_to_bf16_bits(round_bf16(x1 * c) + round_bf16(x0 * s));
-  }
 }
 
-__global__ void add_one_kernel(const int *__restrict__ a, int *__restrict__ b, int n) {
-  int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) b[i] = a[i] + 1;
-}
 
 // W_UK^T: out[h][j][d] = kv_b[h*(nope+v) + d][j]  (a pure re-arrangement, no arithmetic)
 __global__ void transpose_wuk_kernel(const uint16_t *__restrict__ kv_b, uint16_t *__restrict__ out, int heads, int nope,
@@ -397,15 +398,14 @@ extern "C" int blok_mla_decode(blok_mla_layer_t *L, const blok_bf16_t *n, blok_b
   if ((rc = launch_bf16_gemv_splitk(w.q_b, L->qa, L->q, nullptr, w.heads * qk_head, w.q_rank, B, L->sk_ws, L->sk_bytes, stream))) return rc;
   // kv_a; norm of c_kv, RoPE of k_pe and of q's rope part, cache append   (:816-824)
   if ((rc = launch_bf16_gemv_splitk(w.kv_a, n, L->kva, nullptr, lat_w, w.hidden, B, L->sk_ws, L->sk_bytes, stream))) return rc;
-  mla_prep_kernel<<<B, 256, 0, stream>>>(L->kva, w.kv_a_ln, L->q, L->inv_freq, ctx_len, cache, ctx_stride, L->q_full,
-                                         w.heads, w.qk_nope, w.qk_rope, w.kv_rank, w.rms_eps);
+  mla_prep_kernel<<<dim3(1 + (w.heads * (w.qk_rope / 2) + 255) / 256, B), 256, 0, stream>>>(
+      L->kva, w.kv_a_ln, L->q, L->inv_freq, ctx_len, cache, ctx_stride, L->q_full, L->seq, w.heads, w.qk_nope, w.qk_rope,
+      w.kv_rank, w.rms_eps);
   if ((rc = launch_status("mla_prep_kernel"))) return rc;
   // q_abs = W_UK^T q_nope
   if ((rc = launch_head_gemv(L->wuk_t, (long)w.kv_rank * w.qk_nope, L->q, (long)w.heads * qk_head, qk_head, L->q_full,
                              (long)w.heads * lat_w, lat_w, w.kv_rank, w.qk_nope, w.heads, B, stream)))
     return rc;
-  add_one_kernel<<<1, 32, 0, stream>>>(ctx_len, L->seq, B);
-  if ((rc = launch_status("add_one_kernel"))) return rc;
   if ((rc = attend_and_merge(L, L->q_full, cache, ctx_stride, L->seq, B, L->scale, L->o_lat, stream))) return rc;
   // out_h = W_UV o_lat_h, then o_proj   (:826)
   if ((rc = launch_head_gemv(w.kv_b + (size_t)w.qk_nope * w.kv_rank, (long)(w.qk_nope + w.v_head) * w.kv_rank, L->o_lat,

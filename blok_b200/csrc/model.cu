@@ -308,15 +308,16 @@ static int step_body(blok_model_t *m, int B, blok_stream_t stream_) {
   const size_t H = c.hidden;
   int rc;
   if ((rc = blok_embed(tp<uint16_t>(m->top, "embed_tokens"), m->ids, c.vocab, c.hidden, B, m->x, stream_))) return rc;  // :802
+  // Every residual add is fused with the RMSNorm that follows it (blok_add_rmsnorm), so a layer is: attention on n,
+  // x += attention | n = norm(x), feed-forward on n, x += feed-forward | n = the next layer's (or the final) norm.
+  if ((rc = blok_rmsnorm(m->x, tp<uint16_t>(m->layers[0].t, "input_layernorm"), m->n, B, c.hidden, c.rms_eps, stream_))) return rc;
   for (int l = 0; l < c.layers; ++l) {
     auto &L = m->layers[l];
     // attention block, :812-827
-    if ((rc = blok_rmsnorm(m->x, tp<uint16_t>(L.t, "input_layernorm"), m->n, B, c.hidden, c.rms_eps, stream_))) return rc;
     if ((rc = blok_mla_decode(L.mla, m->n, L.cache, c.max_ctx, m->pos, B, m->tmp, stream_))) return rc;
-    if ((rc = blok_add_bf16(m->x, m->tmp, (long)B * H, stream_))) return rc;
-    // feed-forward block, :829-877
-    if ((rc = blok_rmsnorm(m->x, tp<uint16_t>(L.t, "post_attention_layernorm"), m->n, B, c.hidden, c.rms_eps, stream_)))
+    if ((rc = blok_add_rmsnorm(m->x, m->tmp, tp<uint16_t>(L.t, "post_attention_layernorm"), m->n, B, c.hidden, c.rms_eps, stream_)))
       return rc;
+    // feed-forward block, :829-877
     for (int b = 0; b < B; ++b) {
       if (l < c.first_dense)
         rc = blok_bf16_mlp(tp<uint16_t>(L.t, "gate_proj"), tp<uint16_t>(L.t, "up_proj"), tp<uint16_t>(L.t, "down_proj"),
@@ -325,9 +326,10 @@ static int step_body(blok_model_t *m, int B, blok_stream_t stream_) {
         rc = blok_moe_decode(L.moe, m->n + b * H, m->tmp + b * H, nullptr, nullptr, stream_);
       if (rc) return rc;
     }
-    if ((rc = blok_add_bf16(m->x, m->tmp, (long)B * H, stream_))) return rc;
+    const bool last = l + 1 == c.layers;
+    const uint16_t *next_ln = last ? tp<uint16_t>(m->top, "norm") : tp<uint16_t>(m->layers[l + 1].t, "input_layernorm");  // :812 / :880
+    if ((rc = blok_add_rmsnorm(m->x, m->tmp, next_ln, m->n, B, c.hidden, last ? c.final_rms_eps : c.rms_eps, stream_))) return rc;
   }
-  if ((rc = blok_rmsnorm(m->x, tp<uint16_t>(m->top, "norm"), m->n, B, c.hidden, c.final_rms_eps, stream_))) return rc;  // :880
   if ((rc = blok_lm_head_argmax(tp<uint16_t>(m->top, "lm_head"), m->n, c.vocab, c.hidden, B, m->next, m->head_ws,
                                 m->head_ws_bytes, stream_)))
     return rc;

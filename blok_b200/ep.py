@@ -59,8 +59,20 @@ class ExpertParallelMoe:
         dist.all_to_all_single(recv, send, output_split_sizes=recv_counts, input_split_sizes=send_counts, group=self.group)
         return recv
 
+    def _side_stream(self, device):
+        if getattr(self, "_side", None) is None:
+            self._side = torch.cuda.Stream(device=device)
+        return self._side
+
     def forward(self, x):
         T, H = x.shape
+        # The shared expert needs nothing from the exchange: on a GPU it runs on a side stream while the tokens travel.
+        shared, side = None, None
+        if self.shared_fn is not None and x.is_cuda:
+            side = self._side_stream(x.device)
+            side.wait_stream(torch.cuda.current_stream(x.device))
+            with torch.cuda.stream(side):
+                shared = self.shared_fn(x)
         ids, wts = self.router_fn(x)
         ids64 = ids.to(torch.int64) & 0xFFFF if ids.dtype == torch.int16 else ids.to(torch.int64)
         order, send_counts_t, local_e = plan_dispatch(ids64, self.experts, self.world)
@@ -82,7 +94,11 @@ class ExpertParallelMoe:
         y_back = self._all_to_all(y_recv.contiguous(), recv_counts, send_counts)
         y_assign = torch.empty_like(y_back)
         y_assign.index_copy_(0, order.to(x.device), y_back)        # back to assignment order t*topk + k
-        shared = self.shared_fn(x) if self.shared_fn is not None else None
+        if side is not None:
+            torch.cuda.current_stream(x.device).wait_stream(side)
+            shared.record_stream(torch.cuda.current_stream(x.device))
+        elif self.shared_fn is not None:
+            shared = self.shared_fn(x)
         remote = sum(c for r, c in enumerate(send_counts) if r != self.rank)
         self.last_stats = dict(assignments=T * self.topk, remote=remote, bytes_each_way=remote * H * x.element_size(),
                                received=int(sum(recv_counts)))

@@ -167,6 +167,16 @@ def rmsnorm(x, w, eps=1e-5, out=None):
     return y
 
 
+
+def add_rmsnorm(x, t, w, eps=1e-5):
+    """x <- bf16(x + t) in place, returns RMSNorm(x) * w (one launch: src/kimi_exec.cu:248-251 then :258-270)."""
+    n = x.shape[-1]
+    T = x.numel() // n if n else 0
+    y = torch.empty_like(x)
+    _check(load().blok_add_rmsnorm(_ptr(x, torch.bfloat16), _ptr(t, torch.bfloat16), _ptr(w, torch.bfloat16), _ptr(y, torch.bfloat16),
+                                   C.c_int(T), C.c_int(n), C.c_float(eps), _stream()))
+    return y
+
 def add_(a, b):
     """a = bf16(a + b), add_k (src/kimi_exec.cu:248-251)."""
     _check(load().blok_add_bf16(_ptr(a, torch.bfloat16), _ptr(b, torch.bfloat16), C.c_long(a.numel()), _stream()))

@@ -132,6 +132,11 @@ int blok_bf16_mlp(const blok_bf16_t *gate, const blok_bf16_t *up, const blok_bf1
 int blok_rmsnorm(const blok_bf16_t *x, const blok_bf16_t *w, blok_bf16_t *y, int T, int n, float eps,
                  blok_stream_t stream);
 
+/* x <- bf16(x + t) in place, then y = RMSNorm(x) * w, in one launch: the residual add that ends one block and the
+ * norm that opens the next (src/kimi_exec.cu:827 + :829, :877 + :812 of the next layer, :877 + :880 after the last). */
+int blok_add_rmsnorm(blok_bf16_t *x, const blok_bf16_t *t, const blok_bf16_t *w, blok_bf16_t *y, int T, int n, float eps,
+                     blok_stream_t stream);
+
 /* a[i] = bf16(a[i] + b[i]).  Replaces add_k (src/kimi_exec.cu:248-251). */
 int blok_add_bf16(blok_bf16_t *a, const blok_bf16_t *b, long n, blok_stream_t stream);
 
@@ -212,7 +217,10 @@ int blok_moe_experts_grouped(blok_moe_layer_t *layer, const blok_bf16_t *x, cons
                              int N, blok_bf16_t *y, blok_stream_t stream);
 
 /* The shared expert for T tokens: out[t] = bf16(W_d(SiLU(W_g x[t]) * W_u x[t])), bf16_mlp
- * (src/kimi_exec.cu:674-686, call site :872-875) without its running-sum side effect. */
+ * (src/kimi_exec.cu:674-686, call site :872-875) without its running-sum side effect.
+ * It shares no scratch with blok_moe_experts_grouped: the one exception to "calls on a
+ * handle are not concurrent" is that these two may run at the same time on two streams
+ * (the expert-parallel layer overlaps the shared expert with the exchange that way). */
 int blok_moe_shared(blok_moe_layer_t *layer, const blok_bf16_t *x, int T, blok_bf16_t *out, blok_stream_t stream);
 
 /* out[t] = bf16(bf16(sum_k wts[t,k] * y_assign[t*topk + k]) + shared[t]) in slot order

@@ -125,3 +125,19 @@ def test_lm_head_argmax_and_embed(cuda, oracle, vocab, hidden, T):
         for t in range(T):
             tok, _ = oracle.lm_head_argmax(wh, nh[t], mode=0)
             assert got[t] == tok
+
+
+@pytest.mark.parametrize("T,n", [(1, 7168), (8, 7168), (3, 1536), (2, 100)])
+def test_add_rmsnorm_is_add_then_rmsnorm(cuda, T, n):
+    """The fused residual add + norm equals the two separate calls bit for bit (rows in registers or the element loop)."""
+    from blok_b200 import lib, synth
+    x = synth.activations(T, n, cuda, 61)
+    t = synth.activations(T, n, cuda, 62)
+    w = (synth.activations(1, n, cuda, 63)[0].float() * 0.1 + 1).bfloat16()
+    x_ref = x.clone()
+    lib.add_(x_ref, t)
+    y_ref = lib.rmsnorm(x_ref, w, eps=1e-5)
+    x_got = x.clone()
+    y = lib.add_rmsnorm(x_got, t, w, eps=1e-5)
+    assert torch.equal(x_got, x_ref) and torch.equal(y, y_ref)
+    assert torch.equal(x_ref, (x.float() + t.float()).bfloat16())
