@@ -56,6 +56,12 @@ __global__ void mb_identity_tiles_kernel(int T, int *tile_expert, int *tile_star
   }
 }
 
+int launch_identity_tiles(int T, int *tile_expert, int *tile_start, int *tile_count, int *num_tiles, cudaStream_t stream) {
+  const int tt = (T + kWgTileTokens - 1) / kWgTileTokens;
+  mb_identity_tiles_kernel<<<(tt + 63) / 64, 64, 0, stream>>>(T, tile_expert, tile_start, tile_count, num_tiles);
+  return launch_status("mb_identity_tiles_kernel");
+}
+
 // One warp per local expert: stable placement (ascending assignment id) of its assignments.
 __global__ void mb_scatter_kernel(const int *__restrict__ expert_local, const int *__restrict__ x_index, int N,
                                   int n_local, const int *__restrict__ offsets, int *__restrict__ sorted_assign,

@@ -2,6 +2,7 @@
 // Reference arithmetic: src/kimi_exec.cu:836-842 with matvec_bf16_f32_k :286-298,
 // sigmoid_k :377-380, add_bf16_k :372-375, router_topk_k :382-397.
 #include "router_topk.cuh"
+#include "wgemm.h"
 
 namespace blok {
 
@@ -53,8 +54,12 @@ int launch_router_topk(const float *logits, const float *bias, int T, int expert
 
 using namespace blok;
 
+// fp32 logits [T, experts], then (for more than 16 tokens) the tile table of the weight-streaming GEMM
+static size_t router_logits_bytes(int T, int experts) { return ((size_t)T * experts * sizeof(float) + 255) / 256 * 256; }
 extern "C" size_t blok_router_workspace_bytes(int T, int experts) {
-  return (T > 0 && experts > 0) ? (size_t)T * experts * sizeof(float) : 0;
+  if (T <= 0 || experts <= 0) return 0;
+  const size_t tiles = (size_t)(T + kWgTileTokens - 1) / kWgTileTokens;
+  return router_logits_bytes(T, experts) + (3 * tiles + 1) * sizeof(int) + 256;
 }
 
 extern "C" int blok_router(const blok_bf16_t *router_w, const float *bias, const blok_bf16_t *x, int T, int experts,
@@ -68,6 +73,20 @@ extern "C" int blok_router(const blok_bf16_t *router_w, const float *bias, const
                "blok_router: workspace too small");
   if (T == 0) return BLOK_OK;
   float *logits = static_cast<float *>(workspace);
+  if (T > 16 && experts % 128 == 0 && hidden % 512 == 0) {
+    // many tokens: one pass of the weight-streaming GEMM over the router matrix instead of T / 8 mat-vec launches
+    const int tiles = (T + kWgTileTokens - 1) / kWgTileTokens;
+    int *tab = reinterpret_cast<int *>(static_cast<unsigned char *>(workspace) + router_logits_bytes(T, experts));
+    int rc = launch_identity_tiles(T, tab, tab + tiles, tab + 2 * tiles, tab + 3 * tiles, (cudaStream_t)stream);
+    if (rc) return rc;
+    WgArgs r;
+    r.w_a = router_w; r.w_b = nullptr; r.s_a = r.s_b = nullptr; r.expert_stride_rows = 0; r.x = x; r.x_index = nullptr;
+    r.K = hidden; r.R = experts; r.out_bf16 = nullptr; r.out_f32 = logits;
+    r.tile_expert = tab; r.tile_start = tab + tiles; r.tile_count = tab + 2 * tiles; r.num_tiles = tab + 3 * tiles;
+    r.out_index = nullptr; r.n_rows = T; r.identity_tiles = 1;
+    if ((rc = launch_wgemm(WG_BF16_PLAIN, r, tiles, (cudaStream_t)stream))) return rc;
+    return launch_router_topk(logits, bias, T, experts, topk, routed_scale, ids, wts, nullptr, 0, (cudaStream_t)stream);
+  }
   for (int t0 = 0; t0 < T; t0 += 8) {
     int n = T - t0 < 8 ? T - t0 : 8;
     int rc = launch_bf16_gemv(router_w, x + (size_t)t0 * hidden, nullptr, logits + (size_t)t0 * experts, experts, hidden,

@@ -35,6 +35,9 @@ struct WgArgs {
 // which streams the weights better at small counts.  BLOK_WGEMM_IMPL=mma / =tc in the environment forces one.
 int launch_wgemm(int mode, const WgArgs &args, int max_tiles, cudaStream_t stream);
 
+// Fills the tile arrays with consecutive 64-row tiles of T rows (one group, expert 0): a dense layer.
+int launch_identity_tiles(int T, int *tile_expert, int *tile_start, int *tile_count, int *num_tiles, cudaStream_t stream);
+
 bool wgemm_tc_supports(int mode, const WgArgs &args);
 int launch_wgemm_tc(int mode, const WgArgs &args, int max_tiles, cudaStream_t stream);
 // *out becomes non-zero if a tcgen05 GEMM CTA has given up on a barrier since the last call (the flag is cleared).
