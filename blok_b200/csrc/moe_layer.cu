@@ -125,6 +125,12 @@ extern "C" int blok_moe_layer_create(const blok_moe_weights *w, int max_tokens, 
   L->shared_out = reinterpret_cast<uint16_t *>(b + o_sout);
   L->io_x = reinterpret_cast<uint16_t *>(b + o_iox);
   L->io_y = reinterpret_cast<uint16_t *>(b + o_ioy);
+  if (cudaMallocHost(&L->io_err_host, sizeof(unsigned)) != cudaSuccess) {
+    cudaGetLastError();
+    L->io_err_host = nullptr;  // the host-buffer entry point then checks with a separate copy
+  } else {
+    *L->io_err_host = 0;
+  }
   if (pl.enabled) {
     L->f_mid = reinterpret_cast<uint16_t *>(b + o_fmid);
     L->f_logits_t = reinterpret_cast<float *>(b + o_flog);
@@ -162,6 +168,7 @@ extern "C" int blok_moe_layer_create(const blok_moe_weights *w, int max_tokens, 
 extern "C" int blok_moe_layer_destroy(blok_moe_layer_t *L) {
   if (!L) return BLOK_OK;
   cudaError_t e = L->ws ? cudaFree(L->ws) : cudaSuccess;
+  if (L->io_err_host) cudaFreeHost(L->io_err_host);
   if (L->bws) {
     cudaError_t e2 = cudaFree(L->bws);
     if (e == cudaSuccess) e = e2;
@@ -231,7 +238,13 @@ extern "C" int blok_moe_decode_host(blok_moe_layer_t *L, const blok_bf16_t *x_ho
   int rc = blok_moe_decode(L, L->io_x, L->io_y, nullptr, nullptr, stream_);
   if (rc) return rc;
   BLOK_CUDA(cudaMemcpyAsync(y_host, L->io_y, bytes, cudaMemcpyDeviceToHost, stream));
-  return blok_moe_layer_check(L, stream_);
+  if (L->f_ctrl && L->io_err_host) {
+    // the kernel's error word rides back behind the result: one synchronisation, no second round trip to the device
+    BLOK_CUDA(cudaMemcpyAsync(L->io_err_host, L->f_ctrl + 5, sizeof(unsigned), cudaMemcpyDeviceToHost, stream));
+    BLOK_CUDA(cudaStreamSynchronize(stream));
+    if (*L->io_err_host == 0) return BLOK_OK;
+  }
+  return blok_moe_layer_check(L, stream_);  // a wait timed out (or no pinned word): report it and reset the handle
 }
 
 extern "C" int blok_moe_layer_trace(blok_moe_layer_t *L, long long *host_out, int max_entries) {

@@ -37,6 +37,7 @@ struct blok_moe_layer {
   uint16_t *shared_out = nullptr;  // [8, hidden]
   uint16_t *io_x = nullptr;        // [hidden] staging for the host-buffer entry point
   uint16_t *io_y = nullptr;        // [hidden]
+  unsigned *io_err_host = nullptr; // pinned: the fused kernel's error word, copied back with every host-buffer call
   // batched path (moe_batched.cu); allocated when max_tokens > 1
   void *bws = nullptr;
   int b_max_assign = 0;          // max_tokens * topk
