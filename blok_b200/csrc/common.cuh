@@ -28,6 +28,8 @@ int cuda_fail(cudaError_t e, const char *what);
   } while (0)
 
 void count_launch();
+void count_launches(long long n);  // kernels replayed from a CUDA graph
+long long launches_so_far();
 
 inline int launch_status(const char *what) {
   count_launch();

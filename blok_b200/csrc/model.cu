@@ -78,6 +78,7 @@ struct blok_model {
   // One CUDA graph of the whole step per batch size: a step is ~16 small launches per layer and the host cannot issue
   // them as fast as the GPU runs them.  steps_seen counts eager steps (the first one also sets kernel attributes).
   cudaGraphExec_t step_graph[9] = {};
+  long long graph_launches[9] = {};  // kernels in each graph, added to the launch counter at every replay
   int steps_seen[9] = {};
   bool graphs_enabled = true;
 };
@@ -349,11 +350,15 @@ extern "C" int blok_model_step(blok_model_t *m, const uint32_t *ids, int B, uint
   const bool can_graph = m->graphs_enabled && stream != nullptr && stream != cudaStreamLegacy;
   if (can_graph && m->step_graph[B]) {
     BLOK_CUDA(cudaGraphLaunch(m->step_graph[B], stream));
+    count_launches(m->graph_launches[B]);
   } else if (can_graph && m->steps_seen[B] >= 1) {
     cudaGraph_t graph = nullptr;
     cudaError_t e = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal);
     if (e == cudaSuccess) {
+      const long long before = launches_so_far();
       rc = step_body(m, B, stream_);
+      m->graph_launches[B] = launches_so_far() - before;
+      count_launches(-m->graph_launches[B]);  // nothing ran during the capture
       cudaError_t e2 = cudaStreamEndCapture(stream, &graph);
       if (rc == BLOK_OK && e2 == cudaSuccess && graph) e = cudaGraphInstantiate(&m->step_graph[B], graph, 0);
       else e = e2 == cudaSuccess ? cudaErrorUnknown : e2;
@@ -366,6 +371,7 @@ extern "C" int blok_model_step(blok_model_t *m, const uint32_t *ids, int B, uint
       rc = step_body(m, B, stream_);
     } else {
       BLOK_CUDA(cudaGraphLaunch(m->step_graph[B], stream));
+      count_launches(m->graph_launches[B]);
       rc = BLOK_OK;
     }
   } else {
