@@ -192,6 +192,35 @@ def other_workload(a, rank, world, device, steps, warmup):
                     "greedy decode%s" % (L, L - 1, "" if world == 1 else ", replicas x%d" % world))
         scaling = "weak"
         metric = "decode tok/s, %d-layer model (batch 1)" % L
+    elif a.workload == "model61":
+        # config 4: the 61-layer model sharded expert-parallel over the ranks (384 / world experts per GPU, attention,
+        # router, shared expert, embedding and lm_head replicated), batch 1, greedy decode after a 16-token prompt replay.
+        # With fewer than 8 GPUs only as many layers as fit are built, and the line says how many.
+        from blok_b200 import ep_model
+        per_layer = 9.513e9 / world + 0.32e9
+        L = a.model_layers if a.model_layers != 12 else min(61, int(140e9 // per_layer))
+        cfg = lib.default_model_config(layers=L, max_batch=1, max_ctx=256, final_rms_eps=1e-6, yarn_factor=32.0)
+        model = ep_model.ExpertParallelModel(cfg, ep_model.synthetic_provider(cfg, rank, world, device, seed=4), max_ctx=256)
+        state = {"ids": torch.randint(0, 163840, (1,), device=device, dtype=torch.int32)}
+        if world > 1:
+            dist.broadcast(state["ids"], 0)
+
+        def run(i):
+            state["ids"] = model.step(state["ids"])
+        prompt_side = torch.cuda.Stream()
+        with torch.cuda.stream(prompt_side):
+            lc0 = lib.kernel_launch_count()
+            run(0)                                   # the first step is always eager: count its kernels
+            launches_per_step = lib.kernel_launch_count() - lc0
+            for _ in range(15):
+                run(0)
+        torch.cuda.synchronize()
+        alg = (L - 1) * (202244096 + 5505024 + 88080384 + 8 * 24772608 / world) + (3 * 18432 * 7168 * 2 + 202244096) + 163840 * 7168 * 2
+        unit_tokens = 1
+        workload = ("config 4: %d-layer model (1 dense + %d MoE layers, full shapes, vocab 163840), batch 1, greedy decode, "
+                    "experts split over %d GPU(s), one all-reduce per MoE layer" % (L, L - 1, world))
+        scaling = "strong"
+        metric = "decode tok/s, %d-layer model (batch 1)" % L
     elif a.workload.startswith("batched"):
         T = int(a.workload[len("batched"):])
         Tl = T // world
@@ -250,6 +279,8 @@ def other_workload(a, rank, world, device, steps, warmup):
         e1.record()
         barrier()
     launches = lib.kernel_launch_count() - l0
+    if a.workload == "model61" and launches == 0:
+        launches = launches_per_step * steps         # replayed from a torch CUDA graph: the library's counter does not see them
     ms = torch.tensor([e0.elapsed_time(e1)], device=device)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
@@ -283,7 +314,7 @@ def main():
     ap.add_argument("--experts", type=int, default=384,
                     help="routed experts per layer; below 384 the run is a reduced case for profiler captures, "
                          "not the benchmark configuration, and the line says so")
-    ap.add_argument("--workload", default="decode", choices=["decode", "batched64", "batched2048", "mla4096", "mla32768", "model"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "batched64", "batched2048", "mla4096", "mla32768", "model", "model61"],
                     help="decode = config 1 (the default, the headline metric); batched* = config 2 (expert parallel "
                          "when --gpus > 1); mla* = config 3 (attention block, batch 8)")
     a = ap.parse_args()

@@ -70,3 +70,60 @@ def test_two_rank_expert_parallel_layer_matches_single_gpu():
             p.terminate()
     assert all(v[0] == "ok" for v in res.values()), res
     assert any(v[1]["remote"] > 0 for v in res.values())
+
+
+def _model_worker(rank, world, port, q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        import torch.distributed as dist
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        from blok_b200 import ep_model, lib
+        cfg = dict(layers=3, first_dense=1, hidden=1024, vocab=2048, dense_inter=512, inter=512, experts=16, topk=8,
+                   shared_inter=512, q_rank=256, max_batch=1, max_ctx=32)
+        with torch.cuda.device(dev):
+            single = lib.Model(seed=41, **cfg)            # the same seeded weights on every rank's GPU
+            prompt = [7, 1, 900, 33]
+            want = single.generate(prompt, 6)
+            side = torch.cuda.Stream()
+            res = {}
+            for graph in (False, True):
+                m = ep_model.ExpertParallelModel(single.cfg, ep_model.provider_from_model(single, rank, world, dev),
+                                                 max_ctx=32, use_graph=graph)
+                with torch.cuda.stream(side):             # a graph cannot be captured on the legacy default stream
+                    res[graph] = m.generate(prompt, 6)
+                    torch.cuda.synchronize()
+                res["captured_%s" % graph] = m.graph is not None
+        dist.barrier()
+        ok = res[False] == want and res[True] == want
+        q.put((rank, "ok" if ok else "mismatch %r %r want %r" % (res[False], res[True], want), dict(graph=res["captured_True"])))
+        dist.destroy_process_group()
+    except Exception as e:
+        import traceback
+        q.put((rank, "error: %r %s" % (e, traceback.format_exc()[-600:]), {}))
+
+
+def test_two_rank_sharded_model_generates_the_single_gpu_tokens():
+    """Config 4 in miniature: 3 layers, experts split over 2 GPUs, one all-reduce per MoE layer; eager and CUDA graph."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_model_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = {}
+    for _ in range(2):
+        r, status, stats = q.get(timeout=300)
+        res[r] = (status, stats)
+    for p in procs:
+        p.join(timeout=60)
+        if p.is_alive():
+            p.terminate()
+    assert all(v[0] == "ok" for v in res.values()), res
