@@ -18,10 +18,6 @@ import torch.distributed as dist
 from . import lib, synth
 
 
-def _bf16(t):
-    return t.contiguous()
-
-
 class ExpertParallelModel:
     """provider(layer, name) -> CUDA tensor of that model tensor on this rank's device; layer -1 holds
     "embed_tokens", "norm", "lm_head".  Expert arrays ("gate_w", "gate_s", "up_w", "up_s", "down_w", "down_s") come
