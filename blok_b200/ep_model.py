@@ -188,3 +188,51 @@ def synthetic_provider(cfg, rank, world, device, seed=4):
                  "shared_down": (H, c.shared_inter)}[name]
         return synth.normal_bf16(shape, g, device, 0.006)
     return get
+
+
+def provider_from_index(index_path, cfg, rank, world, device):
+    """Tensors for `rank` read from a materialised checkpoint: the text index "blok-runtime-index-v1" of the
+    reference's scripts/model_fetch.py:113-127 is first checked against the forward contract for cfg
+    (blok_index_validate: src/kimi_exec.cu:736-778), then every tensor this rank needs is read once from its byte
+    range [data, data + data_bytes) of the shard file; a rank reads only the experts it owns (experts / world of
+    them, stacked expert-major as the kernels expect)."""
+    import numpy as np
+    lib.index_validate(index_path, cfg)
+    entries = {}
+    with open(index_path) as fh:
+        fh.readline()
+        for line in fh:
+            f = line.split()
+            # tensor name role layer expert slot dtype shape off bytes align data data_bytes file
+            entries[(int(f[3]), int(f[4]), f[2], f[5])] = (f[6], f[7], int(f[11]), int(f[12]), f[13])
+    per = cfg.experts // world
+    names = {"input_layernorm": ("resident", "input_layernorm"), "post_attention_layernorm": ("resident", "post_attention_layernorm"),
+             "embed_tokens": ("resident", "embed_tokens"), "norm": ("resident", "norm"), "lm_head": ("resident", "lm_head"),
+             "gate_proj": ("dense_ffn_rowcol", "gate_proj"), "up_proj": ("dense_ffn_rowcol", "up_proj"),
+             "down_proj": ("dense_ffn_rowcol", "down_proj"), "router": ("router", "gate"),
+             "router_bias": ("router", "e_score_correction_bias"), "shared_gate": ("shared_expert_resident", "gate_proj"),
+             "shared_up": ("shared_expert_resident", "up_proj"), "shared_down": ("shared_expert_resident", "down_proj")}
+    for n in ("q_a_proj", "q_a_layernorm", "q_b_proj", "kv_a_proj_with_mqa", "kv_a_layernorm", "kv_b_proj", "o_proj"):
+        names[n] = ("attention_resident", n)
+    experts = {"gate_w": "gate_proj.weight_packed", "gate_s": "gate_proj.weight_scale", "up_w": "up_proj.weight_packed",
+               "up_s": "up_proj.weight_scale", "down_w": "down_proj.weight_packed", "down_s": "down_proj.weight_scale"}
+
+    def read(key):
+        dtype, shape, data, nbytes, path = entries[key]
+        with open(path, "rb") as fh:
+            fh.seek(data)
+            raw = fh.read(nbytes)
+        if len(raw) != nbytes:
+            raise lib.BlokError(-1, "short read of %s from %s" % (key, path))
+        a = np.frombuffer(raw, dtype=np.int32 if dtype == "i32" else np.int16)
+        return a.reshape([int(d) for d in shape.split("x")])
+
+    def get(layer, name):
+        if name in experts:
+            parts = [read((layer, e, "routed_expert", experts[name])) for e in range(rank * per, (rank + 1) * per)]
+            t = torch.from_numpy(np.stack(parts)).to(device)
+            return t if name.endswith("_w") else t.view(torch.bfloat16)
+        role, slot = names[name]
+        t = torch.from_numpy(read((layer, -1, role, slot)).copy()).to(device).view(torch.bfloat16)
+        return t.float() if name == "router_bias" else t     # the correction bias is fp32 at the ABI
+    return get
