@@ -75,16 +75,27 @@ class ExpertParallelMoe:
                 shared = self.shared_fn(x)
         ids, wts = self.router_fn(x)
         ids64 = ids.to(torch.int64) & 0xFFFF if ids.dtype == torch.int16 else ids.to(torch.int64)
-        order, send_counts_t, local_e = plan_dispatch(ids64, self.experts, self.world)
-        send_counts = [int(v) for v in send_counts_t.tolist()]
-        # counts first, so that every rank can size its receive buffers
+        # Plan and counts with ONE wait for the device: the per-destination counts and the number of ids outside the
+        # expert range travel together, every rank gathers every rank's row, and a bad id is reported on all ranks
+        # (none is left waiting in a collective for a peer that raised).
+        per = self.experts // self.world
+        flat = ids64.reshape(-1)
+        bad = (flat < 0) | (flat >= self.experts)
+        dest = torch.where(bad, torch.zeros_like(flat), flat) // per
+        order = torch.sort(dest, stable=True).indices
+        local_e = (flat[order] % per).to(torch.int32)
+        meta = torch.cat([torch.bincount(dest, minlength=self.world), bad.sum().view(1)])
         if self.world > 1:
-            rc = torch.empty_like(send_counts_t)
-            dist.all_to_all_single(rc, send_counts_t.to(x.device) if send_counts_t.device != x.device else send_counts_t,
-                                   group=self.group)
-            recv_counts = [int(v) for v in rc.tolist()]
+            table = [torch.empty_like(meta) for _ in range(self.world)]
+            dist.all_gather(table, meta, group=self.group)
+            table = torch.stack(table).tolist()
         else:
-            recv_counts = list(send_counts)
+            table = [meta.tolist()]
+        culprits = [r for r in range(self.world) if table[r][self.world]]
+        if culprits:
+            raise RoutingError("expert id outside [0, %d) on rank(s) %s" % (self.experts, culprits))
+        send_counts = [int(v) for v in table[self.rank][:self.world]]
+        recv_counts = [int(table[r][self.rank]) for r in range(self.world)]
         rows = x.index_select(0, (order // self.topk).to(x.device))
         recv_rows = self._all_to_all(rows, send_counts, recv_counts)
         recv_e = self._all_to_all(local_e.to(x.device), send_counts, recv_counts)
