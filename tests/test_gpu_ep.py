@@ -88,7 +88,9 @@ def _model_worker(rank, world, port, q):
             want = single.generate(prompt, 6)
             side = torch.cuda.Stream()
             res = {}
-            for graph in (False, True):
+            # the CUDA-graph variant (NCCL all-reduce inside the capture) passed here too but takes two minutes to
+            # capture under NCCL: opt in with BLOK_TEST_EP_GRAPH=1
+            for graph in ((False, True) if os.environ.get("BLOK_TEST_EP_GRAPH") == "1" else (False,)):
                 m = ep_model.ExpertParallelModel(single.cfg, ep_model.provider_from_model(single, rank, world, dev),
                                                  max_ctx=32, use_graph=graph)
                 with torch.cuda.stream(side):             # a graph cannot be captured on the legacy default stream
@@ -96,8 +98,8 @@ def _model_worker(rank, world, port, q):
                     torch.cuda.synchronize()
                 res["captured_%s" % graph] = m.graph is not None
         dist.barrier()
-        ok = res[False] == want and res[True] == want
-        q.put((rank, "ok" if ok else "mismatch %r %r want %r" % (res[False], res[True], want), dict(graph=res["captured_True"])))
+        ok = all(res[g] == want for g in (False, True) if g in res)
+        q.put((rank, "ok" if ok else "mismatch %r want %r" % (res, want), dict(graph=res.get("captured_True", False))))
         dist.destroy_process_group()
     except Exception as e:
         import traceback
@@ -105,7 +107,7 @@ def _model_worker(rank, world, port, q):
 
 
 def test_two_rank_sharded_model_generates_the_single_gpu_tokens():
-    """Config 4 in miniature: 3 layers, experts split over 2 GPUs, one all-reduce per MoE layer; eager and CUDA graph."""
+    """Config 4 in miniature: 3 layers, experts split over 2 GPUs, one all-reduce per MoE layer."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
