@@ -42,8 +42,15 @@ def _single(x, W, wr):
 
 
 def _worker(rank, world, port, fault, q):
+    import datetime
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    # a short process-group timeout: a peer that is gone must end the survivors' next collective with an error
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    if fault == "peer_exits" and rank == 1:
+        dist.barrier()       # the group is up; then this rank leaves between steps, with nothing of its own in flight
+        os._exit(0)
+    if fault == "peer_exits":
+        dist.barrier()
     from blok_b200 import ep
     W, wr = _weights()
     per = E // world
@@ -93,13 +100,16 @@ def _run(world, fault=None):
     procs = [ctx.Process(target=_worker, args=(r, world, port, fault, q)) for r in range(world)]
     for p in procs:
         p.start()
-    res = {}
-    for _ in range(world):
+    import queue as _queue
+    import time as _time
+    res, deadline = {}, _time.time() + 120
+    while len(res) < world and _time.time() < deadline:
         try:
-            r, status, info = q.get(timeout=120)
+            r, status, info = q.get(timeout=2)
             res[r] = (status, info)
-        except Exception:
-            break
+        except _queue.Empty:
+            if not any(p.is_alive() for p in procs) and q.empty():
+                break  # a rank that left without reporting (fault injection) is not waited for
     for p in procs:
         p.join(timeout=30)
         if p.is_alive():
@@ -138,3 +148,12 @@ def test_plan_dispatch_properties():
         ep.plan_dispatch(ids, 16, 3)
     o2, c2, _ = ep.plan_dispatch(torch.zeros((0, 4), dtype=torch.int64), 16, 4)
     assert o2.numel() == 0 and c2.tolist() == [0, 0, 0, 0]
+
+
+def test_a_peer_that_left_ends_the_collective_with_an_error_not_a_hang():
+    """Host-side failure detection: rank 1 exits between steps; rank 0's next exchange fails within the group timeout."""
+    import time
+    t0 = time.time()
+    res = _run(2, fault="peer_exits")
+    assert 0 in res and res[0][0] == "error", res
+    assert time.time() - t0 < 90
