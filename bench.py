@@ -47,6 +47,20 @@ def measured_peak():
         return HBM_FALLBACK_GBS, "fallback"
 
 
+def tensor_roofline(flops, ms_per_step):
+    """For the batched layer: the same step against the measured dense bf16 throughput (sustained figure)."""
+    if not flops:
+        return {}
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            tf, kind = float(json.load(f)["bf16_tflops_sustained"]), "measured"
+    except Exception:
+        tf, kind = 1400.0, "fallback"
+    got = flops / (ms_per_step * 1e-3) / 1e12
+    return {"roofline_tensor": {"bound": "tensor", "achieved": got, "peak": tf, "unit": "TFLOP/s", "frac": got / tf,
+                                "peak_kind": kind}}
+
+
 class ClockSampler:
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -171,6 +185,7 @@ def other_workload(a, rank, world, device, steps, warmup):
             torch.cuda.synchronize()
 
     peak, peak_kind = measured_peak()
+    flops = None  # set by the batched workloads: multiply-add work of a step on this GPU
     if a.workload == "model":
         # config 4 on what ONE GPU holds: layer 0 dense + (model_layers - 1) MoE layers of the full shapes, full
         # vocabulary, batch 1, greedy decode after a 32-token prompt replay.  A step is one new token through every
@@ -245,6 +260,9 @@ def other_workload(a, rank, world, device, steps, warmup):
         distinct = int(mine.numel())
         alg = distinct * 24772608 / world + 5505024 + 88080384 + 4 * Tl * 7168  # per-GPU estimate, own tokens' routing
         unit_tokens = T
+        # multiply-adds of the pass on this GPU: its share of the T x 8 assignments through three 7168 x 2048 matrices,
+        # its tokens through the shared expert and the router
+        flops = 2.0 * (T * 8 / world * 3 * 7168 * 2048 + Tl * (3 * 7168 * 2048 + 7168 * a.experts))
         workload = "config 2: batched routed-MoE layer, T=%d tokens, %s" % (T, "1 GPU" if world == 1 else "expert parallel x%d, NCCL all-to-all" % world)
         if a.experts != 384:
             workload = "REDUCED CASE (%d experts, profiler capture size) of " % a.experts + workload
@@ -296,6 +314,7 @@ def other_workload(a, rank, world, device, steps, warmup):
                        "l2": "weights and caches rotated over several copies larger than L2"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind, "traffic": None},
+            **tensor_roofline(flops, per_step),
             "gpu_launches": int(launches)}))
     if world > 1:
         dist.destroy_process_group()
