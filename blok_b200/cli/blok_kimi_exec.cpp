@@ -60,6 +60,7 @@ int main(int argc, char **argv) {
     else if (f == "--heads") cfg.heads = (int)u64(argv[i + 1], "heads");
     else if (f == "--q-rank") cfg.q_rank = (int)u64(argv[i + 1], "q-rank");
     else if (f == "--kv-rank") cfg.kv_rank = (int)u64(argv[i + 1], "kv-rank");
+    else if (f == "--prefill-chunk") cfg.prefill_chunk = (int)u64(argv[i + 1], "prefill-chunk");
     else die("unknown flag: " + f);
   }
   if ((index.empty() && !synthetic) || prompt.empty() || tokens == 0) die("bad args");

@@ -85,7 +85,9 @@ __global__ void __launch_bounds__(256) mla_prep_kernel(const uint16_t *__restric
                                                        const uint16_t *__restrict__ q, const float *__restrict__ inv_freq,
                                                        const int *__restrict__ ctx_len, uint16_t *__restrict__ cache,
                                                        long ctx_stride, uint16_t *__restrict__ q_full, int *__restrict__ seq,
-                                                       int heads, int nope, int rope, int kv_rank, float eps) {
+                                                       int heads, int nope, int rope, int kv_rank, float eps,
+                                                       const int *__restrict__ block_table, const int *__restrict__ slot_of,
+                                                       int table_stride, int page_rows) {
   __shared__ float red[32];
   const int b = blockIdx.y, tid = threadIdx.x;
   const int pos = ctx_len[b];
@@ -108,7 +110,11 @@ __global__ void __launch_bounds__(256) mla_prep_kernel(const uint16_t *__restric
   }
   if (tid == 0) seq[b] = pos + 1;
   const uint16_t *kr = kva + (size_t)b * lat_w;
-  uint16_t *row = cache + ((size_t)b * ctx_stride + pos) * lat_w;
+  // dense: sequence b's rows start at b * ctx_stride; paged: the row's page comes from the sequence's block table
+  uint16_t *row = block_table
+                      ? cache + ((size_t)block_table[(size_t)(slot_of ? slot_of[b] : b) * table_stride + pos / page_rows] * page_rows +
+                                 pos % page_rows) * lat_w
+                      : cache + ((size_t)b * ctx_stride + pos) * lat_w;
   float v = 0.f;
   for (int i = tid; i < kv_rank; i += blockDim.x) {
     float a = bf16_bits_to_f32(kr[i]);
@@ -136,6 +142,11 @@ __global__ void __launch_bounds__(256) mla_prep_kernel(const uint16_t *__restric
   }
 }
 
+// ctx[i] = first[0] + i: the positions of the T consecutive tokens of a prefill chunk.
+__global__ void mla_chunk_positions_kernel(const int *__restrict__ first, int T, int *__restrict__ ctx) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < T) ctx[i] = first[0] + i;
+}
 
 // W_UK^T: out[h][j][d] = kv_b[h*(nope+v) + d][j]  (a pure re-arrangement, no arithmetic)
 __global__ void transpose_wuk_kernel(const uint16_t *__restrict__ kv_b, uint16_t *__restrict__ out, int heads, int nope,
@@ -190,6 +201,9 @@ __global__ void mla_merge_kernel(const float *__restrict__ part_o, const float *
 size_t mla_attend_smem_bytes();
 int launch_mla_attend(const uint16_t *q, const uint16_t *cache, long ctx_stride, const int *seq_len, int B, int splits,
                       float scale, float *part_o, float *part_ml, cudaStream_t stream);
+int launch_mla_attend_paged(const uint16_t *q, const uint16_t *pool, const int *block_table, const int *slot_of,
+                            int table_stride, int page_rows, const int *seq_len, int B, int splits, float scale,
+                            float *part_o, float *part_ml, cudaStream_t stream);
 
 static int launch_head_gemv(const uint16_t *w, long w_head_stride, const uint16_t *x, long x_tok_stride,
                             long x_head_stride, uint16_t *y, long y_tok_stride, long y_head_stride, int rows, int cols,
@@ -201,6 +215,8 @@ static int launch_head_gemv(const uint16_t *w, long w_head_stride, const uint16_
 }
 
 static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+constexpr int kMlaMaxBatch = 64;  // sequences (or tokens of a prefill chunk) per call; the mat-vecs take them 8 at a time
 
 }  // namespace blok
 
@@ -219,6 +235,7 @@ struct blok_mla_layer {
   uint16_t *o_lat = nullptr;   // [B, heads, kv_rank]
   uint16_t *av = nullptr;      // [B, heads * v_head]
   int *seq = nullptr;          // [B]
+  int *chunk_pos = nullptr;    // [B] positions of a prefill chunk's tokens
   void *sk_ws = nullptr;       // split-K partial sums and tickets of the projections (zeroed at create)
   size_t sk_bytes = 0;
   float *part_o = nullptr;     // [max_splits * max_batch..]
@@ -253,8 +270,8 @@ extern "C" float blok_mla_softmax_scale(const blok_mla_weights *w) {
 
 extern "C" int blok_mla_layer_create(const blok_mla_weights *w, int max_batch, int max_ctx, blok_mla_layer_t **out) {
   BLOK_REQUIRE(w && out, BLOK_ERR_ARG, "blok_mla_layer_create: null pointer");
-  BLOK_REQUIRE(max_batch >= 1 && max_batch <= 8 && max_ctx >= 1, BLOK_ERR_ARG,
-               "blok_mla_layer_create: need 1 <= max_batch <= 8 and max_ctx >= 1");
+  BLOK_REQUIRE(max_batch >= 1 && max_batch <= kMlaMaxBatch && max_ctx >= 1, BLOK_ERR_ARG,
+               "blok_mla_layer_create: need 1 <= max_batch <= %d and max_ctx >= 1", kMlaMaxBatch);
   BLOK_REQUIRE(w->heads == 64 && w->kv_rank == 512 && w->qk_rope == 64 && w->qk_nope % 32 == 0 && w->v_head % 16 == 0 &&
                    w->hidden % 32 == 0 && w->q_rank % 32 == 0,
                BLOK_ERR_SHAPE,
@@ -285,6 +302,7 @@ extern "C" int blok_mla_layer_create(const blok_mla_weights *w, int max_batch, i
   size_t o_ol = take((size_t)max_batch * w->heads * w->kv_rank * 2);
   size_t o_av = take((size_t)max_batch * w->heads * w->v_head * 2);
   size_t o_seq = take((size_t)max_batch * 4);
+  size_t o_cpos = take((size_t)max_batch * 4);
   size_t o_po = take((size_t)(L->max_splits + max_batch) * w->heads * w->kv_rank * 4);
   size_t o_pml = take((size_t)(L->max_splits + max_batch) * w->heads * 2 * 4);
   L->sk_bytes = bf16_gemv_splitk_workspace_bytes(std::max(std::max(w->q_rank, lat_w), std::max(w->heads * qk_head, w->hidden)));
@@ -310,6 +328,7 @@ extern "C" int blok_mla_layer_create(const blok_mla_weights *w, int max_batch, i
   L->o_lat = reinterpret_cast<uint16_t *>(b + o_ol);
   L->av = reinterpret_cast<uint16_t *>(b + o_av);
   L->seq = reinterpret_cast<int *>(b + o_seq);
+  L->chunk_pos = reinterpret_cast<int *>(b + o_cpos);
   L->part_o = reinterpret_cast<float *>(b + o_po);
   L->part_ml = reinterpret_cast<float *>(b + o_pml);
   L->sk_ws = b + o_sk;
@@ -350,24 +369,44 @@ extern "C" int blok_mla_layer_destroy(blok_mla_layer_t *L) {
   return e == cudaSuccess ? BLOK_OK : cuda_fail(e, "cudaFree(mla layer workspace)");
 }
 
+// Where the latent rows of the sequences of a call live.
+struct CacheRef {
+  uint16_t *base = nullptr;         // dense cache, or the page pool
+  long seq_stride = 0;              // dense: rows between consecutive sequences; 0 = every entry is the same sequence
+  long ctx_cap = 0;                 // rows one sequence can hold (bounds the context splits)
+  const int *block_table = nullptr; // paged when non-null: int32 [slots, table_stride] page numbers
+  const int *slot_of = nullptr;     // paged: table row of batch entry b (null: b)
+  int table_stride = 0, page_rows = 0;
+};
+
 // Context splits per sequence: enough CTAs to fill the GPU, but never more than one per 64 rows of the cache
-// allocation (the sequence lengths live on the device; ctx_stride bounds them), so that a short cache is not cut
+// allocation (the sequence lengths live on the device; the capacity bounds them), so that a short cache is not cut
 // into slivers whose merge costs more than the attention.
-static int splits_for(const blok_mla_layer *L, int B, long ctx_stride) {
+static int splits_for(const blok_mla_layer *L, int B, long ctx_cap) {
   long s = L->max_splits / B;
-  const long cap = (ctx_stride + 63) / 64;
+  const long cap = (ctx_cap + 63) / 64;
   if (s > cap) s = cap;
   return s < 1 ? 1 : (int)s;
 }
 
-static int attend_and_merge(blok_mla_layer *L, const uint16_t *q, const uint16_t *cache, long ctx_stride,
-                            const int *seq_len, int B, float scale, uint16_t *o_lat, cudaStream_t stream) {
-  const int splits = splits_for(L, B, ctx_stride);
-  int rc = launch_mla_attend(q, cache, ctx_stride, seq_len, B, splits, scale, L->part_o, L->part_ml, stream);
+static int attend_and_merge(blok_mla_layer *L, const uint16_t *q, const CacheRef &c, const int *seq_len, int B, float scale,
+                            uint16_t *o_lat, cudaStream_t stream) {
+  const int splits = splits_for(L, B, c.ctx_cap);
+  int rc = c.block_table ? launch_mla_attend_paged(q, c.base, c.block_table, c.slot_of, c.table_stride, c.page_rows, seq_len, B,
+                                                   splits, scale, L->part_o, L->part_ml, stream)
+                         : launch_mla_attend(q, c.base, c.seq_stride, seq_len, B, splits, scale, L->part_o, L->part_ml, stream);
   if (rc) return rc;
   mla_merge_kernel<<<dim3(L->w.heads, B), 128, (size_t)splits * sizeof(float), stream>>>(L->part_o, L->part_ml, splits, L->w.heads, L->w.kv_rank,
                                                            o_lat);
   return launch_status("mla_merge_kernel");
+}
+
+static int check_paged(const char *who, const void *pool, const int *block_table, int table_stride, int page_rows) {
+  BLOK_REQUIRE(pool && block_table, BLOK_ERR_ARG, "%s: null pointer", who);
+  BLOK_REQUIRE((reinterpret_cast<uintptr_t>(pool) & 15) == 0, BLOK_ERR_ARG, "%s: the pool must be 16-byte aligned", who);
+  BLOK_REQUIRE(table_stride >= 1 && page_rows >= 32 && page_rows % 32 == 0, BLOK_ERR_SHAPE,
+               "%s: page_rows (%d) must be a positive multiple of 32 and table_stride (%d) >= 1", who, page_rows, table_stride);
+  return BLOK_OK;
 }
 
 extern "C" int blok_mla_attend(blok_mla_layer_t *L, const blok_bf16_t *q, const blok_bf16_t *cache, long ctx_stride,
@@ -378,7 +417,76 @@ extern "C" int blok_mla_attend(blok_mla_layer_t *L, const blok_bf16_t *q, const 
                L->max_batch);
   BLOK_REQUIRE((reinterpret_cast<uintptr_t>(q) & 15) == 0 && (reinterpret_cast<uintptr_t>(cache) & 15) == 0, BLOK_ERR_ARG,
                "blok_mla_attend: q and cache must be 16-byte aligned");
-  return attend_and_merge(L, q, cache, ctx_stride, seq_len, B, softmax_scale, o_lat, (cudaStream_t)stream);
+  CacheRef c;
+  c.base = const_cast<uint16_t *>(cache);
+  c.seq_stride = c.ctx_cap = ctx_stride;
+  return attend_and_merge(L, q, c, seq_len, B, softmax_scale, o_lat, (cudaStream_t)stream);
+}
+
+extern "C" int blok_mla_attend_paged(blok_mla_layer_t *L, const blok_bf16_t *q, const blok_bf16_t *pool, const int *block_table,
+                                     const int *slot_of, int table_stride, int page_rows, const int *seq_len, int B,
+                                     float softmax_scale, blok_bf16_t *o_lat, blok_stream_t stream) {
+  BLOK_REQUIRE(L && q && seq_len && o_lat, BLOK_ERR_ARG, "blok_mla_attend_paged: null pointer");
+  BLOK_REQUIRE(B >= 1 && B <= L->max_batch, BLOK_ERR_SHAPE, "blok_mla_attend_paged: B=%d outside [1, %d]", B, L->max_batch);
+  BLOK_REQUIRE((reinterpret_cast<uintptr_t>(q) & 15) == 0, BLOK_ERR_ARG, "blok_mla_attend_paged: q must be 16-byte aligned");
+  if (int rc = check_paged("blok_mla_attend_paged", pool, block_table, table_stride, page_rows)) return rc;
+  CacheRef c;
+  c.base = const_cast<uint16_t *>(pool);
+  c.ctx_cap = (long)table_stride * page_rows;
+  c.block_table = block_table;
+  c.slot_of = slot_of;
+  c.table_stride = table_stride;
+  c.page_rows = page_rows;
+  return attend_and_merge(L, q, c, seq_len, B, softmax_scale, o_lat, (cudaStream_t)stream);
+}
+
+// The attention block for B entries (sequences, or the tokens of a prefill chunk): projections, cache append,
+// attention, output projection.  The mat-vec kernels take up to 8 tokens per launch, so larger B goes through them
+// in groups of 8 (the weights of a later group come from L2 where they fit).
+static int decode_body(blok_mla_layer *L, const uint16_t *n, const CacheRef &c, const int *ctx_len, int B, uint16_t *out,
+                       blok_stream_t stream_) {
+  const blok_mla_weights &w = L->w;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const int lat_w = w.kv_rank + w.qk_rope, qk_head = w.qk_nope + w.qk_rope;
+  const size_t q_row = (size_t)w.heads * qk_head, qf_row = (size_t)w.heads * lat_w, ol_row = (size_t)w.heads * w.kv_rank,
+               av_row = (size_t)w.heads * w.v_head;
+  int rc;
+  // q_a -> RMSNorm -> q_b   (:813-815)
+  for (int b0 = 0; b0 < B; b0 += 8)
+    if ((rc = launch_bf16_gemv_splitk(w.q_a, n + (size_t)b0 * w.hidden, L->qa + (size_t)b0 * w.q_rank, nullptr, w.q_rank, w.hidden,
+                                      std::min(8, B - b0), L->sk_ws, L->sk_bytes, stream)))
+      return rc;
+  if ((rc = blok_rmsnorm(L->qa, w.q_a_ln, L->qa, B, w.q_rank, w.rms_eps, stream_))) return rc;
+  for (int b0 = 0; b0 < B; b0 += 8)
+    if ((rc = launch_bf16_gemv_splitk(w.q_b, L->qa + (size_t)b0 * w.q_rank, L->q + b0 * q_row, nullptr, w.heads * qk_head, w.q_rank,
+                                      std::min(8, B - b0), L->sk_ws, L->sk_bytes, stream)))
+      return rc;
+  // kv_a; norm of c_kv, RoPE of k_pe and of q's rope part, cache append   (:816-824)
+  for (int b0 = 0; b0 < B; b0 += 8)
+    if ((rc = launch_bf16_gemv_splitk(w.kv_a, n + (size_t)b0 * w.hidden, L->kva + (size_t)b0 * lat_w, nullptr, lat_w, w.hidden,
+                                      std::min(8, B - b0), L->sk_ws, L->sk_bytes, stream)))
+      return rc;
+  mla_prep_kernel<<<dim3(1 + (w.heads * (w.qk_rope / 2) + 255) / 256, B), 256, 0, stream>>>(
+      L->kva, w.kv_a_ln, L->q, L->inv_freq, ctx_len, c.base, c.seq_stride, L->q_full, L->seq, w.heads, w.qk_nope, w.qk_rope,
+      w.kv_rank, w.rms_eps, c.block_table, c.slot_of, c.table_stride, c.page_rows);
+  if ((rc = launch_status("mla_prep_kernel"))) return rc;
+  // q_abs = W_UK^T q_nope
+  for (int b0 = 0; b0 < B; b0 += 8)
+    if ((rc = launch_head_gemv(L->wuk_t, (long)w.kv_rank * w.qk_nope, L->q + b0 * q_row, (long)q_row, qk_head, L->q_full + b0 * qf_row,
+                               (long)qf_row, lat_w, w.kv_rank, w.qk_nope, w.heads, std::min(8, B - b0), stream)))
+      return rc;
+  if ((rc = attend_and_merge(L, L->q_full, c, L->seq, B, L->scale, L->o_lat, stream))) return rc;
+  // out_h = W_UV o_lat_h, then o_proj   (:826)
+  for (int b0 = 0; b0 < B; b0 += 8)
+    if ((rc = launch_head_gemv(w.kv_b + (size_t)w.qk_nope * w.kv_rank, (long)(w.qk_nope + w.v_head) * w.kv_rank, L->o_lat + b0 * ol_row,
+                               (long)ol_row, w.kv_rank, L->av + b0 * av_row, (long)av_row, w.v_head, w.v_head, w.kv_rank, w.heads,
+                               std::min(8, B - b0), stream)))
+      return rc;
+  for (int b0 = 0; b0 < B; b0 += 8)
+    if ((rc = launch_bf16_gemv_splitk(w.o, L->av + b0 * av_row, out + (size_t)b0 * w.hidden, nullptr, w.hidden, w.heads * w.v_head,
+                                      std::min(8, B - b0), L->sk_ws, L->sk_bytes, stream)))
+      return rc;
+  return BLOK_OK;
 }
 
 extern "C" int blok_mla_decode(blok_mla_layer_t *L, const blok_bf16_t *n, blok_bf16_t *cache, long ctx_stride,
@@ -388,29 +496,41 @@ extern "C" int blok_mla_decode(blok_mla_layer_t *L, const blok_bf16_t *n, blok_b
                L->max_batch);
   BLOK_REQUIRE((reinterpret_cast<uintptr_t>(n) & 15) == 0 && (reinterpret_cast<uintptr_t>(cache) & 15) == 0, BLOK_ERR_ARG,
                "blok_mla_decode: n and cache must be 16-byte aligned");
-  const blok_mla_weights &w = L->w;
-  cudaStream_t stream = (cudaStream_t)stream_;
-  const int lat_w = w.kv_rank + w.qk_rope, qk_head = w.qk_nope + w.qk_rope;
-  int rc;
-  // q_a -> RMSNorm -> q_b   (:813-815)
-  if ((rc = launch_bf16_gemv_splitk(w.q_a, n, L->qa, nullptr, w.q_rank, w.hidden, B, L->sk_ws, L->sk_bytes, stream))) return rc;
-  if ((rc = blok_rmsnorm(L->qa, w.q_a_ln, L->qa, B, w.q_rank, w.rms_eps, stream_))) return rc;
-  if ((rc = launch_bf16_gemv_splitk(w.q_b, L->qa, L->q, nullptr, w.heads * qk_head, w.q_rank, B, L->sk_ws, L->sk_bytes, stream))) return rc;
-  // kv_a; norm of c_kv, RoPE of k_pe and of q's rope part, cache append   (:816-824)
-  if ((rc = launch_bf16_gemv_splitk(w.kv_a, n, L->kva, nullptr, lat_w, w.hidden, B, L->sk_ws, L->sk_bytes, stream))) return rc;
-  mla_prep_kernel<<<dim3(1 + (w.heads * (w.qk_rope / 2) + 255) / 256, B), 256, 0, stream>>>(
-      L->kva, w.kv_a_ln, L->q, L->inv_freq, ctx_len, cache, ctx_stride, L->q_full, L->seq, w.heads, w.qk_nope, w.qk_rope,
-      w.kv_rank, w.rms_eps);
-  if ((rc = launch_status("mla_prep_kernel"))) return rc;
-  // q_abs = W_UK^T q_nope
-  if ((rc = launch_head_gemv(L->wuk_t, (long)w.kv_rank * w.qk_nope, L->q, (long)w.heads * qk_head, qk_head, L->q_full,
-                             (long)w.heads * lat_w, lat_w, w.kv_rank, w.qk_nope, w.heads, B, stream)))
-    return rc;
-  if ((rc = attend_and_merge(L, L->q_full, cache, ctx_stride, L->seq, B, L->scale, L->o_lat, stream))) return rc;
-  // out_h = W_UV o_lat_h, then o_proj   (:826)
-  if ((rc = launch_head_gemv(w.kv_b + (size_t)w.qk_nope * w.kv_rank, (long)(w.qk_nope + w.v_head) * w.kv_rank, L->o_lat,
-                             (long)w.heads * w.kv_rank, w.kv_rank, L->av, (long)w.heads * w.v_head, w.v_head, w.v_head,
-                             w.kv_rank, w.heads, B, stream)))
-    return rc;
-  return launch_bf16_gemv_splitk(w.o, L->av, out, nullptr, w.hidden, w.heads * w.v_head, B, L->sk_ws, L->sk_bytes, stream);
+  CacheRef c;
+  c.base = cache;
+  c.seq_stride = c.ctx_cap = ctx_stride;
+  return decode_body(L, n, c, ctx_len, B, out, stream_);
+}
+
+extern "C" int blok_mla_prefill(blok_mla_layer_t *L, const blok_bf16_t *n, blok_bf16_t *cache, long ctx_cap, const int *first_pos,
+                                int T, blok_bf16_t *out, blok_stream_t stream_) {
+  BLOK_REQUIRE(L && n && cache && first_pos && out, BLOK_ERR_ARG, "blok_mla_prefill: null pointer");
+  BLOK_REQUIRE(T >= 1 && T <= L->max_batch && ctx_cap >= T, BLOK_ERR_SHAPE,
+               "blok_mla_prefill: T=%d outside [1, %d] or larger than the cache (%ld rows)", T, L->max_batch, ctx_cap);
+  BLOK_REQUIRE((reinterpret_cast<uintptr_t>(n) & 15) == 0 && (reinterpret_cast<uintptr_t>(cache) & 15) == 0, BLOK_ERR_ARG,
+               "blok_mla_prefill: n and cache must be 16-byte aligned");
+  mla_chunk_positions_kernel<<<(T + 63) / 64, 64, 0, (cudaStream_t)stream_>>>(first_pos, T, L->chunk_pos);
+  if (int rc = launch_status("mla_chunk_positions_kernel")) return rc;
+  CacheRef c;
+  c.base = cache;
+  c.seq_stride = 0;  // every token of the chunk appends to, and reads, the same sequence
+  c.ctx_cap = ctx_cap;
+  return decode_body(L, n, c, L->chunk_pos, T, out, stream_);
+}
+
+extern "C" int blok_mla_decode_paged(blok_mla_layer_t *L, const blok_bf16_t *n, blok_bf16_t *pool, const int *block_table,
+                                     const int *slot_of, int table_stride, int page_rows, const int *ctx_len, int B,
+                                     blok_bf16_t *out, blok_stream_t stream_) {
+  BLOK_REQUIRE(L && n && ctx_len && out, BLOK_ERR_ARG, "blok_mla_decode_paged: null pointer");
+  BLOK_REQUIRE(B >= 1 && B <= L->max_batch, BLOK_ERR_SHAPE, "blok_mla_decode_paged: B=%d outside [1, %d]", B, L->max_batch);
+  BLOK_REQUIRE((reinterpret_cast<uintptr_t>(n) & 15) == 0, BLOK_ERR_ARG, "blok_mla_decode_paged: n must be 16-byte aligned");
+  if (int rc = check_paged("blok_mla_decode_paged", pool, block_table, table_stride, page_rows)) return rc;
+  CacheRef c;
+  c.base = pool;
+  c.ctx_cap = (long)table_stride * page_rows;
+  c.block_table = block_table;
+  c.slot_of = slot_of;
+  c.table_stride = table_stride;
+  c.page_rows = page_rows;
+  return decode_body(L, n, c, ctx_len, B, out, stream_);
 }

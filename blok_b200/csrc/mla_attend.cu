@@ -39,10 +39,16 @@ size_t mla_attend_smem_bytes() {
 }
 
 // grid = (splits, B).  part_o fp32 [B, splits, 64, 512] (unnormalised), part_ml fp32 [B, splits, 64, 2].
+// Dense cache: sequence b's rows start at cache + b * ctx_stride rows (ctx_stride 0: every b reads the same rows, the
+// tokens of one prefill chunk).  PAGED: cache is a pool of pages of page_rows rows (a multiple of the 32-row tile, so
+// a tile never straddles two pages); row t of sequence b lives in page block_table[slot * table_stride + t / page_rows]
+// with slot = slot_of[b] (b itself when slot_of is null).
+template <bool PAGED>
 __global__ void __launch_bounds__(kAttThreads, 1)
     mla_attend_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict__ cache, long ctx_stride,
                       const int *__restrict__ seq_len, float scale, float *__restrict__ part_o,
-                      float *__restrict__ part_ml) {
+                      float *__restrict__ part_ml, const int *__restrict__ block_table, const int *__restrict__ slot_of,
+                      int table_stride, int page_rows) {
   extern __shared__ __align__(16) unsigned char smem[];
   unsigned char *Qs = smem;
   unsigned char *KVs = Qs + (size_t)kAttHeads * kAttPitch;
@@ -65,14 +71,22 @@ __global__ void __launch_bounds__(kAttThreads, 1)
   }
   const uint32_t Qs_a = (uint32_t)__cvta_generic_to_shared(Qs);
   const uint32_t KVs_a = (uint32_t)__cvta_generic_to_shared(KVs);
-  const uint16_t *cache_b = cache + (size_t)b * ctx_stride * kAttD;
+  const uint16_t *cache_b = PAGED ? cache : cache + (size_t)b * ctx_stride * kAttD;
+  const int *table_b = PAGED ? block_table + (size_t)(slot_of ? slot_of[b] : b) * table_stride : nullptr;
 
   auto load_tile = [&](int tile, int buf) {
     constexpr int per_row = kAttD * 2 / 16;  // 72 uint4 per row
+    const uint16_t *base = cache_b;
+    int first = 0;  // the row of `base` that holds the tile's first token
+    if (PAGED) {
+      const int t0 = tile * kAttTile;
+      base = cache + (size_t)table_b[t0 / page_rows] * page_rows * kAttD;
+      first = t0 % page_rows - t0;
+    }
     for (int u = tid; u < kAttTile * per_row; u += kAttThreads) {
       int r = u / per_row, c = u - r * per_row;
       int tok = min(tile * kAttTile + r, seq - 1);  // rows past the end repeat the last token; they are masked
-      att_cp16(KVs_a + (uint32_t)(buf * kAttTile + r) * kAttPitch + c * 16, cache_b + (size_t)tok * kAttD + c * 8);
+      att_cp16(KVs_a + (uint32_t)(buf * kAttTile + r) * kAttPitch + c * 16, base + (size_t)(tok + first) * kAttD + c * 8);
     }
   };
   {
@@ -215,12 +229,27 @@ int launch_mla_attend(const uint16_t *q, const uint16_t *cache, long ctx_stride,
   static bool configured = false;
   const size_t smem = mla_attend_smem_bytes();
   if (!configured) {
-    BLOK_CUDA(cudaFuncSetAttribute(mla_attend_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    BLOK_CUDA(cudaFuncSetAttribute(mla_attend_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
-  mla_attend_kernel<<<dim3(splits, B), kAttThreads, smem, stream>>>(q, cache, ctx_stride, seq_len, scale, part_o,
-                                                                   part_ml);
+  mla_attend_kernel<false><<<dim3(splits, B), kAttThreads, smem, stream>>>(q, cache, ctx_stride, seq_len, scale, part_o,
+                                                                          part_ml, nullptr, nullptr, 0, 0);
   return launch_status("mla_attend_kernel");
+}
+
+// The same over a paged pool: page_rows must be a positive multiple of the kernel's 32-row tile.
+int launch_mla_attend_paged(const uint16_t *q, const uint16_t *pool, const int *block_table, const int *slot_of,
+                            int table_stride, int page_rows, const int *seq_len, int B, int splits, float scale,
+                            float *part_o, float *part_ml, cudaStream_t stream) {
+  static bool configured = false;
+  const size_t smem = mla_attend_smem_bytes();
+  if (!configured) {
+    BLOK_CUDA(cudaFuncSetAttribute(mla_attend_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  mla_attend_kernel<true><<<dim3(splits, B), kAttThreads, smem, stream>>>(q, pool, 0, seq_len, scale, part_o, part_ml,
+                                                                         block_table, slot_of, table_stride, page_rows);
+  return launch_status("mla_attend_kernel(paged)");
 }
 
 }  // namespace blok

@@ -42,10 +42,12 @@ __global__ void fill_f32_kernel(float *p, size_t n, uint64_t key, float std) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) p[i] = unit_normal(key, i) * std;
 }
-__global__ void advance_kernel(int *pos, int n) {
+__global__ void advance_kernel(int *pos, int n, int by) {
   int i = threadIdx.x;
-  if (i < n) pos[i] += 1;
+  if (i < n) pos[i] += by;
 }
+
+constexpr int kMaxBatch = 64;  // sequences per step, and tokens per prefill chunk
 
 struct Tensor {
   void *ptr = nullptr;
@@ -67,7 +69,10 @@ struct blok_model {
   std::map<std::string, blok::Tensor> top;
   std::vector<void *> allocations;
   // step buffers
-  uint16_t *x = nullptr, *n = nullptr, *tmp = nullptr;  // [max_batch, hidden]
+  uint16_t *x = nullptr, *n = nullptr, *tmp = nullptr;  // [max(max_batch, prefill_chunk), hidden]
+  uint32_t *prompt_ids = nullptr;                       // [max_ctx] a prompt given on the host (prefill_chunk >= 1)
+  int rows = 0;                                         // max(max_batch, prefill_chunk)
+  bool moe_batched_ok = false;                          // the layer sizes fit the grouped-GEMM kernels
   int *pos = nullptr;                                   // [max_batch]
   uint32_t *ids = nullptr, *next = nullptr;             // [max_batch]
   void *mlp_ws = nullptr;
@@ -77,9 +82,9 @@ struct blok_model {
   uint64_t seed = 0, counter = 0;
   // One CUDA graph of the whole step per batch size: a step is ~16 small launches per layer and the host cannot issue
   // them as fast as the GPU runs them.  steps_seen counts eager steps (the first one also sets kernel attributes).
-  cudaGraphExec_t step_graph[9] = {};
-  long long graph_launches[9] = {};  // kernels in each graph, added to the launch counter at every replay
-  int steps_seen[9] = {};
+  cudaGraphExec_t step_graph[blok::kMaxBatch + 1] = {};
+  long long graph_launches[blok::kMaxBatch + 1] = {};  // kernels in each graph, added to the launch counter at every replay
+  int steps_seen[blok::kMaxBatch + 1] = {};
   bool graphs_enabled = true;
 };
 
@@ -125,6 +130,10 @@ T *tp(const std::map<std::string, Tensor> &m, const char *name) {
 
 int build(blok_model *m) {
   const blok_model_config &c = m->cfg;
+  m->rows = c.max_batch > c.prefill_chunk ? c.max_batch : c.prefill_chunk;
+  // the grouped-GEMM form of the MoE layer (blok_moe_batched) serves prefill chunks and steps of more than 8 sequences
+  m->moe_batched_ok = m->rows > 1 && c.first_dense < c.layers && c.hidden % 512 == 0 && c.inter % 512 == 0 &&
+                      c.experts % 128 == 0 && c.shared_inter % 512 == 0;
   const size_t H = c.hidden;
   const float wstd = 0.006f;
   int rc;
@@ -184,7 +193,7 @@ int build(blok_model *m) {
     mw.q_b = tp<uint16_t>(L.t, "q_b_proj"); mw.kv_a = tp<uint16_t>(L.t, "kv_a_proj_with_mqa");
     mw.kv_a_ln = tp<uint16_t>(L.t, "kv_a_layernorm"); mw.kv_b = tp<uint16_t>(L.t, "kv_b_proj");
     mw.o = tp<uint16_t>(L.t, "o_proj");
-    if ((rc = blok_mla_layer_create(&mw, c.max_batch, c.max_ctx, &L.mla))) return rc;
+    if ((rc = blok_mla_layer_create(&mw, m->rows, c.max_ctx, &L.mla))) return rc;
     if (l >= c.first_dense) {
       blok_moe_weights ew;
       memset(&ew, 0, sizeof(ew));
@@ -196,18 +205,19 @@ int build(blok_model *m) {
       ew.down_w = tp<uint32_t>(L.t, "down_w"); ew.down_s = tp<uint16_t>(L.t, "down_s");
       ew.shared_gate = tp<uint16_t>(L.t, "shared_gate"); ew.shared_up = tp<uint16_t>(L.t, "shared_up");
       ew.shared_down = tp<uint16_t>(L.t, "shared_down");
-      if ((rc = blok_moe_layer_create(&ew, 1, &L.moe))) return rc;
+      if ((rc = blok_moe_layer_create(&ew, m->moe_batched_ok ? m->rows : 1, &L.moe))) return rc;
     }
   }
   void *p;
-  const size_t act = (size_t)c.max_batch * c.hidden * 2;
+  const size_t act = (size_t)m->rows * c.hidden * 2;
   if ((rc = dev_alloc(m, act, &p))) return rc; m->x = static_cast<uint16_t *>(p);
   if ((rc = dev_alloc(m, act, &p))) return rc; m->n = static_cast<uint16_t *>(p);
   if ((rc = dev_alloc(m, act, &p))) return rc; m->tmp = static_cast<uint16_t *>(p);
   if ((rc = dev_alloc(m, c.max_batch * 4, &p))) return rc; m->pos = static_cast<int *>(p);
-  if ((rc = dev_alloc(m, c.max_batch * 4, &p))) return rc; m->ids = static_cast<uint32_t *>(p);
-  if ((rc = dev_alloc(m, c.max_batch * 4, &p))) return rc; m->next = static_cast<uint32_t *>(p);
-  m->mlp_ws_bytes = blok_bf16_mlp_workspace_bytes(c.hidden, c.dense_inter > 0 ? c.dense_inter : 32, 1);
+  if ((rc = dev_alloc(m, m->rows * 4, &p))) return rc; m->ids = static_cast<uint32_t *>(p);
+  if ((rc = dev_alloc(m, m->rows * 4, &p))) return rc; m->next = static_cast<uint32_t *>(p);
+  if ((rc = dev_alloc(m, (size_t)(c.prefill_chunk > 0 ? c.max_ctx : 1) * 4, &p))) return rc; m->prompt_ids = static_cast<uint32_t *>(p);
+  m->mlp_ws_bytes = blok_bf16_mlp_workspace_bytes(c.hidden, c.dense_inter > 0 ? c.dense_inter : 32, 8);
   if ((rc = dev_alloc(m, m->mlp_ws_bytes, &m->mlp_ws))) return rc;
   m->head_ws_bytes = blok_lm_head_workspace_bytes(c.vocab, c.max_batch);
   if ((rc = dev_alloc(m, m->head_ws_bytes, &m->head_ws))) return rc;
@@ -250,7 +260,8 @@ extern "C" int blok_model_destroy(blok_model_t *m) {
 extern "C" int blok_model_create_synthetic(const blok_model_config *cfg, uint64_t seed, blok_model_t **out) {
   BLOK_REQUIRE(cfg && out, BLOK_ERR_ARG, "blok_model_create_synthetic: null pointer");
   BLOK_REQUIRE(cfg->layers >= 1 && cfg->first_dense >= 0 && cfg->first_dense <= cfg->layers && cfg->vocab > 0 &&
-                   cfg->hidden % 256 == 0 && cfg->max_batch >= 1 && cfg->max_batch <= 8 && cfg->max_ctx >= 1,
+                   cfg->hidden % 256 == 0 && cfg->max_batch >= 1 && cfg->max_batch <= kMaxBatch && cfg->max_ctx >= 1 &&
+                   cfg->prefill_chunk >= 0 && cfg->prefill_chunk <= kMaxBatch,
                BLOK_ERR_SHAPE, "blok_model_create_synthetic: unsupported configuration");
   BLOK_REQUIRE(cfg->first_dense == 0 || (cfg->dense_inter > 0 && cfg->dense_inter % 32 == 0), BLOK_ERR_SHAPE,
                "blok_model_create_synthetic: dense_inter %d must be a positive multiple of 32", cfg->dense_inter);
@@ -301,47 +312,73 @@ extern "C" int blok_model_reset(blok_model_t *m) {
   return BLOK_OK;
 }
 
+// The feed-forward half of layer l for T rows: m->n -> m->tmp (:829-877 without the residual add).  Steps of up to 8
+// sequences take the batch-1 kernels row by row; prefill chunks and larger steps take the grouped GEMM for the routed
+// experts where the sizes fit it, and the dense layer 8 rows at a time.
+static int ffn_rows(blok_model_t *m, int l, int T, bool chunk, blok_stream_t stream_) {
+  const blok_model_config &c = m->cfg;
+  auto &L = m->layers[l];
+  const size_t H = c.hidden;
+  const bool wide = chunk ? T > 1 : T > 8;
+  int rc = BLOK_OK;
+  if (l < c.first_dense) {
+    // rows per call: up to 8, fewer when 8 rows of the wider of the two vectors would not fit in shared memory
+    const size_t row_bytes = (size_t)(c.hidden > c.dense_inter ? c.hidden : c.dense_inter) * 2 + 64;
+    int group = wide ? 8 : 1;
+    while (group > 1 && row_bytes * group > 200 * 1024) --group;
+    for (int b = 0; b < T && !rc; b += group)
+      rc = blok_bf16_mlp(tp<uint16_t>(L.t, "gate_proj"), tp<uint16_t>(L.t, "up_proj"), tp<uint16_t>(L.t, "down_proj"), m->n + b * H,
+                         m->tmp + b * H, c.hidden, c.dense_inter, T - b < group ? T - b : group, m->mlp_ws, m->mlp_ws_bytes, stream_);
+    return rc;
+  }
+  if (wide && m->moe_batched_ok) return blok_moe_batched(L.moe, m->n, T, m->tmp, nullptr, nullptr, stream_);
+  for (int b = 0; b < T && !rc; ++b) rc = blok_moe_decode(L.moe, m->n + b * H, m->tmp + b * H, nullptr, nullptr, stream_);
+  return rc;
+}
+
+// Embedding and every layer for T rows of m->ids; leaves the final-normed hidden states in m->n.  chunk: the rows are
+// consecutive tokens of sequence 0 (a prefill chunk); otherwise row b is the next token of sequence b.
+static int layers_body(blok_model_t *m, int T, bool chunk, blok_stream_t stream_) {
+  const blok_model_config &c = m->cfg;
+  int rc;
+  if ((rc = blok_embed(tp<uint16_t>(m->top, "embed_tokens"), m->ids, c.vocab, c.hidden, T, m->x, stream_))) return rc;  // :802
+  // Every residual add is fused with the RMSNorm that follows it (blok_add_rmsnorm), so a layer is: attention on n,
+  // x += attention | n = norm(x), feed-forward on n, x += feed-forward | n = the next layer's (or the final) norm.
+  if ((rc = blok_rmsnorm(m->x, tp<uint16_t>(m->layers[0].t, "input_layernorm"), m->n, T, c.hidden, c.rms_eps, stream_))) return rc;
+  for (int l = 0; l < c.layers; ++l) {
+    auto &L = m->layers[l];
+    // attention block, :812-827
+    rc = chunk ? blok_mla_prefill(L.mla, m->n, L.cache, c.max_ctx, m->pos, T, m->tmp, stream_)
+               : blok_mla_decode(L.mla, m->n, L.cache, c.max_ctx, m->pos, T, m->tmp, stream_);
+    if (rc) return rc;
+    if ((rc = blok_add_rmsnorm(m->x, m->tmp, tp<uint16_t>(L.t, "post_attention_layernorm"), m->n, T, c.hidden, c.rms_eps, stream_)))
+      return rc;
+    if ((rc = ffn_rows(m, l, T, chunk, stream_))) return rc;  // :829-877
+    const bool last = l + 1 == c.layers;
+    const uint16_t *next_ln = last ? tp<uint16_t>(m->top, "norm") : tp<uint16_t>(m->layers[l + 1].t, "input_layernorm");  // :812 / :880
+    if ((rc = blok_add_rmsnorm(m->x, m->tmp, next_ln, m->n, T, c.hidden, last ? c.final_rms_eps : c.rms_eps, stream_))) return rc;
+  }
+  return BLOK_OK;
+}
+
 // The launches of one decode step on `stream`, reading m->ids and writing m->next; every position and length is device
 // resident, so the same sequence of launches serves every step and can be replayed from a graph.
 static int step_body(blok_model_t *m, int B, blok_stream_t stream_) {
   const blok_model_config &c = m->cfg;
   cudaStream_t stream = (cudaStream_t)stream_;
-  const size_t H = c.hidden;
   int rc;
-  if ((rc = blok_embed(tp<uint16_t>(m->top, "embed_tokens"), m->ids, c.vocab, c.hidden, B, m->x, stream_))) return rc;  // :802
-  // Every residual add is fused with the RMSNorm that follows it (blok_add_rmsnorm), so a layer is: attention on n,
-  // x += attention | n = norm(x), feed-forward on n, x += feed-forward | n = the next layer's (or the final) norm.
-  if ((rc = blok_rmsnorm(m->x, tp<uint16_t>(m->layers[0].t, "input_layernorm"), m->n, B, c.hidden, c.rms_eps, stream_))) return rc;
-  for (int l = 0; l < c.layers; ++l) {
-    auto &L = m->layers[l];
-    // attention block, :812-827
-    if ((rc = blok_mla_decode(L.mla, m->n, L.cache, c.max_ctx, m->pos, B, m->tmp, stream_))) return rc;
-    if ((rc = blok_add_rmsnorm(m->x, m->tmp, tp<uint16_t>(L.t, "post_attention_layernorm"), m->n, B, c.hidden, c.rms_eps, stream_)))
+  if ((rc = layers_body(m, B, false, stream_))) return rc;
+  for (int b = 0; b < B; b += 8)  // the sampler takes 8 rows per call
+    if ((rc = blok_lm_head_argmax(tp<uint16_t>(m->top, "lm_head"), m->n + (size_t)b * c.hidden, c.vocab, c.hidden, B - b < 8 ? B - b : 8,
+                                  m->next + b, m->head_ws, m->head_ws_bytes, stream_)))
       return rc;
-    // feed-forward block, :829-877
-    for (int b = 0; b < B; ++b) {
-      if (l < c.first_dense)
-        rc = blok_bf16_mlp(tp<uint16_t>(L.t, "gate_proj"), tp<uint16_t>(L.t, "up_proj"), tp<uint16_t>(L.t, "down_proj"),
-                           m->n + b * H, m->tmp + b * H, c.hidden, c.dense_inter, 1, m->mlp_ws, m->mlp_ws_bytes, stream_);
-      else
-        rc = blok_moe_decode(L.moe, m->n + b * H, m->tmp + b * H, nullptr, nullptr, stream_);
-      if (rc) return rc;
-    }
-    const bool last = l + 1 == c.layers;
-    const uint16_t *next_ln = last ? tp<uint16_t>(m->top, "norm") : tp<uint16_t>(m->layers[l + 1].t, "input_layernorm");  // :812 / :880
-    if ((rc = blok_add_rmsnorm(m->x, m->tmp, next_ln, m->n, B, c.hidden, last ? c.final_rms_eps : c.rms_eps, stream_))) return rc;
-  }
-  if ((rc = blok_lm_head_argmax(tp<uint16_t>(m->top, "lm_head"), m->n, c.vocab, c.hidden, B, m->next, m->head_ws,
-                                m->head_ws_bytes, stream_)))
-    return rc;
-  advance_kernel<<<1, 32, 0, stream>>>(m->pos, B);
+  advance_kernel<<<1, 64, 0, stream>>>(m->pos, B, 1);
   return launch_status("advance_kernel");
 }
 
 extern "C" int blok_model_step(blok_model_t *m, const uint32_t *ids, int B, uint32_t *next_ids, blok_stream_t stream_) {
   BLOK_REQUIRE(m && ids && next_ids, BLOK_ERR_ARG, "blok_model_step: null pointer");
-  BLOK_REQUIRE(B >= 1 && B <= m->cfg.max_batch && B <= 8, BLOK_ERR_SHAPE, "blok_model_step: B=%d outside [1, %d]", B,
-               m->cfg.max_batch);
+  BLOK_REQUIRE(B >= 1 && B <= m->cfg.max_batch, BLOK_ERR_SHAPE, "blok_model_step: B=%d outside [1, %d]", B, m->cfg.max_batch);
   cudaStream_t stream = (cudaStream_t)stream_;
   if (ids != m->ids) BLOK_CUDA(cudaMemcpyAsync(m->ids, ids, (size_t)B * 4, cudaMemcpyDeviceToDevice, stream));
   int rc = BLOK_OK;
@@ -383,6 +420,29 @@ extern "C" int blok_model_step(blok_model_t *m, const uint32_t *ids, int B, uint
   return BLOK_OK;
 }
 
+extern "C" int blok_model_prefill(blok_model_t *m, const uint32_t *ids, int n, uint32_t *next_id, blok_stream_t stream_) {
+  BLOK_REQUIRE(m && ids && next_id, BLOK_ERR_ARG, "blok_model_prefill: null pointer");
+  BLOK_REQUIRE(m->cfg.prefill_chunk >= 1, BLOK_ERR_STATE, "blok_model_prefill: the model was created with prefill_chunk = 0");
+  BLOK_REQUIRE(n >= 1, BLOK_ERR_ARG, "blok_model_prefill: no tokens");
+  const blok_model_config &c = m->cfg;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  for (int at = 0; at < n; at += c.prefill_chunk) {
+    const int T = n - at < c.prefill_chunk ? n - at : c.prefill_chunk;
+    BLOK_CUDA(cudaMemcpyAsync(m->ids, ids + at, (size_t)T * 4, cudaMemcpyDeviceToDevice, stream));
+    int rc = layers_body(m, T, true, stream_);
+    if (rc) return rc;
+    if (at + T == n) {  // only the prompt's last token is sampled (:886 keeps the last step's id)
+      if ((rc = blok_lm_head_argmax(tp<uint16_t>(m->top, "lm_head"), m->n + (size_t)(T - 1) * c.hidden, c.vocab, c.hidden, 1, m->next,
+                                    m->head_ws, m->head_ws_bytes, stream_)))
+        return rc;
+    }
+    advance_kernel<<<1, 64, 0, stream>>>(m->pos, 1, T);
+    if ((rc = launch_status("advance_kernel"))) return rc;
+  }
+  if (next_id != m->next) BLOK_CUDA(cudaMemcpyAsync(next_id, m->next, 4, cudaMemcpyDeviceToDevice, stream));
+  return BLOK_OK;
+}
+
 extern "C" int blok_model_generate(blok_model_t *m, const uint32_t *prompt, int n_prompt, int max_new, uint32_t *out,
                                    int *n_out) {
   BLOK_REQUIRE(m && prompt && out && n_out, BLOK_ERR_ARG, "blok_model_generate: null pointer");
@@ -395,10 +455,16 @@ extern "C" int blok_model_generate(blok_model_t *m, const uint32_t *prompt, int 
   if (rc) return rc;
   *n_out = 0;
   uint32_t next = prompt[0];
-  // prompt replay, token by token; only the last step's sample is used (:886)
-  for (int i = 0; i < n_prompt; ++i) {
-    BLOK_CUDA(cudaMemcpyAsync(m->ids, prompt + i, 4, cudaMemcpyHostToDevice, nullptr));
-    if ((rc = blok_model_step(m, m->ids, 1, m->next, nullptr))) return rc;
+  if (m->cfg.prefill_chunk >= 1) {
+    // the prompt in chunks: every layer's weights are read once per chunk instead of once per token
+    BLOK_CUDA(cudaMemcpyAsync(m->prompt_ids, prompt, (size_t)n_prompt * 4, cudaMemcpyHostToDevice, nullptr));
+    if ((rc = blok_model_prefill(m, m->prompt_ids, n_prompt, m->next, nullptr))) return rc;
+  } else {
+    // prompt replay, token by token; only the last step's sample is used (:886)
+    for (int i = 0; i < n_prompt; ++i) {
+      BLOK_CUDA(cudaMemcpyAsync(m->ids, prompt + i, 4, cudaMemcpyHostToDevice, nullptr));
+      if ((rc = blok_model_step(m, m->ids, 1, m->next, nullptr))) return rc;
+    }
   }
   BLOK_CUDA(cudaMemcpy(&next, m->next, 4, cudaMemcpyDeviceToHost));
   for (int i = 0; i < max_new && next != m->cfg.eos_id; ++i) {  // :887-890

@@ -401,6 +401,89 @@ class MlaLayer:
                                       _stream()))
         return o
 
+    def prefill(self, n, cache, first_pos, out=None):
+        """A prefill chunk of one sequence: n bf16 [T, hidden] (consecutive tokens), cache bf16 [ctx_cap, 576] (rows
+        first_pos .. first_pos+T-1 are written), first_pos int32 [1] (device)."""
+        T = n.shape[0]
+        y = torch.empty((T, self.hidden), dtype=torch.bfloat16, device=n.device) if out is None else out
+        _check(load().blok_mla_prefill(self._handle, _ptr(n, torch.bfloat16, "n"), _ptr(cache, torch.bfloat16, "cache"),
+                                       C.c_long(cache.shape[0]), _ptr(first_pos, torch.int32, "first_pos"), C.c_int(T),
+                                       _ptr(y, torch.bfloat16, "out"), _stream()))
+        return y
+
+    def decode_paged(self, n, pool, block_table, ctx_len, slot_of=None, out=None):
+        """decode() over a paged pool: pool bf16 [pages, page_rows, 576], block_table int32 [slots, table_stride]
+        (device), slot_of int32 [B] (device) or None for slot b."""
+        B = n.shape[0]
+        y = torch.empty((B, self.hidden), dtype=torch.bfloat16, device=n.device) if out is None else out
+        _check(load().blok_mla_decode_paged(
+            self._handle, _ptr(n, torch.bfloat16, "n"), _ptr(pool, torch.bfloat16, "pool"),
+            _ptr(block_table, torch.int32, "block_table"), _ptr(slot_of, torch.int32, "slot_of") if slot_of is not None else None,
+            C.c_int(block_table.shape[1]), C.c_int(pool.shape[1]), _ptr(ctx_len, torch.int32, "ctx_len"), C.c_int(B),
+            _ptr(y, torch.bfloat16, "out"), _stream()))
+        return y
+
+    def attend_paged(self, q, pool, block_table, seq_len, slot_of=None, scale=None, out=None):
+        """attend() over a paged pool."""
+        B = q.shape[0]
+        o = torch.empty((B, self.heads, self.kv_rank), dtype=torch.bfloat16, device=q.device) if out is None else out
+        _check(load().blok_mla_attend_paged(
+            self._handle, _ptr(q, torch.bfloat16, "q"), _ptr(pool, torch.bfloat16, "pool"),
+            _ptr(block_table, torch.int32, "block_table"), _ptr(slot_of, torch.int32, "slot_of") if slot_of is not None else None,
+            C.c_int(block_table.shape[1]), C.c_int(pool.shape[1]), _ptr(seq_len, torch.int32, "seq_len"), C.c_int(B),
+            C.c_float(self.scale if scale is None else scale), _ptr(o, torch.bfloat16, "o_lat"), _stream()))
+        return o
+
+
+class KvPages:
+    """Host-side page bookkeeping of a paged latent cache (blok_kv_pages_*): no GPU needed except upload()."""
+
+    def __init__(self, n_pages, page_rows, slots, table_stride):
+        self.n_pages, self.page_rows, self.slots, self.table_stride = n_pages, page_rows, slots, table_stride
+        self._handle = C.c_void_p()
+        _check(load().blok_kv_pages_create(C.c_int(n_pages), C.c_int(page_rows), C.c_int(slots), C.c_int(table_stride),
+                                           C.byref(self._handle)))
+
+    def close(self):
+        if getattr(self, "_handle", None) is not None and self._handle.value:
+            load().blok_kv_pages_destroy(self._handle)
+            self._handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def reserve(self, slot, n_rows):
+        _check(load().blok_kv_pages_reserve(self._handle, C.c_int(slot), C.c_long(n_rows)))
+
+    def release(self, slot):
+        _check(load().blok_kv_pages_release(self._handle, C.c_int(slot)))
+
+    def fork(self, src_slot, dst_slot, n_rows):
+        _check(load().blok_kv_pages_fork(self._handle, C.c_int(src_slot), C.c_int(dst_slot), C.c_long(n_rows)))
+
+    @property
+    def free(self):
+        return int(load().blok_kv_pages_free_count(self._handle))
+
+    def rows(self, slot):
+        f = load().blok_kv_pages_rows
+        f.restype = C.c_long
+        return int(f(self._handle, C.c_int(slot)))
+
+    def table(self):
+        """A copy of the host table as a numpy int32 array [slots, table_stride]."""
+        import numpy as np
+        f = load().blok_kv_pages_table
+        f.restype = C.POINTER(C.c_int)
+        ptr = f(self._handle)
+        return np.ctypeslib.as_array(ptr, shape=(self.slots, self.table_stride)).copy()
+
+    def upload(self, device_table):
+        _check(load().blok_kv_pages_upload(self._handle, _ptr(device_table, torch.int32, "device_table"), _stream()))
+
 
 class ModelConfig(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("layers", "first_dense", "hidden", "vocab", "dense_inter", "inter", "experts", "topk",
@@ -408,7 +491,7 @@ class ModelConfig(C.Structure):
                [(n, C.c_int) for n in ("heads", "qk_nope", "qk_rope", "v_head", "q_rank", "kv_rank")] + \
                [(n, C.c_float) for n in ("rms_eps", "final_rms_eps", "rope_theta", "yarn_factor", "yarn_beta_fast",
                                          "yarn_beta_slow", "yarn_original_ctx", "yarn_mscale_all_dim")] + \
-               [("max_batch", C.c_int), ("max_ctx", C.c_int), ("eos_id", C.c_uint32)]
+               [("max_batch", C.c_int), ("max_ctx", C.c_int), ("eos_id", C.c_uint32), ("prefill_chunk", C.c_int)]
 
 
 def index_validate(path, cfg):
@@ -504,6 +587,13 @@ class Model:
         """ids int32 [B] on the device -> next ids int32 [B] on the device."""
         nxt = torch.empty_like(ids)
         _check(load().blok_model_step(self._handle, _ptr(ids, torch.int32, "ids"), C.c_int(ids.numel()), _ptr(nxt), _stream()))
+        return nxt
+
+    def prefill(self, ids):
+        """The next tokens of sequence 0 in chunks (blok_model_prefill): ids int32 [n] on the device -> the greedy id
+        after the last one, int32 [1] on the device.  The model needs prefill_chunk >= 1."""
+        nxt = torch.empty(1, dtype=torch.int32, device=ids.device)
+        _check(load().blok_model_prefill(self._handle, _ptr(ids, torch.int32, "ids"), C.c_int(ids.numel()), _ptr(nxt), _stream()))
         return nxt
 
     def generate(self, prompt, max_new):

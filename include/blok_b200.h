@@ -279,8 +279,9 @@ typedef struct blok_mla_weights {
 
 typedef struct blok_mla_layer blok_mla_layer_t;
 
-/* Allocates the layer's workspace for up to max_batch (<= 8) sequences and up to
- * max_ctx cached tokens each, and a transposed copy of the W_UK half of kv_b. */
+/* Allocates the layer's workspace for up to max_batch (<= 64) sequences, or tokens of a
+ * prefill chunk, and up to max_ctx cached tokens each, and a transposed copy of the W_UK
+ * half of kv_b. */
 int blok_mla_layer_create(const blok_mla_weights *weights, int max_batch, int max_ctx, blok_mla_layer_t **out);
 int blok_mla_layer_destroy(blok_mla_layer_t *layer);
 /* Rebuilds what create derived from the weights (the transposed W_UK copy) after the caller has overwritten kv_b in
@@ -308,9 +309,65 @@ int blok_mla_decode(blok_mla_layer_t *layer, const blok_bf16_t *n, blok_bf16_t *
 int blok_mla_attend(blok_mla_layer_t *layer, const blok_bf16_t *q, const blok_bf16_t *cache, long ctx_stride,
                     const int *seq_len, int B, float softmax_scale, blok_bf16_t *o_lat, blok_stream_t stream);
 
+/* A prefill chunk: T consecutive tokens of ONE sequence through the attention block in one call, instead of the
+ * reference's token-by-token prompt replay (src/kimi_exec.cu:885-886).  Token i sits at position first_pos[0] + i;
+ * all T latent rows are appended first, then token i attends to positions 0..first_pos[0]+i (causal), which is what
+ * T calls of blok_mla_decode would compute.
+ *   n          bf16 [T, hidden]        cache   bf16 [ctx_cap, kv_rank+qk_rope], this sequence's rows
+ *   first_pos  int32 [1] on the device: tokens already cached; first_pos[0] + T <= ctx_cap is the caller's duty
+ *   out        bf16 [T, hidden]        T <= max_batch of the handle (<= 64) */
+int blok_mla_prefill(blok_mla_layer_t *layer, const blok_bf16_t *n, blok_bf16_t *cache, long ctx_cap, const int *first_pos,
+                     int T, blok_bf16_t *out, blok_stream_t stream);
+
+/* blok_mla_decode over a PAGED latent cache (the reference's KvCache, src/kimi_exec.cu:192-238, holds one contiguous
+ * region per layer and refuses sequences past its capacity at :205; pages let sequences of different lengths share
+ * one pool).  pool is bf16 [pages, page_rows, kv_rank+qk_rope]; page_rows is a multiple of 32.  block_table is int32
+ * [slots, table_stride] on the device: entry [s, j] is the page holding rows [j*page_rows, (j+1)*page_rows) of the
+ * sequence in slot s.  slot_of int32 [B] (device) names the slot of batch entry b; NULL means slot b.  Several
+ * entries may name the same slot with consecutive ctx_len values: that is a prefill chunk of that sequence.
+ * The page of row ctx_len[b] must already be in the table (blok_kv_pages_reserve does that on the host). */
+int blok_mla_decode_paged(blok_mla_layer_t *layer, const blok_bf16_t *n, blok_bf16_t *pool, const int *block_table,
+                          const int *slot_of, int table_stride, int page_rows, const int *ctx_len, int B,
+                          blok_bf16_t *out, blok_stream_t stream);
+
+/* blok_mla_attend over the same paged pool. */
+int blok_mla_attend_paged(blok_mla_layer_t *layer, const blok_bf16_t *q, const blok_bf16_t *pool, const int *block_table,
+                          const int *slot_of, int table_stride, int page_rows, const int *seq_len, int B,
+                          float softmax_scale, blok_bf16_t *o_lat, blok_stream_t stream);
+
 /* The softmax scale the layer uses: (qk_nope+qk_rope)^-1/2 * mscale^2, mscale =
  * 0.1 * mscale_all_dim * ln(yarn_factor) + 1 (src/kimi_exec.cu:428-429). */
 float blok_mla_softmax_scale(const blok_mla_weights *weights);
+
+/* ------------------------------------------------------------------------- */
+/* Paged latent cache: host-side page bookkeeping                              */
+/* ------------------------------------------------------------------------- */
+
+/* Which pages of a pool every sequence slot holds.  The reference's KvCache (src/kimi_exec.cu:192-238) gives each
+ * layer one contiguous region and dies when a sequence outgrows it (:205); here sequences of different lengths draw
+ * pages from one pool and return them when they finish.  A page number addresses the same page of every layer's
+ * pool, so one table serves all layers.  The handle is host memory only: create, reserve, release and fork make no
+ * CUDA call and work without a GPU. */
+typedef struct blok_kv_pages blok_kv_pages_t;
+
+/* n_pages pages of page_rows rows (a multiple of 32); `slots` sequences of at most table_stride pages each. */
+int blok_kv_pages_create(int n_pages, int page_rows, int slots, int table_stride, blok_kv_pages_t **out);
+int blok_kv_pages_destroy(blok_kv_pages_t *pages);
+/* Grows the slot's reservation to cover n_rows rows (never shrinks).  BLOK_ERR_WORKSPACE when the pool has too few
+ * free pages, BLOK_ERR_SHAPE when n_rows exceeds table_stride * page_rows; the reservation is unchanged then. */
+int blok_kv_pages_reserve(blok_kv_pages_t *pages, int slot, long n_rows);
+/* Returns the slot's pages to the pool (a page shared through fork goes back when its last holder releases it). */
+int blok_kv_pages_release(blok_kv_pages_t *pages, int slot);
+/* Lets the empty slot dst share the first n_rows rows (whole pages) of slot src: a common prompt prefix is cached
+ * once.  Rows past n_rows of dst go to pages of its own (reserve). */
+int blok_kv_pages_fork(blok_kv_pages_t *pages, int src_slot, int dst_slot, long n_rows);
+int blok_kv_pages_free_count(const blok_kv_pages_t *pages);
+/* Rows the slot's reservation covers. */
+long blok_kv_pages_rows(const blok_kv_pages_t *pages, int slot);
+/* HOST pointer to the table, int32 [slots, table_stride]; entries past a slot's reservation are 0. */
+const int *blok_kv_pages_table(const blok_kv_pages_t *pages);
+/* Copies the table to device_table (int32 [slots, table_stride]) on `stream` if it changed since the last upload. */
+int blok_kv_pages_upload(blok_kv_pages_t *pages, int *device_table, blok_stream_t stream);
 
 /* ------------------------------------------------------------------------- */
 /* A11  embedding fetch and greedy sampler                                    */
@@ -349,9 +406,11 @@ typedef struct blok_model_config {
   float rms_eps;       /* 1e-5, every per-layer norm */
   float final_rms_eps; /* 1e-5 in the reference (:880 uses RMS_EPS); 1e-6 in the benchmark configuration */
   float rope_theta, yarn_factor, yarn_beta_fast, yarn_beta_slow, yarn_original_ctx, yarn_mscale_all_dim;
-  int max_batch;     /* <= 8 */
+  int max_batch;     /* <= 64 sequences per step */
   int max_ctx;       /* tokens of latent cache per sequence and layer */
   uint32_t eos_id;   /* 163586 (:186) */
+  int prefill_chunk; /* 0: the prompt is replayed token by token as in the reference (:886); 1..64: prompts go
+                        through blok_model_prefill in chunks of this many tokens */
 } blok_model_config;
 
 typedef struct blok_model blok_model_t;
@@ -403,9 +462,18 @@ int blok_model_reset(blok_model_t *model);
  * src/kimi_exec.cu:801-884.  Positions advance by one. */
 int blok_model_step(blok_model_t *model, const uint32_t *ids, int B, uint32_t *next_ids, blok_stream_t stream);
 
+/* Prompt processing for sequence 0 in chunks instead of the reference's token-by-token replay (src/kimi_exec.cu:
+ * 885-886): ids uint32 [n] on the device are the next n tokens of the sequence.  Each chunk of up to prefill_chunk
+ * tokens runs every layer once: the attention block as a causal chunk (blok_mla_prefill), the routed experts through
+ * the grouped GEMM (blok_moe_batched; token by token when the layer's sizes do not fit that kernel).  Only the last
+ * token is sampled: next_id uint32 [1] on the device.  The position of sequence 0 advances by n.  The result is what
+ * n calls of blok_model_step would give, up to the summation order of the batched kernels.  Needs prefill_chunk >= 1. */
+int blok_model_prefill(blok_model_t *model, const uint32_t *ids, int n, uint32_t *next_id, blok_stream_t stream);
+
 /* Greedy generation for one sequence with HOST token arrays, as generate()
- * (src/kimi_exec.cu:885-890): the prompt is replayed token by token, then up to
- * max_new tokens are produced, stopping before eos_id.  Returns the count in *n_out. */
+ * (src/kimi_exec.cu:885-890): the prompt is replayed token by token (through
+ * blok_model_prefill when prefill_chunk >= 1), then up to max_new tokens are
+ * produced, stopping before eos_id.  Returns the count in *n_out. */
 int blok_model_generate(blok_model_t *model, const uint32_t *prompt, int n_prompt, int max_new, uint32_t *out,
                         int *n_out);
 
