@@ -190,9 +190,9 @@ def other_workload(a, rank, world, device, steps, warmup):
         # config 4 on what ONE GPU holds: layer 0 dense + (model_layers - 1) MoE layers of the full shapes, full
         # vocabulary, batch 1, greedy decode after a 32-token prompt replay.  A step is one new token through every
         # layer (embedding, MLA, dense / MoE, final norm, lm_head, argmax); a step reads > 6 GB, far beyond L2.
-        L = a.model_layers
-        model = lib.Model(seed=4 + rank, layers=L, max_batch=1, max_ctx=max(256, 64 + steps + warmup + 8))
-        ids = torch.randint(0, 163840, (1,), device=device, dtype=torch.int32)
+        L, B = a.model_layers, a.batch
+        model = lib.Model(seed=4 + rank, layers=L, max_batch=B, max_ctx=max(256, 64 + steps + warmup + 8))
+        ids = torch.randint(0, 163840, (B,), device=device, dtype=torch.int32)
         for _ in range(32):
             ids = model.step(ids)
         state = {"ids": ids}
@@ -201,12 +201,35 @@ def other_workload(a, rank, world, device, steps, warmup):
             state["ids"] = model.step(state["ids"])
         moe_bytes = 291767808 + 202244096          # routed-MoE decode layer + MLA projections, per MoE layer
         dense_bytes = 3 * 18432 * 7168 * 2 + 202244096
+        # batch 1: 8 experts per layer; a batch touches more (counted as B x 8 distinct, an upper bound, capped at 384)
+        moe_bytes += (min(384, 8 * B) - 8) * 24772608
         alg = (L - 1) * moe_bytes + dense_bytes + 163840 * 7168 * 2   # + lm_head; the cache (<= 300 tokens) is negligible
-        unit_tokens = world
-        workload = ("config 4 on one GPU: %d of the 61 layers (1 dense + %d MoE, full shapes), vocab 163840, batch 1, "
-                    "greedy decode%s" % (L, L - 1, "" if world == 1 else ", replicas x%d" % world))
+        unit_tokens = world * B
+        workload = ("config 4 on one GPU: %d of the 61 layers (1 dense + %d MoE, full shapes), vocab 163840, batch %d, "
+                    "greedy decode%s" % (L, L - 1, B, "" if world == 1 else ", replicas x%d" % world))
         scaling = "weak"
-        metric = "decode tok/s, %d-layer model (batch 1)" % L
+        metric = "decode tok/s, %d-layer model (batch %d)" % (L, B)
+    elif a.workload == "prefill512":
+        # config 4's prompt on what ONE GPU holds: 512 random ids through the first model_layers layers in chunks of 64
+        # tokens (blok_model_prefill); a step is the whole prompt and samples its last token.  The reference replays the
+        # prompt token by token (src/kimi_exec.cu:885-886); `--workload model` times that form per token.
+        L, P, chunk = a.model_layers, 512, 64
+        model = lib.Model(seed=4 + rank, layers=L, max_batch=1, max_ctx=P + 8, prefill_chunk=chunk)
+        prompts = [torch.randint(0, 163840, (P,), device=device, dtype=torch.int32) for _ in range(4)]
+
+        def run(i):
+            model.reset()
+            model.prefill(prompts[i % 4])
+        # per chunk and MoE layer: attention weights once per 8 tokens, the experts the chunk routes to once (at most
+        # 64 x 8 distinct, capped at 384), router and shared expert once; the dense layer once per 5 tokens
+        per_chunk = (L - 1) * (202244096 * (chunk // 8) + 384 * 24772608 + 5505024 + 88080384) + \
+            (3 * 18432 * 7168 * 2) * ((chunk + 4) // 5) + 202244096 * (chunk // 8)
+        alg = per_chunk * (P // chunk) + 163840 * 7168 * 2
+        unit_tokens = world * P
+        workload = ("config 4's 512-token prompt on one GPU: %d of the 61 layers (1 dense + %d MoE, full shapes), chunks of %d "
+                    "tokens, last token sampled%s" % (L, L - 1, chunk, "" if world == 1 else ", replicas x%d" % world))
+        scaling = "weak"
+        metric = "prefill tok/s, %d-layer model (512-token prompt)" % L
     elif a.workload == "model61":
         # config 4: the 61-layer model sharded expert-parallel over the ranks (384 / world experts per GPU, attention,
         # router, shared expert, embedding and lm_head replicated), batch 1, greedy decode after a 16-token prompt replay.
@@ -329,11 +352,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=3, help="distinct synthetic layers rotated between steps")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=1, help="sequences per step of the `model` workload (up to 64)")
     ap.add_argument("--model-layers", type=int, default=12, help="layers of the `model` workload (one GPU holds about 15)")
     ap.add_argument("--experts", type=int, default=384,
                     help="routed experts per layer; below 384 the run is a reduced case for profiler captures, "
                          "not the benchmark configuration, and the line says so")
-    ap.add_argument("--workload", default="decode", choices=["decode", "batched64", "batched2048", "mla4096", "mla32768", "model", "model61"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "batched64", "batched2048", "mla4096", "mla32768", "model", "model61", "prefill512"],
                     help="decode = config 1 (the default, the headline metric); batched* = config 2 (expert parallel "
                          "when --gpus > 1); mla* = config 3 (attention block, batch 8)")
     a = ap.parse_args()

@@ -49,6 +49,24 @@ __global__ void advance_kernel(int *pos, int n, int by) {
 
 constexpr int kMaxBatch = 64;  // sequences per step, and tokens per prefill chunk
 
+// Paged model: batch entry b is the sequence in slot slot_of[b].
+__global__ void gather_positions_kernel(const int *__restrict__ pos, const int *__restrict__ slot_of, int n, int *__restrict__ ctx) {
+  const int b = threadIdx.x;
+  if (b < n) ctx[b] = pos[slot_of[b]];
+}
+__global__ void advance_slots_kernel(int *__restrict__ pos, const int *__restrict__ slot_of, int n) {
+  const int b = threadIdx.x;
+  if (b < n) pos[slot_of[b]] += 1;  // the slots of a step are distinct
+}
+// A prompt chunk of the sequence in `slot`: entry i is that slot at position pos[slot] + i.
+__global__ void chunk_slots_kernel(const int *__restrict__ pos, int slot, int n, int *__restrict__ ctx, int *__restrict__ slot_of) {
+  const int i = threadIdx.x;
+  if (i < n) {
+    ctx[i] = pos[slot] + i;
+    slot_of[i] = slot;
+  }
+}
+
 struct Tensor {
   void *ptr = nullptr;
   size_t bytes = 0;
@@ -58,7 +76,7 @@ struct LayerWeights {
   std::map<std::string, Tensor> t;
   blok_mla_layer_t *mla = nullptr;
   blok_moe_layer_t *moe = nullptr;
-  uint16_t *cache = nullptr;  // [max_batch, max_ctx, kv_rank + qk_rope]
+  uint16_t *cache = nullptr;  // [max_batch, max_ctx, kv_rank + qk_rope], or the page pool [kv_pages, kv_page_rows, ...]
 };
 
 }  // namespace blok
@@ -73,6 +91,12 @@ struct blok_model {
   uint32_t *prompt_ids = nullptr;                       // [max_ctx] a prompt given on the host (prefill_chunk >= 1)
   int rows = 0;                                         // max(max_batch, prefill_chunk)
   bool moe_batched_ok = false;                          // the layer sizes fit the grouped-GEMM kernels
+  std::vector<long> host_pos;                           // tokens cached per sequence (host mirror of pos)
+  // paged cache (cfg.kv_page_rows > 0): one table for all layers' pools
+  blok_kv_pages_t *pages = nullptr;
+  int table_stride = 0;
+  int *table_dev = nullptr;                             // [max_batch, table_stride]
+  int *slot_of = nullptr, *ctx_b = nullptr;             // [rows] slot and position of every batch entry of the call in flight
   int *pos = nullptr;                                   // [max_batch]
   uint32_t *ids = nullptr, *next = nullptr;             // [max_batch]
   void *mlp_ws = nullptr;
@@ -176,7 +200,8 @@ int build(blok_model *m) {
       }
     }
     void *cache = nullptr;
-    if ((rc = dev_alloc(m, (size_t)c.max_batch * c.max_ctx * lat_w * 2, &cache))) return rc;
+    const size_t cache_rows = c.kv_page_rows > 0 ? (size_t)c.kv_pages * c.kv_page_rows : (size_t)c.max_batch * c.max_ctx;
+    if ((rc = dev_alloc(m, cache_rows * lat_w * 2, &cache))) return rc;
     m->layers[l].cache = static_cast<uint16_t *>(cache);
   }
 #undef MK
@@ -222,6 +247,15 @@ int build(blok_model *m) {
   m->head_ws_bytes = blok_lm_head_workspace_bytes(c.vocab, c.max_batch);
   if ((rc = dev_alloc(m, m->head_ws_bytes, &m->head_ws))) return rc;
   BLOK_CUDA(cudaMemset(m->pos, 0, c.max_batch * 4));
+  m->host_pos.assign(c.max_batch, 0);
+  if (c.kv_page_rows > 0) {
+    m->table_stride = (c.max_ctx + c.kv_page_rows - 1) / c.kv_page_rows;
+    if ((rc = blok_kv_pages_create(c.kv_pages, c.kv_page_rows, c.max_batch, m->table_stride, &m->pages))) return rc;
+    if ((rc = dev_alloc(m, (size_t)c.max_batch * m->table_stride * 4, &p))) return rc; m->table_dev = static_cast<int *>(p);
+    BLOK_CUDA(cudaMemset(m->table_dev, 0, (size_t)c.max_batch * m->table_stride * 4));
+    if ((rc = dev_alloc(m, m->rows * 4, &p))) return rc; m->slot_of = static_cast<int *>(p);
+    if ((rc = dev_alloc(m, m->rows * 4, &p))) return rc; m->ctx_b = static_cast<int *>(p);
+  }
   return BLOK_OK;
 }
 
@@ -244,6 +278,7 @@ extern "C" int blok_model_destroy(blok_model_t *m) {
     for (auto &g : m->step_graph)
       if (g) cudaGraphExecDestroy(g);
   if (!m) return BLOK_OK;
+  blok_kv_pages_destroy(m->pages);
   for (auto &L : m->layers) {
     if (L.mla) blok_mla_layer_destroy(L.mla);
     if (L.moe) blok_moe_layer_destroy(L.moe);
@@ -263,6 +298,9 @@ extern "C" int blok_model_create_synthetic(const blok_model_config *cfg, uint64_
                    cfg->hidden % 256 == 0 && cfg->max_batch >= 1 && cfg->max_batch <= kMaxBatch && cfg->max_ctx >= 1 &&
                    cfg->prefill_chunk >= 0 && cfg->prefill_chunk <= kMaxBatch,
                BLOK_ERR_SHAPE, "blok_model_create_synthetic: unsupported configuration");
+  BLOK_REQUIRE(cfg->kv_page_rows == 0 || (cfg->kv_page_rows >= 32 && cfg->kv_page_rows % 32 == 0 && cfg->kv_pages >= 1),
+               BLOK_ERR_SHAPE, "blok_model_create_synthetic: kv_page_rows %d must be 0 or a multiple of 32 with kv_pages >= 1",
+               cfg->kv_page_rows);
   BLOK_REQUIRE(cfg->first_dense == 0 || (cfg->dense_inter > 0 && cfg->dense_inter % 32 == 0), BLOK_ERR_SHAPE,
                "blok_model_create_synthetic: dense_inter %d must be a positive multiple of 32", cfg->dense_inter);
   blok_model *m = new (std::nothrow) blok_model();
@@ -309,6 +347,10 @@ extern "C" int blok_model_refresh_derived(blok_model_t *m) {
 extern "C" int blok_model_reset(blok_model_t *m) {
   BLOK_REQUIRE(m, BLOK_ERR_ARG, "blok_model_reset: null pointer");
   BLOK_CUDA(cudaMemset(m->pos, 0, m->cfg.max_batch * 4));
+  for (int s = 0; s < m->cfg.max_batch; ++s) {
+    m->host_pos[s] = 0;
+    if (m->pages) blok_kv_pages_release(m->pages, s);
+  }
   return BLOK_OK;
 }
 
@@ -348,8 +390,12 @@ static int layers_body(blok_model_t *m, int T, bool chunk, blok_stream_t stream_
   for (int l = 0; l < c.layers; ++l) {
     auto &L = m->layers[l];
     // attention block, :812-827
-    rc = chunk ? blok_mla_prefill(L.mla, m->n, L.cache, c.max_ctx, m->pos, T, m->tmp, stream_)
-               : blok_mla_decode(L.mla, m->n, L.cache, c.max_ctx, m->pos, T, m->tmp, stream_);
+    if (m->pages)  // entry b is slot slot_of[b] at position ctx_b[b], for steps and chunks alike
+      rc = blok_mla_decode_paged(L.mla, m->n, L.cache, m->table_dev, m->slot_of, m->table_stride, c.kv_page_rows, m->ctx_b, T, m->tmp,
+                                 stream_);
+    else
+      rc = chunk ? blok_mla_prefill(L.mla, m->n, L.cache, c.max_ctx, m->pos, T, m->tmp, stream_)
+                 : blok_mla_decode(L.mla, m->n, L.cache, c.max_ctx, m->pos, T, m->tmp, stream_);
     if (rc) return rc;
     if ((rc = blok_add_rmsnorm(m->x, m->tmp, tp<uint16_t>(L.t, "post_attention_layernorm"), m->n, T, c.hidden, c.rms_eps, stream_)))
       return rc;
@@ -372,13 +418,56 @@ static int step_body(blok_model_t *m, int B, blok_stream_t stream_) {
     if ((rc = blok_lm_head_argmax(tp<uint16_t>(m->top, "lm_head"), m->n + (size_t)b * c.hidden, c.vocab, c.hidden, B - b < 8 ? B - b : 8,
                                   m->next + b, m->head_ws, m->head_ws_bytes, stream_)))
       return rc;
-  advance_kernel<<<1, 64, 0, stream>>>(m->pos, B, 1);
+  if (m->pages) advance_slots_kernel<<<1, 64, 0, stream>>>(m->pos, m->slot_of, B);
+  else advance_kernel<<<1, 64, 0, stream>>>(m->pos, B, 1);
   return launch_status("advance_kernel");
+}
+
+extern "C" int blok_model_step_slots(blok_model_t *m, const int *slots, int B, const uint32_t *ids, uint32_t *next_ids,
+                                     blok_stream_t stream_) {
+  BLOK_REQUIRE(m && slots && ids && next_ids, BLOK_ERR_ARG, "blok_model_step_slots: null pointer");
+  const blok_model_config &c = m->cfg;
+  BLOK_REQUIRE(B >= 1 && B <= c.max_batch, BLOK_ERR_SHAPE, "blok_model_step_slots: B=%d outside [1, %d]", B, c.max_batch);
+  bool identity = true;
+  for (int b = 0; b < B; ++b) {
+    BLOK_REQUIRE(slots[b] >= 0 && slots[b] < c.max_batch, BLOK_ERR_ARG, "blok_model_step_slots: slot %d outside [0, %d)", slots[b],
+                 c.max_batch);
+    for (int a = 0; a < b; ++a) BLOK_REQUIRE(slots[a] != slots[b], BLOK_ERR_ARG, "blok_model_step_slots: slot %d named twice", slots[b]);
+    BLOK_REQUIRE(m->host_pos[slots[b]] + 1 <= c.max_ctx, BLOK_ERR_SHAPE,
+                 "blok_model_step_slots: the sequence in slot %d already holds max_ctx = %d tokens", slots[b], c.max_ctx);  // :205
+    identity = identity && slots[b] == b;
+  }
+  if (!m->pages) {
+    BLOK_REQUIRE(identity, BLOK_ERR_STATE, "blok_model_step_slots: a model with a dense cache steps slots 0..B-1 only");
+    return blok_model_step(m, ids, B, next_ids, stream_);
+  }
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int rc;
+  for (int b = 0; b < B; ++b)
+    if ((rc = blok_kv_pages_reserve(m->pages, slots[b], m->host_pos[slots[b]] + 1))) return rc;
+  if ((rc = blok_kv_pages_upload(m->pages, m->table_dev, stream_))) return rc;
+  BLOK_CUDA(cudaMemcpyAsync(m->slot_of, slots, (size_t)B * 4, cudaMemcpyHostToDevice, stream));
+  if (ids != m->ids) BLOK_CUDA(cudaMemcpyAsync(m->ids, ids, (size_t)B * 4, cudaMemcpyDeviceToDevice, stream));
+  gather_positions_kernel<<<1, 64, 0, stream>>>(m->pos, m->slot_of, B, m->ctx_b);
+  if ((rc = launch_status("gather_positions_kernel"))) return rc;
+  if ((rc = step_body(m, B, stream_))) return rc;
+  for (int b = 0; b < B; ++b) ++m->host_pos[slots[b]];
+  if (next_ids != m->next) BLOK_CUDA(cudaMemcpyAsync(next_ids, m->next, (size_t)B * 4, cudaMemcpyDeviceToDevice, stream));
+  return BLOK_OK;
 }
 
 extern "C" int blok_model_step(blok_model_t *m, const uint32_t *ids, int B, uint32_t *next_ids, blok_stream_t stream_) {
   BLOK_REQUIRE(m && ids && next_ids, BLOK_ERR_ARG, "blok_model_step: null pointer");
   BLOK_REQUIRE(B >= 1 && B <= m->cfg.max_batch, BLOK_ERR_SHAPE, "blok_model_step: B=%d outside [1, %d]", B, m->cfg.max_batch);
+  if (m->pages) {
+    int slots[kMaxBatch];
+    for (int b = 0; b < B; ++b) slots[b] = b;
+    return blok_model_step_slots(m, slots, B, ids, next_ids, stream_);
+  }
+  for (int b = 0; b < B; ++b)
+    BLOK_REQUIRE(m->host_pos[b] + 1 <= m->cfg.max_ctx, BLOK_ERR_SHAPE, "blok_model_step: sequence %d already holds max_ctx = %d tokens", b,
+                 m->cfg.max_ctx);  // the reference's capacity check, :205
+  for (int b = 0; b < B; ++b) ++m->host_pos[b];
   cudaStream_t stream = (cudaStream_t)stream_;
   if (ids != m->ids) BLOK_CUDA(cudaMemcpyAsync(m->ids, ids, (size_t)B * 4, cudaMemcpyDeviceToDevice, stream));
   int rc = BLOK_OK;
@@ -420,28 +509,58 @@ extern "C" int blok_model_step(blok_model_t *m, const uint32_t *ids, int B, uint
   return BLOK_OK;
 }
 
-extern "C" int blok_model_prefill(blok_model_t *m, const uint32_t *ids, int n, uint32_t *next_id, blok_stream_t stream_) {
+extern "C" int blok_model_prefill_slot(blok_model_t *m, int slot, const uint32_t *ids, int n, uint32_t *next_id, blok_stream_t stream_) {
   BLOK_REQUIRE(m && ids && next_id, BLOK_ERR_ARG, "blok_model_prefill: null pointer");
   BLOK_REQUIRE(m->cfg.prefill_chunk >= 1, BLOK_ERR_STATE, "blok_model_prefill: the model was created with prefill_chunk = 0");
   BLOK_REQUIRE(n >= 1, BLOK_ERR_ARG, "blok_model_prefill: no tokens");
   const blok_model_config &c = m->cfg;
+  BLOK_REQUIRE(slot >= 0 && slot < c.max_batch && (m->pages || slot == 0), BLOK_ERR_ARG,
+               "blok_model_prefill: slot %d (a model with a dense cache prefills sequence 0 only)", slot);
+  BLOK_REQUIRE(m->host_pos[slot] + n <= c.max_ctx, BLOK_ERR_SHAPE, "blok_model_prefill: %ld cached + %d new tokens exceed max_ctx = %d",
+               m->host_pos[slot], n, c.max_ctx);  // :205
   cudaStream_t stream = (cudaStream_t)stream_;
+  int rc;
+  if (m->pages && (rc = blok_kv_pages_reserve(m->pages, slot, m->host_pos[slot] + n))) return rc;  // all or nothing, before any launch
+  if (m->pages && (rc = blok_kv_pages_upload(m->pages, m->table_dev, stream_))) return rc;
   for (int at = 0; at < n; at += c.prefill_chunk) {
     const int T = n - at < c.prefill_chunk ? n - at : c.prefill_chunk;
     BLOK_CUDA(cudaMemcpyAsync(m->ids, ids + at, (size_t)T * 4, cudaMemcpyDeviceToDevice, stream));
-    int rc = layers_body(m, T, true, stream_);
-    if (rc) return rc;
+    if (m->pages) {
+      chunk_slots_kernel<<<1, 64, 0, stream>>>(m->pos, slot, T, m->ctx_b, m->slot_of);
+      if ((rc = launch_status("chunk_slots_kernel"))) return rc;
+    }
+    if ((rc = layers_body(m, T, true, stream_))) return rc;
     if (at + T == n) {  // only the prompt's last token is sampled (:886 keeps the last step's id)
       if ((rc = blok_lm_head_argmax(tp<uint16_t>(m->top, "lm_head"), m->n + (size_t)(T - 1) * c.hidden, c.vocab, c.hidden, 1, m->next,
                                     m->head_ws, m->head_ws_bytes, stream_)))
         return rc;
     }
-    advance_kernel<<<1, 64, 0, stream>>>(m->pos, 1, T);
+    advance_kernel<<<1, 64, 0, stream>>>(m->pos + slot, 1, T);
     if ((rc = launch_status("advance_kernel"))) return rc;
+    m->host_pos[slot] += T;
   }
   if (next_id != m->next) BLOK_CUDA(cudaMemcpyAsync(next_id, m->next, 4, cudaMemcpyDeviceToDevice, stream));
   return BLOK_OK;
 }
+
+extern "C" int blok_model_prefill(blok_model_t *m, const uint32_t *ids, int n, uint32_t *next_id, blok_stream_t stream) {
+  return blok_model_prefill_slot(m, 0, ids, n, next_id, stream);
+}
+
+extern "C" int blok_model_slot_release(blok_model_t *m, int slot, blok_stream_t stream) {
+  BLOK_REQUIRE(m, BLOK_ERR_ARG, "blok_model_slot_release: null pointer");
+  BLOK_REQUIRE(slot >= 0 && slot < m->cfg.max_batch, BLOK_ERR_ARG, "blok_model_slot_release: slot %d outside [0, %d)", slot,
+               m->cfg.max_batch);
+  BLOK_CUDA(cudaMemsetAsync(m->pos + slot, 0, 4, (cudaStream_t)stream));
+  m->host_pos[slot] = 0;
+  return m->pages ? blok_kv_pages_release(m->pages, slot) : BLOK_OK;
+}
+
+extern "C" long blok_model_slot_length(blok_model_t *m, int slot) {
+  return (m && slot >= 0 && slot < m->cfg.max_batch) ? m->host_pos[slot] : -1;
+}
+
+extern "C" int blok_model_free_pages(blok_model_t *m) { return (m && m->pages) ? blok_kv_pages_free_count(m->pages) : -1; }
 
 extern "C" int blok_model_generate(blok_model_t *m, const uint32_t *prompt, int n_prompt, int max_new, uint32_t *out,
                                    int *n_out) {

@@ -491,7 +491,8 @@ class ModelConfig(C.Structure):
                [(n, C.c_int) for n in ("heads", "qk_nope", "qk_rope", "v_head", "q_rank", "kv_rank")] + \
                [(n, C.c_float) for n in ("rms_eps", "final_rms_eps", "rope_theta", "yarn_factor", "yarn_beta_fast",
                                          "yarn_beta_slow", "yarn_original_ctx", "yarn_mscale_all_dim")] + \
-               [("max_batch", C.c_int), ("max_ctx", C.c_int), ("eos_id", C.c_uint32), ("prefill_chunk", C.c_int)]
+               [("max_batch", C.c_int), ("max_ctx", C.c_int), ("eos_id", C.c_uint32), ("prefill_chunk", C.c_int),
+                ("kv_page_rows", C.c_int), ("kv_pages", C.c_int)]
 
 
 def index_validate(path, cfg):
@@ -595,6 +596,34 @@ class Model:
         nxt = torch.empty(1, dtype=torch.int32, device=ids.device)
         _check(load().blok_model_prefill(self._handle, _ptr(ids, torch.int32, "ids"), C.c_int(ids.numel()), _ptr(nxt), _stream()))
         return nxt
+
+    def step_slots(self, slots, ids):
+        """A step of the sequences in the given slots (host list of distinct ints); ids int32 [B] on the device in the
+        same order.  On a paged model any subset of the resident sequences may step."""
+        B = len(slots)
+        arr = (C.c_int * B)(*slots)
+        nxt = torch.empty_like(ids)
+        _check(load().blok_model_step_slots(self._handle, arr, C.c_int(B), _ptr(ids, torch.int32, "ids"), _ptr(nxt), _stream()))
+        return nxt
+
+    def prefill_slot(self, slot, ids):
+        """prefill() for the sequence in `slot` of a paged model."""
+        nxt = torch.empty(1, dtype=torch.int32, device=ids.device)
+        _check(load().blok_model_prefill_slot(self._handle, C.c_int(slot), _ptr(ids, torch.int32, "ids"), C.c_int(ids.numel()),
+                                              _ptr(nxt), _stream()))
+        return nxt
+
+    def release_slot(self, slot):
+        _check(load().blok_model_slot_release(self._handle, C.c_int(slot), _stream()))
+
+    def slot_length(self, slot):
+        f = load().blok_model_slot_length
+        f.restype = C.c_long
+        return int(f(self._handle, C.c_int(slot)))
+
+    @property
+    def free_pages(self):
+        return int(load().blok_model_free_pages(self._handle))
 
     def generate(self, prompt, max_new):
         """Greedy generation with host token lists, like the reference executor's command line."""

@@ -411,6 +411,10 @@ typedef struct blok_model_config {
   uint32_t eos_id;   /* 163586 (:186) */
   int prefill_chunk; /* 0: the prompt is replayed token by token as in the reference (:886); 1..64: prompts go
                         through blok_model_prefill in chunks of this many tokens */
+  int kv_page_rows;  /* 0: every sequence owns max_ctx rows of every layer's cache (the reference's KvCache, :192-238);
+                        a multiple of 32: the layers' caches are pools of pages of this many rows, shared by the
+                        max_batch resident sequences (slots) through one page table */
+  int kv_pages;      /* pages per layer's pool when kv_page_rows > 0 */
 } blok_model_config;
 
 typedef struct blok_model blok_model_t;
@@ -469,6 +473,22 @@ int blok_model_step(blok_model_t *model, const uint32_t *ids, int B, uint32_t *n
  * token is sampled: next_id uint32 [1] on the device.  The position of sequence 0 advances by n.  The result is what
  * n calls of blok_model_step would give, up to the summation order of the batched kernels.  Needs prefill_chunk >= 1. */
 int blok_model_prefill(blok_model_t *model, const uint32_t *ids, int n, uint32_t *next_id, blok_stream_t stream);
+
+/* The paged model (kv_page_rows > 0): batch entry b of a step is the resident sequence in slot slots[b] (HOST array of
+ * B distinct slots in [0, max_batch)), so a step can run any subset of the resident sequences.  Before launching, the
+ * pages for each sequence's next row are reserved; when the pool cannot supply them the call returns
+ * BLOK_ERR_WORKSPACE and launches nothing.  ids / next_ids uint32 [B] on the device, in batch order.
+ * blok_model_step on a paged model is this call with slots 0..B-1. */
+int blok_model_step_slots(blok_model_t *model, const int *slots, int B, const uint32_t *ids, uint32_t *next_ids,
+                          blok_stream_t stream);
+/* blok_model_prefill for the sequence in `slot` of a paged model (a dense model accepts slot 0 only). */
+int blok_model_prefill_slot(blok_model_t *model, int slot, const uint32_t *ids, int n, uint32_t *next_id,
+                            blok_stream_t stream);
+/* Ends the sequence in `slot`: its position returns to 0 and, on a paged model, its pages go back to the pool. */
+int blok_model_slot_release(blok_model_t *model, int slot, blok_stream_t stream);
+/* Tokens cached for the sequence in `slot` (host-side count), and free pages of the pool (-1 on a dense model). */
+long blok_model_slot_length(blok_model_t *model, int slot);
+int blok_model_free_pages(blok_model_t *model);
 
 /* Greedy generation for one sequence with HOST token arrays, as generate()
  * (src/kimi_exec.cu:885-890): the prompt is replayed token by token (through

@@ -213,3 +213,94 @@ def test_model_steps_twelve_sequences(cuda, oracle):
     with pytest.raises(lib.BlokError):
         model.step(torch.zeros(B + 1, dtype=torch.int32, device=cuda))
     model.close()
+
+
+# ---- the model over a page pool: the same kernels with another address rule, so the tokens must be identical ----
+
+CFGS = dict(layers=3, first_dense=1, hidden=1024, vocab=2048, dense_inter=512, inter=256, experts=16, topk=8,
+            shared_inter=256, q_rank=256, max_batch=3, max_ctx=64, yarn_factor=64.0)
+
+
+def _ids(values, device):
+    return torch.tensor(values, dtype=torch.int32, device=device)
+
+
+def test_paged_model_equals_dense_model(cuda):
+    from blok_b200 import lib
+    from test_gpu_model import _sharpen
+    dense = lib.Model(seed=8, **CFGS)
+    paged = lib.Model(seed=8, **dict(CFGS, kv_page_rows=32, kv_pages=6))
+    _sharpen(dense)
+    _sharpen(paged)
+    assert paged.free_pages == 6 and dense.free_pages == -1
+    ids = _ids([5, 900, 77], cuda)
+    for _ in range(5):
+        a, b = dense.step(ids), paged.step(ids)
+        assert torch.equal(a, b)
+        ids = a
+    assert paged.free_pages == 3 and [paged.slot_length(s) for s in range(3)] == [5, 5, 5]
+    # a subset of the resident sequences, in another order
+    a = dense.step(ids)
+    b = paged.step_slots([2, 0], ids[[2, 0]].contiguous())
+    assert torch.equal(b, a[[2, 0]])
+    assert [paged.slot_length(s) for s in range(3)] == [6, 5, 6]
+    # the sequence in slot 1 ends, another one starts there: it must behave like a fresh sequence
+    paged.release_slot(1)
+    assert paged.free_pages == 4 and paged.slot_length(1) == 0
+    fresh = lib.Model(seed=8, **dict(CFGS, max_batch=1))
+    _sharpen(fresh)
+    tok = _ids([1234], cuda)
+    for _ in range(3):
+        want, got = fresh.step(tok), paged.step_slots([1], tok)
+        assert torch.equal(want, got)
+        tok = want
+    with pytest.raises(lib.BlokError):
+        paged.step_slots([0, 0], _ids([1, 2], cuda))        # a slot twice
+    with pytest.raises(lib.BlokError):
+        dense.step_slots([1, 0], _ids([1, 2], cuda))        # a dense cache has no slot indirection
+    for m in (dense, paged, fresh):
+        m.close()
+
+
+def test_paged_model_pool_exhaustion_is_an_error_not_a_fault(cuda):
+    from blok_b200 import lib
+    model = lib.Model(seed=9, **dict(CFGS, kv_page_rows=32, kv_pages=4))
+    ids = _ids([1, 2, 3], cuda)
+    for _ in range(32):                     # every sequence fills its first page
+        ids = model.step(ids)
+    assert model.free_pages == 1
+    with pytest.raises(lib.BlokError) as e:  # three sequences need a second page, one is left
+        model.step(ids)
+    assert e.value.code == -6
+    assert [model.slot_length(s) for s in range(3)] == [32, 32, 32]   # nothing was launched, nothing advanced
+    model.release_slot(2)
+    nxt = model.step_slots([0, 1], ids[:2].contiguous())
+    assert nxt.shape == (2,) and [model.slot_length(s) for s in range(3)] == [33, 33, 0]
+    with pytest.raises(lib.BlokError) as e:  # max_ctx bounds a sequence as the reference's capacity check does (:205)
+        for _ in range(40):
+            nxt = model.step_slots([0], nxt[:1].contiguous())
+    assert e.value.code == -2 and model.slot_length(0) == 64
+    model.reset()
+    assert model.free_pages == 4 and model.slot_length(0) == 0
+    model.close()
+
+
+def test_paged_model_prefill_equals_dense_prefill(cuda):
+    from blok_b200 import lib
+    from test_gpu_model import _sharpen
+    dense = lib.Model(seed=10, **dict(CFGS, max_batch=1, prefill_chunk=8))
+    paged = lib.Model(seed=10, **dict(CFGS, prefill_chunk=8, kv_page_rows=32, kv_pages=5))
+    _sharpen(dense)
+    _sharpen(paged)
+    prompt = _ids([int(t) for t in np.random.default_rng(3).integers(0, CFGS["vocab"], size=37)], cuda)  # crosses into a second page
+    a, b = dense.prefill(prompt), paged.prefill_slot(2, prompt)
+    assert torch.equal(a, b) and paged.slot_length(2) == 37 and paged.free_pages == 3
+    for _ in range(3):
+        a, b = dense.step(a), paged.step_slots([2], b)
+        assert torch.equal(a, b)
+    with pytest.raises(lib.BlokError):
+        paged.prefill_slot(0, _ids(list(range(65)), cuda))   # longer than max_ctx
+    with pytest.raises(lib.BlokError):
+        dense.prefill_slot(1, prompt)
+    dense.close()
+    paged.close()
