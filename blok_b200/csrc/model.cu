@@ -88,7 +88,7 @@ struct blok_model {
   std::vector<void *> allocations;
   // step buffers
   uint16_t *x = nullptr, *n = nullptr, *tmp = nullptr;  // [max(max_batch, prefill_chunk), hidden]
-  uint32_t *prompt_ids = nullptr;                       // [max_ctx] a prompt given on the host (prefill_chunk >= 1)
+  uint32_t *prompt_ids = nullptr;                       // [max(max_ctx, rows)] token ids given on the host (prefill_chunk >= 1)
   int rows = 0;                                         // max(max_batch, prefill_chunk)
   bool moe_batched_ok = false;                          // the layer sizes fit the grouped-GEMM kernels
   std::vector<long> host_pos;                           // tokens cached per sequence (host mirror of pos)
@@ -241,7 +241,8 @@ int build(blok_model *m) {
   if ((rc = dev_alloc(m, c.max_batch * 4, &p))) return rc; m->pos = static_cast<int *>(p);
   if ((rc = dev_alloc(m, m->rows * 4, &p))) return rc; m->ids = static_cast<uint32_t *>(p);
   if ((rc = dev_alloc(m, m->rows * 4, &p))) return rc; m->next = static_cast<uint32_t *>(p);
-  if ((rc = dev_alloc(m, (size_t)(c.prefill_chunk > 0 ? c.max_ctx : 1) * 4, &p))) return rc; m->prompt_ids = static_cast<uint32_t *>(p);
+  if ((rc = dev_alloc(m, (size_t)(c.prefill_chunk > 0 ? (c.max_ctx > m->rows ? c.max_ctx : m->rows) : 1) * 4, &p))) return rc;
+  m->prompt_ids = static_cast<uint32_t *>(p);
   m->mlp_ws_bytes = blok_bf16_mlp_workspace_bytes(c.hidden, c.dense_inter > 0 ? c.dense_inter : 32, 8);
   if ((rc = dev_alloc(m, m->mlp_ws_bytes, &m->mlp_ws))) return rc;
   m->head_ws_bytes = blok_lm_head_workspace_bytes(c.vocab, c.max_batch);
@@ -594,4 +595,82 @@ extern "C" int blok_model_generate(blok_model_t *m, const uint32_t *prompt, int 
     }
   }
   return BLOK_OK;
+}
+
+// The serving loop of blok_model_generate_many over an existing batcher (the caller destroys it).
+static int serve_requests(blok_model_t *m, blok_batcher_t *bt, const uint32_t *prompts, const int *prompt_offsets, int n_requests,
+                          int max_new, uint32_t *out, int *n_out) {
+  const blok_model_config &c = m->cfg;
+  int rc = BLOK_OK;
+  for (int r = 0; r < n_requests && !rc; ++r) {
+    int id = -1;
+    rc = blok_batcher_submit(bt, prompt_offsets[r + 1] - prompt_offsets[r], max_new, &id);
+    n_out[r] = 0;
+  }
+  std::vector<int> admit_slots(c.max_batch), admit_req(c.max_batch), decode_slots(c.max_batch), slot_req(c.max_batch, -1);
+  std::vector<uint32_t> last(c.max_batch, 0), ids(c.max_batch), sampled(c.max_batch);
+  // one sampled token of the sequence in `slot`: emitted unless it is EOS (:887); the batcher says whether the sequence ended
+  auto take = [&](int slot, uint32_t tok) -> int {
+    const int r = slot_req[slot];
+    const int eos = tok == c.eos_id;
+    if (!eos) out[(size_t)r * max_new + n_out[r]++] = tok;
+    last[slot] = tok;
+    int finished = 0;
+    int e = blok_batcher_token(bt, slot, eos, &finished);
+    if (e) return e;
+    if (finished) {
+      slot_req[slot] = -1;
+      return blok_model_slot_release(m, slot, nullptr);
+    }
+    return BLOK_OK;
+  };
+  while (!rc && blok_batcher_unfinished(bt) > 0) {
+    int n_admit = 0, n_decode = 0;
+    if ((rc = blok_batcher_plan(bt, admit_slots.data(), admit_req.data(), &n_admit, decode_slots.data(), &n_decode))) break;
+    if (n_admit == 0 && n_decode == 0) {  // cannot happen: submit refused what can never fit, and finished sequences free their budget
+      set_error("blok_model_generate_many: no sequence can make progress");
+      rc = BLOK_ERR_STATE;
+      break;
+    }
+    if (n_decode) {  // the running sequences step together; their ids come back for the EOS test, as at :882
+      for (int b = 0; b < n_decode; ++b) ids[b] = last[decode_slots[b]];
+      BLOK_CUDA(cudaMemcpyAsync(m->prompt_ids, ids.data(), (size_t)n_decode * 4, cudaMemcpyHostToDevice, nullptr));
+      if ((rc = blok_model_step_slots(m, decode_slots.data(), n_decode, m->prompt_ids, m->next, nullptr))) break;
+      BLOK_CUDA(cudaMemcpy(sampled.data(), m->next, (size_t)n_decode * 4, cudaMemcpyDeviceToHost));
+      for (int b = 0; b < n_decode && !rc; ++b) rc = take(decode_slots[b], sampled[b]);
+      if (rc) break;
+    }
+    for (int a = 0; a < n_admit && !rc; ++a) {  // arrivals: the prompt in chunks, its last token sampled
+      const int slot = admit_slots[a], r = admit_req[a];
+      const int n = prompt_offsets[r + 1] - prompt_offsets[r];
+      slot_req[slot] = r;
+      BLOK_CUDA(cudaMemcpyAsync(m->prompt_ids, prompts + prompt_offsets[r], (size_t)n * 4, cudaMemcpyHostToDevice, nullptr));
+      if ((rc = blok_model_prefill_slot(m, slot, m->prompt_ids, n, m->next, nullptr))) break;
+      uint32_t tok = 0;
+      BLOK_CUDA(cudaMemcpy(&tok, m->next, 4, cudaMemcpyDeviceToHost));
+      rc = take(slot, tok);
+    }
+  }
+  return rc;
+}
+
+extern "C" int blok_model_generate_many(blok_model_t *m, const uint32_t *prompts, const int *prompt_offsets, int n_requests,
+                                        int max_new, uint32_t *out, int *n_out) {
+  BLOK_REQUIRE(m && prompts && prompt_offsets && out && n_out, BLOK_ERR_ARG, "blok_model_generate_many: null pointer");
+  BLOK_REQUIRE(m->pages && m->cfg.prefill_chunk >= 1, BLOK_ERR_STATE,
+               "blok_model_generate_many: needs a paged model (kv_page_rows > 0) with prefill_chunk >= 1");
+  BLOK_REQUIRE(n_requests >= 1 && max_new >= 1, BLOK_ERR_ARG, "blok_model_generate_many: no requests or max_new < 1");
+  const blok_model_config &c = m->cfg;
+  for (int r = 0; r < n_requests; ++r) {
+    BLOK_REQUIRE(prompt_offsets[r + 1] > prompt_offsets[r], BLOK_ERR_ARG, "blok_model_generate_many: request %d has an empty prompt", r);
+    for (int i = prompt_offsets[r]; i < prompt_offsets[r + 1]; ++i)
+      BLOK_REQUIRE(prompts[i] < (uint32_t)c.vocab, BLOK_ERR_ARG, "blok_model_generate_many: prompt token outside vocabulary");  // :552
+  }
+  int rc = blok_model_reset(m);
+  if (rc) return rc;
+  blok_batcher_t *bt = nullptr;
+  if ((rc = blok_batcher_create(c.max_batch, c.kv_pages, c.kv_page_rows, c.max_ctx, &bt))) return rc;
+  rc = serve_requests(m, bt, prompts, prompt_offsets, n_requests, max_new, out, n_out);
+  blok_batcher_destroy(bt);
+  return rc;
 }

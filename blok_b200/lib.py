@@ -485,6 +485,62 @@ class KvPages:
         _check(load().blok_kv_pages_upload(self._handle, _ptr(device_table, torch.int32, "device_table"), _stream()))
 
 
+class Batcher:
+    """Host-side continuous-batching scheduler (blok_batcher_*): no GPU needed."""
+
+    def __init__(self, slots, n_pages, page_rows, max_ctx):
+        self.slots = slots
+        self._handle = C.c_void_p()
+        _check(load().blok_batcher_create(C.c_int(slots), C.c_int(n_pages), C.c_int(page_rows), C.c_int(max_ctx),
+                                          C.byref(self._handle)))
+
+    def close(self):
+        if getattr(self, "_handle", None) is not None and self._handle.value:
+            load().blok_batcher_destroy(self._handle)
+            self._handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def submit(self, n_prompt, max_new):
+        rid = C.c_int(-1)
+        _check(load().blok_batcher_submit(self._handle, C.c_int(n_prompt), C.c_int(max_new), C.byref(rid)))
+        return rid.value
+
+    def plan(self):
+        """-> (admitted [(slot, request)], decode slots)"""
+        A = C.c_int * self.slots
+        a_s, a_r, d_s, na, nd = A(), A(), A(), C.c_int(0), C.c_int(0)
+        _check(load().blok_batcher_plan(self._handle, a_s, a_r, C.byref(na), d_s, C.byref(nd)))
+        return [(a_s[i], a_r[i]) for i in range(na.value)], [d_s[i] for i in range(nd.value)]
+
+    def token(self, slot, is_eos=False):
+        """Reports a sampled token of the sequence in `slot`; True when the sequence ended."""
+        fin = C.c_int(0)
+        _check(load().blok_batcher_token(self._handle, C.c_int(slot), C.c_int(1 if is_eos else 0), C.byref(fin)))
+        return bool(fin.value)
+
+    @property
+    def unfinished(self):
+        return int(load().blok_batcher_unfinished(self._handle))
+
+    @property
+    def waiting(self):
+        return int(load().blok_batcher_waiting(self._handle))
+
+    @property
+    def committed_pages(self):
+        f = load().blok_batcher_committed_pages
+        f.restype = C.c_long
+        return int(f(self._handle))
+
+    def emitted(self, request):
+        return int(load().blok_batcher_emitted(self._handle, C.c_int(request)))
+
+
 class ModelConfig(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("layers", "first_dense", "hidden", "vocab", "dense_inter", "inter", "experts", "topk",
                                        "shared_inter")] + [("routed_scale", C.c_float)] + \
@@ -624,6 +680,20 @@ class Model:
     @property
     def free_pages(self):
         return int(load().blok_model_free_pages(self._handle))
+
+    def generate_many(self, prompts, max_new):
+        """Greedy generation for several prompts at once on a paged model (blok_model_generate_many): a list of token
+        lists in, a list of token lists out, in the same order."""
+        import numpy as np
+        flat = np.ascontiguousarray([t for p in prompts for t in p], np.uint32)
+        offs = np.zeros(len(prompts) + 1, np.int32)
+        offs[1:] = np.cumsum([len(p) for p in prompts])
+        out = np.zeros(len(prompts) * max_new, np.uint32)
+        n = np.zeros(len(prompts), np.int32)
+        _check(load().blok_model_generate_many(self._handle, flat.ctypes.data_as(C.c_void_p), offs.ctypes.data_as(C.c_void_p),
+                                               C.c_int(len(prompts)), C.c_int(max_new), out.ctypes.data_as(C.c_void_p),
+                                               n.ctypes.data_as(C.c_void_p)))
+        return [out[r * max_new:r * max_new + n[r]].tolist() for r in range(len(prompts))]
 
     def generate(self, prompt, max_new):
         """Greedy generation with host token lists, like the reference executor's command line."""

@@ -490,6 +490,42 @@ int blok_model_slot_release(blok_model_t *model, int slot, blok_stream_t stream)
 long blok_model_slot_length(blok_model_t *model, int slot);
 int blok_model_free_pages(blok_model_t *model);
 
+/* ------------------------------------------------------------------------- */
+/* Continuous batching: host-side scheduler                                    */
+/* ------------------------------------------------------------------------- */
+
+/* Decides, iteration by iteration, which queued request enters which sequence slot and which slots step.  Every
+ * sequence follows the reference's own rule (src/kimi_exec.cu:885-890: prompt, then one token per iteration until EOS
+ * or max_new tokens; EOS is not emitted); up to `slots` of them run side by side over a pool of n_pages pages of
+ * page_rows rows.  Admission is in arrival order and reserves a request's whole budget (prompt + max_new rows), so a
+ * running sequence never finds the pool empty and none is evicted.  Host memory only: no CUDA call, works without a GPU. */
+typedef struct blok_batcher blok_batcher_t;
+int blok_batcher_create(int slots, int n_pages, int page_rows, int max_ctx, blok_batcher_t **out);
+int blok_batcher_destroy(blok_batcher_t *batcher);
+/* Queues a request; ids count up from 0.  BLOK_ERR_SHAPE when n_prompt + max_new exceeds max_ctx (the reference's
+ * check, :784), BLOK_ERR_WORKSPACE when the pool could never hold it. */
+int blok_batcher_submit(blok_batcher_t *batcher, int n_prompt, int max_new, int *request_id);
+/* The next iteration: decode_slots[0..n_decode) are the running sequences, which step once; admit_slots[i] /
+ * admit_requests[i], i < n_admit, are the requests that enter now (the caller prefills their prompts).  All arrays
+ * hold `slots` ints.  Every slot listed must be answered with blok_batcher_token before the next plan. */
+int blok_batcher_plan(blok_batcher_t *batcher, int *admit_slots, int *admit_requests, int *n_admit, int *decode_slots,
+                      int *n_decode);
+/* The sequence in `slot` sampled a token (is_eos: it was the end-of-sequence id).  *finished = 1 when the sequence
+ * ended (EOS, or max_new tokens emitted): its slot and its pages are free for the next plan. */
+int blok_batcher_token(blok_batcher_t *batcher, int slot, int is_eos, int *finished);
+int blok_batcher_unfinished(const blok_batcher_t *batcher);       /* requests not finished yet (waiting or running) */
+int blok_batcher_waiting(const blok_batcher_t *batcher);          /* requests not admitted yet */
+long blok_batcher_committed_pages(const blok_batcher_t *batcher); /* pages promised to the running sequences */
+int blok_batcher_emitted(const blok_batcher_t *batcher, int request_id); /* tokens emitted for a request */
+
+/* Greedy generation for n_requests prompts at once on a paged model with prefill_chunk >= 1 (HOST arrays): prompt r
+ * is prompts[prompt_offsets[r] .. prompt_offsets[r+1]); out holds n_requests * max_new ids, request r's tokens at
+ * out + r * max_new, their count in n_out[r].  Each request gets what blok_model_generate gives for it alone (up to
+ * the summation order of the batched kernels); the requests share the model's slots and page pool through a
+ * blok_batcher: prompts are prefilled as they are admitted, all running sequences step together. */
+int blok_model_generate_many(blok_model_t *model, const uint32_t *prompts, const int *prompt_offsets, int n_requests,
+                             int max_new, uint32_t *out, int *n_out);
+
 /* Greedy generation for one sequence with HOST token arrays, as generate()
  * (src/kimi_exec.cu:885-890): the prompt is replayed token by token (through
  * blok_model_prefill when prefill_chunk >= 1), then up to max_new tokens are
