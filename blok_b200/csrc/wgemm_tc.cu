@@ -8,13 +8,15 @@
 // and up rows of the same indices, or rows r and r + 128 of the down projection).  The
 // weight rows are the M = 128 dimension of tcgen05.mma, the tokens the N dimension, so
 // a weight byte is read from HBM and dequantised once per tile whatever the token
-// count.  Per 64-column step the 256 threads (one weight row each) unpack their packed
-// words into shared memory in the K-major core-matrix layout the instruction reads
-// (no swizzle: 8 rows x 16 bytes per core matrix), permute the tile's activations the
-// same way, and one thread issues the MMAs; tcgen05.commit on an mbarrier frees the
-// stage.  The global loads of the next step are in registers while this one is
-// unpacked.  Every mbarrier wait is bounded; on a timeout the CTA records an error,
-// still releases its tensor memory and returns.
+// count.  Eight producer warps (one weight row per thread) copy 256 packed columns and
+// their scales per step into shared memory with coalesced cp.async (rows XOR-swizzled
+// against bank conflicts), dequantise them exactly and write them to TENSOR MEMORY with
+// tcgen05.st as the A operand, 64 columns per pipeline stage; the tile's activations go
+// to shared memory in the K-major core-matrix layout the instruction reads (no swizzle:
+// 8 rows x 16 bytes per core matrix) as the B operand.  A ninth warp's first lane issues
+// the MMAs; producers arrive on a `full` mbarrier per stage, tcgen05.commit on an `empty`
+// mbarrier frees it.  Every mbarrier wait is bounded; on a timeout the CTA records an
+// error, still releases its tensor memory and returns.
 #include "common.cuh"
 #include "wgemm.h"
 
