@@ -25,6 +25,11 @@ NVCC_FLAGS = [
 ]
 
 
+# Extra nvcc flags for experiments with the kernels' compile-time knobs, e.g.
+#   BLOK_NVCC_EXTRA="-DBLOK_I4_ACC_CHAINS=2 -DBLOK_RING_DEPTH=5" python -m blok_b200.build --force
+EXTRA = os.environ.get("BLOK_NVCC_EXTRA", "").split()
+
+
 def _deps():
     hdrs = glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.h"))
     hdrs.append(os.path.join(HERE, "..", "include", "blok_b200.h"))
@@ -36,7 +41,7 @@ def _compile(src, verbose_ptxas):
     deps = [src] + _deps()
     if os.path.exists(obj) and all(os.path.getmtime(d) <= os.path.getmtime(obj) for d in deps):
         return obj, ""
-    cmd = ["nvcc"] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose_ptxas else []) + ["-c", src, "-o", obj]
+    cmd = ["nvcc"] + NVCC_FLAGS + EXTRA + (["-Xptxas", "-v"] if verbose_ptxas else []) + ["-c", src, "-o", obj]
     p = subprocess.run(cmd, capture_output=True, text=True)
     if p.returncode != 0:
         raise RuntimeError("nvcc failed for %s:\n%s\n%s" % (src, p.stdout, p.stderr))
