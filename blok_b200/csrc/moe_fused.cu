@@ -36,6 +36,8 @@
 // cp.async ring in shared memory (each lane copies and later reads back its own
 // words, so the ring needs no barrier).
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 #include <vector>
 
 #include "bf16_mma.cuh"
@@ -704,18 +706,25 @@ int fused_plan(const blok_moe_weights &w, FusedPlan *plan) {
   plan->grid = sms;
   plan->smem = smem;
   plan->total_warps = plan->grid * kFusedWarps;
-  // chunking (steps of 1 KB of weights per warp)
+  // chunking (steps of 1 KB of weights per warp); BLOK_FUSED_CHUNK_STEPS="R,A,B,C2" overrides the target steps per
+  // chunk of the four phases that are cut (a tuning aid; the defaults are the measured configuration)
+  int tgt[4] = {28, 28, 14, 32};
+  if (const char *e = getenv("BLOK_FUSED_CHUNK_STEPS")) {
+    int v[4];
+    if (sscanf(e, "%d,%d,%d,%d", &v[0], &v[1], &v[2], &v[3]) == 4 && v[0] > 0 && v[1] > 0 && v[2] > 0 && v[3] > 0)
+      for (int i = 0; i < 4; ++i) tgt[i] = v[i];
+  }
   plan->sprR = w.hidden / 32;
-  cut(plan->sprR, 28, &plan->spcR, &plan->cprR);
+  cut(plan->sprR, tgt[0], &plan->spcR, &plan->cprR);
   plan->sprA = w.hidden / 32;
-  cut(plan->sprA, 28, &plan->spcA, &plan->cprA);
+  cut(plan->sprA, tgt[1], &plan->spcA, &plan->cprA);
   plan->sprB = w.hidden / 128;
-  cut(plan->sprB, 14, &plan->spcB, &plan->cprB);
+  cut(plan->sprB, tgt[2], &plan->spcB, &plan->cprB);
   plan->sprC1 = w.inter / 128;
   plan->sprC2 = w.shared_inter / 32;
   plan->spcC2 = 1;
   plan->cprC2 = 1;
-  if (w.shared_inter) cut(plan->sprC2, 32, &plan->spcC2, &plan->cprC2);
+  if (w.shared_inter) cut(plan->sprC2, tgt[3], &plan->spcC2, &plan->cprC2);
   plan->nrbR = w.experts / 16;
   plan->nrbA = w.shared_inter / 8;
   plan->nrbB = w.topk * (w.inter / 8);
