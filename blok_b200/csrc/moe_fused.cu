@@ -273,17 +273,23 @@ __device__ __forceinline__ void ld_tagged_units(const uint2 *p, int stride, int 
   for (int i = 0; i < NU; ++i) out[i] = make_uint4(r[i][0], r[i][2], r[i][4], r[i][6]);
 }
 
+#ifndef BLOK_FUSED_STAGE_UNITS
+#define BLOK_FUSED_STAGE_UNITS 2
+#endif
+constexpr int kStageUnits = BLOK_FUSED_STAGE_UNITS;
+
 // One warp stages `cols` mid values (tagged pairs written earlier in this launch by other
 // warps; values that are not there yet are polled) into INT4 fragment order with group sums.
 __device__ __noinline__ void warp_stage_i4(const uint2 *src, uint4 *xfrag, float *xsum, int cols, int lane,
                                               unsigned epoch, unsigned *err) {
   const int units = cols / 8;  // 32-byte tagged units; lane handles units lane, lane + 32, ...
-  for (int u0 = lane; u0 < units; u0 += 64) {
-    uint4 vv[2];
-    const int n = min(2, (units - u0 + 31) / 32);
-    ld_tagged_units<2>(src + (size_t)u0 * 4, 32 * 4, n, epoch, err, vv);
+  // kStageUnits units per lane are requested before any tag is looked at: one L2 round trip per kStageUnits * 32 units
+  for (int u0 = lane; u0 < units; u0 += 32 * kStageUnits) {
+    uint4 vv[kStageUnits];
+    const int n = min(kStageUnits, (units - u0 + 31) / 32);
+    ld_tagged_units<kStageUnits>(src + (size_t)u0 * 4, 32 * 4, n, epoch, err, vv);
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
+    for (int j = 0; j < kStageUnits; ++j) {
       const int u = u0 + 32 * j;
       if (u < units) {  // units is a multiple of 32, so this is warp-uniform
         const uint4 v = vv[j];
