@@ -4,6 +4,7 @@
 //   blok-kimi-exec --index <runtime-index.blok> --prompt-tokens <id,id,...> --tokens <n>
 //                  [--synthetic-seed <s>] [--layers <n>] [--experts <n>] [--vocab <n>] [--max-ctx <n>]
 //                  [--hidden --inter --dense-inter --shared-inter --heads --q-rank --kv-rank <n>]
+//                  [--prefill-chunk <n>]   prompt in chunks of n tokens (1..64) instead of token by token
 //
 // Success: exit 0 and exactly one stdout line {"status":"ok","token_ids":[...]}.
 // Failure: a message on stderr and exit 1, which blok/runtime.py:86-94 turns into

@@ -29,6 +29,8 @@ def test_argument_errors_exit_1_with_message(exe):
                       (["--index", "x", "--prompt-tokens", "1,a", "--tokens", "2"], "bad prompt token"),
                       (["--index", "x", "--prompt-tokens", "999999", "--tokens", "2"], "prompt token outside vocabulary"),
                       (["--index", "x", "--prompt-tokens", "1", "--tokens", "0"], "bad args"),
+                      (["--index", "x", "--prompt-tokens", "1", "--tokens", "2", "--prefill-chunk", "8"],
+                       "index: runtime index: cannot open x"),
                       (["--index", "x", "--prompt-tokens", "1", "--tokens", "2"], "index: runtime index: cannot open x")):
         p = run(exe, *args)
         assert p.returncode == 1 and msg in p.stderr and p.stdout == "", (args, p.stderr)

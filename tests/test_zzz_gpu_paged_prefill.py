@@ -330,3 +330,19 @@ def test_generate_many_serves_every_request_like_generate_alone(cuda):
         many.generate_many([[1] * 60], 5)      # longer than max_ctx
     alone.close()
     many.close()
+
+
+def test_cli_prefill_chunk_flag_runs_the_prompt_in_chunks():
+    import json
+    from test_cli import run, EXE
+    from blok_b200 import build
+    build.build()
+    exe = EXE
+    args = ["--index", "unused", "--prompt-tokens", "5,6,7,8,9,10,11", "--tokens", "3", "--synthetic-seed", "1", "--layers", "2",
+            "--experts", "16", "--vocab", "4096"]
+    replay, chunks = run(exe, *args), run(exe, *args, "--prefill-chunk", "4")
+    assert replay.returncode == 0 and chunks.returncode == 0, (replay.stderr, chunks.stderr)
+    a, b = json.loads(replay.stdout)["token_ids"], json.loads(chunks.stdout)["token_ids"]
+    assert 1 <= len(b) <= 3 and all(0 <= t < 4096 for t in b) and len(a) == len(b)
+    p = run(exe, *args, "--prefill-chunk", "65")
+    assert p.returncode == 1 and "unsupported configuration" in p.stderr
