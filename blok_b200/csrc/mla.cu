@@ -17,6 +17,7 @@
 #include <new>
 
 #include "bf16_mma.cuh"
+#include "wgemm.h"
 
 namespace blok {
 
@@ -236,6 +237,8 @@ struct blok_mla_layer {
   uint16_t *av = nullptr;      // [B, heads * v_head]
   int *seq = nullptr;          // [B]
   int *chunk_pos = nullptr;    // [B] positions of a prefill chunk's tokens
+  int *tiles = nullptr;        // tile table of the weight-streaming GEMM (projections of 16 or more entries)
+  int n_tiles = 0;
   void *sk_ws = nullptr;       // split-K partial sums and tickets of the projections (zeroed at create)
   size_t sk_bytes = 0;
   float *part_o = nullptr;     // [max_splits * max_batch..]
@@ -303,6 +306,8 @@ extern "C" int blok_mla_layer_create(const blok_mla_weights *w, int max_batch, i
   size_t o_av = take((size_t)max_batch * w->heads * w->v_head * 2);
   size_t o_seq = take((size_t)max_batch * 4);
   size_t o_cpos = take((size_t)max_batch * 4);
+  L->n_tiles = (max_batch + kWgTileTokens - 1) / kWgTileTokens;
+  size_t o_tiles = take((size_t)(3 * L->n_tiles + 1) * sizeof(int));
   size_t o_po = take((size_t)(L->max_splits + max_batch) * w->heads * w->kv_rank * 4);
   size_t o_pml = take((size_t)(L->max_splits + max_batch) * w->heads * 2 * 4);
   L->sk_bytes = bf16_gemv_splitk_workspace_bytes(std::max(std::max(w->q_rank, lat_w), std::max(w->heads * qk_head, w->hidden)));
@@ -329,6 +334,7 @@ extern "C" int blok_mla_layer_create(const blok_mla_weights *w, int max_batch, i
   L->av = reinterpret_cast<uint16_t *>(b + o_av);
   L->seq = reinterpret_cast<int *>(b + o_seq);
   L->chunk_pos = reinterpret_cast<int *>(b + o_cpos);
+  L->tiles = reinterpret_cast<int *>(b + o_tiles);
   L->part_o = reinterpret_cast<float *>(b + o_po);
   L->part_ml = reinterpret_cast<float *>(b + o_pml);
   L->sk_ws = b + o_sk;
@@ -440,6 +446,28 @@ extern "C" int blok_mla_attend_paged(blok_mla_layer_t *L, const blok_bf16_t *q, 
   return attend_and_merge(L, q, c, seq_len, B, softmax_scale, o_lat, (cudaStream_t)stream);
 }
 
+// y[b, :] = bf16(W x[b, :]) for B entries.  Up to 15 entries go through the mat-vec kernel 8 at a time; from 16 on, and
+// where the matrix fits its tiling, one pass of the weight-streaming GEMM reads the weights once for all entries
+// (`tiles_ready`: the identity tile table for B entries has been written on this stream).
+static int project(blok_mla_layer *L, const uint16_t *w, const uint16_t *x, uint16_t *y, int rows, int cols, int B, bool tiles_ready,
+                   cudaStream_t stream) {
+  if (tiles_ready && rows % 128 == 0 && cols % 512 == 0) {
+    const int tiles = (B + kWgTileTokens - 1) / kWgTileTokens;
+    int *tab = L->tiles;
+    WgArgs r;
+    r.w_a = w; r.w_b = nullptr; r.s_a = r.s_b = nullptr; r.expert_stride_rows = 0; r.x = x; r.x_index = nullptr;
+    r.K = cols; r.R = rows; r.out_bf16 = y; r.out_f32 = nullptr;
+    r.tile_expert = tab; r.tile_start = tab + L->n_tiles; r.tile_count = tab + 2 * L->n_tiles; r.num_tiles = tab + 3 * L->n_tiles;
+    r.out_index = nullptr; r.n_rows = B; r.identity_tiles = 1;
+    return launch_wgemm(WG_BF16_PLAIN, r, tiles, stream);
+  }
+  for (int b0 = 0; b0 < B; b0 += 8)
+    if (int rc = launch_bf16_gemv_splitk(w, x + (size_t)b0 * cols, y + (size_t)b0 * rows, nullptr, rows, cols, std::min(8, B - b0), L->sk_ws,
+                                         L->sk_bytes, stream))
+      return rc;
+  return BLOK_OK;
+}
+
 // The attention block for B entries (sequences, or the tokens of a prefill chunk): projections, cache append,
 // attention, output projection.  The mat-vec kernels take up to 8 tokens per launch, so larger B goes through them
 // in groups of 8 (the weights of a later group come from L2 where they fit).
@@ -451,21 +479,15 @@ static int decode_body(blok_mla_layer *L, const uint16_t *n, const CacheRef &c, 
   const size_t q_row = (size_t)w.heads * qk_head, qf_row = (size_t)w.heads * lat_w, ol_row = (size_t)w.heads * w.kv_rank,
                av_row = (size_t)w.heads * w.v_head;
   int rc;
+  const bool gemm = B >= 16;  // enough entries for the GEMM form of the projections to pay
+  if (gemm && (rc = launch_identity_tiles(B, L->tiles, L->tiles + L->n_tiles, L->tiles + 2 * L->n_tiles, L->tiles + 3 * L->n_tiles, stream)))
+    return rc;
   // q_a -> RMSNorm -> q_b   (:813-815)
-  for (int b0 = 0; b0 < B; b0 += 8)
-    if ((rc = launch_bf16_gemv_splitk(w.q_a, n + (size_t)b0 * w.hidden, L->qa + (size_t)b0 * w.q_rank, nullptr, w.q_rank, w.hidden,
-                                      std::min(8, B - b0), L->sk_ws, L->sk_bytes, stream)))
-      return rc;
+  if ((rc = project(L, w.q_a, n, L->qa, w.q_rank, w.hidden, B, gemm, stream))) return rc;
   if ((rc = blok_rmsnorm(L->qa, w.q_a_ln, L->qa, B, w.q_rank, w.rms_eps, stream_))) return rc;
-  for (int b0 = 0; b0 < B; b0 += 8)
-    if ((rc = launch_bf16_gemv_splitk(w.q_b, L->qa + (size_t)b0 * w.q_rank, L->q + b0 * q_row, nullptr, w.heads * qk_head, w.q_rank,
-                                      std::min(8, B - b0), L->sk_ws, L->sk_bytes, stream)))
-      return rc;
+  if ((rc = project(L, w.q_b, L->qa, L->q, w.heads * qk_head, w.q_rank, B, gemm, stream))) return rc;
   // kv_a; norm of c_kv, RoPE of k_pe and of q's rope part, cache append   (:816-824)
-  for (int b0 = 0; b0 < B; b0 += 8)
-    if ((rc = launch_bf16_gemv_splitk(w.kv_a, n + (size_t)b0 * w.hidden, L->kva + (size_t)b0 * lat_w, nullptr, lat_w, w.hidden,
-                                      std::min(8, B - b0), L->sk_ws, L->sk_bytes, stream)))
-      return rc;
+  if ((rc = project(L, w.kv_a, n, L->kva, lat_w, w.hidden, B, gemm, stream))) return rc;
   mla_prep_kernel<<<dim3(1 + (w.heads * (w.qk_rope / 2) + 255) / 256, B), 256, 0, stream>>>(
       L->kva, w.kv_a_ln, L->q, L->inv_freq, ctx_len, c.base, c.seq_stride, L->q_full, L->seq, w.heads, w.qk_nope, w.qk_rope,
       w.kv_rank, w.rms_eps, c.block_table, c.slot_of, c.table_stride, c.page_rows);
@@ -482,11 +504,7 @@ static int decode_body(blok_mla_layer *L, const uint16_t *n, const CacheRef &c, 
                                (long)ol_row, w.kv_rank, L->av + b0 * av_row, (long)av_row, w.v_head, w.v_head, w.kv_rank, w.heads,
                                std::min(8, B - b0), stream)))
       return rc;
-  for (int b0 = 0; b0 < B; b0 += 8)
-    if ((rc = launch_bf16_gemv_splitk(w.o, L->av + b0 * av_row, out + (size_t)b0 * w.hidden, nullptr, w.hidden, w.heads * w.v_head,
-                                      std::min(8, B - b0), L->sk_ws, L->sk_bytes, stream)))
-      return rc;
-  return BLOK_OK;
+  return project(L, w.o, L->av, out, w.hidden, w.heads * w.v_head, B, gemm, stream);
 }
 
 extern "C" int blok_mla_decode(blok_mla_layer_t *L, const blok_bf16_t *n, blok_bf16_t *cache, long ctx_stride,

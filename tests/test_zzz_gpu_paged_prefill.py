@@ -71,10 +71,11 @@ def test_decode_paged_equals_dense(cuda, layer16):
     assert torch.equal(pool[~changed], pool_before[~changed]), "rows other than the appended ones are untouched"
 
 
-def test_prefill_chunk_equals_token_by_token(cuda, layer16):
+@pytest.mark.parametrize("T", [11, 16])   # 16 entries and more take the GEMM form of the projections
+def test_prefill_chunk_equals_token_by_token(cuda, layer16, T):
     from blok_b200 import synth
     _, layer = layer16
-    first, T, cap = 5, 11, 128
+    first, cap = 5, 128
     cache = synth.latent_cache(1, cap, cuda, seed=23)
     seq_cache, chunk_cache = cache.clone(), cache[0].clone()
     n = synth.activations(T, 7168, cuda, 6)
