@@ -273,6 +273,13 @@ __device__ __forceinline__ void ld_tagged_units(const uint2 *p, int stride, int 
   for (int i = 0; i < NU; ++i) out[i] = make_uint4(r[i][0], r[i][2], r[i][4], r[i][6]);
 }
 
+// Partial sums a finisher requests per round trip when it collects a row-block (the router and the shared gate/up
+// have 7 to collect with the default chunking: two rounds of 4, or one of 8).
+#ifndef BLOK_FUSED_COLLECT
+#define BLOK_FUSED_COLLECT 4
+#endif
+constexpr int kCollect = BLOK_FUSED_COLLECT;
+
 #ifndef BLOK_FUSED_STAGE_UNITS
 #define BLOK_FUSED_STAGE_UNITS 2
 #endif
@@ -555,12 +562,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
     if (np > 1 && lane < 16) {
       const uint2 *src = piece_part(ch) + (size_t)ch.rb * np * 16 + lane;
       float s = 0.f;
-      for (int i0 = 0; i0 < np - 1; i0 += 4) {  // index order, then the own (last) chunk
-        float part[4];
-        const int n = min(4, np - 1 - i0);
-        ld_tagged_n<4>(src + (size_t)i0 * 16, 16, n, epoch, err, part);
+      for (int i0 = 0; i0 < np - 1; i0 += kCollect) {  // index order, then the own (last) chunk
+        float part[kCollect];
+        const int n = min(kCollect, np - 1 - i0);
+        ld_tagged_n<kCollect>(src + (size_t)i0 * 16, 16, n, epoch, err, part);
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < kCollect; ++j)
           if (j < n) s += part[j];
       }
       total = s + total;
