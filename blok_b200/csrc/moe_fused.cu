@@ -53,6 +53,15 @@ namespace blok {
 #ifndef BLOK_RING_DEPTH
 #define BLOK_RING_DEPTH 6
 #endif
+// Output row-blocks (16 rows each) of one routed down chunk.  A chunk stages its slot's mid values once, so 2 or 4
+// row-blocks per chunk halve or quarter that staging (16 KB of tagged reads per 18 KB of weights at 1) and keep the
+// weight ring fed across the row-block boundary.  1 is the measured configuration.
+#ifndef BLOK_FUSED_C1_BLOCKS
+#define BLOK_FUSED_C1_BLOCKS 1
+#endif
+constexpr int kC1Blocks = BLOK_FUSED_C1_BLOCKS;
+static_assert(kC1Blocks == 1 || kC1Blocks == 2 || kC1Blocks == 4, "BLOK_FUSED_C1_BLOCKS must be 1, 2 or 4");
+
 constexpr int kFusedWarps = BLOK_FUSED_WARPS;
 constexpr int kFusedThreads = kFusedWarps * 32;
 constexpr unsigned kSpinLimit = 1u << 22;  // polls before a wait gives up with an error word
@@ -181,7 +190,24 @@ struct Chunk {
   int slot;     // routed slot (B, C1); topk for the shared expert
   const uint4 *w_lo, *w_hi;  // the lane's two weight rows (row start, uint4 units)
   const uint16_t *s_sel;     // the scale row this lane post-scales (INT4 kinds)
+#if BLOK_FUSED_C1_BLOCKS > 1
+  int spr1;                  // C1: steps per row-block (the chunk runs kC1Blocks row-blocks back to back)
+  uint2 *ys;                 // C1: tagged output of the chunk's first row-block
+#endif
 };
+
+#if BLOK_FUSED_C1_BLOCKS > 1
+#define BLOK_C1_EPOCH_ARG , epoch
+#else
+#define BLOK_C1_EPOCH_ARG
+#endif
+
+#if BLOK_FUSED_C1_BLOCKS > 1
+// Row-block of step s inside a routed down chunk of up to four row-blocks.
+__device__ __forceinline__ int c1_block_of(const Chunk &ch, int s) {
+  return (s >= ch.spr1) + (s >= 2 * ch.spr1) + (s >= 3 * ch.spr1);
+}
+#endif
 
 __device__ __forceinline__ bool kind_is_i4(int kind) { return kind == KIND_B || kind == KIND_C1; }
 
@@ -189,11 +215,21 @@ __device__ __forceinline__ void ring_issue(const Chunk &ch, int s, uint32_t ring
   if (s < ch.n) {
     const int t = lane & 3;
     const uint32_t base = ring + (uint32_t)(s % kRingDepth) * kRingStepBytes + (uint32_t)lane * 16;
+#if BLOK_FUSED_C1_BLOCKS > 1
+    size_t off = (size_t)(ch.k0 + s) * 4;  // in uint4 units of a weight row and, equally, in scales of a scale row
+    // the next row-block starts 16 rows = 64 spr1 units further; the step index has already advanced 4 spr1 of them
+    if (ch.kind == KIND_C1) off += (size_t)c1_block_of(ch, s) * 60 * ch.spr1;
+    cp_async16(base, ch.w_lo + off + t);
+    cp_async16(base + 512, ch.w_hi + off + t);
+    if (kind_is_i4(ch.kind))
+      cp_async4(ring + (uint32_t)(s % kRingDepth) * kRingStepBytes + 1024 + (uint32_t)lane * 4, ch.s_sel + off);
+#else
     cp_async16(base, ch.w_lo + (size_t)(ch.k0 + s) * 4 + t);
     cp_async16(base + 512, ch.w_hi + (size_t)(ch.k0 + s) * 4 + t);
     if (kind_is_i4(ch.kind))
       cp_async4(ring + (uint32_t)(s % kRingDepth) * kRingStepBytes + 1024 + (uint32_t)lane * 4,
                 ch.s_sel + (size_t)(ch.k0 + s) * 4);
+#endif
   }
   cp_async_commit();
 }
@@ -209,7 +245,11 @@ __device__ __forceinline__ void ring_prologue(const Chunk &ch, uint32_t ring, in
 // whose first step is kx0.
 __device__ __forceinline__ float ring_consume(const Chunk &ch, uint32_t ring, const unsigned char *ring_ptr,
                                               const XFragLane &xl, const float *xsum, const uint4 *xrow, int kx0,
-                                              int lane) {
+                                              int lane
+#if BLOK_FUSED_C1_BLOCKS > 1
+                                              , unsigned epoch
+#endif
+) {
   const int t = lane & 3;
   const bool hi_row = (t >> 1) != 0;
   const int j0 = 2 * (t & 1);
@@ -221,7 +261,16 @@ __device__ __forceinline__ float ring_consume(const Chunk &ch, uint32_t ring, co
     const unsigned char *slotp = ring_ptr + (size_t)(s % kRingDepth) * kRingStepBytes;
     const uint4 wl = *reinterpret_cast<const uint4 *>(slotp + lane * 16);
     const uint4 wh = *reinterpret_cast<const uint4 *>(slotp + 512 + lane * 16);
+#if BLOK_FUSED_C1_BLOCKS == 1
     const int kx = ch.k0 - kx0 + s;
+#else
+    int kx = ch.k0 - kx0 + s;
+    int blk = 0;
+    if (ch.kind == KIND_C1) {
+      blk = c1_block_of(ch, s);
+      kx = s - blk * ch.spr1;  // every row-block runs over the whole staged mid vector
+    }
+#endif
     if (i4) {
       const uint32_t sc = *reinterpret_cast<const uint32_t *>(slotp + 1024 + lane * 4);
       float dd[4] = {0.f, 0.f, 0.f, 0.f};
@@ -231,6 +280,15 @@ __device__ __forceinline__ float ring_consume(const Chunk &ch, uint32_t ring, co
       const float db = hi_row ? dd[3] : dd[1];
       acc = fmaf(bf16lo(sc), fmaf(-kNibOffset, xs.x, da), acc);
       acc = fmaf(bf16hi(sc), fmaf(-kNibOffset, xs.y, db), acc);
+#if BLOK_FUSED_C1_BLOCKS > 1
+      if (ch.kind == KIND_C1 && kx == ch.spr1 - 1 && s != ch.n - 1) {
+        // a row-block other than the chunk's last is complete: publish its 16 outputs and start the next sum
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        const float total = __shfl_sync(0xffffffffu, acc, ((lane & 7) << 2) + ((lane >> 3) & 1) * 2);
+        if (lane < 16) st_tagged(ch.ys + blk * 16 + lane, round_bf16(total), epoch);
+        acc = 0.f;
+      }
+#endif
     } else {
       const uint4 xb = xrow[kx * 4];
       mma_bf16_16816(d, wl.x, wh.x, wl.y, wh.y, xb.x, xb.y);
@@ -418,13 +476,17 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
       ch.s_sel = ((t >> 1) ? p.up_s : p.gate_s) + ebase + 2 * (t & 1);
     } else if (c < p.cC20) {
       const int rb = (int)(c - p.cC10);
-      const int rb_per_slot = p.hidden / 16;
+      const int rb_per_slot = p.hidden / 16 / kC1Blocks;  // chunks per slot
       ch.kind = KIND_C1;
       ch.slot = rb / rb_per_slot;
-      ch.rb = rb - ch.slot * rb_per_slot;  // output row-block
+      ch.rb = (rb - ch.slot * rb_per_slot) * kC1Blocks;  // (first) output row-block
       ch.kc = 0;
       ch.k0 = 0;
-      ch.n = p.sprC1;
+      ch.n = p.sprC1 * kC1Blocks;
+#if BLOK_FUSED_C1_BLOCKS > 1
+      ch.spr1 = p.sprC1;
+      ch.ys = p.ys + (size_t)ch.slot * p.hidden + ch.rb * 16;
+#endif
       const size_t wrow = p.inter / 32;
       const size_t ebase = (size_t)w_ids[ch.slot] * p.hidden * wrow;
       ch.w_lo = reinterpret_cast<const uint4 *>(p.down_w) + ebase + (size_t)(ch.rb * 16 + g) * wrow;
@@ -515,7 +577,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
   auto arrive = [&](const Chunk &ch, float v) {
     if (ch.kind == KIND_C1) {
       const float total = __shfl_sync(0xffffffffu, v, ((lane & 7) << 2) + ((lane >> 3) & 1) * 2);
-      if (lane < 16) st_tagged(p.ys + (size_t)ch.slot * p.hidden + ch.rb * 16 + lane, round_bf16(total), epoch);
+      // the value in hand is the chunk's last row-block (earlier ones were published as they completed)
+      if (lane < 16) st_tagged(p.ys + (size_t)ch.slot * p.hidden + (ch.rb + kC1Blocks - 1) * 16 + lane, round_bf16(total), epoch);
       return;
     }
     const int np = piece_n(ch);
@@ -614,7 +677,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
       if (cur.kind == KIND_C1) {
         warp_stage_i4(p.mid + (size_t)cur.slot * p.mid_stride / 2, reinterpret_cast<uint4 *>(wstage), msum, p.inter, lane,
                       epoch, err);
-        v = ring_consume(cur, ring, ring_ptr, xl_m, msum, nullptr, 0, lane);
+        v = ring_consume(cur, ring, ring_ptr, xl_m, msum, nullptr, 0, lane BLOK_C1_EPOCH_ARG);
       } else {
         uint4 *seg = reinterpret_cast<uint4 *>(wstage);
         const uint2 *src = p.mid + (size_t)p.topk * p.mid_stride / 2 + (size_t)cur.k0 * 16;
@@ -627,13 +690,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
             if (u0 + 32 * j < cur.n * 4) seg[u0 + 32 * j] = vv[j];
         }
         __syncwarp();
-        v = ring_consume(cur, ring, ring_ptr, xl_m, msum, seg + t, cur.k0, lane);
+        v = ring_consume(cur, ring, ring_ptr, xl_m, msum, seg + t, cur.k0, lane BLOK_C1_EPOCH_ARG);
       }
       __syncwarp();  // the staged segment is free again
     } else if (cur.kind == KIND_B) {
-      v = ring_consume(cur, ring, ring_ptr, xl_x, xsum, nullptr, 0, lane);
+      v = ring_consume(cur, ring, ring_ptr, xl_x, xsum, nullptr, 0, lane BLOK_C1_EPOCH_ARG);
     } else {
-      v = ring_consume(cur, ring, ring_ptr, xl_x, xsum, xnat + t, 0, lane);
+      v = ring_consume(cur, ring, ring_ptr, xl_x, xsum, xnat + t, 0, lane BLOK_C1_EPOCH_ARG);
     }
     // ---- hand in (without waiting), put the next chunk's weights in flight, then look at the count ----
     if (tr) p.trace[16 + (size_t)blockIdx.x * kTraceSlots + 8 + traced * 4 + 1] = global_ns();
@@ -704,6 +767,7 @@ int fused_plan(const blok_moe_weights &w, FusedPlan *plan) {
   plan->enabled = false;
   if (w.experts % 16 || w.topk > 16 || w.shared_inter % 32 || w.inter % 256 || w.hidden % 256) return BLOK_OK;
   if (w.experts_local != w.experts || w.expert_base != 0) return BLOK_OK;
+  if (kC1Blocks > 1 && (w.shared_inter == 0 || (w.hidden / 16) % kC1Blocks)) return BLOK_OK;  // multi-row-block down chunks
   if (w.shared_inter > w.inter && w.shared_inter > 0 && 16 * 64 > w.inter * 2) return BLOK_OK;
   int dev = 0, coop = 0, sms = 0;
   BLOK_CUDA(cudaGetDevice(&dev));
@@ -776,7 +840,7 @@ int launch_moe_decode_fused(blok_moe_layer *L, const uint16_t *x, uint16_t *y, u
   p.cA0 = (unsigned)pl.nrbR * pl.cprR;
   p.cB0 = p.cA0 + (unsigned)pl.nrbA * pl.cprA;
   p.cC10 = p.cB0 + (unsigned)pl.nrbB * pl.cprB;
-  p.cC20 = p.cC10 + (unsigned)pl.nrbC1;
+  p.cC20 = p.cC10 + (unsigned)pl.nrbC1 / kC1Blocks;
   p.total = p.cC20 + (unsigned)pl.nrbC2 * pl.cprC2;
   p.ctrl = L->f_ctrl;
   p.trace = L->f_trace;
