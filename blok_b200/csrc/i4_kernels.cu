@@ -3,6 +3,9 @@
 // :253-256 (silu_mul_k), :853-869 (per-slot body of the routed-expert loop).
 #include <mutex>
 
+#include <cstdlib>
+#include <cstring>
+
 #include "i4_mma.cuh"
 
 namespace blok {
@@ -304,6 +307,9 @@ int launch_i4_down(const uint32_t *down_w, const uint16_t *down_s, const uint16_
 
 static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+int launch_i4_gemv16_imma(const uint32_t *w, const uint16_t *scale, const uint16_t *x, uint16_t *y_bf16, float *y_f32, int rows,
+                          int cols, cudaStream_t stream);
+
 }  // namespace blok
 
 using namespace blok;
@@ -327,6 +333,12 @@ static int i4_gemv_common(const uint32_t *w, const blok_bf16_t *scale, const blo
   if (rows == 0) return BLOK_OK;  // empty tensors may carry null pointers
   BLOK_REQUIRE(w && scale && (x_bf16 || x_f32) && (y_bf16 || y_f32), BLOK_ERR_ARG, "blok_i4_gemv: null pointer");
   BLOK_REQUIRE(aligned16(w), BLOK_ERR_ARG, "blok_i4_gemv: weight_packed must be 16-byte aligned");
+  // BLOK_I4_GEMV_IMPL=imma (read at every call): the integer tensor-core consumer of i4_imma.cuh, an experiment in
+  // cutting the unpack work; it keeps 14 bits below the largest activation of each 32-column group
+  if (x_bf16 && rows % 16 == 0 && cols % 128 == 0 && aligned16(x_bf16) && cols <= 32768) {
+    const char *impl = getenv("BLOK_I4_GEMV_IMPL");
+    if (impl && strcmp(impl, "imma") == 0) return launch_i4_gemv16_imma(w, scale, x_bf16, y_bf16, y_f32, rows, cols, stream);
+  }
   bool tc = x_bf16 && rows % 16 == 0 && cols % 256 == 0 && aligned16(x_bf16) && cols <= 32768;
   if (tc) return launch_i4_gemv16(w, scale, x_bf16, y_bf16, y_f32, rows, cols, stream);
   unsigned blocks = (unsigned)((rows + 7) / 8);
