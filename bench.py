@@ -291,6 +291,23 @@ def other_workload(a, rank, world, device, steps, warmup):
             workload = "REDUCED CASE (%d experts, profiler capture size) of " % a.experts + workload
         scaling = "strong"
         metric = "tok/s, INT4 MoE layer (T=%d)" % T
+    elif a.workload == "gemv":
+        # config 0's building block at a size the launch rate does not bound: one INT4 mat-vec y = W x (matvec_i4_slice,
+        # src/kimi_exec.cu:688) over 32 experts' gate matrices stacked, [65536, 7168] = 264 MB per call, 3 such matrices
+        # rotated.  BLOK_I4_GEMV_IMPL=imma in the environment times the integer tensor-core consumer instead of the
+        # bf16-operand one.
+        R = 65536
+        g = torch.Generator(device=device).manual_seed(11 + rank)
+        mats = [(torch.randint(-2 ** 31, 2 ** 31 - 1, (R, 896), generator=g, device=device, dtype=torch.int32),
+                 (torch.randn((R, 224), generator=g, device=device) * 0.003).abs().bfloat16()) for _ in range(3)]
+        xv = synth.activations(1, 7168, device, 5).view(-1).contiguous()
+        run = lambda i: lib.i4_gemv(mats[i % 3][0], mats[i % 3][1], xv)
+        alg = R * 896 * 4 + R * 224 * 2 + 7168 * 2 + R * 2
+        unit_tokens = world
+        workload = ("config 0 building block: INT4 mat-vec [%d x 7168] (32 gate matrices stacked), batch 1, impl=%s%s" %
+                    (R, os.environ.get("BLOK_I4_GEMV_IMPL", "bf16-operand"), "" if world == 1 else ", replicas x%d" % world))
+        scaling = "weak"
+        metric = "mat-vecs/s, INT4 [%d x 7168]" % R
     else:
         ctx = int(a.workload[len("mla"):])
         layer = lib.MlaLayer(synth.mla_weights(device, seed=3), yarn_factor=32.0, max_batch=8, max_ctx=ctx + 8)
@@ -357,7 +374,7 @@ def main():
     ap.add_argument("--experts", type=int, default=384,
                     help="routed experts per layer; below 384 the run is a reduced case for profiler captures, "
                          "not the benchmark configuration, and the line says so")
-    ap.add_argument("--workload", default="decode", choices=["decode", "batched64", "batched2048", "mla4096", "mla32768", "model", "model61", "prefill512"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "batched64", "batched2048", "mla4096", "mla32768", "model", "model61", "prefill512", "gemv"],
                     help="decode = config 1 (the default, the headline metric); batched* = config 2 (expert parallel "
                          "when --gpus > 1); mla* = config 3 (attention block, batch 8)")
     a = ap.parse_args()
