@@ -57,50 +57,56 @@ __device__ __forceinline__ ImmaStage imma_stage_carve(unsigned char *smem, int c
   return s;
 }
 
-// Quantises x (bf16, global) to block integers in MMA order.  Called by all threads of the CTA (a multiple of 32);
-// unit u = 8 consecutive values = one packed word's columns; the four units of a scale group sit in four adjacent lanes.
+// Quantises one unit (8 consecutive bf16 values = one packed word's columns, v as they lie in memory) of unit index u
+// and stores its bytes; lane i == 0 of the group also stores the group's meta word.  The four units of a scale group
+// must be in four ADJACENT, converged lanes (the group exponent and sum are exchanged with xor-shuffles 1 and 2);
+// lanes with live == false take part in the shuffles and store nothing.
+__device__ __forceinline__ void imma_stage_unit(const uint4 &v, int u, bool live, unsigned char *xq, uint2 *meta) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  // biased exponent of the largest magnitude in the unit, then in the group
+  uint32_t e = 0;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    e = max(e, (w[k] >> 7) & 0xffu);
+    e = max(e, (w[k] >> 23) & 0xffu);
+  }
+  e = max(e, __shfl_xor_sync(0xffffffffu, e, 1));
+  e = max(e, __shfl_xor_sync(0xffffffffu, e, 2));
+  // groups whose values are all below 2^-108 (or zero) contribute nothing; a NaN/Inf exponent is clamped
+  const bool dead = e < 20u;
+  e = min(e, 254u);
+  const float up = __uint_as_float((267u - e) << 23);  // 2^(13 - (e - 127)) = 2^(140 - e)
+  int sum = 0;
+  uint32_t hb[2] = {0, 0}, lb[2] = {0, 0};  // [parity of the column] four bytes each
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float xv = (k & 1) ? bf16hi(w[k >> 1]) : bf16lo(w[k >> 1]);
+    int X = dead ? 0 : __float2int_rn(xv * up);
+    X = max(-16383, min(16383, X));
+    sum += X;
+    const int h = (X + 128) >> 8;
+    const int l = X - h * 256;
+    hb[k & 1] |= (uint32_t)(h & 0xff) << (8 * (k >> 1));
+    lb[k & 1] |= (uint32_t)(l & 0xff) << (8 * (k >> 1));
+  }
+  sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+  sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+  if (live) {
+    const int kb = u >> 4, t = (u >> 2) & 3, i = u & 3;
+    unsigned char *base = xq + (size_t)kb * 256 + t * 64 + i * 8;
+    *reinterpret_cast<uint2 *>(base) = make_uint2(hb[0], hb[1]);
+    *reinterpret_cast<uint2 *>(base + 32) = make_uint2(lb[0], lb[1]);
+    if (i == 0) meta[u >> 2] = make_uint2(dead ? 0u : (e - 17u) << 23, (uint32_t)(128 * sum));
+  }
+}
+
+// Quantises x (bf16, global) to block integers in MMA order.  Called by all threads of the CTA (a multiple of 32).
 __device__ __forceinline__ void stage_x_imma(const uint4 *x, const ImmaStage &st, int cols, int tid, int nthreads) {
   const int units = cols / 8;
   for (int u0 = 0; u0 < units; u0 += nthreads) {
     const int u = u0 + tid;
     const bool live = u < units;  // units is a multiple of 4, so a group's four lanes are live together
-    const uint4 v = live ? x[u] : make_uint4(0, 0, 0, 0);
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-    // biased exponent of the largest magnitude in the unit, then in the group
-    uint32_t e = 0;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      e = max(e, (w[k] >> 7) & 0xffu);
-      e = max(e, (w[k] >> 23) & 0xffu);
-    }
-    e = max(e, __shfl_xor_sync(0xffffffffu, e, 1));
-    e = max(e, __shfl_xor_sync(0xffffffffu, e, 2));
-    // groups whose values are all below 2^-109 (or zero) contribute nothing; a NaN/Inf exponent is clamped
-    const bool dead = e < 20u;
-    e = min(e, 254u);
-    const float up = __uint_as_float((267u - e) << 23);  // 2^(13 - (e - 127)) = 2^(140 - e)
-    int sum = 0;
-    uint32_t hb[2] = {0, 0}, lb[2] = {0, 0};  // [parity of the column] four bytes each
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const float xv = (k & 1) ? bf16hi(w[k >> 1]) : bf16lo(w[k >> 1]);
-      int X = dead ? 0 : __float2int_rn(xv * up);
-      X = max(-16383, min(16383, X));
-      sum += X;
-      const int h = (X + 128) >> 8;
-      const int l = X - (h << 8);
-      hb[k & 1] |= (uint32_t)(h & 0xff) << (8 * (k >> 1));
-      lb[k & 1] |= (uint32_t)(l & 0xff) << (8 * (k >> 1));
-    }
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    if (live) {
-      const int kb = u >> 4, t = (u >> 2) & 3, i = u & 3;
-      unsigned char *base = st.xq + (size_t)kb * 256 + t * 64 + i * 8;
-      *reinterpret_cast<uint2 *>(base) = make_uint2(hb[0], hb[1]);
-      *reinterpret_cast<uint2 *>(base + 32) = make_uint2(lb[0], lb[1]);
-      if (i == 0) st.meta[u >> 2] = make_uint2(dead ? 0u : (e - 17u) << 23, (uint32_t)(128 * sum));
-    }
+    imma_stage_unit(live ? x[u] : make_uint4(0, 0, 0, 0), u, live, st.xq, st.meta);
   }
   for (int u = tid; u < 8; u += nthreads) st.zero[u] = make_uint4(0, 0, 0, 0);
 }

@@ -42,6 +42,7 @@
 
 #include "bf16_mma.cuh"
 #include "i4_mma.cuh"
+#include "i4_imma.cuh"
 #include "moe_layer.h"
 #include "router_topk.cuh"
 
@@ -61,6 +62,14 @@ namespace blok {
 #endif
 constexpr int kC1Blocks = BLOK_FUSED_C1_BLOCKS;
 static_assert(kC1Blocks == 1 || kC1Blocks == 2 || kC1Blocks == 4, "BLOK_FUSED_C1_BLOCKS must be 1, 2 or 4");
+
+// 1: the routed experts' INT4 weights go through the integer tensor-core consumer of i4_imma.cuh (nibbles as bytes,
+// block-integer activations) instead of the bf16-operand one.  0 is the measured configuration.
+#ifndef BLOK_FUSED_I4_IMMA
+#define BLOK_FUSED_I4_IMMA 0
+#endif
+static_assert(!(BLOK_FUSED_I4_IMMA && BLOK_FUSED_C1_BLOCKS > 1), "the integer consumer is written for one row-block per down chunk");
+constexpr int kMetaBytes = BLOK_FUSED_I4_IMMA ? 8 : 4;  // per scale group: (factor, offset) or the plain sum
 
 constexpr int kFusedWarps = BLOK_FUSED_WARPS;
 constexpr int kFusedThreads = kFusedWarps * 32;
@@ -254,6 +263,9 @@ __device__ __forceinline__ float ring_consume(const Chunk &ch, uint32_t ring, co
   const bool hi_row = (t >> 1) != 0;
   const int j0 = 2 * (t & 1);
   float acc = 0.f;
+#if BLOK_FUSED_I4_IMMA
+  float acc2 = 0.f;  // the lane's high row (acc is its low row): every lane sums its own scale group of both rows
+#endif
   float d[4] = {0.f, 0.f, 0.f, 0.f};
   const bool i4 = kind_is_i4(ch.kind);
   for (int s = 0; s < ch.n; ++s) {
@@ -270,6 +282,25 @@ __device__ __forceinline__ float ring_consume(const Chunk &ch, uint32_t ring, co
       blk = c1_block_of(ch, s);
       kx = s - blk * ch.spr1;  // every row-block runs over the whole staged mid vector
     }
+#endif
+#if BLOK_FUSED_I4_IMMA
+    if (i4) {
+      // the lane's scale word holds groups (j0, j0 + 1) of one of its two rows; group t of the low row is with quad
+      // lane t >> 1, of the high row with quad lane 2 + (t >> 1), in half t & 1
+      const uint32_t sc = *reinterpret_cast<const uint32_t *>(slotp + 1024 + lane * 4);
+      const uint32_t sw_lo = __shfl_sync(0xffffffffu, sc, (lane & ~3) + (t >> 1));
+      const uint32_t sw_hi = __shfl_sync(0xffffffffu, sc, (lane & ~3) + 2 + (t >> 1));
+      int di[4] = {0, 0, 0, 0};
+      imma_kblock(wl, wh, xl.ptr + kx * xl.kb_stride, di);
+      imma_post(di, reinterpret_cast<const uint2 *>(xsum)[kx * 4 + t], (t & 1) ? bf16hi(sw_lo) : bf16lo(sw_lo),
+                (t & 1) ? bf16hi(sw_hi) : bf16lo(sw_hi), acc, acc2);
+    } else {
+      const uint4 xb = xrow[kx * 4];
+      mma_bf16_16816(d, wl.x, wh.x, wl.y, wh.y, xb.x, xb.y);
+      mma_bf16_16816(d, wl.z, wh.z, wl.w, wh.w, xb.z, xb.w);
+    }
+    ring_issue(ch, s + kRingDepth, ring, lane);
+    continue;
 #endif
     if (i4) {
       const uint32_t sc = *reinterpret_cast<const uint32_t *>(slotp + 1024 + lane * 4);
@@ -296,10 +327,20 @@ __device__ __forceinline__ float ring_consume(const Chunk &ch, uint32_t ring, co
     }
     ring_issue(ch, s + kRingDepth, ring, lane);
   }
+#if BLOK_FUSED_I4_IMMA
+  if (i4) {  // a row's four groups sit in the four lanes of its quad; callers read row g from t = 0, row g + 8 from t = 2
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    acc2 += __shfl_xor_sync(0xffffffffu, acc2, 1);
+    acc2 += __shfl_xor_sync(0xffffffffu, acc2, 2);
+    return (t & 2) ? acc2 : acc;
+  }
+#else
   if (i4) {
     acc += __shfl_xor_sync(0xffffffffu, acc, 1);
     return acc;
   }
+#endif
   return (t & 2) ? d[2] : d[0];
 }
 
@@ -358,6 +399,10 @@ __device__ __noinline__ void warp_stage_i4(const uint2 *src, uint4 *xfrag, float
       const int u = u0 + 32 * j;
       if (u < units) {  // units is a multiple of 32, so this is warp-uniform
         const uint4 v = vv[j];
+#if BLOK_FUSED_I4_IMMA
+        imma_stage_unit(v, u, true, reinterpret_cast<unsigned char *>(xfrag), reinterpret_cast<uint2 *>(xsum));
+        continue;
+#endif
         int kb = u >> 4, t = (u >> 2) & 3, i = u & 3;
         uint4 o;
         o.x = __byte_perm(v.x, v.z, 0x5410);
@@ -391,11 +436,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
   // half of the banks than the fragment words the supplying lanes read in the same 8-lane phase
   uint4 *zero = reinterpret_cast<uint4 *>(sp);
   sp += 384;
-  float *xsum = reinterpret_cast<float *>(sp);
-  sp += (size_t)(p.hidden / 32) * 4;
+  float *xsum = reinterpret_cast<float *>(sp);  // per scale group: the sum of x, or (factor, offset) of the integer form
+  sp += (size_t)(p.hidden / 32) * kMetaBytes;
   unsigned char *ring_ptr = sp + (size_t)warp * kRingDepth * kRingStepBytes;  // this warp's weight ring
   sp += (size_t)kFusedWarps * kRingDepth * kRingStepBytes;
-  const size_t wstage_bytes = (size_t)p.inter * 2 + (size_t)(p.inter / 32) * 4;
+  const size_t wstage_bytes = (size_t)p.inter * 2 + (size_t)(p.inter / 32) * kMetaBytes;
   unsigned char *wstage = sp + (size_t)warp * wstage_bytes;  // this warp's private segment of mid
   sp += (size_t)kFusedWarps * wstage_bytes;
   int *w_ids = reinterpret_cast<int *>(sp);  // the CTA's copy of the routing
@@ -410,6 +455,27 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
 
   if (tid == 0) trace_cta(p, 0);
   for (int u = tid; u < p.hidden / 8; u += kFusedThreads) xnat[u] = reinterpret_cast<const uint4 *>(p.x)[u];
+#if BLOK_FUSED_I4_IMMA
+  {
+    ImmaStage st;
+    st.xq = reinterpret_cast<unsigned char *>(xfrag);
+    st.meta = reinterpret_cast<uint2 *>(xsum);
+    st.zero = zero;
+    stage_x_imma(reinterpret_cast<const uint4 *>(p.x), st, p.hidden, tid, kFusedThreads);
+    for (int u = 8 + tid; u < 24; u += kFusedThreads) zero[u] = make_uint4(0, 0, 0, 0);  // the bf16 kinds read further in
+  }
+  __syncthreads();
+  if (tid == 0) trace_cta(p, 1);
+
+  // integer form: lanes with (g >> 1) == t supply limb g & 1 of their own scale group (two uint4 per k-block)
+  const bool supply = ((g >> 1) == t);
+  XFragLane xl_x;
+  xl_x.ptr = supply ? reinterpret_cast<const uint4 *>(reinterpret_cast<unsigned char *>(xfrag) + t * 64 + (g & 1) * 32) : zero + 4 + (lane & 1);
+  xl_x.kb_stride = supply ? 16 : 0;
+  XFragLane xl_m;
+  xl_m.ptr = supply ? reinterpret_cast<const uint4 *>(wstage + t * 64 + (g & 1) * 32) : zero + 4 + (lane & 1);
+  xl_m.kb_stride = supply ? 16 : 0;
+#else
   {
     I4Stage st;
     st.xfrag = xfrag;
@@ -427,6 +493,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
   XFragLane xl_m;  // fragments of this warp's staged mid
   xl_m.ptr = supply ? reinterpret_cast<const uint4 *>(wstage) + t : zero + 4 + t;
   xl_m.kb_stride = supply ? 16 : 0;
+#endif
   float *msum = reinterpret_cast<float *>(wstage + (size_t)p.inter * 2);
 
   const unsigned epoch = p.ctrl[CTRL_EPOCH] + 1u;  // stable during the launch; the last CTA to leave bumps it
@@ -748,8 +815,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
 static int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 size_t fused_smem_bytes(const blok_moe_weights &w) {
-  return (size_t)w.hidden * 4 + 384 + (size_t)(w.hidden / 32) * 4 + (size_t)kFusedWarps * kRingDepth * kRingStepBytes +
-         (size_t)kFusedWarps * ((size_t)w.inter * 2 + (size_t)(w.inter / 32) * 4) + (size_t)kFusedWarps * 16 * 8 +
+  return (size_t)w.hidden * 4 + 384 + (size_t)(w.hidden / 32) * kMetaBytes + (size_t)kFusedWarps * kRingDepth * kRingStepBytes +
+         (size_t)kFusedWarps * ((size_t)w.inter * 2 + (size_t)(w.inter / 32) * kMetaBytes) + (size_t)kFusedWarps * 16 * 8 +
          (size_t)w.experts * 2 * sizeof(float);
 }
 

@@ -16,6 +16,7 @@ FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "--e
     (["-DBLOK_FUSED_C1_BLOCKS=2"], 0),
     (["-DBLOK_FUSED_C1_BLOCKS=4", "-DBLOK_I4_ACC_CHAINS=2"], 0),
     (["-DBLOK_FUSED_STAGE_UNITS=4", "-DBLOK_FUSED_COLLECT=8"], 400),   # these trade a few spilled registers per chunk
+    (["-DBLOK_FUSED_I4_IMMA=1"], 0),                            # the integer consumer for the routed experts
 ])
 def test_fused_kernel_variants_compile(tmp_path, defines, max_spill_bytes):
     out = str(tmp_path / "moe_fused.cubin")
