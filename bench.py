@@ -218,7 +218,10 @@ def other_workload(a, rank, world, device, steps, warmup):
         prompts = [torch.randint(0, 163840, (P,), device=device, dtype=torch.int32) for _ in range(4)]
 
         def run(i):
+            # reset clears the positions on the default stream: fence it against the prompt on the timing stream
+            torch.cuda.synchronize()
             model.reset()
+            torch.cuda.synchronize()
             model.prefill(prompts[i % 4])
         # per chunk and MoE layer: attention weights once per 8 tokens, the experts the chunk routes to once (at most
         # 64 x 8 distinct, capped at 384), router and shared expert once; the dense layer once per 5 tokens
