@@ -14,6 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libblok_b200.so")
 
 OK = 0
+ABI_VERSION = 2  # BLOK_ABI_VERSION of include/blok_b200.h: the layout of the structures mirrored below
 
 
 class BlokError(RuntimeError):
@@ -45,6 +46,9 @@ def load():
     if not os.path.exists(LIB_PATH):
         raise BlokError(-100, "%s is missing: run `python -m blok_b200.build` (there is no CPU fallback)" % LIB_PATH)
     lib = C.CDLL(LIB_PATH)
+    if lib.blok_abi_version() != ABI_VERSION:
+        raise BlokError(-100, "%s has ABI version %d, this front end needs %d: rebuild with `python -m blok_b200.build --force`"
+                        % (LIB_PATH, lib.blok_abi_version(), ABI_VERSION))
     lib.blok_last_error.restype = C.c_char_p
     lib.blok_kernel_launch_count.restype = C.c_longlong
     for name in ("blok_expert_ffn_workspace_bytes", "blok_bf16_mlp_workspace_bytes", "blok_router_workspace_bytes"):

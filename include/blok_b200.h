@@ -44,7 +44,8 @@ enum {
   BLOK_ERR_ROUTE = -7        /* routed expert id not held by this rank / capacity exceeded */
 };
 
-#define BLOK_ABI_VERSION 1
+/* 2: blok_model_config gained prefill_chunk, kv_page_rows and kv_pages (appended). */
+#define BLOK_ABI_VERSION 2
 
 /* Message of the last failure on this thread ("" if none). */
 const char *blok_last_error(void);

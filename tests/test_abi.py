@@ -32,7 +32,7 @@ def test_header_symbols_exported(lib):
 
 
 def test_version_and_error_string(lib):
-    assert lib.blok_abi_version() == 1
+    assert lib.blok_abi_version() == 2
     lib.blok_last_error.restype = C.c_char_p
     rc = lib.blok_i4_dequant(None, None, None, 1, 32, None)
     assert rc == -1
