@@ -59,7 +59,7 @@ def build(force=False, verbose_ptxas=False):
     objs = [r[0] for r in results]
     log = "".join(r[1] for r in results)
     if force or not os.path.exists(OUT) or any(os.path.getmtime(o) > os.path.getmtime(OUT) for o in objs):
-        cmd = ["nvcc", "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", OUT] + objs + ["-lcudart"]
+        cmd = ["nvcc", "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", OUT] + objs + ["-lcudart", "-ldl"]
         subprocess.check_call(cmd)
     cli_src = os.path.join(HERE, "cli", "blok_kimi_exec.cpp")
     if os.path.exists(cli_src) and (force or not os.path.exists(CLI) or os.path.getmtime(cli_src) > os.path.getmtime(CLI)

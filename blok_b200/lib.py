@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libblok_b200.so")
 
 OK = 0
-ABI_VERSION = 2  # BLOK_ABI_VERSION of include/blok_b200.h: the layout of the structures mirrored below
+ABI_VERSION = 3  # BLOK_ABI_VERSION of include/blok_b200.h: the layout of the structures mirrored below
 
 
 class BlokError(RuntimeError):
@@ -316,6 +316,114 @@ class MoeLayer:
             _check(load().blok_moe_decode_host(self._handle, C.c_void_p(x_host.data_ptr()), C.c_void_p(y_host.data_ptr()),
                                                _stream()))
         return y_host
+
+
+def _moe_weights_struct(w, topk, routed_scale, expert_base):
+    E, H = w["router_w"].shape
+    n, I = w["gate_w"].shape[0], w["gate_w"].shape[1]
+    S = w["shared_gate"].shape[0] if w.get("shared_gate") is not None else 0
+    return MoeWeights(
+        hidden=H, inter=I, experts=E, topk=topk, shared_inter=S, routed_scale=routed_scale,
+        router_w=_ptr(w["router_w"], torch.bfloat16, "router_w").value,
+        router_bias=_ptr(w["router_bias"], torch.float32, "router_bias").value,
+        expert_base=expert_base, experts_local=n,
+        gate_w=_ptr(w["gate_w"], torch.int32, "gate_w").value, gate_s=_ptr(w["gate_s"], torch.bfloat16, "gate_s").value,
+        up_w=_ptr(w["up_w"], torch.int32, "up_w").value, up_s=_ptr(w["up_s"], torch.bfloat16, "up_s").value,
+        down_w=_ptr(w["down_w"], torch.int32, "down_w").value, down_s=_ptr(w["down_s"], torch.bfloat16, "down_s").value,
+        shared_gate=_ptr(w.get("shared_gate"), torch.bfloat16).value,
+        shared_up=_ptr(w.get("shared_up"), torch.bfloat16).value,
+        shared_down=_ptr(w.get("shared_down"), torch.bfloat16).value,
+    )
+
+
+COMM_ID_BYTES = 128
+
+
+def comm_unique_id():
+    """128 bytes that one rank creates and every rank passes to Comm (blok_comm_unique_id)."""
+    buf = C.create_string_buffer(COMM_ID_BYTES)
+    _check(load().blok_comm_unique_id(buf))
+    return bytes(buf.raw)
+
+
+class Comm:
+    """The library's communicator (blok_comm_*): one per process, on the current CUDA device.  With `group` (or an
+    initialised torch.distributed default group) rank 0 creates the id and broadcasts it over that group; the
+    communicator itself is the library's own (NCCL resolved inside the library)."""
+
+    def __init__(self, rank=None, world=None, unique_id=None, group=None):
+        import torch.distributed as dist
+        if rank is None:
+            rank = dist.get_rank(group) if dist.is_initialized() else 0
+            world = dist.get_world_size(group) if dist.is_initialized() else 1
+        if world > 1 and unique_id is None:
+            holder = [comm_unique_id() if rank == 0 else None]
+            dist.broadcast_object_list(holder, src=0, group=group)
+            unique_id = holder[0]
+        self.rank, self.world = rank, world
+        self._handle = C.c_void_p()
+        idbuf = C.create_string_buffer(unique_id, COMM_ID_BYTES) if unique_id is not None else None
+        _check(load().blok_comm_create(idbuf, C.c_int(rank), C.c_int(world), C.byref(self._handle)))
+
+    def close(self):
+        if getattr(self, "_handle", None) is not None and self._handle.value:
+            load().blok_comm_destroy(self._handle)
+            self._handle = C.c_void_p()
+
+    def check(self):
+        _check(load().blok_comm_check(self._handle))
+
+    def all_reduce_(self, t):
+        """In-place sum over the ranks of a float32 CUDA tensor."""
+        _check(load().blok_comm_all_reduce_f32(self._handle, _ptr(t, torch.float32), C.c_long(t.numel()), _stream()))
+        return t
+
+    def broadcast_(self, t, root=0):
+        _check(load().blok_comm_broadcast(self._handle, _ptr(t), C.c_long(t.numel() * t.element_size()), C.c_int(root), _stream()))
+        return t
+
+
+class MoeEp:
+    """The expert-parallel batched layer (blok_moe_ep_*).  `weights` as for MoeLayer, the expert arrays holding this
+    rank's experts [experts / world, ...] only; router and shared expert replicated."""
+
+    def __init__(self, comm, weights, topk=8, routed_scale=2.827, max_tokens=256):
+        self.comm, self.weights = comm, dict(weights)
+        E, H = weights["router_w"].shape
+        per = E // comm.world
+        self.hidden, self.topk, self.experts, self.max_tokens = H, topk, E, max_tokens
+        mw = _moe_weights_struct(self.weights, topk, routed_scale, comm.rank * per)
+        self._handle = C.c_void_p()
+        self.device = weights["router_w"].device
+        with torch.cuda.device(self.device):
+            _check(load().blok_moe_ep_create(comm._handle, C.byref(mw), C.c_int(max_tokens), C.byref(self._handle)))
+
+    def close(self):
+        if getattr(self, "_handle", None) is not None and self._handle.value:
+            load().blok_moe_ep_destroy(self._handle)
+            self._handle = C.c_void_p()
+
+    def forward(self, x, out=None, return_routing=False):
+        """x bf16 [T, hidden] (this rank's tokens) -> y bf16 [T, hidden]; every rank calls it once per pass."""
+        T = x.shape[0]
+        y = torch.empty((T, self.hidden), dtype=torch.bfloat16, device=x.device) if out is None else out
+        ids = wts = None
+        if return_routing:
+            ids = torch.empty((T, self.topk), dtype=torch.int16, device=x.device)
+            wts = torch.empty((T, self.topk), dtype=torch.float32, device=x.device)
+        _check(load().blok_moe_ep_forward(self._handle, _ptr(x, torch.bfloat16, "x"), C.c_int(T), _ptr(y, torch.bfloat16), _ptr(ids),
+                                          _ptr(wts), _stream()))
+        return (y, ids, wts) if return_routing else y
+
+    def check(self):
+        _check(load().blok_moe_ep_check(self._handle, _stream()))
+
+    def stats(self):
+        """After a pass: assignments sent, of those to other ranks, rows received, GEMM tiles (synchronises)."""
+        out = (C.c_longlong * 4)()
+        _check(load().blok_moe_ep_stats(self._handle, out, _stream()))
+        return dict(assignments=out[0], remote=out[1], received=out[2], tiles=out[3],
+                    bytes_each_way=out[1] * self.hidden * 2)
 
 
 def lm_head_argmax(w, n):

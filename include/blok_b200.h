@@ -41,11 +41,13 @@ enum {
   BLOK_ERR_STATE = -4,       /* handle misuse */
   BLOK_ERR_TIMEOUT = -5,     /* a bounded device-side wait gave up */
   BLOK_ERR_WORKSPACE = -6,   /* workspace too small */
-  BLOK_ERR_ROUTE = -7        /* routed expert id not held by this rank / capacity exceeded */
+  BLOK_ERR_ROUTE = -7,       /* routed expert id not held by this rank / capacity exceeded */
+  BLOK_ERR_COMM = -8         /* NCCL missing or failed; a peer's memory could not be mapped */
 };
 
-/* 2: blok_model_config gained prefill_chunk, kv_page_rows and kv_pages (appended). */
-#define BLOK_ABI_VERSION 2
+/* 2: blok_model_config gained prefill_chunk, kv_page_rows and kv_pages (appended).
+ * 3: blok_comm_*, blok_moe_ep_*, blok_model_set_comm; blok_model_config gained ep_rank and ep_world (appended). */
+#define BLOK_ABI_VERSION 3
 
 /* Message of the last failure on this thread ("" if none). */
 const char *blok_last_error(void);
@@ -249,6 +251,54 @@ int blok_moe_layer_trace(blok_moe_layer_t *layer, long long *host_out, int max_e
  * makes the two copies asynchronous with respect to the host. */
 int blok_moe_decode_host(blok_moe_layer_t *layer, const blok_bf16_t *x_host, blok_bf16_t *y_host,
                          blok_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* Expert parallelism (config 2 at 2/4/8 GPUs; the model of config 4)          */
+/* ------------------------------------------------------------------------- */
+
+/* The reference runs on one GPU and has no collective (src/kimi_exec.cu has no multi-GPU code), so nothing in this
+ * section replaces a reference function; per token the arithmetic is still :836-877.  One process per GPU; expert e
+ * lives on rank e / (experts / world). */
+typedef struct blok_comm blok_comm_t;
+#define BLOK_COMM_ID_BYTES 128
+/* HOST: fills id_out (BLOK_COMM_ID_BYTES bytes) with a fresh NCCL unique id.  One rank calls it and hands the bytes to
+ * the others by whatever means the launcher offers (a file, an environment, a torch.distributed broadcast). */
+int blok_comm_unique_id(void *id_out);
+/* Collective over all `world` ranks: joins the communicator on the CURRENT device.  NCCL is resolved at run time
+ * (dlopen of libnccl.so.2, or the path in BLOK_NCCL_LIB), so single-GPU users of the library need none. world == 1
+ * needs no id and no NCCL.  BLOK_ERR_COMM when NCCL is missing or refuses. */
+int blok_comm_create(const void *unique_id, int rank, int world, blok_comm_t **out);
+int blok_comm_destroy(blok_comm_t *comm);
+int blok_comm_rank(const blok_comm_t *comm);
+int blok_comm_world(const blok_comm_t *comm);
+/* BLOK_ERR_COMM if NCCL has reported an asynchronous error on the communicator (a peer that died, a deadline). */
+int blok_comm_check(blok_comm_t *comm);
+/* In-place sum over the ranks of n floats on the device, and a broadcast of bytes from `root`: the two collectives
+ * the sharded model needs (one all-reduce per MoE layer at batch 1). */
+int blok_comm_all_reduce_f32(blok_comm_t *comm, float *buf, long n, blok_stream_t stream);
+int blok_comm_broadcast(blok_comm_t *comm, void *buf, long bytes, int root, blok_stream_t stream);
+
+/* The batched layer (blok_moe_batched) with the experts split over the ranks.  `weights` describes THIS rank's shard:
+ * experts_local = experts / world, expert_base = rank * experts_local, the expert arrays holding only those experts;
+ * router and shared expert are replicated.  max_tokens bounds the tokens a rank brings to one pass.
+ * Collective: every rank creates its handle at the same point (the ranks map one another's receive buffers:
+ * world * max_tokens * topk rows of hidden bf16, twice, per rank). */
+typedef struct blok_moe_ep blok_moe_ep_t;
+int blok_moe_ep_create(blok_comm_t *comm, const blok_moe_weights *weights, int max_tokens, blok_moe_ep_t **out);
+int blok_moe_ep_destroy(blok_moe_ep_t *ep);
+/* One pass; every rank must call it the same number of times (T may differ per rank and may be 0).  x, y bf16
+ * [T, hidden] are this rank's tokens; ids_out uint16 [T, topk] (global expert ids) and wts_out fp32 [T, topk] may be
+ * NULL.  Dispatch and combine run inside the library's kernels over peer memory (plain stores and loads over NVLink,
+ * flags that carry the pass number); nothing synchronises with the host.  y[t] = bf16(bf16(sum_k w_k expert_k(x[t]))
+ * + shared(x[t])), slot order as :868-871, :684. */
+int blok_moe_ep_forward(blok_moe_ep_t *ep, const blok_bf16_t *x, int T, blok_bf16_t *y, uint16_t *ids_out, float *wts_out,
+                        blok_stream_t stream);
+/* Synchronises `stream`; BLOK_ERR_TIMEOUT if a bounded wait for a peer gave up in an earlier pass (the message says
+ * which), BLOK_ERR_ROUTE if more rows arrived than the receive buffer holds, BLOK_ERR_COMM for an NCCL error. */
+int blok_moe_ep_check(blok_moe_ep_t *ep, blok_stream_t stream);
+/* HOST out[4] after synchronising `stream`, for the last pass: assignments this rank sent, of those to other ranks,
+ * rows this rank received, tiles its grouped GEMM ran. */
+int blok_moe_ep_stats(blok_moe_ep_t *ep, long long *host_out4, blok_stream_t stream);
 
 /* ------------------------------------------------------------------------- */
 /* A8-A10  MLA decode attention (config 3)                                    */

@@ -32,7 +32,7 @@ def test_header_symbols_exported(lib):
 
 
 def test_version_and_error_string(lib):
-    assert lib.blok_abi_version() == 2
+    assert lib.blok_abi_version() == 3
     lib.blok_last_error.restype = C.c_char_p
     rc = lib.blok_i4_dequant(None, None, None, 1, 32, None)
     assert rc == -1
@@ -52,6 +52,13 @@ def test_argument_validation_needs_no_gpu(lib):
     out = C.c_void_p()
     assert lib.blok_moe_layer_create(None, 1, C.byref(out)) == -1
     assert lib.blok_moe_layer_destroy(None) == 0
+    # expert parallelism: argument errors come before NCCL or a device is touched
+    assert lib.blok_comm_unique_id(None) == -1
+    assert lib.blok_comm_create(None, 2, 2, C.byref(out)) == -1        # rank outside the world
+    assert lib.blok_comm_create(None, 0, 2, C.byref(out)) == -1        # more than one rank needs an id
+    assert lib.blok_comm_destroy(None) == 0
+    assert lib.blok_moe_ep_create(None, None, 8, C.byref(out)) == -1
+    assert lib.blok_moe_ep_destroy(None) == 0
     # zero-sized work is a no-op, not an error
     assert lib.blok_i4_gemv(p, p, p, p, 0, 64, None) == 0
     assert lib.blok_add_bf16(p, p, C.c_long(0), None) == 0

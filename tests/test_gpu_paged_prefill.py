@@ -347,29 +347,3 @@ def test_cli_prefill_chunk_flag_runs_the_prompt_in_chunks():
     assert 1 <= len(b) <= 3 and all(0 <= t < 4096 for t in b) and len(a) == len(b)
     p = run(exe, *args, "--prefill-chunk", "65")
     assert p.returncode == 1 and "unsupported configuration" in p.stderr
-
-
-# ---- the integer tensor-core consumer of the INT4 mat-vec (BLOK_I4_GEMV_IMPL=imma), against the oracle ----
-
-@pytest.mark.parametrize("rows,cols", [(16, 128), (64, 7168), (2048, 7168), (7168, 2048), (48, 384)])
-def test_i4_gemv_integer_path(cuda, oracle, monkeypatch, rows, cols):
-    from blok_b200 import lib
-    from test_gpu_i4 import _dev_i4
-    rng = np.random.default_rng(rows * 5 + cols)
-    w, s, dw, ds = _dev_i4(rng, rows, cols, cuda)
-    x = oracle.bf16_round(rng.normal(size=cols).astype(np.float32))
-    xd = torch.from_numpy(x).to(cuda).bfloat16()
-    base = util.t2np_f32(lib.i4_gemv(dw, ds, xd))
-    monkeypatch.setenv("BLOK_I4_GEMV_IMPL", "imma")
-    y = util.t2np_f32(lib.i4_gemv(dw, ds, xd))
-    monkeypatch.delenv("BLOK_I4_GEMV_IMPL")
-    wide = oracle.i4_gemv(w, s, x, mode=0, round_out=True)
-    util.assert_close(y, wide, "integer-path i4_gemv %dx%d" % (rows, cols))
-    util.assert_close(y, base, "integer path vs the bf16-operand path")
-    # both are bf16 roundings of nearly the same sum: a step of the last place at most, equal almost everywhere
-    assert np.all(np.abs(y - base) <= np.maximum(np.abs(base), 1e-30) * 2.0 ** -7)
-    assert np.mean(y == base) > 0.8
-    # zero in, zero out; scaling the input by a power of two scales the output exactly
-    monkeypatch.setenv("BLOK_I4_GEMV_IMPL", "imma")
-    assert torch.count_nonzero(lib.i4_gemv(dw, ds, torch.zeros_like(xd))) == 0
-    assert torch.equal(lib.i4_gemv(dw, ds, xd * 8).float(), lib.i4_gemv(dw, ds, xd).float() * 8)
