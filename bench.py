@@ -35,7 +35,9 @@ sys.path.insert(0, ROOT)
 METRIC = "decode tok/s, INT4 MoE layer (batch 1)"
 WORKLOAD = "config 1: routed-MoE decode layer, batch 1, 384 INT4 experts top-8 + bf16 shared expert, hidden 7168"
 HBM_FALLBACK_GBS = 6650.0
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 292.6e6  # 287.5 MB read + 5.1 MB written (profiles/moe_decode_fused_config1.md)
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the decode kernel (ncu capture of a 64-expert layer; a
+# launch reads 8 experts whatever the expert count): 287.5 MB read + 5.1 MB written
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 292.6e6
 
 
 def measured_peak():
@@ -146,6 +148,15 @@ def oracle_layer_token(orc, h, x_f32):
     return out
 
 
+def decode_config(world, n_layers, pool, experts=384):
+    """The `config` object of the headline line; both arms print the same one."""
+    from blok_b200 import synth
+    return {"workload": WORKLOAD if experts == 384 else "REDUCED CASE (%d experts, profiler capture size) of " % experts + WORKLOAD,
+            "parallelism": "1 GPU" if world == 1 else "replicas x%d" % world,
+            "l2": "rotating %d distinct layers and %d tokens; a step's 292 MB were last read > L2 capacity ago" % (n_layers, pool),
+            "algorithmic_bytes_per_step": synth.moe_layer_bytes()}
+
+
 def cpu_arm(steps, warmup, device):
     """Times the reference arithmetic (oracle port, all host threads) on `steps` layer-tokens of config 1."""
     import numpy as np
@@ -172,11 +183,133 @@ def cpu_arm(steps, warmup, device):
     return steps / dt, dt, orc.num_threads()
 
 
+def ep_parity_check(rank, world, device, comm):
+    """A reduced layer through the expert-parallel path on every rank against the single-GPU batched layer on the rank's
+    own tokens, with one GEMM implementation forced at a time (the same kernel then computes every row on both sides):
+    the outputs must be bit-equal.  Returns (ok on every rank, worst absolute difference over the ranks)."""
+    import torch
+    import torch.distributed as dist
+    from blok_b200 import lib, synth
+    hidden, inter, experts, shared = 1024, 512, 128, 512
+    w = synth.moe_layer_weights(device, seed=77, hidden=hidden, inter=inter, experts=experts, shared_inter=shared)
+    for k in ("gate_s", "up_s", "down_s"):
+        w[k] = (w[k].float() * 8).bfloat16()
+    w["router_w"] = (w["router_w"].float() * 20).bfloat16()
+    per = experts // world
+    shard = dict(w)
+    for k in ("gate_w", "gate_s", "up_w", "up_s", "down_w", "down_s"):
+        shard[k] = w[k][rank * per:(rank + 1) * per].contiguous()
+    layer = lib.MoeEp(comm, shard, max_tokens=64)
+    full = lib.MoeLayer(w, max_tokens=64)
+    ok, worst = True, 0.0
+    old = os.environ.get("BLOK_WGEMM_IMPL")
+    for step, impl in enumerate(("mma", "tc")):
+        os.environ["BLOK_WGEMM_IMPL"] = impl
+        x = synth.activations(24 + 5 * rank, hidden, device, 900 + rank + 10 * step)
+        y, ids, wts = layer.forward(x, return_routing=True)
+        layer.check()
+        ref, rid, rw = full.batched(x, return_routing=True)
+        ok = ok and torch.equal(ids, rid) and torch.equal(wts, rw) and torch.equal(y, ref)
+        worst = max(worst, float((y.float() - ref.float()).abs().max()))
+    if old is None:
+        del os.environ["BLOK_WGEMM_IMPL"]
+    else:
+        os.environ["BLOK_WGEMM_IMPL"] = old
+    flag = torch.tensor([0.0 if ok else 1.0, worst], device=device)
+    if world > 1:
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    layer.close()
+    full.close()
+    return float(flag[0]) == 0.0, float(flag[1])
+
+
+def ep_measure(T, rank, world, device, comm, steps, warmup, experts=384):
+    """Config 2 at T tokens with the experts split over the ranks (blok_moe_ep_*): per-pass device time (max over the
+    ranks), this rank-set's roofline figures (the slowest rank's bytes), the exchange volume and the phase times."""
+    import torch
+    import torch.distributed as dist
+    from blok_b200 import lib, synth
+    Tl = T // world
+    per = experts // world
+    nl = 2 if experts == 384 else 1
+    reps = []
+    for i in range(nl):
+        w = synth.moe_layer_weights(device, seed=2 + 31 * i, experts=experts)
+        if world > 1:
+            for k in ("gate_w", "gate_s", "up_w", "up_s", "down_w", "down_s"):
+                w[k] = w[k][rank * per:(rank + 1) * per].contiguous()
+            torch.cuda.empty_cache()
+        reps.append(lib.MoeEp(comm, w, max_tokens=max(Tl, 1)))
+    xs = [synth.activations(Tl, 7168, device, 2 + 7 * i + rank) for i in range(4)]
+    outs = torch.empty((Tl, 7168), dtype=torch.bfloat16, device=device)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for i in range(max(warmup, 3)):
+            reps[i % nl].forward(xs[i % 4], out=outs)
+        barrier()
+        l0 = lib.kernel_launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            reps[i % nl].forward(xs[i % 4], out=outs)
+        e1.record()
+        barrier()
+        launches = lib.kernel_launch_count() - l0
+        for r in reps:
+            r.check()
+        # one more pass of layer 0 on input 0 with the phase events on, and its routing for the byte counts
+        reps[0].profile(True)
+        _, ids, _ = reps[0].forward(xs[0], out=outs, return_routing=True)
+        phases = reps[0].phase_ms()
+        stats = reps[0].stats()
+        reps[0].profile(False)
+        torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+    # distinct experts of THIS rank that the whole batch routes to (every rank's ids gathered)
+    ids32 = (ids.view(torch.int16).to(torch.int32) & 0xFFFF).contiguous()      # NCCL carries no 16-bit integers
+    ids_all = [torch.empty_like(ids32) for _ in range(world)] if world > 1 else [ids32]
+    if world > 1:
+        dist.all_gather(ids_all, ids32)
+    flat = torch.cat([t.long().view(-1) for t in ids_all])
+    mine = flat[(flat >= rank * per) & (flat < (rank + 1) * per)].unique()
+    fig = torch.tensor([float(mine.numel()), float(stats["received"]), float(stats["remote"]), phases["route"], phases["dispatch"],
+                        phases["shared"], phases["wait_rows"], phases["experts"], phases["combine"]], device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(fig, op=dist.ReduceOp.MAX)
+    per_step = float(ms.item()) / steps
+    distinct, received, remote = int(fig[0]), int(fig[1]), int(fig[2])
+    alg = distinct * 24772608 + 5505024 + 88080384 + 4 * Tl * 7168 + 2 * received * 7168 * 2   # the busiest rank
+    flops = 2.0 * (received * 3 * 7168 * 2048 + Tl * (3 * 7168 * 2048 + 7168 * experts))
+    peak, peak_kind = measured_peak()
+    rec = {"T": T, "parallelism": "expert parallel x%d" % world if world > 1 else "1 GPU, through the same exchange kernels",
+           "ms_per_pass": per_step, "tok_per_s": T / (per_step * 1e-3),
+           "experts_per_gpu": per, "distinct_experts_busiest_gpu": distinct, "rows_received_busiest_gpu": received,
+           "remote_assignments_busiest_gpu": remote, "exchange_bytes_each_way_busiest_gpu": remote * 7168 * 2,
+           "roofline": {"bound": "hbm", "achieved": alg / (per_step * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                        "frac": alg / (per_step * 1e-3) / 1e9 / peak, "peak_kind": peak_kind, "bytes_busiest_gpu": alg},
+           "phase_ms_max_over_ranks": {k: float(fig[3 + i]) for i, k in enumerate(("route", "dispatch", "shared", "wait_rows",
+                                                                                  "experts", "combine"))},
+           "launches_per_pass": launches / steps, **tensor_roofline(flops, per_step)}
+    for r in reps:
+        r.close()
+    del reps
+    torch.cuda.empty_cache()
+    return rec, launches
+
+
 def other_workload(a, rank, world, device, steps, warmup):
     """Configs 2 and 3 through the same timing rules (CUDA events, barrier both sides, max over ranks)."""
     import torch
     import torch.distributed as dist
-    from blok_b200 import ep, lib, synth
+    from blok_b200 import lib, synth
 
     def barrier():
         torch.cuda.synchronize()
@@ -264,32 +397,41 @@ def other_workload(a, rank, world, device, steps, warmup):
         metric = "decode tok/s, %d-layer model (batch 1)" % L
     elif a.workload.startswith("batched"):
         T = int(a.workload[len("batched"):])
-        Tl = T // world
-        per = a.experts // world
-        # every rank draws the same layer and keeps its shard; two layers are rotated (2 x 9.5 GB / world per GPU)
+        if world > 1:
+            comm = lib.Comm()
+            ok, worst = ep_parity_check(rank, world, device, comm)
+            if not ok:
+                if rank == 0:
+                    print(json.dumps({"error": "expert-parallel parity check failed", "worst_abs_diff": worst}))
+                return 3
+            rec, launches = ep_measure(T, rank, world, device, comm, steps, warmup, a.experts)
+            if rank == 0:
+                print(json.dumps({
+                    "metric": "tok/s, INT4 MoE layer (T=%d)" % T, "value": rec["tok_per_s"], "unit": "tok/s", "n_gpus": world,
+                    "steps": steps, "warmup": warmup, "ms_per_step": rec["ms_per_pass"], "higher_is_better": True,
+                    "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                    "config": {"workload": "config 2: batched routed-MoE layer, T=%d tokens, expert parallel x%d (%d experts per "
+                                           "GPU), dispatch/combine in the library's kernels over NVLink peer memory" %
+                                           (T, world, a.experts // world),
+                               "l2": "two layers and four inputs rotated", "ep_parity": "bit-equal to the single-GPU layer"},
+                    "roofline": rec["roofline"], "roofline_tensor": rec.get("roofline_tensor"), "ep": rec,
+                    "gpu_launches": int(launches)}))
+            comm.close()
+            dist.destroy_process_group()
+            return 0
         nl = 2 if a.experts == 384 else 1  # a reduced case (profiler capture) holds one layer
-        shards, reps = [], []
-        for i in range(nl):
-            w = synth.moe_layer_weights(device, seed=2 + 31 * i, experts=a.experts)
-            if world > 1:
-                for k in ("gate_w", "gate_s", "up_w", "up_s", "down_w", "down_s"):
-                    w[k] = w[k][rank * per:(rank + 1) * per].contiguous()
-                torch.cuda.empty_cache()
-                reps.append(ep.gpu_layer(w, a.experts, max_tokens=max(Tl, 2)))
-            else:
-                reps.append(lib.MoeLayer(w, max_tokens=max(T, 2)))
-        xs = [synth.activations(Tl, 7168, device, 2 + 7 * i + rank) for i in range(4)]
-        run = (lambda i: reps[i % nl].forward(xs[i % 4])) if world > 1 else (lambda i: reps[i % nl].batched(xs[i % 4]))
-        ids = lib.router(reps[0].layer.weights["router_w"] if world > 1 else reps[0].weights["router_w"],
-                         reps[0].layer.weights["router_bias"] if world > 1 else reps[0].weights["router_bias"], xs[0])[0]
-        mine = (ids.view(torch.int16).long() & 0xFFFF).unique()
-        distinct = int(mine.numel())
-        alg = distinct * 24772608 / world + 5505024 + 88080384 + 4 * Tl * 7168  # per-GPU estimate, own tokens' routing
+        reps = [lib.MoeLayer(synth.moe_layer_weights(device, seed=2 + 31 * i, experts=a.experts), max_tokens=max(T, 2))
+                for i in range(nl)]
+        xs = [synth.activations(T, 7168, device, 2 + 7 * i + rank) for i in range(4)]
+        run = lambda i: reps[i % nl].batched(xs[i % 4])
+        ids = lib.router(reps[0].weights["router_w"], reps[0].weights["router_bias"], xs[0])[0]
+        distinct = int((ids.view(torch.int16).long() & 0xFFFF).unique().numel())
+        alg = distinct * 24772608 + 5505024 + 88080384 + 4 * T * 7168
         unit_tokens = T
-        # multiply-adds of the pass on this GPU: its share of the T x 8 assignments through three 7168 x 2048 matrices,
-        # its tokens through the shared expert and the router
-        flops = 2.0 * (T * 8 / world * 3 * 7168 * 2048 + Tl * (3 * 7168 * 2048 + 7168 * a.experts))
-        workload = "config 2: batched routed-MoE layer, T=%d tokens, %s" % (T, "1 GPU" if world == 1 else "expert parallel x%d, NCCL all-to-all" % world)
+        # multiply-adds of the pass: T x 8 assignments through three 7168 x 2048 matrices, the tokens through the shared
+        # expert and the router
+        flops = 2.0 * (T * 8 * 3 * 7168 * 2048 + T * (3 * 7168 * 2048 + 7168 * a.experts))
+        workload = "config 2: batched routed-MoE layer, T=%d tokens, 1 GPU" % T
         if a.experts != 384:
             workload = "REDUCED CASE (%d experts, profiler capture size) of " % a.experts + workload
         scaling = "strong"
@@ -398,8 +540,9 @@ def main():
         line = {"impl": "reference", "metric": METRIC, "value": rate, "unit": "tok/s", "n_gpus": a.gpus, "steps": steps,
                 "warmup": warmup, "ms_per_step": 1e3 / rate, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": WORKLOAD, "note": "reference arithmetic on host cores (oracle port); the reference's "
-                           "GPU executor needs its NVMe/uGDS storage stack and cannot run"},
+                "config": decode_config(a.gpus, a.layers, 64),
+                "note": "reference arithmetic on host cores (oracle port); the reference's GPU executor needs its NVMe/uGDS "
+                        "storage stack and cannot run",
                 "cpu_baseline": {"value": rate, "unit": "tok/s", "cores": threads, "kind": "port",
                                  "sample": "%d layer-tokens of config 1 (%.1f s)" % (steps_run, dt)},
                 "e2e": {"value": rate, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -434,11 +577,11 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
-    for i in range(max(warmup, 3)):
-        step(i)
     sampler = ClockSampler(local_rank)
     if rank == 0:
-        sampler.start()
+        sampler.start()      # before the warm-up, so that a short timed region still has samples under load
+    for i in range(max(warmup, 3)):
+        step(i)
     barrier()
     l0 = lib.kernel_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -472,6 +615,25 @@ def main():
         dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
     e2e_ms = float(e2e_ms.item())
 
+    # N > 1: the sharded path of the same layer type (config 2, expert parallel) measured in the same run
+    ep_rec = None
+    if world > 1:
+        for L in layers:
+            L.close()
+        del layers
+        torch.cuda.empty_cache()
+        comm = lib.Comm()
+        ok, worst = ep_parity_check(rank, world, device, comm)
+        if not ok:
+            if rank == 0:
+                print(json.dumps({"error": "expert-parallel parity check failed", "worst_abs_diff": worst}))
+            return 3
+        ep_rec = {"parity": "bit-equal to the single-GPU batched layer on every rank (reduced layer, both GEMM kernels)"}
+        for T in (2048, 64):
+            ep_rec["T%d" % T], _ = ep_measure(T, rank, world, device, comm, 20, 5)
+        comm.close()
+        layers = []
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -486,23 +648,18 @@ def main():
         "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD if a.experts == 384 else
-                   "REDUCED CASE (%d experts, profiler capture size) of " % a.experts + WORKLOAD,
-                   "parallelism": "1 GPU" if world == 1 else "replicas x%d" % world,
-                   "l2": "rotating %d distinct layers and %d tokens; a step's 292 MB were last read > L2 capacity ago"
-                         % (len(layers), pool),
-                   "algorithmic_bytes_per_step": alg_bytes},
+        "config": decode_config(world, a.layers, pool, a.experts),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": peak_kind, "frac_of_nominal_8TBs": achieved / 8000.0,
                      "kernel": "moe decode layer (%d launches per step)" % round(launches / steps),
-                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised
-                     # in profiles/moe_decode_fused_config1.md (a launch reads 8 experts whatever the expert count)
                      "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
         "e2e": {"value": world * e2e_steps / (e2e_ms / 1e3), "unit": "tok/s", "h2d_bytes_per_step": 7168 * 2,
                 "d2h_bytes_per_step": 7168 * 2, "ms_per_step": e2e_ms / e2e_steps},
         "gpu_launches": int(launches),
         "clocks": clocks,
     }
+    if ep_rec is not None:
+        line["ep"] = ep_rec
     if world == 1 and not a.no_cpu_baseline:
         for L in layers:
             L.close()

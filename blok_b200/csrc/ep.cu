@@ -433,6 +433,8 @@ struct blok_moe_ep {
   unsigned *done = nullptr, *err = nullptr;
   long long *stats = nullptr;
   unsigned epoch = 0;
+  bool profile = false;          // record an event between the phases of a pass
+  cudaEvent_t ev[7] = {};
 };
 
 // ---- communicator -------------------------------------------------------------------------------------------------------
@@ -515,6 +517,8 @@ extern "C" int blok_moe_ep_destroy(blok_moe_ep_t *ep) {
   if (!ep) return BLOK_OK;
   cudaDeviceSynchronize();
   if (ep->layer) blok_moe_layer_destroy(ep->layer);
+  for (cudaEvent_t e : ep->ev)
+    if (e) cudaEventDestroy(e);
   sym_free(&ep->sym);
   if (ep->d_peers) cudaFree(ep->d_peers);
   if (ep->dws) cudaFree(ep->dws);
@@ -590,6 +594,10 @@ extern "C" int blok_moe_ep_forward(blok_moe_ep_t *ep, const blok_bf16_t *x, int 
   p.err = ep->err; p.cursor = ep->cursor; p.send_base = ep->send_base; p.dst_rank = ep->dst_rank; p.dst_row = ep->dst_row;
   p.done = ep->done; p.stats = ep->stats;
 
+  auto mark = [&](int i) {
+    if (ep->profile) cudaEventRecord(ep->ev[i], stream);
+  };
+  mark(0);
   // 1. route this rank's tokens (fp32 logits, unrounded, :297; then the top-k kernel)
   if (T > 0) {
     if (w.experts % 128 == 0) {  // the same kernel as blok_moe_batched at every T, so that the two agree bit for bit
@@ -610,6 +618,7 @@ extern "C" int blok_moe_ep_forward(blok_moe_ep_t *ep, const blok_bf16_t *x, int 
     if ((rc = launch_router_topk(L->logits, w.router_bias, T, w.experts, w.topk, w.routed_scale, L->ids, L->wts, nullptr, 0, stream)))
       return rc;
   }
+  mark(1);
   // 2-4. counts to every rank, plan, rows to their owners
   ep_count_kernel<<<1, 1024, (size_t)w.experts * sizeof(int), stream>>>(p, L->ids, N);
   if ((rc = launch_status("ep_count_kernel"))) return rc;
@@ -619,15 +628,18 @@ extern "C" int blok_moe_ep_forward(blok_moe_ep_t *ep, const blok_bf16_t *x, int 
   if ((rc = launch_status("ep_plan_kernel"))) return rc;
   ep_dispatch_kernel<<<std::max(T, 1), 256, 0, stream>>>(p, x, L->ids, T);
   if ((rc = launch_status("ep_dispatch_kernel"))) return rc;
+  mark(2);
   // 5. the shared expert on the rank's own tokens while the rows travel
   const uint16_t *shared = nullptr;
   if (w.shared_inter > 0 && T > 0) {
     if ((rc = blok_moe_shared(L, x, T, L->b_sout, stream_))) return rc;
     shared = L->b_sout;
   }
+  mark(3);
   // 6. every source's rows are here -> grouped GEMM over the receive buffer -> tell every rank
   ep_wait_kernel<<<1, 64, 0, stream>>>(p, ep->reg.dflag, 30u);
   if ((rc = launch_status("ep_wait_kernel"))) return rc;
+  mark(4);
   {
     unsigned char *me = static_cast<unsigned char *>(ep->sym.local);
     const uint16_t *rx = reinterpret_cast<const uint16_t *>(me + ep->reg.recv_x);
@@ -644,6 +656,7 @@ extern "C" int blok_moe_ep_forward(blok_moe_ep_t *ep, const blok_bf16_t *x, int 
     d.x = L->b_mid; d.K = w.inter; d.R = w.hidden; d.out_bf16 = ry;
     if ((rc = launch_wgemm(WG_I4_PLAIN, d, max_tiles, stream))) return rc;
   }
+  mark(5);
   ep_signal_kernel<<<1, 64, 0, stream>>>(p, ep->reg.rflag);
   if ((rc = launch_status("ep_signal_kernel"))) return rc;
   // 7. combine (waits for every owner's flag)
@@ -657,6 +670,24 @@ extern "C" int blok_moe_ep_forward(blok_moe_ep_t *ep, const blok_bf16_t *x, int 
     ep_wait_kernel<<<1, 64, 0, stream>>>(p, ep->reg.rflag, 40u);
     if ((rc = launch_status("ep_wait_kernel"))) return rc;
   }
+  mark(6);
+  return BLOK_OK;
+}
+
+extern "C" int blok_moe_ep_profile(blok_moe_ep_t *ep, int on) {
+  BLOK_REQUIRE(ep, BLOK_ERR_ARG, "blok_moe_ep_profile: null handle");
+  if (on)
+    for (cudaEvent_t &e : ep->ev)
+      if (!e) BLOK_CUDA(cudaEventCreate(&e));
+  ep->profile = on != 0;
+  return BLOK_OK;
+}
+
+extern "C" int blok_moe_ep_phase_ms(blok_moe_ep_t *ep, float *host_out6) {
+  BLOK_REQUIRE(ep && host_out6, BLOK_ERR_ARG, "blok_moe_ep_phase_ms: null pointer");
+  BLOK_REQUIRE(ep->profile && ep->ev[6], BLOK_ERR_STATE, "blok_moe_ep_phase_ms: profiling is off");
+  BLOK_CUDA(cudaEventSynchronize(ep->ev[6]));
+  for (int i = 0; i < 6; ++i) BLOK_CUDA(cudaEventElapsedTime(host_out6 + i, ep->ev[i], ep->ev[i + 1]));
   return BLOK_OK;
 }
 

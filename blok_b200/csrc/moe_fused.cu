@@ -42,7 +42,6 @@
 
 #include "bf16_mma.cuh"
 #include "i4_mma.cuh"
-#include "i4_imma.cuh"
 #include "moe_layer.h"
 #include "router_topk.cuh"
 
@@ -52,24 +51,9 @@ namespace blok {
 #define BLOK_FUSED_WARPS 16
 #endif
 #ifndef BLOK_RING_DEPTH
-#define BLOK_RING_DEPTH 6
+#define BLOK_RING_DEPTH 5
 #endif
-// Output row-blocks (16 rows each) of one routed down chunk.  A chunk stages its slot's mid values once, so 2 or 4
-// row-blocks per chunk halve or quarter that staging (16 KB of tagged reads per 18 KB of weights at 1) and keep the
-// weight ring fed across the row-block boundary.  1 is the measured configuration.
-#ifndef BLOK_FUSED_C1_BLOCKS
-#define BLOK_FUSED_C1_BLOCKS 1
-#endif
-constexpr int kC1Blocks = BLOK_FUSED_C1_BLOCKS;
-static_assert(kC1Blocks == 1 || kC1Blocks == 2 || kC1Blocks == 4, "BLOK_FUSED_C1_BLOCKS must be 1, 2 or 4");
-
-// 1: the routed experts' INT4 weights go through the integer tensor-core consumer of i4_imma.cuh (nibbles as bytes,
-// block-integer activations) instead of the bf16-operand one.  0 is the measured configuration.
-#ifndef BLOK_FUSED_I4_IMMA
-#define BLOK_FUSED_I4_IMMA 0
-#endif
-static_assert(!(BLOK_FUSED_I4_IMMA && BLOK_FUSED_C1_BLOCKS > 1), "the integer consumer is written for one row-block per down chunk");
-constexpr int kMetaBytes = BLOK_FUSED_I4_IMMA ? 8 : 4;  // per scale group: (factor, offset) or the plain sum
+constexpr int kMetaBytes = 4;  // per scale group: the sum of x
 
 constexpr int kFusedWarps = BLOK_FUSED_WARPS;
 constexpr int kFusedThreads = kFusedWarps * 32;
@@ -175,14 +159,24 @@ __device__ __forceinline__ float swiglu_ref_rounding(float g, float u) {
 // registers: no other lane touches a lane's words, and no barrier is needed.  One
 // commit group per step, always (empty groups keep the count uniform), so
 // "wait until at most kRingDepth-1 groups are pending" means "step s has landed".
+//
+// The scales of an INT4 chunk (8 bytes per row and k-block) are NOT fetched step by step: eight bytes per row per
+// step touch a new 32-byte sector in 16 rows every step and fetch every sector four times over, which alone held the
+// stream of weights + scales to 4.3-5.8 TB/s against 6.7 TB/s for the weights alone (measured with a trivial consumer).
+// They are staged whole when the chunk's first weights are requested: consecutive lanes copy consecutive 8-byte pieces
+// of a row, so a row's scales travel as full lines, once.
 constexpr int kRingDepth = BLOK_RING_DEPTH;
-constexpr int kRingStepBytes = 2 * 512 + 128;  // low rows, high rows, scales
+constexpr int kRingStepBytes = 2 * 512;                  // low rows, high rows
+constexpr int kScaleMaxSteps = 16;                       // k-blocks an INT4 chunk may have
+constexpr int kScaleRowBytes = kScaleMaxSteps * 8 + 8;   // 136: the odd multiple of 8 spreads the 16 rows over all banks
+constexpr int kScaleStageBytes = 16 * kScaleRowBytes;
+constexpr int kWarpRingBytes = kRingDepth * kRingStepBytes + kScaleStageBytes;
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
-__device__ __forceinline__ void cp_async4(uint32_t dst, const void *src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void *src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -198,25 +192,9 @@ struct Chunk {
   int k0, n;    // first step and number of steps
   int slot;     // routed slot (B, C1); topk for the shared expert
   const uint4 *w_lo, *w_hi;  // the lane's two weight rows (row start, uint4 units)
-  const uint16_t *s_sel;     // the scale row this lane post-scales (INT4 kinds)
-#if BLOK_FUSED_C1_BLOCKS > 1
-  int spr1;                  // C1: steps per row-block (the chunk runs kC1Blocks row-blocks back to back)
-  uint2 *ys;                 // C1: tagged output of the chunk's first row-block
-#endif
+  const uint16_t *s_lo, *s_hi;  // INT4 kinds: scale rows of A rows 0..7 and 8..15 (row start)
+  int s_stride;                 // elements between consecutive scale rows
 };
-
-#if BLOK_FUSED_C1_BLOCKS > 1
-#define BLOK_C1_EPOCH_ARG , epoch
-#else
-#define BLOK_C1_EPOCH_ARG
-#endif
-
-#if BLOK_FUSED_C1_BLOCKS > 1
-// Row-block of step s inside a routed down chunk of up to four row-blocks.
-__device__ __forceinline__ int c1_block_of(const Chunk &ch, int s) {
-  return (s >= ch.spr1) + (s >= 2 * ch.spr1) + (s >= 3 * ch.spr1);
-}
-#endif
 
 __device__ __forceinline__ bool kind_is_i4(int kind) { return kind == KIND_B || kind == KIND_C1; }
 
@@ -224,26 +202,26 @@ __device__ __forceinline__ void ring_issue(const Chunk &ch, int s, uint32_t ring
   if (s < ch.n) {
     const int t = lane & 3;
     const uint32_t base = ring + (uint32_t)(s % kRingDepth) * kRingStepBytes + (uint32_t)lane * 16;
-#if BLOK_FUSED_C1_BLOCKS > 1
-    size_t off = (size_t)(ch.k0 + s) * 4;  // in uint4 units of a weight row and, equally, in scales of a scale row
-    // the next row-block starts 16 rows = 64 spr1 units further; the step index has already advanced 4 spr1 of them
-    if (ch.kind == KIND_C1) off += (size_t)c1_block_of(ch, s) * 60 * ch.spr1;
-    cp_async16(base, ch.w_lo + off + t);
-    cp_async16(base + 512, ch.w_hi + off + t);
-    if (kind_is_i4(ch.kind))
-      cp_async4(ring + (uint32_t)(s % kRingDepth) * kRingStepBytes + 1024 + (uint32_t)lane * 4, ch.s_sel + off);
-#else
     cp_async16(base, ch.w_lo + (size_t)(ch.k0 + s) * 4 + t);
     cp_async16(base + 512, ch.w_hi + (size_t)(ch.k0 + s) * 4 + t);
-    if (kind_is_i4(ch.kind))
-      cp_async4(ring + (uint32_t)(s % kRingDepth) * kRingStepBytes + 1024 + (uint32_t)lane * 4,
-                ch.s_sel + (size_t)(ch.k0 + s) * 4);
-#endif
   }
   cp_async_commit();
 }
 
+// The chunk's scales, whole: 16 rows x n k-blocks x 8 bytes, into the warp's scale stage (behind the ring).
+__device__ __forceinline__ void scale_issue(const Chunk &ch, uint32_t ring, int lane) {
+  const uint32_t stage = ring + kRingDepth * kRingStepBytes;
+  const int pieces = 16 * ch.n;
+  for (int pc = lane; pc < pieces; pc += 32) {
+    const int row = pc / ch.n, s = pc - row * ch.n;
+    const uint16_t *src = ((row & 8) ? ch.s_hi : ch.s_lo) + (size_t)(row & 7) * ch.s_stride + (size_t)(ch.k0 + s) * 4;
+    cp_async8(stage + (uint32_t)(row * kScaleRowBytes + s * 8), src);
+  }
+}
+
 __device__ __forceinline__ void ring_prologue(const Chunk &ch, uint32_t ring, int lane) {
+  __syncwarp();  // every lane is done with the previous chunk's scales
+  if (kind_is_i4(ch.kind)) scale_issue(ch, ring, lane);  // joins the first step's commit group
 #pragma unroll
   for (int i = 0; i < kRingDepth; ++i) ring_issue(ch, i, ring, lane);
 }
@@ -254,56 +232,24 @@ __device__ __forceinline__ void ring_prologue(const Chunk &ch, uint32_t ring, in
 // whose first step is kx0.
 __device__ __forceinline__ float ring_consume(const Chunk &ch, uint32_t ring, const unsigned char *ring_ptr,
                                               const XFragLane &xl, const float *xsum, const uint4 *xrow, int kx0,
-                                              int lane
-#if BLOK_FUSED_C1_BLOCKS > 1
-                                              , unsigned epoch
-#endif
-) {
+                                              int lane) {
   const int t = lane & 3;
   const bool hi_row = (t >> 1) != 0;
   const int j0 = 2 * (t & 1);
   float acc = 0.f;
-#if BLOK_FUSED_I4_IMMA
-  float acc2 = 0.f;  // the lane's high row (acc is its low row): every lane sums its own scale group of both rows
-#endif
   float d[4] = {0.f, 0.f, 0.f, 0.f};
   const bool i4 = kind_is_i4(ch.kind);
+  // this lane post-scales groups (j0, j0 + 1) of A row g + 8 * (t >> 1)
+  const unsigned char *sc_lane = ring_ptr + kRingDepth * kRingStepBytes + ((lane >> 2) + 8 * (t >> 1)) * kScaleRowBytes + (t & 1) * 4;
   for (int s = 0; s < ch.n; ++s) {
     cp_async_wait<kRingDepth - 1>();
+    if (s == 0) __syncwarp();  // the scales were copied by other lanes: their first group has landed as well
     const unsigned char *slotp = ring_ptr + (size_t)(s % kRingDepth) * kRingStepBytes;
     const uint4 wl = *reinterpret_cast<const uint4 *>(slotp + lane * 16);
     const uint4 wh = *reinterpret_cast<const uint4 *>(slotp + 512 + lane * 16);
-#if BLOK_FUSED_C1_BLOCKS == 1
     const int kx = ch.k0 - kx0 + s;
-#else
-    int kx = ch.k0 - kx0 + s;
-    int blk = 0;
-    if (ch.kind == KIND_C1) {
-      blk = c1_block_of(ch, s);
-      kx = s - blk * ch.spr1;  // every row-block runs over the whole staged mid vector
-    }
-#endif
-#if BLOK_FUSED_I4_IMMA
     if (i4) {
-      // the lane's scale word holds groups (j0, j0 + 1) of one of its two rows; group t of the low row is with quad
-      // lane t >> 1, of the high row with quad lane 2 + (t >> 1), in half t & 1
-      const uint32_t sc = *reinterpret_cast<const uint32_t *>(slotp + 1024 + lane * 4);
-      const uint32_t sw_lo = __shfl_sync(0xffffffffu, sc, (lane & ~3) + (t >> 1));
-      const uint32_t sw_hi = __shfl_sync(0xffffffffu, sc, (lane & ~3) + 2 + (t >> 1));
-      int di[4] = {0, 0, 0, 0};
-      imma_kblock(wl, wh, xl.ptr + kx * xl.kb_stride, di);
-      imma_post(di, reinterpret_cast<const uint2 *>(xsum)[kx * 4 + t], (t & 1) ? bf16hi(sw_lo) : bf16lo(sw_lo),
-                (t & 1) ? bf16hi(sw_hi) : bf16lo(sw_hi), acc, acc2);
-    } else {
-      const uint4 xb = xrow[kx * 4];
-      mma_bf16_16816(d, wl.x, wh.x, wl.y, wh.y, xb.x, xb.y);
-      mma_bf16_16816(d, wl.z, wh.z, wl.w, wh.w, xb.z, xb.w);
-    }
-    ring_issue(ch, s + kRingDepth, ring, lane);
-    continue;
-#endif
-    if (i4) {
-      const uint32_t sc = *reinterpret_cast<const uint32_t *>(slotp + 1024 + lane * 4);
+      const uint32_t sc = *reinterpret_cast<const uint32_t *>(sc_lane + s * 8);
       float dd[4] = {0.f, 0.f, 0.f, 0.f};
       i4_kblock_mma(wl, wh, xl.ptr + kx * xl.kb_stride, dd);
       const float2 xs = *reinterpret_cast<const float2 *>(xsum + kx * 4 + j0);
@@ -311,15 +257,6 @@ __device__ __forceinline__ float ring_consume(const Chunk &ch, uint32_t ring, co
       const float db = hi_row ? dd[3] : dd[1];
       acc = fmaf(bf16lo(sc), fmaf(-kNibOffset, xs.x, da), acc);
       acc = fmaf(bf16hi(sc), fmaf(-kNibOffset, xs.y, db), acc);
-#if BLOK_FUSED_C1_BLOCKS > 1
-      if (ch.kind == KIND_C1 && kx == ch.spr1 - 1 && s != ch.n - 1) {
-        // a row-block other than the chunk's last is complete: publish its 16 outputs and start the next sum
-        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-        const float total = __shfl_sync(0xffffffffu, acc, ((lane & 7) << 2) + ((lane >> 3) & 1) * 2);
-        if (lane < 16) st_tagged(ch.ys + blk * 16 + lane, round_bf16(total), epoch);
-        acc = 0.f;
-      }
-#endif
     } else {
       const uint4 xb = xrow[kx * 4];
       mma_bf16_16816(d, wl.x, wh.x, wl.y, wh.y, xb.x, xb.y);
@@ -327,20 +264,10 @@ __device__ __forceinline__ float ring_consume(const Chunk &ch, uint32_t ring, co
     }
     ring_issue(ch, s + kRingDepth, ring, lane);
   }
-#if BLOK_FUSED_I4_IMMA
-  if (i4) {  // a row's four groups sit in the four lanes of its quad; callers read row g from t = 0, row g + 8 from t = 2
-    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-    acc2 += __shfl_xor_sync(0xffffffffu, acc2, 1);
-    acc2 += __shfl_xor_sync(0xffffffffu, acc2, 2);
-    return (t & 2) ? acc2 : acc;
-  }
-#else
   if (i4) {
     acc += __shfl_xor_sync(0xffffffffu, acc, 1);
     return acc;
   }
-#endif
   return (t & 2) ? d[2] : d[0];
 }
 
@@ -372,17 +299,10 @@ __device__ __forceinline__ void ld_tagged_units(const uint2 *p, int stride, int 
   for (int i = 0; i < NU; ++i) out[i] = make_uint4(r[i][0], r[i][2], r[i][4], r[i][6]);
 }
 
-// Partial sums a finisher requests per round trip when it collects a row-block (the router and the shared gate/up
-// have 7 to collect with the default chunking: two rounds of 4, or one of 8).
-#ifndef BLOK_FUSED_COLLECT
-#define BLOK_FUSED_COLLECT 4
-#endif
-constexpr int kCollect = BLOK_FUSED_COLLECT;
-
-#ifndef BLOK_FUSED_STAGE_UNITS
-#define BLOK_FUSED_STAGE_UNITS 2
-#endif
-constexpr int kStageUnits = BLOK_FUSED_STAGE_UNITS;
+// Partial sums a finisher requests per round trip when it collects a row-block, and tagged 32-byte units a lane
+// requests per round trip when it stages mid values (8 and 4 were measured slower: they spill).
+constexpr int kCollect = 4;
+constexpr int kStageUnits = 2;
 
 // One warp stages `cols` mid values (tagged pairs written earlier in this launch by other
 // warps; values that are not there yet are polled) into INT4 fragment order with group sums.
@@ -399,10 +319,6 @@ __device__ __noinline__ void warp_stage_i4(const uint2 *src, uint4 *xfrag, float
       const int u = u0 + 32 * j;
       if (u < units) {  // units is a multiple of 32, so this is warp-uniform
         const uint4 v = vv[j];
-#if BLOK_FUSED_I4_IMMA
-        imma_stage_unit(v, u, true, reinterpret_cast<unsigned char *>(xfrag), reinterpret_cast<uint2 *>(xsum));
-        continue;
-#endif
         int kb = u >> 4, t = (u >> 2) & 3, i = u & 3;
         uint4 o;
         o.x = __byte_perm(v.x, v.z, 0x5410);
@@ -438,8 +354,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
   sp += 384;
   float *xsum = reinterpret_cast<float *>(sp);  // per scale group: the sum of x, or (factor, offset) of the integer form
   sp += (size_t)(p.hidden / 32) * kMetaBytes;
-  unsigned char *ring_ptr = sp + (size_t)warp * kRingDepth * kRingStepBytes;  // this warp's weight ring
-  sp += (size_t)kFusedWarps * kRingDepth * kRingStepBytes;
+  unsigned char *ring_ptr = sp + (size_t)warp * kWarpRingBytes;  // this warp's weight ring, then its scale stage
+  sp += (size_t)kFusedWarps * kWarpRingBytes;
   const size_t wstage_bytes = (size_t)p.inter * 2 + (size_t)(p.inter / 32) * kMetaBytes;
   unsigned char *wstage = sp + (size_t)warp * wstage_bytes;  // this warp's private segment of mid
   sp += (size_t)kFusedWarps * wstage_bytes;
@@ -455,27 +371,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
 
   if (tid == 0) trace_cta(p, 0);
   for (int u = tid; u < p.hidden / 8; u += kFusedThreads) xnat[u] = reinterpret_cast<const uint4 *>(p.x)[u];
-#if BLOK_FUSED_I4_IMMA
-  {
-    ImmaStage st;
-    st.xq = reinterpret_cast<unsigned char *>(xfrag);
-    st.meta = reinterpret_cast<uint2 *>(xsum);
-    st.zero = zero;
-    stage_x_imma(reinterpret_cast<const uint4 *>(p.x), st, p.hidden, tid, kFusedThreads);
-    for (int u = 8 + tid; u < 24; u += kFusedThreads) zero[u] = make_uint4(0, 0, 0, 0);  // the bf16 kinds read further in
-  }
-  __syncthreads();
-  if (tid == 0) trace_cta(p, 1);
-
-  // integer form: lanes with (g >> 1) == t supply limb g & 1 of their own scale group (two uint4 per k-block)
-  const bool supply = ((g >> 1) == t);
-  XFragLane xl_x;
-  xl_x.ptr = supply ? reinterpret_cast<const uint4 *>(reinterpret_cast<unsigned char *>(xfrag) + t * 64 + (g & 1) * 32) : zero + 4 + (lane & 1);
-  xl_x.kb_stride = supply ? 16 : 0;
-  XFragLane xl_m;
-  xl_m.ptr = supply ? reinterpret_cast<const uint4 *>(wstage + t * 64 + (g & 1) * 32) : zero + 4 + (lane & 1);
-  xl_m.kb_stride = supply ? 16 : 0;
-#else
   {
     I4Stage st;
     st.xfrag = xfrag;
@@ -493,7 +388,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
   XFragLane xl_m;  // fragments of this warp's staged mid
   xl_m.ptr = supply ? reinterpret_cast<const uint4 *>(wstage) + t : zero + 4 + t;
   xl_m.kb_stride = supply ? 16 : 0;
-#endif
   float *msum = reinterpret_cast<float *>(wstage + (size_t)p.inter * 2);
 
   const unsigned epoch = p.ctrl[CTRL_EPOCH] + 1u;  // stable during the launch; the last CTA to leave bumps it
@@ -513,7 +407,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
       const size_t wrow = p.hidden / 8;
       ch.w_lo = reinterpret_cast<const uint4 *>(p.router_w) + (size_t)(ch.rb * 16 + g) * wrow;
       ch.w_hi = ch.w_lo + 8 * wrow;
-      ch.s_sel = nullptr;
+      ch.s_lo = ch.s_hi = nullptr;
+      ch.s_stride = 0;
     } else if (c < p.cB0) {
       const int ci = (int)(c - p.cA0);
       ch.kind = KIND_A;
@@ -525,7 +420,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
       const size_t wrow = p.hidden / 8;
       ch.w_lo = reinterpret_cast<const uint4 *>(p.shared_gate) + (size_t)(ch.rb * 8 + g) * wrow;
       ch.w_hi = reinterpret_cast<const uint4 *>(p.shared_up) + (size_t)(ch.rb * 8 + g) * wrow;
-      ch.s_sel = nullptr;
+      ch.s_lo = ch.s_hi = nullptr;
+      ch.s_stride = 0;
     } else if (c < p.cC10) {
       const int ci = (int)(c - p.cB0);
       ch.kind = KIND_B;
@@ -537,28 +433,29 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
       ch.slot = ch.rb / rb_per_slot;
       const int jb = ch.rb - ch.slot * rb_per_slot;
       const size_t wrow = p.hidden / 32;
-      const size_t ebase = (size_t)w_ids[ch.slot] * p.inter * wrow + (size_t)(jb * 8 + g) * wrow;
+      const size_t ebase0 = (size_t)w_ids[ch.slot] * p.inter * wrow + (size_t)(jb * 8) * wrow;
+      const size_t ebase = ebase0 + (size_t)g * wrow;
       ch.w_lo = reinterpret_cast<const uint4 *>(p.gate_w) + ebase;
       ch.w_hi = reinterpret_cast<const uint4 *>(p.up_w) + ebase;
-      ch.s_sel = ((t >> 1) ? p.up_s : p.gate_s) + ebase + 2 * (t & 1);
+      ch.s_lo = p.gate_s + ebase0;
+      ch.s_hi = p.up_s + ebase0;
+      ch.s_stride = (int)wrow;
     } else if (c < p.cC20) {
       const int rb = (int)(c - p.cC10);
-      const int rb_per_slot = p.hidden / 16 / kC1Blocks;  // chunks per slot
+      const int rb_per_slot = p.hidden / 16;  // chunks per slot
       ch.kind = KIND_C1;
       ch.slot = rb / rb_per_slot;
-      ch.rb = (rb - ch.slot * rb_per_slot) * kC1Blocks;  // (first) output row-block
+      ch.rb = rb - ch.slot * rb_per_slot;  // output row-block
       ch.kc = 0;
       ch.k0 = 0;
-      ch.n = p.sprC1 * kC1Blocks;
-#if BLOK_FUSED_C1_BLOCKS > 1
-      ch.spr1 = p.sprC1;
-      ch.ys = p.ys + (size_t)ch.slot * p.hidden + ch.rb * 16;
-#endif
+      ch.n = p.sprC1;
       const size_t wrow = p.inter / 32;
       const size_t ebase = (size_t)w_ids[ch.slot] * p.hidden * wrow;
       ch.w_lo = reinterpret_cast<const uint4 *>(p.down_w) + ebase + (size_t)(ch.rb * 16 + g) * wrow;
       ch.w_hi = ch.w_lo + 8 * wrow;
-      ch.s_sel = p.down_s + ebase + (size_t)(ch.rb * 16 + g + 8 * (t >> 1)) * wrow + 2 * (t & 1);
+      ch.s_lo = p.down_s + ebase + (size_t)(ch.rb * 16) * wrow;
+      ch.s_hi = ch.s_lo + 8 * wrow;
+      ch.s_stride = (int)wrow;
     } else {
       const int ci = (int)(c - p.cC20);
       ch.kind = KIND_C2;
@@ -570,7 +467,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
       const size_t wrow = p.shared_inter / 8;
       ch.w_lo = reinterpret_cast<const uint4 *>(p.shared_down) + (size_t)(ch.rb * 16 + g) * wrow;
       ch.w_hi = ch.w_lo + 8 * wrow;
-      ch.s_sel = nullptr;
+      ch.s_lo = ch.s_hi = nullptr;
+      ch.s_stride = 0;
     }
     return ch;
   };
@@ -644,8 +542,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
   auto arrive = [&](const Chunk &ch, float v) {
     if (ch.kind == KIND_C1) {
       const float total = __shfl_sync(0xffffffffu, v, ((lane & 7) << 2) + ((lane >> 3) & 1) * 2);
-      // the value in hand is the chunk's last row-block (earlier ones were published as they completed)
-      if (lane < 16) st_tagged(p.ys + (size_t)ch.slot * p.hidden + (ch.rb + kC1Blocks - 1) * 16 + lane, round_bf16(total), epoch);
+      if (lane < 16) st_tagged(p.ys + (size_t)ch.slot * p.hidden + ch.rb * 16 + lane, round_bf16(total), epoch);
       return;
     }
     const int np = piece_n(ch);
@@ -744,7 +641,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
       if (cur.kind == KIND_C1) {
         warp_stage_i4(p.mid + (size_t)cur.slot * p.mid_stride / 2, reinterpret_cast<uint4 *>(wstage), msum, p.inter, lane,
                       epoch, err);
-        v = ring_consume(cur, ring, ring_ptr, xl_m, msum, nullptr, 0, lane BLOK_C1_EPOCH_ARG);
+        v = ring_consume(cur, ring, ring_ptr, xl_m, msum, nullptr, 0, lane);
       } else {
         uint4 *seg = reinterpret_cast<uint4 *>(wstage);
         const uint2 *src = p.mid + (size_t)p.topk * p.mid_stride / 2 + (size_t)cur.k0 * 16;
@@ -757,13 +654,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
             if (u0 + 32 * j < cur.n * 4) seg[u0 + 32 * j] = vv[j];
         }
         __syncwarp();
-        v = ring_consume(cur, ring, ring_ptr, xl_m, msum, seg + t, cur.k0, lane BLOK_C1_EPOCH_ARG);
+        v = ring_consume(cur, ring, ring_ptr, xl_m, msum, seg + t, cur.k0, lane);
       }
       __syncwarp();  // the staged segment is free again
     } else if (cur.kind == KIND_B) {
-      v = ring_consume(cur, ring, ring_ptr, xl_x, xsum, nullptr, 0, lane BLOK_C1_EPOCH_ARG);
+      v = ring_consume(cur, ring, ring_ptr, xl_x, xsum, nullptr, 0, lane);
     } else {
-      v = ring_consume(cur, ring, ring_ptr, xl_x, xsum, xnat + t, 0, lane BLOK_C1_EPOCH_ARG);
+      v = ring_consume(cur, ring, ring_ptr, xl_x, xsum, xnat + t, 0, lane);
     }
     // ---- hand in (without waiting), put the next chunk's weights in flight, then look at the count ----
     if (tr) p.trace[16 + (size_t)blockIdx.x * kTraceSlots + 8 + traced * 4 + 1] = global_ns();
@@ -815,7 +712,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
 static int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 size_t fused_smem_bytes(const blok_moe_weights &w) {
-  return (size_t)w.hidden * 4 + 384 + (size_t)(w.hidden / 32) * kMetaBytes + (size_t)kFusedWarps * kRingDepth * kRingStepBytes +
+  return (size_t)w.hidden * 4 + 384 + (size_t)(w.hidden / 32) * kMetaBytes + (size_t)kFusedWarps * kWarpRingBytes +
          (size_t)kFusedWarps * ((size_t)w.inter * 2 + (size_t)(w.inter / 32) * kMetaBytes) + (size_t)kFusedWarps * 16 * 8 +
          (size_t)w.experts * 2 * sizeof(float);
 }
@@ -834,7 +731,6 @@ int fused_plan(const blok_moe_weights &w, FusedPlan *plan) {
   plan->enabled = false;
   if (w.experts % 16 || w.topk > 16 || w.shared_inter % 32 || w.inter % 256 || w.hidden % 256) return BLOK_OK;
   if (w.experts_local != w.experts || w.expert_base != 0) return BLOK_OK;
-  if (kC1Blocks > 1 && (w.shared_inter == 0 || (w.hidden / 16) % kC1Blocks)) return BLOK_OK;  // multi-row-block down chunks
   if (w.shared_inter > w.inter && w.shared_inter > 0 && 16 * 64 > w.inter * 2) return BLOK_OK;
   int dev = 0, coop = 0, sms = 0;
   BLOK_CUDA(cudaGetDevice(&dev));
@@ -852,7 +748,7 @@ int fused_plan(const blok_moe_weights &w, FusedPlan *plan) {
   plan->total_warps = plan->grid * kFusedWarps;
   // chunking (steps of 1 KB of weights per warp); BLOK_FUSED_CHUNK_STEPS="R,A,B,C2" overrides the target steps per
   // chunk of the four phases that are cut (a tuning aid; the defaults are the measured configuration)
-  int tgt[4] = {28, 28, 14, 32};
+  int tgt[4] = {14, 28, 14, 16};
   if (const char *e = getenv("BLOK_FUSED_CHUNK_STEPS")) {
     int v[4];
     if (sscanf(e, "%d,%d,%d,%d", &v[0], &v[1], &v[2], &v[3]) == 4 && v[0] > 0 && v[1] > 0 && v[2] > 0 && v[3] > 0)
@@ -865,6 +761,7 @@ int fused_plan(const blok_moe_weights &w, FusedPlan *plan) {
   plan->sprB = w.hidden / 128;
   cut(plan->sprB, tgt[2], &plan->spcB, &plan->cprB);
   plan->sprC1 = w.inter / 128;
+  if (plan->spcB > kScaleMaxSteps || plan->sprC1 > kScaleMaxSteps) return BLOK_OK;  // an INT4 chunk's scales are staged whole
   plan->sprC2 = w.shared_inter / 32;
   plan->spcC2 = 1;
   plan->cprC2 = 1;
@@ -907,7 +804,7 @@ int launch_moe_decode_fused(blok_moe_layer *L, const uint16_t *x, uint16_t *y, u
   p.cA0 = (unsigned)pl.nrbR * pl.cprR;
   p.cB0 = p.cA0 + (unsigned)pl.nrbA * pl.cprA;
   p.cC10 = p.cB0 + (unsigned)pl.nrbB * pl.cprB;
-  p.cC20 = p.cC10 + (unsigned)pl.nrbC1 / kC1Blocks;
+  p.cC20 = p.cC10 + (unsigned)pl.nrbC1;
   p.total = p.cC20 + (unsigned)pl.nrbC2 * pl.cprC2;
   p.ctrl = L->f_ctrl;
   p.trace = L->f_trace;

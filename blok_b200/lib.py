@@ -418,6 +418,15 @@ class MoeEp:
     def check(self):
         _check(load().blok_moe_ep_check(self._handle, _stream()))
 
+    def profile(self, on=True):
+        _check(load().blok_moe_ep_profile(self._handle, C.c_int(1 if on else 0)))
+
+    def phase_ms(self):
+        """Device milliseconds of the last pass by phase (profiling must be on); waits for the pass."""
+        out = (C.c_float * 6)()
+        _check(load().blok_moe_ep_phase_ms(self._handle, out))
+        return dict(zip(("route", "dispatch", "shared", "wait_rows", "experts", "combine"), [float(v) for v in out]))
+
     def stats(self):
         """After a pass: assignments sent, of those to other ranks, rows received, GEMM tiles (synchronises)."""
         out = (C.c_longlong * 4)()

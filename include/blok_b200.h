@@ -299,6 +299,11 @@ int blok_moe_ep_check(blok_moe_ep_t *ep, blok_stream_t stream);
 /* HOST out[4] after synchronising `stream`, for the last pass: assignments this rank sent, of those to other ranks,
  * rows this rank received, tiles its grouped GEMM ran. */
 int blok_moe_ep_stats(blok_moe_ep_t *ep, long long *host_out4, blok_stream_t stream);
+/* Measurement aid: with profiling on, a pass records a CUDA event between its phases; blok_moe_ep_phase_ms waits for
+ * the last pass and returns HOST out[6], milliseconds on the device: routing; counts + plan + dispatch; shared expert;
+ * waiting for the other ranks' rows; the grouped expert GEMM; flags + combine (which waits for the owners). */
+int blok_moe_ep_profile(blok_moe_ep_t *ep, int on);
+int blok_moe_ep_phase_ms(blok_moe_ep_t *ep, float *host_out6);
 
 /* ------------------------------------------------------------------------- */
 /* A8-A10  MLA decode attention (config 3)                                    */

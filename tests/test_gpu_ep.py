@@ -13,9 +13,11 @@ sys.path.insert(0, ROOT)
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, impl):
     try:
-        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        # one GEMM implementation on every rank and in the single-GPU layer: which kernel a launch picks depends on how
+        # many rows it gets, and the two kernels sum in different orders (equal only within rounding)
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", BLOK_WGEMM_IMPL=impl)
         import torch.distributed as dist
         torch.cuda.set_device(rank)
         dev = torch.device("cuda", rank)
@@ -55,7 +57,8 @@ def _worker(rank, world, port, q):
         q.put((rank, "error: %r %s" % (e, traceback.format_exc()[-800:]), {}))
 
 
-def test_two_rank_expert_parallel_layer_matches_single_gpu():
+@pytest.mark.parametrize("impl", ["mma", "tc"])
+def test_two_rank_expert_parallel_layer_matches_single_gpu(impl):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
@@ -65,7 +68,7 @@ def test_two_rank_expert_parallel_layer_matches_single_gpu():
     s.close()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, impl)) for r in range(2)]
     for p in procs:
         p.start()
     res = {}
