@@ -32,6 +32,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "ep_plan.h"
 #include "moe_layer.h"
 #include "wgemm.h"
 
@@ -269,50 +270,19 @@ __global__ void ep_plan_kernel(EpParams p, int *__restrict__ counts, int *__rest
     atomicExch(p.err, 10u + threadIdx.x);
   __syncthreads();
   const volatile int *table = reinterpret_cast<const volatile int *>(me + p.o_table);
-  for (int g = threadIdx.x; g < p.experts; g += blockDim.x) {
-    int t = 0, b = 0;
-    for (int s = 0; s < p.world; ++s) {
-      int c = table[(size_t)s * p.experts + g];
-      c = max(0, min(c, (int)min(p.cap_rows, (long)0x3fffffff)));  // a peer that timed out may have left anything here
-      if (s < p.rank) b += c;
-      t += c;
-    }
-    tot[g] = t;
-    before[g] = b;
-  }
+  for (int g = threadIdx.x; g < p.experts; g += blockDim.x) ep_expert_totals(table, p.world, p.experts, p.rank, p.cap_rows, g, tot + g, before + g);
   __syncthreads();
-  if (threadIdx.x < p.world) {  // owner d: exclusive scan over its experts
-    int off = 0;
-    for (int e = 0; e < p.per; ++e) {
-      const int g = threadIdx.x * p.per + e;
-      base[g] = off;
-      off = (int)min((long)off + tot[g], p.cap_rows);
-    }
-  }
+  if (threadIdx.x < p.world) ep_owner_bases(tot, p.per, threadIdx.x, p.cap_rows, base);
   __syncthreads();
   for (int g = threadIdx.x; g < p.experts; g += blockDim.x) p.send_base[g] = base[g] + before[g];
   if (threadIdx.x == 0) {  // this rank as owner: counts, offsets and tiles of 64 rows of one expert
-    int off = 0, nt = 0;
-    for (int e = 0; e < p.per; ++e) {
-      const int g = p.rank * p.per + e;
-      int c = tot[g];
-      if ((long)off + c > p.cap_rows) {
-        c = (int)(p.cap_rows - off);
-        atomicExch(p.err, 20u);
-      }
-      counts[e] = c;
-      offsets[e] = off;
-      for (int s = 0; s < c && nt < max_tiles; s += kWgTileTokens) {
-        tile_expert[nt] = e;
-        tile_start[nt] = off + s;
-        tile_count[nt] = min(kWgTileTokens, c - s);
-        ++nt;
-      }
-      off += c;
-    }
-    offsets[p.per] = off;
+    long rows = 0;
+    int overflow = 0;
+    const int nt = ep_owner_tiles(tot, p.per, p.rank, p.cap_rows, kWgTileTokens, max_tiles, counts, offsets, tile_expert, tile_start,
+                                  tile_count, &rows, &overflow);
+    if (overflow) atomicExch(p.err, 20u);
     *num_tiles = nt;
-    p.stats[2] = off;
+    p.stats[2] = rows;
     p.stats[3] = nt;
   }
 }
@@ -509,6 +479,29 @@ extern "C" int blok_comm_broadcast(blok_comm_t *c, void *buf, long bytes, int ro
                "blok_comm_broadcast: bad argument");
   if (c->world == 1 || bytes == 0) return BLOK_OK;
   BLOK_NCCL(g_nccl.Broadcast(buf, buf, (size_t)bytes, ncclUint8, root, c->nccl, (cudaStream_t)stream));
+  return BLOK_OK;
+}
+
+// The plan of one rank from the gathered count table, on the HOST: the same functions the plan kernel runs.
+extern "C" int blok_ep_plan_host(const int *table, int world, int experts, int rank, long cap_rows, int max_tiles, int *send_base,
+                                 int *counts, int *offsets, int *tile_expert, int *tile_start, int *tile_count, int *num_tiles) {
+  BLOK_REQUIRE(table && send_base && counts && offsets && tile_expert && tile_start && tile_count && num_tiles, BLOK_ERR_ARG,
+               "blok_ep_plan_host: null pointer");
+  BLOK_REQUIRE(world >= 1 && experts >= world && experts % world == 0 && rank >= 0 && rank < world && cap_rows >= 0 && max_tiles >= 0,
+               BLOK_ERR_SHAPE, "blok_ep_plan_host: rank %d of %d, %d experts", rank, world, experts);
+  const int per = experts / world;
+  std::vector<int> tot(experts), before(experts), base(experts);
+  for (int g = 0; g < experts; ++g) ep_expert_totals(table, world, experts, rank, cap_rows, g, &tot[g], &before[g]);
+  for (int d = 0; d < world; ++d) ep_owner_bases(tot.data(), per, d, cap_rows, base.data());
+  for (int g = 0; g < experts; ++g) send_base[g] = base[g] + before[g];
+  long rows = 0;
+  int overflow = 0;
+  *num_tiles = ep_owner_tiles(tot.data(), per, rank, cap_rows, kWgTileTokens, max_tiles, counts, offsets, tile_expert, tile_start,
+                              tile_count, &rows, &overflow);
+  if (overflow) {
+    set_error("blok_ep_plan_host: rank %d would receive more than %ld rows", rank, cap_rows);
+    return BLOK_ERR_ROUTE;
+  }
   return BLOK_OK;
 }
 

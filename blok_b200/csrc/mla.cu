@@ -88,10 +88,14 @@ __global__ void __launch_bounds__(256) mla_prep_kernel(const uint16_t *__restric
                                                        long ctx_stride, uint16_t *__restrict__ q_full, int *__restrict__ seq,
                                                        int heads, int nope, int rope, int kv_rank, float eps,
                                                        const int *__restrict__ block_table, const int *__restrict__ slot_of,
-                                                       int table_stride, int page_rows) {
+                                                       int table_stride, int page_rows, long ctx_cap, unsigned *__restrict__ err) {
   __shared__ float red[32];
   const int b = blockIdx.y, tid = threadIdx.x;
-  const int pos = ctx_len[b];
+  int pos = ctx_len[b];
+  // A position outside the sequence's rows (dense: ctx_cap rows; paged: table_stride pages) must not become a store or
+  // a read: the row is not written, the attention is kept inside the rows, and the host learns of it from *err.
+  const bool in_range = pos >= 0 && (long)pos < ctx_cap;
+  if (!in_range) pos = pos < 0 ? 0 : (int)(ctx_cap - 1);
   const int half = rope / 2, lat_w = kv_rank + rope;
   if (blockIdx.x > 0) {
     // thread = (head, pair): interleaved pair (2p, 2p+1) -> de-interleaved (p, half+p); every product rounded (:353-356)
@@ -109,7 +113,11 @@ __global__ void __launch_bounds__(256) mla_prep_kernel(const uint16_t *__restric
     }
     return;
   }
-  if (tid == 0) seq[b] = pos + 1;
+  if (tid == 0) {
+    seq[b] = pos + 1;
+    if (!in_range) atomicExch(err, 1u + (unsigned)b);
+  }
+  if (!in_range) return;
   const uint16_t *kr = kva + (size_t)b * lat_w;
   // dense: sequence b's rows start at b * ctx_stride; paged: the row's page comes from the sequence's block table
   uint16_t *row = block_table
@@ -236,6 +244,7 @@ struct blok_mla_layer {
   uint16_t *o_lat = nullptr;   // [B, heads, kv_rank]
   uint16_t *av = nullptr;      // [B, heads * v_head]
   int *seq = nullptr;          // [B]
+  unsigned *err = nullptr;     // [1] 1 + b when entry b of a call had a position outside its sequence's rows
   int *chunk_pos = nullptr;    // [B] positions of a prefill chunk's tokens
   int *tiles = nullptr;        // tile table of the weight-streaming GEMM (projections of 16 or more entries)
   int n_tiles = 0;
@@ -306,6 +315,7 @@ extern "C" int blok_mla_layer_create(const blok_mla_weights *w, int max_batch, i
   size_t o_av = take((size_t)max_batch * w->heads * w->v_head * 2);
   size_t o_seq = take((size_t)max_batch * 4);
   size_t o_cpos = take((size_t)max_batch * 4);
+  size_t o_err = take(4);
   L->n_tiles = (max_batch + kWgTileTokens - 1) / kWgTileTokens;
   size_t o_tiles = take((size_t)(3 * L->n_tiles + 1) * sizeof(int));
   size_t o_po = take((size_t)(L->max_splits + max_batch) * w->heads * w->kv_rank * 4);
@@ -334,6 +344,7 @@ extern "C" int blok_mla_layer_create(const blok_mla_weights *w, int max_batch, i
   L->av = reinterpret_cast<uint16_t *>(b + o_av);
   L->seq = reinterpret_cast<int *>(b + o_seq);
   L->chunk_pos = reinterpret_cast<int *>(b + o_cpos);
+  L->err = reinterpret_cast<unsigned *>(b + o_err);
   L->tiles = reinterpret_cast<int *>(b + o_tiles);
   L->part_o = reinterpret_cast<float *>(b + o_po);
   L->part_ml = reinterpret_cast<float *>(b + o_pml);
@@ -373,6 +384,17 @@ extern "C" int blok_mla_layer_destroy(blok_mla_layer_t *L) {
   cudaError_t e = L->ws ? cudaFree(L->ws) : cudaSuccess;
   delete L;
   return e == cudaSuccess ? BLOK_OK : cuda_fail(e, "cudaFree(mla layer workspace)");
+}
+
+extern "C" int blok_mla_layer_check(blok_mla_layer_t *L, blok_stream_t stream) {
+  BLOK_REQUIRE(L, BLOK_ERR_ARG, "blok_mla_layer_check: null pointer");
+  BLOK_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  unsigned err = 0;
+  BLOK_CUDA(cudaMemcpy(&err, L->err, sizeof(err), cudaMemcpyDeviceToHost));
+  if (err == 0) return BLOK_OK;
+  BLOK_CUDA(cudaMemset(L->err, 0, sizeof(err)));
+  set_error("blok_mla_decode: entry %u had a position outside its sequence's cache rows; its row was not stored", err - 1);
+  return BLOK_ERR_SHAPE;
 }
 
 // Where the latent rows of the sequences of a call live.
@@ -490,7 +512,7 @@ static int decode_body(blok_mla_layer *L, const uint16_t *n, const CacheRef &c, 
   if ((rc = project(L, w.kv_a, n, L->kva, lat_w, w.hidden, B, gemm, stream))) return rc;
   mla_prep_kernel<<<dim3(1 + (w.heads * (w.qk_rope / 2) + 255) / 256, B), 256, 0, stream>>>(
       L->kva, w.kv_a_ln, L->q, L->inv_freq, ctx_len, c.base, c.seq_stride, L->q_full, L->seq, w.heads, w.qk_nope, w.qk_rope,
-      w.kv_rank, w.rms_eps, c.block_table, c.slot_of, c.table_stride, c.page_rows);
+      w.kv_rank, w.rms_eps, c.block_table, c.slot_of, c.table_stride, c.page_rows, c.ctx_cap, L->err);
   if ((rc = launch_status("mla_prep_kernel"))) return rc;
   // q_abs = W_UK^T q_nope
   for (int b0 = 0; b0 < B; b0 += 8)

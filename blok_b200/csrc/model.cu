@@ -26,15 +26,17 @@ __device__ __forceinline__ float unit_normal(uint64_t key, uint64_t i) {
   return sqrtf(-2.0f * logf(u1)) * cosf(6.28318530718f * u2);
 }
 
-__global__ void fill_words_kernel(uint32_t *p, size_t n, uint64_t key) {
+// `first` is the index, in the whole tensor, of the first element generated: a rank's shard of the experts holds exactly
+// the values the unsharded tensor has at those positions.
+__global__ void fill_words_kernel(uint32_t *p, size_t n, uint64_t key, size_t first) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) p[i] = (uint32_t)mix64(key ^ mix64(i));
+  if (i < n) p[i] = (uint32_t)mix64(key ^ mix64(i + first));
 }
 // mode 0: N(0, std); mode 1: |N(0, std)|; mode 2: constant std
-__global__ void fill_bf16_kernel(uint16_t *p, size_t n, uint64_t key, float std, int mode) {
+__global__ void fill_bf16_kernel(uint16_t *p, size_t n, uint64_t key, float std, int mode, size_t first) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
-  float v = mode == 2 ? std : unit_normal(key, i) * std;
+  float v = mode == 2 ? std : unit_normal(key, i + first) * std;
   if (mode == 1) v = fabsf(v);
   p[i] = f32_to_bf16_bits(v);
 }
@@ -66,6 +68,45 @@ __global__ void chunk_slots_kernel(const int *__restrict__ pos, int slot, int n,
     slot_of[i] = slot;
   }
 }
+
+// Expert-parallel decode (every rank holds the same rows): the weighted sum of the selected experts THIS rank holds,
+// unrounded, rows of experts held elsewhere skipped; the ranks' sums are added by one all-reduce per layer.
+__global__ void sharded_partial_kernel(const uint16_t *__restrict__ y_assign, const float *__restrict__ wts,
+                                       const int *__restrict__ local_ids, int n_local, int hidden, int topk, float *__restrict__ part) {
+  const int t = blockIdx.y;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (c >= hidden) return;
+  float o0 = 0.f, o1 = 0.f;
+  for (int k = 0; k < topk; ++k) {
+    const int e = local_ids[(size_t)t * topk + k];
+    if (e < 0 || e >= n_local) continue;
+    const uint32_t v = *reinterpret_cast<const uint32_t *>(y_assign + ((size_t)t * topk + k) * hidden + c);
+    const float w = wts[(size_t)t * topk + k];
+    o0 = fmaf(bf16lo(v), w, o0);
+    o1 = fmaf(bf16hi(v), w, o1);
+  }
+  *reinterpret_cast<float2 *>(part + (size_t)t * hidden + c) = make_float2(o0, o1);
+}
+// out = bf16(bf16(routed sum) + shared), the rounding points of src/kimi_exec.cu:871 and :684.
+__global__ void sharded_finish_kernel(const float *__restrict__ part, const uint16_t *__restrict__ shared, int hidden,
+                                      uint16_t *__restrict__ out) {
+  const int t = blockIdx.y;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (c >= hidden) return;
+  const float2 v = *reinterpret_cast<const float2 *>(part + (size_t)t * hidden + c);
+  float o0 = round_bf16(v.x), o1 = round_bf16(v.y);
+  if (shared) {
+    const uint32_t s = *reinterpret_cast<const uint32_t *>(shared + (size_t)t * hidden + c);
+    o0 = round_bf16(o0 + bf16lo(s));
+    o1 = round_bf16(o1 + bf16hi(s));
+  }
+  *reinterpret_cast<uint32_t *>(out + (size_t)t * hidden + c) = pack_bf16x2(o0, o1);
+}
+
+int launch_bf16_gemv(const uint16_t *w, const uint16_t *x, uint16_t *y_bf16, float *y_f32, int rows, int cols, int T,
+                     cudaStream_t stream);
+int launch_router_topk(const float *logits, const float *bias, int T, int experts, int topk, float routed_scale,
+                       uint16_t *ids, float *wts, int *local_ids, int expert_base, cudaStream_t stream);
 
 struct Tensor {
   void *ptr = nullptr;
@@ -110,6 +151,17 @@ struct blok_model {
   long long graph_launches[blok::kMaxBatch + 1] = {};  // kernels in each graph, added to the launch counter at every replay
   int steps_seen[blok::kMaxBatch + 1] = {};
   bool graphs_enabled = true;
+  // expert parallelism (cfg.ep_world > 1): this rank holds experts [ep_base, ep_base + ep_local) of every MoE layer
+  blok_comm_t *comm = nullptr;
+  int ep_base = 0, ep_local = 0;
+  float *ep_logits = nullptr;   // [rows, experts]
+  uint16_t *ep_ids = nullptr;   // [rows, topk]
+  int *ep_local_ids = nullptr;  // [rows, topk] id - ep_base (outside [0, ep_local): held by another rank)
+  int *ep_rows = nullptr;       // [rows * topk] row of assignment a: a / topk
+  float *ep_wts = nullptr;      // [rows, topk]
+  uint16_t *ep_y = nullptr;     // [rows * topk, hidden] outputs of the assignments held here
+  float *ep_part = nullptr;     // [rows, hidden] this rank's weighted sum, then the sum over the ranks
+  uint16_t *ep_shared = nullptr;  // [rows, hidden]
 };
 
 using namespace blok;
@@ -126,7 +178,8 @@ int dev_alloc(blok_model *m, size_t bytes, void **out) {
 
 enum Fill { F_NORMAL, F_ABS, F_ONE, F_WORDS, F_F32 };
 
-int make_tensor(blok_model *m, std::map<std::string, Tensor> &into, const char *name, size_t elems, Fill fill, float std) {
+int make_tensor(blok_model *m, std::map<std::string, Tensor> &into, const char *name, size_t elems, Fill fill, float std,
+                size_t first = 0) {
   size_t esz = (fill == F_WORDS || fill == F_F32) ? 4 : 2;
   Tensor t;
   t.bytes = elems * esz;
@@ -135,10 +188,10 @@ int make_tensor(blok_model *m, std::map<std::string, Tensor> &into, const char *
   const uint64_t key = m->seed * 0x100000001b3ull + (++m->counter) * 0x9e3779b97f4a7c15ull;
   const unsigned blocks = (unsigned)((elems + 255) / 256);
   if (elems) {
-    if (fill == F_WORDS) fill_words_kernel<<<blocks, 256>>>(static_cast<uint32_t *>(t.ptr), elems, key);
+    if (fill == F_WORDS) fill_words_kernel<<<blocks, 256>>>(static_cast<uint32_t *>(t.ptr), elems, key, first);
     else if (fill == F_F32) fill_f32_kernel<<<blocks, 256>>>(static_cast<float *>(t.ptr), elems, key, std);
     else fill_bf16_kernel<<<blocks, 256>>>(static_cast<uint16_t *>(t.ptr), elems, key, fill == F_ONE ? 1.0f : std,
-                                           fill == F_ONE ? 2 : (fill == F_ABS ? 1 : 0));
+                                           fill == F_ONE ? 2 : (fill == F_ABS ? 1 : 0), first);
     rc = launch_status("synthetic fill");
     if (rc) return rc;
   }
@@ -155,6 +208,9 @@ T *tp(const std::map<std::string, Tensor> &m, const char *name) {
 int build(blok_model *m) {
   const blok_model_config &c = m->cfg;
   m->rows = c.max_batch > c.prefill_chunk ? c.max_batch : c.prefill_chunk;
+  const int world = c.ep_world > 1 ? c.ep_world : 1;
+  m->ep_local = c.experts / world;
+  m->ep_base = (world > 1 ? c.ep_rank : 0) * m->ep_local;
   // the grouped-GEMM form of the MoE layer (blok_moe_batched) serves prefill chunks and steps of more than 8 sequences
   m->moe_batched_ok = m->rows > 1 && c.first_dense < c.layers && c.hidden % 512 == 0 && c.inter % 512 == 0 &&
                       c.experts % 128 == 0 && c.shared_inter % 512 == 0;
@@ -185,14 +241,18 @@ int build(blok_model *m) {
       MK(t, "down_proj", H * (size_t)c.dense_inter, F_NORMAL, wstd);
     } else {
       const size_t E = c.experts, I = c.inter;
+      const size_t El = m->ep_local, E0 = m->ep_base;  // this rank's experts; the values are those of the whole tensor
       MK(t, "router", E * H, F_NORMAL, wstd);
       MK(t, "router_bias", E, F_F32, 0.01f);
-      MK(t, "gate_w", E * I * (H / 8), F_WORDS, 0.f);
-      MK(t, "gate_s", E * I * (H / 32), F_ABS, 0.003f);
-      MK(t, "up_w", E * I * (H / 8), F_WORDS, 0.f);
-      MK(t, "up_s", E * I * (H / 32), F_ABS, 0.003f);
-      MK(t, "down_w", E * H * (I / 8), F_WORDS, 0.f);
-      MK(t, "down_s", E * H * (I / 32), F_ABS, 0.003f);
+#define MKE(name, per_expert, fill, std) \
+  if ((rc = make_tensor(m, t, name, El * (size_t)(per_expert), fill, std, E0 * (size_t)(per_expert)))) return rc;
+      MKE("gate_w", I * (H / 8), F_WORDS, 0.f);
+      MKE("gate_s", I * (H / 32), F_ABS, 0.003f);
+      MKE("up_w", I * (H / 8), F_WORDS, 0.f);
+      MKE("up_s", I * (H / 32), F_ABS, 0.003f);
+      MKE("down_w", H * (I / 8), F_WORDS, 0.f);
+      MKE("down_s", H * (I / 32), F_ABS, 0.003f);
+#undef MKE
       if (c.shared_inter) {
         MK(t, "shared_gate", (size_t)c.shared_inter * H, F_NORMAL, wstd);
         MK(t, "shared_up", (size_t)c.shared_inter * H, F_NORMAL, wstd);
@@ -224,13 +284,15 @@ int build(blok_model *m) {
       memset(&ew, 0, sizeof(ew));
       ew.hidden = c.hidden; ew.inter = c.inter; ew.experts = c.experts; ew.topk = c.topk; ew.shared_inter = c.shared_inter;
       ew.routed_scale = c.routed_scale; ew.router_w = tp<uint16_t>(L.t, "router");
-      ew.router_bias = tp<float>(L.t, "router_bias"); ew.expert_base = 0; ew.experts_local = c.experts;
+      ew.router_bias = tp<float>(L.t, "router_bias"); ew.expert_base = m->ep_base; ew.experts_local = m->ep_local;
       ew.gate_w = tp<uint32_t>(L.t, "gate_w"); ew.gate_s = tp<uint16_t>(L.t, "gate_s");
       ew.up_w = tp<uint32_t>(L.t, "up_w"); ew.up_s = tp<uint16_t>(L.t, "up_s");
       ew.down_w = tp<uint32_t>(L.t, "down_w"); ew.down_s = tp<uint16_t>(L.t, "down_s");
       ew.shared_gate = tp<uint16_t>(L.t, "shared_gate"); ew.shared_up = tp<uint16_t>(L.t, "shared_up");
       ew.shared_down = tp<uint16_t>(L.t, "shared_down");
-      if ((rc = blok_moe_layer_create(&ew, m->moe_batched_ok ? m->rows : 1, &L.moe))) return rc;
+      // a sharded layer always runs its experts through the grouped kernels, which need the batched scratch
+      const int moe_rows = world > 1 ? (m->rows > 2 ? m->rows : 2) : (m->moe_batched_ok ? m->rows : 1);
+      if ((rc = blok_moe_layer_create(&ew, moe_rows, &L.moe))) return rc;
     }
   }
   void *p;
@@ -247,6 +309,21 @@ int build(blok_model *m) {
   if ((rc = dev_alloc(m, m->mlp_ws_bytes, &m->mlp_ws))) return rc;
   m->head_ws_bytes = blok_lm_head_workspace_bytes(c.vocab, c.max_batch);
   if ((rc = dev_alloc(m, m->head_ws_bytes, &m->head_ws))) return rc;
+  if (world > 1) {
+    if ((rc = dev_alloc(m, (size_t)m->rows * c.experts * 4, &p))) return rc; m->ep_logits = static_cast<float *>(p);
+    if ((rc = dev_alloc(m, (size_t)m->rows * c.topk * 2, &p))) return rc; m->ep_ids = static_cast<uint16_t *>(p);
+    if ((rc = dev_alloc(m, (size_t)m->rows * c.topk * 4, &p))) return rc; m->ep_local_ids = static_cast<int *>(p);
+    if ((rc = dev_alloc(m, (size_t)m->rows * c.topk * 4, &p))) return rc; m->ep_wts = static_cast<float *>(p);
+    if ((rc = dev_alloc(m, (size_t)m->rows * c.topk * 4, &p))) return rc; m->ep_rows = static_cast<int *>(p);
+    {
+      std::vector<int> rows_of((size_t)m->rows * c.topk);
+      for (size_t a = 0; a < rows_of.size(); ++a) rows_of[a] = (int)(a / c.topk);
+      BLOK_CUDA(cudaMemcpy(m->ep_rows, rows_of.data(), rows_of.size() * 4, cudaMemcpyHostToDevice));
+    }
+    if ((rc = dev_alloc(m, (size_t)m->rows * c.topk * c.hidden * 2, &p))) return rc; m->ep_y = static_cast<uint16_t *>(p);
+    if ((rc = dev_alloc(m, (size_t)m->rows * c.hidden * 4, &p))) return rc; m->ep_part = static_cast<float *>(p);
+    if ((rc = dev_alloc(m, (size_t)m->rows * c.hidden * 2, &p))) return rc; m->ep_shared = static_cast<uint16_t *>(p);
+  }
   BLOK_CUDA(cudaMemset(m->pos, 0, c.max_batch * 4));
   m->host_pos.assign(c.max_batch, 0);
   if (c.kv_page_rows > 0) {
@@ -304,11 +381,16 @@ extern "C" int blok_model_create_synthetic(const blok_model_config *cfg, uint64_
                cfg->kv_page_rows);
   BLOK_REQUIRE(cfg->first_dense == 0 || (cfg->dense_inter > 0 && cfg->dense_inter % 32 == 0), BLOK_ERR_SHAPE,
                "blok_model_create_synthetic: dense_inter %d must be a positive multiple of 32", cfg->dense_inter);
+  BLOK_REQUIRE(cfg->ep_world <= 1 || (cfg->ep_rank >= 0 && cfg->ep_rank < cfg->ep_world && cfg->experts % cfg->ep_world == 0 &&
+                                       cfg->hidden % 512 == 0 && cfg->inter % 512 == 0 && cfg->kv_page_rows == 0),
+               BLOK_ERR_SHAPE, "blok_model_create_synthetic: expert parallelism needs 0 <= ep_rank < ep_world, experts divisible "
+                               "by ep_world, hidden and inter multiples of 512 and a dense cache");
   blok_model *m = new (std::nothrow) blok_model();
   BLOK_REQUIRE(m, BLOK_ERR_ARG, "blok_model_create_synthetic: out of host memory");
   m->cfg = *cfg;
+  if (cfg->ep_world > 1) m->graphs_enabled = false;  // a step holds collectives: captured only when BLOK_MODEL_GRAPH=1 asks for it
+  if (const char *g = getenv("BLOK_MODEL_GRAPH")) m->graphs_enabled = strcmp(g, "0") != 0;
   m->seed = seed;
-  if (const char *g = getenv("BLOK_MODEL_GRAPH")) m->graphs_enabled = strcmp(g, "0") != 0;  // BLOK_MODEL_GRAPH=0: eager launches
   int rc = build(m);
   if (rc) {
     blok_model_destroy(m);
@@ -345,6 +427,39 @@ extern "C" int blok_model_refresh_derived(blok_model_t *m) {
   return BLOK_OK;
 }
 
+extern "C" int blok_model_set_comm(blok_model_t *m, blok_comm_t *comm) {
+  BLOK_REQUIRE(m && comm, BLOK_ERR_ARG, "blok_model_set_comm: null pointer");
+  BLOK_REQUIRE(m->cfg.ep_world > 1 && blok_comm_world(comm) == m->cfg.ep_world && blok_comm_rank(comm) == m->cfg.ep_rank, BLOK_ERR_STATE,
+               "blok_model_set_comm: the communicator is rank %d of %d, the model was created as rank %d of %d", blok_comm_rank(comm),
+               blok_comm_world(comm), m->cfg.ep_rank, m->cfg.ep_world);
+  m->comm = comm;
+  return BLOK_OK;
+}
+
+extern "C" int blok_model_check(blok_model_t *m, blok_stream_t stream) {
+  BLOK_REQUIRE(m, BLOK_ERR_ARG, "blok_model_check: null pointer");
+  int first = BLOK_OK;
+  std::string message;
+  for (size_t l = 0; l < m->layers.size(); ++l) {
+    auto &L = m->layers[l];
+    int rc = L.moe ? blok_moe_layer_check(L.moe, stream) : BLOK_OK;
+    if (rc == BLOK_OK && L.mla) rc = blok_mla_layer_check(L.mla, stream);
+    if (rc != BLOK_OK && first == BLOK_OK) {  // keep checking: every layer's error word is cleared by its check
+      first = rc;
+      message = "layer " + std::to_string(l) + ": " + blok_last_error();
+    }
+  }
+  if (first == BLOK_OK && m->comm) return blok_comm_check(m->comm);
+  if (first != BLOK_OK) set_error("%s", message.c_str());
+  return first;
+}
+
+extern "C" int blok_model_debug_set_layer_error(blok_model_t *m, int layer, unsigned code, blok_stream_t stream) {
+  BLOK_REQUIRE(m && layer >= 0 && layer < (int)m->layers.size() && m->layers[layer].moe, BLOK_ERR_ARG,
+               "blok_model_debug_set_layer_error: layer %d is not a MoE layer of this model", layer);
+  return blok_moe_layer_debug_set_error(m->layers[layer].moe, code, stream);
+}
+
 extern "C" int blok_model_reset(blok_model_t *m) {
   BLOK_REQUIRE(m, BLOK_ERR_ARG, "blok_model_reset: null pointer");
   BLOK_CUDA(cudaMemset(m->pos, 0, m->cfg.max_batch * 4));
@@ -353,6 +468,37 @@ extern "C" int blok_model_reset(blok_model_t *m) {
     if (m->pages) blok_kv_pages_release(m->pages, s);
   }
   return BLOK_OK;
+}
+
+// The MoE layer with the experts split over the ranks, for T rows that every rank holds alike (the attention block is
+// replicated): route (replicated, so all ranks agree without talking), run the selected experts this rank holds, add the
+// ranks' weighted sums with ONE all-reduce, round, add the shared expert (replicated).  m->n -> m->tmp.
+static int moe_sharded_rows(blok_model_t *m, blok::LayerWeights &L, int T, blok_stream_t stream_) {
+  const blok_model_config &c = m->cfg;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  BLOK_REQUIRE(m->comm, BLOK_ERR_STATE, "blok_model_step: a model with ep_world > 1 needs blok_model_set_comm first");
+  const uint16_t *router = tp<uint16_t>(L.t, "router");
+  int rc;
+  for (int t0 = 0; t0 < T; t0 += 8)
+    if ((rc = launch_bf16_gemv(router, m->n + (size_t)t0 * c.hidden, nullptr, m->ep_logits + (size_t)t0 * c.experts, c.experts, c.hidden,
+                               T - t0 < 8 ? T - t0 : 8, stream)))
+      return rc;
+  if ((rc = launch_router_topk(m->ep_logits, tp<float>(L.t, "router_bias"), T, c.experts, c.topk, c.routed_scale, m->ep_ids, m->ep_wts,
+                               m->ep_local_ids, m->ep_base, stream)))
+    return rc;
+  // assignments of experts held elsewhere carry ids outside [0, ep_local): the grouped kernels skip them
+  if ((rc = blok_moe_experts_grouped(L.moe, m->n, m->ep_rows, m->ep_local_ids, T * c.topk, m->ep_y, stream_))) return rc;
+  const dim3 grid((c.hidden / 2 + 255) / 256, T);
+  sharded_partial_kernel<<<grid, 256, 0, stream>>>(m->ep_y, m->ep_wts, m->ep_local_ids, m->ep_local, c.hidden, c.topk, m->ep_part);
+  if ((rc = launch_status("sharded_partial_kernel"))) return rc;
+  if ((rc = blok_comm_all_reduce_f32(m->comm, m->ep_part, (long)T * c.hidden, stream_))) return rc;
+  const uint16_t *shared = nullptr;
+  if (c.shared_inter > 0) {
+    if ((rc = blok_moe_shared(L.moe, m->n, T, m->ep_shared, stream_))) return rc;
+    shared = m->ep_shared;
+  }
+  sharded_finish_kernel<<<grid, 256, 0, stream>>>(m->ep_part, shared, c.hidden, m->tmp);
+  return launch_status("sharded_finish_kernel");
 }
 
 // The feed-forward half of layer l for T rows: m->n -> m->tmp (:829-877 without the residual add).  Steps of up to 8
@@ -374,6 +520,7 @@ static int ffn_rows(blok_model_t *m, int l, int T, bool chunk, blok_stream_t str
                          m->tmp + b * H, c.hidden, c.dense_inter, T - b < group ? T - b : group, m->mlp_ws, m->mlp_ws_bytes, stream_);
     return rc;
   }
+  if (c.ep_world > 1) return moe_sharded_rows(m, L, T, stream_);
   if (wide && m->moe_batched_ok) return blok_moe_batched(L.moe, m->n, T, m->tmp, nullptr, nullptr, stream_);
   for (int b = 0; b < T && !rc; ++b) rc = blok_moe_decode(L.moe, m->n + b * H, m->tmp + b * H, nullptr, nullptr, stream_);
   return rc;
@@ -594,7 +741,8 @@ extern "C" int blok_model_generate(blok_model_t *m, const uint32_t *prompt, int 
       BLOK_CUDA(cudaMemcpy(&next, m->next, 4, cudaMemcpyDeviceToHost));
     }
   }
-  return BLOK_OK;
+  // a bounded device-side wait that gave up (or a position outside a cache) in any layer makes the tokens void
+  return blok_model_check(m, nullptr);
 }
 
 // The serving loop of blok_model_generate_many over an existing batcher (the caller destroys it).
@@ -672,5 +820,5 @@ extern "C" int blok_model_generate_many(blok_model_t *m, const uint32_t *prompts
   if ((rc = blok_batcher_create(c.max_batch, c.kv_pages, c.kv_page_rows, c.max_ctx, &bt))) return rc;
   rc = serve_requests(m, bt, prompts, prompt_offsets, n_requests, max_new, out, n_out);
   blok_batcher_destroy(bt);
-  return rc;
+  return rc ? rc : blok_model_check(m, nullptr);
 }

@@ -208,8 +208,12 @@ extern "C" int blok_model_load_index(blok_model_t *model, const char *index_path
     if ((rc = blok_model_tensor(model, p.layer, p.model_name, &dst, &dst_bytes))) break;
     size_t slice = dst_bytes, at = 0;
     if (p.expert >= 0) {
-      slice = dst_bytes / cfg.experts;
-      at = slice * (size_t)p.expert;
+      // an expert-parallel rank holds experts [base, base + local) only: it reads those and skips the rest
+      const int world = cfg.ep_world > 1 ? cfg.ep_world : 1;
+      const int local = cfg.experts / world, base = (world > 1 ? cfg.ep_rank : 0) * local;
+      if (p.expert < base || p.expert >= base + local) continue;
+      slice = dst_bytes / local;
+      at = slice * (size_t)(p.expert - base);
     }
     const size_t want = p.widen_bf16_to_f32 ? slice / 2 : slice;
     if (p.t->data_bytes != want) {

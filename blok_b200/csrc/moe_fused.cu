@@ -9,39 +9,51 @@
 // with an atomic counter, so the load balances itself and nothing waits at a
 // phase boundary except where the data really is not there yet:
 //
-//   R   router logits, bf16               16 rows x 28 k-steps per chunk
+//   R   router logits, bf16               16 rows x 14 k-steps per chunk
 //   A   shared-expert gate/up, bf16       (8 gate + 8 up rows) x 28 k-steps
 //   B   the selected experts' INT4 gate/up (8 + 8 rows) x 14 k-blocks; needs the routing
 //   C1  INT4 down, one (slot, 16 output rows) block per chunk; needs that slot's mid values
 //   C2  shared-expert down, bf16          16 rows x 32 k-steps; needs the shared mid
 //
+// Weights stream through a warp-private cp.async ring in shared memory (each lane copies and
+// later reads back its own words, so the ring needs no barrier).  The INT4 chunks run on the
+// integer tensor-core consumer of i4_imma.cuh (nibbles taken as bytes, activations as 15-bit
+// block integers per scale group, exact int32 sums, scales applied per group in fp32): measured
+// with this ring on a 148-CTA grid it sustains 6.0-6.4 TB/s where the bf16-operand consumer of
+// i4_mma.cuh sustains 4.8-4.9 TB/s.
+//
 // A chunk covers a row-block only partly.  Its 16 partial dot products go to a
-// scratch slot indexed by the chunk's position in the row-block.  The warp that holds
-// the LAST chunk of a row-block in queue order is its finisher: it sums the slots in
-// index order and runs the row-block's epilogue: logits; SiLU*up -> mid; or, for the
+// scratch slot indexed by the chunk's position in the row-block, followed by one
+// release/acquire increment of the row-block's counter.  The warp whose increment completes
+// the row-block is its finisher (no warp ever waits for another chunk): it sums the slots in a
+// fixed order and runs the row-block's epilogue: logits; SiLU*up -> mid; or, for the
 // shared-expert down rows, the weighted combine of all nine contributions
 //   y = bf16(bf16(sum_k w_k * bf16(y_k)) + bf16(shared)).
 // Which warp computes a chunk varies from run to run; what is summed in which
 // order does not, so results are deterministic.
 //
-// Everything one warp hands to another (partial sums, logits, mid values, per-slot
-// outputs) travels as an 8-byte (value, tag) pair written with one store; the tag is
-// the launch's epoch.  A reader polls a slot until the tag matches, so there is no
-// fence, no arrival counter and no grid barrier: a down-projection chunk only waits
-// if the very mid values it needs are not written yet, and its weight loads are in
-// flight before it looks.  The routing is computed once per CTA from the tagged
-// logits.  Every poll is bounded and records an error word read by
-// blok_moe_layer_check; the launch is cooperative (all CTAs resident), so the warps
-// being waited for are always running.  Weights stream through a warp-private
-// cp.async ring in shared memory (each lane copies and later reads back its own
-// words, so the ring needs no barrier).
+// Hand-offs between warps:
+//  - counters only grow (the value expected in launch n is n times the per-launch count, modulo 2^32), so
+//    nothing is cleared between launches.
+//  - the router's per-expert scores, the routing and the per-slot down outputs travel as 8-byte
+//    (value, tag) pairs written with one store; the tag is the launch's epoch and a reader polls until
+//    the tag matches.
+//  - the mid vector of a slot (2,048 values, needed whole by every down chunk of the slot) is written
+//    plainly, 16 bytes per row-block, followed by a fence and one increment of the slot's counter
+//    (counters only grow: the value expected in launch n is n * row-blocks, modulo 2^32).  In every
+//    CTA the first warp that needs a slot waits for its counter, quantises the vector ONCE into
+//    shared memory for all 16 warps, and raises a shared-memory flag.
+// The router's finishers publish, per expert, the selection value and the score as tagged pairs; one warp per CTA derives
+// the routing from them when the CTA first needs it.  Every poll is bounded and records an
+// error word read by blok_moe_layer_check; the launch is cooperative (all CTAs resident), so the warps
+// being waited for are always running.
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 #include <vector>
 
 #include "bf16_mma.cuh"
-#include "i4_mma.cuh"
+#include "i4_imma.cuh"
 #include "moe_layer.h"
 #include "router_topk.cuh"
 
@@ -53,11 +65,14 @@ namespace blok {
 #ifndef BLOK_RING_DEPTH
 #define BLOK_RING_DEPTH 5
 #endif
-constexpr int kMetaBytes = 4;  // per scale group: the sum of x
+#ifndef BLOK_I4_UNROLL2
+#define BLOK_I4_UNROLL2 0
+#endif
 
 constexpr int kFusedWarps = BLOK_FUSED_WARPS;
 constexpr int kFusedThreads = kFusedWarps * 32;
-constexpr unsigned kSpinLimit = 1u << 22;  // polls before a wait gives up with an error word
+constexpr unsigned kSpinLimit = 1u << 20;  // polls (about a microsecond apart once backed off) before a wait gives up with an error word
+constexpr int kMaxTopk = 16;
 
 enum { CTRL_QUEUE = 0, CTRL_EXIT = 4, CTRL_ERROR = 5, CTRL_EPOCH = 6 };  // word indices in the control block
 constexpr int kTraceSlots = 16;
@@ -74,11 +89,14 @@ struct FusedParams {
   uint16_t *y;
   uint16_t *ids_out;
   float *wts_out;
-  uint2 *logits;   // [experts] (router logit, launch tag)
-  uint2 *mid;      // [topk + 1][mid_stride / 2] (two bf16 mid values, launch tag); row topk is the shared expert's
+  uint2 *logits;      // [2][experts] per expert (sel = sigmoid(logit) + bias, launch tag), then (sigmoid(logit), launch tag)
+  int r_local;        // 1: the chunks of a router row-block are exactly one CTA's first chunks and are reduced in shared memory
+  uint32_t *mid;      // [topk + 1][mid_stride / 2] bf16 pairs, plain; row topk is the shared expert's
+  unsigned *mid_cnt;  // [topk + 1] row-blocks of mid written so far, over all launches
   int mid_stride;
-  uint2 *ys;       // [topk + 1][hidden] (bf16-valued per-slot down output, launch tag)
-  uint2 *partR, *partA, *partB, *partC2;  // [row-block][chunk][16] (partial dot product, launch tag)
+  uint2 *ys;          // [topk][hidden] (bf16-valued per-slot down output, launch tag)
+  float *partR, *partA, *partB, *partC2;  // [row-block][chunk][16] partial dot products of the chunks of a row-block
+  unsigned *cntR, *cntA, *cntB, *cntC2;   // [row-block] chunks of the row-block handed in so far, over all launches
   // chunking: steps per row-block, steps per chunk, chunks per row-block
   int sprR, spcR, cprR;
   int sprA, spcA, cprA;
@@ -86,6 +104,7 @@ struct FusedParams {
   int sprC1;
   int sprC2, spcC2, cprC2;
   unsigned cA0, cB0, cC10, cC20, total;  // first queue index of each phase; queue length
+  float inv_cprR, inv_cprA, inv_cprB, inv_cprC2, inv_rbB, inv_rbC1;  // reciprocals of the divisors of the queue-index arithmetic
   unsigned *ctrl;
   long long *trace;  // optional: [0..15] launch-wide stamps, then [grid][kTraceSlots] per-CTA stamps (ns)
 };
@@ -102,31 +121,25 @@ __device__ __forceinline__ void trace_launch(const FusedParams &p, int slot) {
   if (p.trace) p.trace[slot] = global_ns();
 }
 
-// Results that one warp hands to another travel as (value, tag) pairs written with one
-// 8-byte store; the tag is the launch's epoch, so a reader that polls a slot until the
-// tag matches knows the value is this launch's, without any fence or counter.
+// A waiting warp must not eat the issue slots of the warps it waits for (it shares a scheduler with three others): every
+// poll loop sleeps between polls, longer each time, up to about a microsecond.
+__device__ __forceinline__ void backoff(unsigned &ns) {
+  __nanosleep(ns);
+  ns = min(ns * 2u, 1024u);
+}
+// q = a / b for small non-negative a (< 2^22), with inv = 1 / b as a float: no integer division in the per-chunk code.
+__device__ __forceinline__ int div_small(int a, float inv) { return (int)(((float)a + 0.5f) * inv); }
+
+// ---- tagged hand-offs ---------------------------------------------------------------------------
 __device__ __forceinline__ void st_tagged(uint2 *p, float v, unsigned tag) {
   asm volatile("st.global.cg.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
-}
-__device__ __forceinline__ float ld_tagged(const uint2 *p, unsigned tag, unsigned *err) {
-  unsigned v, tg, it = 0;
-  for (;;) {
-    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v), "=r"(tg) : "l"(p) : "memory");
-    if (tg == tag) break;
-    if (++it > kSpinLimit) {
-      atomicExch(err, 3u);
-      break;
-    }
-    __nanosleep(20);
-  }
-  return __uint_as_float(v);
 }
 // N tagged values at p[0], p[stride], ...: all loads are issued before any tag is looked at,
 // so the wait is one memory round trip, not N; the batch is re-read only while a tag is missing.
 template <int N>
-__device__ __noinline__ void ld_tagged_n(const uint2 *p, int stride, int n, unsigned tag, unsigned *err,
-                                            float (&out)[N]) {
+__device__ __forceinline__ void ld_tagged_n(const uint2 *p, int stride, int n, unsigned tag, unsigned *err, float (&out)[N]) {
   unsigned v[N], tg[N];
+  unsigned ns = 32;
   for (unsigned it = 0;; ++it) {
 #pragma unroll
     for (int i = 0; i < N; ++i)
@@ -140,10 +153,24 @@ __device__ __noinline__ void ld_tagged_n(const uint2 *p, int stride, int n, unsi
       atomicExch(err, 3u);
       break;
     }
-    __nanosleep(20);
+    backoff(ns);
   }
 #pragma unroll
   for (int i = 0; i < N; ++i) out[i] = i < n ? __uint_as_float(v[i]) : 0.f;
+}
+
+// Hands a chunk's results in: one release + acquire increment of the row-block's counter (the partial sums stored by the
+// warp's lanes before the __syncwarp are covered by it).  Returns the counter's value before the increment.
+__device__ __forceinline__ unsigned arrive_counter(unsigned *cnt) {
+  unsigned old;
+  asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(cnt) : "memory");
+  return old;
+}
+
+__device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned *p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
 }
 
 __device__ __forceinline__ float swiglu_ref_rounding(float g, float u) {
@@ -198,12 +225,12 @@ struct Chunk {
 
 __device__ __forceinline__ bool kind_is_i4(int kind) { return kind == KIND_B || kind == KIND_C1; }
 
-__device__ __forceinline__ void ring_issue(const Chunk &ch, int s, uint32_t ring, int lane) {
-  if (s < ch.n) {
-    const int t = lane & 3;
+// w_lo / w_hi: the lane's two weight rows at the chunk's first step (+ t), n: steps of the chunk
+__device__ __forceinline__ void ring_issue(const uint4 *w_lo, const uint4 *w_hi, int n, int s, uint32_t ring, int lane) {
+  if (s < n) {
     const uint32_t base = ring + (uint32_t)(s % kRingDepth) * kRingStepBytes + (uint32_t)lane * 16;
-    cp_async16(base, ch.w_lo + (size_t)(ch.k0 + s) * 4 + t);
-    cp_async16(base + 512, ch.w_hi + (size_t)(ch.k0 + s) * 4 + t);
+    cp_async16(base, w_lo + (size_t)s * 4);
+    cp_async16(base + 512, w_hi + (size_t)s * 4);
   }
   cp_async_commit();
 }
@@ -212,8 +239,9 @@ __device__ __forceinline__ void ring_issue(const Chunk &ch, int s, uint32_t ring
 __device__ __forceinline__ void scale_issue(const Chunk &ch, uint32_t ring, int lane) {
   const uint32_t stage = ring + kRingDepth * kRingStepBytes;
   const int pieces = 16 * ch.n;
+  const float inv_n = 1.0f / (float)ch.n;
   for (int pc = lane; pc < pieces; pc += 32) {
-    const int row = pc / ch.n, s = pc - row * ch.n;
+    const int row = div_small(pc, inv_n), s = pc - row * ch.n;
     const uint16_t *src = ((row & 8) ? ch.s_hi : ch.s_lo) + (size_t)(row & 7) * ch.s_stride + (size_t)(ch.k0 + s) * 4;
     cp_async8(stage + (uint32_t)(row * kScaleRowBytes + s * 8), src);
   }
@@ -222,119 +250,314 @@ __device__ __forceinline__ void scale_issue(const Chunk &ch, uint32_t ring, int 
 __device__ __forceinline__ void ring_prologue(const Chunk &ch, uint32_t ring, int lane) {
   __syncwarp();  // every lane is done with the previous chunk's scales
   if (kind_is_i4(ch.kind)) scale_issue(ch, ring, lane);  // joins the first step's commit group
+  const uint4 *w_lo = ch.w_lo + (size_t)ch.k0 * 4 + (lane & 3), *w_hi = ch.w_hi + (size_t)ch.k0 * 4 + (lane & 3);
 #pragma unroll
-  for (int i = 0; i < kRingDepth; ++i) ring_issue(ch, i, ring, lane);
+  for (int i = 0; i < kRingDepth; ++i) ring_issue(w_lo, w_hi, ch.n, i, ring, lane);
 }
 
-// Consumes the chunk's steps from the ring (issuing the steps beyond the prologue
-// as slots free up) and returns the chunk's partial dot product for A row
-// g + 8*(t>>1).  xfrag/xsum (INT4) or xrow (bf16) address the activation segment,
-// whose first step is kx0.
-__device__ __forceinline__ float ring_consume(const Chunk &ch, uint32_t ring, const unsigned char *ring_ptr,
-                                              const XFragLane &xl, const float *xsum, const uint4 *xrow, int kx0,
-                                              int lane) {
-  const int t = lane & 3;
-  const bool hi_row = (t >> 1) != 0;
-  const int j0 = 2 * (t & 1);
-  float acc = 0.f;
+// The two streaming loops are kept out of line with plain arguments: they then get registers of their own, and what the
+// chunk-level code around them keeps alive is saved once per chunk, not spilled inside the loops.
+//
+// bf16 weights: the chunk's partial dot product for A row g + 8 * (t >> 1).  w_lo / w_hi: the lane's weight rows at the
+// chunk's first step (+ t); xrow: the activations of that step (bf16, natural order, + t).
+// What a streaming loop hands back: the chunk's partial dot product and, in lane 0, the warp's next queue index.  The index
+// is drawn when only a ring's worth of steps is left, not a whole chunk ahead: a chunk that has been handed out is then
+// being worked on within one chunk's time, which is what every dependent (the routing, a slot's mid vector) waits for.
+struct Consumed {
+  float v;
+  unsigned next;
+};
+__device__ __forceinline__ void draw_next(int s, int n, unsigned *queue, unsigned W, int lane, unsigned &next) {
+  if (s == max(n - kRingDepth - 2, 0) && lane == 0) next = W + atomicAdd(queue, 1u);
+}
+
+__device__ __noinline__ Consumed consume_bf16(const uint4 *w_lo, const uint4 *w_hi, int n, uint32_t ring, const unsigned char *ring_ptr,
+                                              const uint4 *xrow, unsigned *queue, unsigned W, int lane) {
   float d[4] = {0.f, 0.f, 0.f, 0.f};
-  const bool i4 = kind_is_i4(ch.kind);
-  // this lane post-scales groups (j0, j0 + 1) of A row g + 8 * (t >> 1)
-  const unsigned char *sc_lane = ring_ptr + kRingDepth * kRingStepBytes + ((lane >> 2) + 8 * (t >> 1)) * kScaleRowBytes + (t & 1) * 4;
-  for (int s = 0; s < ch.n; ++s) {
+  unsigned next = 0;
+  for (int s = 0; s < n; ++s) {
+    draw_next(s, n, queue, W, lane, next);
     cp_async_wait<kRingDepth - 1>();
-    if (s == 0) __syncwarp();  // the scales were copied by other lanes: their first group has landed as well
     const unsigned char *slotp = ring_ptr + (size_t)(s % kRingDepth) * kRingStepBytes;
     const uint4 wl = *reinterpret_cast<const uint4 *>(slotp + lane * 16);
     const uint4 wh = *reinterpret_cast<const uint4 *>(slotp + 512 + lane * 16);
-    const int kx = ch.k0 - kx0 + s;
-    if (i4) {
-      const uint32_t sc = *reinterpret_cast<const uint32_t *>(sc_lane + s * 8);
-      float dd[4] = {0.f, 0.f, 0.f, 0.f};
-      i4_kblock_mma(wl, wh, xl.ptr + kx * xl.kb_stride, dd);
-      const float2 xs = *reinterpret_cast<const float2 *>(xsum + kx * 4 + j0);
-      const float da = hi_row ? dd[2] : dd[0];
-      const float db = hi_row ? dd[3] : dd[1];
-      acc = fmaf(bf16lo(sc), fmaf(-kNibOffset, xs.x, da), acc);
-      acc = fmaf(bf16hi(sc), fmaf(-kNibOffset, xs.y, db), acc);
-    } else {
-      const uint4 xb = xrow[kx * 4];
-      mma_bf16_16816(d, wl.x, wh.x, wl.y, wh.y, xb.x, xb.y);
-      mma_bf16_16816(d, wl.z, wh.z, wl.w, wh.w, xb.z, xb.w);
-    }
-    ring_issue(ch, s + kRingDepth, ring, lane);
+    const uint4 xb = xrow[s * 4];
+    mma_bf16_16816(d, wl.x, wh.x, wl.y, wh.y, xb.x, xb.y);
+    mma_bf16_16816(d, wl.z, wh.z, wl.w, wh.w, xb.z, xb.w);
+    ring_issue(w_lo, w_hi, n, s + kRingDepth, ring, lane);
   }
-  if (i4) {
-    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-    return acc;
-  }
-  return (t & 2) ? d[2] : d[0];
+  return Consumed{(lane & 2) ? d[2] : d[0], next};
 }
 
-// Up to NU tagged 32-byte units (8 mid values each) at p, p + stride, ...: loads first, tags after.
-template <int NU>
-__device__ __forceinline__ void ld_tagged_units(const uint2 *p, int stride, int n, unsigned tag, unsigned *err,
-                                                uint4 (&out)[NU]) {
-  unsigned r[NU][8];
-  for (unsigned it = 0;; ++it) {
-#pragma unroll
-    for (int i = 0; i < NU; ++i)
-      if (i < n) {
-        const uint2 *q = p + (size_t)i * stride;
-        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(r[i][0]), "=r"(r[i][1]), "=r"(r[i][2]), "=r"(r[i][3]) : "l"(q) : "memory");
-        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(r[i][4]), "=r"(r[i][5]), "=r"(r[i][6]), "=r"(r[i][7]) : "l"(q + 2) : "memory");
-      }
-    bool ok = true;
-#pragma unroll
-    for (int i = 0; i < NU; ++i)
-      if (i < n && (r[i][1] != tag || r[i][3] != tag || r[i][5] != tag || r[i][7] != tag)) ok = false;
-    if (ok) break;
-    if (it > kSpinLimit) {
-      atomicExch(err, 4u);
-      break;
-    }
-    __nanosleep(20);
+// INT4 weights on the integer tensor-core consumer: activations staged by imma_stage_unit (bytes, per-group meta).
+// xp: the lane's operand words of the chunk's first k-block (stride xstride uint4 per k-block); meta: that k-block's
+// groups.  Every lane post-scales its own scale group (t) of rows g and g + 8; the quad is summed at the end.
+// Returns the chunk's partial dot product: row g in lanes t < 2, row g + 8 in lanes t >= 2.
+__device__ __noinline__ Consumed consume_i4(const uint4 *w_lo, const uint4 *w_hi, int n, uint32_t ring, const unsigned char *ring_ptr,
+                                            const uint4 *xp, int xstride, const uint2 *meta, unsigned *queue, unsigned W, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  float acc_lo = 0.f, acc_hi = 0.f, acc_lo1 = 0.f, acc_hi1 = 0.f;
+  unsigned next = 0;
+  const unsigned char *sc_lo = ring_ptr + kRingDepth * kRingStepBytes + g * kScaleRowBytes + t * 2;
+  const unsigned char *sc_hi = sc_lo + 8 * kScaleRowBytes;
+  meta += t;
+  // two k-blocks per turn: their unpacking, MMAs and post-scaling are independent instruction streams, which is what a
+  // warp that issues one instruction every dozen cycles needs
+  int s = 0;
+#if BLOK_I4_UNROLL2
+  for (; s + 1 < n; s += 2) {
+    draw_next(s, n, queue, W, lane, next);
+    draw_next(s + 1, n, queue, W, lane, next);
+    cp_async_wait<kRingDepth - 2>();
+    if (s == 0) __syncwarp();  // the scales were copied by other lanes: their first group has landed as well
+    const unsigned char *slot0 = ring_ptr + (size_t)(s % kRingDepth) * kRingStepBytes;
+    const unsigned char *slot1 = ring_ptr + (size_t)((s + 1) % kRingDepth) * kRingStepBytes;
+    const uint4 wl0 = *reinterpret_cast<const uint4 *>(slot0 + lane * 16);
+    const uint4 wh0 = *reinterpret_cast<const uint4 *>(slot0 + 512 + lane * 16);
+    const uint4 wl1 = *reinterpret_cast<const uint4 *>(slot1 + lane * 16);
+    const uint4 wh1 = *reinterpret_cast<const uint4 *>(slot1 + 512 + lane * 16);
+    const float s_lo0 = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(sc_lo + s * 8));
+    const float s_hi0 = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(sc_hi + s * 8));
+    const float s_lo1 = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(sc_lo + s * 8 + 8));
+    const float s_hi1 = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(sc_hi + s * 8 + 8));
+    int d0[4] = {0, 0, 0, 0}, d1[4] = {0, 0, 0, 0};
+    imma_kblock(wl0, wh0, xp + s * xstride, d0);
+    imma_kblock(wl1, wh1, xp + (s + 1) * xstride, d1);
+    imma_post(d0, meta[s * 4], s_lo0, s_hi0, acc_lo, acc_hi);
+    imma_post(d1, meta[s * 4 + 4], s_lo1, s_hi1, acc_lo1, acc_hi1);
+    ring_issue(w_lo, w_hi, n, s + kRingDepth, ring, lane);
+    ring_issue(w_lo, w_hi, n, s + 1 + kRingDepth, ring, lane);
   }
-#pragma unroll
-  for (int i = 0; i < NU; ++i) out[i] = make_uint4(r[i][0], r[i][2], r[i][4], r[i][6]);
+#endif
+  for (; s < n; ++s) {  // one k-block per turn (and an odd last step)
+    draw_next(s, n, queue, W, lane, next);
+    cp_async_wait<kRingDepth - 1>();
+    if (s == 0) __syncwarp();
+    const unsigned char *slotp = ring_ptr + (size_t)(s % kRingDepth) * kRingStepBytes;
+    const uint4 wl = *reinterpret_cast<const uint4 *>(slotp + lane * 16);
+    const uint4 wh = *reinterpret_cast<const uint4 *>(slotp + 512 + lane * 16);
+    const float s_lo = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(sc_lo + s * 8));
+    const float s_hi = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(sc_hi + s * 8));
+    int di[4] = {0, 0, 0, 0};
+    imma_kblock(wl, wh, xp + s * xstride, di);
+    imma_post(di, meta[s * 4], s_lo, s_hi, acc_lo, acc_hi);
+    ring_issue(w_lo, w_hi, n, s + kRingDepth, ring, lane);
+  }
+  acc_lo += acc_lo1;
+  acc_hi += acc_hi1;
+  acc_lo += __shfl_xor_sync(0xffffffffu, acc_lo, 1);
+  acc_lo += __shfl_xor_sync(0xffffffffu, acc_lo, 2);
+  acc_hi += __shfl_xor_sync(0xffffffffu, acc_hi, 1);
+  acc_hi += __shfl_xor_sync(0xffffffffu, acc_hi, 2);
+  return Consumed{(t & 2) ? acc_hi : acc_lo, next};
 }
 
-// Partial sums a finisher requests per round trip when it collects a row-block, and tagged 32-byte units a lane
-// requests per round trip when it stages mid values (8 and 4 were measured slower: they spill).
-constexpr int kCollect = 4;
-constexpr int kStageUnits = 2;
-
-// One warp stages `cols` mid values (tagged pairs written earlier in this launch by other
-// warps; values that are not there yet are polled) into INT4 fragment order with group sums.
-__device__ __noinline__ void warp_stage_i4(const uint2 *src, uint4 *xfrag, float *xsum, int cols, int lane,
-                                              unsigned epoch, unsigned *err) {
-  const int units = cols / 8;  // 32-byte tagged units; lane handles units lane, lane + 32, ...
-  // kStageUnits units per lane are requested before any tag is looked at: one L2 round trip per kStageUnits * 32 units
-  for (int u0 = lane; u0 < units; u0 += 32 * kStageUnits) {
-    uint4 vv[kStageUnits];
-    const int n = min(kStageUnits, (units - u0 + 31) / 32);
-    ld_tagged_units<kStageUnits>(src + (size_t)u0 * 4, 32 * 4, n, epoch, err, vv);
-#pragma unroll
-    for (int j = 0; j < kStageUnits; ++j) {
-      const int u = u0 + 32 * j;
-      if (u < units) {  // units is a multiple of 32, so this is warp-uniform
-        const uint4 v = vv[j];
-        int kb = u >> 4, t = (u >> 2) & 3, i = u & 3;
-        uint4 o;
-        o.x = __byte_perm(v.x, v.z, 0x5410);
-        o.y = __byte_perm(v.x, v.z, 0x7632);
-        o.z = __byte_perm(v.y, v.w, 0x5410);
-        o.w = __byte_perm(v.y, v.w, 0x7632);
-        xfrag[kb * 16 + i * 4 + t] = o;
-        float s = ((bf16lo(v.x) + bf16hi(v.x)) + (bf16lo(v.y) + bf16hi(v.y))) +
-                  ((bf16lo(v.z) + bf16hi(v.z)) + (bf16lo(v.w) + bf16hi(v.w)));
-        s += __shfl_xor_sync(0xffffffffu, s, 1);
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        if ((u & 3) == 0) xsum[u >> 2] = s;
+// Shared-memory flag of something one warp of the CTA prepares for all: 0 nobody has it, 1 in progress, 2 ready.
+// Returns true to exactly one warp (the one that has to prepare it); the others return false once it is ready.
+__device__ __forceinline__ bool claim_or_wait(int *state, int lane, unsigned *err, unsigned code) {
+  int st = 0;
+  if (lane == 0) st = atomicCAS(state, 0, 1);
+  st = __shfl_sync(0xffffffffu, st, 0);
+  if (st == 0) return true;
+  if (st == 1) {
+    if (lane == 0) {
+      unsigned it = 0, ns = 64;
+      while (*reinterpret_cast<volatile int *>(state) != 2) {
+        if (++it > kSpinLimit) {
+          atomicExch(err, code);
+          break;
+        }
+        backoff(ns);
       }
+    }
+    __syncwarp();
+  }
+  __threadfence_block();
+  return false;
+}
+__device__ __forceinline__ void publish(int *state, int lane) {
+  __threadfence_block();
+  __syncwarp();
+  if (lane == 0) atomicExch(state, 2);
+}
+
+// ---- the rare, register-hungry parts, kept out of line so that the streaming loops keep their registers ----------
+
+// The routing (src/kimi_exec.cu:382-397): k rounds of argmax over sel = sigmoid(logit) + bias with strict '>' scanning
+// ascending indices, so the lowest index wins a tie and NaN is never chosen; weights s / (sum + 1e-20) * routed_scale, the
+// sum taken in selection order.  The router's finishers publish sel and s per expert as tagged values; one warp per CTA
+// (the first that needs the routing) derives it from them: same inputs, same rule, so every CTA selects the same experts,
+// and no CTA waits for another to publish a result.  Lane l keeps experts l, l + 32, ... in registers together with its
+// own best; a round is one butterfly over the lanes' bests, and only the winning lane looks for its next best.
+template <int NREG>  // candidates per lane: experts <= 32 * NREG
+__device__ __noinline__ void routing_from_scores(const uint2 *sel_t, const uint2 *score_t, int *w_ids, float *w_wts, uint16_t *ids_out,
+                                                 float *wts_out, int experts, int topk, float routed_scale, unsigned epoch, unsigned *err,
+                                                 int lane) {
+  float sel[NREG];
+  {
+    const int n = max(0, min(NREG, (experts - lane + 31) / 32));
+    ld_tagged_n<NREG>(sel_t + lane, 32, n, epoch, err, sel);  // all of the lane's candidates in one round trip
+#pragma unroll
+    for (int j = 0; j < NREG; ++j)
+      if (j >= n) sel[j] = -INFINITY;
+  }
+  float lb = -INFINITY;  // this lane's best candidate and its register
+  int lj = -1;
+#pragma unroll
+  for (int j = 0; j < NREG; ++j)
+    if (sel[j] > lb) lb = sel[j], lj = j;
+  int my_id = 0;
+  unsigned s_bits = 0, s_tag = epoch;
+  for (int k = 0; k < topk; ++k) {
+    float best = lb;
+    int id = lj >= 0 ? lane + 32 * lj : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, id, o);
+      if (ob > best || (ob == best && oi < id)) best = ob, id = oi;
+    }
+    const bool mine = lj >= 0 && id == lane + 32 * lj;
+    if (id == 0x7fffffff) id = 0;  // every candidate left is -inf or NaN: the reference keeps id 0
+    if (lane == k) {  // the winner's score is requested now and looked at after the last round
+      my_id = id;
+      asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(s_bits), "=r"(s_tag) : "l"(score_t + id) : "memory");
+    }
+    if (mine) {  // the chosen one leaves the pool; its lane finds its next best
+      lb = -INFINITY;
+      const int gone = lj;
+      lj = -1;
+#pragma unroll
+      for (int j = 0; j < NREG; ++j) {
+        if (j == gone) sel[j] = -INFINITY;
+        if (sel[j] > lb) lb = sel[j], lj = j;
+      }
+    }
+  }
+  float my_s = __uint_as_float(s_bits);
+  if (lane < topk && s_tag != epoch) {  // sel was there but its score's store had not landed yet: wait for it
+    float v[1];
+    ld_tagged_n<1>(score_t + my_id, 0, 1, epoch, err, v);
+    my_s = v[0];
+  }
+  if (lane >= topk) my_s = 0.f;
+  float sum = 0.f;
+  for (int k = 0; k < topk; ++k) sum += __shfl_sync(0xffffffffu, my_s, k);  // selection order, as the reference adds
+  const float my_w = my_s / (sum + 1.0e-20f) * routed_scale;
+  if (lane < topk) {
+    w_ids[lane] = my_id;
+    w_wts[lane] = my_w;
+    if (ids_out) ids_out[lane] = (uint16_t)my_id;
+    if (wts_out) wts_out[lane] = my_w;
+  }
+}
+
+// x -> shared memory: bf16 as it lies (operand of the bf16 chunks) and block integers (operand of the INT4 gate/up chunks).
+// A thread's loads are all issued before anything is done with them: one memory round trip for the whole vector.
+__device__ __noinline__ void stage_x_both(const uint16_t *x, uint4 *xnat, unsigned char *xq, uint2 *meta, uint4 *zero, int hidden, int tid) {
+  const int units = hidden / 8;  // a multiple of 32: the four units of a scale group sit in four adjacent, live lanes
+  const uint4 *src = reinterpret_cast<const uint4 *>(x);
+  for (int u0 = 0; u0 < units; u0 += 2 * kFusedThreads) {
+    const int ua = u0 + tid, ub = ua + kFusedThreads;
+    const bool la = ua < units, lb = ub < units;
+    const uint4 va = la ? src[ua] : make_uint4(0, 0, 0, 0);
+    const uint4 vb = lb ? src[ub] : make_uint4(0, 0, 0, 0);
+    if (la) xnat[ua] = va;
+    if (lb) xnat[ub] = vb;
+    imma_stage_unit(va, ua, la, xq, meta);
+    imma_stage_unit(vb, ub, lb, xq, meta);
+  }
+  for (int u = tid; u < 8; u += kFusedThreads) zero[u] = make_uint4(0, 0, 0, 0);
+}
+
+// Waits until `row_blocks` more row-blocks of a slot's mid vector have been written in this launch.
+__device__ __forceinline__ void wait_mid_counter(const unsigned *cnt, int row_blocks, unsigned epoch, unsigned *err, int lane) {
+  if (lane == 0) {
+    const unsigned want = epoch * (unsigned)row_blocks;  // counters only grow; modulo 2^32 like the epoch itself
+    unsigned it = 0, ns = 64;
+    while ((int)(ld_acquire_gpu(cnt) - want) < 0) {
+      if (++it > kSpinLimit) {
+        atomicExch(err, 2u);
+        break;
+      }
+      backoff(ns);
     }
   }
   __syncwarp();
+}
+
+// A routed slot's mid vector -> block integers in shared memory (one warp, once per CTA and slot).
+__device__ __noinline__ void stage_mid_i4(const unsigned *cnt, const uint32_t *mid_row, int inter, unsigned char *dst, unsigned epoch,
+                                          unsigned *err, int lane) {
+  wait_mid_counter(cnt, inter / 8, epoch, err, lane);
+  const uint4 *src = reinterpret_cast<const uint4 *>(mid_row);
+  uint2 *meta = reinterpret_cast<uint2 *>(dst + (size_t)inter * 2);
+  const int units = inter / 8;  // a multiple of 32: a scale group's four units sit in four adjacent lanes
+  for (int u = lane; u < units; u += 32) imma_stage_unit(__ldcg(src + u), u, true, dst, meta);
+}
+
+// The shared expert's mid vector, bf16 as it lies.
+__device__ __noinline__ void stage_mid_bf16(const unsigned *cnt, const uint32_t *mid_row, int shared_inter, uint4 *smid, unsigned epoch,
+                                            unsigned *err, int lane) {
+  wait_mid_counter(cnt, shared_inter / 8, epoch, err, lane);
+  const uint4 *src = reinterpret_cast<const uint4 *>(mid_row);
+  for (int u = lane; u < shared_inter / 8; u += 32) smid[u] = __ldcg(src + u);
+}
+
+// out rows [ob*16, +16): every slot's contribution (tagged) weighted in slot order, plus the shared expert's
+__device__ __noinline__ void combine_rows(const uint2 *ys, uint16_t *y, int hidden, int topk, bool has_shared, const float *w_wts, int ob,
+                                          float shared_val, unsigned epoch, unsigned *err, int lane) {
+  if (lane < 16) {
+    float o = 0.f;
+    for (int k0 = 0; k0 < topk; k0 += 8) {
+      float yk[8];
+      const int n = min(8, topk - k0);
+      ld_tagged_n<8>(ys + (size_t)k0 * hidden + ob * 16 + lane, hidden, n, epoch, err, yk);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j < n) o = fmaf(yk[j], w_wts[k0 + j], o);
+    }
+    o = round_bf16(o);
+    if (has_shared) o = round_bf16(o + shared_val);
+    y[ob * 16 + lane] = f32_to_bf16_bits(o);
+  }
+}
+
+// The warp that hands in the LAST chunk of a row-block (it learns so from the row-block's counter) is its finisher: every
+// chunk's partial sums are in memory by then (each was followed by a release on the counter), and it adds them in chunk
+// order: lane (half, row) takes chunks half, half + 2, ..., the two halves are added last.  Lanes 0..15 return the rows.
+__device__ __noinline__ float collect_row_block(const float *part_rb, int np, int lane) {
+  const int half = lane >> 4, row = lane & 15;
+  const float *src = part_rb + row;
+  float s = 0.f;
+  for (int i0 = half; i0 < np; i0 += 32) {
+    float pv[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) pv[j] = i0 + 2 * j < np ? __ldcg(src + (size_t)(i0 + 2 * j) * 16) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) s += pv[j];
+  }
+  return s + __shfl_down_sync(0xffffffffu, s, 16);
+}
+
+// Epilogue of a gate/up row-block: rows 0..7 gate, 8..15 up (lanes 0..15 of `total`) -> eight mid values = 16 bytes,
+// written by one lane, then a fence and the slot's counter.  Returns the counter's value before the increment (lane 0).
+__device__ __noinline__ unsigned publish_mid(float total, uint32_t *dst, unsigned *cnt, int lane) {
+  const float up = __shfl_down_sync(0xffffffffu, total, 8);
+  const uint32_t m = f32_to_bf16_bits(swiglu_ref_rounding(total, up));
+  const uint32_t pair = m | (__shfl_down_sync(0xffffffffu, m, 1) << 16);  // lanes 0, 2, 4, 6 hold the pairs
+  uint4 out;
+  out.x = __shfl_sync(0xffffffffu, pair, 0);
+  out.y = __shfl_sync(0xffffffffu, pair, 2);
+  out.z = __shfl_sync(0xffffffffu, pair, 4);
+  out.w = __shfl_sync(0xffffffffu, pair, 6);
+  unsigned before = 0;
+  if (lane == 0) {
+    *reinterpret_cast<uint4 *>(dst) = out;
+    __threadfence();
+    before = atomicAdd(cnt, 1u);
+  }
+  return before;
 }
 
 __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(const FusedParams p) {
@@ -344,62 +567,40 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
 
   // ---- shared memory carve-up -------------------------------------------------
   unsigned char *sp = smem;
-  uint4 *xnat = reinterpret_cast<uint4 *>(sp);  // x, natural order (bf16 operand)
+  uint4 *xnat = reinterpret_cast<uint4 *>(sp);  // x, natural order (bf16 operand of R and A)
   sp += (size_t)p.hidden * 2;
-  uint4 *xfrag = reinterpret_cast<uint4 *>(sp);  // x, INT4 fragment order
-  sp += (size_t)p.hidden * 2;
-  // what the non-supplying lanes of an INT4 mma read: 256 bytes, entered 64 bytes in so that they fall on the other
-  // half of the banks than the fragment words the supplying lanes read in the same 8-lane phase
-  uint4 *zero = reinterpret_cast<uint4 *>(sp);
-  sp += 384;
-  float *xsum = reinterpret_cast<float *>(sp);  // per scale group: the sum of x, or (factor, offset) of the integer form
-  sp += (size_t)(p.hidden / 32) * kMetaBytes;
+  ImmaStage xq = imma_stage_carve(sp, p.hidden);  // x as block integers (operand of B); its zero region serves every INT4 chunk
+  sp += imma_stage_bytes(p.hidden);
+  const size_t midq_bytes = (size_t)p.inter * 2 + (size_t)(p.inter / 32) * 8;
+  unsigned char *midq = sp;  // [topk] a slot's mid vector as block integers (operand of C1), staged once per CTA
+  sp += (size_t)p.topk * midq_bytes;
+  uint4 *smid = reinterpret_cast<uint4 *>(sp);  // the shared expert's mid, bf16 natural order (operand of C2)
+  sp += (size_t)p.shared_inter * 2;
   unsigned char *ring_ptr = sp + (size_t)warp * kWarpRingBytes;  // this warp's weight ring, then its scale stage
   sp += (size_t)kFusedWarps * kWarpRingBytes;
-  const size_t wstage_bytes = (size_t)p.inter * 2 + (size_t)(p.inter / 32) * kMetaBytes;
-  unsigned char *wstage = sp + (size_t)warp * wstage_bytes;  // this warp's private segment of mid
-  sp += (size_t)kFusedWarps * wstage_bytes;
-  int *w_ids = reinterpret_cast<int *>(sp);  // the CTA's copy of the routing
-  sp += (size_t)kFusedWarps * 16 * 4;
-  float *w_wts = reinterpret_cast<float *>(sp);
-  sp += (size_t)kFusedWarps * 16 * 4;
-  __shared__ int s_route_state;  // 0 nobody has it, 1 one warp is computing it, 2 ready
-  if (tid == 0) s_route_state = 0;
-  float *s_score = reinterpret_cast<float *>(sp);  // top-k scratch (one warp of the grid uses it)
-  float *s_sel = s_score + p.experts;
+  __shared__ int w_ids[kMaxTopk];    // the CTA's copy of the routing
+  __shared__ float w_wts[kMaxTopk];
+  __shared__ float s_rpart[kFusedWarps][16];  // router row-block reduced inside the CTA (r_local)
+  __shared__ int s_rcount;
+  __shared__ int s_route_state;
+  __shared__ int s_mid_state[kMaxTopk + 1];  // [slot]; entry topk is the shared expert's mid
+  if (tid == 0) s_route_state = 0, s_rcount = 0;
+  if (tid <= kMaxTopk) s_mid_state[tid] = 0;
   const uint32_t ring = (uint32_t)__cvta_generic_to_shared(ring_ptr);
-
-  if (tid == 0) trace_cta(p, 0);
-  for (int u = tid; u < p.hidden / 8; u += kFusedThreads) xnat[u] = reinterpret_cast<const uint4 *>(p.x)[u];
-  {
-    I4Stage st;
-    st.xfrag = xfrag;
-    st.zero = zero;
-    st.xsum = xsum;
-    stage_x_i4<false>(reinterpret_cast<const uint4 *>(p.x), st, p.hidden, 1, tid, kFusedThreads);
-  }
-  __syncthreads();
-  if (tid == 0) trace_cta(p, 1);
-
-  const bool supply = (t == (g & 3));
-  XFragLane xl_x;  // fragments of x
-  xl_x.ptr = supply ? xfrag + t : zero + 4 + t;
-  xl_x.kb_stride = supply ? 16 : 0;
-  XFragLane xl_m;  // fragments of this warp's staged mid
-  xl_m.ptr = supply ? reinterpret_cast<const uint4 *>(wstage) + t : zero + 4 + t;
-  xl_m.kb_stride = supply ? 16 : 0;
-  float *msum = reinterpret_cast<float *>(wstage + (size_t)p.inter * 2);
 
   const unsigned epoch = p.ctrl[CTRL_EPOCH] + 1u;  // stable during the launch; the last CTA to leave bumps it
   unsigned *const err = p.ctrl + CTRL_ERROR;
   bool have_routing = false;
+  if (tid == 0) trace_cta(p, 0);
 
   // Queue index -> chunk.  B and C1 chunks need the routing (w_ids) to be in hand.
   auto decode = [&](unsigned c) {
     Chunk ch;
+    ch.s_lo = ch.s_hi = nullptr;
+    ch.s_stride = 0;
     if (c < p.cA0) {
       ch.kind = KIND_R;
-      ch.rb = (int)c / p.cprR;
+      ch.rb = div_small((int)c, p.inv_cprR);
       ch.kc = (int)c - ch.rb * p.cprR;
       ch.k0 = ch.kc * p.spcR;
       ch.n = min(p.spcR, p.sprR - ch.k0);
@@ -407,12 +608,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
       const size_t wrow = p.hidden / 8;
       ch.w_lo = reinterpret_cast<const uint4 *>(p.router_w) + (size_t)(ch.rb * 16 + g) * wrow;
       ch.w_hi = ch.w_lo + 8 * wrow;
-      ch.s_lo = ch.s_hi = nullptr;
-      ch.s_stride = 0;
     } else if (c < p.cB0) {
       const int ci = (int)(c - p.cA0);
       ch.kind = KIND_A;
-      ch.rb = ci / p.cprA;
+      ch.rb = div_small(ci, p.inv_cprA);
       ch.kc = ci - ch.rb * p.cprA;
       ch.k0 = ch.kc * p.spcA;
       ch.n = min(p.spcA, p.sprA - ch.k0);
@@ -420,17 +619,15 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
       const size_t wrow = p.hidden / 8;
       ch.w_lo = reinterpret_cast<const uint4 *>(p.shared_gate) + (size_t)(ch.rb * 8 + g) * wrow;
       ch.w_hi = reinterpret_cast<const uint4 *>(p.shared_up) + (size_t)(ch.rb * 8 + g) * wrow;
-      ch.s_lo = ch.s_hi = nullptr;
-      ch.s_stride = 0;
     } else if (c < p.cC10) {
       const int ci = (int)(c - p.cB0);
       ch.kind = KIND_B;
-      ch.rb = ci / p.cprB;
+      ch.rb = div_small(ci, p.inv_cprB);
       ch.kc = ci - ch.rb * p.cprB;
       ch.k0 = ch.kc * p.spcB;
       ch.n = min(p.spcB, p.sprB - ch.k0);
       const int rb_per_slot = p.inter / 8;
-      ch.slot = ch.rb / rb_per_slot;
+      ch.slot = div_small(ch.rb, p.inv_rbB);
       const int jb = ch.rb - ch.slot * rb_per_slot;
       const size_t wrow = p.hidden / 32;
       const size_t ebase0 = (size_t)w_ids[ch.slot] * p.inter * wrow + (size_t)(jb * 8) * wrow;
@@ -444,7 +641,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
       const int rb = (int)(c - p.cC10);
       const int rb_per_slot = p.hidden / 16;  // chunks per slot
       ch.kind = KIND_C1;
-      ch.slot = rb / rb_per_slot;
+      ch.slot = div_small(rb, p.inv_rbC1);
       ch.rb = rb - ch.slot * rb_per_slot;  // output row-block
       ch.kc = 0;
       ch.k0 = 0;
@@ -459,7 +656,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
     } else {
       const int ci = (int)(c - p.cC20);
       ch.kind = KIND_C2;
-      ch.rb = ci / p.cprC2;  // output row-block
+      ch.rb = div_small(ci, p.inv_cprC2);  // output row-block
       ch.kc = ci - ch.rb * p.cprC2;
       ch.k0 = ch.kc * p.spcC2;
       ch.n = min(p.spcC2, p.sprC2 - ch.k0);
@@ -467,8 +664,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
       const size_t wrow = p.shared_inter / 8;
       ch.w_lo = reinterpret_cast<const uint4 *>(p.shared_down) + (size_t)(ch.rb * 16 + g) * wrow;
       ch.w_hi = ch.w_lo + 8 * wrow;
-      ch.s_lo = ch.s_hi = nullptr;
-      ch.s_stride = 0;
     }
     return ch;
   };
@@ -477,212 +672,207 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
   // logits (polled until the router's finishers have written them); same inputs, same rule,
   // so every CTA selects the same experts.  The other warps wait on a shared-memory flag.
   auto fetch_routing = [&]() {
-    int st = 0;
-    if (lane == 0) st = atomicCAS(&s_route_state, 0, 1);
-    st = __shfl_sync(0xffffffffu, st, 0);
-    if (st == 0) {
-      for (int i0 = lane; i0 < p.experts; i0 += 32 * 4) {
-        float lg[4];
-        const int n = min(4, (p.experts - i0 + 31) / 32);
-        ld_tagged_n<4>(p.logits + i0, 32, n, epoch, err, lg);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int i = i0 + 32 * j;
-          if (j < n) {
-            const float sc = 1.0f / (1.0f + expf(-lg[j]));
-            s_score[i] = sc;
-            s_sel[i] = sc + p.router_bias[i];
-          }
-        }
-      }
-      __syncwarp();
-      int my_id;
-      float my_w;
-      warp_topk(s_score, s_sel, p.experts, p.topk, p.routed_scale, lane, my_id, my_w);
-      if (lane < p.topk) {
-        w_ids[lane] = my_id;
-        w_wts[lane] = my_w;
-        if (blockIdx.x == 0) {
-          if (p.ids_out) p.ids_out[lane] = (uint16_t)my_id;
-          if (p.wts_out) p.wts_out[lane] = my_w;
-        }
-      }
-      __threadfence_block();
-      __syncwarp();
-      if (lane == 0) {
-        atomicExch(&s_route_state, 2);
-        if (blockIdx.x == 0) trace_launch(p, 1);
-      }
-    } else if (st == 1) {
-      if (lane == 0) {
-        unsigned it = 0;
-        while (atomicAdd(&s_route_state, 0) != 2) {
-          if (++it > kSpinLimit) {
-            atomicExch(err, 1u);
-            break;
-          }
-          __nanosleep(100);
-        }
-      }
-      __syncwarp();
+    if (claim_or_wait(&s_route_state, lane, err, 1u)) {
+      if (lane == 0) trace_cta(p, 3);
+      uint16_t *ids_out = blockIdx.x == 0 ? p.ids_out : nullptr;  // CTA 0 reports the routing to the caller
+      float *wts_out = blockIdx.x == 0 ? p.wts_out : nullptr;
+      if (p.experts <= 128) routing_from_scores<4>(p.logits, p.logits + p.experts, w_ids, w_wts, ids_out, wts_out, p.experts, p.topk, p.routed_scale, epoch, err, lane);
+      else routing_from_scores<12>(p.logits, p.logits + p.experts, w_ids, w_wts, ids_out, wts_out, p.experts, p.topk, p.routed_scale, epoch, err, lane);
+      if (lane == 0 && blockIdx.x == 0) trace_launch(p, 1);
+      publish(&s_route_state, lane);
+      if (lane == 0) trace_cta(p, 2);
     }
-    __threadfence_block();
     have_routing = true;
   };
 
-  // Handing a finished chunk in: arrive() publishes the chunk's partial result as tagged
-  // values and returns at once (no fence, no atomic).  The warp that holds the LAST chunk of
-  // a row-block in queue order is its finisher: complete() makes it collect the other
-  // chunks' values (polling a slot only if its writer is still at work), sum them in index
-  // order and run the row-block's epilogue.  Chunks are handed out in order, so the chunks a
-  // finisher waits for are already being worked on by warps that never wait for it.
+  // A slot's mid vector (slot == topk: the shared expert's), prepared once per CTA by the first warp that needs it.
+  auto ensure_mid = [&](int slot) {
+    if (!claim_or_wait(&s_mid_state[slot], lane, err, 4u)) return;
+    stage_mid_i4(p.mid_cnt + slot, p.mid + (size_t)slot * (p.mid_stride / 2), p.inter, midq + (size_t)slot * midq_bytes, epoch, err, lane);
+    publish(&s_mid_state[slot], lane);
+  };
+  auto ensure_smid = [&]() {
+    if (!claim_or_wait(&s_mid_state[p.topk], lane, err, 5u)) return;
+    stage_mid_bf16(p.mid_cnt + p.topk, p.mid + (size_t)p.topk * (p.mid_stride / 2), p.shared_inter, smid, epoch, err, lane);
+    publish(&s_mid_state[p.topk], lane);
+  };
+
   auto piece_part = [&](const Chunk &ch) { return ch.kind == KIND_R ? p.partR : ch.kind == KIND_A ? p.partA : ch.kind == KIND_B ? p.partB : p.partC2; };
+  auto piece_cnt = [&](const Chunk &ch) { return ch.kind == KIND_R ? p.cntR : ch.kind == KIND_A ? p.cntA : ch.kind == KIND_B ? p.cntB : p.cntC2; };
   auto piece_n = [&](const Chunk &ch) { return ch.kind == KIND_R ? p.cprR : ch.kind == KIND_A ? p.cprA : ch.kind == KIND_B ? p.cprB : p.cprC2; };
 
-  auto arrive = [&](const Chunk &ch, float v) {
+  // v holds A row g + 8 * (t >> 1) in every lane of a quad half; lanes 0..15 receive rows 0..15
+  auto rows_to_lanes = [&](float v) { return __shfl_sync(0xffffffffu, v, ((lane & 7) << 2) + ((lane >> 3) & 1) * 2); };
+
+  // Handing a finished chunk in.  No warp ever waits for another chunk of its row-block: every chunk stores its 16 partial
+  // sums and increments the row-block's counter; the warp whose increment completes the row-block finishes it (complete()).
+  // arrive() returns the counter's old value in lane 0; the increment's latency is covered by what the caller does before
+  // it looks at the value (the next chunk's first requests).
+  auto arrive = [&](const Chunk &ch, float v) -> unsigned {
+    if (ch.kind == KIND_R && p.r_local) {
+      // the 16 chunks of a router row-block are this CTA's 16 first chunks: their sums meet in shared memory, no global
+      // round trip lies between the last weight byte of the router and its logits
+      if ((t & 1) == 0) s_rpart[warp][g + 8 * (t >> 1)] = v;
+      __threadfence_block();
+      __syncwarp();
+      unsigned old = 0;
+      if (lane == 0) old = (unsigned)atomicAdd(&s_rcount, 1);
+      return old;
+    }
     if (ch.kind == KIND_C1) {
-      const float total = __shfl_sync(0xffffffffu, v, ((lane & 7) << 2) + ((lane >> 3) & 1) * 2);
+      const float total = rows_to_lanes(v);
       if (lane < 16) st_tagged(p.ys + (size_t)ch.slot * p.hidden + ch.rb * 16 + lane, round_bf16(total), epoch);
-      return;
+      return 0u;
     }
     const int np = piece_n(ch);
-    if (np > 1 && ch.kc != np - 1 && (t & 1) == 0)
-      st_tagged(piece_part(ch) + ((size_t)ch.rb * np + ch.kc) * 16 + g + 8 * (t >> 1), v, epoch);
+    if (np == 1) return epoch - 1u;  // the only chunk of its row-block completes it
+    if ((t & 1) == 0) __stcg(piece_part(ch) + ((size_t)ch.rb * np + ch.kc) * 16 + g + 8 * (t >> 1), v);
+    __syncwarp();
+    unsigned old = 0;
+    if (lane == 0) old = arrive_counter(piece_cnt(ch) + ch.rb);
+    return old;
   };
 
-  // out rows [ob*16, +16): every slot's contribution (tagged) weighted in slot order, plus the shared expert's
-  auto combine_rows = [&](int ob, float own, int own_slot) {
+  // lanes 0..15 hold the 16 logits of router row-block rb, unrounded (:297): s = 1 / (1 + expf(-logit)) (:379),
+  // sel = s + bias (:374), both published per expert
+  auto publish_scores = [&](int rb, float logit) {
     if (lane < 16) {
-      float o = 0.f;
-      for (int k0 = 0; k0 < p.topk; k0 += 4) {
-        float yk[4];
-        const int n = min(4, p.topk - k0);
-        if (own_slot >= k0 && own_slot < k0 + n) {  // the own slot's value is not in memory: read the others one by one
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            yk[j] = (j >= n || k0 + j == own_slot) ? own : ld_tagged(p.ys + (size_t)(k0 + j) * p.hidden + ob * 16 + lane, epoch, err);
-        } else {
-          ld_tagged_n<4>(p.ys + (size_t)k0 * p.hidden + ob * 16 + lane, p.hidden, n, epoch, err, yk);
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (j < n) o = fmaf(yk[j], w_wts[k0 + j], o);
-      }
-      o = round_bf16(o);
-      if (p.shared_inter) o = round_bf16(o + own);
-      p.y[ob * 16 + lane] = f32_to_bf16_bits(o);
+      const int e = rb * 16 + lane;
+      const float sc = 1.0f / (1.0f + expf(-logit));
+      st_tagged(p.logits + e, sc + p.router_bias[e], epoch);
+      st_tagged(p.logits + p.experts + e, sc, epoch);
     }
   };
 
-  auto complete = [&](const Chunk &ch, float v) {
+  auto complete = [&](const Chunk &ch, float v, unsigned old) {
     if (ch.kind == KIND_C1) {
-      // without a shared expert the last routed slot finishes the output rows
-      if (p.shared_inter == 0 && ch.slot == p.topk - 1) {
-        const float total = round_bf16(__shfl_sync(0xffffffffu, v, ((lane & 7) << 2) + ((lane >> 3) & 1) * 2));
-        combine_rows(ch.rb, total, ch.slot);
-      }
+      // without a shared expert the last routed slot finishes the output rows (its own rows are in memory by now: arrive())
+      if (p.shared_inter == 0 && ch.slot == p.topk - 1) combine_rows(p.ys, p.y, p.hidden, p.topk, false, w_wts, ch.rb, 0.f, epoch, err, lane);
       return;
     }
     const int np = piece_n(ch);
-    if (ch.kc != np - 1) return;
-    float total = __shfl_sync(0xffffffffu, v, ((lane & 7) << 2) + ((lane >> 3) & 1) * 2);  // this chunk's rows in lanes 0..15
-    if (np > 1 && lane < 16) {
-      const uint2 *src = piece_part(ch) + (size_t)ch.rb * np * 16 + lane;
-      float s = 0.f;
-      for (int i0 = 0; i0 < np - 1; i0 += kCollect) {  // index order, then the own (last) chunk
-        float part[kCollect];
-        const int n = min(kCollect, np - 1 - i0);
-        ld_tagged_n<kCollect>(src + (size_t)i0 * 16, 16, n, epoch, err, part);
-#pragma unroll
-        for (int j = 0; j < kCollect; ++j)
-          if (j < n) s += part[j];
-      }
-      total = s + total;
+    old = __shfl_sync(0xffffffffu, old, 0);
+    if (ch.kind == KIND_R && p.r_local) {
+      if (old + 1u != (unsigned)kFusedWarps) return;
+      __threadfence_block();
+      float total = 0.f;
+      if (lane < 16)
+        for (int wi = 0; wi < kFusedWarps; ++wi) total += s_rpart[wi][lane];  // chunk order
+      publish_scores(ch.rb, total);
+      if (lane == 0) trace_launch(p, 5);
+      return;
     }
+    if (old + 1u != epoch * (unsigned)np) return;  // another chunk of the row-block is still out
+    const float total = np > 1 ? collect_row_block(piece_part(ch) + (size_t)ch.rb * np * 16, np, lane) : rows_to_lanes(v);
     if (ch.kind == KIND_R) {
-      if (lane < 16) st_tagged(p.logits + ch.rb * 16 + lane, total, epoch);
+      publish_scores(ch.rb, total);
       if (lane == 0) trace_launch(p, 5);
       return;
     }
     if (ch.kind == KIND_A || ch.kind == KIND_B) {
-      const float up = __shfl_down_sync(0xffffffffu, total, 8);
       const int row0 = ch.kind == KIND_A ? ch.rb * 8 : (ch.rb - ch.slot * (p.inter / 8)) * 8;
-      const uint32_t m = f32_to_bf16_bits(swiglu_ref_rounding(total, up));
-      const uint32_t hi = __shfl_down_sync(0xffffffffu, m, 1);
-      if (lane < 8 && (lane & 1) == 0)
-        st_tagged(p.mid + ((size_t)ch.slot * p.mid_stride + row0 + lane) / 2, __uint_as_float(m | (hi << 16)), epoch);
+      const unsigned before = publish_mid(total, p.mid + ((size_t)ch.slot * p.mid_stride + row0) / 2, p.mid_cnt + ch.slot, lane);
+      if (p.trace && lane == 0) {
+        trace_launch(p, ch.kind == KIND_A ? 11 : 12);
+        if (ch.kind == KIND_B && before + 1u == epoch * (unsigned)(p.inter / 8)) {  // a slot's mid vector is complete
+          if (ch.slot == 0) trace_launch(p, 14);
+          if (ch.slot == 3) trace_launch(p, 4);
+          if (ch.slot == 5) trace_launch(p, 6);
+          if (ch.slot == p.topk - 1) trace_launch(p, 15);
+        }
+      }
       return;
     }
     // KIND_C2: the shared expert's rows are complete, and with them the output rows
-    combine_rows(ch.rb, round_bf16(total), -1);
+    combine_rows(p.ys, p.y, p.hidden, p.topk, p.shared_inter != 0, w_wts, ch.rb, round_bf16(total), epoch, err, lane);
+    if (lane == 0) trace_launch(p, 13);
   };
 
-  // The first chunk of every warp is its own index (no herd of atomics at the start); later
-  // chunks come from the queue counter, fetched one chunk ahead.
+  // ---- the first chunk's weights go in flight before anything else: the first pass over the queue is the router and
+  // the shared expert's gate/up, which need nothing but x ------------------------------------------------------------
   const unsigned W = gridDim.x * kFusedWarps;
-  unsigned next = 0;
   unsigned c = blockIdx.x * kFusedWarps + warp;
   Chunk cur;
   cur.kind = KIND_NONE;
-  if (c < p.total) {
-    if (lane == 0) next = W + atomicAdd(p.ctrl + CTRL_QUEUE, 1u);
-    if (c >= p.cB0 && c < p.cC20) fetch_routing();
+  const bool early = c < p.cB0 && c < p.total;  // needs no routing
+  if (early) {
     cur = decode(c);
     ring_prologue(cur, ring, lane);
   }
-  int traced = 0;
+  if (tid == 0) trace_cta(p, 4);
+  stage_x_both(p.x, xnat, xq.xq, xq.meta, xq.zero, p.hidden, tid);
+  if (tid == 0) trace_cta(p, 5);
+  __syncthreads();
+  if (tid == 0) trace_cta(p, 1);
+  if (c < p.total) {
+    if (!early) {
+      if (c < p.cC20) fetch_routing();
+      cur = decode(c);
+      ring_prologue(cur, ring, lane);
+    }
+  }
+
+  // integer form: lanes with (g >> 1) == t supply limb g & 1 of their own scale group (two uint4 per k-block)
+  const bool supply = ((g >> 1) == t);
+  ImmaLane xl_x;  // x
+  xl_x.ptr = supply ? reinterpret_cast<const uint4 *>(xq.xq + t * 64 + (g & 1) * 32) : xq.zero + 4 + (lane & 1);
+  xl_x.kb_stride = supply ? 16 : 0;
+
+  int traced = 0, traced_w = 0;
   while (cur.kind != KIND_NONE) {
     // ---- the chunk's weights are in flight; now the activations -------------------------------
-    float v;
-    const bool tr = p.trace && warp == 1 && lane == 0 && traced < 2;
-    if (tr) p.trace[16 + (size_t)blockIdx.x * kTraceSlots + 8 + traced * 4 + 0] = global_ns();
-    if (cur.kind == KIND_C1 || cur.kind == KIND_C2) {
+    Consumed got;
+    const bool tr = p.trace && warp == 0 && lane == 0 && traced < 1;
+    if (tr) p.trace[16 + (size_t)blockIdx.x * kTraceSlots + 11] = global_ns();
+    const uint4 *w_lo = cur.w_lo + (size_t)cur.k0 * 4 + t, *w_hi = cur.w_hi + (size_t)cur.k0 * 4 + t;
+    if (cur.kind == KIND_C1) {
+      ensure_mid(cur.slot);
+      const unsigned char *mq = midq + (size_t)cur.slot * midq_bytes;
+      const uint4 *xp = supply ? reinterpret_cast<const uint4 *>(mq + t * 64 + (g & 1) * 32) : xq.zero + 4 + (lane & 1);
+      got = consume_i4(w_lo, w_hi, cur.n, ring, ring_ptr, xp, supply ? 16 : 0, reinterpret_cast<const uint2 *>(mq + (size_t)p.inter * 2),
+                       p.ctrl + CTRL_QUEUE, W, lane);
+    } else if (cur.kind == KIND_C2) {
       if (!have_routing) fetch_routing();  // the combine needs the routing weights
-      if (cur.kind == KIND_C1) {
-        warp_stage_i4(p.mid + (size_t)cur.slot * p.mid_stride / 2, reinterpret_cast<uint4 *>(wstage), msum, p.inter, lane,
-                      epoch, err);
-        v = ring_consume(cur, ring, ring_ptr, xl_m, msum, nullptr, 0, lane);
-      } else {
-        uint4 *seg = reinterpret_cast<uint4 *>(wstage);
-        const uint2 *src = p.mid + (size_t)p.topk * p.mid_stride / 2 + (size_t)cur.k0 * 16;
-        for (int u0 = lane; u0 < cur.n * 4; u0 += 64) {
-          uint4 vv[2];
-          const int n = min(2, (cur.n * 4 - u0 + 31) / 32);
-          ld_tagged_units<2>(src + (size_t)u0 * 4, 32 * 4, n, epoch, err, vv);
-#pragma unroll
-          for (int j = 0; j < 2; ++j)
-            if (u0 + 32 * j < cur.n * 4) seg[u0 + 32 * j] = vv[j];
-        }
-        __syncwarp();
-        v = ring_consume(cur, ring, ring_ptr, xl_m, msum, seg + t, cur.k0, lane);
-      }
-      __syncwarp();  // the staged segment is free again
+      ensure_smid();
+      got = consume_bf16(w_lo, w_hi, cur.n, ring, ring_ptr, smid + (size_t)cur.k0 * 4 + t, p.ctrl + CTRL_QUEUE, W, lane);
     } else if (cur.kind == KIND_B) {
-      v = ring_consume(cur, ring, ring_ptr, xl_x, xsum, nullptr, 0, lane);
+      got = consume_i4(w_lo, w_hi, cur.n, ring, ring_ptr, xl_x.ptr + (size_t)cur.k0 * xl_x.kb_stride, xl_x.kb_stride,
+                       xq.meta + (size_t)cur.k0 * 4, p.ctrl + CTRL_QUEUE, W, lane);
     } else {
-      v = ring_consume(cur, ring, ring_ptr, xl_x, xsum, xnat + t, 0, lane);
+      got = consume_bf16(w_lo, w_hi, cur.n, ring, ring_ptr, xnat + (size_t)cur.k0 * 4 + t, p.ctrl + CTRL_QUEUE, W, lane);
     }
     // ---- hand in (without waiting), put the next chunk's weights in flight, then look at the count ----
-    if (tr) p.trace[16 + (size_t)blockIdx.x * kTraceSlots + 8 + traced * 4 + 1] = global_ns();
-    arrive(cur, v);
-    c = __shfl_sync(0xffffffffu, next, 0);
+    if (tr) p.trace[16 + (size_t)blockIdx.x * kTraceSlots + 12] = global_ns(), ++traced;
+    const float v = got.v;
+    if (p.trace && lane == 0 && traced_w < 1) {  // per warp: when its first chunk was consumed
+      p.trace[(size_t)(gridDim.x + 1) * 16 + ((size_t)blockIdx.x * kFusedWarps + warp) * 2] = global_ns();
+    }
+    const unsigned old = arrive(cur, v);
+    c = __shfl_sync(0xffffffffu, got.next, 0);
     Chunk nx;
     nx.kind = KIND_NONE;
     bool completed = false;
     if (c < p.total) {
-      if (lane == 0) next = W + atomicAdd(p.ctrl + CTRL_QUEUE, 1u);
+      if (p.trace && lane == 0) {  // when the queue reaches each phase, and its end
+        if (c == p.cB0) trace_launch(p, 7);
+        if (c == p.cC10) trace_launch(p, 8);
+        if (c == p.cC20) trace_launch(p, 9);
+        if (c == p.total - 1) trace_launch(p, 10);
+      }
       if (c >= p.cB0 && c < p.cC20 && !have_routing) {
         // the routing may depend on the chunk in hand: finish it before waiting
-        complete(cur, v);
+        complete(cur, v, old);
         completed = true;
         fetch_routing();
       }
       nx = decode(c);
       ring_prologue(nx, ring, lane);
     }
-    if (tr) p.trace[16 + (size_t)blockIdx.x * kTraceSlots + 8 + traced * 4 + 2] = global_ns();
-    if (!completed) complete(cur, v);
-    if (tr) p.trace[16 + (size_t)blockIdx.x * kTraceSlots + 8 + traced * 4 + 3] = global_ns(), ++traced;
+    if (!completed) complete(cur, v, old);
+    if (p.trace && lane == 0 && traced_w < 1) {  // ... and when the warp was through with it (row-block finished, if it was its finisher)
+      p.trace[(size_t)(gridDim.x + 1) * 16 + ((size_t)blockIdx.x * kFusedWarps + warp) * 2 + 1] = global_ns();
+      ++traced_w;
+    }
     cur = nx;
   }
 
@@ -712,9 +902,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
 static int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 size_t fused_smem_bytes(const blok_moe_weights &w) {
-  return (size_t)w.hidden * 4 + 384 + (size_t)(w.hidden / 32) * kMetaBytes + (size_t)kFusedWarps * kWarpRingBytes +
-         (size_t)kFusedWarps * ((size_t)w.inter * 2 + (size_t)(w.inter / 32) * kMetaBytes) + (size_t)kFusedWarps * 16 * 8 +
-         (size_t)w.experts * 2 * sizeof(float);
+  return (size_t)w.hidden * 2 + imma_stage_bytes(w.hidden) + (size_t)w.topk * ((size_t)w.inter * 2 + (size_t)(w.inter / 32) * 8) +
+         (size_t)w.shared_inter * 2 + (size_t)kFusedWarps * kWarpRingBytes;
 }
 
 // Cuts a row-block of `spr` steps into equal chunks of about `target` steps.
@@ -729,9 +918,11 @@ static void cut(int spr, int target, int *spc, int *cpr) {
 // plan->enabled set either way; a CUDA failure is an error.
 int fused_plan(const blok_moe_weights &w, FusedPlan *plan) {
   plan->enabled = false;
-  if (w.experts % 16 || w.topk > 16 || w.shared_inter % 32 || w.inter % 256 || w.hidden % 256) return BLOK_OK;
+  if (w.experts % 16 || w.topk > kMaxTopk || w.shared_inter % 32 || w.inter % 256 || w.hidden % 256) return BLOK_OK;
+  // the routing keeps every candidate in registers, 12 per lane.  (A 32-per-lane instance for up to 1,024 experts made
+  // the whole kernel spill: a callee that wants that many registers costs every caller of the kernel its own.)
+  if (w.experts > 384) return BLOK_OK;
   if (w.experts_local != w.experts || w.expert_base != 0) return BLOK_OK;
-  if (w.shared_inter > w.inter && w.shared_inter > 0 && 16 * 64 > w.inter * 2) return BLOK_OK;
   int dev = 0, coop = 0, sms = 0;
   BLOK_CUDA(cudaGetDevice(&dev));
   BLOK_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
@@ -748,7 +939,7 @@ int fused_plan(const blok_moe_weights &w, FusedPlan *plan) {
   plan->total_warps = plan->grid * kFusedWarps;
   // chunking (steps of 1 KB of weights per warp); BLOK_FUSED_CHUNK_STEPS="R,A,B,C2" overrides the target steps per
   // chunk of the four phases that are cut (a tuning aid; the defaults are the measured configuration)
-  int tgt[4] = {14, 28, 14, 16};
+  int tgt[4] = {14, 28, 14, 32};
   if (const char *e = getenv("BLOK_FUSED_CHUNK_STEPS")) {
     int v[4];
     if (sscanf(e, "%d,%d,%d,%d", &v[0], &v[1], &v[2], &v[3]) == 4 && v[0] > 0 && v[1] > 0 && v[2] > 0 && v[3] > 0)
@@ -771,8 +962,6 @@ int fused_plan(const blok_moe_weights &w, FusedPlan *plan) {
   plan->nrbB = w.topk * (w.inter / 8);
   plan->nrbC1 = w.topk * (w.hidden / 16);
   plan->nrbC2 = w.shared_inter ? w.hidden / 16 : 0;
-  // a C2 chunk's activation segment must fit the per-warp staging area
-  if ((size_t)plan->spcC2 * 64 > (size_t)w.inter * 2) return BLOK_OK;
   plan->enabled = true;
   return BLOK_OK;
 }
@@ -792,10 +981,12 @@ int launch_moe_decode_fused(blok_moe_layer *L, const uint16_t *x, uint16_t *y, u
   p.ids_out = ids_out ? ids_out : L->ids;
   p.wts_out = wts_out ? wts_out : L->wts;
   p.logits = reinterpret_cast<uint2 *>(L->f_logits_t);
-  p.mid = reinterpret_cast<uint2 *>(L->f_mid); p.mid_stride = L->f_mid_stride;
+  p.r_local = pl.cprR == kFusedWarps && pl.nrbR <= pl.grid ? 1 : 0;
+  p.mid = reinterpret_cast<uint32_t *>(L->f_mid); p.mid_stride = L->f_mid_stride;
+  p.mid_cnt = L->f_cntOut + 8;  // [topk + 1] of the 64 spare counters behind the per-row-block ones
   p.ys = reinterpret_cast<uint2 *>(L->f_ys);
-  p.partR = reinterpret_cast<uint2 *>(L->f_partR); p.partA = reinterpret_cast<uint2 *>(L->f_partA);
-  p.partB = reinterpret_cast<uint2 *>(L->f_partB); p.partC2 = reinterpret_cast<uint2 *>(L->f_partC2);
+  p.partR = L->f_partR; p.partA = L->f_partA; p.partB = L->f_partB; p.partC2 = L->f_partC2;
+  p.cntR = L->f_cntR; p.cntA = L->f_cntA; p.cntB = L->f_cntB; p.cntC2 = L->f_cntC2;
   p.sprR = pl.sprR; p.spcR = pl.spcR; p.cprR = pl.cprR;
   p.sprA = pl.sprA; p.spcA = pl.spcA; p.cprA = pl.cprA;
   p.sprB = pl.sprB; p.spcB = pl.spcB; p.cprB = pl.cprB;
@@ -806,6 +997,8 @@ int launch_moe_decode_fused(blok_moe_layer *L, const uint16_t *x, uint16_t *y, u
   p.cC10 = p.cB0 + (unsigned)pl.nrbB * pl.cprB;
   p.cC20 = p.cC10 + (unsigned)pl.nrbC1;
   p.total = p.cC20 + (unsigned)pl.nrbC2 * pl.cprC2;
+  p.inv_cprR = 1.0f / pl.cprR; p.inv_cprA = 1.0f / pl.cprA; p.inv_cprB = 1.0f / pl.cprB; p.inv_cprC2 = 1.0f / pl.cprC2;
+  p.inv_rbB = 1.0f / (w.inter / 8); p.inv_rbC1 = 1.0f / (w.hidden / 16);
   p.ctrl = L->f_ctrl;
   p.trace = L->f_trace;
   void *args[] = {&p};

@@ -90,19 +90,19 @@ extern "C" int blok_moe_layer_create(const blok_moe_weights *w, int max_tokens, 
   if (pl.enabled) {
     L->f_mid_stride = (int)align_up((size_t)std::max(w->inter, w->shared_inter), 64);
     o_fmid = take((size_t)(w->topk + 1) * L->f_mid_stride * 4);
-    o_flog = take((size_t)w->experts * 8);
+    o_flog = take((size_t)w->experts * 16);  // two tagged values per expert
     o_fys = take((size_t)(w->topk + 1) * w->hidden * 2 * sizeof(float));
     o_route = take(32 * sizeof(float));
     o_pR = take((size_t)pl.nrbR * pl.cprR * 16 * 2 * sizeof(float));
     o_pA = take((size_t)std::max(pl.nrbA, 1) * pl.cprA * 16 * 2 * sizeof(float));
     o_pB = take((size_t)pl.nrbB * pl.cprB * 16 * 2 * sizeof(float));
     o_pC2 = take((size_t)std::max(pl.nrbC2, 1) * pl.cprC2 * 16 * 2 * sizeof(float));
-    n_cnt = (size_t)pl.nrbR + pl.nrbA + pl.nrbB + pl.nrbC2 + w->hidden / 16 + 8;
+    n_cnt = (size_t)pl.nrbR + pl.nrbA + pl.nrbB + pl.nrbC2 + w->hidden / 16 + 8 + 64;  // + 64: the last block holds at least 64 words
     o_cnt = take(n_cnt * sizeof(unsigned));
   }
   const char *trace_env = std::getenv("BLOK_MOE_TRACE");
   const bool want_trace = pl.enabled && trace_env && trace_env[0] == '1';
-  size_t o_trace = want_trace ? take(((size_t)pl.grid + 1) * 16 * sizeof(long long)) : 0;
+  size_t o_trace = want_trace ? take(((size_t)pl.grid + 1) * 48 * sizeof(long long)) : 0;  // 16 stamps per CTA, then 2 per warp
   L->ws_bytes = off;
   cudaError_t e = cudaMalloc(&L->ws, L->ws_bytes);
   if (e != cudaSuccess) {
@@ -229,6 +229,14 @@ extern "C" int blok_moe_layer_check(blok_moe_layer_t *L, blok_stream_t stream_) 
   return BLOK_ERR_TIMEOUT;
 }
 
+extern "C" int blok_moe_layer_debug_set_error(blok_moe_layer_t *L, unsigned code, blok_stream_t stream) {
+  BLOK_REQUIRE(L, BLOK_ERR_ARG, "blok_moe_layer_debug_set_error: null pointer");
+  BLOK_REQUIRE(L->f_ctrl, BLOK_ERR_STATE, "blok_moe_layer_debug_set_error: this layer has no fused decode kernel (no error word)");
+  BLOK_CUDA(cudaMemcpyAsync(L->f_ctrl + 5, &code, sizeof(code), cudaMemcpyHostToDevice, (cudaStream_t)stream));
+  BLOK_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  return BLOK_OK;
+}
+
 extern "C" int blok_moe_decode_host(blok_moe_layer_t *L, const blok_bf16_t *x_host, blok_bf16_t *y_host,
                                     blok_stream_t stream_) {
   BLOK_REQUIRE(L && x_host && y_host, BLOK_ERR_ARG, "blok_moe_decode_host: null pointer");
@@ -250,7 +258,7 @@ extern "C" int blok_moe_decode_host(blok_moe_layer_t *L, const blok_bf16_t *x_ho
 extern "C" int blok_moe_layer_trace(blok_moe_layer_t *L, long long *host_out, int max_entries) {
   BLOK_REQUIRE(L && host_out, BLOK_ERR_ARG, "blok_moe_layer_trace: null pointer");
   if (!L->f_trace) return 0;
-  int n = (L->plan.grid + 1) * 16;
+  int n = (L->plan.grid + 1) * 48;
   if (n > max_entries) n = max_entries;
   BLOK_CUDA(cudaDeviceSynchronize());
   BLOK_CUDA(cudaMemcpy(host_out, L->f_trace, (size_t)n * sizeof(long long), cudaMemcpyDeviceToHost));

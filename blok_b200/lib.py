@@ -471,7 +471,7 @@ class MlaLayer:
     latent cache.  `weights`: dict of CUDA bf16 tensors q_a [1536,7168], q_a_ln [1536], q_b [12288,1536],
     kv_a [576,7168], kv_a_ln [512], kv_b [16384,512], o [7168,8192].  The tensors are borrowed."""
 
-    def __init__(self, weights, yarn_factor=32.0, rope_theta=50000.0, rms_eps=1e-5, max_batch=8, max_ctx=32768,
+    def __init__(self, weights, yarn_factor=64.0, rope_theta=50000.0, rms_eps=1e-5, max_batch=8, max_ctx=32768,
                  heads=64, qk_nope=128, qk_rope=64, v_head=128):
         self.weights = dict(weights)
         w = self.weights
@@ -511,6 +511,10 @@ class MlaLayer:
                                       C.c_long(cache.shape[1]), _ptr(ctx_len, torch.int32, "ctx_len"), C.c_int(B),
                                       _ptr(y, torch.bfloat16, "out"), _stream()))
         return y
+
+    def check(self):
+        """Synchronises and raises if an earlier decode call had a position outside its sequence's cache rows."""
+        _check(load().blok_mla_layer_check(self._handle, _stream()))
 
     def attend(self, q, cache, seq_len, scale=None, out=None):
         """The attention core: q bf16 [B, heads, 576], seq_len int32 [B] (device) -> o_lat bf16 [B, heads, 512]."""
@@ -669,7 +673,7 @@ class ModelConfig(C.Structure):
                [(n, C.c_float) for n in ("rms_eps", "final_rms_eps", "rope_theta", "yarn_factor", "yarn_beta_fast",
                                          "yarn_beta_slow", "yarn_original_ctx", "yarn_mscale_all_dim")] + \
                [("max_batch", C.c_int), ("max_ctx", C.c_int), ("eos_id", C.c_uint32), ("prefill_chunk", C.c_int),
-                ("kv_page_rows", C.c_int), ("kv_pages", C.c_int)]
+                ("kv_page_rows", C.c_int), ("kv_pages", C.c_int), ("ep_rank", C.c_int), ("ep_world", C.c_int)]
 
 
 def index_validate(path, cfg):
@@ -730,6 +734,15 @@ class Model:
             self.close()
         except Exception:
             pass
+
+    def set_comm(self, comm):
+        """Expert parallelism: the communicator of a model created with ep_world > 1 (kept alive by this object)."""
+        _check(load().blok_model_set_comm(self._handle, comm._handle))
+        self._comm = comm
+
+    def check(self):
+        """Synchronises; raises if a layer's device-side wait gave up, a position left its cache or the communicator failed."""
+        _check(load().blok_model_check(self._handle, _stream()))
 
     def tensor(self, layer, name, dtype, shape=None):
         """Host copy (numpy) of a weight tensor."""

@@ -237,6 +237,11 @@ int blok_moe_combine(const blok_bf16_t *y_assign, const float *wts, const blok_b
  * on one another (src/kimi_exec.cu launches are all on the default stream). */
 int blok_moe_layer_check(blok_moe_layer_t *layer, blok_stream_t stream);
 
+/* Test hook (host-side fault injection; nothing faults or hangs on the device): stores `code` in the handle's device
+ * error word exactly as a wait that gave up would, so that the reporting path (blok_moe_layer_check, blok_model_check,
+ * blok_moe_decode_host) can be exercised. */
+int blok_moe_layer_debug_set_error(blok_moe_layer_t *layer, unsigned code, blok_stream_t stream);
+
 /* Diagnostics (no counterpart in the reference): when the handle was created with
  * the environment variable BLOK_MOE_TRACE=1, the fused decode kernel records
  * nanosecond time stamps: 16 launch-wide slots, then 16 slots per CTA.  Copies up to max_entries of
@@ -299,6 +304,16 @@ int blok_moe_ep_check(blok_moe_ep_t *ep, blok_stream_t stream);
 /* HOST out[4] after synchronising `stream`, for the last pass: assignments this rank sent, of those to other ranks,
  * rows this rank received, tiles its grouped GEMM ran. */
 int blok_moe_ep_stats(blok_moe_ep_t *ep, long long *host_out4, blok_stream_t stream);
+/* The exchange plan of one rank, on the HOST (no GPU needed), from the count table every rank holds after the
+ * histograms were gathered: table int32 [world, experts], table[s, g] = assignments rank s sends to expert g.  It runs
+ * the same code as the plan kernel of blok_moe_ep_forward and exists so that this arithmetic can be exercised among
+ * CPU ranks.  Outputs: send_base [experts] = the row, in the owner's receive buffer, of this rank's first assignment
+ * to expert g (the owner's buffer is ordered by expert, then by source rank); as owner: counts [experts/world],
+ * offsets [experts/world + 1], and the tiles (<= 64 rows of one expert) of its grouped GEMM, at most max_tiles of them.
+ * BLOK_ERR_ROUTE when more than cap_rows rows would arrive. */
+int blok_ep_plan_host(const int *table, int world, int experts, int rank, long cap_rows, int max_tiles, int *send_base, int *counts,
+                      int *offsets, int *tile_expert, int *tile_start, int *tile_count, int *num_tiles);
+
 /* Measurement aid: with profiling on, a pass records a CUDA event between its phases; blok_moe_ep_phase_ms waits for
  * the last pass and returns HOST out[6], milliseconds on the device: routing; counts + plan + dispatch; shared expert;
  * waiting for the other ranks' rows; the grouped expert GEMM; flags + combine (which waits for the owners). */
@@ -356,6 +371,13 @@ int blok_mla_layer_refresh(blok_mla_layer_t *layer);
  * Attention covers positions 0..ctx_len[b] inclusive.  ctx_len[b] < ctx_stride. */
 int blok_mla_decode(blok_mla_layer_t *layer, const blok_bf16_t *n, blok_bf16_t *cache, long ctx_stride,
                     const int *ctx_len, int B, blok_bf16_t *out, blok_stream_t stream);
+
+/* The cache positions live on the device (ctx_len), so a position outside a sequence's rows (ctx_len[b] >= ctx_stride;
+ * paged: beyond table_stride pages) cannot be refused before the launch.  The kernels then skip the store of that row,
+ * keep the attention inside the rows and record the entry; this call synchronises `stream` and returns BLOK_ERR_SHAPE
+ * once for it.  (The reference dies on the host at its capacity check, src/kimi_exec.cu:205.)  The page numbers in a
+ * block table are the caller's: they are not checked against the pool. */
+int blok_mla_layer_check(blok_mla_layer_t *layer, blok_stream_t stream);
 
 /* The attention core alone, for measurement and parity: q bf16 [B, heads,
  * kv_rank+qk_rope] (absorbed nope part, then roped part), seq_len int32 [B] on the
@@ -471,6 +493,9 @@ typedef struct blok_model_config {
                         a multiple of 32: the layers' caches are pools of pages of this many rows, shared by the
                         max_batch resident sequences (slots) through one page table */
   int kv_pages;      /* pages per layer's pool when kv_page_rows > 0 */
+  int ep_rank;       /* expert parallelism: with ep_world > 1 this handle is rank ep_rank of ep_world processes, one per GPU; */
+  int ep_world;      /* it holds experts [ep_rank, ep_rank + 1) * experts / ep_world of every MoE layer and everything else in
+                        full.  0 or 1: the whole model on this GPU.  Needs blok_model_set_comm before the first step. */
 } blok_model_config;
 
 typedef struct blok_model blok_model_t;
@@ -512,6 +537,24 @@ int blok_model_load_index(blok_model_t *model, const char *index_path);
 /* The same checks without a model or a GPU: parses the index and verifies the forward contract for cfg.  Returns the
  * number of tensors the model would load and their total bytes. */
 int blok_index_validate(const char *index_path, const blok_model_config *cfg, long *n_tensors, unsigned long long *n_bytes);
+
+/* Expert parallelism (config 4 over the GPUs of a node; the reference is a single-GPU program and has no counterpart).
+ * Every rank creates its handle with the same configuration and seed apart from ep_rank (the synthetic expert tensors
+ * of a rank are the slices of the unsharded tensors), gives it the communicator, and then makes the SAME calls with
+ * the same token ids: attention, router, shared expert, embedding and sampler are replicated, so all ranks agree on
+ * the routing and on the next token without talking; per MoE layer each rank runs the selected experts it holds and
+ * ONE all-reduce (rows x hidden floats) adds the weighted sums, which are then rounded as at :871 and :684.
+ * blok_model_tensor returns a rank's shard for the expert tensors.  Steps are launched eagerly unless BLOK_MODEL_GRAPH=1. */
+int blok_model_set_comm(blok_model_t *model, blok_comm_t *comm);
+
+/* Synchronises `stream` and reports, once, whether any layer's bounded device-side wait gave up since the last check
+ * (BLOK_ERR_TIMEOUT), a decode position lay outside a cache (BLOK_ERR_SHAPE) or the communicator failed (BLOK_ERR_COMM).
+ * blok_model_generate and blok_model_generate_many end with this check: tokens are not returned after such an event.
+ * Callers that drive blok_model_step themselves call it where they synchronise anyway. */
+int blok_model_check(blok_model_t *model, blok_stream_t stream);
+
+/* Test hook: blok_moe_layer_debug_set_error on the MoE layer `layer` of the model. */
+int blok_model_debug_set_layer_error(blok_model_t *model, int layer, unsigned code, blok_stream_t stream);
 
 /* Forgets all cached tokens (positions restart at 0). */
 int blok_model_reset(blok_model_t *model);

@@ -51,7 +51,9 @@ def build_ref(reference, force=False):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("BLOK_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("BLOK_REFERENCE") or
+                    os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"),
+                    help="the reference checkout (default: BLOK_REFERENCE, else a `reference` folder beside this repository)")
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()
     print(build_oracle(a.force))

@@ -1,9 +1,17 @@
-"""Expert-parallel dispatch/combine logic among CPU ranks (gloo, world size 2 and 4) with stand-in experts:
-the sharded result must equal the single-process result, and routing faults must surface as errors."""
+"""The expert-parallel exchange plan among CPU ranks (gloo, world size 2 and 4).
+
+On the GPUs the ranks gather their histograms into every rank's count table with peer stores and each derives, from the
+table alone, where its rows land in every owner's receive buffer (blok_moe_ep_forward, csrc/ep.cu).  That arithmetic is
+shared with blok_ep_plan_host (csrc/ep_plan.h), so the same code runs here: every rank routes its own ragged batch,
+gloo carries the histograms, each rank plans with the C entry point, the rows are "sent" as (owner, row) records, and
+the owners must find their buffers filled exactly once, grouped by expert, source ranks in order, with the tiles
+covering exactly the received rows.  The reference is a single-GPU program; nothing here has a counterpart in it."""
+import ctypes as C
 import os
 import socket
 import sys
 
+import numpy as np
 import pytest
 import torch
 import torch.distributed as dist
@@ -12,33 +20,20 @@ import torch.multiprocessing as mp
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
-E, TOPK, H = 16, 4, 8
+E, TOPK = 32, 4
 
 
-def _weights():
-    g = torch.Generator().manual_seed(0)
-    return torch.randn(E, H, H, generator=g) * 0.3, torch.randn(E, H, generator=g)
-
-
-def _router(x, wr):
-    s = torch.sigmoid(x @ wr.t())
-    wts, ids = torch.topk(s, TOPK, dim=-1)
-    return ids, (wts / wts.sum(-1, keepdim=True)).float()
-
-
-def _expert(rows, e_global, W):
-    return torch.einsum("nh,nkh->nk", rows, W[e_global])
-
-
-def _combine(y, wts, shared):
-    out = (y.reshape(wts.shape[0], TOPK, -1) * wts[..., None]).sum(1)
-    return out + shared if shared is not None else out
-
-
-def _single(x, W, wr):
-    ids, wts = _router(x, wr)
-    y = _expert(x.repeat_interleave(TOPK, 0), ids.reshape(-1), W)
-    return _combine(y, wts, x * 0.5)
+def plan_host(lib, table, world, rank, cap, max_tiles=4096):
+    per = E // world
+    i32 = lambda n: np.zeros(n, np.int32)
+    send_base, counts, offsets = i32(E), i32(per), i32(per + 1)
+    te, ts, tc, nt = i32(max_tiles), i32(max_tiles), i32(max_tiles), i32(1)
+    p = lambda a: a.ctypes.data_as(C.c_void_p)
+    tab = np.ascontiguousarray(table, np.int32)
+    rc = lib.blok_ep_plan_host(p(tab), world, E, rank, C.c_long(cap), max_tiles, p(send_base), p(counts), p(offsets), p(te), p(ts),
+                               p(tc), p(nt))
+    n = int(nt[0])
+    return rc, send_base, counts, offsets, te[:n], ts[:n], tc[:n]
 
 
 def _worker(rank, world, port, fault, q):
@@ -46,36 +41,47 @@ def _worker(rank, world, port, fault, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     # a short process-group timeout: a peer that is gone must end the survivors' next collective with an error
     dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
-    if fault == "peer_exits" and rank == 1:
-        dist.barrier()       # the group is up; then this rank leaves between steps, with nothing of its own in flight
-        os._exit(0)
-    if fault == "peer_exits":
-        dist.barrier()
-    from blok_b200 import ep
-    W, wr = _weights()
-    per = E // world
-    g = torch.Generator().manual_seed(100 + rank)
-    x = torch.randn(5 + 3 * rank, H, generator=g)          # ragged: every rank has a different token count
-
-    def experts_fn(rows, local_e):
-        if fault == "short" and rank == 0:
-            return rows[:-1] if rows.shape[0] else rows
-        return _expert(rows, local_e.long() + rank * per, W)
-
-    def router_fn(xx):
-        ids, wts = _router(xx, wr)
-        if fault == "bad_id" and rank == 1:
-            ids = ids.clone()
-            ids[0, 0] = E + 3
-        return ids, wts
-
-    layer = ep.ExpertParallelMoe(router_fn, experts_fn, _combine, lambda xx: xx * 0.5, E, TOPK)
     try:
-        out = layer.forward(x)
-        ok = torch.allclose(out, _single(x, W, wr), atol=1e-5)
-        q.put((rank, "ok" if ok else "mismatch", layer.last_stats))
-    except ep.RoutingError as e:
-        q.put((rank, "routing_error", str(e)))
+        if fault == "peer_exits":
+            dist.barrier()       # the group is up
+            if rank == 1:
+                os._exit(0)      # this rank leaves between steps, with nothing of its own in flight
+        import blok_b200
+        lib = blok_b200.load()
+        per = E // world
+        rng = np.random.default_rng(100 + rank)
+        T = 5 + 3 * rank if fault != "empty_rank" or rank != 0 else 0          # ragged: every rank has a different token count
+        ids = np.stack([rng.choice(E, TOPK, replace=False) for _ in range(T)]) if T else np.zeros((0, TOPK), np.int64)
+        hist = torch.from_numpy(np.bincount(ids.reshape(-1), minlength=E).astype(np.int32))
+        table = [torch.zeros(E, dtype=torch.int32) for _ in range(world)]
+        dist.all_gather(table, hist)                                            # every rank's row of the count table
+        table = torch.stack(table).numpy()
+        cap = 3 if fault == "overflow" else world * 16 * TOPK
+        rc, send_base, counts, offsets, te, ts, tc = plan_host(lib, table, world, rank, cap)
+        if fault == "overflow":
+            q.put((rank, "rc", rc))
+            return
+        assert rc == 0
+        # dispatch: assignment a goes to row send_base[g] + (its position among this rank's assignments to g)
+        cursor = np.zeros(E, np.int64)
+        rec = []
+        for a, g in enumerate(ids.reshape(-1)):
+            rec.append((int(g) // per, int(send_base[g] + cursor[g]), int(g), rank, a))
+            cursor[g] += 1
+        everyone = [None] * world
+        dist.all_gather_object(everyone, rec)
+        mine = sorted(r for part in everyone for r in part if r[0] == rank)     # what lands in this owner's buffer, by row
+        rows = [r[1] for r in mine]
+        ok = rows == list(range(len(rows))) and len(rows) == int(offsets[per])                  # filled exactly once, no gaps
+        for e in range(per):
+            seg = mine[offsets[e]:offsets[e] + counts[e]]
+            ok = ok and all(r[2] == rank * per + e for r in seg)                                   # grouped by expert
+            ok = ok and [r[3] for r in seg] == sorted(r[3] for r in seg)                           # source ranks in order
+        covered = sorted(x for s, c in zip(ts, tc) for x in range(s, s + c))
+        ok = ok and covered == list(range(len(rows))) and all(c <= 64 for c in tc)                # tiles cover the rows
+        ok = ok and all(offsets[e] <= s < offsets[e] + max(counts[e], 1) for e, s in zip(te, ts))
+        q.put((rank, "ok" if ok else "mismatch", dict(received=len(rows), assignments=len(rec),
+                                                      remote=sum(1 for r in rec if r[0] != rank))))
     except Exception as e:  # a peer that failed makes the collective fail on the others
         q.put((rank, "error", type(e).__name__))
     finally:
@@ -118,36 +124,37 @@ def _run(world, fault=None):
 
 
 @pytest.mark.parametrize("world", [2, 4])
-def test_sharded_equals_single_process(world):
+def test_every_assignment_lands_once_grouped_by_expert(world):
     res = _run(world)
     assert len(res) == world and all(v[0] == "ok" for v in res.values()), res
-    # every assignment is received exactly once across the ranks
     assert sum(v[1]["received"] for v in res.values()) == sum(v[1]["assignments"] for v in res.values())
     assert any(v[1]["remote"] > 0 for v in res.values())
 
 
-def test_bad_expert_id_is_reported_on_the_routing_rank():
-    res = _run(2, fault="bad_id")
-    assert res[1][0] == "routing_error" and "expert id outside" in res[1][1]
+def test_a_rank_without_tokens_still_takes_part():
+    res = _run(2, fault="empty_rank")
+    assert len(res) == 2 and all(v[0] == "ok" for v in res.values()), res
+    assert res[0][1]["assignments"] == 0 and res[0][1]["received"] > 0
 
 
-def test_short_return_from_experts_is_detected():
-    res = _run(2, fault="short")
-    assert res[0][0] == "routing_error" and "returned" in res[0][1]
+def test_more_rows_than_the_receive_buffer_holds_is_an_error_code():
+    res = _run(2, fault="overflow")
+    assert all(v == ("rc", -7) for v in res.values()), res       # BLOK_ERR_ROUTE on every rank, nothing written past the buffer
 
 
-def test_plan_dispatch_properties():
-    from blok_b200 import ep
-    ids = torch.tensor([[0, 15, 7, 8], [3, 4, 12, 1]])
-    order, counts, local = ep.plan_dispatch(ids, 16, 4)
-    assert counts.tolist() == [3, 2, 1, 2]
-    dest = (ids.reshape(-1) // 4)[order]
-    assert torch.equal(dest, torch.sort(dest).values)
-    assert torch.equal(local.long(), ids.reshape(-1)[order] % 4)
-    with pytest.raises(ep.RoutingError):
-        ep.plan_dispatch(ids, 16, 3)
-    o2, c2, _ = ep.plan_dispatch(torch.zeros((0, 4), dtype=torch.int64), 16, 4)
-    assert o2.numel() == 0 and c2.tolist() == [0, 0, 0, 0]
+def test_plan_clamps_counts_a_timed_out_peer_may_have_left():
+    """A rank whose wait for a peer's counts gave up may read anything in that peer's row: negative or huge counts must
+    not turn into positions outside the buffers."""
+    import blok_b200
+    lib = blok_b200.load()
+    table = np.zeros((2, E), np.int32)
+    table[0, :4] = 3
+    table[1, 0] = -5
+    table[1, 1] = 2 ** 31 - 1
+    rc, send_base, counts, offsets, te, ts, tc = plan_host(lib, table, 2, 0, cap=64)
+    assert rc == -7                                                  # the huge count overflows the buffer: reported
+    assert all(0 <= b <= 64 for b in send_base) and int(offsets[-1]) <= 64
+    assert all(s + c <= 64 for s, c in zip(ts, tc))
 
 
 def test_a_peer_that_left_ends_the_collective_with_an_error_not_a_hang():

@@ -1,5 +1,6 @@
-"""Expert parallelism on real GPUs: 2 ranks over NCCL, each holding half of the experts; the sharded layer must
-reproduce the single-GPU batched layer on every rank's own tokens.  Skipped with fewer than 2 GPUs."""
+"""Expert parallelism on real GPUs through the C ABI (blok_comm_*, blok_moe_ep_*, blok_model_* with ep_world = 2): two
+ranks, each holding half of the experts; the sharded layer must reproduce the single-GPU batched layer on every rank's
+own tokens, the sharded model the single-GPU model's tokens.  Skipped with fewer than 2 GPUs."""
 import os
 import socket
 import sys
@@ -89,36 +90,44 @@ def _model_worker(rank, world, port, q):
         import torch.distributed as dist
         torch.cuda.set_device(rank)
         dev = torch.device("cuda", rank)
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-        from blok_b200 import ep_model, lib
+        dist.init_process_group("gloo", rank=rank, world_size=world)   # only carries the communicator's id
+        from blok_b200 import lib
         cfg = dict(layers=3, first_dense=1, hidden=1024, vocab=2048, dense_inter=512, inter=512, experts=16, topk=8,
-                   shared_inter=512, q_rank=256, max_batch=1, max_ctx=32)
+                   shared_inter=512, q_rank=256, max_batch=4, max_ctx=32)
         with torch.cuda.device(dev):
-            single = lib.Model(seed=41, **cfg)            # the same seeded weights on every rank's GPU
+            single = lib.Model(seed=41, **cfg)            # the whole model on every rank's GPU: the result to reproduce
             prompt = [7, 1, 900, 33]
             want = single.generate(prompt, 6)
-            side = torch.cuda.Stream()
+            ids = torch.tensor([5, 6, 7, 8], dtype=torch.int32, device=dev)
+            want_step = single.step(single.step(ids))     # two steps of a batch of 4
+            comm = lib.Comm()
             res = {}
-            # the CUDA-graph variant (NCCL all-reduce inside the capture) passed here too but takes two minutes to
-            # capture under NCCL: opt in with BLOK_TEST_EP_GRAPH=1
-            for graph in ((False, True) if os.environ.get("BLOK_TEST_EP_GRAPH") == "1" else (False,)):
-                m = ep_model.ExpertParallelModel(single.cfg, ep_model.provider_from_model(single, rank, world, dev),
-                                                 max_ctx=32, use_graph=graph)
-                with torch.cuda.stream(side):             # a graph cannot be captured on the legacy default stream
-                    res[graph] = m.generate(prompt, 6)
+            for graph in (False, True):                   # eager launches, then one CUDA graph per step (all-reduces captured)
+                os.environ["BLOK_MODEL_GRAPH"] = "1" if graph else "0"
+                m = lib.Model(seed=41, **dict(cfg, ep_rank=rank, ep_world=world))   # same seed: its experts are single's slices
+                m.set_comm(comm)
+                side = torch.cuda.Stream()                # a graph cannot be captured on the legacy default stream
+                with torch.cuda.stream(side):
+                    got_step = m.step(m.step(ids))
                     torch.cuda.synchronize()
-                res["captured_%s" % graph] = m.graph is not None
+                m.reset()
+                res[graph] = (m.generate(prompt, 6), got_step.tolist())
+                m.check()
+                m.close()
+            os.environ.pop("BLOK_MODEL_GRAPH", None)
         dist.barrier()
-        ok = all(res[g] == want for g in (False, True) if g in res)
-        q.put((rank, "ok" if ok else "mismatch %r want %r" % (res, want), dict(graph=res.get("captured_True", False))))
+        ok = all(res[g] == (want, want_step.tolist()) for g in res)
+        q.put((rank, "ok" if ok else "mismatch %r want %r" % (res, (want, want_step.tolist())), {}))
+        comm.close()
         dist.destroy_process_group()
     except Exception as e:
         import traceback
-        q.put((rank, "error: %r %s" % (e, traceback.format_exc()[-600:]), {}))
+        q.put((rank, "error: %r %s" % (e, traceback.format_exc()[-800:]), {}))
 
 
 def test_two_rank_sharded_model_generates_the_single_gpu_tokens():
-    """Config 4 in miniature: 3 layers, experts split over 2 GPUs, one all-reduce per MoE layer."""
+    """Config 4 in miniature through the C ABI (blok_model_* with ep_world = 2): 3 layers, experts split over 2 GPUs, one
+    all-reduce per MoE layer; the tokens must be the single-GPU model's, at batch 1 (generate) and at batch 4 (steps)."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp

@@ -122,3 +122,28 @@ def test_mla_rejects_bad_arguments(cuda, layer32):
     q = torch.zeros((9, 64, 576), dtype=torch.bfloat16, device=cuda)
     with pytest.raises(lib.BlokError):
         layer.attend(q, torch.zeros((9, 4, 576), dtype=torch.bfloat16, device=cuda), torch.ones(9, dtype=torch.int32, device=cuda))
+
+
+def test_position_outside_the_cache_is_reported_not_stored(cuda, layer32):
+    """ctx_len lives on the device, so a sequence already at its capacity cannot be refused before the launch: the
+    kernel must skip the store (the row would land in the NEXT sequence's first row), keep its attention inside the
+    sequence's rows, and blok_mla_layer_check must report the entry.  (The reference dies on the host, :205.)"""
+    from blok_b200 import lib, synth
+    w, layer = layer32
+    ctx = 64
+    cache = synth.latent_cache(3, ctx, cuda, seed=9)
+    before = cache.clone()
+    n = synth.activations(3, 7168, cuda, 9)
+    ctx_len = torch.tensor([10, ctx, 20], dtype=torch.int32, device=cuda)     # entry 1 is full: position 64 of 64 rows
+    out = layer.decode(n, cache, ctx_len)
+    with pytest.raises(lib.BlokError) as e:
+        layer.check()
+    assert e.value.code == -2 and "entry 1" in str(e.value)
+    layer.check()                                                            # reported once, then clear
+    changed = (cache != before).any(dim=2)
+    assert changed[0, 10] and changed[2, 20] and int(changed.sum()) == 2     # only the two legal rows were written
+    assert torch.isfinite(out.float()).all()
+    # a legal call afterwards is unaffected
+    ctx_len2 = torch.tensor([11, 5, 21], dtype=torch.int32, device=cuda)
+    layer.decode(n, cache, ctx_len2)
+    layer.check()

@@ -156,3 +156,58 @@ def test_load_index_replaces_every_weight(cuda, tmp_path):
     assert got == a.generate(prompt, 8)
     a.close()
     b.close()
+
+
+def test_sharded_model_holds_the_slices_of_the_unsharded_tensors(cuda, tmp_path):
+    """Expert parallelism (config 4): rank r of w holds experts [r E/w, (r+1) E/w) of every MoE layer and everything else
+    in full.  Its synthetic expert tensors are the slices of the unsharded model's, and the index loader reads into a
+    shard only the experts the rank holds."""
+    from blok_b200 import lib
+    CFG = dict(globals()["CFG"], inter=512, shared_inter=512)      # the sizes the grouped expert kernels take
+    full = lib.Model(seed=31, **CFG)
+    c = full.cfg
+    world = 4
+    per = c.experts // world
+    shapes = {"gate_w": (c.inter, c.hidden // 8), "down_w": (c.hidden, c.inter // 8), "up_s": (c.inter, c.hidden // 32)}
+    other = lib.Model(seed=77, **CFG)
+    path = util.write_checkpoint(str(tmp_path), util.checkpoint_tensors(other.cfg, lambda l, n, dt, sh: other.tensor(l, n, dt, sh)),
+                                 shards=3)
+    for rank in (0, 3):
+        shard = lib.Model(seed=31, **dict(CFG, ep_rank=rank, ep_world=world))
+        for name, sh in shapes.items():
+            dt = np.uint32 if name.endswith("_w") else np.uint16
+            want = full.tensor(2, name, dt, (c.experts,) + sh)[rank * per:(rank + 1) * per]
+            assert np.array_equal(shard.tensor(2, name, dt, (per,) + sh), want), (rank, name)
+        assert np.array_equal(shard.tensor(1, "router", np.uint16), full.tensor(1, "router", np.uint16))
+        assert np.array_equal(shard.tensor(-1, "lm_head", np.uint16), full.tensor(-1, "lm_head", np.uint16))
+        shard.load_index(path)          # the checkpoint of ANOTHER model: the shard must now hold that model's slices
+        for name, sh in shapes.items():
+            dt = np.uint32 if name.endswith("_w") else np.uint16
+            want = other.tensor(1, name, dt, (c.experts,) + sh)[rank * per:(rank + 1) * per]
+            assert np.array_equal(shard.tensor(1, name, dt, (per,) + sh), want), (rank, name)
+        assert np.array_equal(shard.tensor(2, "kv_b_proj", np.uint16), other.tensor(2, "kv_b_proj", np.uint16))
+        with pytest.raises(lib.BlokError) as e:          # no communicator yet: a step is refused, nothing is launched
+            shard.step(torch.zeros(1, dtype=torch.int32, device=cuda))
+        assert e.value.code == -4
+        shard.close()
+    with pytest.raises(lib.BlokError):
+        lib.Model(seed=1, **dict(CFG, ep_rank=4, ep_world=4))
+    full.close()
+    other.close()
+
+
+def test_a_wait_that_gave_up_in_a_layer_voids_the_generation(cuda):
+    """The decode kernels' waits are bounded and leave an error word; generate() must not return tokens after one.
+    The word is set from the host here (blok_moe_layer_debug_set_error): no wait is made to run out on the device."""
+    import ctypes as C
+    from blok_b200 import lib
+    m = lib.Model(seed=5, **CFG)
+    want = m.generate([3, 1, 4], 4)
+    m.check()
+    assert lib.load().blok_model_debug_set_layer_error(m._handle, C.c_int(1), C.c_uint(2), None) == 0
+    with pytest.raises(lib.BlokError) as e:
+        m.check()
+    assert e.value.code == -5 and "layer 1" in str(e.value)
+    m.check()                                   # reported once; the handle stays usable
+    assert m.generate([3, 1, 4], 4) == want
+    m.close()

@@ -65,35 +65,3 @@ def test_missing_index_file(tiny):
     with pytest.raises(lib.BlokError) as e:
         lib.index_validate(str(tmp / "nope.blok"), cfg)
     assert "cannot open" in str(e.value)
-
-
-def test_sharded_provider_reads_only_the_ranks_experts(tiny):
-    """The expert-parallel model's loader: rank r of w gets experts [r E/w, (r+1) E/w) stacked expert-major, everything
-    else whole; the bytes are the checkpoint's (CPU tensors here, the same code feeds the GPUs)."""
-    import torch
-    from blok_b200 import ep_model
-    lib, cfg, tensors, tmp = tiny
-    path = util.write_checkpoint(str(tmp), tensors, shards=3)
-    by_name = {t[0]: t[7] for t in tensors}
-    world = 4
-    per = cfg.experts // world
-    for rank in (0, 3):
-        get = ep_model.provider_from_index(path, cfg, rank, world, torch.device("cpu"))
-        gw = get(1, "down_w")
-        assert gw.dtype == torch.int32 and tuple(gw.shape) == (per, cfg.hidden, cfg.inter // 8)
-        for i in range(per):
-            src = by_name["language_model.model.layers.1.mlp.experts.%d.down_proj.weight_packed" % (rank * per + i)]
-            assert np.array_equal(gw[i].numpy().view(np.uint32), src)
-        gs = get(1, "gate_s")
-        src = by_name["language_model.model.layers.1.mlp.experts.%d.gate_proj.weight_scale" % (rank * per)]
-        assert gs.dtype == torch.bfloat16 and np.array_equal(gs[0].view(torch.int16).numpy().view(np.uint16), src)
-        head = get(-1, "lm_head")
-        assert np.array_equal(head.view(torch.int16).numpy().view(np.uint16), by_name["language_model.lm_head.weight"])
-        bias = get(1, "router_bias")
-        want = util.bf16_np_to_f32(by_name["language_model.model.layers.1.mlp.gate.e_score_correction_bias"])
-        assert bias.dtype == torch.float32 and np.array_equal(bias.numpy(), want)
-    # a checkpoint that breaks the contract is refused before anything is read
-    lines = [l for l in open(path).read().splitlines() if " q_b_proj " not in l]
-    open(path, "w").write("\n".join(lines) + "\n")
-    with pytest.raises(lib.BlokError):
-        ep_model.provider_from_index(path, cfg, 0, world, torch.device("cpu"))
