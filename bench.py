@@ -370,12 +370,14 @@ def other_workload(a, rank, world, device, steps, warmup):
         # config 4: the 61-layer model sharded expert-parallel over the ranks (384 / world experts per GPU, attention,
         # router, shared expert, embedding and lm_head replicated), batch 1, greedy decode after a 16-token prompt replay.
         # With fewer than 8 GPUs only as many layers as fit are built, and the line says how many.
-        from blok_b200 import ep_model
+        B = a.batch
         per_layer = 9.513e9 / world + 0.32e9
         L = a.model_layers if a.model_layers != 12 else min(61, int(140e9 // per_layer))
-        cfg = lib.default_model_config(layers=L, max_batch=1, max_ctx=256, final_rms_eps=1e-6, yarn_factor=32.0)
-        model = ep_model.ExpertParallelModel(cfg, ep_model.synthetic_provider(cfg, rank, world, device, seed=4), max_ctx=256)
-        state = {"ids": torch.randint(0, 163840, (1,), device=device, dtype=torch.int32)}
+        comm = lib.Comm() if world > 1 else None
+        model = lib.Model(seed=4, layers=L, max_batch=B, max_ctx=max(256, 32 + steps + warmup + 8), ep_rank=rank, ep_world=world)
+        if comm is not None:
+            model.set_comm(comm)
+        state = {"ids": torch.randint(0, 163840, (B,), device=device, dtype=torch.int32)}
         if world > 1:
             dist.broadcast(state["ids"], 0)
 
@@ -383,18 +385,27 @@ def other_workload(a, rank, world, device, steps, warmup):
             state["ids"] = model.step(state["ids"])
         prompt_side = torch.cuda.Stream()
         with torch.cuda.stream(prompt_side):
-            lc0 = lib.kernel_launch_count()
-            run(0)                                   # the first step is always eager: count its kernels
-            launches_per_step = lib.kernel_launch_count() - lc0
-            for _ in range(15):
+            for _ in range(16):
                 run(0)
         torch.cuda.synchronize()
-        alg = (L - 1) * (202244096 + 5505024 + 88080384 + 8 * 24772608 / world) + (3 * 18432 * 7168 * 2 + 202244096) + 163840 * 7168 * 2
-        unit_tokens = 1
-        workload = ("config 4: %d-layer model (1 dense + %d MoE layers, full shapes, vocab 163840), batch 1, greedy decode, "
-                    "experts split over %d GPU(s), one all-reduce per MoE layer" % (L, L - 1, world))
+        model.check()
+        # every rank must hold the same next ids: the layers are the same arithmetic on every rank after the all-reduce
+        if world > 1:
+            both = [torch.empty_like(state["ids"]) for _ in range(world)]
+            dist.all_gather(both, state["ids"])
+            if any(not torch.equal(both[0], t) for t in both):
+                if rank == 0:
+                    print(json.dumps({"error": "sharded model: ranks disagree on the next token"}))
+                return 3
+        # per GPU and step: the replicated weights once, and this GPU's share of the experts the batch routes to (B x 8
+        # distinct at most, capped at 384, spread evenly over the ranks)
+        alg = (L - 1) * (202244096 + 5505024 + 88080384 + min(384, 8 * B) * 24772608 / world) + \
+            (3 * 18432 * 7168 * 2 + 202244096) + 163840 * 7168 * 2
+        unit_tokens = B
+        workload = ("config 4: %d-layer model (1 dense + %d MoE layers, full shapes, vocab 163840), batch %d, greedy decode, "
+                    "experts split over %d GPU(s), one all-reduce per MoE layer" % (L, L - 1, B, world))
         scaling = "strong"
-        metric = "decode tok/s, %d-layer model (batch 1)" % L
+        metric = "decode tok/s, %d-layer model (batch %d)" % (L, B)
     elif a.workload.startswith("batched"):
         T = int(a.workload[len("batched"):])
         if world > 1:
@@ -482,8 +493,6 @@ def other_workload(a, rank, world, device, steps, warmup):
         e1.record()
         barrier()
     launches = lib.kernel_launch_count() - l0
-    if a.workload == "model61" and launches == 0:
-        launches = launches_per_step * steps         # replayed from a torch CUDA graph: the library's counter does not see them
     ms = torch.tensor([e0.elapsed_time(e1)], device=device)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)

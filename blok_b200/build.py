@@ -25,8 +25,7 @@ NVCC_FLAGS = [
 ]
 
 
-# Extra nvcc flags for experiments with the kernels' compile-time knobs, e.g.
-#   BLOK_NVCC_EXTRA="-DBLOK_I4_ACC_CHAINS=2 -DBLOK_RING_DEPTH=5" python -m blok_b200.build --force
+# Extra nvcc flags for a one-off build, e.g. BLOK_NVCC_EXTRA="-Xptxas -warn-spills" python -m blok_b200.build --force
 EXTRA = os.environ.get("BLOK_NVCC_EXTRA", "").split()
 
 

@@ -110,34 +110,18 @@ __device__ __forceinline__ XFragLane xfrag_lane(const I4Stage &st, int lane, int
   return x;
 }
 
-// All four words of one k-block: d = per-group dot products (offset form).
-// BLOK_I4_ACC_CHAINS (compile-time, default 1) is the number of independent accumulator chains the eight MMAs of a
-// k-block are spread over: 1 is one chain of eight dependent MMAs (the measured configuration), 2 halves the chain at
-// the price of four registers and four adds per k-block.
-#ifndef BLOK_I4_ACC_CHAINS
-#define BLOK_I4_ACC_CHAINS 1
-#endif
+// All four words of one k-block: d = per-group dot products (offset form).  One chain of eight dependent MMAs; two
+// chains of four (four more registers and adds per k-block) measured the same.
 __device__ __forceinline__ void i4_kblock_mma(const uint4 &wl, const uint4 &wh, const uint4 *xp, float (&d)[4]) {
   const uint32_t al[4] = {wl.x, wl.y, wl.z, wl.w};
   const uint32_t ah[4] = {wh.x, wh.y, wh.z, wh.w};
-#if BLOK_I4_ACC_CHAINS == 2
-  float e[4] = {0.f, 0.f, 0.f, 0.f};
-#endif
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     uint4 xb = xp[i * 4];
     uint32_t a = al[i], b = ah[i];
     mma_bf16_16816(d, nib_pair(a), nib_pair(b), nib_pair(a >> 4), nib_pair(b >> 4), xb.x, xb.y);
-#if BLOK_I4_ACC_CHAINS == 2
-    mma_bf16_16816(e, nib_pair(a >> 8), nib_pair(b >> 8), nib_pair(a >> 12), nib_pair(b >> 12), xb.z, xb.w);
-#else
     mma_bf16_16816(d, nib_pair(a >> 8), nib_pair(b >> 8), nib_pair(a >> 12), nib_pair(b >> 12), xb.z, xb.w);
-#endif
   }
-#if BLOK_I4_ACC_CHAINS == 2
-#pragma unroll
-  for (int k = 0; k < 4; ++k) d[k] += e[k];
-#endif
 }
 
 // Accumulate NB = nbatch*BATCH k-blocks starting at k-block kb0 for this warp's 16

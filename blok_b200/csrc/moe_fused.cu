@@ -59,17 +59,9 @@
 
 namespace blok {
 
-#ifndef BLOK_FUSED_WARPS
-#define BLOK_FUSED_WARPS 16
-#endif
-#ifndef BLOK_RING_DEPTH
-#define BLOK_RING_DEPTH 5
-#endif
-#ifndef BLOK_I4_UNROLL2
-#define BLOK_I4_UNROLL2 0
-#endif
-
-constexpr int kFusedWarps = BLOK_FUSED_WARPS;
+// 16 warps per CTA with 5 KB of weights in flight each: 20 warps and a ring of 6 steps measured the same (85-86 us),
+// 8 warps and a ring of 4 slower.
+constexpr int kFusedWarps = 16;
 constexpr int kFusedThreads = kFusedWarps * 32;
 constexpr unsigned kSpinLimit = 1u << 20;  // polls (about a microsecond apart once backed off) before a wait gives up with an error word
 constexpr int kMaxTopk = 16;
@@ -106,6 +98,7 @@ struct FusedParams {
   unsigned cA0, cB0, cC10, cC20, total;  // first queue index of each phase; queue length
   float inv_cprR, inv_cprA, inv_cprB, inv_cprC2, inv_rbB, inv_rbC1;  // reciprocals of the divisors of the queue-index arithmetic
   unsigned *ctrl;
+  unsigned *err_host;  // optional: pinned host word that receives the launch's error word when the last CTA leaves
   long long *trace;  // optional: [0..15] launch-wide stamps, then [grid][kTraceSlots] per-CTA stamps (ns)
 };
 
@@ -192,7 +185,7 @@ __device__ __forceinline__ float swiglu_ref_rounding(float g, float u) {
 // stream of weights + scales to 4.3-5.8 TB/s against 6.7 TB/s for the weights alone (measured with a trivial consumer).
 // They are staged whole when the chunk's first weights are requested: consecutive lanes copy consecutive 8-byte pieces
 // of a row, so a row's scales travel as full lines, once.
-constexpr int kRingDepth = BLOK_RING_DEPTH;
+constexpr int kRingDepth = 5;
 constexpr int kRingStepBytes = 2 * 512;                  // low rows, high rows
 constexpr int kScaleMaxSteps = 16;                       // k-blocks an INT4 chunk may have
 constexpr int kScaleRowBytes = kScaleMaxSteps * 8 + 8;   // 136: the odd multiple of 8 spreads the 16 rows over all banks
@@ -296,40 +289,13 @@ __device__ __noinline__ Consumed consume_bf16(const uint4 *w_lo, const uint4 *w_
 __device__ __noinline__ Consumed consume_i4(const uint4 *w_lo, const uint4 *w_hi, int n, uint32_t ring, const unsigned char *ring_ptr,
                                             const uint4 *xp, int xstride, const uint2 *meta, unsigned *queue, unsigned W, int lane) {
   const int g = lane >> 2, t = lane & 3;
-  float acc_lo = 0.f, acc_hi = 0.f, acc_lo1 = 0.f, acc_hi1 = 0.f;
+  float acc_lo = 0.f, acc_hi = 0.f;
   unsigned next = 0;
   const unsigned char *sc_lo = ring_ptr + kRingDepth * kRingStepBytes + g * kScaleRowBytes + t * 2;
   const unsigned char *sc_hi = sc_lo + 8 * kScaleRowBytes;
   meta += t;
-  // two k-blocks per turn: their unpacking, MMAs and post-scaling are independent instruction streams, which is what a
-  // warp that issues one instruction every dozen cycles needs
-  int s = 0;
-#if BLOK_I4_UNROLL2
-  for (; s + 1 < n; s += 2) {
-    draw_next(s, n, queue, W, lane, next);
-    draw_next(s + 1, n, queue, W, lane, next);
-    cp_async_wait<kRingDepth - 2>();
-    if (s == 0) __syncwarp();  // the scales were copied by other lanes: their first group has landed as well
-    const unsigned char *slot0 = ring_ptr + (size_t)(s % kRingDepth) * kRingStepBytes;
-    const unsigned char *slot1 = ring_ptr + (size_t)((s + 1) % kRingDepth) * kRingStepBytes;
-    const uint4 wl0 = *reinterpret_cast<const uint4 *>(slot0 + lane * 16);
-    const uint4 wh0 = *reinterpret_cast<const uint4 *>(slot0 + 512 + lane * 16);
-    const uint4 wl1 = *reinterpret_cast<const uint4 *>(slot1 + lane * 16);
-    const uint4 wh1 = *reinterpret_cast<const uint4 *>(slot1 + 512 + lane * 16);
-    const float s_lo0 = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(sc_lo + s * 8));
-    const float s_hi0 = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(sc_hi + s * 8));
-    const float s_lo1 = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(sc_lo + s * 8 + 8));
-    const float s_hi1 = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(sc_hi + s * 8 + 8));
-    int d0[4] = {0, 0, 0, 0}, d1[4] = {0, 0, 0, 0};
-    imma_kblock(wl0, wh0, xp + s * xstride, d0);
-    imma_kblock(wl1, wh1, xp + (s + 1) * xstride, d1);
-    imma_post(d0, meta[s * 4], s_lo0, s_hi0, acc_lo, acc_hi);
-    imma_post(d1, meta[s * 4 + 4], s_lo1, s_hi1, acc_lo1, acc_hi1);
-    ring_issue(w_lo, w_hi, n, s + kRingDepth, ring, lane);
-    ring_issue(w_lo, w_hi, n, s + 1 + kRingDepth, ring, lane);
-  }
-#endif
-  for (; s < n; ++s) {  // one k-block per turn (and an odd last step)
+  // one k-block per turn; two per turn (independent unpack / MMA / post-scale streams) measured no faster
+  for (int s = 0; s < n; ++s) {
     draw_next(s, n, queue, W, lane, next);
     cp_async_wait<kRingDepth - 1>();
     if (s == 0) __syncwarp();
@@ -343,8 +309,6 @@ __device__ __noinline__ Consumed consume_i4(const uint4 *w_lo, const uint4 *w_hi
     imma_post(di, meta[s * 4], s_lo, s_hi, acc_lo, acc_hi);
     ring_issue(w_lo, w_hi, n, s + kRingDepth, ring, lane);
   }
-  acc_lo += acc_lo1;
-  acc_hi += acc_hi1;
   acc_lo += __shfl_xor_sync(0xffffffffu, acc_lo, 1);
   acc_lo += __shfl_xor_sync(0xffffffffu, acc_lo, 2);
   acc_hi += __shfl_xor_sync(0xffffffffu, acc_hi, 1);
@@ -884,12 +848,17 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
   if (tid == 0) {
     trace_cta(p, 7);
     const unsigned epoch_now = p.ctrl[CTRL_EPOCH] + 1u;
-    __threadfence();
+    if (p.err_host) __threadfence_system();  // y may lie in host memory
+    else __threadfence();
     unsigned old = atomicAdd(p.ctrl + CTRL_EXIT, 1u);
     if (old == gridDim.x - 1) {
       p.ctrl[CTRL_QUEUE] = 0;
       p.ctrl[CTRL_EXIT] = 0;
       p.ctrl[CTRL_EPOCH] = epoch_now;
+      if (p.err_host) {  // every CTA's outputs were fenced before its exit count: the host sees them before this word
+        *reinterpret_cast<volatile unsigned *>(p.err_host) = __ldcg(p.ctrl + CTRL_ERROR);
+        __threadfence_system();
+      }
       __threadfence();
       trace_launch(p, 3);
     }
@@ -967,7 +936,7 @@ int fused_plan(const blok_moe_weights &w, FusedPlan *plan) {
 }
 
 int launch_moe_decode_fused(blok_moe_layer *L, const uint16_t *x, uint16_t *y, uint16_t *ids_out, float *wts_out,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, unsigned *err_host) {
   const blok_moe_weights &w = L->w;
   const FusedPlan &pl = L->plan;
   FusedParams p;
@@ -1000,6 +969,7 @@ int launch_moe_decode_fused(blok_moe_layer *L, const uint16_t *x, uint16_t *y, u
   p.inv_cprR = 1.0f / pl.cprR; p.inv_cprA = 1.0f / pl.cprA; p.inv_cprB = 1.0f / pl.cprB; p.inv_cprC2 = 1.0f / pl.cprC2;
   p.inv_rbB = 1.0f / (w.inter / 8); p.inv_rbC1 = 1.0f / (w.hidden / 16);
   p.ctrl = L->f_ctrl;
+  p.err_host = err_host;
   p.trace = L->f_trace;
   void *args[] = {&p};
   BLOK_CUDA(cudaLaunchCooperativeKernel((const void *)moe_decode_fused_kernel, dim3(pl.grid), dim3(kFusedThreads), args,

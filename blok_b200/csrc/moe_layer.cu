@@ -27,7 +27,7 @@ int launch_i4_down(const uint32_t *down_w, const uint16_t *down_s, const uint16_
 int fused_plan(const blok_moe_weights &w, FusedPlan *plan);
 int batched_alloc(blok_moe_layer *L);
 int launch_moe_decode_fused(blok_moe_layer *L, const uint16_t *x, uint16_t *y, uint16_t *ids_out, float *wts_out,
-                            cudaStream_t stream);
+                            cudaStream_t stream, unsigned *err_host = nullptr);
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -237,22 +237,50 @@ extern "C" int blok_moe_layer_debug_set_error(blok_moe_layer_t *L, unsigned code
   return BLOK_OK;
 }
 
+// The device address of a host buffer the GPU can write directly (pinned memory), or NULL.  The last answer is kept:
+// a caller that reuses its buffers pays for the query once.
+static void *mapped_address(blok_moe_layer *L, const void *host) {
+  if (host == L->io_last_host) return L->io_last_dev;
+  cudaPointerAttributes at;
+  void *dev = nullptr;
+  if (cudaPointerGetAttributes(&at, host) == cudaSuccess && at.type == cudaMemoryTypeHost) dev = at.devicePointer;
+  else cudaGetLastError();
+  L->io_last_host = host;
+  L->io_last_dev = dev;
+  return dev;
+}
+
 extern "C" int blok_moe_decode_host(blok_moe_layer_t *L, const blok_bf16_t *x_host, blok_bf16_t *y_host,
                                     blok_stream_t stream_) {
   BLOK_REQUIRE(L && x_host && y_host, BLOK_ERR_ARG, "blok_moe_decode_host: null pointer");
   cudaStream_t stream = (cudaStream_t)stream_;
   const size_t bytes = (size_t)L->w.hidden * sizeof(uint16_t);
   BLOK_CUDA(cudaMemcpyAsync(L->io_x, x_host, bytes, cudaMemcpyHostToDevice, stream));
+  const blok_moe_weights &w = L->w;
+  if (L->use_fused && L->io_err_host && w.experts_local == w.experts && w.expert_base == 0) {
+    // One copy in, one launch, one synchronisation: when y_host is pinned the kernel's finishers store the result
+    // straight into it (14 KB over the bus while the kernel still runs), and the last CTA to leave stores the launch's
+    // error word into a pinned word of the handle; the host reads both after the stream has drained.
+    uint16_t *y_dev = static_cast<uint16_t *>(mapped_address(L, y_host));
+    void *err_dev = nullptr;
+    if (cudaHostGetDevicePointer(&err_dev, L->io_err_host, 0) != cudaSuccess) {
+      cudaGetLastError();
+      err_dev = nullptr;
+    }
+    if (err_dev) {
+      *L->io_err_host = 0;
+      int rc = launch_moe_decode_fused(L, L->io_x, y_dev ? y_dev : L->io_y, nullptr, nullptr, stream, static_cast<unsigned *>(err_dev));
+      if (rc) return rc;
+      if (!y_dev) BLOK_CUDA(cudaMemcpyAsync(y_host, L->io_y, bytes, cudaMemcpyDeviceToHost, stream));  // pageable: staged copy
+      BLOK_CUDA(cudaStreamSynchronize(stream));
+      if (*L->io_err_host == 0) return BLOK_OK;
+      return blok_moe_layer_check(L, stream_);  // a wait gave up: report it and reset the handle
+    }
+  }
   int rc = blok_moe_decode(L, L->io_x, L->io_y, nullptr, nullptr, stream_);
   if (rc) return rc;
   BLOK_CUDA(cudaMemcpyAsync(y_host, L->io_y, bytes, cudaMemcpyDeviceToHost, stream));
-  if (L->f_ctrl && L->io_err_host) {
-    // the kernel's error word rides back behind the result: one synchronisation, no second round trip to the device
-    BLOK_CUDA(cudaMemcpyAsync(L->io_err_host, L->f_ctrl + 5, sizeof(unsigned), cudaMemcpyDeviceToHost, stream));
-    BLOK_CUDA(cudaStreamSynchronize(stream));
-    if (*L->io_err_host == 0) return BLOK_OK;
-  }
-  return blok_moe_layer_check(L, stream_);  // a wait timed out (or no pinned word): report it and reset the handle
+  return blok_moe_layer_check(L, stream_);
 }
 
 extern "C" int blok_moe_layer_trace(blok_moe_layer_t *L, long long *host_out, int max_entries) {

@@ -37,7 +37,9 @@ struct blok_moe_layer {
   uint16_t *shared_out = nullptr;  // [8, hidden]
   uint16_t *io_x = nullptr;        // [hidden] staging for the host-buffer entry point
   uint16_t *io_y = nullptr;        // [hidden]
-  unsigned *io_err_host = nullptr; // pinned: the fused kernel's error word, copied back with every host-buffer call
+  unsigned *io_err_host = nullptr; // pinned: the fused kernel's error word, written by the kernel's last CTA in host-buffer calls
+  const void *io_last_host = nullptr;  // the host buffer last asked about, and its device address (NULL: not pinned)
+  void *io_last_dev = nullptr;
   // batched path (moe_batched.cu); allocated when max_tokens > 1
   void *bws = nullptr;
   int b_max_assign = 0;          // max_tokens * topk
