@@ -99,6 +99,13 @@ struct FusedParams {
   float inv_cprR, inv_cprA, inv_cprB, inv_cprC2, inv_rbB, inv_rbC1;  // reciprocals of the divisors of the queue-index arithmetic
   unsigned *ctrl;
   unsigned *err_host;  // optional: pinned host word that receives the launch's error word when the last CTA leaves
+  // A rank's share of the layer (experts split over ranks): part_out != NULL.  The gate/up/down arrays then hold experts
+  // [expert_base, expert_base + experts_local) only, the queue carries the B and C1 chunks of the selected experts that lie
+  // in that range (the others' are another rank's work), and instead of y the kernel writes part_out[hidden] = the
+  // weighted sum of those experts' outputs, fp32 and unrounded, and shared_out[hidden] = the shared expert's output.
+  int expert_base, experts_local;
+  float *part_out;
+  uint16_t *shared_out;
   long long *trace;  // optional: [0..15] launch-wide stamps, then [grid][kTraceSlots] per-CTA stamps (ns)
 };
 
@@ -470,7 +477,8 @@ __device__ __noinline__ void stage_mid_bf16(const unsigned *cnt, const uint32_t 
 
 // out rows [ob*16, +16): every slot's contribution (tagged) weighted in slot order, plus the shared expert's
 __device__ __noinline__ void combine_rows(const uint2 *ys, uint16_t *y, int hidden, int topk, bool has_shared, const float *w_wts, int ob,
-                                          float shared_val, unsigned epoch, unsigned *err, int lane) {
+                                          float shared_val, unsigned epoch, unsigned *err, int lane, float *part_out,
+                                          uint16_t *shared_out) {
   if (lane < 16) {
     float o = 0.f;
     for (int k0 = 0; k0 < topk; k0 += 8) {
@@ -480,6 +488,11 @@ __device__ __noinline__ void combine_rows(const uint2 *ys, uint16_t *y, int hidd
 #pragma unroll
       for (int j = 0; j < 8; ++j)
         if (j < n) o = fmaf(yk[j], w_wts[k0 + j], o);
+    }
+    if (part_out) {  // a rank's share: the other ranks' sums are added before anything is rounded
+      part_out[ob * 16 + lane] = o;
+      shared_out[ob * 16 + lane] = f32_to_bf16_bits(shared_val);
+      return;
     }
     o = round_bf16(o);
     if (has_shared) o = round_bf16(o + shared_val);
@@ -548,7 +561,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
   __shared__ int s_rcount;
   __shared__ int s_route_state;
   __shared__ int s_mid_state[kMaxTopk + 1];  // [slot]; entry topk is the shared expert's mid
-  if (tid == 0) s_route_state = 0, s_rcount = 0;
+  __shared__ unsigned s_bound[3];  // first queue index of C1 and of C2, queue length: a rank's share shortens B and C1
+  __shared__ int s_slots;          // routed slots in the queue: topk, or the selected experts this rank holds
+  __shared__ int s_last;
+  if (tid == 0) s_route_state = 0, s_rcount = 0, s_bound[0] = p.cC10, s_bound[1] = p.cC20, s_bound[2] = p.total, s_slots = p.topk;
   if (tid <= kMaxTopk) s_mid_state[tid] = 0;
   const uint32_t ring = (uint32_t)__cvta_generic_to_shared(ring_ptr);
 
@@ -583,7 +599,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
       const size_t wrow = p.hidden / 8;
       ch.w_lo = reinterpret_cast<const uint4 *>(p.shared_gate) + (size_t)(ch.rb * 8 + g) * wrow;
       ch.w_hi = reinterpret_cast<const uint4 *>(p.shared_up) + (size_t)(ch.rb * 8 + g) * wrow;
-    } else if (c < p.cC10) {
+    } else if (c < s_bound[0]) {
       const int ci = (int)(c - p.cB0);
       ch.kind = KIND_B;
       ch.rb = div_small(ci, p.inv_cprB);
@@ -601,8 +617,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
       ch.s_lo = p.gate_s + ebase0;
       ch.s_hi = p.up_s + ebase0;
       ch.s_stride = (int)wrow;
-    } else if (c < p.cC20) {
-      const int rb = (int)(c - p.cC10);
+    } else if (c < s_bound[1]) {
+      const int rb = (int)(c - s_bound[0]);
       const int rb_per_slot = p.hidden / 16;  // chunks per slot
       ch.kind = KIND_C1;
       ch.slot = div_small(rb, p.inv_rbC1);
@@ -618,7 +634,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
       ch.s_hi = ch.s_lo + 8 * wrow;
       ch.s_stride = (int)wrow;
     } else {
-      const int ci = (int)(c - p.cC20);
+      const int ci = (int)(c - s_bound[1]);
       ch.kind = KIND_C2;
       ch.rb = div_small(ci, p.inv_cprC2);  // output row-block
       ch.kc = ci - ch.rb * p.cprC2;
@@ -643,6 +659,28 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
       if (p.experts <= 128) routing_from_scores<4>(p.logits, p.logits + p.experts, w_ids, w_wts, ids_out, wts_out, p.experts, p.topk, p.routed_scale, epoch, err, lane);
       else routing_from_scores<12>(p.logits, p.logits + p.experts, w_ids, w_wts, ids_out, wts_out, p.experts, p.topk, p.routed_scale, epoch, err, lane);
       if (lane == 0 && blockIdx.x == 0) trace_launch(p, 1);
+      if (p.part_out) {
+        // keep the slots whose expert this rank holds, in selection order, with the expert's index in the rank's arrays;
+        // the queue's B and C1 phases shrink to those slots
+        __syncwarp();
+        const int id = lane < p.topk ? w_ids[lane] - p.expert_base : -1;
+        const float wv = lane < p.topk ? w_wts[lane] : 0.f;
+        const bool mine = id >= 0 && id < p.experts_local;
+        const unsigned m = __ballot_sync(0xffffffffu, mine);
+        __syncwarp();
+        if (mine) {
+          const int j = __popc(m & ((1u << lane) - 1u));
+          w_ids[j] = id;
+          w_wts[j] = wv;
+        }
+        if (lane == 0) {
+          const unsigned n = (unsigned)__popc(m);
+          s_slots = (int)n;
+          s_bound[0] = p.cB0 + n * ((p.cC10 - p.cB0) / (unsigned)p.topk);
+          s_bound[1] = s_bound[0] + n * ((p.cC20 - p.cC10) / (unsigned)p.topk);
+          s_bound[2] = s_bound[1] + (p.total - p.cC20);
+        }
+      }
       publish(&s_route_state, lane);
       if (lane == 0) trace_cta(p, 2);
     }
@@ -711,7 +749,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
   auto complete = [&](const Chunk &ch, float v, unsigned old) {
     if (ch.kind == KIND_C1) {
       // without a shared expert the last routed slot finishes the output rows (its own rows are in memory by now: arrive())
-      if (p.shared_inter == 0 && ch.slot == p.topk - 1) combine_rows(p.ys, p.y, p.hidden, p.topk, false, w_wts, ch.rb, 0.f, epoch, err, lane);
+      if (p.shared_inter == 0 && ch.slot == p.topk - 1)
+        combine_rows(p.ys, p.y, p.hidden, p.topk, false, w_wts, ch.rb, 0.f, epoch, err, lane, nullptr, nullptr);
       return;
     }
     const int np = piece_n(ch);
@@ -748,7 +787,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
       return;
     }
     // KIND_C2: the shared expert's rows are complete, and with them the output rows
-    combine_rows(p.ys, p.y, p.hidden, p.topk, p.shared_inter != 0, w_wts, ch.rb, round_bf16(total), epoch, err, lane);
+    combine_rows(p.ys, p.y, p.hidden, s_slots, p.shared_inter != 0, w_wts, ch.rb, round_bf16(total), epoch, err, lane, p.part_out,
+                 p.shared_out);
     if (lane == 0) trace_launch(p, 13);
   };
 
@@ -768,9 +808,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
   if (tid == 0) trace_cta(p, 5);
   __syncthreads();
   if (tid == 0) trace_cta(p, 1);
-  if (c < p.total) {
-    if (!early) {
-      if (c < p.cC20) fetch_routing();
+  if (!early && c < p.total) {
+    if (c < p.cC20 || p.part_out) fetch_routing();  // a rank's share: the routing also fixes where C2 starts in the queue
+    if (c < s_bound[2]) {
       cur = decode(c);
       ring_prologue(cur, ring, lane);
     }
@@ -823,14 +863,16 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
         if (c == p.cC20) trace_launch(p, 9);
         if (c == p.total - 1) trace_launch(p, 10);
       }
-      if (c >= p.cB0 && c < p.cC20 && !have_routing) {
+      if (c >= p.cB0 && (c < p.cC20 || p.part_out) && !have_routing) {
         // the routing may depend on the chunk in hand: finish it before waiting
         complete(cur, v, old);
         completed = true;
         fetch_routing();
       }
-      nx = decode(c);
-      ring_prologue(nx, ring, lane);
+      if (c < p.cB0 || c < s_bound[2]) {
+        nx = decode(c);
+        ring_prologue(nx, ring, lane);
+      }
     }
     if (!completed) complete(cur, v, old);
     if (p.trace && lane == 0 && traced_w < 1) {  // ... and when the warp was through with it (row-block finished, if it was its finisher)
@@ -840,7 +882,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
     cur = nx;
   }
 
-  if (blockIdx.x == 0 && warp == 0 && !have_routing) fetch_routing();  // CTA 0 reports the routing to the caller
+  // CTA 0 reports the routing to the caller; with a rank's share every CTA may turn out to be the last one, which must
+  // know how many slots the launch used
+  if (warp == 0 && !have_routing && (blockIdx.x == 0 || p.part_out)) fetch_routing();
   // ---- the last CTA to leave resets the launch-wide counters ------------------------------------
   cp_async_wait<0>();
   if (warp == 0 && lane == 0) trace_cta(p, 6);
@@ -851,6 +895,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
     if (p.err_host) __threadfence_system();  // y may lie in host memory
     else __threadfence();
     unsigned old = atomicAdd(p.ctrl + CTRL_EXIT, 1u);
+    s_last = old == gridDim.x - 1;
     if (old == gridDim.x - 1) {
       p.ctrl[CTRL_QUEUE] = 0;
       p.ctrl[CTRL_EXIT] = 0;
@@ -861,6 +906,16 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_decode_fused_kernel(cons
       }
       __threadfence();
       trace_launch(p, 3);
+    }
+  }
+  if (p.part_out) {
+    // The counters count over all launches (a row-block is complete at launch number x its chunks).  The slots this launch
+    // left out of the queue did not count: the last CTA to leave sets their counters to what a full launch leaves behind.
+    __syncthreads();
+    if (s_last) {
+      const int rb_slot = p.inter / 8;
+      for (int i = s_slots * rb_slot + tid; i < p.topk * rb_slot; i += kFusedThreads) p.cntB[i] = epoch * (unsigned)p.cprB;
+      for (int j = s_slots + tid; j < p.topk; j += kFusedThreads) p.mid_cnt[j] = epoch * (unsigned)rb_slot;
     }
   }
 }
@@ -891,7 +946,9 @@ int fused_plan(const blok_moe_weights &w, FusedPlan *plan) {
   // the routing keeps every candidate in registers, 12 per lane.  (A 32-per-lane instance for up to 1,024 experts made
   // the whole kernel spill: a callee that wants that many registers costs every caller of the kernel its own.)
   if (w.experts > 384) return BLOK_OK;
-  if (w.experts_local != w.experts || w.expert_base != 0) return BLOK_OK;
+  // a rank's share of the experts is served through part_out (launch_moe_decode_fused), which relies on the shared
+  // expert's last phase to finish the output rows
+  if ((w.experts_local != w.experts || w.expert_base != 0) && w.shared_inter == 0) return BLOK_OK;
   int dev = 0, coop = 0, sms = 0;
   BLOK_CUDA(cudaGetDevice(&dev));
   BLOK_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
@@ -936,7 +993,7 @@ int fused_plan(const blok_moe_weights &w, FusedPlan *plan) {
 }
 
 int launch_moe_decode_fused(blok_moe_layer *L, const uint16_t *x, uint16_t *y, uint16_t *ids_out, float *wts_out,
-                            cudaStream_t stream, unsigned *err_host) {
+                            cudaStream_t stream, unsigned *err_host, float *part_out, uint16_t *shared_out) {
   const blok_moe_weights &w = L->w;
   const FusedPlan &pl = L->plan;
   FusedParams p;
@@ -970,6 +1027,8 @@ int launch_moe_decode_fused(blok_moe_layer *L, const uint16_t *x, uint16_t *y, u
   p.inv_rbB = 1.0f / (w.inter / 8); p.inv_rbC1 = 1.0f / (w.hidden / 16);
   p.ctrl = L->f_ctrl;
   p.err_host = err_host;
+  p.expert_base = w.expert_base; p.experts_local = w.experts_local;
+  p.part_out = part_out; p.shared_out = shared_out;
   p.trace = L->f_trace;
   void *args[] = {&p};
   BLOK_CUDA(cudaLaunchCooperativeKernel((const void *)moe_decode_fused_kernel, dim3(pl.grid), dim3(kFusedThreads), args,

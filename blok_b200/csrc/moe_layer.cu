@@ -27,7 +27,8 @@ int launch_i4_down(const uint32_t *down_w, const uint16_t *down_s, const uint16_
 int fused_plan(const blok_moe_weights &w, FusedPlan *plan);
 int batched_alloc(blok_moe_layer *L);
 int launch_moe_decode_fused(blok_moe_layer *L, const uint16_t *x, uint16_t *y, uint16_t *ids_out, float *wts_out,
-                            cudaStream_t stream, unsigned *err_host = nullptr);
+                            cudaStream_t stream, unsigned *err_host = nullptr, float *part_out = nullptr,
+                            uint16_t *shared_out = nullptr);
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -208,6 +209,16 @@ extern "C" int blok_moe_decode(blok_moe_layer_t *L, const blok_bf16_t *x, blok_b
   if (wts_out) BLOK_CUDA(cudaMemcpyAsync(wts_out, L->wts, w.topk * sizeof(float), cudaMemcpyDeviceToDevice, stream));
   return BLOK_OK;
 }
+
+extern "C" int blok_moe_decode_partial(blok_moe_layer_t *L, const blok_bf16_t *x, float *part, blok_bf16_t *shared_out,
+                                       uint16_t *ids_out, float *wts_out, blok_stream_t stream_) {
+  BLOK_REQUIRE(L && x && part && shared_out, BLOK_ERR_ARG, "blok_moe_decode_partial: null pointer");
+  BLOK_REQUIRE(L->use_fused && L->w.shared_inter > 0, BLOK_ERR_STATE,
+               "blok_moe_decode_partial: this layer has no fused decode kernel (blok_moe_layer_has_partial)");
+  return launch_moe_decode_fused(L, x, nullptr, ids_out, wts_out, (cudaStream_t)stream_, nullptr, part, shared_out);
+}
+
+extern "C" int blok_moe_layer_has_partial(blok_moe_layer_t *L) { return L && L->use_fused && L->w.shared_inter > 0 ? 1 : 0; }
 
 extern "C" int blok_moe_layer_check(blok_moe_layer_t *L, blok_stream_t stream_) {
   BLOK_REQUIRE(L, BLOK_ERR_ARG, "blok_moe_layer_check: null pointer");

@@ -272,6 +272,22 @@ class MoeLayer:
                                       _ptr(wts), _stream()))
         return (y, ids, wts) if return_routing else y
 
+    def has_partial(self):
+        return bool(load().blok_moe_layer_has_partial(self._handle))
+
+    def decode_partial(self, x, return_routing=False):
+        """A rank's share of the batch-1 layer (blok_moe_decode_partial): x bf16 [hidden] -> (part fp32 [hidden], the
+        weighted sum of the selected experts this handle holds; shared bf16 [hidden], the shared expert's output)."""
+        part = torch.empty(self.hidden, dtype=torch.float32, device=x.device)
+        shared = torch.empty(self.hidden, dtype=torch.bfloat16, device=x.device)
+        ids = wts = None
+        if return_routing:
+            ids = torch.empty(self.topk, dtype=torch.int16, device=x.device)
+            wts = torch.empty(self.topk, dtype=torch.float32, device=x.device)
+        _check(load().blok_moe_decode_partial(self._handle, _ptr(x, torch.bfloat16, "x"), _ptr(part), _ptr(shared), _ptr(ids),
+                                              _ptr(wts), _stream()))
+        return (part, shared, ids, wts) if return_routing else (part, shared)
+
     def batched(self, x, return_routing=False):
         """Batched layer (config 2): x bf16 [T, hidden] -> y bf16 [T, hidden]; T <= max_tokens of the handle."""
         T = x.shape[0]
@@ -743,6 +759,20 @@ class Model:
     def check(self):
         """Synchronises; raises if a layer's device-side wait gave up, a position left its cache or the communicator failed."""
         _check(load().blok_model_check(self._handle, _stream()))
+
+    def hidden(self, rows):
+        """The final-normed hidden states of the last step's first `rows` sequences (blok_model_hidden): a bf16
+        [rows, hidden] tensor copied off the model's buffer after a synchronise."""
+        ptr, cap = C.c_void_p(), C.c_int()
+        _check(load().blok_model_hidden(self._handle, C.byref(ptr), C.byref(cap)))
+        if rows > cap.value:
+            raise BlokError(-2, "hidden(): %d rows asked, the buffer holds %d" % (rows, cap.value))
+        torch.cuda.synchronize()
+        out = torch.empty((rows, self.cfg.hidden), dtype=torch.bfloat16, device="cuda")
+        rc = _rt().cudaMemcpy(C.c_void_p(out.data_ptr()), ptr, C.c_size_t(out.numel() * 2), C.c_int(3))
+        if rc != 0:
+            raise BlokError(-3, "cudaMemcpy D2D failed: %d" % rc)
+        return out
 
     def tensor(self, layer, name, dtype, shape=None):
         """Host copy (numpy) of a weight tensor."""

@@ -231,6 +231,18 @@ int blok_moe_shared(blok_moe_layer_t *layer, const blok_bf16_t *x, int T, blok_b
 int blok_moe_combine(const blok_bf16_t *y_assign, const float *wts, const blok_bf16_t *shared, int T, int topk, int hidden,
                      blok_bf16_t *out, blok_stream_t stream);
 
+/* One token through a layer whose handle holds a RANGE of the experts (experts_local < experts): the router and the
+ * shared expert run whole, of the selected experts only those in [expert_base, expert_base + experts_local), in the same
+ * single launch as blok_moe_decode.  part[hidden] (fp32) = sum over those experts of wts_k * bf16(expert_k(x)),
+ * unrounded; shared_out[hidden] (bf16) = the shared expert's output.  Summing `part` over the ranks that together hold
+ * every expert, rounding to bf16 and adding shared_out gives blok_moe_decode's y up to the order of the fp32 sum
+ * (expert_accum_k :399 adds in selection order; here each rank adds its own experts in selection order first).
+ * ids_out / wts_out (may be NULL) receive the full routing.  Needs a shared expert and a layer the single-launch kernel
+ * serves: blok_moe_layer_has_partial tells (1 / 0); BLOK_ERR_STATE otherwise. */
+int blok_moe_decode_partial(blok_moe_layer_t *layer, const blok_bf16_t *x, float *part, blok_bf16_t *shared_out,
+                            uint16_t *ids_out, float *wts_out, blok_stream_t stream);
+int blok_moe_layer_has_partial(blok_moe_layer_t *layer);
+
 /* Synchronises `stream` and reports whether a device-side wait of an earlier
  * blok_moe_decode on this handle gave up (BLOK_ERR_TIMEOUT; the handle is reset
  * and stays usable).  The reference has no such state: its kernels never wait
@@ -520,6 +532,11 @@ int blok_model_tensor(blok_model_t *model, int layer, const char *name, void **p
 /* The configuration the model was created with. */
 int blok_model_get_config(blok_model_t *model, blok_model_config *cfg);
 
+/* The device buffer that holds, after a step or a prefill chunk has run on its stream, the final-normed hidden states
+ * the sampler read (src/kimi_exec.cu:880-881): bf16 [rows used by that call, hidden], row b = sequence b of the step (or
+ * token b of the chunk).  *rows is the buffer's capacity in rows.  For parity checks; valid until the next call. */
+int blok_model_hidden(blok_model_t *model, const blok_bf16_t **ptr, int *rows);
+
 /* After weights were overwritten in place through blok_model_tensor: rebuilds the copies derived from them at
  * creation (each layer's transposed W_UK). */
 int blok_model_refresh_derived(blok_model_t *model);
@@ -544,7 +561,8 @@ int blok_index_validate(const char *index_path, const blok_model_config *cfg, lo
  * the same token ids: attention, router, shared expert, embedding and sampler are replicated, so all ranks agree on
  * the routing and on the next token without talking; per MoE layer each rank runs the selected experts it holds and
  * ONE all-reduce (rows x hidden floats) adds the weighted sums, which are then rounded as at :871 and :684.
- * blok_model_tensor returns a rank's shard for the expert tensors.  Steps are launched eagerly unless BLOK_MODEL_GRAPH=1. */
+ * blok_model_tensor returns a rank's shard for the expert tensors.  Steps are replayed from a CUDA graph that
+ * holds the all-reduces as well; BLOK_MODEL_GRAPH=0 in the environment keeps every launch eager. */
 int blok_model_set_comm(blok_model_t *model, blok_comm_t *comm);
 
 /* Synchronises `stream` and reports, once, whether any layer's bounded device-side wait gave up since the last check

@@ -87,6 +87,50 @@ def test_moe_decode_rejects_partial_expert_set(cuda):
     from blok_b200 import lib, synth
     w = synth.moe_layer_weights(cuda, seed=3, hidden=256, inter=256, experts=16, shared_inter=0, experts_local=8)
     layer = lib.MoeLayer(w)
+    assert not layer.has_partial()       # no shared expert: the share's output rows would have no finisher
     with pytest.raises(lib.BlokError) as e:
         layer.decode(torch.zeros(256, dtype=torch.bfloat16, device=cuda))
     assert e.value.code == -7
+
+
+@pytest.mark.parametrize("hidden,inter,experts,shared_inter,cuts", [(1024, 512, 32, 512, (0, 8, 32)), (512, 256, 16, 256, (0, 4, 9, 16)),
+                                                                    (7168, 2048, 32, 2048, (0, 12, 32))])
+def test_moe_decode_partial_shares_add_up(cuda, hidden, inter, experts, shared_inter, cuts):
+    """blok_moe_decode_partial on handles that each hold a range of the experts: every handle reports the whole layer's
+    routing and the same shared-expert output, and the shares, summed in fp32, rounded and added to the shared expert's
+    output, give blok_moe_decode's result (equal up to the order of the fp32 sum of the slots: a last place of bf16).
+    Many tokens in a row on the same handles: the number of slots a share runs changes from launch to launch (0 included),
+    which is what its launch-spanning counters must survive."""
+    from blok_b200 import lib, synth
+    w = synth.moe_layer_weights(cuda, seed=31, hidden=hidden, inter=inter, experts=experts, shared_inter=shared_inter)
+    whole = lib.MoeLayer(w)
+    shares = []
+    for lo, hi in zip(cuts[:-1], cuts[1:]):
+        ws = dict(w)
+        for k in ("gate_w", "gate_s", "up_w", "up_s", "down_w", "down_s"):
+            ws[k] = w[k][lo:hi].contiguous()
+        shares.append(lib.MoeLayer(ws, expert_base=lo))
+        assert shares[-1].has_partial()
+    xs = synth.activations(40, hidden, cuda, 31)
+    slots_seen = set()
+    for i in range(40):
+        y, ids, wts = whole.decode(xs[i], return_routing=True)
+        total = torch.zeros(hidden, dtype=torch.float32, device=cuda)
+        for (lo, hi), sh in zip(zip(cuts[:-1], cuts[1:]), shares):
+            part, shared, pid, pwt = sh.decode_partial(xs[i], return_routing=True)
+            assert torch.equal(pid, ids) and torch.equal(pwt, wts)
+            total += part
+            n_mine = int(((ids.int() & 0xFFFF) >= lo).sum() - ((ids.int() & 0xFFFF) >= hi).sum())
+            slots_seen.add(n_mine)
+            if n_mine == 0:
+                assert torch.count_nonzero(part) == 0
+        got = (total.bfloat16().float() + shared.float()).bfloat16()
+        diff = (got.float() - y.float()).abs()
+        assert float((diff / y.float().abs().clamp_min(1e-3)).max()) < 2 ** -6, i
+        assert float((got == y).float().mean()) > 0.9, i
+    for sh in shares:
+        sh.check()
+        sh.close()
+    whole.check()
+    whole.close()
+    assert len(slots_seen) > 2, slots_seen
