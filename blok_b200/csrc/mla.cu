@@ -14,6 +14,8 @@
 // One pass over the cache with an online softmax; the sequence is split over CTAs
 // (flash-decoding) and the partial results are merged by a second kernel.
 #include <cmath>
+#include <cstdlib>
+#include <cstring>
 #include <new>
 
 #include "bf16_mma.cuh"
@@ -210,6 +212,12 @@ __global__ void mla_merge_kernel(const float *__restrict__ part_o, const float *
 size_t mla_attend_smem_bytes();
 int launch_mla_attend(const uint16_t *q, const uint16_t *cache, long ctx_stride, const int *seq_len, int B, int splits,
                       float scale, float *part_o, float *part_ml, cudaStream_t stream);
+int launch_mla_attend_tc(const uint16_t *q, const uint16_t *cache, long ctx_stride, const int *seq_len, int B, int splits,
+                         float scale, float *part_o, float *part_ml, cudaStream_t stream);
+int launch_mla_attend_tc_paged(const uint16_t *q, const uint16_t *pool, const int *block_table, const int *slot_of,
+                               int table_stride, int page_rows, const int *seq_len, int B, int splits, float scale, float *part_o,
+                               float *part_ml, cudaStream_t stream);
+int mla_attend_tc_take_error(unsigned *out);
 int launch_mla_attend_paged(const uint16_t *q, const uint16_t *pool, const int *block_table, const int *slot_of,
                             int table_stride, int page_rows, const int *seq_len, int B, int splits, float scale,
                             float *part_o, float *part_ml, cudaStream_t stream);
@@ -389,6 +397,12 @@ extern "C" int blok_mla_layer_destroy(blok_mla_layer_t *L) {
 extern "C" int blok_mla_layer_check(blok_mla_layer_t *L, blok_stream_t stream) {
   BLOK_REQUIRE(L, BLOK_ERR_ARG, "blok_mla_layer_check: null pointer");
   BLOK_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  unsigned tc_err = 0;
+  if (int rc = mla_attend_tc_take_error(&tc_err)) return rc;
+  if (tc_err) {
+    set_error("blok_mla_decode: the attention core gave up on wait %u (1 tile buffer, 2-5 MMA thread, 6-9 softmax warps)", tc_err);
+    return BLOK_ERR_TIMEOUT;
+  }
   unsigned err = 0;
   BLOK_CUDA(cudaMemcpy(&err, L->err, sizeof(err), cudaMemcpyDeviceToHost));
   if (err == 0) return BLOK_OK;
@@ -420,9 +434,19 @@ static int splits_for(const blok_mla_layer *L, int B, long ctx_cap) {
 static int attend_and_merge(blok_mla_layer *L, const uint16_t *q, const CacheRef &c, const int *seq_len, int B, float scale,
                             uint16_t *o_lat, cudaStream_t stream) {
   const int splits = splits_for(L, B, c.ctx_cap);
-  int rc = c.block_table ? launch_mla_attend_paged(q, c.base, c.block_table, c.slot_of, c.table_stride, c.page_rows, seq_len, B,
-                                                   splits, scale, L->part_o, L->part_ml, stream)
-                         : launch_mla_attend(q, c.base, c.seq_stride, seq_len, B, splits, scale, L->part_o, L->part_ml, stream);
+  // the tcgen05 core by default; BLOK_MLA_ATTEND_IMPL=mma (read at every call) selects the mma.sync kernel, which also
+  // serves page sizes that are not a multiple of the tcgen05 core's 64-token tile
+  const char *impl = getenv("BLOK_MLA_ATTEND_IMPL");
+  const bool tc = !(impl && strcmp(impl, "mma") == 0) && (!c.block_table || c.page_rows % 64 == 0);
+  int rc;
+  if (tc)
+    rc = c.block_table ? launch_mla_attend_tc_paged(q, c.base, c.block_table, c.slot_of, c.table_stride, c.page_rows, seq_len, B, splits,
+                                                    scale, L->part_o, L->part_ml, stream)
+                       : launch_mla_attend_tc(q, c.base, c.seq_stride, seq_len, B, splits, scale, L->part_o, L->part_ml, stream);
+  else
+    rc = c.block_table ? launch_mla_attend_paged(q, c.base, c.block_table, c.slot_of, c.table_stride, c.page_rows, seq_len, B,
+                                                 splits, scale, L->part_o, L->part_ml, stream)
+                       : launch_mla_attend(q, c.base, c.seq_stride, seq_len, B, splits, scale, L->part_o, L->part_ml, stream);
   if (rc) return rc;
   mla_merge_kernel<<<dim3(L->w.heads, B), 128, (size_t)splits * sizeof(float), stream>>>(L->part_o, L->part_ml, splits, L->w.heads, L->w.kv_rank,
                                                            o_lat);

@@ -70,7 +70,10 @@ def test_attend_properties_at_full_size(cuda, layer32):
     # the same sequences one at a time use 148 splits instead of 18: the merged result must agree
     for b in (0, 7):
         o1 = layer.attend(q[b:b + 1].contiguous(), cache[b:b + 1].contiguous(), seq[b:b + 1].contiguous())
-        assert util.max_abs_rel(util.t2np_f32(o1[0]), util.t2np_f32(o8[b])) < 5e-3
+        # every probability enters the second product rounded to bf16 (src/kimi_exec.cu:466) relative to its split's own
+        # reference maximum, so two splittings differ by that rounding: about 2^-9 of an output's typical size, a few
+        # times that of the largest output at most
+        assert util.max_abs_rel(util.t2np_f32(o1[0]), util.t2np_f32(o8[b])) < 1e-2
     # softmax weights are a convex combination: every output lies inside the range of the cached values
     lo = cache[:, :, :512].float().amin(dim=1, keepdim=True)
     hi = cache[:, :, :512].float().amax(dim=1, keepdim=True)
