@@ -218,6 +218,7 @@ int launch_mla_attend_tc_paged(const uint16_t *q, const uint16_t *pool, const in
                                int table_stride, int page_rows, const int *seq_len, int B, int splits, float scale, float *part_o,
                                float *part_ml, cudaStream_t stream);
 int mla_attend_tc_take_error(unsigned *out);
+int mla_attend_tc_trace(long long *host_out, int max_entries);
 int launch_mla_attend_paged(const uint16_t *q, const uint16_t *pool, const int *block_table, const int *slot_of,
                             int table_stride, int page_rows, const int *seq_len, int B, int splits, float scale,
                             float *part_o, float *part_ml, cudaStream_t stream);
@@ -392,6 +393,11 @@ extern "C" int blok_mla_layer_destroy(blok_mla_layer_t *L) {
   cudaError_t e = L->ws ? cudaFree(L->ws) : cudaSuccess;
   delete L;
   return e == cudaSuccess ? BLOK_OK : cuda_fail(e, "cudaFree(mla layer workspace)");
+}
+
+extern "C" int blok_mla_attend_trace(long long *host_out, int max_entries) {
+  if (!host_out || max_entries <= 0) return 0;
+  return mla_attend_tc_trace(host_out, max_entries);
 }
 
 extern "C" int blok_mla_layer_check(blok_mla_layer_t *L, blok_stream_t stream) {

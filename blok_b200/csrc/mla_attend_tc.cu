@@ -14,7 +14,7 @@
 //                                                            (four blocks of 128 latent columns), B = P (K-major)
 //
 // The tile lies in shared memory in 8 x 16-byte core matrices without swizzle: element (token t, column c) at
-// (c / 8) * 1024 + (t / 8) * 128 + (t % 8) * 16 + (c % 8) * 2.  Read K-major that is a [64 tokens x 576] operand, read
+// (c / 8) * 1040 + (t / 8) * 128 + (t % 8) * 16 + (c % 8) * 2.  Read K-major that is a [64 tokens x 576] operand, read
 // MN-major the same bytes are a [512 x 64 tokens] operand: one copy from HBM serves both products.
 //
 // The running maximum is kept lazily: a head's reference m changes only when a tile's maximum exceeds it by more than
@@ -35,7 +35,9 @@ constexpr int kTaTile = 64;                              // tokens per tile
 constexpr int kTaKG = kTaD / 8;                          // 16-byte column groups of a cache row
 constexpr int kTaLbo = kTaTile * 16;                     // bytes between column groups (tile, Q and P alike: 64 rows)
 constexpr int kTaSbo = 128;                              // bytes between 8-row groups
-constexpr int kTaTileBytes = kTaKG * kTaLbo;             // 73,728
+constexpr int kTaTLbo = kTaLbo + 16;                     // the tile's column groups: + 16 bytes, so that a row's 8 neighbouring
+                                                         // groups, copied by 8 neighbouring lanes, land in 8 different banks
+constexpr int kTaTileBytes = kTaKG * kTaTLbo;            // 74,880
 constexpr int kTaQBytes = kTaKG * kTaLbo;                // 64 head rows
 constexpr int kTaPBytes = (kTaTile / 8) * kTaLbo;        // P: [64 heads x 64 tokens] bf16, K (token) major
 constexpr int kTaSmemBytes = kTaQBytes + 2 * kTaTileBytes + kTaPBytes;
@@ -45,6 +47,27 @@ constexpr int kTaTmemCols = 512;                         // S: 2 x 64 columns, O
 constexpr int kTaColO = 128;
 constexpr unsigned kTaSpinLimit = 1u << 21;
 constexpr float kTaLazy = 57.7f;                         // 40 natural units in the log2 domain
+constexpr int kTaTraceTiles = 64;
+// The score product as M = 64 (the 64 heads, no idle rows): its accumulator rows 16 w .. 16 w + 15 lie in lanes 0..15 of
+// warp w's quarter of tensor memory, so all four consumer warps take 16 head rows each.  false: M = 128 with 64 idle
+// rows, head h in lane h, two softmax warps.
+#ifndef BLOK_MLA_TC_M64
+#define BLOK_MLA_TC_M64 1
+#endif
+constexpr bool kTaM64 = BLOK_MLA_TC_M64 != 0;
+constexpr int kTaSoftmaxWarps = kTaM64 ? 4 : 2;
+
+__device__ __forceinline__ float ta_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// bf16 pair (hi in the upper half), both rounded to nearest even
+__device__ __forceinline__ uint32_t ta_pack_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
 
 __device__ unsigned g_mla_tc_error = 0;
 
@@ -130,12 +153,13 @@ template <bool PAGED>
 __global__ void __launch_bounds__(kTaThreads, 1)
     mla_attend_tc_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict__ cache, long ctx_stride,
                          const int *__restrict__ seq_len, float scale, float *__restrict__ part_o, float *__restrict__ part_ml,
-                         const int *__restrict__ block_table, const int *__restrict__ slot_of, int table_stride, int page_rows) {
+                         const int *__restrict__ block_table, const int *__restrict__ slot_of, int table_stride, int page_rows,
+                         long long *__restrict__ trace) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) unsigned long long s_bar[9];
   __shared__ uint32_t s_tmem;
   __shared__ float s_alpha[kTaHeads];
-  __shared__ int s_need[2][2];
+  __shared__ int s_need[2][4];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int split = blockIdx.x, splits = gridDim.x, b = blockIdx.y;
   const int seq = seq_len[b];
@@ -163,10 +187,10 @@ __global__ void __launch_bounds__(kTaThreads, 1)
     for (int i = 0; i < 2; ++i) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 2;" ::"r"(bar_full + 8 * i) : "memory");
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_sfull + 8 * i) : "memory");
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 2;" ::"r"(bar_sfree + 8 * i) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_sfree + 8 * i), "r"(kTaSoftmaxWarps) : "memory");
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_empty + 8 * i) : "memory");
     }
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 2;" ::"r"(bar_pfull) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_pfull), "r"(kTaSoftmaxWarps) : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
@@ -191,18 +215,28 @@ __global__ void __launch_bounds__(kTaThreads, 1)
   tc_fence_after();
   const uint32_t tmem = s_tmem;
   bool failed = false;
+  // diagnostics (trace != NULL): CTA (0, 0) stamps, per tile, [0] buffer free, [1] tile landed, [2] S issued,
+  // [3] S seen by the softmax warps, [4] P handed over, [5] P.C issued (nanoseconds)
+  auto stamp = [&](int n, int slot) {
+    if (trace && blockIdx.x == 0 && blockIdx.y == 0 && n < kTaTraceTiles) {
+      long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      trace[n * 16 + slot] = t;
+    }
+  };
 
   if (warp >= 4 && warp < 8) {
     // ---- producers: warps 4, 5 fill buffer 0 with the even tiles, warps 6, 7 buffer 1 with the odd ones ----
     const int buf = (warp - 4) >> 1, wi = (warp - 4) & 1;
     const uint16_t *cache_b = PAGED ? cache : cache + (size_t)b * ctx_stride * kTaD;
     const int *table_b = PAGED ? block_table + (size_t)(slot_of ? slot_of[b] : b) * table_stride : nullptr;
-    const int t8 = lane & 7, kq = lane >> 3;
+    const int g8 = lane & 7, t4 = lane >> 3;
     for (int n = buf; n < nt; n += 2) {
       if (n >= 2 && !ta_wait(bar_empty + 8 * buf, (uint32_t)(((n >> 1) - 1) & 1), 1u)) {
         failed = true;
         break;
       }
+      if (wi == 0 && lane == 0) stamp(n, 0);
       const int tok0 = (ts + n) * kTaTile;
       const uint16_t *base = cache_b;
       int first = 0;  // the row of `base` that holds token 0
@@ -210,50 +244,92 @@ __global__ void __launch_bounds__(kTaThreads, 1)
         base = cache + (size_t)table_b[tok0 / page_rows] * page_rows * kTaD;
         first = tok0 % page_rows - tok0;
       }
-      const uint32_t dst0 = sT + buf * kTaTileBytes + t8 * 16 + kq * kTaLbo;
-      // a warp's copy: 8 tokens x 4 column groups = 64 contiguous bytes of each of 8 rows in HBM, and per group of 8
-      // lanes 128 contiguous bytes of shared memory
-#pragma unroll 4
-      for (int it = wi; it < (kTaTile / 8) * (kTaKG / 4); it += 2) {
-        const int a = it & 7, bq = it >> 3;
-        const int tok = tok0 + 8 * a + t8;
-        const int row = min(tok, seq - 1) + first;  // rows past the end are filled with zeros (their P is zero too)
-        ta_cp16_zfill(dst0 + a * kTaSbo + bq * 4 * kTaLbo, base + (size_t)row * kTaD + (bq * 4 + kq) * 8, tok < seq ? 16u : 0u);
+      // a warp's copy: 4 tokens x 8 column groups = 128 contiguous bytes (a whole line) of each of 4 rows in HBM; the
+      // 32 pieces fall into the 8 bank groups of shared memory four times each
+      const uint32_t dst0 = sT + buf * kTaTileBytes + g8 * kTaTLbo + t4 * 16;
+      if (tok0 + kTaTile <= seq) {
+        // a whole tile: every address is a constant offset from two per-tile bases, so the warp issues its 72 copies
+        // back to back (one warp per scheduler has nobody to hide address arithmetic behind)
+        const unsigned char *src0 = reinterpret_cast<const unsigned char *>(base + (size_t)(tok0 + first + t4) * kTaD) + g8 * 16;
+#pragma unroll
+        for (int i = 0; i < kTaTile / 8; ++i) {
+          const unsigned char *sa = src0 + (size_t)(2 * i + wi) * 4 * kTaD * 2;  // tokens 8 i + 4 wi + t4
+          const uint32_t da = dst0 + i * kTaSbo + wi * 64;
+#pragma unroll
+          for (int kb = 0; kb < kTaKG / 8; ++kb)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(da + kb * 8 * kTaTLbo), "l"(sa + kb * 128));
+        }
+      } else {
+#pragma unroll 2
+        for (int i = 0; i < kTaTile / 8; ++i) {
+          const int tok = tok0 + 8 * i + 4 * wi + t4;
+          const int row = min(tok, seq - 1) + first;  // rows past the end are filled with zeros (their P is zero too)
+          const uint16_t *sa = base + (size_t)row * kTaD + g8 * 8;
+          const uint32_t da = dst0 + i * kTaSbo + wi * 64;
+          for (int kb = 0; kb < kTaKG / 8; ++kb) ta_cp16_zfill(da + kb * 8 * kTaTLbo, sa + kb * 64, tok < seq ? 16u : 0u);
+        }
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
+      if (wi == 0 && lane == 0 && n + 2 < nt) {
+        // The buffer's next tile starts its way from HBM to L2 now: by the time the buffer is free again (this tile's
+        // two products later) the copies above find it there, and HBM has been busy meanwhile.  A tile is contiguous
+        // (dense cache, or inside a page); only rows of the sequence are touched.
+        const int ptok = tok0 + 2 * kTaTile;
+        const int prow = min(kTaTile, seq - ptok);
+        const uint16_t *pbase = cache_b;
+        int pfirst = 0;
+        if (PAGED) {
+          pbase = cache + (size_t)table_b[ptok / page_rows] * page_rows * kTaD;
+          pfirst = ptok % page_rows - ptok;
+        }
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pbase + (size_t)(ptok + pfirst) * kTaD),
+                     "r"((uint32_t)(prow * kTaD * 2))
+                     : "memory");
+      }
+      if (wi == 0 && lane == 0) stamp(n, 6);
       asm volatile("cp.async.wait_group 0;" ::: "memory");
+      if (wi == 0 && lane == 0) stamp(n, 7);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tile is read by the tensor core's proxy
       __syncwarp();
       if (lane == 0) ta_arrive(bar_full + 8 * buf);
+      if (wi == 0 && lane == 0) stamp(n, 1);
     }
   } else if (warp == 8) {
     if (lane == 0) {
       // ---- the MMA thread ----
-      const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTaTile >> 3) << 17) | ((128u >> 4) << 24);
-      const uint32_t idesc_pv = idesc_s | (1u << 15);  // A (the tile) MN-major
+      const uint32_t idesc_128 = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTaTile >> 3) << 17) | ((128u >> 4) << 24);
+      const uint32_t idesc_s = kTaM64 ? (idesc_128 & ~(31u << 24)) | ((64u >> 4) << 24) : idesc_128;
+      const uint32_t idesc_pv = idesc_128 | (1u << 15);  // A (the tile) MN-major
       const uint64_t q_desc = ta_desc(sQ, kTaLbo, kTaSbo);
       auto issue_s = [&](int n) {
         const int buf = n & 1;
-        const uint64_t c_desc = ta_desc(sT + buf * kTaTileBytes, kTaLbo, kTaSbo);
+        stamp(n, 12);
+        const uint64_t c_desc = ta_desc(sT + buf * kTaTileBytes, kTaTLbo, kTaSbo);
 #pragma unroll 4
         for (int kk = 0; kk < kTaD / 16; ++kk)
-          ta_mma(tmem + 64 * buf, q_desc + (uint64_t)(kk * ((2 * kTaLbo) >> 4)), c_desc + (uint64_t)(kk * ((2 * kTaLbo) >> 4)), idesc_s,
+          ta_mma(tmem + 64 * buf, q_desc + (uint64_t)(kk * ((2 * kTaLbo) >> 4)), c_desc + (uint64_t)(kk * ((2 * kTaTLbo) >> 4)), idesc_s,
                  kk > 0 ? 1u : 0u);
         ta_commit(bar_sfull + 8 * buf);
+        stamp(n, 2);
       };
       auto issue_pv = [&](int n) {
         const int buf = n & 1;
+        stamp(n, 13);
+        // block j: latent columns [128 j, +128) = column groups [16 j, +16); a K step is 16 tokens = two 8-row groups.
+        // The four blocks take turns: consecutive MMAs then accumulate into different columns of tensor memory and do
+        // not wait for one another.
+        const uint64_t p_desc = ta_desc(sP, kTaLbo, kTaSbo);
 #pragma unroll
-        for (int j = 0; j < kTaDV / 128; ++j) {
-          // block j: latent columns [128 j, +128) = column groups [16 j, +16); a K step is 16 tokens = two 8-row groups
-          const uint64_t a_desc = ta_desc(sT + buf * kTaTileBytes + j * 16 * kTaLbo, kTaSbo, kTaLbo);
-          const uint64_t p_desc = ta_desc(sP, kTaLbo, kTaSbo);
+        for (int kk = 0; kk < kTaTile / 16; ++kk) {
 #pragma unroll
-          for (int kk = 0; kk < kTaTile / 16; ++kk)
+          for (int j = 0; j < kTaDV / 128; ++j) {
+            const uint64_t a_desc = ta_desc(sT + buf * kTaTileBytes + j * 16 * kTaTLbo, kTaSbo, kTaTLbo);
             ta_mma(tmem + kTaColO + 64 * j, a_desc + (uint64_t)(kk * ((2 * kTaSbo) >> 4)), p_desc + (uint64_t)(kk * ((2 * kTaLbo) >> 4)),
                    idesc_pv, (n > 0 || kk > 0) ? 1u : 0u);
+          }
         }
         ta_commit(bar_empty + 8 * buf);
+        stamp(n, 5);
       };
       if (!ta_wait(bar_full, 0u, 2u)) failed = true;
       if (!failed) {
@@ -291,48 +367,60 @@ __global__ void __launch_bounds__(kTaThreads, 1)
     // ---- consumers ----
     const float sl2 = scale * 1.4426950408889634f;
     float m_ref = -INFINITY, l = 0.f;
+    // this thread's head row of S (row_ok: the lane holds one)
+    const bool row_ok = kTaM64 ? lane < 16 : true;
+    const int head = kTaM64 ? 16 * warp + lane : tid;
     for (int n = 0; n < nt; ++n) {
       const int buf = n & 1;
       uint32_t pk[kTaTile / 2];
-      if (warp < 2) {
+      if (warp < kTaSoftmaxWarps) {
         bool need = false;
         if (!failed && !ta_wait(bar_sfull + 8 * buf, (uint32_t)((n >> 1) & 1), 6u)) failed = true;
         if (!failed) {
+          if (tid == 0) stamp(n, 3);
           tc_fence_after();
           uint32_t r[kTaTile];
           tmem_ld64(tmem + ((uint32_t)(32 * warp) << 16) + 64 * buf, r);
           tmem_wait_ld();
+          if (tid == 0) stamp(n, 8);
           tc_fence_before();
           __syncwarp();
           if (lane == 0) ta_arrive(bar_sfree + 8 * buf);
           const int tok0 = (ts + n) * kTaTile;
-          float mx = -INFINITY;
+          if (tok0 + kTaTile > seq) {  // the sequence's last tile: tokens past the end take no weight
 #pragma unroll
-          for (int j = 0; j < kTaTile; ++j) {
-            const float v = tok0 + j < seq ? __uint_as_float(r[j]) * sl2 : -INFINITY;
-            r[j] = __float_as_uint(v);
-            mx = fmaxf(mx, v);
+            for (int j = 0; j < kTaTile; ++j)
+              if (tok0 + j >= seq) r[j] = 0xff800000u;
           }
+          float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < kTaTile; j += 2) {
+            mx0 = fmaxf(mx0, __uint_as_float(r[j]));
+            mx1 = fmaxf(mx1, __uint_as_float(r[j + 1]));
+          }
+          const float mx = fmaxf(mx0, mx1) * sl2;  // the scale is positive
           float alpha = 1.f;
           if (n == 0) {
             m_ref = mx;  // the split's first tile holds at least one token
           } else if (mx > m_ref + kTaLazy) {
             alpha = exp2f(m_ref - mx);
             m_ref = mx;
-            need = true;
+            need = row_ok;
           }
-          s_alpha[tid] = alpha;
-          float sum = 0.f;
+          if (row_ok) s_alpha[head] = alpha;
+          const float nm = -m_ref;
+          float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
           for (int j = 0; j < kTaTile; j += 2) {
             // the probabilities enter the second product rounded to bf16 (as the reference rounds them, :466); the
             // normaliser sums the same rounded values
-            const float p0 = round_bf16(exp2f(__uint_as_float(r[j]) - m_ref));
-            const float p1 = round_bf16(exp2f(__uint_as_float(r[j + 1]) - m_ref));
-            sum += p0 + p1;
-            pk[j >> 1] = pack_bf16x2(p0, p1);
+            const uint32_t pp = ta_pack_bf16x2(ta_ex2(fmaf(__uint_as_float(r[j]), sl2, nm)), ta_ex2(fmaf(__uint_as_float(r[j + 1]), sl2, nm)));
+            sum0 += __uint_as_float(pp << 16);
+            sum1 += __uint_as_float(pp & 0xffff0000u);
+            pk[j >> 1] = pp;
           }
-          l = l * alpha + sum;
+          l = l * alpha + (sum0 + sum1);
+          if (tid == 0) stamp(n, 9);
         }
         need = __any_sync(0xffffffffu, need);
         if (lane == 0) s_need[buf][warp] = need ? 1 : 0;
@@ -341,7 +429,7 @@ __global__ void __launch_bounds__(kTaThreads, 1)
         failed = true;
         break;
       }
-      if (s_need[buf][0] | s_need[buf][1]) {
+      if (s_need[buf][0] | s_need[buf][1] | (kTaM64 ? s_need[buf][2] | s_need[buf][3] : 0)) {
         // a head's reference maximum moved (never in tile 0): every lane of O^T scales its 4 x 64 head columns, once the
         // previous tile's MMAs have finished with them
         if (!ta_wait(bar_empty + 8 * ((n - 1) & 1), (uint32_t)(((n - 1) >> 1) & 1), 7u)) failed = true;
@@ -365,16 +453,21 @@ __global__ void __launch_bounds__(kTaThreads, 1)
           break;
         }
       }
-      if (warp < 2 && !failed) {
+      if (tid == 0) stamp(n, 10);
+      if (warp < kTaSoftmaxWarps && !failed) {
         if (n > 0 && !ta_wait(bar_empty + 8 * ((n - 1) & 1), (uint32_t)(((n - 1) >> 1) & 1), 8u)) {
           failed = true;  // reaches the others at the next tile's barrier
         } else {
+          if (tid == 0) stamp(n, 11);
+          if (row_ok) {
 #pragma unroll
-          for (int kg = 0; kg < kTaTile / 8; ++kg)
-            *reinterpret_cast<uint4 *>(Pp + kg * kTaLbo + tid * 16) = make_uint4(pk[4 * kg], pk[4 * kg + 1], pk[4 * kg + 2], pk[4 * kg + 3]);
+            for (int kg = 0; kg < kTaTile / 8; ++kg)
+              *reinterpret_cast<uint4 *>(Pp + kg * kTaLbo + head * 16) = make_uint4(pk[4 * kg], pk[4 * kg + 1], pk[4 * kg + 2], pk[4 * kg + 3]);
+          }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           __syncwarp();
           if (lane == 0) ta_arrive(bar_pfull);
+          if (tid == 0) stamp(n, 4);
         }
       }
     }
@@ -395,9 +488,9 @@ __global__ void __launch_bounds__(kTaThreads, 1)
           for (int c = 0; c < 32; ++c) po[(size_t)(32 * half + c) * kTaDV + 128 * j + 32 * warp + lane] = __uint_as_float(o[c]);
         }
       }
-      if (tid < kTaHeads) {
-        my_ml[tid * 2] = m_ref * 0.6931471805599453f;  // back to natural units
-        my_ml[tid * 2 + 1] = l;
+      if (warp < kTaSoftmaxWarps && row_ok) {
+        my_ml[head * 2] = m_ref * 0.6931471805599453f;  // back to natural units
+        my_ml[head * 2 + 1] = l;
       }
     }
   }
@@ -415,6 +508,27 @@ int mla_attend_tc_take_error(unsigned *out) {
   return BLOK_OK;
 }
 
+// BLOK_MLA_TRACE=1 in the environment at the first launch: CTA (0, 0) of every launch records the time stamps described
+// in the kernel; blok_mla_attend_trace copies them out.
+static long long *g_trace_buf = nullptr;
+static long long *trace_buffer() {
+  static bool asked = false;
+  if (!asked) {
+    asked = true;
+    const char *e = getenv("BLOK_MLA_TRACE");
+    if (e && e[0] == '1' && cudaMalloc(&g_trace_buf, kTaTraceTiles * 16 * sizeof(long long)) == cudaSuccess)
+      cudaMemset(g_trace_buf, 0, kTaTraceTiles * 16 * sizeof(long long));
+  }
+  return g_trace_buf;
+}
+int mla_attend_tc_trace(long long *host_out, int max_entries) {
+  if (!g_trace_buf) return 0;
+  const int n = max_entries < kTaTraceTiles * 16 ? max_entries : kTaTraceTiles * 16;
+  if (cudaDeviceSynchronize() != cudaSuccess || cudaMemcpy(host_out, g_trace_buf, (size_t)n * sizeof(long long), cudaMemcpyDeviceToHost) != cudaSuccess)
+    return 0;
+  return n;
+}
+
 int launch_mla_attend_tc(const uint16_t *q, const uint16_t *cache, long ctx_stride, const int *seq_len, int B, int splits,
                          float scale, float *part_o, float *part_ml, cudaStream_t stream) {
   static bool configured = false;
@@ -423,7 +537,7 @@ int launch_mla_attend_tc(const uint16_t *q, const uint16_t *cache, long ctx_stri
     configured = true;
   }
   mla_attend_tc_kernel<false><<<dim3(splits, B), kTaThreads, kTaSmemBytes, stream>>>(q, cache, ctx_stride, seq_len, scale, part_o,
-                                                                                     part_ml, nullptr, nullptr, 0, 0);
+                                                                                     part_ml, nullptr, nullptr, 0, 0, trace_buffer());
   return launch_status("mla_attend_tc_kernel");
 }
 
@@ -437,7 +551,8 @@ int launch_mla_attend_tc_paged(const uint16_t *q, const uint16_t *pool, const in
     configured = true;
   }
   mla_attend_tc_kernel<true><<<dim3(splits, B), kTaThreads, kTaSmemBytes, stream>>>(q, pool, 0, seq_len, scale, part_o, part_ml,
-                                                                                    block_table, slot_of, table_stride, page_rows);
+                                                                                    block_table, slot_of, table_stride, page_rows,
+                                                                                    trace_buffer());
   return launch_status("mla_attend_tc_kernel(paged)");
 }
 

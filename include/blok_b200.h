@@ -254,6 +254,12 @@ int blok_moe_layer_check(blok_moe_layer_t *layer, blok_stream_t stream);
  * blok_moe_decode_host) can be exercised. */
 int blok_moe_layer_debug_set_error(blok_moe_layer_t *layer, unsigned code, blok_stream_t stream);
 
+/* Diagnostics (no counterpart in the reference): with BLOK_MLA_TRACE=1 in the environment at the first attention
+ * launch, CTA (0, 0) of the attention core records, for its first 64 tiles of 64 tokens, 16 slots of nanosecond time
+ * stamps per tile (buffer free, tile landed, scores issued, scores seen, probabilities handed over, P.C issued, ...: the
+ * kernel's source lists them).  Copies up to max_entries of them to host_out after a device synchronise; returns the count (0: tracing off). */
+int blok_mla_attend_trace(long long *host_out, int max_entries);
+
 /* Diagnostics (no counterpart in the reference): when the handle was created with
  * the environment variable BLOK_MOE_TRACE=1, the fused decode kernel records
  * nanosecond time stamps: 16 launch-wide slots, then 16 slots per CTA.  Copies up to max_entries of
