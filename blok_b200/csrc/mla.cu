@@ -212,9 +212,9 @@ __global__ void mla_merge_kernel(const float *__restrict__ part_o, const float *
 size_t mla_attend_smem_bytes();
 int launch_mla_attend(const uint16_t *q, const uint16_t *cache, long ctx_stride, const int *seq_len, int B, int splits,
                       float scale, float *part_o, float *part_ml, cudaStream_t stream);
-int launch_mla_attend_tc(const uint16_t *q, const uint16_t *cache, long ctx_stride, const int *seq_len, int B, int splits,
+int launch_mla_attend_tc(const uint16_t *q, const uint16_t *cache, long ctx_stride, long total_rows, const int *seq_len, int B, int splits,
                          float scale, float *part_o, float *part_ml, cudaStream_t stream);
-int launch_mla_attend_tc_paged(const uint16_t *q, const uint16_t *pool, const int *block_table, const int *slot_of,
+int launch_mla_attend_tc_paged(const uint16_t *q, const uint16_t *pool, long pool_rows, const int *block_table, const int *slot_of,
                                int table_stride, int page_rows, const int *seq_len, int B, int splits, float scale, float *part_o,
                                float *part_ml, cudaStream_t stream);
 int mla_attend_tc_take_error(unsigned *out);
@@ -445,11 +445,14 @@ static int attend_and_merge(blok_mla_layer *L, const uint16_t *q, const CacheRef
   const char *impl = getenv("BLOK_MLA_ATTEND_IMPL");
   const bool tc = !(impl && strcmp(impl, "mma") == 0) && (!c.block_table || c.page_rows % 64 == 0);
   int rc;
-  if (tc)
-    rc = c.block_table ? launch_mla_attend_tc_paged(q, c.base, c.block_table, c.slot_of, c.table_stride, c.page_rows, seq_len, B, splits,
-                                                    scale, L->part_o, L->part_ml, stream)
-                       : launch_mla_attend_tc(q, c.base, c.seq_stride, seq_len, B, splits, scale, L->part_o, L->part_ml, stream);
-  else
+  if (tc) {
+    // the rows the tensor map may address: the whole dense cache (reads past it give zeros); a paged tile never leaves
+    // its page, so the pool needs no tighter bound than the coordinate range
+    const long dense_rows = c.seq_stride > 0 ? (long)B * c.seq_stride : c.ctx_cap;
+    rc = c.block_table ? launch_mla_attend_tc_paged(q, c.base, (1l << 31) - 64, c.block_table, c.slot_of, c.table_stride, c.page_rows, seq_len,
+                                                    B, splits, scale, L->part_o, L->part_ml, stream)
+                       : launch_mla_attend_tc(q, c.base, c.seq_stride, dense_rows, seq_len, B, splits, scale, L->part_o, L->part_ml, stream);
+  } else
     rc = c.block_table ? launch_mla_attend_paged(q, c.base, c.block_table, c.slot_of, c.table_stride, c.page_rows, seq_len, B,
                                                  splits, scale, L->part_o, L->part_ml, stream)
                        : launch_mla_attend(q, c.base, c.seq_stride, seq_len, B, splits, scale, L->part_o, L->part_ml, stream);

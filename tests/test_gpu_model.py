@@ -70,6 +70,7 @@ class OracleModel:
             x = o.add_round(x, f)
         n = o.rmsnorm(x, self.norm, c.final_rms_eps, mode=1)
         logits = o.bf16_gemv(self.head, n, mode=0, round_out=True)
+        self.last_hidden = n        # the final-normed hidden state the sampler reads (:880-881)
         self.pos += 1
         order = np.argsort(-logits, kind="stable")
         return int(order[0]), float(logits[order[0]] - logits[order[1]]), x
@@ -102,6 +103,31 @@ def test_model_steps_match_oracle(cuda, oracle):
             assert got == want, "step %d: got %d want %d (margin %.3f)" % (step, got, want, margin)
         ids = torch.tensor([want], dtype=torch.int32, device=cuda)
     assert clear >= total - 2
+    model.close()
+
+
+def test_full_size_layers_and_full_vocabulary_match_oracle(cuda, oracle):
+    """Config 4's shapes at full size, two layers deep (the dense layer and one MoE layer of 384 experts, hidden 7168,
+    MLA with 64 heads, vocabulary 163840): three decode steps against the oracle's composition of the same layers.
+    Checked per step: the final-normed hidden state (blok_model_hidden) and the greedy token over the whole vocabulary."""
+    from blok_b200 import lib
+    model = lib.Model(seed=4, layers=2, max_batch=1, max_ctx=16)
+    _sharpen(model)
+    orc = OracleModel(oracle, model)
+    ids = torch.tensor([11], dtype=torch.int32, device=cuda)
+    clear = 0
+    for step in range(3):
+        nxt = model.step(ids)
+        got_hidden = util.t2np_f32(model.hidden(1))[0]
+        want, margin, _ = orc.step(int(ids[0]))
+        r, c = util.assert_close(got_hidden, util.bf16_np_to_f32(util.f32_to_bf16_np(orc.last_hidden)), "full-size hidden state, step %d" % step)
+        if margin > 0.02:
+            clear += 1
+            assert int(nxt[0]) == want, "step %d: got %d want %d (margin %.3f)" % (step, int(nxt[0]), want, margin)
+        print("step %d: hidden max-abs-rel %.2e cosine %.6f, token %d (oracle %d, margin %.3f)" % (step, r, c, int(nxt[0]), want, margin))
+        ids = torch.tensor([want], dtype=torch.int32, device=cuda)
+    assert clear >= 2
+    model.check()
     model.close()
 
 

@@ -66,6 +66,37 @@ def test_moe_batched_agrees_with_decode_path_at_2048_tokens(cuda):
     layer.close()
 
 
+def test_moe_batched_2048_tokens_against_the_oracle(cuda, oracle):
+    """Config 2's large case at full size (T = 2048, 384 experts): the routing of EVERY token against the oracle, in
+    selection order, and the layer output of 64 tokens spread over the batch against the oracle's layer."""
+    from blok_b200 import lib, synth
+    w = synth.moe_layer_weights(cuda, seed=2)
+    layer = lib.MoeLayer(w, max_tokens=2048)
+    x = synth.activations(2048, 7168, cuda, 2)
+    y, ids, wts = layer.batched(x, return_routing=True)
+    layer.check()
+    ids_h, wts_h = util.ids_np(ids), util.t2np_f32(wts)
+    oid, owt, margin, _ = oracle.router(util.t2np_bf16(w["router_w"]), util.t2np_f32(w["router_bias"]), util.t2np_f32(x), mode=0)
+    # a token's selection is beyond doubt when the 8th and 9th candidates are apart (margin) and so are the selected ones
+    # among themselves (their weights are the scores, normalised: distinct weights, distinct scores)
+    gaps = np.abs(np.diff(np.sort(owt, axis=1), axis=1)).min(axis=1)
+    clear = (margin > MARGIN) & (gaps > 1e-6)
+    assert clear.mean() > 0.9
+    assert np.array_equal(ids_h[clear], oid[clear]), "top-k ids, in selection order"
+    np.testing.assert_allclose(wts_h[clear], owt[clear], rtol=2e-5)
+    sample = np.nonzero(clear)[0][:: max(1, int(clear.sum()) // 64)][:64]
+    assert len(sample) == 64
+    xs = x[torch.from_numpy(sample).to(cuda)]
+    out, _, _ = _oracle_layer(oracle, w, xs, list(oid[sample].ravel()))
+    yh = util.t2np_f32(y)
+    worst = 0.0
+    for i, t in enumerate(sample):
+        r, c = util.assert_close(yh[t], out[i], "T=2048 token %d" % t)
+        worst = max(worst, r)
+    print("T=2048: %d tokens routed as the oracle routes them, 64 outputs checked, worst max-abs-rel %.2e" % (int(clear.sum()), worst))
+    layer.close()
+
+
 @pytest.mark.parametrize("impl", ["mma", "tc"])
 def test_experts_grouped_handles_empty_and_ragged_groups(cuda, oracle, monkeypatch, impl):
     """Assignments concentrated on few experts (others get zero tokens), more than one 64-token tile for one expert."""
