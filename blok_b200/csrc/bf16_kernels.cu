@@ -115,6 +115,10 @@ __global__ void bf16_gemv_scalar_kernel(const uint16_t *__restrict__ w, const ui
 // so that every SM streams weights whatever the row count, and a CTA stages only its own K-range of the
 // activations.  Partial sums go to `part` ([ksplit][rows / 16][16][8] fp32); the CTA that draws the last ticket of a
 // row block adds them in split order (deterministic) and writes the rounded result, then re-arms the ticket.
+// STAGE false: the activations are not copied to shared memory at all; every lane reads its token's 16 bytes of a k-step
+// straight from global memory, which the L1 keeps (the weights bypass it).  With more than two tokens a CTA's staged
+// slice is no longer small against its 16 weight rows, and without shared memory more CTAs fit on an SM.
+template <bool STAGE>
 __global__ void __launch_bounds__(128) bf16_gemv16_splitk_kernel(const uint16_t *__restrict__ w, const uint16_t *__restrict__ x,
                                                                  uint16_t *__restrict__ y_bf16, float *__restrict__ y_f32,
                                                                  int rows, int cols, int T, int ksteps_per_split,
@@ -130,16 +134,19 @@ __global__ void __launch_bounds__(128) bf16_gemv16_splitk_kernel(const uint16_t 
   // stage x[:, 32 kbeg .. 32 (kbeg + kn)) with the row skew of stage_x_bf16
   const int per_row = kn * 4;  // uint4 per token row
   const size_t row_bytes = bf16_x_row_bytes(kn * 32);
-  for (int u = tid; u < per_row * T; u += blockDim.x) {
-    const int tok = u / per_row, c = u - tok * per_row;
-    reinterpret_cast<uint4 *>(smem + tok * row_bytes)[c] = reinterpret_cast<const uint4 *>(x + (size_t)tok * cols)[kbeg * 4 + c];
+  if (STAGE) {
+    for (int u = tid; u < per_row * T; u += blockDim.x) {
+      const int tok = u / per_row, c = u - tok * per_row;
+      reinterpret_cast<uint4 *>(smem + tok * row_bytes)[c] = reinterpret_cast<const uint4 *>(x + (size_t)tok * cols)[kbeg * 4 + c];
+    }
+    __syncthreads();
   }
-  __syncthreads();
   const size_t wrow = cols / 8;
   const uint4 *w_lo = reinterpret_cast<const uint4 *>(w) + (size_t)(blockIdx.x * 16 + g) * wrow + (size_t)kbeg * 4;
   const uint4 *w_hi = w_lo + 8 * wrow;
   const int tok = g < T ? g : T - 1;
-  const uint4 *xrow = reinterpret_cast<const uint4 *>(smem + tok * row_bytes) + t;
+  const uint4 *xrow = STAGE ? reinterpret_cast<const uint4 *>(smem + tok * row_bytes) + t
+                            : reinterpret_cast<const uint4 *>(x + (size_t)tok * cols) + (size_t)kbeg * 4 + t;
   const int base = kn / 4, rem = kn % 4;
   const int ks0 = warp * base + (warp < rem ? warp : rem);
   const int nsteps = base + (warp < rem ? 1 : 0);
@@ -296,17 +303,21 @@ int launch_bf16_gemv_splitk(const uint16_t *w, const uint16_t *x, uint16_t *y_bf
   const bool ok = rows % 16 == 0 && cols % 32 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 &&
                   (reinterpret_cast<uintptr_t>(x) & 15) == 0 && T >= 1 && T <= 8 && ws &&
                   ws_bytes >= bf16_gemv_splitk_workspace_bytes(rows);
-  // with more than two tokens the staged activation slice is no longer small against a CTA's 16 weight rows
-  if (!ok || ksplit < 2 || T > 2) return launch_bf16_gemv(w, x, y_bf16, y_f32, rows, cols, T, stream);
+  if (!ok || (ksplit < 2 && T <= 2)) return launch_bf16_gemv(w, x, y_bf16, y_f32, rows, cols, T, stream);
+  ksplit = std::max(ksplit, 1);
   const int per = (ksteps + ksplit - 1) / ksplit;
   ksplit = (ksteps + per - 1) / per;
   // the ticket block is sized for the largest matrix the workspace was made for; this matrix uses its first rb words
   unsigned *tickets = static_cast<unsigned *>(ws);
   float *part = reinterpret_cast<float *>(static_cast<unsigned char *>(ws) + (ws_bytes - ((size_t)4 * sm_count() + rb) * 128 * 4) / 256 * 256);
+  if (T > 2) {  // activations through the L1, no shared memory
+    bf16_gemv16_splitk_kernel<false><<<dim3(rb, ksplit), 128, 0, stream>>>(w, x, y_bf16, y_f32, rows, cols, T, per, part, tickets);
+    return launch_status("bf16_gemv16_splitk_kernel<l1>");
+  }
   const size_t smem = bf16_x_row_bytes(per * 32) * T;
   if (smem > 48 * 1024)
-    BLOK_CUDA(cudaFuncSetAttribute(bf16_gemv16_splitk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  bf16_gemv16_splitk_kernel<<<dim3(rb, ksplit), 128, smem, stream>>>(w, x, y_bf16, y_f32, rows, cols, T, per, part, tickets);
+    BLOK_CUDA(cudaFuncSetAttribute(bf16_gemv16_splitk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  bf16_gemv16_splitk_kernel<true><<<dim3(rb, ksplit), 128, smem, stream>>>(w, x, y_bf16, y_f32, rows, cols, T, per, part, tickets);
   return launch_status("bf16_gemv16_splitk_kernel");
 }
 

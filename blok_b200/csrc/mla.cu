@@ -201,11 +201,39 @@ __global__ void mla_merge_kernel(const float *__restrict__ part_o, const float *
   L = (s_red[1][0] + s_red[1][1]) + (s_red[1][2] + s_red[1][3]);
   const float inv = L > 0.f ? 1.0f / L : 0.f;
   const float *po = part_o + ((size_t)b * splits * heads + h) * kv_rank;  // split s at + s * heads * kv_rank
-  for (int j = tid; j < kv_rank; j += blockDim.x) {
-    float acc = 0.f;
-#pragma unroll 4
-    for (int s = 0; s < splits; ++s) acc = fmaf(s_wt[s], po[(size_t)s * heads * kv_rank + j], acc);
-    o_lat[((size_t)b * heads + h) * kv_rank + j] = f32_to_bf16_bits(acc * inv);
+  // four columns per thread, eight splits' worth of loads in flight per thread: the partial results (B x splits x 128 KB)
+  // come from L2 or HBM, and the kernel is as fast as it keeps bytes in flight.  Each column still adds its splits in
+  // ascending order.
+  const float4 *po4 = reinterpret_cast<const float4 *>(po);
+  const size_t stride4 = (size_t)heads * kv_rank / 4;
+  for (int j4 = tid; j4 < kv_rank / 4; j4 += blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    int s = 0;
+    for (; s + 8 <= splits; s += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = __ldg(po4 + (size_t)(s + i) * stride4 + j4);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float wt = s_wt[s + i];
+        acc.x = fmaf(wt, v[i].x, acc.x);
+        acc.y = fmaf(wt, v[i].y, acc.y);
+        acc.z = fmaf(wt, v[i].z, acc.z);
+        acc.w = fmaf(wt, v[i].w, acc.w);
+      }
+    }
+    for (; s < splits; ++s) {
+      const float4 v = __ldg(po4 + (size_t)s * stride4 + j4);
+      const float wt = s_wt[s];
+      acc.x = fmaf(wt, v.x, acc.x);
+      acc.y = fmaf(wt, v.y, acc.y);
+      acc.z = fmaf(wt, v.z, acc.z);
+      acc.w = fmaf(wt, v.w, acc.w);
+    }
+    uint2 o;
+    o.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+    o.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2 *>(o_lat + ((size_t)b * heads + h) * kv_rank + (size_t)j4 * 4) = o;
   }
 }
 

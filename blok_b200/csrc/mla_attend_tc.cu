@@ -8,7 +8,7 @@
 // 64 x (576 + 512) multiply-adds.  A CTA owns one (sequence, token range) and walks it in tiles of 64 tokens:
 //
 //   S [heads x tokens]     = Q [heads x 576] . C^T          36 MMAs M64 N64 K16: A = Q (shared memory, K-major, no
-//                                                            swizzle), B = the tile read K-major
+//                                                            swizzle), B = the tile read K-major; two partial sums
 //   P = exp2(S * scale * log2 e - m)                         one head row per thread (tcgen05.ld), bf16, to shared memory
 //   O^T [latent x heads]  += C^T [latent x tokens] . P^T     16 MMAs M128 N64 K16: A = the SAME tile bytes read MN-major
 //                                                            (four blocks of 128 latent columns), B = P (K-major)
@@ -46,8 +46,8 @@ constexpr int kTaPBytes = (kTaTile / 8) * kTaLbo;        // P: [64 heads x 64 to
 constexpr int kTaSmemBytes = 2 * kTaTileBytes + kTaQBytes + kTaPBytes + 1024;  // + 1024: the tiles start on a 1,024-byte boundary
 constexpr int kTaConsumers = 128;
 constexpr int kTaThreads = kTaConsumers + 64;
-constexpr int kTaTmemCols = 512;                         // S: 2 x 64 columns, O^T: 4 x 64 columns
-constexpr int kTaColO = 128;
+constexpr int kTaTmemCols = 512;                         // S: 2 buffers x 2 partial sums x 64 columns, O^T: 4 x 64 columns
+constexpr int kTaColO = 256;
 constexpr unsigned kTaSpinLimit = 1u << 21;
 constexpr float kTaLazy = 57.7f;                         // 40 natural units in the log2 domain
 constexpr int kTaTraceTiles = 64;
@@ -310,14 +310,18 @@ __global__ void __launch_bounds__(kTaThreads, 1)
       };
       auto issue_s = [&](int n) {
         const int buf = n & 1;
-        const uint32_t tile = sT + buf * kTaTileBytes;
+        // every descriptor below is a per-tile base plus a constant: the start address sits in the low bits (16-byte units,
+        // 14 bits for 256 KB) and no offset used here carries out of them
+        const uint64_t c_desc = ta_desc_sw128(sT + buf * kTaTileBytes, 16, 1024);
 #pragma unroll
         for (int c = 0; c < kTaChunks; ++c) {
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4) {
             const int kk = 4 * c + k4;  // K step of 16 columns: two column groups of Q, 32 bytes of the chunk's rows
-            ta_mma(tmem + 64 * buf, q_desc + (uint64_t)(kk * ((2 * kTaLbo) >> 4)), ta_desc_sw128(tile + c * kTaChunkBytes + k4 * 32, 16, 1024),
-                   idesc_s, kk > 0 ? 1u : 0u);
+            // even and odd K steps accumulate into two partial sums: an MMA of this size is shorter than the wait for the
+            // previous one's accumulator, and two chains halve that wait
+            ta_mma(tmem + 128 * buf + 64 * (kk & 1), q_desc + (uint64_t)(kk * ((2 * kTaLbo) >> 4)),
+                   c_desc + (uint64_t)((c * kTaChunkBytes + k4 * 32) >> 4), idesc_s, kk > 1 ? 1u : 0u);
           }
         }
         ta_commit(bar_sfull + 8 * buf);
@@ -325,7 +329,7 @@ __global__ void __launch_bounds__(kTaThreads, 1)
       };
       auto issue_pv = [&](int n) {
         const int buf = n & 1;
-        const uint32_t tile = sT + buf * kTaTileBytes;
+        const uint64_t a_desc = ta_desc_sw128(sT + buf * kTaTileBytes, kTaChunkBytes, 1024);
         // block j: latent columns [128 j, +128) = chunks 2 j and 2 j + 1; a K step is 16 tokens = two 8-row groups.  The
         // four blocks take turns: consecutive MMAs then accumulate into different columns of tensor memory and do not
         // wait for one another.
@@ -333,7 +337,7 @@ __global__ void __launch_bounds__(kTaThreads, 1)
         for (int kk = 0; kk < kTaTile / 16; ++kk) {
 #pragma unroll
           for (int j = 0; j < kTaDV / 128; ++j)
-            ta_mma(tmem + kTaColO + 64 * j, ta_desc_sw128(tile + 2 * j * kTaChunkBytes + kk * 2048, kTaChunkBytes, 1024),
+            ta_mma(tmem + kTaColO + 64 * j, a_desc + (uint64_t)((2 * j * kTaChunkBytes + kk * 2048) >> 4),
                    p_desc + (uint64_t)(kk * ((2 * kTaLbo) >> 4)), idesc_pv, (n > 0 || kk > 0) ? 1u : 0u);
         }
         ta_commit(bar_empty + 8 * buf);
@@ -384,8 +388,14 @@ __global__ void __launch_bounds__(kTaThreads, 1)
         if (tid == 0) stamp(n, 3);
         tc_fence_after();
         uint32_t r[kTaTile];
-        tmem_ld64(tmem + ((uint32_t)(32 * warp) << 16) + 64 * buf, r);
-        tmem_wait_ld();
+        {
+          uint32_t r2[kTaTile];  // the two partial sums of the score product
+          tmem_ld64(tmem + ((uint32_t)(32 * warp) << 16) + 128 * buf, r);
+          tmem_ld64(tmem + ((uint32_t)(32 * warp) << 16) + 128 * buf + 64, r2);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < kTaTile; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+        }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) ta_arrive(bar_sfree + 8 * buf);
