@@ -319,6 +319,8 @@ def other_workload(a, rank, world, device, steps, warmup):
 
     peak, peak_kind = measured_peak()
     flops = None  # set by the batched workloads: multiply-add work of a step on this GPU
+    extra = {}    # workload-specific figures that go into the line's config
+    unit = "tok/s"
     if a.workload == "model":
         # config 4 on what ONE GPU holds: layer 0 dense + (model_layers - 1) MoE layers of the full shapes, full
         # vocabulary, batch 1, greedy decode after a 32-token prompt replay.  A step is one new token through every
@@ -447,6 +449,44 @@ def other_workload(a, rank, world, device, steps, warmup):
             workload = "REDUCED CASE (%d experts, profiler capture size) of " % a.experts + workload
         scaling = "strong"
         metric = "tok/s, INT4 MoE layer (T=%d)" % T
+    elif a.workload == "expert":
+        # config 0: ONE routed expert's SwiGLU FFN at batch 1 (blok_expert_ffn: two launches, gate/up with the SiLU*up
+        # epilogue and down).  A step runs 16 experts back to back out of 48 rotated ones (1.19 GB, so an expert's 24.8 MB
+        # were last read 1.17 GB ago); per-expert time = step / 16.  The cold latency of a single call (L2 flushed by a
+        # 512 MB write, one expert, events around it) is measured before the timed loop and reported beside it.
+        NE = 48
+        g = torch.Generator(device=device).manual_seed(20 + rank)
+        ew = synth.expert_weights(NE, 7168, 2048, g, device)
+        xv = synth.activations(1, 7168, device, 0).view(-1).contiguous()
+        ws = torch.empty(lib.load().blok_expert_ffn_workspace_bytes(7168, 2048), dtype=torch.uint8, device=device)
+        one = lambda e: lib.expert_ffn(ew["gate_w"][e], ew["gate_s"][e], ew["up_w"][e], ew["up_s"][e], ew["down_w"][e],
+                                       ew["down_s"][e], xv, workspace=ws)
+
+        def run(i):
+            for k in range(16):
+                one((16 * i + k) % NE)
+        flush = torch.empty(512 << 20, dtype=torch.uint8, device=device)
+        cold = []
+        for r in range(8):
+            flush.fill_(r)
+            c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            c0.record()
+            one(r)
+            c1.record()
+            torch.cuda.synchronize()
+            cold.append(c0.elapsed_time(c1) * 1e3)
+        del flush
+        cold.sort()
+        extra["cold_single_expert_us"] = {"median": cold[len(cold) // 2], "min": cold[0], "samples": len(cold)}
+        extra["experts_per_step"] = 16
+        alg = 16 * 24772608 + 16 * 2 * 7168 * 2
+        unit_tokens = 16 * world
+        workload = ("config 0: single routed expert SwiGLU FFN, batch 1, 16 experts per step out of 48 rotated (1.19 GB)%s"
+                    % ("" if world == 1 else ", replicas x%d" % world))
+        scaling = "weak"
+        metric = "expert FFNs/s, INT4 W4A16 (batch 1)"
+        unit = "experts/s"
     elif a.workload == "gemv":
         # config 0's building block at a size the launch rate does not bound: one INT4 mat-vec y = W x (matvec_i4_slice,
         # src/kimi_exec.cu:688) over 32 experts' gate matrices stacked, [65536, 7168] = 264 MB per call, 3 such matrices
@@ -464,6 +504,7 @@ def other_workload(a, rank, world, device, steps, warmup):
                     (R, os.environ.get("BLOK_I4_GEMV_IMPL", "bf16-operand"), "" if world == 1 else ", replicas x%d" % world))
         scaling = "weak"
         metric = "mat-vecs/s, INT4 [%d x 7168]" % R
+        unit = "mat-vecs/s"
     else:
         ctx = int(a.workload[len("mla"):])
         layer = lib.MlaLayer(synth.mla_weights(device, seed=3), yarn_factor=32.0, max_batch=8, max_ctx=ctx + 8)
@@ -501,11 +542,11 @@ def other_workload(a, rank, world, device, steps, warmup):
         per_step = ms / steps
         achieved = alg / (per_step * 1e-3) / 1e9
         print(json.dumps({
-            "metric": metric, "value": unit_tokens * steps / (ms / 1e3), "unit": "tok/s", "n_gpus": world, "steps": steps,
+            "metric": metric, "value": unit_tokens * steps / (ms / 1e3), "unit": unit, "n_gpus": world, "steps": steps,
             "warmup": warmup, "ms_per_step": per_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": workload, "algorithmic_bytes_per_step_per_gpu": alg,
-                       "l2": "weights and caches rotated over several copies larger than L2"},
+                       "l2": "weights and caches rotated over several copies larger than L2", **extra},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind, "traffic": None},
             **tensor_roofline(flops, per_step),
@@ -528,7 +569,7 @@ def main():
     ap.add_argument("--experts", type=int, default=384,
                     help="routed experts per layer; below 384 the run is a reduced case for profiler captures, "
                          "not the benchmark configuration, and the line says so")
-    ap.add_argument("--workload", default="decode", choices=["decode", "batched64", "batched2048", "mla4096", "mla32768", "model", "model61", "prefill512", "gemv"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "expert", "batched64", "batched2048", "mla4096", "mla32768", "model", "model61", "prefill512", "gemv"],
                     help="decode = config 1 (the default, the headline metric); batched* = config 2 (expert parallel "
                          "when --gpus > 1); mla* = config 3 (attention block, batch 8)")
     a = ap.parse_args()
