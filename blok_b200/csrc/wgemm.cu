@@ -57,6 +57,7 @@ __global__ void __launch_bounds__(kWgThreads) wgemm_kernel(const WgArgs a) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int e = a.tile_expert[tile], p0 = a.tile_start[tile], cnt = a.tile_count[tile];
+  if (a.small_max && cnt <= a.small_max) return;  // a small group: wgemv_small.cu has it
   const int ntiles = (cnt + 7) >> 3;
 
   // the lane's two weight rows
@@ -191,9 +192,18 @@ static int wgemm_forced_impl() {  // read at every launch, so that a test can sw
   return 0;
 }
 
-int launch_wgemm(int mode, const WgArgs &args, int max_tiles, cudaStream_t stream) {
+int launch_wgemm(int mode, const WgArgs &args_in, int max_tiles, cudaStream_t stream) {
   const int forced = wgemm_forced_impl();
   const bool i4 = mode == WG_I4_SWIGLU || mode == WG_I4_PLAIN;
+  WgArgs args = args_in;
+  {
+    // groups of a few tokens first, through the mat-vec-style kernel; the kernel below then skips them
+    const char *sm = getenv("BLOK_WGEMM_SMALL");
+    if (i4 && !(sm && sm[0] == '0') && wgemv_small_supports(mode, args)) {
+      if (int rc = launch_wgemv_small(mode, args, stream)) return rc;
+      args.small_max = kWgSmallTokens;
+    }
+  }
   const bool enough = args.n_rows >= (i4 ? 256 : 512);
   if (forced != 1 && (forced == 2 || enough) && wgemm_tc_supports(mode, args)) return launch_wgemm_tc(mode, args, max_tiles, stream);
   const size_t smem = wgemm_smem_bytes();

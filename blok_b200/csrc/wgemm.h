@@ -8,6 +8,7 @@ namespace blok {
 
 enum { WG_BF16_PLAIN = 0, WG_BF16_SWIGLU = 1, WG_I4_SWIGLU = 2, WG_I4_PLAIN = 3 };
 constexpr int kWgTileTokens = 64;
+constexpr int kWgSmallTokens = 4;  // groups of up to this many tokens take the mat-vec-style kernel (wgemv_small.cu)
 
 struct WgArgs {
   const void *w_a;
@@ -28,6 +29,7 @@ struct WgArgs {
   const int *out_index;
   int identity_tiles = 0;  // the tiles are consecutive 64-row blocks of x (one group: a dense layer over n_rows tokens)
   int n_rows = 0;  // rows of x the launch covers (tokens, or token-expert assignments): picks the kernel
+  int small_max = 0;  // > 0: tiles of at most this many tokens are somebody else's (wgemv_small.cu) and are skipped
 };
 
 // Dispatches to the tcgen05 kernels (wgemm_tc.cu) when they cover the mode and shape and the launch has enough rows
@@ -37,6 +39,12 @@ int launch_wgemm(int mode, const WgArgs &args, int max_tiles, cudaStream_t strea
 
 // Fills the tile arrays with consecutive 64-row tiles of T rows (one group, expert 0): a dense layer.
 int launch_identity_tiles(int T, int *tile_expert, int *tile_start, int *tile_count, int *num_tiles, cudaStream_t stream);
+
+// The INT4 modes for groups of up to kWgSmallTokens tokens: streams the weights like the batch-1 decode kernel and
+// leaves the larger groups alone.  launch_wgemm runs it in front of the kernel that takes the rest
+// (BLOK_WGEMM_SMALL=0 in the environment: every group through the GEMM kernels).
+bool wgemv_small_supports(int mode, const WgArgs &args);
+int launch_wgemv_small(int mode, const WgArgs &args, cudaStream_t stream);
 
 bool wgemm_tc_supports(int mode, const WgArgs &args);
 int launch_wgemm_tc(int mode, const WgArgs &args, int max_tiles, cudaStream_t stream);

@@ -186,6 +186,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) wgemm_tc_kernel(const WgArgs a)
   if (tile >= *a.num_tiles) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int e = a.tile_expert[tile], p0 = a.tile_start[tile], cnt = a.tile_count[tile];
+  if (a.small_max && cnt <= a.small_max) return;  // a small group: wgemv_small.cu has it (nothing is allocated yet)
   const int N = max(16, (cnt + 15) & ~15);  // token columns the MMAs cover
 
   // ---- this thread unpacks weight row r of block blk: threads 0..127 block 0 (gate rows / rows r), 128..255 block 1 ----
