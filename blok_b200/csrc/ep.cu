@@ -601,6 +601,7 @@ extern "C" int blok_moe_ep_forward(blok_moe_ep_t *ep, const blok_bf16_t *x, int 
       r.K = w.hidden; r.R = w.experts; r.out_bf16 = nullptr; r.out_f32 = L->logits;
       r.tile_expert = L->b_ttile_expert; r.tile_start = L->b_ttile_start; r.tile_count = L->b_ttile_count;
       r.num_tiles = L->b_num_ttiles; r.out_index = nullptr; r.n_rows = T; r.identity_tiles = 1;
+      r.splitk_ws = L->b_splitk; r.splitk_bytes = L->b_splitk_bytes;
       if ((rc = launch_wgemm(WG_BF16_PLAIN, r, tt, stream))) return rc;
     } else {
       for (int t0 = 0; t0 < T; t0 += 8)

@@ -127,6 +127,11 @@ int batched_alloc(blok_moe_layer *L) {
   size_t o_ar = take(N * 4);
   size_t o_mid = take(N * (size_t)w.inter * 2), o_y = take(N * (size_t)w.hidden * 2);
   size_t o_smid = take(T * (size_t)std::max(w.shared_inter, 8) * 2), o_sout = take(T * (size_t)w.hidden * 2);
+  // K-split partial sums of the bf16 products over a single tile of tokens (router, shared gate/up, shared down)
+  L->b_splitk_bytes = std::max(wgemm_splitk_bytes(WG_BF16_PLAIN, w.hidden, w.experts),
+                               std::max(wgemm_splitk_bytes(WG_BF16_SWIGLU, w.hidden, std::max(w.shared_inter, 8)),
+                                        wgemm_splitk_bytes(WG_BF16_PLAIN, std::max(w.shared_inter, 8), w.hidden)));
+  size_t o_sk = take(std::max(L->b_splitk_bytes, (size_t)16));
   BLOK_CUDA(cudaMalloc(&L->bws, off));
   unsigned char *b = static_cast<unsigned char *>(L->bws);
   L->b_counts = (int *)(b + o_counts); L->b_offsets = (int *)(b + o_offsets);
@@ -138,6 +143,7 @@ int batched_alloc(blok_moe_layer *L) {
   L->b_assign_row = (int *)(b + o_ar);
   L->b_mid = (uint16_t *)(b + o_mid); L->b_y = (uint16_t *)(b + o_y);
   L->b_smid = (uint16_t *)(b + o_smid); L->b_sout = (uint16_t *)(b + o_sout);
+  L->b_splitk = (float *)(b + o_sk);
   return BLOK_OK;
 }
 
@@ -211,6 +217,7 @@ extern "C" int blok_moe_batched(blok_moe_layer_t *L, const blok_bf16_t *x, int T
   r.K = w.hidden; r.R = w.experts; r.out_bf16 = nullptr; r.out_f32 = L->logits;
   r.tile_expert = L->b_ttile_expert; r.tile_start = L->b_ttile_start; r.tile_count = L->b_ttile_count;
   r.num_tiles = L->b_num_ttiles; r.out_index = nullptr; r.n_rows = T; r.identity_tiles = 1;
+  r.splitk_ws = L->b_splitk; r.splitk_bytes = L->b_splitk_bytes;
   if ((rc = launch_wgemm(WG_BF16_PLAIN, r, tt, stream))) return rc;
   if ((rc = launch_router_topk(L->logits, w.router_bias, T, w.experts, w.topk, w.routed_scale, L->ids, L->wts, L->local_ids,
                                w.expert_base, stream)))
@@ -254,6 +261,7 @@ extern "C" int blok_moe_shared(blok_moe_layer_t *L, const blok_bf16_t *x, int T,
   s.K = w.hidden; s.R = w.shared_inter; s.out_bf16 = L->b_smid; s.out_f32 = nullptr;
   s.tile_expert = L->b_ttile_expert; s.tile_start = L->b_ttile_start; s.tile_count = L->b_ttile_count;
   s.num_tiles = L->b_num_ttiles; s.out_index = nullptr; s.n_rows = T; s.identity_tiles = 1;
+  s.splitk_ws = L->b_splitk; s.splitk_bytes = L->b_splitk_bytes;
   if ((rc = launch_wgemm(WG_BF16_SWIGLU, s, tt, stream))) return rc;
   WgArgs d = s;
   d.w_a = w.shared_down; d.w_b = nullptr; d.x = L->b_smid; d.K = w.shared_inter; d.R = w.hidden; d.out_bf16 = out;

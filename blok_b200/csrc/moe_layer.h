@@ -55,6 +55,8 @@ struct blok_moe_layer {
   uint16_t *b_y = nullptr;       // [N, hidden] assignment order
   uint16_t *b_smid = nullptr;    // [T, shared_inter]
   uint16_t *b_sout = nullptr;    // [T, hidden]
+  float *b_splitk = nullptr;     // K-split partial sums of the bf16 products over one tile of tokens
+  size_t b_splitk_bytes = 0;
   // fused decode kernel scratch
   blok::FusedPlan plan;
   bool use_fused = false;

@@ -14,6 +14,7 @@
 // multiply on packed bf16 pairs) and reused across the tile's token columns.
 #include "common.cuh"
 #include "wgemm.h"
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
 
@@ -76,7 +77,10 @@ __global__ void __launch_bounds__(kWgThreads) wgemm_kernel(const WgArgs a) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
-  for (int c0 = 0; c0 < a.K; c0 += kWgChunk) {
+  // K split over blockIdx.z (bf16 modes over one tile of tokens, see wgemm_splitk_factor): whole 512-column chunks
+  const int kchunks = a.K / kWgChunk, nz = gridDim.z, kz = blockIdx.z;
+  const int c_begin = (int)((long)kz * kchunks / nz) * kWgChunk, c_end = (int)((long)(kz + 1) * kchunks / nz) * kWgChunk;
+  for (int c0 = c_begin; c0 < c_end; c0 += kWgChunk) {
     // INT4: the chunk's weights (4 k-blocks of the lane's two rows) and scales go in flight first; they do not
     // depend on the activations being staged below
     uint4 pwl[kWgChunk / 128], pwh[kWgChunk / 128];
@@ -166,6 +170,13 @@ __global__ void __launch_bounds__(kWgThreads) wgemm_kernel(const WgArgs a) {
     for (int c = 0; c < 2; ++c) {
       const int tok = 8 * nt + 2 * t + c;
       if (tok >= cnt) continue;
+      if (nz > 1) {  // partial sums [split][row of x][gate rows, then up rows | rows]: the reduce kernel finishes them
+        const int cols = kSwiglu ? 2 * a.R : a.R;
+        float *ps = a.splitk_ws + ((size_t)kz * a.n_rows + (p0 + tok)) * cols;
+        ps[row0 + g] = acc[nt][c];
+        ps[(kSwiglu ? a.R : 8) + row0 + g] = acc[nt][2 + c];
+        continue;
+      }
       const size_t p = a.out_index ? (size_t)a.out_index[p0 + tok] : (size_t)(p0 + tok);
       if (kSwiglu) {
         float gv = round_bf16(acc[nt][c]), uv = round_bf16(acc[nt][2 + c]);
@@ -180,6 +191,42 @@ __global__ void __launch_bounds__(kWgThreads) wgemm_kernel(const WgArgs a) {
       }
     }
   }
+}
+
+// Adds the K-split partial sums in split order and applies the epilogue of wgemm_kernel.  grid = (ceil(R / 256), n_rows).
+template <bool SWIGLU>
+__global__ void wgemm_splitk_reduce_kernel(const WgArgs a, int nz) {
+  const int p = blockIdx.y, row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= a.R) return;
+  const int cols = SWIGLU ? 2 * a.R : a.R;
+  const float *ps = a.splitk_ws + (size_t)p * cols + row;
+  const size_t stride = (size_t)a.n_rows * cols;
+  float v = 0.f, u = 0.f;
+  for (int z = 0; z < nz; ++z) {
+    v += ps[z * stride];
+    if (SWIGLU) u += ps[z * stride + a.R];
+  }
+  const size_t o = (a.out_index ? (size_t)a.out_index[p] : (size_t)p) * a.R + row;
+  if (SWIGLU) {
+    const float gv = round_bf16(v), uv = round_bf16(u);
+    a.out_bf16[o] = f32_to_bf16_bits(round_bf16(round_bf16(gv / (1.0f + expf(-gv))) * uv));
+  } else if (a.out_f32) {
+    a.out_f32[o] = v;
+  } else {
+    a.out_bf16[o] = f32_to_bf16_bits(v);
+  }
+}
+
+int wgemm_splitk_factor(int mode, int K, int R) {
+  if (mode != WG_BF16_PLAIN && mode != WG_BF16_SWIGLU) return 1;
+  const int rows_per_cta = mode == WG_BF16_SWIGLU ? 8 * kWgWarps : 16 * kWgWarps;
+  if (R % rows_per_cta || K % kWgChunk) return 1;
+  const int ctas = R / rows_per_cta, chunks = K / kWgChunk;
+  return std::max(1, std::min(chunks, 2 * sm_count() / ctas));
+}
+size_t wgemm_splitk_bytes(int mode, int K, int R) {
+  const int nz = wgemm_splitk_factor(mode, K, R);
+  return nz > 1 ? (size_t)nz * kWgTokens * (mode == WG_BF16_SWIGLU ? 2 * R : R) * sizeof(float) : 0;
 }
 
 size_t wgemm_smem_bytes() { return (size_t)kWgTokens * kWgTokPitch; }
@@ -212,6 +259,8 @@ int launch_wgemm(int mode, const WgArgs &args_in, int max_tiles, cudaStream_t st
   BLOK_REQUIRE(args.R % rows_per_cta == 0 && args.K % kWgChunk == 0, BLOK_ERR_SHAPE,
                "wgemm: rows %d must be a multiple of %d and columns %d of %d", args.R, rows_per_cta, args.K, kWgChunk);
   dim3 grid(args.R / rows_per_cta, max_tiles);
+  const int nz = !i4 && args.n_rows <= kWgTokens && max_tiles == 1 && args.splitk_ws ? wgemm_splitk_factor(mode, args.K, args.R) : 1;
+  if (nz > 1 && args.splitk_bytes >= wgemm_splitk_bytes(mode, args.K, args.R)) grid.z = nz;
 #define BLOK_WG_LAUNCH(M)                                                                                         \
   {                                                                                                                \
     BLOK_CUDA(cudaFuncSetAttribute(wgemm_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));      \
@@ -224,7 +273,14 @@ int launch_wgemm(int mode, const WgArgs &args_in, int max_tiles, cudaStream_t st
     default: BLOK_WG_LAUNCH(WG_I4_PLAIN) break;
   }
 #undef BLOK_WG_LAUNCH
-  return launch_status("wgemm_kernel");
+  if (int rc = launch_status("wgemm_kernel")) return rc;
+  if (grid.z > 1) {
+    const dim3 rg((args.R + 255) / 256, args.n_rows);
+    if (swiglu) wgemm_splitk_reduce_kernel<true><<<rg, 256, 0, stream>>>(args, (int)grid.z);
+    else wgemm_splitk_reduce_kernel<false><<<rg, 256, 0, stream>>>(args, (int)grid.z);
+    return launch_status("wgemm_splitk_reduce_kernel");
+  }
+  return BLOK_OK;
 }
 
 }  // namespace blok

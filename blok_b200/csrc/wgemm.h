@@ -30,12 +30,23 @@ struct WgArgs {
   int identity_tiles = 0;  // the tiles are consecutive 64-row blocks of x (one group: a dense layer over n_rows tokens)
   int n_rows = 0;  // rows of x the launch covers (tokens, or token-expert assignments): picks the kernel
   int small_max = 0;  // > 0: tiles of at most this many tokens are somebody else's (wgemv_small.cu) and are skipped
+  // bf16 modes over at most one tile of tokens (n_rows <= 64): scratch for the K-split partial sums, see
+  // wgemm_splitk_bytes; NULL: no split
+  float *splitk_ws = nullptr;
+  size_t splitk_bytes = 0;
 };
 
 // Dispatches to the tcgen05 kernels (wgemm_tc.cu) when they cover the mode and shape and the launch has enough rows
 // of x for the tensor cores to matter (INT4: 256 assignments, bf16: 512 tokens), else to the mma.sync kernel,
 // which streams the weights better at small counts.  BLOK_WGEMM_IMPL=mma / =tc in the environment forces one.
 int launch_wgemm(int mode, const WgArgs &args, int max_tiles, cudaStream_t stream);
+
+// A bf16 product over a single tile of tokens has R / 128 (plain) or R / 64 (SwiGLU) CTAs, far fewer than the GPU has
+// SMs (3 for a 384-expert router): the mma.sync kernel then splits K over blockIdx.z, writes fp32 partial sums to
+// args.splitk_ws and a second kernel adds them in split order and applies the epilogue.  The factor depends on the mode,
+// K and R only, never on the token count, so a token's result does not depend on what shares its tile.
+int wgemm_splitk_factor(int mode, int K, int R);
+size_t wgemm_splitk_bytes(int mode, int K, int R);
 
 // Fills the tile arrays with consecutive 64-row tiles of T rows (one group, expert 0): a dense layer.
 int launch_identity_tiles(int T, int *tile_expert, int *tile_start, int *tile_count, int *num_tiles, cudaStream_t stream);
