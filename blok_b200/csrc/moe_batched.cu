@@ -24,24 +24,47 @@ __global__ void mb_count_kernel(const int *__restrict__ expert_local, int N, int
 }
 
 // One block: exclusive scan of the counts and the tile table (tiles of 64 sorted positions of one expert).
-__global__ void mb_plan_kernel(const int *__restrict__ counts, int n_local, int *__restrict__ offsets,
-                               int *__restrict__ tile_expert, int *__restrict__ tile_start, int *__restrict__ tile_count,
-                               int *__restrict__ num_tiles, int max_tiles) {
-  if (threadIdx.x != 0) return;
-  int off = 0, nt = 0;
-  for (int e = 0; e < n_local; ++e) {
-    offsets[e] = off;
-    const int c = counts[e];
-    for (int s = 0; s < c && nt < max_tiles; s += kWgTileTokens) {
-      tile_expert[nt] = e;
-      tile_start[nt] = off + s;
-      tile_count[nt] = min(kWgTileTokens, c - s);
-      ++nt;
+__global__ void __launch_bounds__(1024) mb_plan_kernel(const int *__restrict__ counts, int n_local, int *__restrict__ offsets,
+                                                       int *__restrict__ tile_expert, int *__restrict__ tile_start,
+                                                       int *__restrict__ tile_count, int *__restrict__ num_tiles, int max_tiles) {
+  // one thread per expert (strided if there are more experts than threads); exclusive scans of the counts and of the
+  // tiles per expert through shared memory: offsets and tiles come out in expert order, as a serial walk gives them
+  __shared__ int s_off[1024], s_tiles[1024];
+  __shared__ int s_base_off, s_base_tiles;
+  const int tid = threadIdx.x, nth = blockDim.x;
+  if (tid == 0) s_base_off = 0, s_base_tiles = 0;
+  __syncthreads();
+  for (int e0 = 0; e0 < n_local; e0 += nth) {
+    const int e = e0 + tid;
+    const int c = e < n_local ? counts[e] : 0;
+    const int nt = (c + kWgTileTokens - 1) / kWgTileTokens;
+    s_off[tid] = c;
+    s_tiles[tid] = nt;
+    __syncthreads();
+    for (int d = 1; d < nth; d <<= 1) {  // inclusive scan (Hillis-Steele)
+      const int a = tid >= d ? s_off[tid - d] : 0, t2 = tid >= d ? s_tiles[tid - d] : 0;
+      __syncthreads();
+      s_off[tid] += a;
+      s_tiles[tid] += t2;
+      __syncthreads();
     }
-    off += c;
+    const int off = s_base_off + s_off[tid] - c, first = s_base_tiles + s_tiles[tid] - nt;
+    if (e < n_local) {
+      offsets[e] = off;
+      for (int k = 0; k < nt && first + k < max_tiles; ++k) {
+        tile_expert[first + k] = e;
+        tile_start[first + k] = off + k * kWgTileTokens;
+        tile_count[first + k] = min(kWgTileTokens, c - k * kWgTileTokens);
+      }
+    }
+    __syncthreads();
+    if (tid == nth - 1) s_base_off += s_off[tid], s_base_tiles += s_tiles[tid];
+    __syncthreads();
   }
-  offsets[n_local] = off;
-  *num_tiles = nt;
+  if (tid == 0) {
+    offsets[n_local] = s_base_off;
+    *num_tiles = min(s_base_tiles, max_tiles);
+  }
 }
 
 // Identity tiles over T rows (a single group), for the shared expert and the router logits.
@@ -156,7 +179,7 @@ int grouped_experts(blok_moe_layer *L, const uint16_t *x, const int *x_index, co
   mb_count_kernel<<<(N + 255) / 256, 256, 0, stream>>>(expert_local, N, nl, L->b_counts);
   int rc = launch_status("mb_count_kernel");
   if (rc) return rc;
-  mb_plan_kernel<<<1, 32, 0, stream>>>(L->b_counts, nl, L->b_offsets, L->b_tile_expert, L->b_tile_start, L->b_tile_count,
+  mb_plan_kernel<<<1, 512, 0, stream>>>(L->b_counts, nl, L->b_offsets, L->b_tile_expert, L->b_tile_start, L->b_tile_count,
                                        L->b_num_tiles, L->b_max_tiles);
   if ((rc = launch_status("mb_plan_kernel"))) return rc;
   mb_scatter_kernel<<<(nl * 32 + 255) / 256, 256, 0, stream>>>(expert_local, x_index, N, nl, L->b_offsets,
