@@ -122,10 +122,22 @@ template <bool STAGE>
 __global__ void __launch_bounds__(128) bf16_gemv16_splitk_kernel(const uint16_t *__restrict__ w, const uint16_t *__restrict__ x,
                                                                  uint16_t *__restrict__ y_bf16, float *__restrict__ y_f32,
                                                                  int rows, int cols, int T, int ksteps_per_split,
-                                                                 float *__restrict__ part, unsigned *__restrict__ tickets) {
+                                                                 float *__restrict__ part, unsigned *__restrict__ tickets,
+                                                                 const uint16_t *__restrict__ w2, uint16_t *__restrict__ y2_bf16,
+                                                                 int rows2) {
   extern __shared__ __align__(16) unsigned char smem[];
   __shared__ float partial[4][16][8];
   __shared__ unsigned s_ticket;
+  // w2 != NULL: a second matrix over the same activations in the same launch (q_a and kv_a of the attention block);
+  // its row blocks follow the first matrix's in blockIdx.x
+  int rbx = blockIdx.x;
+  if (w2 && rbx >= rows / 16) {
+    rbx -= rows / 16;
+    w = w2;
+    y_bf16 = y2_bf16;
+    y_f32 = nullptr;
+    rows = rows2;
+  }
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int ksteps = cols / 32;
@@ -142,7 +154,7 @@ __global__ void __launch_bounds__(128) bf16_gemv16_splitk_kernel(const uint16_t 
     __syncthreads();
   }
   const size_t wrow = cols / 8;
-  const uint4 *w_lo = reinterpret_cast<const uint4 *>(w) + (size_t)(blockIdx.x * 16 + g) * wrow + (size_t)kbeg * 4;
+  const uint4 *w_lo = reinterpret_cast<const uint4 *>(w) + (size_t)(rbx * 16 + g) * wrow + (size_t)kbeg * 4;
   const uint4 *w_hi = w_lo + 8 * wrow;
   const int tok = g < T ? g : T - 1;
   const uint4 *xrow = STAGE ? reinterpret_cast<const uint4 *>(smem + tok * row_bytes) + t
@@ -173,7 +185,7 @@ __global__ void __launch_bounds__(128) bf16_gemv16_splitk_kernel(const uint16_t 
     if (tid == 0) tickets[blockIdx.x] = 0;
   }
   if (tk < T) {
-    const size_t o = (size_t)tk * rows + blockIdx.x * 16 + r;
+    const size_t o = (size_t)tk * rows + rbx * 16 + r;
     if (y_f32) y_f32[o] = v;
     else y_bf16[o] = f32_to_bf16_bits(v);
   }
@@ -311,14 +323,46 @@ int launch_bf16_gemv_splitk(const uint16_t *w, const uint16_t *x, uint16_t *y_bf
   unsigned *tickets = static_cast<unsigned *>(ws);
   float *part = reinterpret_cast<float *>(static_cast<unsigned char *>(ws) + (ws_bytes - ((size_t)4 * sm_count() + rb) * 128 * 4) / 256 * 256);
   if (T > 2) {  // activations through the L1, no shared memory
-    bf16_gemv16_splitk_kernel<false><<<dim3(rb, ksplit), 128, 0, stream>>>(w, x, y_bf16, y_f32, rows, cols, T, per, part, tickets);
+    bf16_gemv16_splitk_kernel<false><<<dim3(rb, ksplit), 128, 0, stream>>>(w, x, y_bf16, y_f32, rows, cols, T, per, part, tickets, nullptr,
+                                                                           nullptr, 0);
     return launch_status("bf16_gemv16_splitk_kernel<l1>");
   }
   const size_t smem = bf16_x_row_bytes(per * 32) * T;
   if (smem > 48 * 1024)
     BLOK_CUDA(cudaFuncSetAttribute(bf16_gemv16_splitk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  bf16_gemv16_splitk_kernel<true><<<dim3(rb, ksplit), 128, smem, stream>>>(w, x, y_bf16, y_f32, rows, cols, T, per, part, tickets);
+  bf16_gemv16_splitk_kernel<true><<<dim3(rb, ksplit), 128, smem, stream>>>(w, x, y_bf16, y_f32, rows, cols, T, per, part, tickets, nullptr,
+                                                                           nullptr, 0);
   return launch_status("bf16_gemv16_splitk_kernel");
+}
+
+// Two matrices over the same activations in ONE launch (y1 = W1 x, y2 = W2 x, both bf16): the row blocks of the second
+// follow those of the first in the grid.  `ws` as for launch_bf16_gemv_splitk with rows = rows1 + rows2.  Falls back to
+// two launches where the single one does not apply.
+int launch_bf16_gemv_splitk_pair(const uint16_t *w1, int rows1, uint16_t *y1, const uint16_t *w2, int rows2, uint16_t *y2,
+                                 const uint16_t *x, int cols, int T, void *ws, size_t ws_bytes, cudaStream_t stream) {
+  const int rb = (rows1 + rows2) / 16, ksteps = cols / 32;
+  int ksplit = rb > 0 ? (4 * sm_count() + rb - 1) / rb : 1;
+  ksplit = std::max(1, std::min(ksplit, std::min(32, ksteps / 8)));
+  const bool ok = rows1 % 16 == 0 && rows2 % 16 == 0 && cols % 32 == 0 && (reinterpret_cast<uintptr_t>(w1) & 15) == 0 &&
+                  (reinterpret_cast<uintptr_t>(w2) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && T >= 1 && T <= 8 && ws &&
+                  ws_bytes >= bf16_gemv_splitk_workspace_bytes(rows1 + rows2);
+  if (!ok) {
+    if (int rc = launch_bf16_gemv_splitk(w1, x, y1, nullptr, rows1, cols, T, ws, ws_bytes, stream)) return rc;
+    return launch_bf16_gemv_splitk(w2, x, y2, nullptr, rows2, cols, T, ws, ws_bytes, stream);
+  }
+  const int per = (ksteps + ksplit - 1) / ksplit;
+  ksplit = (ksteps + per - 1) / per;
+  unsigned *tickets = static_cast<unsigned *>(ws);
+  float *part = reinterpret_cast<float *>(static_cast<unsigned char *>(ws) + (ws_bytes - ((size_t)4 * sm_count() + rb) * 128 * 4) / 256 * 256);
+  if (T > 2) {
+    bf16_gemv16_splitk_kernel<false><<<dim3(rb, ksplit), 128, 0, stream>>>(w1, x, y1, nullptr, rows1, cols, T, per, part, tickets, w2, y2, rows2);
+    return launch_status("bf16_gemv16_splitk_kernel<l1, pair>");
+  }
+  const size_t smem = bf16_x_row_bytes(per * 32) * T;
+  if (smem > 48 * 1024)
+    BLOK_CUDA(cudaFuncSetAttribute(bf16_gemv16_splitk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  bf16_gemv16_splitk_kernel<true><<<dim3(rb, ksplit), 128, smem, stream>>>(w1, x, y1, nullptr, rows1, cols, T, per, part, tickets, w2, y2, rows2);
+  return launch_status("bf16_gemv16_splitk_kernel<pair>");
 }
 
 

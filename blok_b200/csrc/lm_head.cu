@@ -16,9 +16,33 @@ __global__ void argmax_bf16_kernel(const uint16_t *__restrict__ logits, int voca
   const uint16_t *row = logits + (size_t)blockIdx.x * vocab;
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+  // eight logits per 16-byte load, four loads in flight per thread; a thread meets its indices in ascending order, and a
+  // strict '>' keeps the lowest index (:482)
+  const bool vec = vocab % 8 == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0;
+  const int units = vec ? vocab / 8 : 0;
+  const uint4 *row4 = reinterpret_cast<const uint4 *>(row);
+  for (int u0 = threadIdx.x; u0 < units; u0 += 4 * blockDim.x) {
+    uint4 q[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int u = u0 + k * blockDim.x;
+      q[k] = u < units ? row4[u] : make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);  // -inf
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int i0 = (u0 + k * blockDim.x) * 8;
+      const uint32_t w[4] = {q[k].x, q[k].y, q[k].z, q[k].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lo = bf16lo(w[j]), hi = bf16hi(w[j]);
+        if (lo > best) best = lo, bi = i0 + 2 * j;
+        if (hi > best) best = hi, bi = i0 + 2 * j + 1;
+      }
+    }
+  }
+  for (int i = units * 8 + threadIdx.x; i < vocab; i += blockDim.x) {
     float v = bf16_bits_to_f32(row[i]);
-    if (v > best) best = v, bi = i;  // ascending scan with strict '>' keeps the lowest index (:482)
+    if (v > best) best = v, bi = i;
   }
 #pragma unroll
   for (int o = 16; o; o >>= 1) {

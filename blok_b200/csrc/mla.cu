@@ -26,6 +26,8 @@ namespace blok {
 int launch_bf16_gemv(const uint16_t *w, const uint16_t *x, uint16_t *y_bf16, float *y_f32, int rows, int cols, int T,
                      cudaStream_t stream);
 size_t bf16_gemv_splitk_workspace_bytes(int rows);
+int launch_bf16_gemv_splitk_pair(const uint16_t *w1, int rows1, uint16_t *y1, const uint16_t *w2, int rows2, uint16_t *y2,
+                                 const uint16_t *x, int cols, int T, void *ws, size_t ws_bytes, cudaStream_t stream);
 int launch_bf16_gemv_splitk(const uint16_t *w, const uint16_t *x, uint16_t *y_bf16, float *y_f32, int rows, int cols, int T,
                             void *ws, size_t ws_bytes, cudaStream_t stream);
 
@@ -565,12 +567,20 @@ static int decode_body(blok_mla_layer *L, const uint16_t *n, const CacheRef &c, 
   const bool gemm = B >= 16;  // enough entries for the GEMM form of the projections to pay
   if (gemm && (rc = launch_identity_tiles(B, L->tiles, L->tiles + L->n_tiles, L->tiles + 2 * L->n_tiles, L->tiles + 3 * L->n_tiles, stream)))
     return rc;
-  // q_a -> RMSNorm -> q_b   (:813-815)
-  if ((rc = project(L, w.q_a, n, L->qa, w.q_rank, w.hidden, B, gemm, stream))) return rc;
+  // q_a -> RMSNorm -> q_b   (:813-815); kv_a (:816) reads the same activations as q_a and shares its launch where the
+  // mat-vec kernel serves both (up to 8 entries per launch)
+  if (!gemm) {
+    for (int b0 = 0; b0 < B; b0 += 8)
+      if ((rc = launch_bf16_gemv_splitk_pair(w.q_a, w.q_rank, L->qa + (size_t)b0 * w.q_rank, w.kv_a, lat_w, L->kva + (size_t)b0 * lat_w,
+                                             n + (size_t)b0 * w.hidden, w.hidden, std::min(8, B - b0), L->sk_ws, L->sk_bytes, stream)))
+        return rc;
+  } else {
+    if ((rc = project(L, w.q_a, n, L->qa, w.q_rank, w.hidden, B, gemm, stream))) return rc;
+    if ((rc = project(L, w.kv_a, n, L->kva, lat_w, w.hidden, B, gemm, stream))) return rc;
+  }
   if ((rc = blok_rmsnorm(L->qa, w.q_a_ln, L->qa, B, w.q_rank, w.rms_eps, stream_))) return rc;
   if ((rc = project(L, w.q_b, L->qa, L->q, w.heads * qk_head, w.q_rank, B, gemm, stream))) return rc;
-  // kv_a; norm of c_kv, RoPE of k_pe and of q's rope part, cache append   (:816-824)
-  if ((rc = project(L, w.kv_a, n, L->kva, lat_w, w.hidden, B, gemm, stream))) return rc;
+  // norm of c_kv, RoPE of k_pe and of q's rope part, cache append   (:816-824)
   mla_prep_kernel<<<dim3(1 + (w.heads * (w.qk_rope / 2) + 255) / 256, B), 256, 0, stream>>>(
       L->kva, w.kv_a_ln, L->q, L->inv_freq, ctx_len, c.base, c.seq_stride, L->q_full, L->seq, w.heads, w.qk_nope, w.qk_rope,
       w.kv_rank, w.rms_eps, c.block_table, c.slot_of, c.table_stride, c.page_rows, c.ctx_cap, L->err);
