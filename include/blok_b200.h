@@ -87,7 +87,7 @@ size_t blok_expert_ffn_workspace_bytes(int hidden, int inter);
 /* Replaces the per-slot body of the routed-expert loop, src/kimi_exec.cu:853-869
  * (gate and up GEMV, silu_mul_k :253, down GEMV).  x bf16 [hidden], y bf16 [hidden].
  * gate/up packed [inter, hidden/8] + scale [inter, hidden/32]; down packed
- * [hidden, inter/8] + scale [hidden, inter/32].  hidden % 128 == 0, inter % 128 == 0. */
+ * [hidden, inter/8] + scale [hidden, inter/32].  hidden % 256 == 0, inter % 256 == 0. */
 int blok_expert_ffn(const uint32_t *gate_w, const blok_bf16_t *gate_s, const uint32_t *up_w, const blok_bf16_t *up_s,
                     const uint32_t *down_w, const blok_bf16_t *down_s, const blok_bf16_t *x, blok_bf16_t *y,
                     int hidden, int inter, void *workspace, size_t workspace_bytes, blok_stream_t stream);
@@ -105,7 +105,12 @@ int blok_expert_ffn(const uint32_t *gate_w, const blok_bf16_t *gate_s, const uin
  *    first call before any stream capture on that device.
  *  - All calls on a device share the one array: two calls whose kernels can overlap
  *    on the GPU (different streams, no dependency between them) race on it.  Calls
- *    on one stream are safe; nothing needs clearing between calls. */
+ *    on one stream are safe; nothing needs clearing between calls.
+ *  - The looked-up address is kept per device for the life of the process.  After
+ *    cudaDeviceReset (or any other destruction and re-creation of the device's
+ *    primary context) that address is stale: a process that resets a device must not
+ *    call this entry point on it afterwards (blok_expert_ffn with a caller workspace
+ *    has no such state). */
 #define BLOK_STATIC_MAX_INTER 8192
 int blok_expert_ffn_static_max_inter(void);
 int blok_expert_ffn_static(const uint32_t *gate_w, const blok_bf16_t *gate_s, const uint32_t *up_w,
