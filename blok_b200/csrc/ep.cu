@@ -112,11 +112,19 @@ static int nccl_fail(ncclResult_t r, const char *what) {
 
 }  // namespace blok
 
+namespace blok {
+struct SymBuf;
+}
 struct blok_comm {
   ncclComm_t nccl = nullptr;
   int rank = 0, world = 1, device = 0;
   cudaStream_t stream = nullptr;  // set-up collectives
   void *scratch = nullptr;        // world * 128 bytes on the device, for the all-gathers of the set-up
+  // the library's own all-reduce for small vectors (the sharded model's one per MoE layer): every rank's receive slots
+  // and flags, mapped by every peer
+  blok::SymBuf *ar = nullptr;
+  unsigned char **ar_peers = nullptr;  // device array: this process's address of every rank's region
+  unsigned *ar_state = nullptr;        // device: [0] calls so far, [1] CTAs of the push that are done, [2] error
 };
 
 namespace blok {
@@ -174,6 +182,71 @@ static void sym_free(SymBuf *b) {
   b->opened.clear();
   if (b->local) cudaFree(b->local);
   b->local = nullptr;
+}
+
+// ---- the library's own all-reduce over peer memory ---------------------------------------------------------------------
+// One-shot: every rank stores its vector into its slot of EVERY rank's region (16-byte peer stores over NVLink), then a
+// flag that carries the call number; every rank then adds the slots in rank order, so all ranks hold the same bits.
+// Two parities of slots: a rank can be one call ahead of a peer that still reads the previous call's slots, never two
+// (its own reduce of call n + 1 needs that peer's flag of call n + 1, which the peer stores after its reduce of call n).
+// The call number lives on the device, so that a CUDA graph replays the same two launches for every call.
+constexpr long kArMaxFloats = 256 * 1024;                 // 1 MB per slot
+constexpr size_t kArSlotBytes = (size_t)kArMaxFloats * 4;
+constexpr unsigned kArSpinLimit = 1u << 22;
+
+__global__ void __launch_bounds__(256) ar_push_kernel(const float4 *__restrict__ src, long n4, unsigned char *const *__restrict__ peers,
+                                                      int world, int rank, unsigned *state) {
+  const unsigned call = state[0] + 1u;  // stored back by the last CTA to finish, after every CTA has read it
+  const size_t slot = ((size_t)(call & 1u) * world + rank) * kArSlotBytes;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long)gridDim.x * blockDim.x) {
+    const float4 v = src[i];
+    for (int d = 0; d < world; ++d) reinterpret_cast<float4 *>(peers[d] + slot)[i] = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned done = atomicAdd(&state[1], 1u);
+    if (done == gridDim.x - 1) {  // every CTA's stores were fenced before its count
+      state[1] = 0;
+      __threadfence_system();
+      for (int d = 0; d < world; ++d) {
+        unsigned *flag = reinterpret_cast<unsigned *>(peers[d] + 2 * (size_t)world * kArSlotBytes) + (call & 1u) * world + rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(call) : "memory");
+      }
+      state[0] = call;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) ar_reduce_kernel(float4 *__restrict__ dst, long n4, const unsigned char *__restrict__ local, int world,
+                                                        unsigned *state) {
+  const unsigned call = state[0];  // this rank's push of the call has finished (stream order)
+  const size_t base = (size_t)(call & 1u) * world * kArSlotBytes;
+  if ((int)threadIdx.x < world) {
+    const unsigned *flag = reinterpret_cast<const unsigned *>(local + 2 * (size_t)world * kArSlotBytes) + (call & 1u) * world + threadIdx.x;
+    unsigned it = 0, seen;
+    for (;;) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+      if (seen == call) break;
+      if (++it > kArSpinLimit) {  // a peer never signalled: record it and add what is there
+        atomicExch(&state[2], 1u + threadIdx.x);
+        break;
+      }
+      __nanosleep(100);
+    }
+  }
+  __syncthreads();
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long)gridDim.x * blockDim.x) {
+    float4 acc = __ldcg(reinterpret_cast<const float4 *>(local + base) + i);  // the peers wrote behind this GPU's L1
+    for (int r = 1; r < world; ++r) {
+      const float4 v = __ldcg(reinterpret_cast<const float4 *>(local + base + (size_t)r * kArSlotBytes) + i);
+      acc.x += v.x;
+      acc.y += v.y;
+      acc.z += v.z;
+      acc.w += v.w;
+    }
+    dst[i] = acc;
+  }
 }
 
 // ---- device side ------------------------------------------------------------------------------------------------------
@@ -441,6 +514,20 @@ extern "C" int blok_comm_create(const void *unique_id, int rank, int world, blok
     memcpy(&id, unique_id, sizeof(id));
     ncclResult_t r = g_nccl.CommInitRank(&c->nccl, world, id, rank);
     if (r != ncclSuccess) return fail(nccl_fail(r, "ncclCommInitRank"));
+    // the regions of the library's own all-reduce: 2 parities x world slots, then 2 x world flags
+    c->ar = new (std::nothrow) SymBuf();
+    if (!c->ar) return fail(BLOK_ERR_ARG);
+    if (int rc = sym_alloc(c, 2 * (size_t)world * kArSlotBytes + 4096, c->ar)) return fail(rc);
+    if ((e = cudaMalloc(&c->ar_peers, (size_t)world * sizeof(void *))) != cudaSuccess) return fail(cuda_fail(e, "cudaMalloc(all-reduce peers)"));
+    if ((e = cudaMemcpy(c->ar_peers, c->ar->peer.data(), (size_t)world * sizeof(void *), cudaMemcpyHostToDevice)) != cudaSuccess)
+      return fail(cuda_fail(e, "cudaMemcpy(all-reduce peers)"));
+    if ((e = cudaMalloc(&c->ar_state, 64)) != cudaSuccess) return fail(cuda_fail(e, "cudaMalloc(all-reduce state)"));
+    if ((e = cudaMemset(c->ar_state, 0, 64)) != cudaSuccess) return fail(cuda_fail(e, "cudaMemset(all-reduce state)"));
+    // nobody stores into a peer's region before every rank has mapped and cleared its own
+    if ((e = cudaMemsetAsync(c->scratch, 0, 128, c->stream)) != cudaSuccess) return fail(cuda_fail(e, "cudaMemsetAsync"));
+    r = g_nccl.AllReduce(c->scratch, c->scratch, 1, ncclFloat32, ncclSum, c->nccl, c->stream);
+    if (r != ncclSuccess) return fail(nccl_fail(r, "ncclAllReduce(set-up barrier)"));
+    if ((e = cudaStreamSynchronize(c->stream)) != cudaSuccess) return fail(cuda_fail(e, "cudaStreamSynchronize"));
   }
   *out = c;
   return BLOK_OK;
@@ -448,6 +535,12 @@ extern "C" int blok_comm_create(const void *unique_id, int rank, int world, blok
 
 extern "C" int blok_comm_destroy(blok_comm_t *c) {
   if (!c) return BLOK_OK;
+  if (c->ar) {
+    sym_free(c->ar);
+    delete c->ar;
+  }
+  if (c->ar_peers) cudaFree(c->ar_peers);
+  if (c->ar_state) cudaFree(c->ar_state);
   if (c->nccl) g_nccl.CommDestroy(c->nccl);
   if (c->scratch) cudaFree(c->scratch);
   if (c->stream) cudaStreamDestroy(c->stream);
@@ -461,6 +554,15 @@ extern "C" int blok_comm_world(const blok_comm_t *c) { return c ? c->world : 0; 
 extern "C" int blok_comm_check(blok_comm_t *c) {
   BLOK_REQUIRE(c, BLOK_ERR_ARG, "blok_comm_check: null pointer");
   if (!c->nccl) return BLOK_OK;
+  if (c->ar_state) {  // the caller has synchronised the streams it used; a peer that never signalled left its rank + 1 here
+    unsigned err = 0;
+    BLOK_CUDA(cudaMemcpy(&err, c->ar_state + 2, sizeof(err), cudaMemcpyDeviceToHost));
+    if (err) {
+      BLOK_CUDA(cudaMemset(c->ar_state + 2, 0, sizeof(err)));
+      set_error("blok_comm_all_reduce_f32: rank %u never signalled its part of an all-reduce", err - 1);
+      return BLOK_ERR_TIMEOUT;
+    }
+  }
   ncclResult_t st = ncclSuccess;
   BLOK_NCCL(g_nccl.CommGetAsyncError(c->nccl, &st));
   if (st != ncclSuccess && st != ncclInProgress) return nccl_fail(st, "blok_comm_check: asynchronous NCCL error");
@@ -470,6 +572,19 @@ extern "C" int blok_comm_check(blok_comm_t *c) {
 extern "C" int blok_comm_all_reduce_f32(blok_comm_t *c, float *buf, long n, blok_stream_t stream) {
   BLOK_REQUIRE(c && (buf || n == 0) && n >= 0, BLOK_ERR_ARG, "blok_comm_all_reduce_f32: bad argument");
   if (c->world == 1 || n == 0) return BLOK_OK;
+  // up to 1 MB: the library's own kernels over peer memory (two launches, no library call; the same bits on every
+  // rank); BLOK_COMM_ALLREDUCE=nccl in the environment, longer or unaligned vectors: ncclAllReduce
+  const char *how = getenv("BLOK_COMM_ALLREDUCE");
+  if (c->ar && n <= kArMaxFloats && n % 4 == 0 && (reinterpret_cast<uintptr_t>(buf) & 15) == 0 && !(how && strcmp(how, "nccl") == 0)) {
+    const long n4 = n / 4;
+    const int ctas = (int)std::min<long>(64, (n4 + 255) / 256);
+    ar_push_kernel<<<ctas, 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<const float4 *>(buf), n4, c->ar_peers, c->world, c->rank,
+                                                         c->ar_state);
+    if (int rc = launch_status("ar_push_kernel")) return rc;
+    ar_reduce_kernel<<<(int)std::min<long>(148, (n4 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<float4 *>(buf), n4, static_cast<const unsigned char *>(c->ar->local), c->world, c->ar_state);
+    return launch_status("ar_reduce_kernel");
+  }
   BLOK_NCCL(g_nccl.AllReduce(buf, buf, (size_t)n, ncclFloat32, ncclSum, c->nccl, (cudaStream_t)stream));
   return BLOK_OK;
 }

@@ -302,7 +302,12 @@ int blok_comm_world(const blok_comm_t *comm);
 /* BLOK_ERR_COMM if NCCL has reported an asynchronous error on the communicator (a peer that died, a deadline). */
 int blok_comm_check(blok_comm_t *comm);
 /* In-place sum over the ranks of n floats on the device, and a broadcast of bytes from `root`: the two collectives
- * the sharded model needs (one all-reduce per MoE layer at batch 1). */
+ * the sharded model needs (one all-reduce per MoE layer).  Up to 262,144 floats (n a multiple of 4, buf 16-byte
+ * aligned) the all-reduce is two launches of the library's own kernels over peer memory: every rank stores its
+ * vector into its slot of every rank's region over NVLink, then a flag with the call number; every rank adds the slots
+ * in rank order, so all ranks end with the same bits.  No library call, no host synchronisation, replayable from a CUDA
+ * graph (the call number lives on the device).  A peer that never signals ends the bounded wait and is reported by
+ * blok_comm_check (BLOK_ERR_TIMEOUT).  Longer vectors, or BLOK_COMM_ALLREDUCE=nccl in the environment: ncclAllReduce. */
 int blok_comm_all_reduce_f32(blok_comm_t *comm, float *buf, long n, blok_stream_t stream);
 int blok_comm_broadcast(blok_comm_t *comm, void *buf, long bytes, int root, blok_stream_t stream);
 

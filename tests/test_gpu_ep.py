@@ -160,3 +160,75 @@ def test_two_rank_sharded_model_generates_the_single_gpu_tokens():
         if p.is_alive():
             p.terminate()
     assert all(v[0] == "ok" for v in res.values()), res
+
+
+def _allreduce_worker(rank, world, port, q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        import torch.distributed as dist
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("gloo", rank=rank, world_size=world)   # only carries the communicator's id
+        from blok_b200 import lib
+        comm = lib.Comm()
+        worst, same = 0.0, True
+        for i, n in enumerate([4, 7168, 3 * 7168, 64 * 7168, 262144, 7168, 7168]):  # the last repeats: both parities of the slots
+            g = torch.Generator(device=dev).manual_seed(100 * i + rank)
+            mine = torch.randn(n, generator=g, device=dev)
+            parts = []
+            for r in range(world):
+                gr = torch.Generator(device=dev).manual_seed(100 * i + r)
+                parts.append(torch.randn(n, generator=gr, device=dev))
+            want = parts[0].clone()
+            for r in range(1, world):
+                want += parts[r]           # rank order, as the library's kernels add
+            got = mine.clone()
+            comm.all_reduce_(got)
+            torch.cuda.synchronize()
+            same = same and torch.equal(got, want)
+            os.environ["BLOK_COMM_ALLREDUCE"] = "nccl"
+            ref = mine.clone()
+            comm.all_reduce_(ref)
+            torch.cuda.synchronize()
+            del os.environ["BLOK_COMM_ALLREDUCE"]
+            worst = max(worst, float((ref - want).abs().max()))
+        comm.check()
+        # a vector longer than a slot takes the NCCL path by itself
+        big = torch.ones(300000, device=dev)
+        comm.all_reduce_(big)
+        torch.cuda.synchronize()
+        ok = same and worst < 1e-5 and bool((big == world).all())
+        dist.barrier()
+        q.put((rank, "ok" if ok else "mismatch same=%r worst=%g" % (same, worst), {}))
+        comm.close()
+        dist.destroy_process_group()
+    except Exception as e:
+        import traceback
+        q.put((rank, "error: %r %s" % (e, traceback.format_exc()[-800:]), {}))
+
+
+def test_two_rank_all_reduce_in_the_librarys_own_kernels():
+    """blok_comm_all_reduce_f32 up to 1 MB runs as two launches over peer memory: every rank must end with the sum taken
+    in rank order, bit for bit (so all ranks hold the same bits), call after call on both parities of the slots; the
+    NCCL path (forced, or chosen by length) must agree within fp32 rounding."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_allreduce_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = {}
+    for _ in range(2):
+        r, status, stats = q.get(timeout=300)
+        res[r] = (status, stats)
+    for p in procs:
+        p.join(timeout=60)
+        if p.is_alive():
+            p.terminate()
+    assert all(v[0] == "ok" for v in res.values()), res

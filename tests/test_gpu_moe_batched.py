@@ -17,12 +17,17 @@ def _oracle_layer(oracle, w, x, ids_needed, topk=8):
                             shared[2], util.t2np_f32(x), topk=topk, mode=0)
 
 
-@pytest.mark.parametrize("impl", ["mma", "tc"])  # the mma.sync kernel and the tcgen05 kernels, whatever the size
+# the mma.sync kernel and the tcgen05 kernels, whatever the size; "auto": the library's own choice, which sends groups of
+# up to four tokens through the mat-vec-style kernel (wgemv_small.cu) and the rest through the kernel the size picks
+@pytest.mark.parametrize("impl", ["mma", "tc", "auto"])
 @pytest.mark.parametrize("T,hidden,inter,experts,shared,seed", [(40, 1024, 512, 128, 512, 31), (1, 1024, 512, 128, 512, 32),
                                                                 (64, 7168, 2048, 384, 2048, 2), (130, 512, 512, 128, 0, 33)])
 def test_moe_batched_vs_oracle(cuda, oracle, monkeypatch, impl, T, hidden, inter, experts, shared, seed):
     from blok_b200 import lib, synth
-    monkeypatch.setenv("BLOK_WGEMM_IMPL", impl)
+    if impl == "auto":
+        monkeypatch.delenv("BLOK_WGEMM_IMPL", raising=False)
+    else:
+        monkeypatch.setenv("BLOK_WGEMM_IMPL", impl)
     w = synth.moe_layer_weights(cuda, seed=seed, hidden=hidden, inter=inter, experts=experts, shared_inter=shared)
     if hidden < 7168:
         for k in ("gate_s", "up_s", "down_s"):
