@@ -217,16 +217,22 @@ __global__ void wgemm_splitk_reduce_kernel(const WgArgs a, int nz) {
   }
 }
 
-int wgemm_splitk_factor(int mode, int K, int R) {
+int wgemm_splitk_factor(int mode, int K, int R, int tiles) {
   if (mode != WG_BF16_PLAIN && mode != WG_BF16_SWIGLU) return 1;
   const int rows_per_cta = mode == WG_BF16_SWIGLU ? 8 * kWgWarps : 16 * kWgWarps;
-  if (R % rows_per_cta || K % kWgChunk) return 1;
-  const int ctas = R / rows_per_cta, chunks = K / kWgChunk;
+  if (R % rows_per_cta || K % kWgChunk || tiles < 1) return 1;
+  const int ctas = R / rows_per_cta * tiles, chunks = K / kWgChunk;
   return std::max(1, std::min(chunks, 2 * sm_count() / ctas));
 }
-size_t wgemm_splitk_bytes(int mode, int K, int R) {
-  const int nz = wgemm_splitk_factor(mode, K, R);
-  return nz > 1 ? (size_t)nz * kWgTokens * (mode == WG_BF16_SWIGLU ? 2 * R : R) * sizeof(float) : 0;
+size_t wgemm_splitk_bytes(int mode, int K, int R, int max_rows) {
+  size_t worst = 0;
+  for (int tiles = 1; tiles <= (max_rows + kWgTokens - 1) / kWgTokens; ++tiles) {
+    const int nz = wgemm_splitk_factor(mode, K, R, tiles);
+    if (nz <= 1) break;  // the factor falls as the tiles grow in number
+    const size_t rows = (size_t)std::min(max_rows, tiles * kWgTokens);
+    worst = std::max(worst, (size_t)nz * rows * (mode == WG_BF16_SWIGLU ? 2 * R : R) * sizeof(float));
+  }
+  return worst;
 }
 
 size_t wgemm_smem_bytes() { return (size_t)kWgTokens * kWgTokPitch; }
@@ -261,8 +267,10 @@ int launch_wgemm(int mode, const WgArgs &args_in, int max_tiles, cudaStream_t st
   BLOK_REQUIRE(args.R % rows_per_cta == 0 && args.K % kWgChunk == 0, BLOK_ERR_SHAPE,
                "wgemm: rows %d must be a multiple of %d and columns %d of %d", args.R, rows_per_cta, args.K, kWgChunk);
   dim3 grid(args.R / rows_per_cta, max_tiles);
-  const int nz = !i4 && args.n_rows <= kWgTokens && max_tiles == 1 && args.splitk_ws ? wgemm_splitk_factor(mode, args.K, args.R) : 1;
-  if (nz > 1 && args.splitk_bytes >= wgemm_splitk_bytes(mode, args.K, args.R)) grid.z = nz;
+  if (!i4 && args.identity_tiles && args.splitk_ws) {
+    const int nz = wgemm_splitk_factor(mode, args.K, args.R, max_tiles);
+    if (nz > 1 && args.splitk_bytes >= (size_t)nz * args.n_rows * (swiglu ? 2 * args.R : args.R) * sizeof(float)) grid.z = nz;
+  }
 #define BLOK_WG_LAUNCH(M)                                                                                         \
   {                                                                                                                \
     BLOK_CUDA(cudaFuncSetAttribute(wgemm_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));      \

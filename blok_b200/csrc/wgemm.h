@@ -30,8 +30,7 @@ struct WgArgs {
   int identity_tiles = 0;  // the tiles are consecutive 64-row blocks of x (one group: a dense layer over n_rows tokens)
   int n_rows = 0;  // rows of x the launch covers (tokens, or token-expert assignments): picks the kernel
   int small_max = 0;  // > 0: tiles of at most this many tokens are somebody else's (wgemv_small.cu) and are skipped
-  // bf16 modes over at most one tile of tokens (n_rows <= 64): scratch for the K-split partial sums, see
-  // wgemm_splitk_bytes; NULL: no split
+  // bf16 modes over identity tiles: scratch for the K-split partial sums, see wgemm_splitk_bytes; NULL: no split
   float *splitk_ws = nullptr;
   size_t splitk_bytes = 0;
 };
@@ -41,12 +40,13 @@ struct WgArgs {
 // which streams the weights better at small counts.  BLOK_WGEMM_IMPL=mma / =tc in the environment forces one.
 int launch_wgemm(int mode, const WgArgs &args, int max_tiles, cudaStream_t stream);
 
-// A bf16 product over a single tile of tokens has R / 128 (plain) or R / 64 (SwiGLU) CTAs, far fewer than the GPU has
-// SMs (3 for a 384-expert router): the mma.sync kernel then splits K over blockIdx.z, writes fp32 partial sums to
-// args.splitk_ws and a second kernel adds them in split order and applies the epilogue.  The factor depends on the mode,
-// K and R only, never on the token count, so a token's result does not depend on what shares its tile.
-int wgemm_splitk_factor(int mode, int K, int R);
-size_t wgemm_splitk_bytes(int mode, int K, int R);
+// A bf16 product over few tiles of tokens has (R / 128 or R / 64) x tiles CTAs, far fewer than the GPU has SMs (3 per
+// tile for a 384-expert router): the mma.sync kernel then splits K over blockIdx.z so that about two CTAs per SM run,
+// writes fp32 partial sums to args.splitk_ws and a second kernel adds them in split order and applies the epilogue.
+// The factor depends on the launch's shape (mode, K, R, number of token tiles), so two launches of the same shape give
+// the same bits.  wgemm_splitk_bytes: the scratch that serves every launch of up to max_rows rows.
+int wgemm_splitk_factor(int mode, int K, int R, int tiles);
+size_t wgemm_splitk_bytes(int mode, int K, int R, int max_rows);
 
 // Fills the tile arrays with consecutive 64-row tiles of T rows (one group, expert 0): a dense layer.
 int launch_identity_tiles(int T, int *tile_expert, int *tile_start, int *tile_count, int *num_tiles, cudaStream_t stream);
