@@ -151,7 +151,7 @@ int batched_alloc(blok_moe_layer *L) {
   size_t o_mid = take(N * (size_t)w.inter * 2), o_y = take(N * (size_t)w.hidden * 2);
   size_t o_smid = take(T * (size_t)std::max(w.shared_inter, 8) * 2), o_sout = take(T * (size_t)w.hidden * 2);
   // K-split partial sums of the bf16 products over a single tile of tokens (router, shared gate/up, shared down)
-  const int rows_sk = (int)std::min<size_t>(T, 511);  // from 512 rows on the bf16 products take the tcgen05 kernel
+  const int rows_sk = (int)std::min<size_t>(T, 639);  // from 640 rows on the bf16 products take the tcgen05 kernel
   // (the router's 384 rows never do: its product is split at every token count the handle allows)
   L->b_splitk_bytes = std::max(wgemm_splitk_bytes(WG_BF16_PLAIN, w.hidden, w.experts, (int)T),
                                std::max(wgemm_splitk_bytes(WG_BF16_SWIGLU, w.hidden, std::max(w.shared_inter, 8), rows_sk),

@@ -259,7 +259,9 @@ int launch_wgemm(int mode, const WgArgs &args_in, int max_tiles, cudaStream_t st
       args.small_max = kWgSmallTokens;
     }
   }
-  const bool enough = args.n_rows >= (i4 ? 256 : 512);
+  // bf16: the tcgen05 kernel's 256-token tiles leave most SMs idle below about 650 tokens (shared expert: 376 us from
+  // 128 to 1,024 tokens, against 106 / 162 / 297 / 585 us for the K-split mma.sync kernel at 128 / 256 / 512 / 1,024)
+  const bool enough = args.n_rows >= (i4 ? 256 : 640);
   if (forced != 1 && (forced == 2 || enough) && wgemm_tc_supports(mode, args)) return launch_wgemm_tc(mode, args, max_tiles, stream);
   const size_t smem = wgemm_smem_bytes();
   const bool swiglu = mode == WG_BF16_SWIGLU || mode == WG_I4_SWIGLU;

@@ -36,7 +36,7 @@ struct WgArgs {
 };
 
 // Dispatches to the tcgen05 kernels (wgemm_tc.cu) when they cover the mode and shape and the launch has enough rows
-// of x for the tensor cores to matter (INT4: 256 assignments, bf16: 512 tokens), else to the mma.sync kernel,
+// of x for the tensor cores to matter (INT4: 256 assignments, bf16: 640 tokens), else to the mma.sync kernel,
 // which streams the weights better at small counts.  BLOK_WGEMM_IMPL=mma / =tc in the environment forces one.
 int launch_wgemm(int mode, const WgArgs &args, int max_tiles, cudaStream_t stream);
 
