@@ -11,6 +11,7 @@
 #include <algorithm>
 
 #include "bf16_mma.cuh"
+#include "wgemm.h"
 
 namespace blok {
 
@@ -392,24 +393,36 @@ extern "C" int blok_bf16_gemv(const blok_bf16_t *w, const blok_bf16_t *x, blok_b
   return launch_bf16_gemv(w, x, y_bf16, y_f32, rows, cols, T, (cudaStream_t)stream);
 }
 
+// mid [T, ffn] bf16, then (more than 8 rows) the K-split partial sums of the down projection
+static size_t mlp_mid_bytes(int ffn, int T) { return ((size_t)ffn * T * sizeof(uint16_t) + 255) / 256 * 256; }
 extern "C" size_t blok_bf16_mlp_workspace_bytes(int hidden, int ffn, int T) {
-  (void)hidden;
-  return (ffn > 0 && T > 0) ? (size_t)ffn * T * sizeof(uint16_t) : 0;
+  if (ffn <= 0 || T <= 0) return 0;
+  if (T <= 8) return (size_t)ffn * T * sizeof(uint16_t);
+  return mlp_mid_bytes(ffn, T) + std::max(wgemm_splitk_bytes(WG_BF16_SWIGLU, hidden, ffn, T), wgemm_splitk_bytes(WG_BF16_PLAIN, ffn, hidden, T));
 }
 
 extern "C" int blok_bf16_mlp(const blok_bf16_t *gate, const blok_bf16_t *up, const blok_bf16_t *down,
                              const blok_bf16_t *x, blok_bf16_t *y, int hidden, int ffn, int T, void *workspace,
                              size_t workspace_bytes, blok_stream_t stream) {
   BLOK_REQUIRE(gate && up && down && x && y && workspace, BLOK_ERR_ARG, "blok_bf16_mlp: null pointer");
-  BLOK_REQUIRE(hidden > 0 && ffn > 0 && hidden % 32 == 0 && ffn % 32 == 0 && hidden % 16 == 0 && T >= 1 && T <= 8,
-               BLOK_ERR_SHAPE, "blok_bf16_mlp: hidden %d, ffn %d must be multiples of 32 and 1 <= T=%d <= 8", hidden, ffn, T);
-  BLOK_REQUIRE(bf16_x_row_bytes(hidden > ffn ? hidden : ffn) * T <= 200 * 1024, BLOK_ERR_SHAPE,
+  BLOK_REQUIRE(hidden > 0 && ffn > 0 && hidden % 32 == 0 && ffn % 32 == 0 && hidden % 16 == 0 && T >= 1 && T <= kWgStreamTokens,
+               BLOK_ERR_SHAPE, "blok_bf16_mlp: hidden %d, ffn %d must be multiples of 32 and 1 <= T=%d <= %d", hidden, ffn, T,
+               kWgStreamTokens);
+  BLOK_REQUIRE(T <= 8 || (hidden % 256 == 0 && ffn % 256 == 0), BLOK_ERR_SHAPE,
+               "blok_bf16_mlp: more than 8 rows need hidden %d and ffn %d to be multiples of 256", hidden, ffn);
+  BLOK_REQUIRE(T > 8 || bf16_x_row_bytes(hidden > ffn ? hidden : ffn) * T <= 200 * 1024, BLOK_ERR_SHAPE,
                "blok_bf16_mlp: T * max(hidden, ffn) does not fit in shared memory");
   BLOK_REQUIRE(workspace_bytes >= blok_bf16_mlp_workspace_bytes(hidden, ffn, T), BLOK_ERR_WORKSPACE,
                "blok_bf16_mlp: workspace too small");
   BLOK_REQUIRE(aligned16(gate) && aligned16(up) && aligned16(down) && aligned16(x) && aligned16(workspace), BLOK_ERR_ARG,
                "blok_bf16_mlp: pointers must be 16-byte aligned");
   uint16_t *mid = static_cast<uint16_t *>(workspace);
+  if (T > 8) {  // 9..64 rows: each matrix streamed once for all rows (wgemm_stream.cu)
+    float *sk = reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) + mlp_mid_bytes(ffn, T));
+    const size_t sk_bytes = workspace_bytes - mlp_mid_bytes(ffn, T);
+    if (int rc = launch_wgemm_rows(WG_BF16_SWIGLU, gate, up, x, mid, nullptr, ffn, hidden, T, sk, sk_bytes, (cudaStream_t)stream)) return rc;
+    return launch_wgemm_rows(WG_BF16_PLAIN, down, nullptr, mid, y, nullptr, hidden, ffn, T, sk, sk_bytes, (cudaStream_t)stream);
+  }
   int rc = launch_bf16_gateup(gate, up, x, mid, ffn, hidden, T, (cudaStream_t)stream);
   if (rc) return rc;
   return launch_bf16_gemv(down, mid, y, nullptr, hidden, ffn, T, (cudaStream_t)stream);

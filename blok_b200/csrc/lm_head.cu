@@ -3,6 +3,7 @@
 // sample_lm_head (:718-734) and argmax_k (:477-493).  The reference walks 640 tiles
 // with two blocking device-to-host copies each; here the ids never leave the device.
 #include "common.cuh"
+#include "wgemm.h"
 
 namespace blok {
 
@@ -90,12 +91,16 @@ extern "C" size_t blok_lm_head_workspace_bytes(int vocab, int T) {
 extern "C" int blok_lm_head_argmax(const blok_bf16_t *w, const blok_bf16_t *n, int vocab, int hidden, int T,
                                    uint32_t *ids, void *workspace, size_t workspace_bytes, blok_stream_t stream) {
   BLOK_REQUIRE(w && n && ids && workspace, BLOK_ERR_ARG, "blok_lm_head_argmax: null pointer");
-  BLOK_REQUIRE(vocab > 0 && hidden > 0 && hidden % 8 == 0 && T >= 1 && T <= 8, BLOK_ERR_SHAPE,
+  BLOK_REQUIRE(vocab > 0 && hidden > 0 && hidden % 8 == 0 && T >= 1 && T <= kWgStreamTokens, BLOK_ERR_SHAPE,
                "blok_lm_head_argmax: unsupported shape vocab=%d hidden=%d T=%d", vocab, hidden, T);
+  BLOK_REQUIRE(T <= 8 || (vocab % 16 == 0 && hidden % 256 == 0), BLOK_ERR_SHAPE,
+               "blok_lm_head_argmax: more than 8 rows need vocab %% 16 == 0 and hidden %% 256 == 0 (vocab=%d hidden=%d)", vocab, hidden);
   BLOK_REQUIRE(workspace_bytes >= blok_lm_head_workspace_bytes(vocab, T), BLOK_ERR_WORKSPACE,
                "blok_lm_head_argmax: workspace too small");
   uint16_t *logits = static_cast<uint16_t *>(workspace);
-  int rc = launch_bf16_gemv(w, n, logits, nullptr, vocab, hidden, T, (cudaStream_t)stream);
+  // up to 8 rows: the mat-vec kernel; 9..64: one pass of the weight-streaming kernel over the table for all rows
+  int rc = T <= 8 ? launch_bf16_gemv(w, n, logits, nullptr, vocab, hidden, T, (cudaStream_t)stream)
+                  : launch_wgemm_rows(WG_BF16_PLAIN, w, nullptr, n, logits, nullptr, vocab, hidden, T, nullptr, 0, (cudaStream_t)stream);
   if (rc) return rc;
   argmax_bf16_kernel<<<T, 1024, 0, (cudaStream_t)stream>>>(logits, vocab, ids);
   return launch_status("argmax_bf16_kernel");

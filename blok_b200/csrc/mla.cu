@@ -289,6 +289,8 @@ struct blok_mla_layer {
   int n_tiles = 0;
   void *sk_ws = nullptr;       // split-K partial sums and tickets of the projections (zeroed at create)
   size_t sk_bytes = 0;
+  float *wg_ws = nullptr;      // K-split partial sums of the projections over 9..64 entries (wgemm_stream.cu)
+  size_t wg_bytes = 0;
   float *part_o = nullptr;     // [max_splits * max_batch..]
   float *part_ml = nullptr;
 };
@@ -361,6 +363,13 @@ extern "C" int blok_mla_layer_create(const blok_mla_weights *w, int max_batch, i
   size_t o_pml = take((size_t)(L->max_splits + max_batch) * w->heads * 2 * 4);
   L->sk_bytes = bf16_gemv_splitk_workspace_bytes(std::max(std::max(w->q_rank, lat_w), std::max(w->heads * qk_head, w->hidden)));
   size_t o_sk = take(L->sk_bytes);
+  if (max_batch > 8) {
+    const int mb = std::min(max_batch, kWgStreamTokens);
+    L->wg_bytes = std::max(std::max(wgemm_splitk_bytes(WG_BF16_PLAIN, w->hidden, w->q_rank, mb), wgemm_splitk_bytes(WG_BF16_PLAIN, w->hidden, lat_w, mb)),
+                           std::max(wgemm_splitk_bytes(WG_BF16_PLAIN, w->q_rank, w->heads * qk_head, mb),
+                                    wgemm_splitk_bytes(WG_BF16_PLAIN, w->heads * w->v_head, w->hidden, mb)));
+  }
+  size_t o_wg = take(std::max(L->wg_bytes, (size_t)16));
   cudaError_t e = cudaMalloc(&L->ws, off);
   if (e != cudaSuccess) {
     delete L;
@@ -388,6 +397,7 @@ extern "C" int blok_mla_layer_create(const blok_mla_weights *w, int max_batch, i
   L->part_o = reinterpret_cast<float *>(b + o_po);
   L->part_ml = reinterpret_cast<float *>(b + o_pml);
   L->sk_ws = b + o_sk;
+  L->wg_ws = reinterpret_cast<float *>(b + o_wg);
   float freq[128];
   yarn_inv_freq_host(*w, freq);
   e = cudaMemcpy(L->inv_freq, freq, (size_t)(w->qk_rope / 2) * 4, cudaMemcpyHostToDevice);
@@ -531,11 +541,13 @@ extern "C" int blok_mla_attend_paged(blok_mla_layer_t *L, const blok_bf16_t *q, 
   return attend_and_merge(L, q, c, seq_len, B, softmax_scale, o_lat, (cudaStream_t)stream);
 }
 
-// y[b, :] = bf16(W x[b, :]) for B entries.  Up to 15 entries go through the mat-vec kernel 8 at a time; from 16 on, and
-// where the matrix fits its tiling, one pass of the weight-streaming GEMM reads the weights once for all entries
-// (`tiles_ready`: the identity tile table for B entries has been written on this stream).
+// y[b, :] = bf16(W x[b, :]) for B entries.  Up to 8 entries go through the split-K mat-vec kernel; 9 to 64 through the
+// weight-streaming kernel, one pass over the weights for all entries; more, where the matrix fits its tiling, through the
+// GEMM (`tiles_ready`: the identity tile table for B entries has been written on this stream), else 8 at a time.
 static int project(blok_mla_layer *L, const uint16_t *w, const uint16_t *x, uint16_t *y, int rows, int cols, int B, bool tiles_ready,
                    cudaStream_t stream) {
+  if (B > 8 && B <= kWgStreamTokens && rows % 16 == 0 && cols % 256 == 0)
+    return launch_wgemm_rows(WG_BF16_PLAIN, w, nullptr, x, y, nullptr, rows, cols, B, L->wg_ws, L->wg_bytes, stream);
   if (tiles_ready && rows % 128 == 0 && cols % 512 == 0) {
     const int tiles = (B + kWgTileTokens - 1) / kWgTileTokens;
     int *tab = L->tiles;
@@ -564,12 +576,13 @@ static int decode_body(blok_mla_layer *L, const uint16_t *n, const CacheRef &c, 
   const size_t q_row = (size_t)w.heads * qk_head, qf_row = (size_t)w.heads * lat_w, ol_row = (size_t)w.heads * w.kv_rank,
                av_row = (size_t)w.heads * w.v_head;
   int rc;
-  const bool gemm = B >= 16;  // enough entries for the GEMM form of the projections to pay
+  const bool gemm = B > kWgStreamTokens;  // the GEMM form of the projections: needs the identity tile table
+  const bool stream_rows = B > 8 && !gemm;  // 9..64 entries: one pass of the weight-streaming kernel per matrix
   if (gemm && (rc = launch_identity_tiles(B, L->tiles, L->tiles + L->n_tiles, L->tiles + 2 * L->n_tiles, L->tiles + 3 * L->n_tiles, stream)))
     return rc;
   // q_a -> RMSNorm -> q_b   (:813-815); kv_a (:816) reads the same activations as q_a and shares its launch where the
   // mat-vec kernel serves both (up to 8 entries per launch)
-  if (!gemm) {
+  if (!gemm && !stream_rows) {
     for (int b0 = 0; b0 < B; b0 += 8)
       if ((rc = launch_bf16_gemv_splitk_pair(w.q_a, w.q_rank, L->qa + (size_t)b0 * w.q_rank, w.kv_a, lat_w, L->kva + (size_t)b0 * lat_w,
                                              n + (size_t)b0 * w.hidden, w.hidden, std::min(8, B - b0), L->sk_ws, L->sk_bytes, stream)))

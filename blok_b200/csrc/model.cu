@@ -9,6 +9,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "wgemm.h"
 
 namespace blok {
 
@@ -142,6 +143,7 @@ struct blok_model {
   uint32_t *ids = nullptr, *next = nullptr;             // [max_batch]
   void *mlp_ws = nullptr;
   size_t mlp_ws_bytes = 0;
+  int mlp_rows = 8;            // rows of the dense layer per call
   void *head_ws = nullptr;
   size_t head_ws_bytes = 0;
   uint64_t seed = 0, counter = 0;
@@ -305,7 +307,9 @@ int build(blok_model *m) {
   if ((rc = dev_alloc(m, m->rows * 4, &p))) return rc; m->next = static_cast<uint32_t *>(p);
   if ((rc = dev_alloc(m, (size_t)(c.prefill_chunk > 0 ? (c.max_ctx > m->rows ? c.max_ctx : m->rows) : 1) * 4, &p))) return rc;
   m->prompt_ids = static_cast<uint32_t *>(p);
-  m->mlp_ws_bytes = blok_bf16_mlp_workspace_bytes(c.hidden, c.dense_inter > 0 ? c.dense_inter : 32, 8);
+  // the dense layer takes up to 64 rows per call where its sizes fit the weight-streaming kernel, else 8
+  m->mlp_rows = (c.hidden % 256 == 0 && c.dense_inter % 256 == 0 && c.dense_inter > 0) ? std::min((int)m->rows, kWgStreamTokens) : 8;
+  m->mlp_ws_bytes = blok_bf16_mlp_workspace_bytes(c.hidden, c.dense_inter > 0 ? c.dense_inter : 32, std::max(m->mlp_rows, 8));
   if ((rc = dev_alloc(m, m->mlp_ws_bytes, &m->mlp_ws))) return rc;
   m->head_ws_bytes = blok_lm_head_workspace_bytes(c.vocab, c.max_batch);
   if ((rc = dev_alloc(m, m->head_ws_bytes, &m->head_ws))) return rc;
@@ -535,6 +539,7 @@ static int ffn_rows(blok_model_t *m, int l, int T, bool chunk, blok_stream_t str
     const size_t row_bytes = (size_t)(c.hidden > c.dense_inter ? c.hidden : c.dense_inter) * 2 + 64;
     int group = wide ? 8 : 1;
     while (group > 1 && row_bytes * group > 200 * 1024) --group;
+    if (wide && T > 8 && m->mlp_rows > 8) group = m->mlp_rows;  // one pass over the weights for up to 64 rows
     for (int b = 0; b < T && !rc; b += group)
       rc = blok_bf16_mlp(tp<uint16_t>(L.t, "gate_proj"), tp<uint16_t>(L.t, "up_proj"), tp<uint16_t>(L.t, "down_proj"), m->n + b * H,
                          m->tmp + b * H, c.hidden, c.dense_inter, T - b < group ? T - b : group, m->mlp_ws, m->mlp_ws_bytes, stream_);
@@ -582,9 +587,11 @@ static int step_body(blok_model_t *m, int B, blok_stream_t stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   int rc;
   if ((rc = layers_body(m, B, false, stream_))) return rc;
-  for (int b = 0; b < B; b += 8)  // the sampler takes 8 rows per call
-    if ((rc = blok_lm_head_argmax(tp<uint16_t>(m->top, "lm_head"), m->n + (size_t)b * c.hidden, c.vocab, c.hidden, B - b < 8 ? B - b : 8,
-                                  m->next + b, m->head_ws, m->head_ws_bytes, stream_)))
+  // the sampler takes 64 rows per call where the sizes fit the weight-streaming kernel (one pass over the table), else 8
+  const int head_rows = (c.vocab % 16 == 0 && c.hidden % 256 == 0) ? kWgStreamTokens : 8;
+  for (int b = 0; b < B; b += head_rows)
+    if ((rc = blok_lm_head_argmax(tp<uint16_t>(m->top, "lm_head"), m->n + (size_t)b * c.hidden, c.vocab, c.hidden,
+                                  B - b < head_rows ? B - b : head_rows, m->next + b, m->head_ws, m->head_ws_bytes, stream_)))
       return rc;
   if (m->pages) advance_slots_kernel<<<1, 64, 0, stream>>>(m->pos, m->slot_of, B);
   else advance_kernel<<<1, 64, 0, stream>>>(m->pos, B, 1);

@@ -226,6 +226,10 @@ int wgemm_splitk_factor(int mode, int K, int R, int tiles) {
 }
 size_t wgemm_splitk_bytes(int mode, int K, int R, int max_rows) {
   size_t worst = 0;
+  {  // the weight-streaming kernel over up to kWgStreamTokens rows
+    const int nz = wgemm_stream_split(mode, K, R);
+    if (nz > 1) worst = (size_t)nz * std::min(max_rows, kWgStreamTokens) * (mode == WG_BF16_SWIGLU ? 2 * R : R) * sizeof(float);
+  }
   for (int tiles = 1; tiles <= (max_rows + kWgTokens - 1) / kWgTokens; ++tiles) {
     const int nz = wgemm_splitk_factor(mode, K, R, tiles);
     if (nz <= 1) break;  // the factor falls as the tiles grow in number
@@ -259,12 +263,23 @@ int launch_wgemm(int mode, const WgArgs &args_in, int max_tiles, cudaStream_t st
       args.small_max = kWgSmallTokens;
     }
   }
+  const bool swiglu = mode == WG_BF16_SWIGLU || mode == WG_I4_SWIGLU;
+  if (!i4 && forced == 0 && wgemm_stream_supports(mode, args)) {
+    int nz = 1;
+    if (int rc = launch_wgemm_stream(mode, args, &nz, stream)) return rc;
+    if (nz > 1) {
+      const dim3 rg((args.R + 255) / 256, args.n_rows);
+      if (swiglu) wgemm_splitk_reduce_kernel<true><<<rg, 256, 0, stream>>>(args, nz);
+      else wgemm_splitk_reduce_kernel<false><<<rg, 256, 0, stream>>>(args, nz);
+      return launch_status("wgemm_splitk_reduce_kernel");
+    }
+    return BLOK_OK;
+  }
   // bf16: the tcgen05 kernel's 256-token tiles leave most SMs idle below about 650 tokens (shared expert: 376 us from
   // 128 to 1,024 tokens, against 106 / 162 / 297 / 585 us for the K-split mma.sync kernel at 128 / 256 / 512 / 1,024)
   const bool enough = args.n_rows >= (i4 ? 256 : 640);
   if (forced != 1 && (forced == 2 || enough) && wgemm_tc_supports(mode, args)) return launch_wgemm_tc(mode, args, max_tiles, stream);
   const size_t smem = wgemm_smem_bytes();
-  const bool swiglu = mode == WG_BF16_SWIGLU || mode == WG_I4_SWIGLU;
   const int rows_per_cta = swiglu ? 8 * kWgWarps : 16 * kWgWarps;
   BLOK_REQUIRE(args.R % rows_per_cta == 0 && args.K % kWgChunk == 0, BLOK_ERR_SHAPE,
                "wgemm: rows %d must be a multiple of %d and columns %d of %d", args.R, rows_per_cta, args.K, kWgChunk);
@@ -290,6 +305,26 @@ int launch_wgemm(int mode, const WgArgs &args_in, int max_tiles, cudaStream_t st
     const dim3 rg((args.R + 255) / 256, args.n_rows);
     if (swiglu) wgemm_splitk_reduce_kernel<true><<<rg, 256, 0, stream>>>(args, (int)grid.z);
     else wgemm_splitk_reduce_kernel<false><<<rg, 256, 0, stream>>>(args, (int)grid.z);
+    return launch_status("wgemm_splitk_reduce_kernel");
+  }
+  return BLOK_OK;
+}
+
+int launch_wgemm_rows(int mode, const void *w_a, const void *w_b, const uint16_t *x, uint16_t *out_bf16, float *out_f32, int R, int K,
+                      int T, float *splitk_ws, size_t splitk_bytes, cudaStream_t stream) {
+  WgArgs r;
+  r.w_a = w_a; r.w_b = w_b; r.s_a = r.s_b = nullptr; r.expert_stride_rows = 0; r.x = x; r.x_index = nullptr;
+  r.K = K; r.R = R; r.out_bf16 = out_bf16; r.out_f32 = out_f32;
+  r.tile_expert = r.tile_start = r.tile_count = r.num_tiles = nullptr; r.out_index = nullptr;
+  r.identity_tiles = 1; r.n_rows = T; r.splitk_ws = splitk_ws; r.splitk_bytes = splitk_bytes;
+  BLOK_REQUIRE(wgemm_stream_supports(mode, r), BLOK_ERR_SHAPE, "wgemm rows: %d rows x %d columns over %d tokens is outside the streaming kernel",
+               R, K, T);
+  int nz = 1;
+  if (int rc = launch_wgemm_stream(mode, r, &nz, stream)) return rc;
+  if (nz > 1) {
+    const dim3 rg((R + 255) / 256, T);
+    if (mode == WG_BF16_SWIGLU) wgemm_splitk_reduce_kernel<true><<<rg, 256, 0, stream>>>(r, nz);
+    else wgemm_splitk_reduce_kernel<false><<<rg, 256, 0, stream>>>(r, nz);
     return launch_status("wgemm_splitk_reduce_kernel");
   }
   return BLOK_OK;

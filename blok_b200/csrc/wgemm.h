@@ -8,6 +8,7 @@ namespace blok {
 
 enum { WG_BF16_PLAIN = 0, WG_BF16_SWIGLU = 1, WG_I4_SWIGLU = 2, WG_I4_PLAIN = 3 };
 constexpr int kWgTileTokens = 64;
+constexpr int kWgStreamTokens = 64;  // bf16 weights over up to this many rows take the weight-streaming kernel (wgemm_stream.cu)
 constexpr int kWgSmallTokens = 4;  // groups of up to this many tokens take the mat-vec-style kernel (wgemv_small.cu)
 
 struct WgArgs {
@@ -56,6 +57,17 @@ int launch_identity_tiles(int T, int *tile_expert, int *tile_start, int *tile_co
 // (BLOK_WGEMM_SMALL=0 in the environment: every group through the GEMM kernels).
 bool wgemv_small_supports(int mode, const WgArgs &args);
 int launch_wgemv_small(int mode, const WgArgs &args, cudaStream_t stream);
+
+// The bf16 modes over 1..kWgStreamTokens rows of x (identity tiles): every warp streams its 16 weight rows through a
+// cp.async ring, the activations are double buffered (wgemm_stream.cu).  *splits > 1: K was split and the partial sums
+// wait in args.splitk_ws for wgemm_splitk_reduce_kernel (launch_wgemm runs it).  wgemm_stream_split: the split of a shape.
+bool wgemm_stream_supports(int mode, const WgArgs &args);
+int wgemm_stream_split(int mode, int K, int R);
+int launch_wgemm_stream(int mode, const WgArgs &args, int *splits, cudaStream_t stream);
+// One dense product through launch_wgemm without tile tables: out[T, R] = W[R, K] x[T, K] (mode WG_BF16_PLAIN; bf16 or
+// fp32 output) or the SwiGLU front half of (w_a = gate, w_b = up) (mode WG_BF16_SWIGLU), for 1 <= T <= kWgStreamTokens.
+int launch_wgemm_rows(int mode, const void *w_a, const void *w_b, const uint16_t *x, uint16_t *out_bf16, float *out_f32, int R, int K,
+                      int T, float *splitk_ws, size_t splitk_bytes, cudaStream_t stream);
 
 bool wgemm_tc_supports(int mode, const WgArgs &args);
 int launch_wgemm_tc(int mode, const WgArgs &args, int max_tiles, cudaStream_t stream);

@@ -26,16 +26,32 @@ namespace blok {
 
 constexpr int kGsWarps = 16, kGsThreads = kGsWarps * 32;
 constexpr int kGsDepth = 5;                               // ring steps of 1 KB (16 rows x 64 bytes) in flight per warp
-constexpr int kGsChunk = 14;                              // k-blocks whose scales are staged together
-constexpr int kGsScaleRow = 16 * 8 + 8;                   // bytes per row of the scale stage (odd multiple of 8: all banks)
+constexpr int kGsMaxChunk = 16;                           // most k-blocks whose scales are staged together
+constexpr int kGsScaleRow = kGsMaxChunk * 8 + 16;         // bytes per row of the scale stage (36 words: rows 4 banks apart)
 constexpr int kGsWarpBytes = kGsDepth * 1024 + 16 * kGsScaleRow;
 constexpr int kGsMaxGroups = 2048;                        // small groups a launch can hold in its shared-memory list
 
 __device__ __forceinline__ void gs_cp16(uint32_t dst, const void *src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
-__device__ __forceinline__ void gs_cp8(uint32_t dst, const void *src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+__device__ __forceinline__ void gs_cp16_ca(uint32_t dst, const void *src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+// Shared-memory loads by 32-bit address: the streaming loop keeps running addresses, not pointers.
+__device__ __forceinline__ uint4 gs_lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint2 gs_lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ float gs_lds_bf16(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return __uint_as_float(v << 16);
 }
 __device__ __forceinline__ float gs_swiglu(float g, float u) {  // :322 rounds both mat-vec outputs, :255 SiLU and the product
   g = round_bf16(g);
@@ -44,6 +60,132 @@ __device__ __forceinline__ float gs_swiglu(float g, float u) {  // :322 rounds b
 }
 
 size_t wgemv_small_smem_bytes(int K) { return (size_t)kWgSmallTokens * imma_stage_bytes(K) + (size_t)kGsWarps * kGsWarpBytes; }
+
+// What a warp needs to stream one row-block (16 A rows: lane (g, t) holds rows g and g + 8, scale group t) over K.
+struct GsStream {
+  const uint4 *w_lo, *w_hi;       // this lane's 16 bytes of k-block 0 of its two rows
+  const uint16_t *s_lo, *s_hi;    // scale rows of A rows 0..7 and 8..15, k-block 0
+  size_t srow;                    // scales per weight row
+  uint32_t ring;                  // the warp's ring, then its scale stage (shared-memory address)
+  uint32_t x0, xstep;             // this lane's B operand of token 0, k-block 0, and its advance per k-block (0: the zero block)
+  uint32_t meta0;                 // (f, off) of token 0, k-block 0, this lane's scale group
+  uint32_t xbytes;                // bytes from one token's stage to the next
+  int steps;                      // k-blocks of a row
+};
+
+// The streaming loop with the group's token count and the chunk length as compile-time constants: no per-token
+// branches, the tokens' MMA chains interleave, and every address is a running value (an earlier form with run-time
+// counts, pointer arithmetic per access and a division in the scale copies spent 164 warp instructions per 1 KB
+// step, 42 of them integer multiply-adds for addresses, and was bound by its instruction stream at 3.4 TB/s).
+template <int CNT, int CHUNK>
+__device__ __forceinline__ void gs_stream(const GsStream &q, int lane, float (&acc_lo)[kWgSmallTokens], float (&acc_hi)[kWgSmallTokens]) {
+  constexpr int kPieces = CHUNK / 2;  // 16-byte pieces (two k-blocks' scales) per row and chunk
+  const int g = lane >> 2, t = lane & 3;
+  const uint32_t ring_lane = q.ring + (uint32_t)lane * 16;
+  const uint32_t sstage = q.ring + kGsDepth * 1024;
+  const uint32_t sc0 = sstage + (uint32_t)(g * kGsScaleRow + t * 2);
+  uint32_t xk = q.x0, mk = q.meta0;
+  for (int k0 = 0; k0 < q.steps; k0 += CHUNK) {
+    const int n = min(CHUNK, q.steps - k0);
+    // ---- the chunk's scales, whole: 16 rows x kPieces pieces of 16 bytes ----
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < (16 * kPieces + 31) / 32; ++i) {
+      const int pc = lane + 32 * i;
+      const int row = pc / kPieces, p = pc - row * kPieces;
+      if (pc < 16 * kPieces && 2 * p < n) {
+        const uint16_t *src = ((row & 8) ? q.s_hi : q.s_lo) + (size_t)(row & 7) * q.srow + (size_t)(k0 + 2 * p) * 4;
+        gs_cp16_ca(sstage + (uint32_t)(row * kGsScaleRow + p * 16), src);
+      }
+    }
+    const uint4 *wl = q.w_lo + (size_t)k0 * 4, *wh = q.w_hi + (size_t)k0 * 4;  // next step to request
+    uint32_t slot_in = ring_lane;
+#pragma unroll
+    for (int s = 0; s < kGsDepth; ++s) {
+      if (s < n) {
+        gs_cp16(slot_in, wl);
+        gs_cp16(slot_in + 512, wh);
+        wl += 4;
+        wh += 4;
+        slot_in += 1024;
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    slot_in = ring_lane;
+    uint32_t slot_out = ring_lane, sc = sc0;
+    asm volatile("cp.async.wait_group %0;" ::"n"(kGsDepth - 1) : "memory");
+    __syncwarp();  // the scales were copied by other lanes
+    for (int s = 0; s < n; ++s) {
+      asm volatile("cp.async.wait_group %0;" ::"n"(kGsDepth - 1) : "memory");
+      const uint4 wlv = gs_lds128(slot_out), whv = gs_lds128(slot_out + 512);
+      const float sl = gs_lds_bf16(sc), sh = gs_lds_bf16(sc + 8 * kGsScaleRow);
+      uint4 x01[CNT], x23[CNT];
+      uint2 meta[CNT];
+#pragma unroll
+      for (int tok = 0; tok < CNT; ++tok) {
+        x01[tok] = gs_lds128(xk + tok * q.xbytes);
+        x23[tok] = gs_lds128(xk + tok * q.xbytes + 16);
+        meta[tok] = gs_lds64(mk + tok * q.xbytes);
+      }
+      // the A operands of the k-block's four MMAs, unpacked once for all tokens
+      const uint32_t wlw[4] = {wlv.x, wlv.y, wlv.z, wlv.w}, whw[4] = {whv.x, whv.y, whv.z, whv.w};
+      uint32_t a0[4], a1[4], a2[4], a3[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        a0[i] = (wlw[i] << 4) & kByteNibMask;
+        a1[i] = (whw[i] << 4) & kByteNibMask;
+        a2[i] = wlw[i] & kByteNibMask;
+        a3[i] = whw[i] & kByteNibMask;
+      }
+      int d[CNT][4];
+#pragma unroll
+      for (int tok = 0; tok < CNT; ++tok) {
+        const int noff = -(int)meta[tok].y;  // the offset 128 sum X rides in the low-limb accumulators
+        d[tok][0] = 0, d[tok][1] = noff, d[tok][2] = 0, d[tok][3] = noff;
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int tok = 0; tok < CNT; ++tok) {
+          const uint32_t b0 = i == 0 ? x01[tok].x : i == 1 ? x01[tok].z : i == 2 ? x23[tok].x : x23[tok].z;
+          const uint32_t b1 = i == 0 ? x01[tok].y : i == 1 ? x01[tok].w : i == 2 ? x23[tok].y : x23[tok].w;
+          mma_u8s8_16832(d[tok], a0[i], a1[i], a2[i], a3[i], b0, b1);
+        }
+      }
+#pragma unroll
+      for (int tok = 0; tok < CNT; ++tok) {
+        const float f = __uint_as_float(meta[tok].x);
+        acc_lo[tok] = fmaf(sl, (float)(d[tok][0] * 256 + d[tok][1]) * f, acc_lo[tok]);
+        acc_hi[tok] = fmaf(sh, (float)(d[tok][2] * 256 + d[tok][3]) * f, acc_hi[tok]);
+      }
+      // the slot just read is free: request step s + depth into it
+      if (s + kGsDepth < n) {
+        gs_cp16(slot_in, wl);
+        gs_cp16(slot_in + 512, wh);
+        wl += 4;
+        wh += 4;
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      slot_out += 1024;
+      if (slot_out == ring_lane + kGsDepth * 1024) slot_out = ring_lane;
+      slot_in = slot_out;
+      sc += 8;
+      xk += q.xstep;
+      mk += 32;
+    }
+  }
+}
+
+template <int CHUNK>
+__device__ __forceinline__ void gs_stream_by_count(int cnt, const GsStream &q, int lane, float (&acc_lo)[kWgSmallTokens],
+                                                   float (&acc_hi)[kWgSmallTokens]) {
+  switch (cnt) {
+    case 1: gs_stream<1, CHUNK>(q, lane, acc_lo, acc_hi); break;
+    case 2: gs_stream<2, CHUNK>(q, lane, acc_lo, acc_hi); break;
+    case 3: gs_stream<3, CHUNK>(q, lane, acc_lo, acc_hi); break;
+    default: gs_stream<4, CHUNK>(q, lane, acc_lo, acc_hi); break;
+  }
+}
 
 template <bool SWIGLU>
 __global__ void __launch_bounds__(kGsThreads, 1) wgemv_small_kernel(const WgArgs a) {
@@ -55,8 +197,7 @@ __global__ void __launch_bounds__(kGsThreads, 1) wgemv_small_kernel(const WgArgs
   const int g = lane >> 2, t = lane & 3;
   const int K = a.K;
   const size_t xbytes = imma_stage_bytes(K);
-  unsigned char *ring_ptr = smem + (size_t)kWgSmallTokens * xbytes + (size_t)warp * kGsWarpBytes;
-  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(ring_ptr);
+  const uint32_t smem_addr = (uint32_t)__cvta_generic_to_shared(smem);
 
   // ---- the launch's small groups, in tile order (every CTA builds the same list) ----
   if (tid == 0) s_ngroups = 0;
@@ -90,9 +231,18 @@ __global__ void __launch_bounds__(kGsThreads, 1) wgemv_small_kernel(const WgArgs
   const long per = (total + gridDim.x - 1) / gridDim.x;
   const long q0 = (long)blockIdx.x * per, q1 = min(total, q0 + per);
 
-  const int steps = K / 128;  // k-blocks of a row
-  const size_t wrow = (size_t)K / 32, srow = (size_t)K / 32;  // uint4 per weight row, scales per row
+  GsStream st;
+  st.steps = K / 128;
+  st.srow = (size_t)K / 32;
+  st.xbytes = (uint32_t)xbytes;
+  st.ring = smem_addr + (uint32_t)(kWgSmallTokens * xbytes) + (uint32_t)(warp * kGsWarpBytes);
+  // lanes with (g >> 1) == t supply limb (g & 1) of their quad-lane's group; the others read the stage's zero block
   const bool supply = (g >> 1) == t;
+  st.x0 = smem_addr + (supply ? (uint32_t)(t * 64 + (g & 1) * 32) : (uint32_t)(K * 2 + (K / 32) * 8 + 64 + (lane & 1) * 16));
+  st.xstep = supply ? 256u : 0u;
+  st.meta0 = smem_addr + (uint32_t)(K * 2) + (uint32_t)t * 8;
+  const size_t wrow = (size_t)K / 32;  // uint4 per weight row
+  const bool chunk16 = st.steps % 16 == 0;
   int staged = -1;
   for (long q = q0; q < q1; ++q) {
     const int gi = (int)(q / runs), run = (int)(q - (long)gi * runs);
@@ -103,8 +253,8 @@ __global__ void __launch_bounds__(kGsThreads, 1) wgemv_small_kernel(const WgArgs
       __syncthreads();  // every warp is done with the previous group's stages
       for (int tok = 0; tok < cnt; ++tok) {
         const size_t xr = a.x_index ? (size_t)a.x_index[p0 + tok] : (size_t)(p0 + tok);
-        const ImmaStage st = imma_stage_carve(smem + (size_t)tok * xbytes, K);
-        stage_x_imma(reinterpret_cast<const uint4 *>(a.x + xr * K), st, K, tid, kGsThreads);
+        const ImmaStage stg = imma_stage_carve(smem + (size_t)tok * xbytes, K);
+        stage_x_imma(reinterpret_cast<const uint4 *>(a.x + xr * K), stg, K, tid, kGsThreads);
       }
       __syncthreads();
       staged = gi;
@@ -114,72 +264,15 @@ __global__ void __launch_bounds__(kGsThreads, 1) wgemv_small_kernel(const WgArgs
     const size_t erow = (size_t)e * a.expert_stride_rows;
     const size_t r_lo = erow + (SWIGLU ? rb * 8 : rb * 16) + g;
     const size_t r_hi = SWIGLU ? r_lo : r_lo + 8;
-    const uint4 *w_lo = reinterpret_cast<const uint4 *>(a.w_a) + r_lo * wrow + t;
-    const uint4 *w_hi = reinterpret_cast<const uint4 *>(SWIGLU ? a.w_b : a.w_a) + r_hi * wrow + t;
-    const uint16_t *s_lo = a.s_a + (r_lo - g) * srow;                    // scale rows of A rows 0..7
-    const uint16_t *s_hi = (SWIGLU ? a.s_b : a.s_a) + (r_hi - g) * srow;  // ... and 8..15
+    st.w_lo = reinterpret_cast<const uint4 *>(a.w_a) + r_lo * wrow + t;
+    st.w_hi = reinterpret_cast<const uint4 *>(SWIGLU ? a.w_b : a.w_a) + r_hi * wrow + t;
+    st.s_lo = a.s_a + (r_lo - g) * st.srow;
+    st.s_hi = (SWIGLU ? a.s_b : a.s_a) + (r_hi - g) * st.srow;
     float acc_lo[kWgSmallTokens], acc_hi[kWgSmallTokens];
 #pragma unroll
     for (int k = 0; k < kWgSmallTokens; ++k) acc_lo[k] = acc_hi[k] = 0.f;
-    const unsigned char *sc_lo = ring_ptr + kGsDepth * 1024 + g * kGsScaleRow + t * 2;
-    const unsigned char *sc_hi = sc_lo + 8 * kGsScaleRow;
-    for (int k0 = 0; k0 < steps; k0 += kGsChunk) {
-      const int n = min(kGsChunk, steps - k0);
-      // the chunk's scales, whole (consecutive lanes copy consecutive 8-byte pieces of a row), then the first steps
-      __syncwarp();
-      for (int pc = lane; pc < 16 * n; pc += 32) {
-        const int row = pc / n, s = pc - row * n;
-        const uint16_t *src = ((row & 8) ? s_hi : s_lo) + (size_t)(row & 7) * srow + (size_t)(k0 + s) * 4;
-        gs_cp8(ring + kGsDepth * 1024 + (uint32_t)(row * kGsScaleRow + s * 8), src);
-      }
-      auto issue = [&](int s) {
-        if (s < n) {
-          const uint32_t base = ring + (uint32_t)(s % kGsDepth) * 1024 + (uint32_t)lane * 16;
-          gs_cp16(base, w_lo + (size_t)(k0 + s) * 4);
-          gs_cp16(base + 512, w_hi + (size_t)(k0 + s) * 4);
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-      };
-#pragma unroll
-      for (int s = 0; s < kGsDepth; ++s) issue(s);
-      for (int s = 0; s < n; ++s) {
-        asm volatile("cp.async.wait_group %0;" ::"n"(kGsDepth - 1) : "memory");
-        if (s == 0) __syncwarp();  // the scales were copied by other lanes
-        const unsigned char *slot = ring_ptr + (size_t)(s % kGsDepth) * 1024;
-        const uint4 wl = *reinterpret_cast<const uint4 *>(slot + lane * 16);
-        const uint4 wh = *reinterpret_cast<const uint4 *>(slot + 512 + lane * 16);
-        const float sl = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(sc_lo + s * 8));
-        const float sh = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(sc_hi + s * 8));
-        // the A operands of the k-block's four MMAs, unpacked once for all tokens
-        const uint32_t wlw[4] = {wl.x, wl.y, wl.z, wl.w}, whw[4] = {wh.x, wh.y, wh.z, wh.w};
-        uint32_t a0[4], a1[4], a2[4], a3[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          a0[i] = (wlw[i] << 4) & kByteNibMask;
-          a1[i] = (whw[i] << 4) & kByteNibMask;
-          a2[i] = wlw[i] & kByteNibMask;
-          a3[i] = whw[i] & kByteNibMask;
-        }
-        const int kb = k0 + s;
-#pragma unroll
-        for (int tok = 0; tok < kWgSmallTokens; ++tok) {
-          if (tok < cnt) {
-            const unsigned char *xs = smem + (size_t)tok * xbytes;
-            const uint4 *xp = supply ? reinterpret_cast<const uint4 *>(xs + (size_t)kb * 256 + t * 64 + (g & 1) * 32)
-                                     : reinterpret_cast<const uint4 *>(xs + (size_t)K * 2 + (size_t)(K / 32) * 8) + 4 + (lane & 1);
-            const uint4 x01 = xp[0], x23 = xp[1];
-            int d[4] = {0, 0, 0, 0};
-            mma_u8s8_16832(d, a0[0], a1[0], a2[0], a3[0], x01.x, x01.y);
-            mma_u8s8_16832(d, a0[1], a1[1], a2[1], a3[1], x01.z, x01.w);
-            mma_u8s8_16832(d, a0[2], a1[2], a2[2], a3[2], x23.x, x23.y);
-            mma_u8s8_16832(d, a0[3], a1[3], a2[3], a3[3], x23.z, x23.w);
-            const uint2 meta = reinterpret_cast<const uint2 *>(xs + (size_t)K * 2)[kb * 4 + t];
-            imma_post(d, meta, sl, sh, acc_lo[tok], acc_hi[tok]);
-          }
-        }
-        issue(s + kGsDepth);
-      }
-    }
+    if (chunk16) gs_stream_by_count<16>(cnt, st, lane, acc_lo, acc_hi);
+    else gs_stream_by_count<14>(cnt, st, lane, acc_lo, acc_hi);
     // ---- a row's four scale groups sit in the four lanes of its quad ----
 #pragma unroll
     for (int tok = 0; tok < kWgSmallTokens; ++tok) {
@@ -206,7 +299,7 @@ __global__ void __launch_bounds__(kGsThreads, 1) wgemv_small_kernel(const WgArgs
 
 bool wgemv_small_supports(int mode, const WgArgs &a) {
   if (mode != WG_I4_SWIGLU && mode != WG_I4_PLAIN) return false;
-  if (a.identity_tiles || a.K % 128 || a.R % 16) return false;
+  if (a.identity_tiles || a.K % 256 || a.R % 16) return false;  // 16-byte scale copies: an even number of k-blocks per row
   return wgemv_small_smem_bytes(a.K) <= 200 * 1024;
 }
 

@@ -28,7 +28,9 @@ def test_bf16_gemv(cuda, oracle, rows, cols, T):
         util.assert_close(y16[t], oracle.bf16_round(wide), "bf16_gemv")
 
 
-@pytest.mark.parametrize("hidden,ffn,T", [(7168, 2048, 1), (7168, 2048, 8), (256, 128, 2)])
+# more than 8 rows: each matrix streamed once for all rows (wgemm_stream.cu), K split for the down projection
+@pytest.mark.parametrize("hidden,ffn,T", [(7168, 2048, 1), (7168, 2048, 8), (256, 128, 2), (7168, 2048, 9), (7168, 2048, 33),
+                                         (512, 256, 64), (1024, 4608, 17)])
 def test_bf16_mlp(cuda, oracle, hidden, ffn, T):
     from blok_b200 import lib
     rng = np.random.default_rng(hidden + ffn + T)
@@ -107,7 +109,7 @@ def test_router_tie_rule_on_device(cuda):
     np.testing.assert_allclose(util.t2np_f32(wts), 2.827 / 8, rtol=1e-6)
 
 
-@pytest.mark.parametrize("vocab,hidden,T", [(163840, 7168, 1), (4096, 512, 3)])
+@pytest.mark.parametrize("vocab,hidden,T", [(163840, 7168, 1), (4096, 512, 3), (4096, 512, 40), (163840, 7168, 64)])
 def test_lm_head_argmax_and_embed(cuda, oracle, vocab, hidden, T):
     from blok_b200 import lib
     g = torch.Generator(device=cuda).manual_seed(vocab)
@@ -120,6 +122,9 @@ def test_lm_head_argmax_and_embed(cuda, oracle, vocab, hidden, T):
     n = (w[torch.tensor([17] + [int(i) for i in ids_in[1:]], device=cuda)].float() * 50).bfloat16()
     got = lib.lm_head_argmax(w, n).cpu().numpy()
     assert got[0] == 17
+    if T > 8:  # the rows of a large call and the same rows 8 at a time select the same ids
+        by8 = torch.cat([lib.lm_head_argmax(w, n[b:b + 8]) for b in range(0, T, 8)]).cpu().numpy()
+        assert (got == by8).all()
     if vocab <= 4096:
         wh, nh = util.t2np_bf16(w), util.t2np_f32(n)
         for t in range(T):

@@ -81,12 +81,14 @@ def test_attend_properties_at_full_size(cuda, layer32):
     assert torch.equal(o8, layer.attend(q, cache, seq)), "deterministic"
 
 
-@pytest.mark.parametrize("factor,B,ctxs", [(32.0, 2, [40, 7]), (64.0, 1, [130]), (32.0, 8, [4096] * 8)])
+@pytest.mark.parametrize("factor,B,ctxs", [(32.0, 2, [40, 7]), (64.0, 1, [130]), (32.0, 8, [4096] * 8),
+                                           (32.0, 12, [90 + 3 * i for i in range(12)]),      # 9..64 entries: projections
+                                           (32.0, 33, [20 + i for i in range(33)])])         # through the streaming kernel
 def test_mla_decode_block(cuda, oracle, factor, B, ctxs):
     """The whole block: projections, norm, RoPE, cache append, attention, o_proj; factor 64 is the reference's own."""
     from blok_b200 import lib, synth
     w = synth.mla_weights(cuda, seed=3, std=0.02)
-    layer = lib.MlaLayer(w, yarn_factor=factor, max_batch=8, max_ctx=8192)
+    layer = lib.MlaLayer(w, yarn_factor=factor, max_batch=max(8, B), max_ctx=8192)
     ctx_stride = max(ctxs) + 8
     cache = synth.latent_cache(B, ctx_stride, cuda, seed=9)
     before = cache.clone()

@@ -112,7 +112,13 @@ def test_more_than_eight_sequences(cuda, layer16):
         want = layer.decode(n[lo:hi].contiguous(), part, torch.tensor(ctxs[lo:hi], dtype=torch.int32, device=cuda))
         for b in range(lo, hi):
             util.assert_close(util.t2np_f32(got[b]), util.t2np_f32(want[b - lo]).astype(np.float64), "sequence %d of 13" % b)
-        assert torch.equal(one_call[lo:hi], part)
+        # 13 entries take one pass of the weight-streaming kernel per projection, 8 and 5 the mat-vec kernel: the appended
+        # rows agree within the summation order, every other row is untouched
+        for b in range(lo, hi):
+            util.assert_close(util.t2np_f32(one_call[b, ctxs[b]]), util.t2np_f32(part[b - lo, ctxs[b]]).astype(np.float64), "appended row %d" % b)
+            keep = torch.ones(cap, dtype=torch.bool, device=cuda)
+            keep[ctxs[b]] = False
+            assert torch.equal(one_call[b][keep], cache[b][keep])
 
 
 def test_paged_prefill_through_one_slot(cuda, layer16):
