@@ -757,7 +757,7 @@ extern "C" int blok_moe_ep_forward(blok_moe_ep_t *ep, const blok_bf16_t *x, int 
     g.w_a = w.gate_w; g.w_b = w.up_w; g.s_a = w.gate_s; g.s_b = w.up_s; g.expert_stride_rows = w.inter;
     g.x = rx; g.x_index = nullptr; g.K = w.hidden; g.R = w.inter; g.out_bf16 = L->b_mid; g.out_f32 = nullptr;
     g.tile_expert = L->b_tile_expert; g.tile_start = L->b_tile_start; g.tile_count = L->b_tile_count;
-    g.num_tiles = L->b_num_tiles; g.out_index = nullptr;
+    g.num_tiles = L->b_num_tiles; g.out_index = nullptr; g.small_limit = L->b_num_tiles + 1;
     g.n_rows = (int)std::min<long>(ep->cap_rows, (long)std::max(N, 1) );  // what a balanced routing sends here; picks the kernel
     if ((rc = launch_wgemm(WG_I4_SWIGLU, g, max_tiles, stream))) return rc;
     WgArgs d = g;

@@ -2,6 +2,7 @@
 // `run` lambda, src/kimi_exec.cu:780-893 (per-layer body :803-878, sampler :880-881,
 // prompt replay and decode loop :885-890).  Weights are resident in HBM; the
 // reference re-reads every tile from storage on every use (:608-649).
+#include <algorithm>
 #include <cstring>
 #include <map>
 #include <new>
@@ -157,6 +158,8 @@ struct blok_model {
   blok_comm_t *comm = nullptr;
   int ep_base = 0, ep_local = 0;
   float *ep_logits = nullptr;   // [rows, experts]
+  float *ep_sk = nullptr;       // K-split partial sums of the router logits over 9..64 rows
+  size_t ep_sk_bytes = 0;
   uint16_t *ep_ids = nullptr;   // [rows, topk]
   int *ep_local_ids = nullptr;  // [rows, topk] id - ep_base (outside [0, ep_local): held by another rank)
   int *ep_rows = nullptr;       // [rows * topk] row of assignment a: a / topk
@@ -315,6 +318,8 @@ int build(blok_model *m) {
   if ((rc = dev_alloc(m, m->head_ws_bytes, &m->head_ws))) return rc;
   if (world > 1) {
     if ((rc = dev_alloc(m, (size_t)m->rows * c.experts * 4, &p))) return rc; m->ep_logits = static_cast<float *>(p);
+    m->ep_sk_bytes = wgemm_splitk_bytes(WG_BF16_PLAIN, c.hidden, c.experts, std::min((int)m->rows, kWgStreamTokens));
+    if ((rc = dev_alloc(m, std::max(m->ep_sk_bytes, (size_t)16), &p))) return rc; m->ep_sk = static_cast<float *>(p);
     if ((rc = dev_alloc(m, (size_t)m->rows * c.topk * 2, &p))) return rc; m->ep_ids = static_cast<uint16_t *>(p);
     if ((rc = dev_alloc(m, (size_t)m->rows * c.topk * 4, &p))) return rc; m->ep_local_ids = static_cast<int *>(p);
     if ((rc = dev_alloc(m, (size_t)m->rows * c.topk * 4, &p))) return rc; m->ep_wts = static_cast<float *>(p);
@@ -504,10 +509,16 @@ static int moe_sharded_rows(blok_model_t *m, blok::LayerWeights &L, int T, blok_
     sharded_finish_kernel<<<grid, 256, 0, stream>>>(m->ep_part, m->ep_shared, c.hidden, m->tmp);
     return launch_status("sharded_finish_kernel");
   }
-  for (int t0 = 0; t0 < T; t0 += 8)
-    if ((rc = launch_bf16_gemv(router, m->n + (size_t)t0 * c.hidden, nullptr, m->ep_logits + (size_t)t0 * c.experts, c.experts, c.hidden,
-                               T - t0 < 8 ? T - t0 : 8, stream)))
-      return rc;
+  // router logits (fp32): 9..64 rows in one pass of the weight-streaming kernel where the sizes fit it, else 8 rows at a time
+  const bool stream_rows = T > 8 && c.experts % 16 == 0 && c.hidden % 256 == 0;
+  for (int t0 = 0; t0 < T; t0 += stream_rows ? kWgStreamTokens : 8) {
+    const int nrows = std::min(T - t0, stream_rows ? kWgStreamTokens : 8);
+    rc = nrows > 8 ? launch_wgemm_rows(WG_BF16_PLAIN, router, nullptr, m->n + (size_t)t0 * c.hidden, nullptr, m->ep_logits + (size_t)t0 * c.experts,
+                                       c.experts, c.hidden, nrows, m->ep_sk, m->ep_sk_bytes, stream)
+                   : launch_bf16_gemv(router, m->n + (size_t)t0 * c.hidden, nullptr, m->ep_logits + (size_t)t0 * c.experts, c.experts, c.hidden,
+                                      nrows, stream);
+    if (rc) return rc;
+  }
   if ((rc = launch_router_topk(m->ep_logits, tp<float>(L.t, "router_bias"), T, c.experts, c.topk, c.routed_scale, m->ep_ids, m->ep_wts,
                                m->ep_local_ids, m->ep_base, stream)))
     return rc;
@@ -525,14 +536,16 @@ static int moe_sharded_rows(blok_model_t *m, blok::LayerWeights &L, int T, blok_
   return launch_status("sharded_finish_kernel");
 }
 
-// The feed-forward half of layer l for T rows: m->n -> m->tmp (:829-877 without the residual add).  Steps of up to 8
-// sequences take the batch-1 kernels row by row; prefill chunks and larger steps take the grouped GEMM for the routed
-// experts where the sizes fit it, and the dense layer 8 rows at a time.
+// The feed-forward half of layer l for T rows: m->n -> m->tmp (:829-877 without the residual add).  Steps of up to 3
+// sequences take the batch-1 kernels row by row; prefill chunks and larger steps take the grouped kernels for the routed
+// experts where the sizes fit them, and the dense layer up to 64 rows at a time.
 static int ffn_rows(blok_model_t *m, int l, int T, bool chunk, blok_stream_t stream_) {
   const blok_model_config &c = m->cfg;
   auto &L = m->layers[l];
   const size_t H = c.hidden;
-  const bool wide = chunk ? T > 1 : T > 8;
+  // the grouped kernels stream each selected expert once for all rows: from four rows on that is cheaper than a launch
+  // of the batch-1 kernel per row (12-layer model, 8 sequences: 10.2 ms a step row by row)
+  const bool wide = chunk ? T > 1 : T > 3;
   int rc = BLOK_OK;
   if (l < c.first_dense) {
     // rows per call: up to 8, fewer when 8 rows of the wider of the two vectors would not fit in shared memory

@@ -145,7 +145,7 @@ int batched_alloc(blok_moe_layer *L) {
   size_t off = 0;
   auto take = [&](size_t b) { size_t at = off; off = al(off + b); return at; };
   size_t o_counts = take((nl + 1) * 4), o_offsets = take((nl + 1) * 4), o_sa = take(N * 4), o_sr = take(N * 4);
-  size_t o_te = take(L->b_max_tiles * 4), o_ts = take(L->b_max_tiles * 4), o_tc = take(L->b_max_tiles * 4), o_nt = take(4);
+  size_t o_te = take(L->b_max_tiles * 4), o_ts = take(L->b_max_tiles * 4), o_tc = take(L->b_max_tiles * 4), o_nt = take(8);  // the tile count, then the small-group kernel's limit
   size_t o_tte = take(L->b_max_ttiles * 4), o_tts = take(L->b_max_ttiles * 4), o_ttc = take(L->b_max_ttiles * 4), o_ntt = take(4);
   size_t o_ar = take(N * 4);
   size_t o_mid = take(N * (size_t)w.inter * 2), o_y = take(N * (size_t)w.hidden * 2);
@@ -191,7 +191,7 @@ int grouped_experts(blok_moe_layer *L, const uint16_t *x, const int *x_index, co
   g.w_a = w.gate_w; g.w_b = w.up_w; g.s_a = w.gate_s; g.s_b = w.up_s; g.expert_stride_rows = w.inter;
   g.x = x; g.x_index = L->b_sorted_row; g.K = w.hidden; g.R = w.inter; g.out_bf16 = L->b_mid; g.out_f32 = nullptr;
   g.tile_expert = L->b_tile_expert; g.tile_start = L->b_tile_start; g.tile_count = L->b_tile_count;
-  g.num_tiles = L->b_num_tiles; g.out_index = nullptr; g.n_rows = N;
+  g.num_tiles = L->b_num_tiles; g.out_index = nullptr; g.n_rows = N; g.small_limit = L->b_num_tiles + 1;
   const int max_tiles = std::min(L->b_max_tiles, (N + kWgTileTokens - 1) / kWgTileTokens + nl);
   if ((rc = launch_wgemm(WG_I4_SWIGLU, g, max_tiles, stream))) return rc;
   WgArgs d = g;

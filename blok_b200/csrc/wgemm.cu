@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(kWgThreads) wgemm_kernel(const WgArgs a) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int e = a.tile_expert[tile], p0 = a.tile_start[tile], cnt = a.tile_count[tile];
-  if (a.small_max && cnt <= a.small_max) return;  // a small group: wgemv_small.cu has it
+  if (a.small_max && cnt <= (a.small_limit ? *a.small_limit : a.small_max)) return;  // a small group: wgemv_small.cu has it
   const int ntiles = (cnt + 7) >> 3;
 
   // the lane's two weight rows

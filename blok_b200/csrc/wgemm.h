@@ -9,7 +9,7 @@ namespace blok {
 enum { WG_BF16_PLAIN = 0, WG_BF16_SWIGLU = 1, WG_I4_SWIGLU = 2, WG_I4_PLAIN = 3 };
 constexpr int kWgTileTokens = 64;
 constexpr int kWgStreamTokens = 64;  // bf16 weights over up to this many rows take the weight-streaming kernel (wgemm_stream.cu)
-constexpr int kWgSmallTokens = 4;  // groups of up to this many tokens take the mat-vec-style kernel (wgemv_small.cu)
+constexpr int kWgSmallTokens = 8;  // groups of up to this many tokens take the mat-vec-style kernel (wgemv_small.cu: four per pass)
 
 struct WgArgs {
   const void *w_a;
@@ -31,6 +31,9 @@ struct WgArgs {
   int identity_tiles = 0;  // the tiles are consecutive 64-row blocks of x (one group: a dense layer over n_rows tokens)
   int n_rows = 0;  // rows of x the launch covers (tokens, or token-expert assignments): picks the kernel
   int small_max = 0;  // > 0: tiles of at most this many tokens are somebody else's (wgemv_small.cu) and are skipped
+  // INT4 modes, optional: a device word in which the small-group kernel leaves the group size up to which it took the
+  // launch's tiles (it takes every group when the larger ones are few); the GEMM kernel behind it skips those
+  int *small_limit = nullptr;
   // bf16 modes over identity tiles: scratch for the K-split partial sums, see wgemm_splitk_bytes; NULL: no split
   float *splitk_ws = nullptr;
   size_t splitk_bytes = 0;

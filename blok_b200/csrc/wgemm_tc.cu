@@ -17,6 +17,8 @@
 // the MMAs; producers arrive on a `full` mbarrier per stage, tcgen05.commit on an `empty`
 // mbarrier frees it.  Every mbarrier wait is bounded; on a timeout the CTA records an
 // error, still releases its tensor memory and returns.
+#include <algorithm>
+
 #include "common.cuh"
 #include "wgemm.h"
 
@@ -182,11 +184,17 @@ __global__ void __launch_bounds__(kTcThreads, 2) wgemm_tc_kernel(const WgArgs a)
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) unsigned long long s_mbar[2 * kTcStages];
   __shared__ uint32_t s_tmem_base;
-  const int tile = blockIdx.y;
-  if (tile >= *a.num_tiles) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // The grid's y extent is a fixed number of tile slots, not the worst-case tile count (tokens / 64 + experts, most of
+  // which a launch does not use or leaves to the small-group kernel: 6,000-11,000 CTAs that only start and leave cost
+  // 36-58 us per launch); a CTA walks the tiles slot, slot + slots, ...
+  const int ntiles = *a.num_tiles;
+  const int skip_upto = a.small_max ? (a.small_limit ? *a.small_limit : a.small_max) : 0;  // groups wgemv_small.cu has taken
+  bool have_tmem = false;
+  uint32_t tmem = 0;
+  for (int tile = blockIdx.y; tile < ntiles; tile += gridDim.y) {
   const int e = a.tile_expert[tile], p0 = a.tile_start[tile], cnt = a.tile_count[tile];
-  if (a.small_max && cnt <= a.small_max) return;  // a small group: wgemv_small.cu has it (nothing is allocated yet)
+  if (cnt <= skip_upto) continue;  // nothing is allocated yet
   const int N = max(16, (cnt + 15) & ~15);  // token columns the MMAs cover
 
   // ---- this thread unpacks weight row r of block blk: threads 0..127 block 0 (gate rows / rows r), 128..255 block 1 ----
@@ -253,18 +261,19 @@ __global__ void __launch_bounds__(kTcThreads, 2) wgemm_tc_kernel(const WgArgs a)
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 0) {
+  if (warp == 0 && !have_tmem) {  // once per CTA, at its first tile; the columns serve every tile the CTA walks
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(&s_tmem_base)),
                  "r"((uint32_t)kTcTmemCols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  have_tmem = true;
   uint4 xnext[2];
   if (producer) fetch_x(0, xnext);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem = s_tmem_base;
+  tmem = s_tmem_base;
   const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((128u >> 4) << 24);
 
   bool failed = false;
@@ -376,8 +385,16 @@ __global__ void __launch_bounds__(kTcThreads, 2) wgemm_tc_kernel(const WgArgs a)
 
   if (producer && !failed) tc_epilogue<SWIGLU>(a, tmem, kTcN, warp, lane, N, cnt, p0, row0);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  // a CTA that gave up on a barrier stops here (every warp: the flag goes through the barrier's OR)
+  if (__syncthreads_or(failed ? 1 : 0)) break;
+  // the next tile sets the barriers up afresh
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < 2 * kTcStages; ++s) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(mbar_full + 8 * s) : "memory");
+  }
   __syncthreads();
-  if (warp == 0)
+  }
+  if (have_tmem && warp == 0)  // block-uniform: every thread walked the same tiles
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)kTcTmemCols) : "memory");
 }
 
@@ -576,12 +593,14 @@ int launch_wgemm_tc(int mode, const WgArgs &args, int max_tiles, cudaStream_t st
     return launch_status("wgemm_tc_bf16_kernel");
   }
   const size_t smem = wgemm_tc_smem_bytes();
+  // tile slots: about eight rounds of CTAs (two per SM); a CTA walks the tiles of its slot
+  const dim3 igrid(grid.x, std::min(max_tiles, std::max(1, 8 * 2 * sm_count() / (int)grid.x)));
   if (swiglu) {
     BLOK_CUDA(cudaFuncSetAttribute(wgemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    wgemm_tc_kernel<true><<<grid, kTcThreads, smem, stream>>>(args);
+    wgemm_tc_kernel<true><<<igrid, kTcThreads, smem, stream>>>(args);
   } else {
     BLOK_CUDA(cudaFuncSetAttribute(wgemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    wgemm_tc_kernel<false><<<grid, kTcThreads, smem, stream>>>(args);
+    wgemm_tc_kernel<false><<<igrid, kTcThreads, smem, stream>>>(args);
   }
   return launch_status("wgemm_tc_kernel");
 }

@@ -25,10 +25,12 @@
 namespace blok {
 
 constexpr int kGsWarps = 16, kGsThreads = kGsWarps * 32;
+constexpr int kGsPass = 4;                                // tokens per pass over a group's weights; a group of 5..8 takes two
 constexpr int kGsDepth = 5;                               // ring steps of 1 KB (16 rows x 64 bytes) in flight per warp
 constexpr int kGsMaxChunk = 16;                           // most k-blocks whose scales are staged together
 constexpr int kGsScaleRow = kGsMaxChunk * 8 + 16;         // bytes per row of the scale stage (36 words: rows 4 banks apart)
 constexpr int kGsWarpBytes = kGsDepth * 1024 + 16 * kGsScaleRow;
+constexpr int kGsBigPasses = 48;                          // most passes of larger groups this kernel takes over from the GEMM kernel
 constexpr int kGsMaxGroups = 2048;                        // small groups a launch can hold in its shared-memory list
 
 __device__ __forceinline__ void gs_cp16(uint32_t dst, const void *src) {
@@ -59,7 +61,7 @@ __device__ __forceinline__ float gs_swiglu(float g, float u) {  // :322 rounds b
   return round_bf16(round_bf16(g / (1.0f + expf(-g))) * u);
 }
 
-size_t wgemv_small_smem_bytes(int K) { return (size_t)kWgSmallTokens * imma_stage_bytes(K) + (size_t)kGsWarps * kGsWarpBytes; }
+size_t wgemv_small_smem_bytes(int K) { return (size_t)kGsPass * imma_stage_bytes(K) + (size_t)kGsWarps * kGsWarpBytes; }
 
 // What a warp needs to stream one row-block (16 A rows: lane (g, t) holds rows g and g + 8, scale group t) over K.
 struct GsStream {
@@ -78,7 +80,7 @@ struct GsStream {
 // counts, pointer arithmetic per access and a division in the scale copies spent 164 warp instructions per 1 KB
 // step, 42 of them integer multiply-adds for addresses, and was bound by its instruction stream at 3.4 TB/s).
 template <int CNT, int CHUNK>
-__device__ __forceinline__ void gs_stream(const GsStream &q, int lane, float (&acc_lo)[kWgSmallTokens], float (&acc_hi)[kWgSmallTokens]) {
+__device__ __forceinline__ void gs_stream(const GsStream &q, int lane, float (&acc_lo)[kGsPass], float (&acc_hi)[kGsPass]) {
   constexpr int kPieces = CHUNK / 2;  // 16-byte pieces (two k-blocks' scales) per row and chunk
   const int g = lane >> 2, t = lane & 3;
   const uint32_t ring_lane = q.ring + (uint32_t)lane * 16;
@@ -177,8 +179,8 @@ __device__ __forceinline__ void gs_stream(const GsStream &q, int lane, float (&a
 }
 
 template <int CHUNK>
-__device__ __forceinline__ void gs_stream_by_count(int cnt, const GsStream &q, int lane, float (&acc_lo)[kWgSmallTokens],
-                                                   float (&acc_hi)[kWgSmallTokens]) {
+__device__ __forceinline__ void gs_stream_by_count(int cnt, const GsStream &q, int lane, float (&acc_lo)[kGsPass],
+                                                   float (&acc_hi)[kGsPass]) {
   switch (cnt) {
     case 1: gs_stream<1, CHUNK>(q, lane, acc_lo, acc_hi); break;
     case 2: gs_stream<2, CHUNK>(q, lane, acc_lo, acc_hi); break;
@@ -190,8 +192,8 @@ __device__ __forceinline__ void gs_stream_by_count(int cnt, const GsStream &q, i
 template <bool SWIGLU>
 __global__ void __launch_bounds__(kGsThreads, 1) wgemv_small_kernel(const WgArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ int s_group[kGsMaxGroups];  // tile indices of the launch's small groups
-  __shared__ int s_ngroups;
+  __shared__ int s_group[kGsMaxGroups];  // the launch's passes: tile index | first token of the pass << 24
+  __shared__ int s_ngroups, s_limit;
   __shared__ int s_wcount[kGsWarps];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
@@ -199,23 +201,46 @@ __global__ void __launch_bounds__(kGsThreads, 1) wgemv_small_kernel(const WgArgs
   const size_t xbytes = imma_stage_bytes(K);
   const uint32_t smem_addr = (uint32_t)__cvta_generic_to_shared(smem);
 
-  // ---- the launch's small groups, in tile order (every CTA builds the same list) ----
-  if (tid == 0) s_ngroups = 0;
-  __syncthreads();
+  // ---- which groups are this kernel's: those of up to kWgSmallTokens tokens, or every group when the larger ones are so
+  // few that the GEMM kernel behind this one would spend a CTA's whole latency (about 100 us per product) on a handful
+  // of tiles, while their passes here are spread over every SM (about 5 us each) ----
   const int ntiles = *a.num_tiles;
+  {
+    int mine = 0;
+    for (int i = tid; i < ntiles; i += kGsThreads) {
+      const int c = a.tile_count[i];
+      if (c > kWgSmallTokens) mine += (c + kGsPass - 1) / kGsPass;
+    }
+    for (int o = 16; o; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+    if (lane == 0) s_wcount[warp] = mine;
+    __syncthreads();
+    if (tid == 0) {
+      int tot = 0;
+      for (int w = 0; w < kGsWarps; ++w) tot += s_wcount[w];
+      s_limit = (a.small_limit && tot <= kGsBigPasses) ? kWgTileTokens : kWgSmallTokens;
+      if (a.small_limit && blockIdx.x == 0) *a.small_limit = s_limit;  // the GEMM kernel skips what this one takes
+      s_ngroups = 0;
+    }
+    __syncthreads();
+  }
+  const int limit = s_limit;
+  // ---- the passes in tile order, up to kGsPass tokens each (every CTA builds the same list) ----
   for (int i0 = 0; i0 < ntiles; i0 += kGsThreads) {
     const int i = i0 + tid;
-    const bool small = i < ntiles && a.tile_count[i] >= 1 && a.tile_count[i] <= kWgSmallTokens;
-    // positions by a block-wide ordered count: ballot per warp, then the warps in order
-    const unsigned m = __ballot_sync(0xffffffffu, small);
-    if (lane == 0) s_wcount[warp] = __popc(m);
-    __syncthreads();
-    int base = s_ngroups;
-    for (int w = 0; w < warp; ++w) base += s_wcount[w];
-    if (small) {
-      const int pos = base + __popc(m & ((1u << lane) - 1u));
-      if (pos < kGsMaxGroups) s_group[pos] = i;
+    const int c = i < ntiles ? a.tile_count[i] : 0;
+    const int np = (c >= 1 && c <= limit) ? (c + kGsPass - 1) / kGsPass : 0;
+    // positions by a block-wide ordered count: a scan inside the warp, then the warps in order
+    int incl = np;
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
     }
+    if (lane == 31) s_wcount[warp] = incl;
+    __syncthreads();
+    int pos = s_ngroups + incl - np;
+    for (int w = 0; w < warp; ++w) pos += s_wcount[w];
+    for (int k = 0; k < np; ++k)
+      if (pos + k < kGsMaxGroups) s_group[pos + k] = i | ((k * kGsPass) << 24);
     __syncthreads();
     if (tid == 0) {
       int tot = s_ngroups;
@@ -235,7 +260,7 @@ __global__ void __launch_bounds__(kGsThreads, 1) wgemv_small_kernel(const WgArgs
   st.steps = K / 128;
   st.srow = (size_t)K / 32;
   st.xbytes = (uint32_t)xbytes;
-  st.ring = smem_addr + (uint32_t)(kWgSmallTokens * xbytes) + (uint32_t)(warp * kGsWarpBytes);
+  st.ring = smem_addr + (uint32_t)(kGsPass * xbytes) + (uint32_t)(warp * kGsWarpBytes);
   // lanes with (g >> 1) == t supply limb (g & 1) of their quad-lane's group; the others read the stage's zero block
   const bool supply = (g >> 1) == t;
   st.x0 = smem_addr + (supply ? (uint32_t)(t * 64 + (g & 1) * 32) : (uint32_t)(K * 2 + (K / 32) * 8 + 64 + (lane & 1) * 16));
@@ -246,8 +271,8 @@ __global__ void __launch_bounds__(kGsThreads, 1) wgemv_small_kernel(const WgArgs
   int staged = -1;
   for (long q = q0; q < q1; ++q) {
     const int gi = (int)(q / runs), run = (int)(q - (long)gi * runs);
-    const int tile = s_group[gi];
-    const int e = a.tile_expert[tile], p0 = a.tile_start[tile], cnt = a.tile_count[tile];
+    const int tile = s_group[gi] & 0xffffff, tok0 = s_group[gi] >> 24;
+    const int e = a.tile_expert[tile], p0 = a.tile_start[tile] + tok0, cnt = min(kGsPass, a.tile_count[tile] - tok0);
     if (gi != staged) {
       // ---- the group's activations as block integers, one stage per token ----
       __syncthreads();  // every warp is done with the previous group's stages
@@ -268,14 +293,14 @@ __global__ void __launch_bounds__(kGsThreads, 1) wgemv_small_kernel(const WgArgs
     st.w_hi = reinterpret_cast<const uint4 *>(SWIGLU ? a.w_b : a.w_a) + r_hi * wrow + t;
     st.s_lo = a.s_a + (r_lo - g) * st.srow;
     st.s_hi = (SWIGLU ? a.s_b : a.s_a) + (r_hi - g) * st.srow;
-    float acc_lo[kWgSmallTokens], acc_hi[kWgSmallTokens];
+    float acc_lo[kGsPass], acc_hi[kGsPass];
 #pragma unroll
-    for (int k = 0; k < kWgSmallTokens; ++k) acc_lo[k] = acc_hi[k] = 0.f;
+    for (int k = 0; k < kGsPass; ++k) acc_lo[k] = acc_hi[k] = 0.f;
     if (chunk16) gs_stream_by_count<16>(cnt, st, lane, acc_lo, acc_hi);
     else gs_stream_by_count<14>(cnt, st, lane, acc_lo, acc_hi);
     // ---- a row's four scale groups sit in the four lanes of its quad ----
 #pragma unroll
-    for (int tok = 0; tok < kWgSmallTokens; ++tok) {
+    for (int tok = 0; tok < kGsPass; ++tok) {
       if (tok < cnt) {
         float lo = acc_lo[tok], hi = acc_hi[tok];
         lo += __shfl_xor_sync(0xffffffffu, lo, 1);
