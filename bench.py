@@ -507,18 +507,19 @@ def other_workload(a, rank, world, device, steps, warmup):
         unit = "mat-vecs/s"
     else:
         ctx = int(a.workload[len("mla"):])
-        layer = lib.MlaLayer(synth.mla_weights(device, seed=3), yarn_factor=32.0, max_batch=8, max_ctx=ctx + 8)
-        ncache = 6 if ctx <= 4096 else 3
-        caches = [synth.latent_cache(8, ctx + 8, device, seed=10 + i + rank) for i in range(ncache)]
-        n = synth.activations(8, 7168, device, 3)
-        ctx_len = torch.full((8,), ctx, dtype=torch.int32, device=device)
-        out = torch.empty((8, 7168), dtype=torch.bfloat16, device=device)
+        B = 8 if a.batch == 1 else min(a.batch, 64)   # config 3 is batch 8; --batch N measures the block at N sequences
+        layer = lib.MlaLayer(synth.mla_weights(device, seed=3), yarn_factor=32.0, max_batch=max(B, 8), max_ctx=ctx + 8)
+        ncache = 6 if ctx <= 4096 and B <= 8 else 3
+        caches = [synth.latent_cache(B, ctx + 8, device, seed=10 + i + rank) for i in range(ncache)]
+        n = synth.activations(B, 7168, device, 3)
+        ctx_len = torch.full((B,), ctx, dtype=torch.int32, device=device)
+        out = torch.empty((B, 7168), dtype=torch.bfloat16, device=device)
         run = lambda i: layer.decode(n, caches[i % ncache], ctx_len, out=out)
-        alg = 8 * ctx * 1152 + 202244096
-        unit_tokens = 8 * world
-        workload = "config 3: MLA absorbed decode block, batch 8, ctx %d, bf16 latent cache%s" % (ctx, "" if world == 1 else ", replicas x%d" % world)
+        alg = B * ctx * 1152 + 202244096
+        unit_tokens = B * world
+        workload = "config 3: MLA absorbed decode block, batch %d, ctx %d, bf16 latent cache%s" % (B, ctx, "" if world == 1 else ", replicas x%d" % world)
         scaling = "weak"
-        metric = "tok/s, MLA decode block (batch 8, ctx %d)" % ctx
+        metric = "tok/s, MLA decode block (batch %d, ctx %d)" % (B, ctx)
     # a side stream: the whole-model step replays a CUDA graph, which the legacy default stream cannot capture
     side = torch.cuda.Stream()
     torch.cuda.synchronize()
@@ -564,7 +565,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=3, help="distinct synthetic layers rotated between steps")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--batch", type=int, default=1, help="sequences per step of the `model` workload (up to 64)")
+    ap.add_argument("--batch", type=int, default=1, help="sequences per step of the `model` workloads (up to 64); with mla*: sequences of the block instead of config 3's 8")
     ap.add_argument("--model-layers", type=int, default=12, help="layers of the `model` workload (one GPU holds about 15)")
     ap.add_argument("--experts", type=int, default=384,
                     help="routed experts per layer; below 384 the run is a reduced case for profiler captures, "

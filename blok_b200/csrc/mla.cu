@@ -38,12 +38,16 @@ int launch_bf16_gemv_splitk(const uint16_t *w, const uint16_t *x, uint16_t *y_bf
 __global__ void __launch_bounds__(128)
     bf16_head_gemv_kernel(const uint16_t *__restrict__ w, long w_head_stride, const uint16_t *__restrict__ x,
                           long x_tok_stride, long x_head_stride, uint16_t *__restrict__ y, long y_tok_stride,
-                          long y_head_stride, int cols, int T) {
+                          long y_head_stride, int cols, int T_all) {
   extern __shared__ __align__(16) unsigned char smem[];
   __shared__ float partial[4][16][8];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int head = blockIdx.y;
+  // blockIdx.z: the group of 8 tokens (the later groups find the head's matrix in L2)
+  const int T = min(8, T_all - 8 * (int)blockIdx.z);
+  x += (size_t)blockIdx.z * 8 * x_tok_stride;
+  y += (size_t)blockIdx.z * 8 * y_tok_stride;
   const int per_row = cols / 8;
   for (int u = tid; u < per_row * T; u += blockDim.x) {
     int tok = u / per_row, c = u - tok * per_row;
@@ -256,8 +260,8 @@ int launch_mla_attend_paged(const uint16_t *q, const uint16_t *pool, const int *
 static int launch_head_gemv(const uint16_t *w, long w_head_stride, const uint16_t *x, long x_tok_stride,
                             long x_head_stride, uint16_t *y, long y_tok_stride, long y_head_stride, int rows, int cols,
                             int heads, int T, cudaStream_t stream) {
-  size_t smem = bf16_x_row_bytes(cols) * T;
-  bf16_head_gemv_kernel<<<dim3(rows / 16, heads), 128, smem, stream>>>(w, w_head_stride, x, x_tok_stride, x_head_stride,
+  size_t smem = bf16_x_row_bytes(cols) * std::min(T, 8);
+  bf16_head_gemv_kernel<<<dim3(rows / 16, heads, (T + 7) / 8), 128, smem, stream>>>(w, w_head_stride, x, x_tok_stride, x_head_stride,
                                                                       y, y_tok_stride, y_head_stride, cols, T);
   return launch_status("bf16_head_gemv_kernel");
 }
@@ -599,17 +603,14 @@ static int decode_body(blok_mla_layer *L, const uint16_t *n, const CacheRef &c, 
       w.kv_rank, w.rms_eps, c.block_table, c.slot_of, c.table_stride, c.page_rows, c.ctx_cap, L->err);
   if ((rc = launch_status("mla_prep_kernel"))) return rc;
   // q_abs = W_UK^T q_nope
-  for (int b0 = 0; b0 < B; b0 += 8)
-    if ((rc = launch_head_gemv(L->wuk_t, (long)w.kv_rank * w.qk_nope, L->q + b0 * q_row, (long)q_row, qk_head, L->q_full + b0 * qf_row,
-                               (long)qf_row, lat_w, w.kv_rank, w.qk_nope, w.heads, std::min(8, B - b0), stream)))
-      return rc;
+  if ((rc = launch_head_gemv(L->wuk_t, (long)w.kv_rank * w.qk_nope, L->q, (long)q_row, qk_head, L->q_full, (long)qf_row, lat_w, w.kv_rank,
+                             w.qk_nope, w.heads, B, stream)))
+    return rc;
   if ((rc = attend_and_merge(L, L->q_full, c, L->seq, B, L->scale, L->o_lat, stream))) return rc;
   // out_h = W_UV o_lat_h, then o_proj   (:826)
-  for (int b0 = 0; b0 < B; b0 += 8)
-    if ((rc = launch_head_gemv(w.kv_b + (size_t)w.qk_nope * w.kv_rank, (long)(w.qk_nope + w.v_head) * w.kv_rank, L->o_lat + b0 * ol_row,
-                               (long)ol_row, w.kv_rank, L->av + b0 * av_row, (long)av_row, w.v_head, w.v_head, w.kv_rank, w.heads,
-                               std::min(8, B - b0), stream)))
-      return rc;
+  if ((rc = launch_head_gemv(w.kv_b + (size_t)w.qk_nope * w.kv_rank, (long)(w.qk_nope + w.v_head) * w.kv_rank, L->o_lat, (long)ol_row,
+                             w.kv_rank, L->av, (long)av_row, w.v_head, w.v_head, w.kv_rank, w.heads, B, stream)))
+    return rc;
   return project(L, w.o, L->av, out, w.hidden, w.heads * w.v_head, B, gemm, stream);
 }
 
