@@ -108,8 +108,16 @@ class ClockSampler:
             os.unlink(self.path)
         except Exception:
             pass
-        if not sm:
-            return None
+        if not sm:  # the sampler produced nothing (a very short run): one reading taken now, marked as such
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=10).stdout.strip().splitlines()[0]
+                parts = [p.strip() for p in out.split(",")]
+                return {"sm_mhz": float(parts[0]), "sm_max_mhz": float(parts[1]),
+                        "reasons": [n for n, v in zip(names, parts[2:6]) if v.lower().startswith("active")], "samples": 0,
+                        "note": "read once after the timed region"}
+            except Exception:
+                return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "note": "nvidia-smi gave no reading"}
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
 
@@ -417,7 +425,11 @@ def other_workload(a, rank, world, device, steps, warmup):
                 if rank == 0:
                     print(json.dumps({"error": "expert-parallel parity check failed", "worst_abs_diff": worst}))
                 return 3
+            sampler = ClockSampler(device.index or 0)
+            if rank == 0:
+                sampler.start()
             rec, launches = ep_measure(T, rank, world, device, comm, steps, warmup, a.experts)
+            clocks = sampler.stop() if rank == 0 else None
             if rank == 0:
                 print(json.dumps({
                     "metric": "tok/s, INT4 MoE layer (T=%d)" % T, "value": rec["tok_per_s"], "unit": "tok/s", "n_gpus": world,
@@ -428,7 +440,7 @@ def other_workload(a, rank, world, device, steps, warmup):
                                            (T, world, a.experts // world),
                                "l2": "two layers and four inputs rotated", "ep_parity": "bit-equal to the single-GPU layer"},
                     "roofline": rec["roofline"], "roofline_tensor": rec.get("roofline_tensor"), "ep": rec,
-                    "gpu_launches": int(launches)}))
+                    "gpu_launches": int(launches), "clocks": clocks}))
             comm.close()
             dist.destroy_process_group()
             return 0
@@ -523,6 +535,9 @@ def other_workload(a, rank, world, device, steps, warmup):
     # a side stream: the whole-model step replays a CUDA graph, which the legacy default stream cannot capture
     side = torch.cuda.Stream()
     torch.cuda.synchronize()
+    sampler = ClockSampler(device.index or 0)
+    if rank == 0:
+        sampler.start()      # before the warm-up, so that a short timed region still has samples under load
     with torch.cuda.stream(side):
         for i in range(max(warmup, 3)):
             run(i)
@@ -535,6 +550,7 @@ def other_workload(a, rank, world, device, steps, warmup):
         e1.record()
         barrier()
     launches = lib.kernel_launch_count() - l0
+    clocks = sampler.stop() if rank == 0 else None
     ms = torch.tensor([e0.elapsed_time(e1)], device=device)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
@@ -551,7 +567,7 @@ def other_workload(a, rank, world, device, steps, warmup):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind, "traffic": None},
             **tensor_roofline(flops, per_step),
-            "gpu_launches": int(launches)}))
+            "gpu_launches": int(launches), "clocks": clocks}))
     if world > 1:
         dist.destroy_process_group()
     return 0

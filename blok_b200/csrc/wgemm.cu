@@ -258,7 +258,7 @@ int launch_wgemm(int mode, const WgArgs &args_in, int max_tiles, cudaStream_t st
     // (not when one GEMM kernel is forced: a forced run wants every row through the same arithmetic, whatever shares
     // its group, which is what the expert-parallel parity checks compare bit for bit)
     const char *sm = getenv("BLOK_WGEMM_SMALL");
-    if (i4 && forced == 0 && !(sm && sm[0] == '0') && wgemv_small_supports(mode, args)) {
+    if (i4 && forced == 0 && !(sm && sm[0] == '0') && wgemv_small_supports(mode, args, max_tiles)) {
       if (int rc = launch_wgemv_small(mode, args, stream)) return rc;
       args.small_max = kWgSmallTokens;
     }

@@ -58,7 +58,7 @@ int launch_identity_tiles(int T, int *tile_expert, int *tile_start, int *tile_co
 // The INT4 modes for groups of up to kWgSmallTokens tokens: streams the weights like the batch-1 decode kernel and
 // leaves the larger groups alone.  launch_wgemm runs it in front of the kernel that takes the rest
 // (BLOK_WGEMM_SMALL=0 in the environment: every group through the GEMM kernels).
-bool wgemv_small_supports(int mode, const WgArgs &args);
+bool wgemv_small_supports(int mode, const WgArgs &args, int max_tiles);
 int launch_wgemv_small(int mode, const WgArgs &args, cudaStream_t stream);
 
 // The bf16 modes over 1..kWgStreamTokens rows of x (identity tiles): every warp streams its 16 weight rows through a

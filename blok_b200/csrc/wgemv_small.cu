@@ -1,4 +1,4 @@
-// The grouped W4A16 product for groups of up to four tokens: a mat-vec-style consumer in place of the dequantising GEMM.
+// The grouped W4A16 product for groups of a few tokens: a mat-vec-style consumer in place of the dequantising GEMM.
 //
 // At T = 64 tokens and 384 experts a group holds 1.8 tokens on average, and the tcgen05 kernel (wgemm_tc.cu) still turns
 // every weight into a bf16 operand (about 15 thread-instructions per packed word) for a tile that is nearly empty.  Here
@@ -8,17 +8,21 @@
 // matvec_i4_bf16_scale_k (src/kimi_exec.cu:300-323) within the floating-point bar (the error model of i4_imma.cuh);
 // the SwiGLU epilogue keeps the reference's rounding points (:322, :255).
 //
-// One persistent CTA per SM (16 warps).  A task is (group, 16 consecutive row-blocks): the group's activations are
-// quantised to block integers in shared memory once per task run, then each warp streams one row-block over the whole
-// K in chunks of 14 k-blocks (the scales of a chunk are staged whole, as in moe_fused.cu).  Tasks are numbered over the
-// launch's small groups only and dealt out in contiguous ranges, so a CTA restages activations about twice per launch.
-// Groups of more than four tokens are left to the tcgen05 kernel, which skips the small ones (WgArgs::small_max).
+// One persistent CTA per SM (16 warps).  A task is (pass, 16 consecutive row-blocks), a pass being up to four tokens of
+// one group (a group of 5..8 tokens is two passes over its weights): the pass's activations are quantised to block
+// integers in shared memory once per task run, then each warp streams one row-block over the whole K in chunks of 14 or
+// 16 k-blocks (the scales of a chunk are staged whole, as in moe_fused.cu).  Tasks are dealt out in contiguous ranges, so
+// a CTA restages activations about twice per launch.  Larger groups are left to the tcgen05 kernel, which skips what this
+// kernel took (WgArgs::small_max, ::small_limit) - unless they are so few (48 passes' worth) that the GEMM kernel would
+// spend a CTA's whole latency, about 100 us per product, on a handful of tiles: then this kernel takes every group.
 //
-// Measured at T = 64 (284 groups, 7.05 GB of expert weights): gate/up 1.35 ms, down 0.72 ms (3.3-3.5 TB/s), the same
-// rate as the tcgen05 kernel on these nearly empty tiles.  Six tokens per group instead of four: slower (gate/up
-// 1.54 ms; the few groups of five or six cost the tcgen05 kernel less than the larger stages cost this one).  Four
-// warps sharing a row-block with K split between them (better locality in HBM, but the CTA meets at two barriers per
-// 14-step task): slower still (layer 2.70 ms against 2.36 ms).
+// Measured at T = 64 (284 groups, 7.05 GB of expert weights): gate/up and down together 1.75 ms (4.0 TB/s); with a
+// run-time token loop and pointer arithmetic per access 2.07 ms (164 warp instructions per 1 KB ring step against 116).
+// Six tokens per pass instead of four: slower (the larger stages cost more than the second pass of the few groups of
+// five or six).  The ring kept running across chunk boundaries (a second scale stage, the next chunk's scales riding
+// with its first weight request): no faster (1.95 ms against 1.93 ms per layer pass; the other fifteen warps of the SM
+// cover a warp's drained ring).  Four warps sharing a row-block with K split between them (better locality in HBM, but
+// the CTA meets at two barriers per 14-step task): slower still (layer 2.70 ms against 2.36 ms then).
 #include "i4_imma.cuh"
 #include "wgemm.h"
 
@@ -192,7 +196,7 @@ __device__ __forceinline__ void gs_stream_by_count(int cnt, const GsStream &q, i
 template <bool SWIGLU>
 __global__ void __launch_bounds__(kGsThreads, 1) wgemv_small_kernel(const WgArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ int s_group[kGsMaxGroups];  // the launch's passes: tile index | first token of the pass << 24
+  __shared__ unsigned short s_group[kGsMaxGroups];  // the launch's passes: tile index | pass of the tile << 12
   __shared__ int s_ngroups, s_limit;
   __shared__ int s_wcount[kGsWarps];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -240,7 +244,7 @@ __global__ void __launch_bounds__(kGsThreads, 1) wgemv_small_kernel(const WgArgs
     int pos = s_ngroups + incl - np;
     for (int w = 0; w < warp; ++w) pos += s_wcount[w];
     for (int k = 0; k < np; ++k)
-      if (pos + k < kGsMaxGroups) s_group[pos + k] = i | ((k * kGsPass) << 24);
+      if (pos + k < kGsMaxGroups) s_group[pos + k] = (unsigned short)(i | (k << 12));
     __syncthreads();
     if (tid == 0) {
       int tot = s_ngroups;
@@ -271,7 +275,7 @@ __global__ void __launch_bounds__(kGsThreads, 1) wgemv_small_kernel(const WgArgs
   int staged = -1;
   for (long q = q0; q < q1; ++q) {
     const int gi = (int)(q / runs), run = (int)(q - (long)gi * runs);
-    const int tile = s_group[gi] & 0xffffff, tok0 = s_group[gi] >> 24;
+    const int tile = s_group[gi] & 0xfff, tok0 = (s_group[gi] >> 12) * kGsPass;
     const int e = a.tile_expert[tile], p0 = a.tile_start[tile] + tok0, cnt = min(kGsPass, a.tile_count[tile] - tok0);
     if (gi != staged) {
       // ---- the group's activations as block integers, one stage per token ----
@@ -322,7 +326,10 @@ __global__ void __launch_bounds__(kGsThreads, 1) wgemv_small_kernel(const WgArgs
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
-bool wgemv_small_supports(int mode, const WgArgs &a) {
+// max_tiles: the most tiles the launch's table can hold; every pass of every tile must fit the kernel's list (two passes
+// per tile of up to kWgSmallTokens tokens, kGsBigPasses more when it takes the larger groups too) and its 12-bit tile index
+bool wgemv_small_supports(int mode, const WgArgs &a, int max_tiles) {
+  if (max_tiles > 4096 || 2 * max_tiles + kGsBigPasses > kGsMaxGroups) return false;
   if (mode != WG_I4_SWIGLU && mode != WG_I4_PLAIN) return false;
   if (a.identity_tiles || a.K % 256 || a.R % 16) return false;  // 16-byte scale copies: an even number of k-blocks per row
   return wgemv_small_smem_bytes(a.K) <= 200 * 1024;

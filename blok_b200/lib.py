@@ -452,7 +452,7 @@ class MoeEp:
 
 
 def lm_head_argmax(w, n):
-    """Greedy sampler (src/kimi_exec.cu:718-734): n bf16 [T<=8, hidden] -> token ids int32 [T] on the device."""
+    """Greedy sampler (src/kimi_exec.cu:718-734): n bf16 [T<=64, hidden] -> token ids int32 [T] on the device."""
     vocab, hidden = w.shape
     n2 = n.reshape(-1, hidden)
     T = n2.shape[0]

@@ -130,7 +130,9 @@ int blok_bf16_gemv(const blok_bf16_t *w, const blok_bf16_t *x, blok_bf16_t *y_bf
 size_t blok_bf16_mlp_workspace_bytes(int hidden, int ffn, int T);
 
 /* y[t] = W_d (SiLU(W_g x[t]) * W_u x[t]); replaces bf16_mlp (src/kimi_exec.cu:674-686)
- * without its running-sum side effect (the caller adds).  T <= 8. */
+ * without its running-sum side effect (the caller adds).  T <= 64; more than 8 rows
+ * need hidden and ffn to be multiples of 256 and stream each matrix once for all rows
+ * (the workspace then also holds the K-split partial sums of the down projection). */
 int blok_bf16_mlp(const blok_bf16_t *gate, const blok_bf16_t *up, const blok_bf16_t *down, const blok_bf16_t *x,
                   blok_bf16_t *y, int hidden, int ffn, int T, void *workspace, size_t workspace_bytes,
                   blok_stream_t stream);
@@ -489,7 +491,8 @@ size_t blok_lm_head_workspace_bytes(int vocab, int T);
 
 /* ids[t] = argmax_v bf16(sum_c W[v,c] n[t,c]), the lowest id winning ties.  Replaces
  * sample_lm_head / argmax_k (src/kimi_exec.cu:718-734, :477-493).  ids stay on the
- * device.  T <= 8. */
+ * device.  T <= 64; more than 8 rows need vocab % 16 == 0 and hidden % 256 == 0 and
+ * read the table once for all rows. */
 int blok_lm_head_argmax(const blok_bf16_t *w, const blok_bf16_t *n, int vocab, int hidden, int T, uint32_t *ids,
                         void *workspace, size_t workspace_bytes, blok_stream_t stream);
 
