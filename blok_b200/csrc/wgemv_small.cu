@@ -128,11 +128,18 @@ __device__ __forceinline__ void gs_stream(const GsStream &q, int lane, float (&a
       uint4 x01[CNT], x23[CNT];
       uint2 meta[CNT];
 #pragma unroll
-      for (int tok = 0; tok < CNT; ++tok) {
-        x01[tok] = gs_lds128(xk + tok * q.xbytes);
-        x23[tok] = gs_lds128(xk + tok * q.xbytes + 16);
-        meta[tok] = gs_lds64(mk + tok * q.xbytes);
+      for (int tok = 0; tok < CNT; ++tok) meta[tok] = gs_lds64(mk + tok * q.xbytes);
+      if (q.xstep) {  // the eight lanes that carry operands
+#pragma unroll
+        for (int tok = 0; tok < CNT; ++tok) {
+          x01[tok] = gs_lds128(xk + tok * q.xbytes);
+          x23[tok] = gs_lds128(xk + tok * q.xbytes + 16);
+        }
+      } else {
+#pragma unroll
+        for (int tok = 0; tok < CNT; ++tok) x01[tok] = x23[tok] = make_uint4(0, 0, 0, 0);
       }
+      __syncwarp();
       // the A operands of the k-block's four MMAs, unpacked once for all tokens
       const uint32_t wlw[4] = {wlv.x, wlv.y, wlv.z, wlv.w}, whw[4] = {whv.x, whv.y, whv.z, whv.w};
       uint32_t a0[4], a1[4], a2[4], a3[4];
