@@ -16,8 +16,9 @@
 // kernel took (WgArgs::small_max, ::small_limit) - unless they are so few (48 passes' worth) that the GEMM kernel would
 // spend a CTA's whole latency, about 100 us per product, on a handful of tiles: then this kernel takes every group.
 //
-// Measured at T = 64 (284 groups, 7.05 GB of expert weights): gate/up and down together 1.75 ms (4.0 TB/s); with a
-// run-time token loop and pointer arithmetic per access 2.07 ms (164 warp instructions per 1 KB ring step against 116).
+// Measured at T = 64 (284 groups, 7.05 GB of expert weights): gate/up and down together about 1.6 ms (4.4 TB/s); with
+// every lane loading a token's operands (24 of 32 read the zero block) 1.75 ms; with a run-time token loop and pointer
+// arithmetic per access 2.07 ms (164 warp instructions per 1 KB ring step against 116).
 // Six tokens per pass instead of four: slower (the larger stages cost more than the second pass of the few groups of
 // five or six).  The ring kept running across chunk boundaries (a second scale stage, the next chunk's scales riding
 // with its first weight request): no faster (1.95 ms against 1.93 ms per layer pass; the other fifteen warps of the SM
