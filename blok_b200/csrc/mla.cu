@@ -268,7 +268,7 @@ static int launch_head_gemv(const uint16_t *w, long w_head_stride, const uint16_
 
 static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
-constexpr int kMlaMaxBatch = 64;  // sequences (or tokens of a prefill chunk) per call; the mat-vecs take them 8 at a time
+constexpr int kMlaMaxBatch = 64;  // sequences (or tokens of a prefill chunk) per call: what one pass of the weight-streaming kernel covers
 
 }  // namespace blok
 
@@ -570,8 +570,8 @@ static int project(blok_mla_layer *L, const uint16_t *w, const uint16_t *x, uint
 }
 
 // The attention block for B entries (sequences, or the tokens of a prefill chunk): projections, cache append,
-// attention, output projection.  The mat-vec kernels take up to 8 tokens per launch, so larger B goes through them
-// in groups of 8 (the weights of a later group come from L2 where they fit).
+// attention, output projection.  Up to 8 entries: the split-K mat-vec kernels; 9..64: one pass of the weight-streaming
+// kernel per projection (project()); the per-head products take every group of 8 entries in one launch.
 static int decode_body(blok_mla_layer *L, const uint16_t *n, const CacheRef &c, const int *ctx_len, int B, uint16_t *out,
                        blok_stream_t stream_) {
   const blok_mla_weights &w = L->w;
