@@ -39,9 +39,11 @@ struct WgArgs {
   size_t splitk_bytes = 0;
 };
 
-// Dispatches to the tcgen05 kernels (wgemm_tc.cu) when they cover the mode and shape and the launch has enough rows
-// of x for the tensor cores to matter (INT4: 256 assignments, bf16: 640 tokens), else to the mma.sync kernel,
-// which streams the weights better at small counts.  BLOK_WGEMM_IMPL=mma / =tc in the environment forces one.
+// Picks the kernels of a launch.  INT4 modes: the small-group kernel first (wgemv_small.cu), then for what it left the
+// tcgen05 kernel (wgemm_tc.cu) from 256 assignments on, below that the mma.sync kernel.  bf16 modes: up to
+// kWgStreamTokens rows of a dense product the weight-streaming kernel (wgemm_stream.cu); from 640 tokens on the tcgen05
+// kernel; in between, and for shapes the others do not cover, the mma.sync kernel with its K-split.
+// BLOK_WGEMM_IMPL=mma / =tc in the environment forces one GEMM kernel for every row (no small-group or streaming kernel).
 int launch_wgemm(int mode, const WgArgs &args, int max_tiles, cudaStream_t stream);
 
 // A bf16 product over few tiles of tokens has (R / 128 or R / 64) x tiles CTAs, far fewer than the GPU has SMs (3 per
@@ -55,8 +57,8 @@ size_t wgemm_splitk_bytes(int mode, int K, int R, int max_rows);
 // Fills the tile arrays with consecutive 64-row tiles of T rows (one group, expert 0): a dense layer.
 int launch_identity_tiles(int T, int *tile_expert, int *tile_start, int *tile_count, int *num_tiles, cudaStream_t stream);
 
-// The INT4 modes for groups of up to kWgSmallTokens tokens: streams the weights like the batch-1 decode kernel and
-// leaves the larger groups alone.  launch_wgemm runs it in front of the kernel that takes the rest
+// The INT4 modes for groups of up to kWgSmallTokens tokens (every group when the larger ones are few, see
+// WgArgs::small_limit): streams the weights like the batch-1 decode kernel and leaves the other groups alone.  launch_wgemm runs it in front of the kernel that takes the rest
 // (BLOK_WGEMM_SMALL=0 in the environment: every group through the GEMM kernels).
 bool wgemv_small_supports(int mode, const WgArgs &args, int max_tiles);
 int launch_wgemv_small(int mode, const WgArgs &args, cudaStream_t stream);
