@@ -21,7 +21,8 @@ def _oracle_layer(oracle, w, x, ids_needed, topk=8):
 # up to four tokens through the mat-vec-style kernel (wgemv_small.cu) and the rest through the kernel the size picks
 @pytest.mark.parametrize("impl", ["mma", "tc", "auto"])
 @pytest.mark.parametrize("T,hidden,inter,experts,shared,seed", [(40, 1024, 512, 128, 512, 31), (1, 1024, 512, 128, 512, 32),
-                                                                (64, 7168, 2048, 384, 2048, 2), (130, 512, 512, 128, 0, 33)])
+                                                                (64, 7168, 2048, 384, 2048, 2), (130, 512, 512, 128, 0, 33),
+                                                                (7, 1024, 512, 128, 512, 34)])
 def test_moe_batched_vs_oracle(cuda, oracle, monkeypatch, impl, T, hidden, inter, experts, shared, seed):
     from blok_b200 import lib, synth
     if impl == "auto":
@@ -102,9 +103,11 @@ def test_moe_batched_2048_tokens_against_the_oracle(cuda, oracle):
     layer.close()
 
 
-@pytest.mark.parametrize("impl", ["mma", "tc"])
+@pytest.mark.parametrize("impl", ["mma", "tc", "auto"])
 def test_experts_grouped_handles_empty_and_ragged_groups(cuda, oracle, monkeypatch, impl):
-    """Assignments concentrated on few experts (others get zero tokens), more than one 64-token tile for one expert."""
+    """Assignments concentrated on few experts (others get zero tokens), more than one 64-token tile for one expert.
+    Left to itself ("auto") the library sends all of them through the small-group kernel: the larger groups are few, so
+    it takes the 64-token tile (sixteen passes of four tokens) and the group of nine as well."""
     from blok_b200 import lib, synth
     monkeypatch.setenv("BLOK_WGEMM_IMPL", impl)
     hidden, inter, experts = 512, 512, 128
